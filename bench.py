@@ -1,0 +1,229 @@
+"""Flagship benchmark: Qwen2.5-VL-7B full-parameter finetune step, ZeRO-3 (FSDP2 semantics), bf16.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+Per GPU: one packed micro-batch of 8192 tokens (4 samples x 2048 tokens, each with two 448x448 images =
+2 x 256 visual tokens), activation checkpointing per layer, AdamW (lr 1e-5, wd 0, no clipping: the
+reference's FSDP2 recipe, examples/qwen2.5vl/finetune_qwen2_5_vl_72b_fsdp.sh), synthetic data,
+random-init weights.  Weak scaling: the global batch is N packs.
+
+Two timed regions of K steps each, both bracketed by barrier + synchronize and timed with CUDA events
+(max over ranks):
+  * ``value``  - inputs already on the device (kernel-only number)
+  * ``e2e``    - every step copies its inputs from pinned host memory and reads the loss back to the host,
+                 through the public ``TrainEngine.train_step`` API.
+Weights + optimizer state (> 100 GB) are far larger than L2, so no explicit L2 flush is needed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BASELINE_TOKENS_PER_CARD = 11042.0  # Qwen2.5-VL-7B finetune, mcore TP=1, tokens/s per 910B2 card (published)
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of this rank's GPU through NVML (read-only) every 200 ms."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:  # noqa: BLE001
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+        }
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                    nv.nvmlDeviceGetCurrentClocksThrottleReasons
+                mask = fn(self.h)
+                for bit, nm in names.items():
+                    if mask & bit:
+                        self.reasons.add(nm)
+            except Exception:  # noqa: BLE001
+                pass
+            self._stop_evt.wait(0.2)
+
+    def stop(self):
+        self._stop_evt.set()
+        if self.ok:
+            self.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def run_reference(args):
+    """The reference arm: the unmodified reference from baseline/_ref through its own public entry point."""
+    why = None
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "mindspeed_mm")):
+        why = "reference not installed under baseline/_ref (offline pip install did not produce the package)"
+    else:
+        sys.path.insert(0, ref_dir)
+        os.environ.setdefault("NON_MEGATRON", "true")
+        try:
+            import importlib
+            importlib.import_module("mindspeed_mm.fsdp.train.trainer")
+        except Exception as e:  # noqa: BLE001
+            why = ("reference trainer cannot be imported unmodified on this image: "
+                   f"{type(e).__name__}: {str(e).splitlines()[0][:160]}")
+        if why is None:
+            why = ("reference native-FSDP path refuses torch versions other than 2.7.1/2.9.0 "
+                   "(fsdp/ops/fully_shard/fully_shard.py:840-847); image has torch " + torch.__version__)
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+    return 0
+
+
+def make_batches(cfg, n_batches, seq_len, samples_per_pack, images_per_sample, image_size, rank, pin):
+    from mindspeed_mm_b200.data.collate import PackedVLMCollator
+    from mindspeed_mm_b200.data.synthetic import SyntheticVLMDataset, SyntheticVLMSpec
+    per = seq_len // samples_per_pack
+    ds = SyntheticVLMDataset(SyntheticVLMSpec(
+        seq_len=per, images_per_sample=images_per_sample, image_size=image_size, vocab_size=cfg.text.vocab_size,
+        image_token_id=cfg.image_token_id, vision_start_token_id=cfg.vision_start_token_id, seed=1234 + rank,
+        pixel_dtype=torch.bfloat16))
+    col = PackedVLMCollator(cfg.image_token_id, cfg.vision_start_token_id, merge=cfg.vision.spatial_merge_size,
+                            patch=cfg.vision.patch_size, window_size=cfg.vision.window_size,
+                            vit_head_dim=cfg.vision.hidden_size // cfg.vision.num_heads,
+                            pixel_dtype=torch.bfloat16, pin=pin)
+    return [col([ds[b * samples_per_pack + i] for i in range(samples_per_pack)]) for b in range(n_batches)]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "library", "reference"])
+    ap.add_argument("--model", default="qwen2_5_vl_7b", choices=["qwen2_5_vl_7b", "tiny"])
+    ap.add_argument("--seq-len", type=int, default=8192)
+    ap.add_argument("--comm", default="auto", choices=["auto", "p2p", "nccl"])
+    ap.add_argument("--layers", type=int, default=0, help="debug only: override decoder depth (invalidates the number)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    from mindspeed_mm_b200 import ops
+    from mindspeed_mm_b200.api import VLMTrainerSpec, build_vlm_trainer
+    from mindspeed_mm_b200.data.collate import batch_nbytes, to_device
+    from mindspeed_mm_b200.models.qwen2_5_vl import Qwen25VLConfig
+    from mindspeed_mm_b200.ops import native
+
+    ops.set_tier("native" if args.impl == "native" else "library")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    cfg = Qwen25VLConfig.qwen2_5_vl_7b() if args.model == "qwen2_5_vl_7b" else Qwen25VLConfig.tiny()
+    if args.layers:
+        cfg.text.num_layers = args.layers
+    small = args.model == "tiny"
+    spec = VLMTrainerSpec(model=cfg, lr=1e-5, weight_decay=0.0, clip_grad=0.0, train_iters=10000,
+                          comm="auto" if args.comm == "auto" else args.comm, log_interval=0)
+    trainer = build_vlm_trainer(spec)
+    dev = trainer.device
+    seq = args.seq_len if not small else 1024
+    host_batches = make_batches(cfg, 4, seq, 4 if not small else 1, 2, 448 if not small else 224, rank, pin=True)
+    dev_batches = [to_device(b, dev) for b in host_batches]
+    tokens_per_step = host_batches[0]["n_tokens"] * world
+    h2d = batch_nbytes(host_batches[0])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def region(batches, steps, e2e):
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = native.LAUNCHES
+        s.record()
+        last = None
+        for i in range(steps):
+            r = trainer.train_step([batches[i % len(batches)]])
+            if e2e:
+                last = float(r["loss"])        # device -> host read of the step's result
+        e.record()
+        barrier()
+        ms = torch.tensor([s.elapsed_time(e)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms) / steps, native.LAUNCHES - l0, last
+
+    # warm-up (untimed), both paths
+    region(dev_batches, max(args.warmup, 3) - 1, False)
+    region(host_batches, 1, True)
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms_dev, launches, _ = region(dev_batches, args.steps, False)
+    ms_e2e, _, loss = region(host_batches, args.steps, True)
+    clocks = sampler.stop()
+    native.check_status() if args.impl == "native" else None
+
+    if rank == 0:
+        value = tokens_per_step / (ms_dev / 1e3)
+        e2e = tokens_per_step / (ms_e2e / 1e3)
+        out = {
+            "metric": "Qwen2.5-VL-7B FSDP2 tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_dev, 2),
+            "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": round(value / (BASELINE_TOKENS_PER_CARD * world), 3), "dtype": "bf16",
+            "data": "synthetic (random-init weights, random text ids, U[0,1] images CLIP-normalised)",
+            "impl": args.impl,
+            "config": {"model": "Qwen2.5-VL-7B" if not small else "tiny", "global_batch": world,
+                       "seq_len": seq, "parallelism": f"fsdp{world}" if world > 1 else "single",
+                       "tokens_per_gpu": host_batches[0]["n_tokens"], "images_per_gpu": 8 if not small else 2,
+                       "recompute": "full per layer", "optimizer": "AdamW fp32 master+moments, fused into backward",
+                       "trainable": "all parameters (ViT + merger + LLM)",
+                       "l2": "inputs_larger_than_L2 (weights+optimizer state >100 GB are streamed every step)",
+                       "baseline_note": "vs_baseline = value / (11042 tokens/s/card x n_gpus), the reference's "
+                                        "published mcore TP=1 figure on 8x910B2; no FSDP2 number is published",
+                       "comm": getattr(trainer.engine, "_p2p", None) is not None and "p2p-fused" or "nccl"},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 2),
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": loss},
+            "gpu_launches": launches,
+            "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

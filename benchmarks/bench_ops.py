@@ -1,0 +1,131 @@
+"""Per-kernel timing on one GPU: CUDA events, >=3 warm-ups, L2 flushed between timed iterations.
+
+    python benchmarks/bench_ops.py [--ops gemm,rmsnorm,...] [--out FILE] [--small]
+
+Prints one JSON line per case: achieved TFLOP/s or GB/s and the fraction of the measured peaks in
+MEASURED_PEAKS.json (fallback 1590 TFLOP/s / 6650 GB/s when the file is absent).  ``--small`` keeps
+inputs just above L2 size so that a profiler capture of the same command stays short.
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from mindspeed_mm_b200 import ops  # noqa: E402
+from mindspeed_mm_b200.ops import native  # noqa: E402
+
+
+def peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["bf16_tflops"], d["hbm_gbs"], "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+_flush = None
+
+
+def time_fn(fn, iters=10, warmup=3):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        _flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def emit(rec, out):
+    line = json.dumps(rec)
+    print(line, flush=True)
+    if out:
+        with open(out, "a") as f:
+            f.write(line + "\n")
+
+
+def bench_gemm(out, small):
+    tf, _, src = peaks()
+    shapes = [("qkv", 8192, 4608, 3584), ("o", 8192, 3584, 3584), ("gate_up", 8192, 37888, 3584),
+              ("down", 8192, 3584, 18944), ("square", 8192, 8192, 8192), ("vit_qkv", 8192, 3840, 1280)]
+    if small:
+        shapes = [("qkv", 8192, 4608, 3584)]
+    for name, M, N, K in shapes:
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+        bt = b.t().contiguous()
+        at = a.t().contiguous()
+        flops = 2.0 * M * N * K
+        cases = [("nt", lambda: native.gemm_nt(a, b), lambda: a @ b.t()),
+                 ("nn", lambda: native.gemm_nn(a, bt), lambda: a @ bt),
+                 ("tn", lambda: native.gemm_tn(at, bt), lambda: at.t() @ bt)]
+        for lay, mine, lib in cases:
+            t = time_fn(mine)
+            tl = time_fn(lib)
+            emit(dict(op="gemm_bf16", case=name, layout=lay, M=M, N=N, K=K, ms=round(t, 4),
+                      tflops=round(flops / t / 1e9, 1), frac_of_peak=round(flops / t / 1e9 / tf, 3), peak=src,
+                      cublas_ms=round(tl, 4), cublas_tflops=round(flops / tl / 1e9, 1),
+                      vs_cublas=round(tl / t, 3)), out)
+        native.check_status()
+
+
+def bench_elementwise(out, small):
+    _, bw, src = peaks()
+    T = 8192 if small else 32768
+    H = 3584
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    dy = torch.randn_like(x)
+
+    def rec(name, fn, nbytes, base=None):
+        t = time_fn(fn)
+        r = dict(op=name, T=T, H=H, ms=round(t, 4), gbs=round(nbytes / t / 1e6, 1),
+                 frac_of_peak=round(nbytes / t / 1e6 / bw, 3), peak=src)
+        if base is not None:
+            tb = time_fn(base)
+            r.update(torch_ms=round(tb, 4), vs_torch=round(tb / t, 2))
+        emit(r, out)
+
+    ops.set_tier("native")
+    rec("rmsnorm_fwd", lambda: ops.rms_norm(x, w, 1e-6), 2 * x.numel() * 2,
+        lambda: torch.nn.functional.rms_norm(x, (H,), w, 1e-6))
+    xg = x.clone().requires_grad_()
+    wg = w.clone().requires_grad_()
+    y = ops.rms_norm(xg, wg, 1e-6)
+    rec("rmsnorm_bwd", lambda: torch.autograd.grad(y, (xg, wg), dy, retain_graph=True), 3 * x.numel() * 2)
+    F = 18944
+    gu = torch.randn(T // 4, 2 * F, device="cuda", dtype=torch.bfloat16)
+    rec("swiglu_fwd", lambda: ops.swiglu(gu), gu.numel() * 2 * 1.5,
+        lambda: torch.nn.functional.silu(gu[:, :F]) * gu[:, F:])
+    n = 256 << 20 if not small else 32 << 20
+    p, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
+    g = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    rec("adamw_shard", lambda: native.adamw_shard(p, m, v, g, p16, 1e-4, 0.9, 0.999, 1e-8, 0.0, 1, n, 1.0), n * 28.0)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ops", default="gemm,elementwise")
+    ap.add_argument("--out", default="")
+    ap.add_argument("--small", action="store_true")
+    a = ap.parse_args()
+    for op in a.ops.split(","):
+        {"gemm": bench_gemm, "elementwise": bench_elementwise}[op](a.out, a.small)
+
+
+if __name__ == "__main__":
+    main()

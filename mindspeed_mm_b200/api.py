@@ -1,0 +1,116 @@
+"""Public, programmatic entry points (what ``bench.py`` and user scripts call).
+
+``build_vlm_trainer`` assembles the pieces the YAML-driven ``Trainer`` assembles from a config file:
+process group + parallel state, the model on the meta device, the sharding engine (which owns the
+optimizer), loss, LR schedule and the ``TrainEngine`` loop.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .models.qwen2_5_vl import Qwen25VLConfig, Qwen25VLModel
+from .parallel.fsdp import FSDPEngine, OptimConfig
+from .parallel.state import get_parallel_state, init_parallel_state
+from .runtime.loss import build_loss
+from .runtime.lr_scheduler import LRSchedule
+from .runtime.train_engine import TrainConfig, TrainEngine
+
+
+def init_distributed(device: Optional[str] = None, timeout_s: int = 600):
+    """One process per GPU; reads RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* from the environment."""
+    import datetime
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if device is None:
+        device = "cuda" if torch.cuda.is_available() else "cpu"
+    if device == "cuda":
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+    else:
+        dev = torch.device("cpu")
+    if world > 1 and not dist.is_initialized():
+        backend = "nccl" if dev.type == "cuda" else "gloo"
+        kw = dict(device_id=dev) if dev.type == "cuda" else {}
+        dist.init_process_group(backend=backend, timeout=datetime.timedelta(seconds=timeout_s), **kw)
+    return dev, (dist.get_rank() if dist.is_initialized() else 0), world
+
+
+def default_init_fn(std: float = 0.02, seed: int = 0):
+    """Random init executed on the unit's device: N(0, std) for matrices, 1 for norm weights, 0 for biases.
+    Seeded per unit name so every rank (and every world size) draws the same full tensor."""
+    def init(name: str, module: nn.Module):
+        for n, p in module.named_parameters():
+            g = torch.Generator(device=p.device).manual_seed((hash((name, n)) & 0x7FFFFFFF) ^ seed)
+            if p.dim() >= 2:
+                p.data.normal_(0.0, std, generator=g)
+            elif n.endswith("bias"):
+                p.data.zero_()
+            else:
+                p.data.fill_(1.0)
+    return init
+
+
+@dataclass
+class VLMTrainerSpec:
+    model: Qwen25VLConfig
+    lr: float = 1e-5
+    weight_decay: float = 0.0
+    clip_grad: float = 0.0
+    train_iters: int = 10000
+    lr_decay_style: str = "cosine"
+    lr_warmup_ratio: float = 0.1
+    micro_batch_size: int = 1
+    gradient_accumulation_steps: int = 1
+    param_dtype: torch.dtype = torch.bfloat16
+    reduce_dtype: torch.dtype = torch.float32
+    recompute: bool = True
+    loss_type: str = "default"
+    seed: int = 0
+    comm: str = "auto"
+    freeze_vision: bool = False
+    log_interval: int = 1
+
+
+def build_vlm_trainer(spec: VLMTrainerSpec, device=None, data_iter=None, checkpointer=None) -> TrainEngine:
+    dev, rank, world = init_distributed(None if device is None else str(device).split(":")[0])
+    ps = init_parallel_state(world_size=world, device_type=dev.type)
+    with torch.device("meta"):
+        model = Qwen25VLModel(spec.model)
+    if spec.freeze_vision:
+        for p in model.visual.parameters():
+            p.requires_grad_(False)
+    opt = OptimConfig(lr=spec.lr, weight_decay=spec.weight_decay, clip_grad=spec.clip_grad)
+    engine = FSDPEngine(model.fsdp_units(), group=ps.get_fsdp_group() if world > 1 else False, device=dev,
+                        param_dtype=spec.param_dtype, reduce_dtype=spec.reduce_dtype, opt=opt,
+                        recompute=spec.recompute, grad_accum_steps=spec.gradient_accumulation_steps, comm=spec.comm)
+    # python's hash() of str is salted per process: use a stable digest instead
+    engine.materialize(stable_init_fn(spec.model.init_std, spec.seed))
+    sched = LRSchedule(lr=spec.lr, train_iters=spec.train_iters, lr_decay_style=spec.lr_decay_style,
+                       lr_warmup_ratio=spec.lr_warmup_ratio)
+    loss_fn = build_loss(spec.loss_type, ps.group("dp"), ps.get_dp_world_size())
+    cfg = TrainConfig(train_iters=spec.train_iters, micro_batch_size=spec.micro_batch_size,
+                      gradient_accumulation_steps=spec.gradient_accumulation_steps, log_interval=spec.log_interval)
+    return TrainEngine(model, engine, loss_fn, sched, cfg, data_iter=data_iter, checkpointer=checkpointer,
+                       dp_group=ps.group("dp"), dp_world=ps.get_dp_world_size(), device=dev)
+
+
+def stable_init_fn(std: float = 0.02, seed: int = 0):
+    import zlib
+
+    def init(name: str, module: nn.Module):
+        for n, p in module.named_parameters():
+            s = (zlib.crc32(f"{name}.{n}".encode()) ^ seed) & 0x7FFFFFFF
+            if p.dim() >= 2:
+                g = torch.Generator(device=p.device).manual_seed(s)
+                p.data.normal_(0.0, std, generator=g)
+            elif n.endswith("bias"):
+                p.data.zero_()
+            else:
+                p.data.fill_(1.0)
+    return init

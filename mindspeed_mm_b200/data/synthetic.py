@@ -1,0 +1,119 @@
+"""Synthetic datasets of the benchmark shapes (no network, no files).
+
+The reference ships a mock-data generator for VLMs
+(mindspeed_mm/fsdp/tools/data_tool/generate_mock_data_for_vlmodel.py) that writes images and a
+JSON to disk; here the samples are produced in memory, already in the form the collators emit:
+token ids with image placeholders, CLIP-normalised patches flattened the way the HF image
+processor does it, labels with the image tokens masked, and the (t, h, w) grid per image.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+from torch.utils.data import Dataset
+
+from .registry import data_register
+
+CLIP_MEAN = (0.48145466, 0.4578275, 0.40821073)
+CLIP_STD = (0.26862954, 0.26130258, 0.27577711)
+
+
+def patchify_image(img: torch.Tensor, patch: int = 14, temporal: int = 2, merge: int = 2) -> torch.Tensor:
+    """[3, H, W] in [0,1] -> [H/p * W/p, 3*temporal*p*p] patches in 2x2-merge order (HF Qwen2-VL layout)."""
+    C, H, W = img.shape
+    mean = torch.tensor(CLIP_MEAN).view(3, 1, 1)
+    std = torch.tensor(CLIP_STD).view(3, 1, 1)
+    x = ((img - mean) / std).unsqueeze(0).repeat(temporal, 1, 1, 1)          # [tp, C, H, W]
+    gh, gw = H // patch, W // patch
+    x = x.view(1, temporal, C, gh // merge, merge, patch, gw // merge, merge, patch)
+    x = x.permute(0, 3, 6, 4, 7, 2, 1, 5, 8)                                  # gt, gh/m, gw/m, m, m, C, tp, p, p
+    return x.reshape(gh * gw, C * temporal * patch * patch)
+
+
+@dataclass
+class SyntheticVLMSpec:
+    seq_len: int = 1024             # tokens per sample (text + image placeholders)
+    images_per_sample: int = 2
+    image_size: int = 224
+    vocab_size: int = 32000
+    image_token_id: int = 31999
+    vision_start_token_id: int = 31997
+    patch: int = 14
+    temporal_patch: int = 2
+    merge: int = 2
+    num_samples: int = 1 << 30
+    seed: int = 0
+    pixel_dtype: torch.dtype = torch.float32
+
+
+@data_register.register("synthetic_vlm")
+class SyntheticVLMDataset(Dataset):
+    """Deterministic random VLM samples: item i depends only on (seed, i)."""
+
+    def __init__(self, spec: SyntheticVLMSpec):
+        self.spec = spec
+        g = spec.image_size // spec.patch
+        self.grid = (1, g, g)
+        self.vis_tokens = g * g // (spec.merge ** 2)
+        need = spec.images_per_sample * (self.vis_tokens + 1)
+        if need >= spec.seq_len:
+            raise ValueError(f"seq_len {spec.seq_len} cannot hold {spec.images_per_sample} images ({need} tokens)")
+
+    def __len__(self):
+        return self.spec.num_samples
+
+    def __getitem__(self, i: int) -> Dict[str, torch.Tensor]:
+        s = self.spec
+        g = torch.Generator().manual_seed(s.seed * 1_000_003 + i)
+        n_text = s.seq_len - s.images_per_sample * (self.vis_tokens + 1)
+        # reserve the special ids at the top of the vocabulary for the placeholders
+        text = torch.randint(0, min(s.vocab_size, s.vision_start_token_id) - 1, (n_text,), generator=g)
+        cuts = sorted(torch.randint(0, n_text + 1, (s.images_per_sample,), generator=g).tolist())
+        pieces, prev = [], 0
+        img_block = torch.cat([torch.tensor([s.vision_start_token_id]),
+                               torch.full((self.vis_tokens,), s.image_token_id)])
+        for c in cuts:
+            pieces += [text[prev:c], img_block]
+            prev = c
+        pieces.append(text[prev:])
+        ids = torch.cat(pieces)
+        labels = ids.clone()
+        labels[(ids == s.image_token_id) | (ids == s.vision_start_token_id)] = -100
+        imgs = torch.rand(s.images_per_sample, 3, s.image_size, s.image_size, generator=g)
+        pix = torch.cat([patchify_image(im, s.patch, s.temporal_patch, s.merge) for im in imgs]).to(s.pixel_dtype)
+        grid = torch.tensor([self.grid] * s.images_per_sample, dtype=torch.long)
+        return dict(input_ids=ids, labels=labels, pixel_values=pix, image_grid_thw=grid)
+
+
+@dataclass
+class SyntheticVideoLatentSpec:
+    """Pre-extracted features for DiT training (the reference's ``load_video_features`` mode,
+    mindspeed_mm/data/datasets/feature_dataset.py:29)."""
+    channels: int = 16
+    frames: int = 21
+    height: int = 90
+    width: int = 160
+    text_len: int = 512
+    text_dim: int = 4096
+    num_samples: int = 1 << 30
+    seed: int = 0
+    dtype: torch.dtype = torch.float32
+
+
+@data_register.register("synthetic_video_latents")
+class SyntheticVideoLatentDataset(Dataset):
+    def __init__(self, spec: SyntheticVideoLatentSpec):
+        self.spec = spec
+
+    def __len__(self):
+        return self.spec.num_samples
+
+    def __getitem__(self, i):
+        s = self.spec
+        g = torch.Generator().manual_seed(s.seed * 1_000_003 + i)
+        return dict(
+            latents=torch.randn(s.channels, s.frames, s.height, s.width, generator=g).to(s.dtype),
+            prompt=torch.randn(s.text_len, s.text_dim, generator=g).to(s.dtype),
+            prompt_mask=torch.ones(s.text_len, dtype=torch.bool))

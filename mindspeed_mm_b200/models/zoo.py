@@ -1,0 +1,2 @@
+"""Imports every built-in model file so that its ``@model_register`` decorators run."""
+from . import qwen2_5_vl  # noqa: F401

@@ -1,0 +1,245 @@
+"""Hot-op front end.
+
+Every model in the package calls the functions below, never ``torch.nn.functional``
+directly, so that one switch decides what executes:
+
+* CPU tensors           -> :mod:`.reference` (plain fp32 PyTorch; what the gloo tests run)
+* CUDA tensors, ``native``  tier -> hand-written sm_100a kernels from ``csrc/`` (:mod:`.native`)
+* CUDA tensors, ``library`` tier -> cuBLAS / flash-attn / torch eager.  This is the
+  "NCCL + cuBLAS" baseline tier the native kernels are measured against.
+
+The tier is process-global (``set_tier``) and defaults to ``native`` on a GPU.  On a GPU
+box the native tier refuses to run if the compiled extension is missing, so a silent
+fallback cannot pass for the product.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import reference as ref
+
+_TIER = os.environ.get("MM_B200_TIER", "native")
+
+
+def set_tier(tier: str) -> None:
+    global _TIER
+    if tier not in ("native", "library"):
+        raise ValueError(f"unknown op tier {tier!r}")
+    _TIER = tier
+
+
+def get_tier() -> str:
+    return _TIER
+
+
+def _native(x: torch.Tensor) -> bool:
+    return x.is_cuda and _TIER == "native"
+
+
+def _nat():
+    from . import native
+    return native
+
+
+# --------------------------------------------------------------------------- norms / elementwise
+def rms_norm(x, weight, eps: float = 1e-6):
+    if _native(x) and x.dtype == torch.bfloat16:
+        return _nat().rms_norm(x, weight, eps)
+    return ref.rms_norm(x, weight, eps)
+
+
+def layer_norm(x, weight=None, bias=None, eps: float = 1e-6):
+    return ref.layer_norm(x, weight, bias, eps)
+
+
+def layer_norm_modulate(x, scale, shift, eps: float = 1e-6):
+    if _native(x) and x.dtype == torch.bfloat16:
+        return _nat().layer_norm_modulate(x, scale, shift, eps)
+    return ref.layer_norm_modulate(x, scale, shift, eps)
+
+
+def gated_residual(x, y, gate):
+    if _native(x) and x.dtype == torch.bfloat16:
+        return _nat().gated_residual(x, y, gate)
+    return ref.gated_residual(x, y, gate)
+
+
+def swiglu(gate_up, clamp: Optional[float] = None):
+    if _native(gate_up) and gate_up.dtype == torch.bfloat16 and clamp is None:
+        return _nat().swiglu(gate_up)
+    return ref.swiglu(gate_up, clamp)
+
+
+def gelu_tanh(x):
+    return F.gelu(x, approximate="tanh")
+
+
+def rope_rotate_half(x, cos, sin):
+    if _native(x) and x.dtype == torch.bfloat16:
+        return _nat().rope(x, cos, sin, interleaved=False)
+    return ref.rope_rotate_half(x, cos, sin)
+
+
+def rope_interleaved(x, cos, sin):
+    if _native(x) and x.dtype == torch.bfloat16:
+        return _nat().rope(x, cos, sin, interleaved=True)
+    return ref.rope_interleaved(x, cos, sin)
+
+
+l2_norm = ref.l2_norm
+gated_rms_norm = ref.gated_rms_norm
+
+
+# --------------------------------------------------------------------------- GEMM
+def linear(x, weight, bias=None):
+    """``x @ weight.T + bias`` (weight is [out, in], K-major for both operands)."""
+    if _native(x) and x.dtype == torch.bfloat16 and _nat().gemm_supported(x, weight):
+        return _nat().linear(x, weight, bias)
+    return F.linear(x, weight, bias)
+
+
+def linear_swiglu(x, weight_gate_up):
+    """``swiglu(x @ W_gate_up.T)`` with the activation folded into the GEMM epilogue on the native tier."""
+    return swiglu(linear(x, weight_gate_up))
+
+
+# --------------------------------------------------------------------------- attention
+def attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max_seqlen_k: int,
+                     causal: bool = False, softmax_scale: Optional[float] = None):
+    """Packed attention.  q: [T, Nq, D]; k, v: [T, Nkv, D]; cu_seqlens int32 on the same device."""
+    if q.is_cuda:
+        if _TIER == "native" and _nat().fmha_supported(q, k, v):
+            return _nat().attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+                                           causal, softmax_scale)
+        return _library_attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+                                         causal, softmax_scale)
+    return ref.attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, causal, softmax_scale)
+
+
+def _library_attention_varlen(q, k, v, cu_q, cu_k, max_q, max_k, causal, scale):
+    from flash_attn import flash_attn_varlen_func
+    D = q.shape[-1]
+    pad = (-D) % 8
+    if pad:  # flash-attn wants head_dim % 8 == 0 (ViT D=80 is fine; guard anyway)
+        q, k, v = (F.pad(t, (0, pad)) for t in (q, k, v))
+        scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    out = flash_attn_varlen_func(q, k, v, cu_q, cu_k, max_q, max_k, softmax_scale=scale, causal=causal)
+    return out[..., :D] if pad else out
+
+
+def attention_dense(q, k, v, causal: bool = False, softmax_scale: Optional[float] = None):
+    """BSND attention (DiT).  q: [B, S, N, D]."""
+    if q.is_cuda:
+        B, Sq, N, D = q.shape
+        Sk = k.shape[1]
+        cq = torch.arange(0, (B + 1) * Sq, Sq, dtype=torch.int32, device=q.device)
+        ck = torch.arange(0, (B + 1) * Sk, Sk, dtype=torch.int32, device=q.device)
+        o = attention_varlen(q.reshape(B * Sq, N, D), k.reshape(B * Sk, -1, D), v.reshape(B * Sk, -1, D),
+                             cq, ck, Sq, Sk, causal, softmax_scale)
+        return o.view(B, Sq, N, D)
+    return ref.attention_dense(q, k, v, causal, softmax_scale)
+
+
+# --------------------------------------------------------------------------- loss
+def linear_cross_entropy(h, weight, labels, ignore_index: int = -100, chunk: int = 2048):
+    """Sum of token CE of ``h @ weight.T`` against ``labels`` without keeping [T, V] logits.
+
+    Returns (loss_sum fp32 scalar, n_valid).  The library/CPU tier computes the loss and both
+    gradients chunk by chunk inside forward (the reference does the same with
+    ``torch.func.grad_and_value``: fsdp/features/memory/chunkloss/chunkloss.py:6-95).
+    """
+    if _native(h) and h.dtype == torch.bfloat16 and _nat().lce_supported(h, weight):
+        return _nat().linear_cross_entropy(h, weight, labels, ignore_index)
+    return _ChunkedLinearCE.apply(h, weight, labels, ignore_index, chunk), (labels != ignore_index).sum()
+
+
+class _ChunkedLinearCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, weight, labels, ignore_index, chunk):
+        T = h.shape[0]
+        dh = torch.empty_like(h)
+        dw = torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
+        loss = torch.zeros((), dtype=torch.float32, device=h.device)
+        for s in range(0, T, chunk):
+            hs = h[s:s + chunk]
+            logits = (hs @ weight.t()).float()
+            lab = labels[s:s + chunk]
+            lse = torch.logsumexp(logits, -1)
+            valid = lab != ignore_index
+            safe = lab.clamp(min=0)
+            tgt = logits.gather(1, safe[:, None]).squeeze(1)
+            loss += ((lse - tgt) * valid).sum()
+            p = torch.exp(logits - lse[:, None])
+            p.scatter_add_(1, safe[:, None], -torch.ones_like(p[:, :1]))
+            p *= valid[:, None]
+            p = p.to(h.dtype)
+            dh[s:s + chunk] = p @ weight
+            dw += (p.t() @ hs).float()
+        ctx.save_for_backward(dh, dw.to(weight.dtype))
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        dh, dw = ctx.saved_tensors
+        return dh * g.to(dh.dtype), dw * g.to(dw.dtype), None, None, None
+
+
+# --------------------------------------------------------------------------- MoE
+def grouped_gemm(x, w, counts):
+    if _native(x) and x.dtype == torch.bfloat16 and _nat().grouped_gemm_supported(x, w):
+        return _nat().grouped_gemm(x, w, counts)
+    return _GroupedGemmLoop.apply(x, w, counts)
+
+
+class _GroupedGemmLoop(torch.autograd.Function):
+    """Loop-of-matmuls grouped GEMM with explicit dgrad / wgrad (fsdp/ops/moe_ops/gemm.py:35-92)."""
+
+    @staticmethod
+    def forward(ctx, x, w, counts):
+        ctx.save_for_backward(x, w)
+        ctx.counts = [int(c) for c in counts]
+        out = x.new_empty(x.shape[0], w.shape[-1])
+        s = 0
+        for e, c in enumerate(ctx.counts):
+            if c:
+                torch.matmul(x[s:s + c], w[e], out=out[s:s + c])
+            s += c
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w = ctx.saved_tensors
+        dx = torch.empty_like(x)
+        dw = torch.zeros_like(w)
+        s = 0
+        for e, c in enumerate(ctx.counts):
+            if c:
+                dx[s:s + c] = g[s:s + c] @ w[e].t()
+                dw[e] = x[s:s + c].t() @ g[s:s + c]
+            s += c
+        return dx, dw, None
+
+
+moe_permute = ref.moe_permute
+moe_unpermute = ref.moe_unpermute
+
+# --------------------------------------------------------------------------- GDN
+def causal_conv1d(x, weight, bias=None, activation="silu", cu_seqlens=None):
+    return ref.causal_conv1d(x, weight, bias, activation, cu_seqlens)
+
+
+def gated_delta_rule(q, k, v, g, beta, scale=None, chunk: int = 64, initial_state=None):
+    return ref.gated_delta_rule_chunked(q, k, v, g, beta, scale, chunk, initial_state)
+
+
+def status() -> dict:
+    """Which ops have a native sm_100a implementation loaded (for logs and DESIGN tables)."""
+    try:
+        return _nat().status()
+    except Exception as e:  # extension absent on a CPU box
+        return {"loaded": False, "why": str(e)}

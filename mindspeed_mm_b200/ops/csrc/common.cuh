@@ -1,0 +1,86 @@
+// Shared device helpers for the sm_100a kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
+
+#define MM_API extern "C" __attribute__((visibility("default")))
+
+// Status word written by kernels whose bounded waits ran out (read by the host; never traps).
+enum MmStatus : int { MM_OK = 0, MM_TIMEOUT_TMA = 1, MM_TIMEOUT_MMA = 2, MM_TIMEOUT_EPI = 3, MM_TIMEOUT_PEER = 4 };
+
+struct alignas(16) Vec8 {
+    bf162 v[4];
+};
+
+__device__ __forceinline__ void unpack8(const Vec8& p, float* f) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 t = __bfloat1622float2(p.v[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+__device__ __forceinline__ Vec8 pack8(const float* f) {
+    Vec8 p;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return p;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the whole block; every thread gets the result.  `red` holds >= 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+        float t = lane < nw ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    __syncthreads();
+    if (lane == 0) {
+        red[wid] = a;
+        red[34 + wid] = b;
+    }
+    __syncthreads();
+    if (wid == 0) {
+        float t = lane < nw ? red[lane] : 0.f;
+        float u = lane < nw ? red[34 + lane] : 0.f;
+        t = warp_sum(t);
+        u = warp_sum(u);
+        if (lane == 0) {
+            red[32] = t;
+            red[33] = u;
+        }
+    }
+    __syncthreads();
+    a = red[32];
+    b = red[33];
+}

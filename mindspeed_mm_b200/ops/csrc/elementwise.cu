@@ -1,0 +1,563 @@
+// Memory-bound fused ops: RMSNorm (fwd/bwd), SwiGLU (fwd/bwd), RoPE (half-rotation and interleaved,
+// fwd/bwd), adaLN LayerNorm-modulate (fwd/bwd), gated residual, sharded AdamW.
+//
+// All kernels move 16-byte vectors (8 bf16), keep a row in registers between the reduction and the
+// write so that every byte crosses HBM once, and size the grid as a multiple of the 148 SMs.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxVec = 4;  // cached 16-byte vectors per thread -> rows up to 256*4*8 = 8192 stay in registers
+
+// ------------------------------------------------------------------------------------------ RMSNorm
+__global__ void __launch_bounds__(kThreads) rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                               bf16* __restrict__ y, float* __restrict__ rstd_out,
+                                                               int T, int H, float eps) {
+    __shared__ float red[72];
+    const int nvec = H >> 3;
+    for (int row = blockIdx.x; row < T; row += gridDim.x) {
+        const Vec8* xr = reinterpret_cast<const Vec8*>(x + (size_t)row * H);
+        Vec8 cache[kMaxVec];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < kMaxVec; ++j) {
+            int i = threadIdx.x + j * kThreads;
+            if (i < nvec) {
+                cache[j] = xr[i];
+                float f[8];
+                unpack8(cache[j], f);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) ss += f[k] * f[k];
+            }
+        }
+        for (int i = threadIdx.x + kMaxVec * kThreads; i < nvec; i += kThreads) {
+            float f[8];
+            unpack8(xr[i], f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ss += f[k] * f[k];
+        }
+        ss = block_sum(ss, red);
+        const float rstd = rsqrtf(ss / (float)H + eps);
+        if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+        Vec8* yr = reinterpret_cast<Vec8*>(y + (size_t)row * H);
+        const Vec8* wr = reinterpret_cast<const Vec8*>(w);
+#pragma unroll
+        for (int j = 0; j < kMaxVec; ++j) {
+            int i = threadIdx.x + j * kThreads;
+            if (i < nvec) {
+                float f[8], g[8];
+                unpack8(cache[j], f);
+                unpack8(wr[i], g);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) f[k] = f[k] * rstd * g[k];
+                yr[i] = pack8(f);
+            }
+        }
+        for (int i = threadIdx.x + kMaxVec * kThreads; i < nvec; i += kThreads) {
+            float f[8], g[8];
+            unpack8(xr[i], f);
+            unpack8(wr[i], g);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) f[k] = f[k] * rstd * g[k];
+            yr[i] = pack8(f);
+        }
+    }
+}
+
+// dx = rstd * (g - xhat * mean(g * xhat)),  g = dy * w,  xhat = x * rstd;   dw += dy * xhat.
+// Each CTA walks rows with stride gridDim.x and keeps its dw partial in registers; partials go to
+// scratch [gridDim.x, H] fp32 and a second kernel folds them.  Requires H <= kThreads*kMaxVec*8.
+__global__ void __launch_bounds__(kThreads) rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                               const bf16* __restrict__ dy,
+                                                               const float* __restrict__ rstd_in,
+                                                               bf16* __restrict__ dx, float* __restrict__ dw_partial,
+                                                               int T, int H) {
+    __shared__ float red[72];
+    const int nvec = H >> 3;
+    float wreg[kMaxVec][8], dwacc[kMaxVec][8];
+    const Vec8* wr = reinterpret_cast<const Vec8*>(w);
+#pragma unroll
+    for (int j = 0; j < kMaxVec; ++j) {
+        int i = threadIdx.x + j * kThreads;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) dwacc[j][k] = 0.f;
+        if (i < nvec) unpack8(wr[i], wreg[j]);
+    }
+    for (int row = blockIdx.x; row < T; row += gridDim.x) {
+        const Vec8* xr = reinterpret_cast<const Vec8*>(x + (size_t)row * H);
+        const Vec8* gr = reinterpret_cast<const Vec8*>(dy + (size_t)row * H);
+        const float rstd = rstd_in[row];
+        float xh[kMaxVec][8], g[kMaxVec][8];
+        float dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < kMaxVec; ++j) {
+            int i = threadIdx.x + j * kThreads;
+            if (i < nvec) {
+                float a[8], b[8];
+                unpack8(xr[i], a);
+                unpack8(gr[i], b);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    xh[j][k] = a[k] * rstd;
+                    dwacc[j][k] += b[k] * xh[j][k];
+                    g[j][k] = b[k] * wreg[j][k];
+                    dot += g[j][k] * xh[j][k];
+                }
+            }
+        }
+        dot = block_sum(dot, red) / (float)H;
+        Vec8* dxr = reinterpret_cast<Vec8*>(dx + (size_t)row * H);
+#pragma unroll
+        for (int j = 0; j < kMaxVec; ++j) {
+            int i = threadIdx.x + j * kThreads;
+            if (i < nvec) {
+                float o[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) o[k] = rstd * (g[j][k] - xh[j][k] * dot);
+                dxr[i] = pack8(o);
+            }
+        }
+    }
+    float* out = dw_partial + (size_t)blockIdx.x * H;
+#pragma unroll
+    for (int j = 0; j < kMaxVec; ++j) {
+        int i = threadIdx.x + j * kThreads;
+        if (i < nvec) {
+            float4* o4 = reinterpret_cast<float4*>(out + i * 8);
+            o4[0] = make_float4(dwacc[j][0], dwacc[j][1], dwacc[j][2], dwacc[j][3]);
+            o4[1] = make_float4(dwacc[j][4], dwacc[j][5], dwacc[j][6], dwacc[j][7]);
+        }
+    }
+}
+
+__global__ void fold_partials_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int P, int H) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= H) return;
+    float s = 0.f;
+    for (int p = 0; p < P; ++p) s += partial[(size_t)p * H + c];
+    out[c] = __float2bfloat16(s);
+}
+
+// ------------------------------------------------------------------------------------------ SwiGLU
+// in: [T, 2F] = [gate | up];  out: [T, F] = silu(gate) * up
+__global__ void swiglu_fwd_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, long long T, int F) {
+    const int fv = F >> 3;
+    const long long total = T * fv;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        long long r = idx / fv;
+        int c = (int)(idx - r * fv);
+        const Vec8* row = reinterpret_cast<const Vec8*>(in + r * 2 * F);
+        float a[8], b[8];
+        unpack8(row[c], a);
+        unpack8(row[fv + c], b);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) a[k] = a[k] / (1.f + __expf(-a[k])) * b[k];
+        reinterpret_cast<Vec8*>(out + r * F)[c] = pack8(a);
+    }
+}
+
+__global__ void swiglu_bwd_kernel(const bf16* __restrict__ in, const bf16* __restrict__ dout, bf16* __restrict__ din,
+                                  long long T, int F) {
+    const int fv = F >> 3;
+    const long long total = T * fv;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        long long r = idx / fv;
+        int c = (int)(idx - r * fv);
+        const Vec8* row = reinterpret_cast<const Vec8*>(in + r * 2 * F);
+        float a[8], b[8], g[8], da[8], db[8];
+        unpack8(row[c], a);
+        unpack8(row[fv + c], b);
+        unpack8(reinterpret_cast<const Vec8*>(dout + r * F)[c], g);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float s = 1.f / (1.f + __expf(-a[k]));
+            float silu = a[k] * s;
+            da[k] = g[k] * b[k] * (s + silu * (1.f - s));
+            db[k] = g[k] * silu;
+        }
+        Vec8* orow = reinterpret_cast<Vec8*>(din + r * 2 * F);
+        orow[c] = pack8(da);
+        orow[fv + c] = pack8(db);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ RoPE
+// x: [T, N, D] with row stride `xs` elements between tokens (heads contiguous); out contiguous.
+// half-rotation: cos/sin [T, D] (bf16): o1 = x1*c1 - x2*s1 ; o2 = x2*c2 + x1*s2  (sign flips for bwd)
+__global__ void rope_half_kernel(const bf16* __restrict__ x, long long xs, const bf16* __restrict__ cosb,
+                                 const bf16* __restrict__ sinb, bf16* __restrict__ out, int T, int N, int D,
+                                 float sign) {
+    const int hv = D >> 4;  // vectors per half
+    const long long total = (long long)T * N * hv;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        int c = (int)(idx % hv);
+        long long tn = idx / hv;
+        int n = (int)(tn % N);
+        long long t = tn / N;
+        const bf16* xp = x + t * xs + (long long)n * D;
+        float x1[8], x2[8], c1[8], c2[8], s1[8], s2[8], o1[8], o2[8];
+        unpack8(reinterpret_cast<const Vec8*>(xp)[c], x1);
+        unpack8(reinterpret_cast<const Vec8*>(xp + D / 2)[c], x2);
+        const bf16* cp = cosb + t * D;
+        const bf16* sp = sinb + t * D;
+        unpack8(reinterpret_cast<const Vec8*>(cp)[c], c1);
+        unpack8(reinterpret_cast<const Vec8*>(cp + D / 2)[c], c2);
+        unpack8(reinterpret_cast<const Vec8*>(sp)[c], s1);
+        unpack8(reinterpret_cast<const Vec8*>(sp + D / 2)[c], s2);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (sign > 0.f) {
+                o1[k] = x1[k] * c1[k] - x2[k] * s1[k];
+                o2[k] = x2[k] * c2[k] + x1[k] * s2[k];
+            } else {  // transpose of the rotation
+                o1[k] = x1[k] * c1[k] + x2[k] * s2[k];
+                o2[k] = x2[k] * c2[k] - x1[k] * s1[k];
+            }
+        }
+        bf16* op = out + (t * N + n) * (long long)D;
+        reinterpret_cast<Vec8*>(op)[c] = pack8(o1);
+        reinterpret_cast<Vec8*>(op + D / 2)[c] = pack8(o2);
+    }
+}
+
+// interleaved pairs: cos/sin [T, D/2] fp32
+__global__ void rope_inter_kernel(const bf16* __restrict__ x, long long xs, const float* __restrict__ cosf_,
+                                  const float* __restrict__ sinf_, bf16* __restrict__ out, int T, int N, int D,
+                                  float sign) {
+    const int dv = D >> 3;
+    const long long total = (long long)T * N * dv;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        int c = (int)(idx % dv);
+        long long tn = idx / dv;
+        int n = (int)(tn % N);
+        long long t = tn / N;
+        float f[8], o[8];
+        unpack8(reinterpret_cast<const Vec8*>(x + t * xs + (long long)n * D)[c], f);
+        const float4 cs = reinterpret_cast<const float4*>(cosf_ + t * (D / 2))[c];
+        const float4 sn = reinterpret_cast<const float4*>(sinf_ + t * (D / 2))[c];
+        const float cc[4] = {cs.x, cs.y, cs.z, cs.w};
+        const float ss[4] = {sn.x * sign, sn.y * sign, sn.z * sign, sn.w * sign};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            o[2 * k] = f[2 * k] * cc[k] - f[2 * k + 1] * ss[k];
+            o[2 * k + 1] = f[2 * k] * ss[k] + f[2 * k + 1] * cc[k];
+        }
+        reinterpret_cast<Vec8*>(out + (t * N + n) * (long long)D)[c] = pack8(o);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ adaLN
+// y = LN(x) * (1 + scale[b]) + shift[b];  x: [B*S, H], scale/shift: [B, H] (bf16); saves mean / rstd.
+__global__ void __launch_bounds__(kThreads) ln_mod_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ scale,
+                                                              const bf16* __restrict__ shift, bf16* __restrict__ y,
+                                                              float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                              int T, int S, int H, float eps) {
+    __shared__ float red[72];
+    const int nvec = H >> 3;
+    for (int row = blockIdx.x; row < T; row += gridDim.x) {
+        const Vec8* xr = reinterpret_cast<const Vec8*>(x + (size_t)row * H);
+        float v[kMaxVec][8];
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int j = 0; j < kMaxVec; ++j) {
+            int i = threadIdx.x + j * kThreads;
+            if (i < nvec) {
+                unpack8(xr[i], v[j]);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    s1 += v[j][k];
+                    s2 += v[j][k] * v[j][k];
+                }
+            }
+        }
+        block_sum2(s1, s2, red);
+        const float mean = s1 / (float)H;
+        const float rstd = rsqrtf(fmaxf(s2 / (float)H - mean * mean, 0.f) + eps);
+        if (threadIdx.x == 0) {
+            mean_out[row] = mean;
+            rstd_out[row] = rstd;
+        }
+        const int b = row / S;
+        const Vec8* sc = reinterpret_cast<const Vec8*>(scale + (size_t)b * H);
+        const Vec8* sh = reinterpret_cast<const Vec8*>(shift + (size_t)b * H);
+        Vec8* yr = reinterpret_cast<Vec8*>(y + (size_t)row * H);
+#pragma unroll
+        for (int j = 0; j < kMaxVec; ++j) {
+            int i = threadIdx.x + j * kThreads;
+            if (i < nvec) {
+                float a[8], c[8], o[8];
+                unpack8(sc[i], a);
+                unpack8(sh[i], c);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) o[k] = (v[j][k] - mean) * rstd * (1.f + a[k]) + c[k];
+                yr[i] = pack8(o);
+            }
+        }
+    }
+}
+
+// dx = rstd * (g - mean(g) - xhat * mean(g * xhat)), g = dy * (1 + scale);
+// dscale[b] += dy * xhat, dshift[b] += dy  -> per-CTA partials (CTA c handles rows of ONE batch entry).
+__global__ void __launch_bounds__(kThreads) ln_mod_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ scale,
+                                                              const bf16* __restrict__ dy,
+                                                              const float* __restrict__ mean_in,
+                                                              const float* __restrict__ rstd_in, bf16* __restrict__ dx,
+                                                              float* __restrict__ dscale_partial,
+                                                              float* __restrict__ dshift_partial, int S, int H,
+                                                              int ctas_per_batch) {
+    __shared__ float red[72];
+    const int nvec = H >> 3;
+    const int b = blockIdx.x / ctas_per_batch, lane_cta = blockIdx.x % ctas_per_batch;
+    float sc[kMaxVec][8], dsc[kMaxVec][8], dsh[kMaxVec][8];
+    const Vec8* scp = reinterpret_cast<const Vec8*>(scale + (size_t)b * H);
+#pragma unroll
+    for (int j = 0; j < kMaxVec; ++j) {
+        int i = threadIdx.x + j * kThreads;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) dsc[j][k] = dsh[j][k] = 0.f;
+        if (i < nvec) unpack8(scp[i], sc[j]);
+    }
+    for (int s = lane_cta; s < S; s += ctas_per_batch) {
+        const size_t row = (size_t)b * S + s;
+        const Vec8* xr = reinterpret_cast<const Vec8*>(x + row * H);
+        const Vec8* gr = reinterpret_cast<const Vec8*>(dy + row * H);
+        const float mean = mean_in[row], rstd = rstd_in[row];
+        float xh[kMaxVec][8], g[kMaxVec][8];
+        float m1 = 0.f, m2 = 0.f;
+#pragma unroll
+        for (int j = 0; j < kMaxVec; ++j) {
+            int i = threadIdx.x + j * kThreads;
+            if (i < nvec) {
+                float a[8], d[8];
+                unpack8(xr[i], a);
+                unpack8(gr[i], d);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    xh[j][k] = (a[k] - mean) * rstd;
+                    dsc[j][k] += d[k] * xh[j][k];
+                    dsh[j][k] += d[k];
+                    g[j][k] = d[k] * (1.f + sc[j][k]);
+                    m1 += g[j][k];
+                    m2 += g[j][k] * xh[j][k];
+                }
+            }
+        }
+        block_sum2(m1, m2, red);
+        m1 /= (float)H;
+        m2 /= (float)H;
+        Vec8* dxr = reinterpret_cast<Vec8*>(dx + row * H);
+#pragma unroll
+        for (int j = 0; j < kMaxVec; ++j) {
+            int i = threadIdx.x + j * kThreads;
+            if (i < nvec) {
+                float o[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) o[k] = rstd * (g[j][k] - m1 - xh[j][k] * m2);
+                dxr[i] = pack8(o);
+            }
+        }
+    }
+    float* o1 = dscale_partial + (size_t)blockIdx.x * H;
+    float* o2 = dshift_partial + (size_t)blockIdx.x * H;
+#pragma unroll
+    for (int j = 0; j < kMaxVec; ++j) {
+        int i = threadIdx.x + j * kThreads;
+        if (i < nvec) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                o1[i * 8 + k] = dsc[j][k];
+                o2[i * 8 + k] = dsh[j][k];
+            }
+        }
+    }
+}
+
+// out[b, c] = sum_p partial[b*P + p, c]
+__global__ void fold_partials_batched_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int P, int H) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    int b = blockIdx.y;
+    if (c >= H) return;
+    float s = 0.f;
+    for (int p = 0; p < P; ++p) s += partial[((size_t)b * P + p) * H + c];
+    out[(size_t)b * H + c] = __float2bfloat16(s);
+}
+
+// out = x + gate[b] * y   (x,y: [B*S, H]; gate: [B, H])
+__global__ void gated_residual_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y,
+                                      const bf16* __restrict__ gate, bf16* __restrict__ out, long long T, int S,
+                                      int H) {
+    const int hv = H >> 3;
+    const long long total = T * hv;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        long long r = idx / hv;
+        int c = (int)(idx - r * hv);
+        int b = (int)(r / S);
+        float a[8], d[8], g[8];
+        unpack8(reinterpret_cast<const Vec8*>(x + r * H)[c], a);
+        unpack8(reinterpret_cast<const Vec8*>(y + r * H)[c], d);
+        unpack8(reinterpret_cast<const Vec8*>(gate + (size_t)b * H)[c], g);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) a[k] += g[k] * d[k];
+        reinterpret_cast<Vec8*>(out + r * H)[c] = pack8(a);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ AdamW
+// One pass over this rank's shard: fp32 master/moments in place, bf16 copy out.  Elements below
+// `split` get weight decay.  `scale_ptr` (optional, device) multiplies the gradient (clip coefficient).
+template <typename G>
+__global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                             const G* __restrict__ g, bf16* __restrict__ p16, long long n, long long split, float lr,
+                             float b1, float b2, float eps, float wd, float bc1, float bc2, float gscale,
+                             const float* __restrict__ scale_ptr) {
+    const float gs = scale_ptr ? gscale * (*scale_ptr) : gscale;
+    const long long nv = n >> 2;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nv;
+         i += (long long)gridDim.x * blockDim.x) {
+        float4 pp = reinterpret_cast<float4*>(p)[i];
+        float4 mm = reinterpret_cast<float4*>(m)[i];
+        float4 vv = reinterpret_cast<float4*>(v)[i];
+        float gg[4];
+        if constexpr (sizeof(G) == 2) {
+            const bf162* gp = reinterpret_cast<const bf162*>(g) + 2 * i;
+            float2 a = __bfloat1622float2(gp[0]), b = __bfloat1622float2(gp[1]);
+            gg[0] = a.x; gg[1] = a.y; gg[2] = b.x; gg[3] = b.y;
+        } else {
+            float4 a = reinterpret_cast<const float4*>(g)[i];
+            gg[0] = a.x; gg[1] = a.y; gg[2] = a.z; gg[3] = a.w;
+        }
+        float* P = &pp.x; float* M = &mm.x; float* V = &vv.x;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float gk = gg[k] * gs;
+            const float decay = (i * 4 + k) < split ? wd : 0.f;
+            M[k] = b1 * M[k] + (1.f - b1) * gk;
+            V[k] = b2 * V[k] + (1.f - b2) * gk * gk;
+            const float denom = sqrtf(V[k] / bc2) + eps;
+            P[k] = P[k] * (1.f - lr * decay) - lr * (M[k] / bc1) / denom;
+        }
+        reinterpret_cast<float4*>(p)[i] = pp;
+        reinterpret_cast<float4*>(m)[i] = mm;
+        reinterpret_cast<float4*>(v)[i] = vv;
+        bf162* o = reinterpret_cast<bf162*>(p16) + 2 * i;
+        o[0] = __floats2bfloat162_rn(pp.x, pp.y);
+        o[1] = __floats2bfloat162_rn(pp.z, pp.w);
+    }
+}
+
+inline int grid_for(long long work_items, int threads, int per_sm = 8) {
+    long long blocks = (work_items + threads - 1) / threads;
+    long long cap = 148LL * per_sm;
+    return (int)(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------ C ABI
+MM_API int mm_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int H, float eps,
+                          cudaStream_t st) {
+    if (H % 8) return -1;
+    int grid = T < 148 * 8 ? T : 148 * 8;
+    rmsnorm_fwd_kernel<<<grid, kThreads, 0, st>>>((const bf16*)x, (const bf16*)w, (bf16*)y, rstd, T, H, eps);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_rmsnorm_bwd_grid(int T) { return T < 148 * 4 ? T : 148 * 4; }
+
+// dw_partial: scratch of mm_rmsnorm_bwd_grid(T) * H floats.
+MM_API int mm_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx, void* dw,
+                          float* dw_partial, int T, int H, cudaStream_t st) {
+    if (H % 8 || H > kThreads * kMaxVec * 8) return -1;
+    int grid = mm_rmsnorm_bwd_grid(T);
+    rmsnorm_bwd_kernel<<<grid, kThreads, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, (bf16*)dx,
+                                                  dw_partial, T, H);
+    fold_partials_kernel<<<(H + 255) / 256, 256, 0, st>>>(dw_partial, (bf16*)dw, grid, H);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_swiglu_fwd(const void* in, void* out, long long T, int F, cudaStream_t st) {
+    if (F % 8) return -1;
+    swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, st>>>((const bf16*)in, (bf16*)out, T, F);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_swiglu_bwd(const void* in, const void* dout, void* din, long long T, int F, cudaStream_t st) {
+    if (F % 8) return -1;
+    swiglu_bwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, st>>>((const bf16*)in, (const bf16*)dout, (bf16*)din, T, F);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_rope_half(const void* x, long long xs, const void* cosb, const void* sinb, void* out, int T, int N,
+                        int D, int backward, cudaStream_t st) {
+    if (D % 16 || xs % 8) return -1;
+    rope_half_kernel<<<grid_for((long long)T * N * (D / 16), 256), 256, 0, st>>>(
+        (const bf16*)x, xs, (const bf16*)cosb, (const bf16*)sinb, (bf16*)out, T, N, D, backward ? -1.f : 1.f);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_rope_interleaved(const void* x, long long xs, const float* cosf_, const float* sinf_, void* out, int T,
+                               int N, int D, int backward, cudaStream_t st) {
+    if (D % 8 || xs % 8) return -1;
+    rope_inter_kernel<<<grid_for((long long)T * N * (D / 8), 256), 256, 0, st>>>(
+        (const bf16*)x, xs, cosf_, sinf_, (bf16*)out, T, N, D, backward ? -1.f : 1.f);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_ln_mod_fwd(const void* x, const void* scale, const void* shift, void* y, float* mean, float* rstd,
+                         int T, int S, int H, float eps, cudaStream_t st) {
+    if (H % 8 || H > kThreads * kMaxVec * 8) return -1;
+    int grid = T < 148 * 8 ? T : 148 * 8;
+    ln_mod_fwd_kernel<<<grid, kThreads, 0, st>>>((const bf16*)x, (const bf16*)scale, (const bf16*)shift, (bf16*)y, mean,
+                                                 rstd, T, S, H, eps);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_ln_mod_bwd_ctas(int B, int S) {
+    int per = (148 * 4) / (B < 1 ? 1 : B);
+    if (per < 1) per = 1;
+    return per < S ? per : S;
+}
+
+// partials: 2 * B * mm_ln_mod_bwd_ctas(B,S) * H floats of scratch.
+MM_API int mm_ln_mod_bwd(const void* x, const void* scale, const void* dy, const float* mean, const float* rstd,
+                         void* dx, void* dscale, void* dshift, float* partials, int B, int S, int H,
+                         cudaStream_t st) {
+    if (H % 8 || H > kThreads * kMaxVec * 8) return -1;
+    int per = mm_ln_mod_bwd_ctas(B, S);
+    float* p1 = partials;
+    float* p2 = partials + (size_t)B * per * H;
+    ln_mod_bwd_kernel<<<B * per, kThreads, 0, st>>>((const bf16*)x, (const bf16*)scale, (const bf16*)dy, mean, rstd,
+                                                    (bf16*)dx, p1, p2, S, H, per);
+    dim3 g((H + 255) / 256, B);
+    fold_partials_batched_kernel<<<g, 256, 0, st>>>(p1, (bf16*)dscale, per, H);
+    fold_partials_batched_kernel<<<g, 256, 0, st>>>(p2, (bf16*)dshift, per, H);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_gated_residual(const void* x, const void* y, const void* gate, void* out, long long T, int S, int H,
+                             cudaStream_t st) {
+    if (H % 8) return -1;
+    gated_residual_kernel<<<grid_for(T * (H / 8), 256), 256, 0, st>>>((const bf16*)x, (const bf16*)y, (const bf16*)gate,
+                                                                      (bf16*)out, T, S, H);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_adamw(float* p, float* m, float* v, const void* g, int g_is_bf16, void* p16, long long n,
+                    long long split, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                    float gscale, const float* scale_ptr, cudaStream_t st) {
+    if (n % 4) return -1;
+    int grid = grid_for(n / 4, 256, 16);
+    if (g_is_bf16)
+        adamw_kernel<bf16><<<grid, 256, 0, st>>>(p, m, v, (const bf16*)g, (bf16*)p16, n, split, lr, b1, b2, eps, wd, bc1,
+                                                 bc2, gscale, scale_ptr);
+    else
+        adamw_kernel<float><<<grid, 256, 0, st>>>(p, m, v, (const float*)g, (bf16*)p16, n, split, lr, b1, b2, eps, wd,
+                                                  bc1, bc2, gscale, scale_ptr);
+    return (int)cudaGetLastError();
+}

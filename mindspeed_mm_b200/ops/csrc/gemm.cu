@@ -1,0 +1,322 @@
+// Persistent, warp-specialised bf16 GEMM on the 5th-gen tensor cores.
+//
+//   C[M,N] (bf16) = op(A) * op(B) (+ bias[N])        fp32 accumulation in TMEM
+//
+// Operand layouts (both row-major in memory):
+//   A_MN = 0: A is [M, K] (K contiguous)      A_MN = 1: A is stored as [K, M] (M contiguous)
+//   B_MN = 0: B is [N, K] (K contiguous)      B_MN = 1: B is stored as [K, N] (N contiguous)
+// so forward  y = x W^T      is (A_MN=0, B_MN=0) on (x [T,K], W [N,K]),
+//    dgrad    dx = dy W      is (A_MN=0, B_MN=1) on (dy [T,N], W [N,K] read as [K'=N, N'=K]),
+//    wgrad    dW = dy^T x    is (A_MN=1, B_MN=1) on (dy [T,N] read as [K'=T, M'=N], x [T,K] read as [K'=T, N'=K]).
+//
+// One CTA per SM walks output tiles of 128 x BN.  Roles:
+//   warp 0     : TMA producer  (cp.async.bulk.tensor into a multi-stage 128B-swizzled smem ring)
+//   warp 1     : MMA issuer    (one elected thread issues tcgen05.mma; tcgen05.commit frees ring slots)
+//   warps 2..5 : epilogue      (tcgen05.ld TMEM -> registers -> bf16 -> swizzled smem -> TMA store)
+// The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps the main
+// loop of tile i+1.  Tiles are visited in groups of 8 M-blocks per N sweep to keep A/B tiles L2-resident.
+// All mbarrier waits are bounded (tc05::mbar_wait); a timeout is reported through `status` and the CTA
+// unwinds: it lets in-flight copies land, frees its TMEM and returns.
+#include "tc05.cuh"
+
+namespace {
+
+using namespace tc05;
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr int kSmemBudget = 227 * 1024;
+
+template <int BN>
+struct Cfg {
+    static constexpr int kABytes = BM * BK * 2;
+    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kCBytes = 2 * BM * 64 * 2;  // two 128x64 bf16 staging slabs
+    static constexpr int kAux = 1024;                // barriers etc.
+    static constexpr int kStages = (kSmemBudget - kCBytes - kAux - 1024) / kStageBytes;
+    static constexpr int kSmem = kStages * kStageBytes + kCBytes + kAux + 1024;
+    static constexpr int kTmemCols = 2 * BN;
+};
+
+struct Params {
+    int M, N, K;
+    const bf16* bias;
+    int* status;
+    int group_m;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int group_m, int& mb, int& nb) {
+    const int per_group = group_m * n_blocks;
+    const int g = tile / per_group;
+    const int first_m = g * group_m;
+    const int gm = min(group_m, m_blocks - first_m);
+    const int r = tile - g * per_group;
+    mb = first_m + r % gm;
+    nb = r / gm;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmC, Params p) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + C::kStages * C::kABytes;
+    uint8_t* sC = sB + C::kStages * C::kBBytes;
+    uint64_t* full = reinterpret_cast<uint64_t*>(sC + C::kCBytes);
+    uint64_t* empty = full + C::kStages;
+    uint64_t* tfull = empty + C::kStages;
+    uint64_t* tempty = tfull + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* epi_stop = abort_flag + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int m_blocks = (p.M + BM - 1) / BM;
+    const int n_blocks = (p.N + BN - 1) / BN;
+    const int n_tiles = m_blocks * n_blocks;
+    const int k_blocks = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&tfull[a], 1);
+            mbar_init(&tempty[a], kEpiThreads);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+        prefetch_tmap(&tmC);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::kTmemCols);
+        tmem_relinquish();
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                int mb, nb;
+                tile_coords(tile, m_blocks, n_blocks, p.group_m, mb, nb);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+                        atomicExch(p.status, MM_TIMEOUT_TMA);
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(&full[stage], C::kStageBytes);
+                    uint8_t* a = sA + stage * C::kABytes;
+                    uint8_t* b = sB + stage * C::kBBytes;
+                    if constexpr (!A_MN) {
+                        tma_load_2d(a, &tmA, &full[stage], kb * BK, mb * BM);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BM / 64; ++j)
+                            tma_load_2d(a + j * (BK * 128), &tmA, &full[stage], mb * BM + j * 64, kb * BK);
+                    }
+                    if constexpr (!B_MN) {
+                        tma_load_2d(b, &tmB, &full[stage], kb * BK, nb * BN);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_2d(b + j * (BK * 128), &tmB, &full[stage], nb * BN + j * 64, kb * BK);
+                    }
+                    if (++stage == C::kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
+                const int acc = it & 1;
+                if (!mbar_wait(&tempty[acc], ((it >> 1) & 1) ^ 1, abort_flag)) {
+                    atomicExch(p.status, MM_TIMEOUT_MMA);
+                    break;
+                }
+                fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&full[stage], phase, abort_flag)) {
+                        atomicExch(p.status, MM_TIMEOUT_MMA);
+                        ok = false;
+                        break;
+                    }
+                    fence_after_sync();
+                    const uint32_t a0 = smem_u32(sA + stage * C::kABytes);
+                    const uint32_t b0 = smem_u32(sB + stage * C::kBBytes);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        // K-major: 16 elements of K = 32 bytes inside the swizzle atom.
+                        // MN-major: 16 rows of K = two 8-row groups = 2048 bytes.
+                        const uint64_t da = A_MN ? smem_desc_sw128(a0 + k * 2048, BK * 128, 1024)
+                                                 : smem_desc_sw128(a0 + k * 32, 16, 1024);
+                        const uint64_t db = B_MN ? smem_desc_sw128(b0 + k * 2048, BK * 128, 1024)
+                                                 : smem_desc_sw128(b0 + k * 32, 16, 1024);
+                        mma_ss(d_tmem, da, db, idesc, (kb | k) ? 1u : 0u);
+                    }
+                    mma_commit(&empty[stage]);  // slot reusable once these MMAs have read it
+                    if (++stage == C::kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (ok) mma_commit(&tfull[acc]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;            // TMEM lane quarter this warp may read
+        const int row = q * 32 + lane;     // row inside the 128-row tile
+        const bool issuer = threadIdx.x == 64;
+        int it = 0;
+        int slab_count = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+            int mb, nb;
+            tile_coords(tile, m_blocks, n_blocks, p.group_m, mb, nb);
+            const int acc = it & 1;
+            if (!mbar_wait(&tfull[acc], (it >> 1) & 1, abort_flag) && lane == 0) atomicExch(p.status, MM_TIMEOUT_EPI);
+            // make the go / no-go decision identical for all 128 epilogue threads before any bar.sync below
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (issuer) *epi_stop = *abort_flag;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (*epi_stop) break;
+            fence_after_sync();
+            const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int slab = 0; slab < BN / 64; ++slab, ++slab_count) {
+                uint8_t* buf = sC + (slab_count & 1) * (BM * 128);
+                if (issuer) tma_wait_read<1>();  // the store that last read this buffer has drained
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                uint32_t r[64];
+                tmem_ld_32x32(t_row + slab * 64, r);
+                tmem_ld_32x32(t_row + slab * 64 + 32, r + 32);
+                tmem_wait_ld();
+                const int n0 = nb * BN + slab * 64;
+                if (p.bias != nullptr) {
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) {
+                        const int n = n0 + c;
+                        const float bv = n < p.N ? __bfloat162float(p.bias[n]) : 0.f;
+                        r[c] = __float_as_uint(__uint_as_float(r[c]) + bv);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    uint4 v;
+                    bf162 t0 = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+                    bf162 t1 = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                    bf162 t2 = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                    bf162 t3 = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                    v.x = *reinterpret_cast<uint32_t*>(&t0);
+                    v.y = *reinterpret_cast<uint32_t*>(&t1);
+                    v.z = *reinterpret_cast<uint32_t*>(&t2);
+                    v.w = *reinterpret_cast<uint32_t*>(&t3);
+                    *reinterpret_cast<uint4*>(buf + row * 128 + ((j ^ (row & 7)) << 4)) = v;
+                }
+                fence_proxy_async();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (issuer) {
+                    tma_store_2d(&tmC, buf, n0, mb * BM);
+                    tma_commit();
+                }
+            }
+            fence_before_sync();
+            mbar_arrive(&tempty[acc]);
+        }
+        if (issuer) tma_wait_all<0>();
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    if (*abort_flag) {
+        // give copies that may still be in flight time to land before the CTA's smem is released
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        fence_after_sync();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int launch(const void* A, const void* B, void* Cc, const void* bias, int M, int N, int K, long long lda, long long ldb,
+           long long ldc, int* status, cudaStream_t st) {
+    using C = Cfg<BN>;
+    CUtensorMap tA, tB, tC;
+    int r;
+    // A_MN: memory is [K, M] -> rows=K, cols=M, box = 64 k-rows x 64 m ;  else rows=M, cols=K, box = 128 x 64
+    r = A_MN ? make_tmap_2d(&tA, A, K, M, lda, BK, 64) : make_tmap_2d(&tA, A, M, K, lda, BM, BK);
+    if (r) return 1000 + r;
+    r = B_MN ? make_tmap_2d(&tB, B, K, N, ldb, BK, 64) : make_tmap_2d(&tB, B, N, K, ldb, BN, BK);
+    if (r) return 2000 + r;
+    r = make_tmap_2d(&tC, Cc, M, N, ldc, BM, 64);
+    if (r) return 3000 + r;
+    auto kern = gemm_kernel<BN, A_MN, B_MN>;
+    static bool done = false;
+    if (!done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
+        if (e != cudaSuccess) return (int)e;
+        done = true;
+    }
+    const int m_blocks = (M + BM - 1) / BM, n_blocks = (N + BN - 1) / BN;
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    const int tiles = m_blocks * n_blocks;
+    Params p{M, N, K, (const bf16*)bias, status, 8};
+    const int grid = tiles < sms ? tiles : sms;
+    kern<<<grid, kThreads, C::kSmem, st>>>(tA, tB, tC, p);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// lda/ldb/ldc: elements between consecutive rows of the tensors as laid out in memory.
+// Requirements: base pointers 16-byte aligned; ld* multiples of 8; `status` is a device int (0 = ok).
+MM_API int mm_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
+                        long long ldb, long long ldc, int a_mn, int b_mn, int bn, int* status, cudaStream_t st) {
+    if ((lda | ldb | ldc) % 8) return -1;
+    if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return -2;
+    if (M <= 0 || N <= 0 || K <= 0) return -3;
+#define MM_DISPATCH(BN_)                                                                                          \
+    if (!a_mn && !b_mn) return launch<BN_, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, status, st);      \
+    if (!a_mn && b_mn) return launch<BN_, false, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, status, st);        \
+    if (a_mn && !b_mn) return launch<BN_, true, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, status, st);        \
+    return launch<BN_, true, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, status, st);
+    if (bn == 128) {
+        MM_DISPATCH(128)
+    }
+    MM_DISPATCH(256)
+#undef MM_DISPATCH
+}

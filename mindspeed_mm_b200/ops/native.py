@@ -1,0 +1,410 @@
+"""ctypes bindings and autograd wrappers for the sm_100a kernels in ``csrc/``.
+
+The library is loaded from ``ops/_lib/libmm_b200_ops.so`` (built in-tree by ``ops/build.py``).  On a
+GPU box a missing or stale library is an error, never a silent fallback.  Kernels take raw device
+pointers and the current CUDA stream; tensors are kept alive by the autograd contexts / callers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import os
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+_LIB = None
+_STATUS: dict = {}
+LAUNCHES = 0  # native kernel launches issued through this module (bench reports it)
+
+_p, _i, _ll, _f = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        path = _build.lib_path()
+        if not os.path.exists(path):
+            raise RuntimeError(f"native op library not built: {path} (run python -m mindspeed_mm_b200.ops.build)")
+        _LIB = C.CDLL(path)
+        _declare(_LIB)
+    return _LIB
+
+
+def _declare(L):
+    sig = {
+        "mm_rmsnorm_fwd": [_p, _p, _p, _p, _i, _i, _f, _p],
+        "mm_rmsnorm_bwd_grid": [_i],
+        "mm_rmsnorm_bwd": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _p],
+        "mm_swiglu_fwd": [_p, _p, _ll, _i, _p],
+        "mm_swiglu_bwd": [_p, _p, _p, _ll, _i, _p],
+        "mm_rope_half": [_p, _ll, _p, _p, _p, _i, _i, _i, _i, _p],
+        "mm_rope_interleaved": [_p, _ll, _p, _p, _p, _i, _i, _i, _i, _p],
+        "mm_ln_mod_fwd": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _f, _p],
+        "mm_ln_mod_bwd_ctas": [_i, _i],
+        "mm_ln_mod_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p],
+        "mm_gated_residual": [_p, _p, _p, _p, _ll, _i, _i, _p],
+        "mm_adamw": [_p, _p, _p, _p, _i, _p, _ll, _ll, _f, _f, _f, _f, _f, _f, _f, _f, _p, _p],
+        "mm_gemm_bf16": [_p, _p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _p, _p],
+    }
+    for name, args in sig.items():
+        if hasattr(L, name):
+            fn = getattr(L, name)
+            fn.argtypes = args
+            fn.restype = _i
+            _STATUS[name] = True
+        else:
+            _STATUS[name] = False
+
+
+def status() -> dict:
+    lib()
+    return {"loaded": True, "path": _build.lib_path(), "symbols": dict(_STATUS)}
+
+
+def _st():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc: int, what: str):
+    global LAUNCHES
+    LAUNCHES += 1
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")
+
+
+_status_words: dict = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Device int the tcgen05 kernels write when a bounded wait ran out (0 = fine)."""
+    key = torch.device(device).index or 0
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[key]
+
+
+def check_status(device=None) -> int:
+    """Host-side read of the status word (synchronises); raises if a kernel reported a timeout."""
+    dev = device if device is not None else torch.cuda.current_device()
+    v = int(status_word(dev).item())
+    if v != 0:
+        status_word(dev).zero_()
+        raise RuntimeError(f"a native kernel gave up a bounded wait (status {v})")
+    return v
+
+
+# --------------------------------------------------------------------------- RMSNorm
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        shape = x.shape
+        H = shape[-1]
+        x2 = x.reshape(-1, H)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        T = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+        wc = w.contiguous()
+        _check(lib().mm_rmsnorm_fwd(x2.data_ptr(), wc.data_ptr(), y.data_ptr(), rstd.data_ptr(), T, H, eps, _st()),
+               "rmsnorm_fwd")
+        ctx.save_for_backward(x2, wc, rstd)
+        ctx.shape = shape
+        return y.view(shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, rstd = ctx.saved_tensors
+        T, H = x2.shape
+        dy2 = dy.reshape(T, H)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = torch.empty_like(x2)
+        dw = torch.empty_like(w)
+        grid = lib().mm_rmsnorm_bwd_grid(T)
+        partial = torch.empty(grid * H, dtype=torch.float32, device=x2.device)
+        _check(lib().mm_rmsnorm_bwd(x2.data_ptr(), w.data_ptr(), dy2.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+                                    dw.data_ptr(), partial.data_ptr(), T, H, _st()), "rmsnorm_bwd")
+        return dx.view(ctx.shape), dw, None
+
+
+def rms_norm(x, w, eps=1e-6):
+    if x.shape[-1] % 8 or x.shape[-1] > 8192:
+        from . import reference
+        return reference.rms_norm(x, w, eps)
+    return _RMSNorm.apply(x, w, eps)
+
+
+# --------------------------------------------------------------------------- SwiGLU
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        F2 = gu.shape[-1]
+        g2 = gu.reshape(-1, F2)
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        T, F = g2.shape[0], F2 // 2
+        out = torch.empty(T, F, dtype=gu.dtype, device=gu.device)
+        _check(lib().mm_swiglu_fwd(g2.data_ptr(), out.data_ptr(), T, F, _st()), "swiglu_fwd")
+        ctx.save_for_backward(g2)
+        ctx.shape = gu.shape
+        return out.view(*gu.shape[:-1], F)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (g2,) = ctx.saved_tensors
+        T, F = g2.shape[0], g2.shape[1] // 2
+        d2 = dout.reshape(T, F)
+        if not d2.is_contiguous():
+            d2 = d2.contiguous()
+        din = torch.empty_like(g2)
+        _check(lib().mm_swiglu_bwd(g2.data_ptr(), d2.data_ptr(), din.data_ptr(), T, F, _st()), "swiglu_bwd")
+        return din.view(ctx.shape)
+
+
+def swiglu(gu):
+    if (gu.shape[-1] // 2) % 8:
+        from . import reference
+        return reference.swiglu(gu)
+    return _SwiGLU.apply(gu)
+
+
+# --------------------------------------------------------------------------- RoPE
+def _rope_call(x, cos, sin, interleaved, backward):
+    # x: [T, N, D] whose last two dims are dense; the token stride may be larger (view into fused qkv)
+    T, N, D = x.shape
+    if x.stride(2) != 1 or x.stride(1) != D or x.stride(0) % 8 or x.data_ptr() % 16:
+        x = x.contiguous()
+    out = torch.empty(T, N, D, dtype=x.dtype, device=x.device)
+    if interleaved:
+        _check(lib().mm_rope_interleaved(x.data_ptr(), x.stride(0), cos.data_ptr(), sin.data_ptr(), out.data_ptr(),
+                                         T, N, D, int(backward), _st()), "rope_interleaved")
+    else:
+        _check(lib().mm_rope_half(x.data_ptr(), x.stride(0), cos.data_ptr(), sin.data_ptr(), out.data_ptr(),
+                                  T, N, D, int(backward), _st()), "rope_half")
+    return out
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, interleaved):
+        ctx.save_for_backward(cos, sin)
+        ctx.interleaved = interleaved
+        return _rope_call(x, cos, sin, interleaved, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin = ctx.saved_tensors
+        return _rope_call(dy, cos, sin, ctx.interleaved, True), None, None, None
+
+
+def rope(x, cos, sin, interleaved: bool):
+    T, N, D = x.shape
+    if interleaved:
+        if D % 8:
+            from . import reference
+            return reference.rope_interleaved(x, cos, sin)
+        cos, sin = cos.float().contiguous(), sin.float().contiguous()
+    else:
+        if D % 16:
+            from . import reference
+            return reference.rope_rotate_half(x, cos, sin)
+        cos, sin = cos.to(torch.bfloat16).contiguous(), sin.to(torch.bfloat16).contiguous()
+    return _Rope.apply(x, cos, sin, interleaved)
+
+
+# --------------------------------------------------------------------------- adaLN
+class _LNMod(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, scale, shift, eps):
+        B, S, H = x.shape
+        xc, sc, sh = x.contiguous(), scale.reshape(B, H).contiguous(), shift.reshape(B, H).contiguous()
+        y = torch.empty_like(xc)
+        mean = torch.empty(B * S, dtype=torch.float32, device=x.device)
+        rstd = torch.empty_like(mean)
+        _check(lib().mm_ln_mod_fwd(xc.data_ptr(), sc.data_ptr(), sh.data_ptr(), y.data_ptr(), mean.data_ptr(),
+                                   rstd.data_ptr(), B * S, S, H, eps, _st()), "ln_mod_fwd")
+        ctx.save_for_backward(xc, sc, mean, rstd)
+        ctx.sshape = scale.shape
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, sc, mean, rstd = ctx.saved_tensors
+        B, S, H = x.shape
+        dyc = dy.contiguous()
+        dx = torch.empty_like(x)
+        dscale = torch.empty_like(sc)
+        dshift = torch.empty_like(sc)
+        per = lib().mm_ln_mod_bwd_ctas(B, S)
+        partial = torch.empty(2 * B * per * H, dtype=torch.float32, device=x.device)
+        _check(lib().mm_ln_mod_bwd(x.data_ptr(), sc.data_ptr(), dyc.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                                   dx.data_ptr(), dscale.data_ptr(), dshift.data_ptr(), partial.data_ptr(), B, S, H,
+                                   _st()), "ln_mod_bwd")
+        return dx, dscale.view(ctx.sshape), dshift.view(ctx.sshape), None
+
+
+def layer_norm_modulate(x, scale, shift, eps=1e-6):
+    """x: [B, S, H]; scale/shift: [B, 1, H] or [B, H]."""
+    if x.dim() != 3 or x.shape[-1] % 8 or x.shape[-1] > 8192 or scale.numel() != x.shape[0] * x.shape[-1]:
+        from . import reference
+        return reference.layer_norm_modulate(x, scale, shift, eps)
+    return _LNMod.apply(x, scale.to(x.dtype), shift.to(x.dtype), eps)
+
+
+class _GatedResidual(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, y, gate):
+        B, S, H = x.shape
+        xc, yc, gc = x.contiguous(), y.contiguous(), gate.reshape(B, H).contiguous()
+        out = torch.empty_like(xc)
+        _check(lib().mm_gated_residual(xc.data_ptr(), yc.data_ptr(), gc.data_ptr(), out.data_ptr(), B * S, S, H,
+                                       _st()), "gated_residual")
+        ctx.save_for_backward(yc, gc)
+        ctx.gshape = gate.shape
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        y, g = ctx.saved_tensors
+        B, S, H = y.shape
+        dy = dout * g.view(B, 1, H)
+        dg = (dout.float() * y.float()).sum(1).to(g.dtype).view(ctx.gshape)
+        return dout, dy, dg
+
+
+def gated_residual(x, y, gate):
+    if x.dim() != 3 or x.shape[-1] % 8 or gate.numel() != x.shape[0] * x.shape[-1]:
+        from . import reference
+        return reference.gated_residual(x, y, gate)
+    return _GatedResidual.apply(x, y, gate.to(x.dtype))
+
+
+# --------------------------------------------------------------------------- AdamW
+def adamw_shard(master, exp_avg, exp_avg_sq, grad, p16, lr, b1, b2, eps, wd, step, split, grad_scale=1.0):
+    n = master.numel()
+    scale_ptr = None
+    gs = 1.0
+    if isinstance(grad_scale, torch.Tensor):
+        scale_ptr = grad_scale.float().reshape(1)
+        sp = scale_ptr.data_ptr()
+    else:
+        gs = float(grad_scale)
+        sp = None
+    bc1 = 1.0 - b1 ** step
+    bc2 = 1.0 - b2 ** step
+    g = grad if grad.dtype in (torch.bfloat16, torch.float32) else grad.float()
+    _check(lib().mm_adamw(master.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(), g.data_ptr(),
+                          int(g.dtype == torch.bfloat16), p16.data_ptr(), n, int(split), lr, b1, b2, eps, wd, bc1, bc2,
+                          gs, sp, _st()), "adamw")
+
+
+# --------------------------------------------------------------------------- GEMM (tcgen05)
+def _gemm_raw(a, b, out, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, bn=None):
+    if bn is None:
+        bn = 256 if N >= 256 else 128
+    st = status_word(a.device)
+    rc = lib().mm_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), None if bias is None else bias.data_ptr(),
+                            M, N, K, lda, ldb, ldc, int(a_mn), int(b_mn), bn, st.data_ptr(), _st())
+    _check(rc, "gemm_bf16")
+
+
+def _ok2d(t):
+    return t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
+
+
+def gemm_supported(x, w) -> bool:
+    return (os.environ.get("MM_B200_GEMM", "1") == "1" and w.dtype == torch.bfloat16 and w.dim() == 2
+            and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0)
+
+
+def gemm_nt(a, b, bias=None, out=None):
+    """a [M,K] @ b[N,K]^T (+bias) -> [M,N]."""
+    if not _ok2d(a):
+        a = a.contiguous()
+    if not _ok2d(b):
+        b = b.contiguous()
+    M, K = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    _gemm_raw(a, b, out, bias, M, N, K, a.stride(0), b.stride(0), out.stride(0), 0, 0)
+    return out
+
+
+def gemm_nn(a, b, out=None):
+    """a [M,K] @ b[K,N] -> [M,N]  (b read N-contiguous: dgrad)."""
+    if not _ok2d(a):
+        a = a.contiguous()
+    if not _ok2d(b):
+        b = b.contiguous()
+    M, K = a.shape
+    N = b.shape[1]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    _gemm_raw(a, b, out, None, M, N, K, a.stride(0), b.stride(0), out.stride(0), 0, 1)
+    return out
+
+
+def gemm_tn(a, b, out=None):
+    """a[K,M]^T @ b[K,N] -> [M,N]  (both read with the contraction dim strided: wgrad)."""
+    if not _ok2d(a):
+        a = a.contiguous()
+    if not _ok2d(b):
+        b = b.contiguous()
+    K, M = a.shape
+    N = b.shape[1]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    _gemm_raw(a, b, out, None, M, N, K, a.stride(0), b.stride(0), out.stride(0), 1, 1)
+    return out
+
+
+_BWD_NATIVE = os.environ.get("MM_B200_GEMM_BWD", "1") == "1"
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.shape = shape
+        y = gemm_nt(x2, w, bias)
+        return y.view(*shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, w.shape[0])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = (gemm_nn(dy2, w) if _BWD_NATIVE else dy2 @ w).view(ctx.shape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm_tn(dy2, x2) if _BWD_NATIVE else dy2.t() @ x2
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy2.dtype)
+        return dx, dw, db
+
+
+def linear(x, w, bias=None):
+    return _Linear.apply(x, w, bias)
+
+
+# --------------------------------------------------------------------------- not yet native
+def fmha_supported(q, k, v) -> bool:
+    return False
+
+
+def lce_supported(h, w) -> bool:
+    return False
+
+
+def grouped_gemm_supported(x, w) -> bool:
+    return False

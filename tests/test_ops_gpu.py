@@ -1,0 +1,182 @@
+"""sm_100a kernels against plain fp32 PyTorch references of the same op."""
+import math
+
+import pytest
+import torch
+
+from mindspeed_mm_b200 import ops
+from mindspeed_mm_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _close(a, b, rtol=2e-2, atol=2e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    scale = b.abs().max().item() + 1e-6
+    assert err <= atol + rtol * scale, f"max err {err} vs scale {scale}"
+
+
+@pytest.fixture(autouse=True)
+def _native_tier():
+    ops.set_tier("native")
+    yield
+    from mindspeed_mm_b200.ops import native
+    native.check_status()
+
+
+@pytest.mark.parametrize("T,H", [(333, 1280), (1024, 3584), (64, 8192), (7, 512)])
+def test_rmsnorm_fwd_bwd(T, H):
+    torch.manual_seed(0)
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
+    y = ops.rms_norm(x, w, 1e-6)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = ref.rms_norm(xr, wr, 1e-6)
+    yr.backward(dy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad)
+    _close(w.grad, wr.grad, rtol=3e-2)
+
+
+@pytest.mark.parametrize("T,F", [(257, 3424), (1024, 18944)])
+def test_swiglu(T, F):
+    torch.manual_seed(0)
+    x = torch.randn(T, 2 * F, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    dy = torch.randn(T, F, device=DEV, dtype=torch.bfloat16)
+    y = ops.swiglu(x)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    yr = ref.swiglu(xr)
+    yr.backward(dy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad)
+
+
+@pytest.mark.parametrize("N,D", [(28, 128), (16, 80), (4, 128)])
+def test_rope_half(N, D):
+    torch.manual_seed(0)
+    T = 515
+    base = torch.randn(T, N * D + 64, device=DEV, dtype=torch.bfloat16)
+    x = base[:, :N * D].view(T, N, D).detach().requires_grad_()          # strided view like q in fused qkv
+    ang = torch.rand(T, D // 2, device=DEV) * 6.28
+    emb = torch.cat([ang, ang], -1)
+    cos, sin = emb.cos().to(torch.bfloat16), emb.sin().to(torch.bfloat16)
+    dy = torch.randn(T, N, D, device=DEV, dtype=torch.bfloat16)
+    y = ops.rope_rotate_half(x, cos, sin)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    yr = ref.rope_rotate_half(xr, cos.float(), sin.float())
+    yr.backward(dy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad)
+
+
+def test_rope_interleaved():
+    torch.manual_seed(0)
+    T, N, D = 300, 5, 128
+    x = torch.randn(T, N, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    cos, sin = ref.rope3d_freqs((3, 10, 10), D, device=DEV)
+    dy = torch.randn(T, N, D, device=DEV, dtype=torch.bfloat16)
+    y = ops.rope_interleaved(x, cos, sin)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    yr = ref.rope_interleaved(xr, cos, sin)
+    yr.backward(dy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad)
+
+
+def test_ln_modulate_and_gated_residual():
+    torch.manual_seed(0)
+    B, S, H = 2, 301, 5120
+    x = torch.randn(B, S, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    sc = (0.1 * torch.randn(B, 1, H, device=DEV)).to(torch.bfloat16).requires_grad_()
+    sh = (0.1 * torch.randn(B, 1, H, device=DEV)).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(B, S, H, device=DEV, dtype=torch.bfloat16)
+    y = ops.layer_norm_modulate(x, sc, sh, 1e-6)
+    y.backward(dy)
+    xr, scr, shr = (t.detach().float().requires_grad_() for t in (x, sc, sh))
+    yr = ref.layer_norm_modulate(xr, scr, shr, 1e-6)
+    yr.backward(dy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad)
+    _close(sc.grad, scr.grad, rtol=3e-2)
+    _close(sh.grad, shr.grad, rtol=3e-2)
+    g = torch.randn(B, 1, H, device=DEV, dtype=torch.bfloat16)
+    o = ops.gated_residual(x.detach(), y.detach(), g)
+    _close(o, ref.gated_residual(x.detach().float(), y.detach().float(), g.float()))
+
+
+def test_adamw_shard():
+    from mindspeed_mm_b200.ops import native
+    torch.manual_seed(0)
+    n = 128 * 1000
+    p = torch.randn(n, device=DEV)
+    m = torch.zeros(n, device=DEV)
+    v = torch.zeros(n, device=DEV)
+    p16 = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    for step in (1, 2, 3):
+        g = torch.randn(n, device=DEV, dtype=torch.bfloat16)
+        native.adamw_shard(p, m, v, g, p16, 1e-2, 0.9, 0.999, 1e-8, 0.1, step, n // 2, 0.5)
+        ref.adamw_step(pr[:n // 2], mr[:n // 2], vr[:n // 2], g[:n // 2], 1e-2, 0.9, 0.999, 1e-8, 0.1, step, 0.5)
+        ref.adamw_step(pr[n // 2:], mr[n // 2:], vr[n // 2:], g[n // 2:], 1e-2, 0.9, 0.999, 1e-8, 0.0, step, 0.5)
+    _close(p, pr, rtol=1e-4, atol=1e-5)
+    _close(m, mr, rtol=1e-4, atol=1e-6)
+    _close(p16, pr, rtol=1e-2, atol=1e-2)
+
+
+GEMM_SHAPES = [(128, 256, 64), (256, 512, 256), (1000, 768, 520), (8192, 4608, 3584), (333, 1280, 1176), (77, 136, 72)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_nt(M, N, K):
+    from mindspeed_mm_b200.ops import native
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    c = native.gemm_nt(a, b, bias)
+    r = a.float() @ b.float().t() + bias.float()
+    _close(c, r, rtol=1e-2, atol=1e-2 * math.sqrt(K))
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_nn(M, N, K):
+    from mindspeed_mm_b200.ops import native
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(K, N, device=DEV, dtype=torch.bfloat16)
+    c = native.gemm_nn(a, b)
+    _close(c, a.float() @ b.float(), rtol=1e-2, atol=1e-2 * math.sqrt(K))
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_tn(M, N, K):
+    from mindspeed_mm_b200.ops import native
+    torch.manual_seed(0)
+    a = torch.randn(K, M, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(K, N, device=DEV, dtype=torch.bfloat16)
+    c = native.gemm_tn(a, b)
+    _close(c, a.float().t() @ b.float(), rtol=1e-2, atol=1e-2 * math.sqrt(K))
+
+
+def test_linear_autograd():
+    torch.manual_seed(0)
+    x = torch.randn(4, 130, 1024, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (0.05 * torch.randn(768, 1024, device=DEV)).to(torch.bfloat16).requires_grad_()
+    b = torch.randn(768, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    dy = torch.randn(4, 130, 768, device=DEV, dtype=torch.bfloat16)
+    y = ops.linear(x, w, b)
+    y.backward(dy)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(dy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad)
+    _close(w.grad, wr.grad, atol=0.5)
+    _close(b.grad, br.grad, atol=0.5)

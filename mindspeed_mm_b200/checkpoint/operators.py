@@ -1,0 +1,306 @@
+"""Weight-conversion operator algebra.
+
+A converter is a list of reversible operators applied to a flat ``{name: tensor}`` dict:
+``apply`` maps source (HuggingFace) names/layouts to target names/layouts, ``revert`` goes back.
+The set mirrors what the reference's converters are built from
+(checkpoint/vlm_model/operator.py:95-614: Rename / Merge / QKVMerge / UpGateMerge / Relocate / Tie /
+ResizeEmbed plus Row/Col/GLU tensor-parallel splits) but is written against a tiny pattern language:
+``{i}`` in a name stands for a layer index and is matched as ``(\\d+)``; more placeholders (``{e}``) work
+the same way.  All operators are pure functions of the dict, CPU only.
+"""
+from __future__ import annotations
+
+import re
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+
+import torch
+from torch import Tensor
+
+StateDict = Dict[str, Tensor]
+_PH = re.compile(r"\{(\w+)\}")
+
+
+def _compile(pattern: str) -> "re.Pattern[str]":
+    out, pos = "", 0
+    for m in _PH.finditer(pattern):
+        out += re.escape(pattern[pos:m.start()]) + f"(?P<{m.group(1)}>\\d+)"
+        pos = m.end()
+    return re.compile("^" + out + re.escape(pattern[pos:]) + "$")
+
+
+def _fill(pattern: str, groups: Dict[str, str]) -> str:
+    return _PH.sub(lambda m: groups[m.group(1)], pattern)
+
+
+class Operator:
+    def apply(self, sd: StateDict) -> None:
+        raise NotImplementedError
+
+    def revert(self, sd: StateDict) -> None:
+        raise NotImplementedError
+
+
+class Rename(Operator):
+    """``src`` -> ``dst`` for every index binding that matches."""
+
+    def __init__(self, src: str, dst: str):
+        self.src, self.dst = src, dst
+
+    def _move(self, sd, a, b):
+        rx = _compile(a)
+        for k in list(sd.keys()):
+            m = rx.match(k)
+            if m:
+                sd[_fill(b, m.groupdict())] = sd.pop(k)
+
+    def apply(self, sd):
+        self._move(sd, self.src, self.dst)
+
+    def revert(self, sd):
+        self._move(sd, self.dst, self.src)
+
+
+class RenamePrefix(Operator):
+    def __init__(self, src: str, dst: str):
+        self.src, self.dst = src, dst
+
+    def _move(self, sd, a, b):
+        for k in list(sd.keys()):
+            if k.startswith(a):
+                sd[b + k[len(a):]] = sd.pop(k)
+
+    def apply(self, sd):
+        self._move(sd, self.src, self.dst)
+
+    def revert(self, sd):
+        self._move(sd, self.dst, self.src)
+
+
+class Merge(Operator):
+    """Concatenate several source tensors along ``dim`` into one (gate|up, q|k|v, ...)."""
+
+    def __init__(self, srcs: Sequence[str], dst: str, dim: int = 0):
+        self.srcs, self.dst, self.dim = list(srcs), dst, dim
+        self._sizes: Dict[str, List[int]] = {}
+
+    def apply(self, sd):
+        rx = _compile(self.srcs[0])
+        for k in list(sd.keys()):
+            m = rx.match(k)
+            if not m:
+                continue
+            g = m.groupdict()
+            names = [_fill(s, g) for s in self.srcs]
+            if not all(n in sd for n in names):
+                continue
+            parts = [sd.pop(n) for n in names]
+            d = _fill(self.dst, g)
+            self._sizes[d] = [p.shape[self.dim] for p in parts]
+            sd[d] = torch.cat(parts, dim=self.dim)
+
+    def revert(self, sd, sizes: Optional[Sequence[int]] = None):
+        rx = _compile(self.dst)
+        for k in list(sd.keys()):
+            m = rx.match(k)
+            if not m:
+                continue
+            t = sd.pop(k)
+            sz = sizes or self._sizes.get(k) or self.split_sizes(t.shape[self.dim])
+            for n, part in zip(self.srcs, torch.split(t, list(sz), dim=self.dim)):
+                sd[_fill(n, m.groupdict())] = part.contiguous()
+
+    def split_sizes(self, total: int) -> List[int]:
+        n = len(self.srcs)
+        if total % n:
+            raise ValueError(f"cannot split {total} evenly into {n} for {self.dst}")
+        return [total // n] * n
+
+
+class QKVMerge(Merge):
+    """q|k|v -> fused qkv.  ``interleave_groups`` > 0 writes Megatron's per-KV-group interleave
+    ``[q_g0.., k_g0, v_g0, q_g1.., k_g1, v_g1, ...]`` (checkpoint/vlm_model/operator.py:12-46)
+    instead of plain concatenation."""
+
+    def __init__(self, srcs, dst, num_heads: int, num_kv_heads: int, head_dim: int, interleave_groups: bool = False):
+        super().__init__(srcs, dst, 0)
+        self.nh, self.nkv, self.hd, self.inter = num_heads, num_kv_heads, head_dim, interleave_groups
+
+    def split_sizes(self, total):
+        return [self.nh * self.hd, self.nkv * self.hd, self.nkv * self.hd]
+
+    def apply(self, sd):
+        super().apply(sd)
+        if self.inter:
+            rx = _compile(self.dst)
+            for k in list(sd.keys()):
+                if rx.match(k):
+                    sd[k] = concat_to_interleaved(sd[k], self.nkv, self.split_sizes(0))
+
+    def revert(self, sd, sizes=None):
+        if self.inter:
+            rx = _compile(self.dst)
+            per_group = [self.nh // self.nkv * self.hd, self.hd, self.hd]
+            for k in list(sd.keys()):
+                if rx.match(k):
+                    sd[k] = interleaved_to_concat(sd[k], self.nkv, per_group)
+        super().revert(sd, self.split_sizes(0))
+
+
+def concat_to_interleaved(qkv: Tensor, groups: int, sizes: Sequence[int]) -> Tensor:
+    q, k, v = torch.split(qkv, list(sizes), dim=0)
+    parts = [torch.chunk(x, groups, dim=0) for x in (q, k, v)]
+    return torch.cat([p for grp in zip(*parts) for p in grp], dim=0)
+
+
+def interleaved_to_concat(qkv: Tensor, groups: int, per_group_sizes: Sequence[int]) -> Tensor:
+    chunks = [torch.split(c, list(per_group_sizes), dim=0) for c in torch.chunk(qkv, groups, dim=0)]
+    return torch.cat([c[i] for i in range(3) for c in chunks], dim=0)
+
+
+class Reshape(Operator):
+    def __init__(self, name: str, to_shape: Callable[[Tensor], Sequence[int]], from_shape: Callable[[Tensor], Sequence[int]]):
+        self.name, self.to_shape, self.from_shape = name, to_shape, from_shape
+
+    def _do(self, sd, fn):
+        rx = _compile(self.name)
+        for k in list(sd.keys()):
+            if rx.match(k):
+                sd[k] = sd[k].reshape(*fn(sd[k]))
+
+    def apply(self, sd):
+        self._do(sd, self.to_shape)
+
+    def revert(self, sd):
+        self._do(sd, self.from_shape)
+
+
+class Tie(Operator):
+    """Target keeps one copy; revert re-creates the tied alias (tied embeddings)."""
+
+    def __init__(self, kept: str, alias: str):
+        self.kept, self.alias = kept, alias
+
+    def apply(self, sd):
+        sd.pop(self.alias, None)
+
+    def revert(self, sd):
+        if self.kept in sd:
+            sd[self.alias] = sd[self.kept]
+
+
+class ResizeEmbed(Operator):
+    """Pad (new rows ~ N(mean, std) of the old ones) or truncate the vocabulary dimension."""
+
+    def __init__(self, name: str, new_vocab: int, seed: int = 0):
+        self.name, self.new_vocab, self.seed, self._orig = name, new_vocab, seed, {}
+
+    def _resize(self, t: Tensor, n: int) -> Tensor:
+        if t.shape[0] == n:
+            return t
+        out = torch.empty(n, *t.shape[1:], dtype=t.dtype)
+        c = min(n, t.shape[0])
+        out[:c] = t[:c]
+        if n > c:
+            g = torch.Generator().manual_seed(self.seed)
+            out[c:] = (torch.randn(n - c, *t.shape[1:], generator=g) * t.float().std() + t.float().mean()).to(t.dtype)
+        return out
+
+    def apply(self, sd):
+        if self.name in sd:
+            self._orig[self.name] = sd[self.name].shape[0]
+            sd[self.name] = self._resize(sd[self.name], self.new_vocab)
+
+    def revert(self, sd):
+        if self.name in sd and self.name in self._orig:
+            sd[self.name] = self._resize(sd[self.name], self._orig[self.name])
+
+
+class Drop(Operator):
+    def __init__(self, pattern: str):
+        self.rx = re.compile(pattern)
+
+    def apply(self, sd):
+        for k in list(sd.keys()):
+            if self.rx.search(k):
+                sd.pop(k)
+
+    def revert(self, sd):
+        pass
+
+
+class ExpertStack(Operator):
+    """Per-expert ``...experts.{e}.w`` tensors <-> one stacked ``[E, ...]`` tensor (optionally transposed so
+    that the stacked layout is [E, in, out] as the fused-MoE modules store it)."""
+
+    def __init__(self, src: str, dst: str, transpose: bool = True):
+        self.src, self.dst, self.transpose = src, dst, transpose
+
+    def apply(self, sd):
+        rx = _compile(self.src)
+        found: Dict[Tuple, Dict[int, Tensor]] = {}
+        for k in list(sd.keys()):
+            m = rx.match(k)
+            if m:
+                g = m.groupdict()
+                e = int(g.pop("e"))
+                found.setdefault(tuple(sorted(g.items())), {})[e] = sd.pop(k)
+        for key, experts in found.items():
+            ts = [experts[i].t() if self.transpose else experts[i] for i in range(len(experts))]
+            sd[_fill(self.dst, dict(key))] = torch.stack(ts).contiguous()
+
+    def revert(self, sd):
+        rx = _compile(self.dst)
+        for k in list(sd.keys()):
+            m = rx.match(k)
+            if m:
+                t = sd.pop(k)
+                for e in range(t.shape[0]):
+                    g = dict(m.groupdict(), e=str(e))
+                    sd[_fill(self.src, g)] = (t[e].t() if self.transpose else t[e]).contiguous()
+
+
+def apply_ops(sd: StateDict, ops: Iterable[Operator]) -> StateDict:
+    for op in ops:
+        op.apply(sd)
+    return sd
+
+
+def revert_ops(sd: StateDict, ops: Sequence[Operator]) -> StateDict:
+    for op in reversed(list(ops)):
+        op.revert(sd)
+    return sd
+
+
+# ------------------------------------------------------------------------------- tensor-parallel splits
+def split_col(t: Tensor, tp: int) -> List[Tensor]:
+    """Column-parallel linear: split the output dim (dim 0 of [out, in])."""
+    return [c.contiguous() for c in torch.chunk(t, tp, dim=0)]
+
+
+def split_row(t: Tensor, tp: int) -> List[Tensor]:
+    """Row-parallel linear: split the input dim (dim 1)."""
+    return [c.contiguous() for c in torch.chunk(t, tp, dim=1)] if t.dim() > 1 else [t] * tp
+
+
+def split_glu(t: Tensor, tp: int) -> List[Tensor]:
+    """Fused [gate | up] column-parallel: every rank takes its slice of gate AND of up."""
+    gate, up = torch.chunk(t, 2, dim=0)
+    return [torch.cat([g, u]).contiguous() for g, u in zip(torch.chunk(gate, tp), torch.chunk(up, tp))]
+
+
+def merge_glu(parts: Sequence[Tensor]) -> Tensor:
+    gates, ups = zip(*[torch.chunk(p, 2, dim=0) for p in parts])
+    return torch.cat([*gates, *ups])
+
+
+def split_qkv_concat(t: Tensor, tp: int, sizes: Sequence[int]) -> List[Tensor]:
+    """Plain-concatenated [q | k | v]: every rank takes its heads of each."""
+    q, k, v = torch.split(t, list(sizes), dim=0)
+    return [torch.cat(p).contiguous() for p in zip(torch.chunk(q, tp), torch.chunk(k, tp), torch.chunk(v, tp))]
+
+
+def merge_qkv_concat(parts: Sequence[Tensor], sizes: Sequence[int]) -> Tensor:
+    tp = len(parts)
+    per = [s // tp for s in sizes]
+    qs, ks, vs = zip(*[torch.split(p, per, dim=0) for p in parts])
+    return torch.cat([*qs, *ks, *vs])

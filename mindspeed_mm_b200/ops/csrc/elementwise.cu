@@ -11,18 +11,25 @@ constexpr int kThreads = 256;
 constexpr int kMaxVec = 4;  // cached 16-byte vectors per thread -> rows up to 256*4*8 = 8192 stay in registers
 
 // ------------------------------------------------------------------------------------------ RMSNorm
-__global__ void __launch_bounds__(kThreads) rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
-                                                               bf16* __restrict__ y, float* __restrict__ rstd_out,
-                                                               int T, int H, float eps) {
+// One 128-thread CTA per row at a time (several CTAs per SM keep enough rows in flight to cover HBM
+// latency); NV = 16-byte vectors cached per thread, so a row of up to 128*NV*8 elements is read once.
+constexpr int kRowThreads = 128;
+
+template <int NV>
+__global__ void __launch_bounds__(kRowThreads) rmsnorm_fwd_kernel(const bf16* __restrict__ x,
+                                                                   const bf16* __restrict__ w, bf16* __restrict__ y,
+                                                                   float* __restrict__ rstd_out, int T, int H,
+                                                                   float eps) {
     __shared__ float red[72];
     const int nvec = H >> 3;
+    const Vec8* wr = reinterpret_cast<const Vec8*>(w);
     for (int row = blockIdx.x; row < T; row += gridDim.x) {
         const Vec8* xr = reinterpret_cast<const Vec8*>(x + (size_t)row * H);
-        Vec8 cache[kMaxVec];
+        Vec8 cache[NV];
         float ss = 0.f;
 #pragma unroll
-        for (int j = 0; j < kMaxVec; ++j) {
-            int i = threadIdx.x + j * kThreads;
+        for (int j = 0; j < NV; ++j) {
+            int i = threadIdx.x + j * kRowThreads;
             if (i < nvec) {
                 cache[j] = xr[i];
                 float f[8];
@@ -31,20 +38,13 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_fwd_kernel(const bf16* __res
                 for (int k = 0; k < 8; ++k) ss += f[k] * f[k];
             }
         }
-        for (int i = threadIdx.x + kMaxVec * kThreads; i < nvec; i += kThreads) {
-            float f[8];
-            unpack8(xr[i], f);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) ss += f[k] * f[k];
-        }
         ss = block_sum(ss, red);
         const float rstd = rsqrtf(ss / (float)H + eps);
         if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
         Vec8* yr = reinterpret_cast<Vec8*>(y + (size_t)row * H);
-        const Vec8* wr = reinterpret_cast<const Vec8*>(w);
 #pragma unroll
-        for (int j = 0; j < kMaxVec; ++j) {
-            int i = threadIdx.x + j * kThreads;
+        for (int j = 0; j < NV; ++j) {
+            int i = threadIdx.x + j * kRowThreads;
             if (i < nvec) {
                 float f[8], g[8];
                 unpack8(cache[j], f);
@@ -54,75 +54,77 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_fwd_kernel(const bf16* __res
                 yr[i] = pack8(f);
             }
         }
-        for (int i = threadIdx.x + kMaxVec * kThreads; i < nvec; i += kThreads) {
-            float f[8], g[8];
-            unpack8(xr[i], f);
-            unpack8(wr[i], g);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) f[k] = f[k] * rstd * g[k];
-            yr[i] = pack8(f);
-        }
     }
 }
 
 // dx = rstd * (g - xhat * mean(g * xhat)),  g = dy * w,  xhat = x * rstd;   dw += dy * xhat.
 // Each CTA walks rows with stride gridDim.x and keeps its dw partial in registers; partials go to
-// scratch [gridDim.x, H] fp32 and a second kernel folds them.  Requires H <= kThreads*kMaxVec*8.
-__global__ void __launch_bounds__(kThreads) rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
-                                                               const bf16* __restrict__ dy,
-                                                               const float* __restrict__ rstd_in,
-                                                               bf16* __restrict__ dx, float* __restrict__ dw_partial,
-                                                               int T, int H) {
+// scratch [gridDim.x, H] fp32 and a second kernel folds them.  Requires H <= 128*NV*8.
+template <int NV>
+__global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_kernel(const bf16* __restrict__ x,
+                                                                   const bf16* __restrict__ w,
+                                                                   const bf16* __restrict__ dy,
+                                                                   const float* __restrict__ rstd_in,
+                                                                   bf16* __restrict__ dx,
+                                                                   float* __restrict__ dw_partial, int T, int H) {
     __shared__ float red[72];
     const int nvec = H >> 3;
-    float wreg[kMaxVec][8], dwacc[kMaxVec][8];
+    float dwacc[NV][8];
     const Vec8* wr = reinterpret_cast<const Vec8*>(w);
 #pragma unroll
-    for (int j = 0; j < kMaxVec; ++j) {
-        int i = threadIdx.x + j * kThreads;
+    for (int j = 0; j < NV; ++j)
 #pragma unroll
         for (int k = 0; k < 8; ++k) dwacc[j][k] = 0.f;
-        if (i < nvec) unpack8(wr[i], wreg[j]);
-    }
     for (int row = blockIdx.x; row < T; row += gridDim.x) {
         const Vec8* xr = reinterpret_cast<const Vec8*>(x + (size_t)row * H);
         const Vec8* gr = reinterpret_cast<const Vec8*>(dy + (size_t)row * H);
         const float rstd = rstd_in[row];
-        float xh[kMaxVec][8], g[kMaxVec][8];
+        Vec8 xc[NV], gc[NV];
         float dot = 0.f;
 #pragma unroll
-        for (int j = 0; j < kMaxVec; ++j) {
-            int i = threadIdx.x + j * kThreads;
+        for (int j = 0; j < NV; ++j) {
+            int i = threadIdx.x + j * kRowThreads;
             if (i < nvec) {
-                float a[8], b[8];
-                unpack8(xr[i], a);
-                unpack8(gr[i], b);
+                xc[j] = xr[i];
+                gc[j] = gr[i];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            int i = threadIdx.x + j * kRowThreads;
+            if (i < nvec) {
+                float a[8], b[8], ww[8];
+                unpack8(xc[j], a);
+                unpack8(gc[j], b);
+                unpack8(wr[i], ww);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
-                    xh[j][k] = a[k] * rstd;
-                    dwacc[j][k] += b[k] * xh[j][k];
-                    g[j][k] = b[k] * wreg[j][k];
-                    dot += g[j][k] * xh[j][k];
+                    const float xh = a[k] * rstd;
+                    dwacc[j][k] += b[k] * xh;
+                    dot += b[k] * ww[k] * xh;
                 }
             }
         }
         dot = block_sum(dot, red) / (float)H;
         Vec8* dxr = reinterpret_cast<Vec8*>(dx + (size_t)row * H);
 #pragma unroll
-        for (int j = 0; j < kMaxVec; ++j) {
-            int i = threadIdx.x + j * kThreads;
+        for (int j = 0; j < NV; ++j) {
+            int i = threadIdx.x + j * kRowThreads;
             if (i < nvec) {
-                float o[8];
+                float a[8], b[8], ww[8], o[8];
+                unpack8(xc[j], a);
+                unpack8(gc[j], b);
+                unpack8(wr[i], ww);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) o[k] = rstd * (g[j][k] - xh[j][k] * dot);
+                for (int k = 0; k < 8; ++k) o[k] = rstd * (b[k] * ww[k] - a[k] * rstd * dot);
                 dxr[i] = pack8(o);
             }
         }
     }
     float* out = dw_partial + (size_t)blockIdx.x * H;
 #pragma unroll
-    for (int j = 0; j < kMaxVec; ++j) {
-        int i = threadIdx.x + j * kThreads;
+    for (int j = 0; j < NV; ++j) {
+        int i = threadIdx.x + j * kRowThreads;
         if (i < nvec) {
             float4* o4 = reinterpret_cast<float4*>(out + i * 8);
             o4[0] = make_float4(dwacc[j][0], dwacc[j][1], dwacc[j][2], dwacc[j][3]);
@@ -131,12 +133,22 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_bwd_kernel(const bf16* __res
     }
 }
 
+// Folds [P, H] fp32 partials into bf16 [H]: one warp per 32 columns, lanes stride over P, then a
+// transposed shuffle-free reduction through shared memory.
 __global__ void fold_partials_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int P, int H) {
-    int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= H) return;
+    __shared__ float tile[8][33];
+    const int c = blockIdx.x * 32 + threadIdx.x;  // blockDim = (32, 8)
     float s = 0.f;
-    for (int p = 0; p < P; ++p) s += partial[(size_t)p * H + c];
-    out[c] = __float2bfloat16(s);
+    if (c < H)
+        for (int p = threadIdx.y; p < P; p += 8) s += partial[(size_t)p * H + c];
+    tile[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < H) {
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t += tile[k][threadIdx.x];
+        out[c] = __float2bfloat16(t);
+    }
 }
 
 // ------------------------------------------------------------------------------------------ SwiGLU
@@ -462,22 +474,34 @@ inline int grid_for(long long work_items, int threads, int per_sm = 8) {
 // ------------------------------------------------------------------------------------------ C ABI
 MM_API int mm_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int H, float eps,
                           cudaStream_t st) {
-    if (H % 8) return -1;
-    int grid = T < 148 * 8 ? T : 148 * 8;
-    rmsnorm_fwd_kernel<<<grid, kThreads, 0, st>>>((const bf16*)x, (const bf16*)w, (bf16*)y, rstd, T, H, eps);
+    if (H % 8 || H > kRowThreads * 8 * 8) return -1;
+    const int grid = T < 148 * 12 ? T : 148 * 12;
+    const int nv = (H / 8 + kRowThreads - 1) / kRowThreads;
+#define MM_RMS_FWD(NV) \
+    rmsnorm_fwd_kernel<NV><<<grid, kRowThreads, 0, st>>>((const bf16*)x, (const bf16*)w, (bf16*)y, rstd, T, H, eps)
+    if (nv <= 2) MM_RMS_FWD(2);
+    else if (nv <= 4) MM_RMS_FWD(4);
+    else MM_RMS_FWD(8);
+#undef MM_RMS_FWD
     return (int)cudaGetLastError();
 }
 
-MM_API int mm_rmsnorm_bwd_grid(int T) { return T < 148 * 4 ? T : 148 * 4; }
+MM_API int mm_rmsnorm_bwd_grid(int T) { return T < 148 * 6 ? T : 148 * 6; }
 
 // dw_partial: scratch of mm_rmsnorm_bwd_grid(T) * H floats.
 MM_API int mm_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx, void* dw,
                           float* dw_partial, int T, int H, cudaStream_t st) {
-    if (H % 8 || H > kThreads * kMaxVec * 8) return -1;
-    int grid = mm_rmsnorm_bwd_grid(T);
-    rmsnorm_bwd_kernel<<<grid, kThreads, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, (bf16*)dx,
-                                                  dw_partial, T, H);
-    fold_partials_kernel<<<(H + 255) / 256, 256, 0, st>>>(dw_partial, (bf16*)dw, grid, H);
+    if (H % 8 || H > kRowThreads * 8 * 8) return -1;
+    const int grid = mm_rmsnorm_bwd_grid(T);
+    const int nv = (H / 8 + kRowThreads - 1) / kRowThreads;
+#define MM_RMS_BWD(NV)                                                                                              \
+    rmsnorm_bwd_kernel<NV><<<grid, kRowThreads, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, \
+                                                         (bf16*)dx, dw_partial, T, H)
+    if (nv <= 2) MM_RMS_BWD(2);
+    else if (nv <= 4) MM_RMS_BWD(4);
+    else MM_RMS_BWD(8);
+#undef MM_RMS_BWD
+    fold_partials_kernel<<<(H + 31) / 32, dim3(32, 8), 0, st>>>(dw_partial, (bf16*)dw, grid, H);
     return (int)cudaGetLastError();
 }
 

@@ -125,12 +125,12 @@ def mrope_cos_sin(position_ids: torch.Tensor, head_dim: int, theta: float,
 def rope3d_freqs(grid: Tuple[int, int, int], head_dim: int, theta: float = 10000.0, device=None):
     """Wan 3-D RoPE tables for a (F, H, W) token grid.  Returns cos, sin: [F*H*W, head_dim/2].
 
-    The head dim is split into (d - 2*(d//3), d//3, d//3) channels for (f, h, w); each
-    part is rotated as interleaved pairs at its own axis position.
+    The head dim is split into (d - 4*(d//6), 2*(d//6), 2*(d//6)) channels for (f, h, w) (44/42/42 for
+    d = 128); each part is rotated as interleaved pairs at its own axis position.
     """
     f, h, w = grid
     d = head_dim
-    dims = (d - 2 * (d // 3), d // 3, d // 3)
+    dims = (d - 4 * (d // 6), 2 * (d // 6), 2 * (d // 6))
     outs = []
     for n, dim in zip((f, h, w), dims):
         inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float64, device=device)[: dim // 2] / dim))

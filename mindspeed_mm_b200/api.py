@@ -53,6 +53,9 @@ def default_init_fn(std: float = 0.02, seed: int = 0):
                 p.data.zero_()
             else:
                 p.data.fill_(1.0)
+        for m in module.modules():
+            if hasattr(m, "post_init"):
+                m.post_init()
     return init
 
 
@@ -113,4 +116,7 @@ def stable_init_fn(std: float = 0.02, seed: int = 0):
                 p.data.zero_()
             else:
                 p.data.fill_(1.0)
+        for m in module.modules():
+            if hasattr(m, "post_init"):
+                m.post_init()
     return init

@@ -248,8 +248,21 @@ class VisionBlock(nn.Module):
         self.norm2 = RMSNorm(c.hidden_size, c.rms_norm_eps)
         self.attn_qkv = Linear(c.hidden_size, 3 * c.hidden_size, bias=True)
         self.attn_proj = Linear(c.hidden_size, c.hidden_size, bias=True)
-        self.mlp_gate_up = Linear(c.hidden_size, 2 * c.intermediate_size, bias=True)
-        self.mlp_down = Linear(c.intermediate_size, c.hidden_size, bias=True)
+        # the FFN width is padded to a multiple of 64 (3420 -> 3456) so that every GEMM operand keeps
+        # 16-byte aligned rows for TMA; the pad rows/columns are zero and contribute nothing
+        self.ffn, self.ffn_padded = c.intermediate_size, (c.intermediate_size + 63) // 64 * 64
+        self.mlp_gate_up = Linear(c.hidden_size, 2 * self.ffn_padded, bias=True)
+        self.mlp_down = Linear(self.ffn_padded, c.hidden_size, bias=True)
+
+    @torch.no_grad()
+    def post_init(self):
+        """Zero the padding of the FFN so the padded model computes exactly the unpadded one."""
+        f, fp = self.ffn, self.ffn_padded
+        if fp != f:
+            for t in (self.mlp_gate_up.weight, self.mlp_gate_up.bias):
+                t[f:fp].zero_()
+                t[fp + f:].zero_()
+            self.mlp_down.weight[:, f:].zero_()
 
     def forward(self, x, cos, sin, cu_seqlens, max_seqlen):
         T = x.shape[0]

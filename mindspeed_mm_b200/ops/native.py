@@ -48,6 +48,7 @@ def _declare(L):
         "mm_gated_residual": [_p, _p, _p, _p, _ll, _i, _i, _p],
         "mm_adamw": [_p, _p, _p, _p, _i, _p, _ll, _ll, _f, _f, _f, _f, _f, _f, _f, _f, _p, _p],
         "mm_gemm_bf16": [_p, _p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _p, _p],
+        "mm_ce_fwd_bwd": [_p, _ll, _p, _p, _i, _i, _i, _p],
     }
     for name, args in sig.items():
         if hasattr(L, name):
@@ -403,7 +404,56 @@ def fmha_supported(q, k, v) -> bool:
 
 
 def lce_supported(h, w) -> bool:
-    return False
+    return gemm_supported(h, w) and h.dim() == 2
+
+
+class _LinearCE(torch.autograd.Function):
+    """loss_sum = sum_t CE(h_t W^T, label_t).  Forward already produces both gradients:
+    logits GEMM (tcgen05) -> in-place softmax-minus-onehot kernel -> dgrad and wgrad GEMMs (tcgen05);
+    backward only scales them by the incoming scalar.  Rows are processed in chunks so that the bf16
+    logits buffer stays a bounded slab (the reference chunks for the same reason:
+    fsdp/features/memory/chunkloss/chunkloss.py:6-95)."""
+
+    @staticmethod
+    def forward(ctx, h, w, labels, ignore_index, chunk):
+        T, H = h.shape
+        V = w.shape[0]
+        h = h.contiguous()
+        labels = labels.contiguous()
+        row_loss = torch.empty(T, dtype=torch.float32, device=h.device)
+        dh = torch.empty_like(h)
+        dw = torch.empty_like(w)
+        chunk = min(chunk, T)
+        logits = torch.empty(chunk, V, dtype=torch.bfloat16, device=h.device)
+        dw_acc = None
+        n_chunks = (T + chunk - 1) // chunk
+        for c in range(n_chunks):
+            a, b = c * chunk, min(T, (c + 1) * chunk)
+            z = logits[: b - a]
+            gemm_nt(h[a:b], w, out=z)
+            _check(lib().mm_ce_fwd_bwd(z.data_ptr(), z.stride(0), labels[a:b].data_ptr(), row_loss[a:b].data_ptr(),
+                                       b - a, V, ignore_index, _st()), "ce_fwd_bwd")
+            gemm_nn(z, w, out=dh[a:b])
+            if n_chunks == 1:
+                gemm_tn(z, h[a:b], out=dw)
+            else:
+                part = gemm_tn(z, h[a:b])
+                dw_acc = part.float() if dw_acc is None else dw_acc.add_(part)
+        if dw_acc is not None:
+            dw.copy_(dw_acc)
+        ctx.save_for_backward(dh, dw)
+        return row_loss.sum()
+
+    @staticmethod
+    def backward(ctx, g):
+        dh, dw = ctx.saved_tensors
+        gs = g.to(dh.dtype)
+        return dh.mul_(gs), dw.mul_(gs), None, None, None
+
+
+def linear_cross_entropy(h, w, labels, ignore_index=-100, chunk=8192):
+    loss = _LinearCE.apply(h, w, labels, ignore_index, chunk)
+    return loss, (labels != ignore_index).sum()
 
 
 def grouped_gemm_supported(x, w) -> bool:

@@ -166,6 +166,8 @@ class Unit:
         self.unsharded = False
         self.ready_event = None
         self.index = -1
+        self.recompute = True          # False: keep the autograd graph (used for the loss head)
+        self.pending_reduce = False    # non-recompute unit whose gradients wait to be reduced
 
     @property
     def trainable(self):
@@ -179,7 +181,8 @@ class FSDPEngine:
                  device: torch.device | str = "cpu", param_dtype: torch.dtype = torch.bfloat16,
                  reduce_dtype: torch.dtype = torch.float32, opt: Optional[OptimConfig] = None,
                  recompute: bool = True, grad_accum_steps: int = 1, prefetch: int = 1,
-                 comm: str = "auto", grad_divide: Optional[float] = None):
+                 comm: str = "auto", grad_divide: Optional[float] = None,
+                 no_recompute: Sequence[str] = ("lm_head",)):
         self.group = group
         self.world = dist.get_world_size(group) if (dist.is_initialized() and group is not False) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
@@ -193,6 +196,7 @@ class FSDPEngine:
         self.units: List[Unit] = [Unit(n, m, self) for n, m in units]
         for i, u in enumerate(self.units):
             u.index = i
+            u.recompute = recompute and u.name not in no_recompute
         self._by_module: Dict[int, Unit] = {id(u.module): u for u in self.units}
         self.cuda = self.device.type == "cuda"
         self.comm_stream = torch.cuda.Stream(self.device) if self.cuda else None
@@ -281,6 +285,14 @@ class FSDPEngine:
             out = module(*args, **kwargs)
             self.reshard(u)
             return out
+        if not u.recompute:
+            # Plain autograd through the unit (its graph is kept).  Its gradients are complete once any
+            # earlier unit starts its backward (or at finish_step), which is where they are reduced.
+            self.unshard(u)
+            self.wait_unshard(u)
+            self._prefetch_forward(u)
+            u.pending_reduce = u.trainable
+            return module(*args, **kwargs)
         tensors, spec = _split_args(args, kwargs)
         outs = _UnitFn.apply(self, u, spec, self._dummy, *tensors)
         return outs[0] if len(outs) == 1 and not u._tuple_out else outs
@@ -296,6 +308,14 @@ class FSDPEngine:
                 self.unshard(self.units[u.index - k])
 
     # ------------------------------------------------------------------ gradient reduce + update
+    def flush_pending(self) -> None:
+        for u in self.units:
+            if u.pending_reduce:
+                u.pending_reduce = False
+                if any(p.grad is not None for g in u.groups for _, p in g.named_params):
+                    self.reduce_and_update(u)
+                self.reshard(u)
+
     def reduce_and_update(self, u: Unit) -> None:
         last_micro = (self.micro_step + 1) % self.grad_accum_steps == 0
         for g in u.groups:
@@ -351,6 +371,7 @@ class FSDPEngine:
     def finish_step(self, lr: Optional[float] = None) -> Optional[torch.Tensor]:
         """Call after the last backward of an optimizer step.  Applies deferred updates (with the
         global-norm clip) and joins the side stream.  Returns the gradient norm when one was computed."""
+        self.flush_pending()
         if self.cuda:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
         norm = None
@@ -515,6 +536,7 @@ class _UnitFn(torch.autograd.Function):
     def backward(ctx, *gouts):
         engine, u = ctx.engine, ctx.u
         tensors = [t.detach().requires_grad_(need) for t, need in zip(ctx.saved_tensors, ctx.needs)]
+        engine.flush_pending()
         engine.unshard(u)
         engine.wait_unshard(u)
         engine._prefetch_backward(u)

@@ -181,3 +181,20 @@ def test_linear_autograd():
     _close(x.grad, xr.grad)
     _close(w.grad, wr.grad, atol=0.5)
     _close(b.grad, br.grad, atol=0.5)
+
+
+@pytest.mark.parametrize("T,H,V", [(300, 512, 32000), (1024, 1024, 152064)])
+def test_linear_cross_entropy(T, H, V):
+    torch.manual_seed(0)
+    h = torch.randn(T, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (0.02 * torch.randn(V, H, device=DEV)).to(torch.bfloat16).requires_grad_()
+    lab = torch.randint(0, V, (T,), device=DEV)
+    lab[::7] = -100
+    loss, n = ops.linear_cross_entropy(h, w, lab)
+    (loss / n).backward()
+    hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lr, nr = ref.linear_cross_entropy(hr, wr, lab)
+    (lr / nr).backward()
+    assert abs(float(loss / n) - float(lr / nr)) < 2e-2 * float(lr / nr)
+    _close(h.grad, hr.grad, rtol=5e-2, atol=1e-5)
+    _close(w.grad, wr.grad, rtol=5e-2, atol=1e-5)

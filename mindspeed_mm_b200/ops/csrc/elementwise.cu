@@ -585,3 +585,62 @@ MM_API int mm_adamw(float* p, float* m, float* v, const void* g, int g_is_bf16, 
                                                   bc1, bc2, gscale, scale_ptr);
     return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------ no-alloc variant
+// RMSNorm backward with its dw partials in a fixed device array instead of caller memory; see mm_noalloc.h
+// for who needs this and for the rules (size limits, first call outside capture, calls share the array).
+#include <mutex>
+#include "mm_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_rms_partials[MM_NOALLOC_MAX_CTAS * MM_NOALLOC_MAX_H];
+
+namespace {
+constexpr int kNoAllocMaxDevices = 64;
+float* g_noalloc_ptr[kNoAllocMaxDevices] = {};
+std::mutex g_noalloc_mu;
+
+// In host code the array's name is only a handle; the kernel needs the address the current device gave it.
+int noalloc_workspace(float** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) return MM_NOALLOC_E_SYMBOL;
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_noalloc_rms_partials) != cudaSuccess || !p) {
+            (void)cudaGetLastError();
+            return MM_NOALLOC_E_SYMBOL;
+        }
+        g_noalloc_ptr[dev] = static_cast<float*>(p);
+    }
+    *out = g_noalloc_ptr[dev];
+    return 0;
+}
+}  // namespace
+
+MM_API const char* mm_noalloc_strerror(int code) {
+    switch (code) {
+        case 0: return "ok";
+        case MM_NOALLOC_E_SIZE:
+            return "mm_rmsnorm_bwd_noalloc: need T >= 1 and H a multiple of 8 with H <= 4096 (fixed workspace)";
+        case MM_NOALLOC_E_SYMBOL:
+            return "mm_rmsnorm_bwd_noalloc: could not resolve the device address of the built-in workspace";
+        default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
+    }
+}
+
+MM_API int mm_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* dy, const float* rstd, void* dx, void* dw,
+                                  int T, int H, cudaStream_t st) {
+    if (T < 1 || H < 8 || H % 8 || H > MM_NOALLOC_MAX_H) return MM_NOALLOC_E_SIZE;
+    float* partial = nullptr;
+    if (int rc = noalloc_workspace(&partial)) return rc;
+    const int grid = T < MM_NOALLOC_MAX_CTAS ? T : MM_NOALLOC_MAX_CTAS;
+    const int nv = (H / 8 + kRowThreads - 1) / kRowThreads;
+    if (nv <= 2)
+        rmsnorm_bwd_kernel<2><<<grid, kRowThreads, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd,
+                                                            (bf16*)dx, partial, T, H);
+    else
+        rmsnorm_bwd_kernel<4><<<grid, kRowThreads, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd,
+                                                            (bf16*)dx, partial, T, H);
+    fold_partials_kernel<<<(H + 31) / 32, dim3(32, 8), 0, st>>>(partial, (bf16*)dw, grid, H);
+    return (int)cudaGetLastError();
+}

@@ -435,9 +435,9 @@ class Qwen25VLModel(nn.Module):
     # -- FSDP plan -------------------------------------------------------------------------
     def fsdp_units(self) -> List[Tuple[str, nn.Module]]:
         """Modules that are sharded/gathered as one unit, in execution order."""
-        units = [("visual.patch_embed", self.visual.patch_embed)]
+        units = [("embed_tokens", self.embed_tokens), ("visual.patch_embed", self.visual.patch_embed)]
         units += [(f"visual.blocks.{i}", b) for i, b in enumerate(self.visual.blocks)]
-        units += [("visual.merger", self.visual.merger), ("embed_tokens", self.embed_tokens)]
+        units += [("visual.merger", self.visual.merger)]
         units += [(f"layers.{i}", l) for i, l in enumerate(self.layers)]
         units += [("lm_head", self.lm_head)]
         return units

@@ -1,0 +1,267 @@
+// Collectives issued from kernels over NVLink peer memory (no NCCL on this path).
+//
+// Every rank owns a symmetric arena (same layout on every GPU, peer base pointers exchanged once).  The
+// kernels below take a table of peer pointers and use plain loads/stores on them: NVSwitch gives every
+// pair full bandwidth, so each collective is one hop and "pull" based - the consumer reads what it needs
+// from the producers' memory:
+//
+//   mm_p2p_allgather      full[p*S + i] = shard_p[i]                      (ZeRO-3 parameter gather)
+//   mm_p2p_rs_adamw       g = sum_p grad_p[r*S + i] / div  (bf16 on the wire, fp32 accumulate)
+//                         -> AdamW on this rank's fp32 master/moments -> bf16 shard    (one pass)
+//   mm_p2p_rs             same reduction, written (or accumulated) as fp32 for a deferred update
+//
+// They use no shared memory and few registers, so they co-reside on SMs that a persistent tcgen05 GEMM
+// (1 CTA/SM, all shared memory) is using, and overlap with it from a side stream.
+//
+// Cross-rank ordering uses sequence-numbered flags in the arena (st.release.sys / ld.acquire.sys):
+//   ready[slot]        written by the owner once its gradients for publication `seq` are in `slot`
+//   done[slot][peer]   written by each reader into the OWNER's arena once it has finished reading
+// Waits are bounded (~8 s); on timeout the kernel records MM_TIMEOUT_PEER in `status`, skips its work and
+// returns, leaving the context usable.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kMaxPeers = 16;
+struct Peers {
+    void* p[kMaxPeers];
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// true when *flag >= want (sequence numbers only grow); false after ~2^34 cycles.
+__device__ bool wait_flag_geq(const uint32_t* flag, uint32_t want) {
+    const long long t0 = clock64();
+    while ((int32_t)(ld_acquire_sys(flag) - want) < 0) {
+        if (clock64() - t0 > (1LL << 34)) return false;
+        __nanosleep(200);
+    }
+    return true;
+}
+
+struct uint4x {
+    uint4 v;
+};
+
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// ------------------------------------------------------------------------------------------ all-gather
+// Peers are visited in a rank-staggered round-robin of 64 KiB chunks so that at any moment every link
+// carries traffic and no owner is read by all ranks at once.
+__global__ void __launch_bounds__(256) p2p_allgather_kernel(Peers shards, uint4* __restrict__ full, long long shard_vec,
+                                                            int world, int rank) {
+    constexpr long long kChunk = 4096;  // uint4 per chunk = 64 KiB
+    const long long chunks_per_peer = (shard_vec + kChunk - 1) / kChunk;
+    const long long total_chunks = chunks_per_peer * world;
+    for (long long c = blockIdx.x; c < total_chunks; c += gridDim.x) {
+        const int hop = (int)(c % world);
+        const int peer = (rank + 1 + hop) % world;  // own shard comes last in each round
+        const long long chunk = c / world;
+        const long long base = chunk * kChunk;
+        const long long n = min(kChunk, shard_vec - base);
+        const uint4* src = reinterpret_cast<const uint4*>(shards.p[peer]) + base;
+        uint4* dst = full + peer * shard_vec + base;
+        for (long long i = threadIdx.x; i < n; i += 4 * 256) {
+            uint4 r[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (i + u * 256 < n) r[u] = ld_stream(src + i + u * 256);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (i + u * 256 < n) dst[i + u * 256] = r[u];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------ reduce-scatter (+AdamW)
+struct RSParams {
+    Peers grads;          // each rank's flat bf16 gradient buffer for this slot (full length)
+    Peers flags;          // each rank's flag block
+    long long shard_elems;
+    int world, rank, slot;
+    uint32_t seq;
+    float inv_div;
+    int* status;
+    uint32_t* counter;    // local, zero between launches
+};
+// flag block layout (uint32): ready[2] | done[2][kMaxPeers]
+__device__ __forceinline__ uint32_t* flag_ready(void* base, int slot) { return reinterpret_cast<uint32_t*>(base) + slot; }
+__device__ __forceinline__ uint32_t* flag_done(void* base, int slot, int peer) {
+    return reinterpret_cast<uint32_t*>(base) + 2 + slot * kMaxPeers + peer;
+}
+
+__device__ bool rs_prologue(const RSParams& P) {
+    __shared__ int ok_s;
+    if (threadIdx.x == 0) ok_s = 1;
+    __syncthreads();
+    // every CTA checks every peer itself: no CTA depends on another CTA of this launch
+    if (threadIdx.x < P.world && threadIdx.x != P.rank) {
+        if (!wait_flag_geq(flag_ready(P.flags.p[threadIdx.x], P.slot), P.seq)) {
+            atomicExch(P.status, MM_TIMEOUT_PEER);
+            ok_s = 0;
+        }
+    }
+    __syncthreads();
+    return ok_s != 0;
+}
+
+__device__ void rs_epilogue(const RSParams& P) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const uint32_t prev = atomicAdd(P.counter, 1u);
+        if (prev == gridDim.x - 1) {
+            *P.counter = 0;
+            __threadfence_system();
+            for (int p = 0; p < P.world; ++p)
+                if (p != P.rank) st_release_sys(flag_done(P.flags.p[p], P.slot, P.rank), P.seq);
+        }
+    }
+}
+
+__device__ __forceinline__ void reduce8(const RSParams& P, long long vec_idx, float* acc) {
+    const long long off = (long long)P.rank * (P.shard_elems >> 3) + vec_idx;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    uint4 r[kMaxPeers];
+#pragma unroll
+    for (int p = 0; p < kMaxPeers; ++p)
+        if (p < P.world) r[p] = ld_stream(reinterpret_cast<const uint4*>(P.grads.p[p]) + off);
+#pragma unroll
+    for (int p = 0; p < kMaxPeers; ++p)
+        if (p < P.world) {
+            float f[8];
+            unpack8(*reinterpret_cast<const Vec8*>(&r[p]), f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] += f[k];
+        }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] *= P.inv_div;
+}
+
+struct AdamParams {
+    float* p;
+    float* m;
+    float* v;
+    bf16* p16;
+    long long split;
+    float lr, b1, b2, eps, wd, bc1, bc2;
+};
+
+__global__ void __launch_bounds__(256) p2p_rs_adamw_kernel(RSParams P, AdamParams A) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        __threadfence_system();
+        st_release_sys(flag_ready(P.flags.p[P.rank], P.slot), P.seq);  // publish: my gradients are in place
+    }
+    if (!rs_prologue(P)) return;
+    const long long nvec = P.shard_elems >> 3;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+        float g[8];
+        reduce8(P, i, g);
+        float4 p0 = reinterpret_cast<float4*>(A.p)[2 * i], p1 = reinterpret_cast<float4*>(A.p)[2 * i + 1];
+        float4 m0 = reinterpret_cast<float4*>(A.m)[2 * i], m1 = reinterpret_cast<float4*>(A.m)[2 * i + 1];
+        float4 v0 = reinterpret_cast<float4*>(A.v)[2 * i], v1 = reinterpret_cast<float4*>(A.v)[2 * i + 1];
+        float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+        float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float decay = (i * 8 + k) < A.split ? A.wd : 0.f;
+            mm[k] = A.b1 * mm[k] + (1.f - A.b1) * g[k];
+            vv[k] = A.b2 * vv[k] + (1.f - A.b2) * g[k] * g[k];
+            pp[k] = pp[k] * (1.f - A.lr * decay) - A.lr * (mm[k] / A.bc1) / (sqrtf(vv[k] / A.bc2) + A.eps);
+        }
+        reinterpret_cast<float4*>(A.p)[2 * i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
+        reinterpret_cast<float4*>(A.p)[2 * i + 1] = make_float4(pp[4], pp[5], pp[6], pp[7]);
+        reinterpret_cast<float4*>(A.m)[2 * i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+        reinterpret_cast<float4*>(A.m)[2 * i + 1] = make_float4(mm[4], mm[5], mm[6], mm[7]);
+        reinterpret_cast<float4*>(A.v)[2 * i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+        reinterpret_cast<float4*>(A.v)[2 * i + 1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+        reinterpret_cast<Vec8*>(A.p16)[i] = pack8(pp);
+    }
+    rs_epilogue(P);
+}
+
+__global__ void __launch_bounds__(256) p2p_rs_kernel(RSParams P, float* __restrict__ out, int accumulate) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        __threadfence_system();
+        st_release_sys(flag_ready(P.flags.p[P.rank], P.slot), P.seq);
+    }
+    if (!rs_prologue(P)) return;
+    const long long nvec = P.shard_elems >> 3;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+        float g[8];
+        reduce8(P, i, g);
+        float4* o = reinterpret_cast<float4*>(out) + 2 * i;
+        if (accumulate) {
+            float4 a = o[0], b = o[1];
+            g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
+            g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+        }
+        o[0] = make_float4(g[0], g[1], g[2], g[3]);
+        o[1] = make_float4(g[4], g[5], g[6], g[7]);
+    }
+    rs_epilogue(P);
+}
+
+// Owner-side wait before a gradient slot is overwritten: all readers of publication `seq` are done.
+__global__ void p2p_wait_done_kernel(void* my_flags, int slot, uint32_t seq, int world, int rank, int* status) {
+    if (threadIdx.x < world && threadIdx.x != rank) {
+        if (!wait_flag_geq(flag_done(my_flags, slot, threadIdx.x), seq)) atomicExch(status, MM_TIMEOUT_PEER);
+    }
+}
+
+Peers make_peers(void* const* ptrs, int world) {
+    Peers P;
+    for (int i = 0; i < kMaxPeers; ++i) P.p[i] = i < world ? ptrs[i] : nullptr;
+    return P;
+}
+
+}  // namespace
+
+MM_API int mm_p2p_flag_bytes() { return (2 + 2 * kMaxPeers + 2) * 4; }
+
+// shard_ptrs[p]: address of rank p's shard (peer-mapped); full: local destination of world*shard_elems bf16.
+MM_API int mm_p2p_allgather(void* const* shard_ptrs, void* full, long long shard_elems, int world, int rank, int ctas,
+                            cudaStream_t st) {
+    if (world > kMaxPeers || shard_elems % 8) return -1;
+    p2p_allgather_kernel<<<ctas, 256, 0, st>>>(make_peers(shard_ptrs, world), (uint4*)full, shard_elems / 8, world, rank);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_p2p_rs_adamw(void* const* grad_ptrs, void* const* flag_ptrs, long long shard_elems, int world, int rank,
+                           int slot, unsigned seq, float inv_div, float* p, float* m, float* v, void* p16,
+                           long long split, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                           int* status, int ctas, cudaStream_t st) {
+    if (world > kMaxPeers || shard_elems % 8) return -1;
+    RSParams P{make_peers(grad_ptrs, world), make_peers(flag_ptrs, world), shard_elems, world, rank, slot, seq, inv_div,
+               status, reinterpret_cast<uint32_t*>(flag_ptrs[rank]) + 2 + 2 * kMaxPeers};
+    AdamParams A{p, m, v, (bf16*)p16, split, lr, b1, b2, eps, wd, bc1, bc2};
+    p2p_rs_adamw_kernel<<<ctas, 256, 0, st>>>(P, A);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_p2p_rs(void* const* grad_ptrs, void* const* flag_ptrs, long long shard_elems, int world, int rank, int slot,
+                     unsigned seq, float inv_div, float* out, int accumulate, int* status, int ctas, cudaStream_t st) {
+    if (world > kMaxPeers || shard_elems % 8) return -1;
+    RSParams P{make_peers(grad_ptrs, world), make_peers(flag_ptrs, world), shard_elems, world, rank, slot, seq, inv_div,
+               status, reinterpret_cast<uint32_t*>(flag_ptrs[rank]) + 2 + 2 * kMaxPeers};
+    p2p_rs_kernel<<<ctas, 256, 0, st>>>(P, out, accumulate);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_p2p_wait_done(void* my_flags, int slot, unsigned seq, int world, int rank, int* status, cudaStream_t st) {
+    p2p_wait_done_kernel<<<1, 32, 0, st>>>(my_flags, slot, seq, world, rank, status);
+    return (int)cudaGetLastError();
+}

@@ -49,6 +49,12 @@ def _declare(L):
         "mm_adamw": [_p, _p, _p, _p, _i, _p, _ll, _ll, _f, _f, _f, _f, _f, _f, _f, _f, _p, _p],
         "mm_gemm_bf16": [_p, _p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _p, _p],
         "mm_ce_fwd_bwd": [_p, _ll, _p, _p, _i, _i, _i, _p],
+        "mm_p2p_flag_bytes": [],
+        "mm_p2p_allgather": [_p, _p, _ll, _i, _i, _i, _p],
+        "mm_p2p_rs_adamw": [_p, _p, _ll, _i, _i, _i, C.c_uint, _f, _p, _p, _p, _p, _ll, _f, _f, _f, _f, _f, _f, _f,
+                            _p, _i, _p],
+        "mm_p2p_rs": [_p, _p, _ll, _i, _i, _i, C.c_uint, _f, _p, _i, _p, _i, _p],
+        "mm_p2p_wait_done": [_p, _i, C.c_uint, _i, _i, _p, _p],
     }
     for name, args in sig.items():
         if hasattr(L, name):

@@ -119,9 +119,9 @@ class FlatGroup:
             self.exp_avg = torch.zeros_like(self.master)
             self.exp_avg_sq = torch.zeros_like(self.master)
 
-    def flat_grads(self) -> torch.Tensor:
+    def flat_grads(self, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Copy the parameters' ``.grad`` into one flat buffer (pads zero) and drop the originals."""
-        g = torch.empty(self.padded, dtype=self.dtype, device=self.device)
+        g = out if out is not None else torch.empty(self.padded, dtype=self.dtype, device=self.device)
         views, srcs, prev_end = [], [], 0
         for (n, p), off, shape, numel in zip(self.named_params, self.offsets, self.shapes, self.numels):
             if off > prev_end:
@@ -166,6 +166,7 @@ class Unit:
         self.unsharded = False
         self.ready_event = None
         self.index = -1
+        self.bwd_done = False          # backward of the current micro-step has run
         self.recompute = True          # False: keep the autograd graph (used for the loss head)
         self.pending_reduce = False    # non-recompute unit whose gradients wait to be reduced
 
@@ -209,6 +210,9 @@ class FSDPEngine:
         self._p2p = None
         self.last_grad_norm: Optional[torch.Tensor] = None
         self.kernel_launches = 0
+        self._exec_order: List[Unit] = []
+        self._exec_pos: Dict[int, int] = {}
+        self._order_known = False
 
     # ------------------------------------------------------------------ materialisation
     def materialize(self, init_fn: Callable[[str, nn.Module], None]) -> None:
@@ -246,6 +250,8 @@ class FSDPEngine:
             with torch.cuda.stream(self.comm_stream):
                 for g, f in zip(u.groups, fulls):
                     self._all_gather(g, f)
+                    if self.world > 1:
+                        f.record_stream(self.comm_stream)
                 u.ready_event = torch.cuda.Event()
                 u.ready_event.record()
         else:
@@ -298,20 +304,42 @@ class FSDPEngine:
         return outs[0] if len(outs) == 1 and not u._tuple_out else outs
 
     def _prefetch_forward(self, u: Unit):
+        """Gather the unit(s) that ran after ``u`` in the recorded forward order (none until one full
+        forward has been seen: the order is learnt, not assumed from the list)."""
+        if not self._order_known:
+            if not self._exec_order or self._exec_order[-1] is not u:
+                self._exec_order.append(u)
+            return
+        pos = self._exec_pos.get(id(u))
+        if pos is None:
+            return
         for k in range(1, self.prefetch + 1):
-            if u.index + k < len(self.units):
-                self.unshard(self.units[u.index + k])
+            if pos + k < len(self._exec_order):
+                self.unshard(self._exec_order[pos + k])
 
     def _prefetch_backward(self, u: Unit):
+        """Backward visits units in (roughly) reverse forward order; a unit prefetched too early or twice
+        is harmless because everything still gathered is released in ``finish_step``."""
+        if not self._order_known:
+            return
+        pos = self._exec_pos.get(id(u))
+        if pos is None:
+            return
         for k in range(1, self.prefetch + 1):
-            if u.index - k >= 0:
-                self.unshard(self.units[u.index - k])
+            if pos - k >= 0 and not self._exec_order[pos - k].bwd_done:
+                self.unshard(self._exec_order[pos - k])
+
+    def _seal_order(self):
+        if not self._order_known and self._exec_order:
+            self._order_known = True
+            self._exec_pos = {id(u): i for i, u in enumerate(self._exec_order)}
 
     # ------------------------------------------------------------------ gradient reduce + update
     def flush_pending(self) -> None:
         for u in self.units:
             if u.pending_reduce:
                 u.pending_reduce = False
+                u.bwd_done = True
                 if any(p.grad is not None for g in u.groups for _, p in g.named_params):
                     self.reduce_and_update(u)
                 self.reshard(u)
@@ -321,7 +349,7 @@ class FSDPEngine:
         for g in u.groups:
             if not g.trainable:
                 continue
-            flat = g.flat_grads()
+            flat = g.flat_grads(self._p2p.grad_slot(g) if self._p2p is not None else None)
             if self.cuda:
                 self.comm_stream.wait_stream(torch.cuda.current_stream())
                 flat.record_stream(self.comm_stream)
@@ -374,6 +402,8 @@ class FSDPEngine:
         self.flush_pending()
         if self.cuda:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
+        if self._p2p is not None and not self.deferred:
+            self._p2p.step_barrier()      # no rank gathers a shard before its owner finished updating it
         norm = None
         if self.deferred:
             groups = [g for u in self.units for g in u.groups if g.trainable and g.grad32 is not None]
@@ -382,13 +412,15 @@ class FSDPEngine:
                 sq = torch.stack([g.grad32.float().pow(2).sum() for g in groups]).sum()
                 if self.world > 1:
                     dist.all_reduce(sq, group=self.group)
-                norm = sq.sqrt()
+                norm = sq.sqrt() / self.grad_accum_steps      # norm of the micro-batch-averaged gradient
                 scale = torch.clamp(self.opt.clip_grad / (norm + 1e-6), max=1.0)
             if self.grad_accum_steps > 1:
                 scale = scale / self.grad_accum_steps
             for g in groups:
                 self._adamw(g, g.grad32, scale)
                 g.grad32 = None
+            if self._p2p is not None:
+                self._p2p.step_barrier()
         self.last_grad_norm = norm
         return norm
 
@@ -396,6 +428,12 @@ class FSDPEngine:
         self.lr = lr
 
     def end_micro_step(self) -> None:
+        """Call after each micro-batch's backward."""
+        self.flush_pending()
+        self._seal_order()
+        for u in self.units:
+            u.bwd_done = False
+            self.reshard(u)       # anything a prefetch gathered but nobody consumed
         self.micro_step += 1
 
     # ------------------------------------------------------------------ state
@@ -551,5 +589,6 @@ class _UnitFn(torch.autograd.Function):
         if u.trainable:
             engine.reduce_and_update(u)
         engine.reshard(u)
+        u.bwd_done = True
         grads = [t.grad if need else None for t, need in zip(tensors, ctx.needs)]
         return (None, None, None, None, *grads)

@@ -1,0 +1,40 @@
+"""Engine under real process groups: gloo on CPU (always) and NCCL + NVLink peer kernels on >= 2 GPUs."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(nproc, *args, timeout=600):
+    port = 29500 + (os.getpid() % 500)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "dist_fsdp_check.py"), *args]
+    env = dict(os.environ, OMP_NUM_THREADS="2")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return r.stdout
+
+
+def test_gloo_world2_matches_single_process():
+    out = _run(2, "--device", "cpu", "--steps", "2")
+    assert "ok=True" in out
+
+
+def test_gloo_world2_with_clipping():
+    out = _run(2, "--device", "cpu", "--steps", "2", "--clip", "0.5")
+    assert "ok=True" in out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("comm", ["p2p", "nccl"])
+def test_gpu_world2(comm):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    out = _run(2, "--device", "cuda", "--comm", comm, "--steps", "3")
+    assert "ok=True" in out
+    if comm == "p2p":
+        assert "p2p=True" in out

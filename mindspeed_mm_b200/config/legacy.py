@@ -1,0 +1,170 @@
+"""Legacy launch schema: Megatron-style flags + ``--mm-model / --mm-data / --mm-tool`` JSON or YAML files.
+
+``parse_legacy_args(argv)`` accepts the flag vocabulary the reference's shell recipes pass
+(examples/qwen2.5vl/finetune_qwen2_5_vl_7b.sh:59-111, examples/wan2.1/14b/t2v/pretrain.sh) - known flags are
+typed, unknown ``--flags`` are kept (as strings / booleans) so that a recipe never dies on an option that
+only matters to another backend - and attaches ``args.mm.{model,data,tool}`` attribute trees
+(mindspeed_mm/configs/config.py:67-140).  A first positional ``*.yaml`` switches to the single-file schema
+(``gpt_args`` / ``lora_args`` flattened to flags, ``MM_TOOL_PATH``; mindspeed_mm/configs/read_yaml_config.py:9-78).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from types import SimpleNamespace
+from typing import Any, Dict, List, Optional, Sequence
+
+import yaml
+
+from .security import check_args_paths
+from .tree import ConfigNode
+
+
+class MMConfig:
+    """``MMConfig({"model": path, "data": path, "tool": path})`` -> ``.model/.data/.tool`` trees.
+    A ``.yaml`` path contributes its top-level entry of the same name."""
+
+    def __init__(self, files: Dict[str, str]):
+        errors = []
+        for name, path in files.items():
+            if not path:
+                continue
+            try:
+                real = os.path.realpath(path)
+                if real.endswith(".json"):
+                    with open(real) as f:
+                        d = json.load(f)
+                elif real.endswith((".yaml", ".yml")):
+                    with open(real) as f:
+                        d = yaml.safe_load(f)[name]
+                else:
+                    raise ValueError("config files must be .json or .yaml")
+                setattr(self, name, ConfigNode(d))
+            except FileNotFoundError as e:
+                errors.append(f"Warning: Config file not found: {path} - {e}")
+            except (json.JSONDecodeError, yaml.YAMLError) as e:
+                errors.append(f"Error: Invalid format in {path}: {e}")
+            except Exception as e:  # noqa: BLE001
+                errors.append(f"Error: Unexpected error loading {path}: {e}")
+        if errors:
+            raise RuntimeError("One or more config files failed to load:\n" + "\n".join(errors))
+
+
+def yaml_to_argv(config_path: str) -> List[str]:
+    """Flatten ``gpt_args`` (+ ``lora_args``) of a single-file recipe into Megatron flags."""
+    with open(config_path) as f:
+        cfg = yaml.safe_load(f)
+    if "gpt_args" not in cfg:
+        raise KeyError("The required keyword 'gpt_args' is missing from the configuration file.")
+    if "MM_TOOL_PATH" not in cfg:
+        raise KeyError("The required keyword 'MM_TOOL_PATH' is missing from the configuration file.")
+    flat: Dict[str, Any] = {}
+
+    def walk(d):
+        for k, v in d.items():
+            if isinstance(v, dict):
+                walk(v)
+            else:
+                flat[k.replace("_", "-")] = v
+
+    walk(cfg["gpt_args"])
+    if "lora_args" in cfg:
+        walk(cfg["lora_args"])
+    argv: List[str] = []
+    for k, v in flat.items():
+        if isinstance(v, bool):
+            if v:
+                argv.append(f"--{k}")
+        elif isinstance(v, list):
+            for x in v:
+                argv += [f"--{k}", str(x)]
+        elif v is not None:
+            argv += [f"--{k}", str(v)]
+    argv += ["--mm-data", config_path, "--mm-model", config_path, "--mm-tool", cfg["MM_TOOL_PATH"]]
+    return argv
+
+
+_INT = ["tensor-model-parallel-size", "pipeline-model-parallel-size", "context-parallel-size",
+        "expert-model-parallel-size", "micro-batch-size", "global-batch-size", "seq-length", "vocab-size",
+        "train-iters", "log-interval", "save-interval", "eval-interval", "eval-iters", "num-workers", "seed",
+        "num-layers", "hidden-size", "num-attention-heads", "max-position-embeddings", "lr-warmup-iters",
+        "exit-interval", "ulysses-degree-in-cp", "virtual-pipeline-model-parallel-size", "recompute-num-layers",
+        "make-vocab-size-divisible-by", "distributed-timeout-minutes", "num-layers-per-virtual-pipeline-stage"]
+_FLOAT = ["lr", "min-lr", "weight-decay", "clip-grad", "adam-beta1", "adam-beta2", "adam-eps", "lr-warmup-fraction",
+          "init-method-std", "exit-duration-in-mins", "attention-dropout", "hidden-dropout"]
+_STR = ["lr-decay-style", "tokenizer-type", "load", "save", "ckpt-format", "distributed-backend", "mm-data",
+        "mm-model", "mm-tool", "context-parallel-algo", "fsdp2-config-path", "normalization", "recompute-granularity",
+        "recompute-method", "position-embedding-type", "optimizer", "tensorboard-dir", "layerzero-config",
+        "load-base-model", "dataloader-type", "attention-mask-type"]
+_BOOL = ["bf16", "fp16", "use-mcore-models", "use-flash-attn", "use-distributed-optimizer", "use-torch-fsdp2",
+         "sequence-parallel", "swiglu", "use-fused-swiglu", "use-fused-rmsnorm", "use-fused-rotary-pos-emb",
+         "no-load-optim", "no-load-rng", "no-save-optim", "no-save-rng", "variable-seq-lengths", "log-tps",
+         "untie-embeddings-and-output-weights", "no-gradient-accumulation-fusion", "use-cpu-initialization",
+         "init-model-with-meta-device", "no-initialization", "overlap-grad-reduce", "overlap-param-gather",
+         "calculate-per-token-loss", "calculate-per-sample-loss", "layerzero", "use-deter-comp", "no-masked-softmax-fusion",
+         "disable-bias-linear", "group-query-attention", "recompute-skip-core-attention", "use-ema", "no-bias-swiglu-fusion"]
+
+
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(allow_abbrev=False, add_help=False)
+    for n in _INT:
+        p.add_argument(f"--{n}", type=int, default=None)
+    for n in _FLOAT:
+        p.add_argument(f"--{n}", type=float, default=None)
+    for n in _STR:
+        p.add_argument(f"--{n}", type=str, default=None)
+    for n in _BOOL:
+        p.add_argument(f"--{n}", action="store_true", default=False)
+    return p
+
+
+DEFAULTS = dict(tensor_model_parallel_size=1, pipeline_model_parallel_size=1, context_parallel_size=1,
+                expert_model_parallel_size=1, micro_batch_size=1, train_iters=10, log_interval=1, lr=1e-5,
+                min_lr=0.0, weight_decay=0.0, clip_grad=1.0, adam_beta1=0.9, adam_beta2=0.999, adam_eps=1e-8,
+                lr_decay_style="cosine", lr_warmup_fraction=0.0, seed=1234, save_interval=0, eval_interval=0,
+                distributed_backend="nccl", ckpt_format="torch", context_parallel_algo="ulysses_cp_algo",
+                mm_model="", mm_data="", mm_tool="", num_workers=0)
+
+
+def parse_legacy_args(argv: Optional[Sequence[str]] = None, check_paths: bool = True) -> SimpleNamespace:
+    import sys
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0].endswith((".yaml", ".yml")):
+        argv = yaml_to_argv(argv[0]) + argv[1:]
+    known, unknown = build_parser().parse_known_args(argv)
+    args = SimpleNamespace(**{k: v for k, v in vars(known).items()})
+    for k, v in DEFAULTS.items():
+        if getattr(args, k, None) is None:
+            setattr(args, k, v)
+    # keep unknown flags: "--flag value" or bare "--flag"
+    extra: Dict[str, Any] = {}
+    i = 0
+    while i < len(unknown):
+        tok = unknown[i]
+        if tok.startswith("--"):
+            key = tok[2:].replace("-", "_")
+            if "=" in key:
+                key, val = key.split("=", 1)
+                extra[key] = val
+            elif i + 1 < len(unknown) and not unknown[i + 1].startswith("--"):
+                extra[key] = unknown[i + 1]
+                i += 1
+            else:
+                extra[key] = True
+        i += 1
+    for k, v in extra.items():
+        if not hasattr(args, k):
+            setattr(args, k, v)
+    args.unknown_args = extra
+    if args.global_batch_size is None:
+        args.global_batch_size = args.micro_batch_size
+    merge_mm_args(args)
+    if check_paths:
+        args.path_warnings = check_args_paths(args, warn=lambda *_: None)
+    return args
+
+
+def merge_mm_args(args) -> None:
+    if not hasattr(args, "mm") or args.mm is None:
+        args.mm = MMConfig({"model": args.mm_model, "data": args.mm_data, "tool": args.mm_tool})

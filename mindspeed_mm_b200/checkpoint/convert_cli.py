@@ -1,0 +1,192 @@
+"""``mm-convert <Converter> <command> [--cfg.a.b value ...]`` - offline checkpoint conversion (CPU, one process).
+
+Command surface of the reference's CLI (checkpoint/convert_cli.py:13, checkpoint/common/converter.py:8-50):
+
+    mm-convert Qwen2_5_VLConverter hf_to_mm --cfg.mm_dir OUT --cfg.hf_config.hf_dir HF \
+        --cfg.parallel_config.llm_pp_layers [[12,16]] --cfg.parallel_config.vit_pp_layers [[32,0]] \
+        --cfg.parallel_config.tp_size 2
+    mm-convert Qwen2_5_VLConverter mm_to_hf --cfg.save_hf_dir OUT --cfg.mm_dir MM --cfg.hf_config.hf_dir HF ...
+    mm-convert Qwen2_5_VLConverter resplit  --cfg.source_dir MM --cfg.target_dir OUT --cfg.source_parallel_config.* --cfg.target_parallel_config.*
+    mm-convert Qwen2_5_VLConverter hf_to_dcp --cfg.hf_dir HF --cfg.dcp_dir OUT
+    mm-convert Qwen2_5_VLConverter dcp_to_hf --cfg.hf_dir HF --cfg.dcp_dir IN --cfg.save_hf_dir OUT
+    mm-convert WanConverter hf_to_mm|mm_to_hf --cfg.source_path IN --cfg.target_path OUT
+
+Dotted ``--cfg.*`` options are collected into a nested dict (values parsed as YAML, so lists work).
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+from typing import Any, Dict, List
+
+import torch
+import yaml
+
+from . import hf as hfio
+from . import megatron as mm
+
+CONVERTERS: Dict[str, type] = {}
+
+
+def register(cls):
+    CONVERTERS[cls.__name__] = cls
+    return cls
+
+
+def parse_cfg(argv: List[str]) -> Dict[str, Any]:
+    cfg: Dict[str, Any] = {}
+    i = 0
+    while i < len(argv):
+        tok = argv[i]
+        if not tok.startswith("--"):
+            raise SystemExit(f"unexpected argument {tok!r}")
+        key, eq, val = tok[2:].partition("=")
+        if not eq:
+            i += 1
+            if i >= len(argv):
+                raise SystemExit(f"missing value for --{key}")
+            val = argv[i]
+        parts = key.split(".")
+        if parts[0] == "cfg":
+            parts = parts[1:]
+        node = cfg
+        for p in parts[:-1]:
+            node = node.setdefault(p, {})
+        node[parts[-1]] = yaml.safe_load(val)
+        i += 1
+    return cfg
+
+
+def _flat_layers(x) -> List[int]:
+    """``[[12,16]]`` (virtual-pipeline outer list) or ``[12,16]`` -> ``[12,16]``."""
+    if x and isinstance(x[0], (list, tuple)):
+        if len(x) != 1:
+            raise NotImplementedError("virtual pipeline chunks (>1 outer list) are written as model0/model1 keys; "
+                                      "use one chunk per stage here")
+        return list(x[0])
+    return list(x)
+
+
+def _hf_model_config(hf_dir: str) -> dict:
+    with open(os.path.join(hf_dir, "config.json")) as f:
+        c = json.load(f)
+    t = c.get("text_config", c)
+    v = c["vision_config"]
+    nh = t["num_attention_heads"]
+    return dict(num_heads=nh, num_kv_heads=t.get("num_key_value_heads", nh),
+                head_dim=t.get("head_dim") or t["hidden_size"] // nh, vit_heads=v["num_heads"],
+                llm_layers=t["num_hidden_layers"], vit_layers=v["depth"])
+
+
+class _VLMConverter:
+    glu_vit = True
+
+    @classmethod
+    def _ops(cls, m):
+        return mm.qwen25vl_mm_ops(m["num_heads"], m["num_kv_heads"], m["head_dim"], m["vit_heads"], cls.glu_vit)
+
+    @classmethod
+    def hf_to_mm(cls, cfg):
+        hf_dir = cfg["hf_config"]["hf_dir"]
+        m = _hf_model_config(hf_dir)
+        pc = cfg.get("parallel_config", {})
+        llm = _flat_layers(pc.get("llm_pp_layers", [[m["llm_layers"]]]))
+        vit = _flat_layers(pc.get("vit_pp_layers", [[m["vit_layers"]] + [0] * (len(llm) - 1)]))
+        if sum(llm) != m["llm_layers"] or sum(vit) != m["vit_layers"] or len(llm) != len(vit):
+            raise SystemExit(f"pp layer lists {vit} / {llm} do not add up to {m['vit_layers']} / {m['llm_layers']}")
+        sds = mm.hf_to_mm(hfio.load_state_dict(hf_dir), cls._ops(m), int(pc.get("tp_size", 1)), vit, llm, cls.glu_vit)
+        mm.save_mm(sds, cfg["mm_dir"])
+
+    @classmethod
+    def mm_to_hf(cls, cfg):
+        hf_dir = cfg["hf_config"]["hf_dir"]
+        m = _hf_model_config(hf_dir)
+        pc = cfg.get("parallel_config", {})
+        llm = _flat_layers(pc.get("llm_pp_layers", [[m["llm_layers"]]]))
+        vit = _flat_layers(pc.get("vit_pp_layers", [[m["vit_layers"]] + [0] * (len(llm) - 1)]))
+        sd = mm.mm_to_hf(mm.load_mm(cfg["mm_dir"]), cls._ops(m), vit, llm, cls.glu_vit)
+        hfio.save_sharded(sd, cfg["save_hf_dir"])
+        for f in os.listdir(hf_dir):
+            if f.endswith((".json", ".txt", ".jinja")) and f != hfio.INDEX:
+                import shutil
+                shutil.copy(os.path.join(hf_dir, f), os.path.join(cfg["save_hf_dir"], f))
+
+    @classmethod
+    def resplit(cls, cfg):
+        m = _hf_model_config(cfg["hf_config"]["hf_dir"]) if "hf_config" in cfg else cfg["model"]
+        s, t = cfg["source_parallel_config"], cfg["target_parallel_config"]
+        ops = cls._ops(m)
+        sd = mm.mm_to_hf(mm.load_mm(cfg["source_dir"]), ops, _flat_layers(s["vit_pp_layers"]),
+                         _flat_layers(s["llm_pp_layers"]), cls.glu_vit, modern_prefix=False)
+        out = mm.hf_to_mm(sd, cls._ops(m), int(t.get("tp_size", 1)), _flat_layers(t["vit_pp_layers"]),
+                          _flat_layers(t["llm_pp_layers"]), cls.glu_vit)
+        mm.save_mm(out, cfg["target_dir"])
+
+    @staticmethod
+    def hf_to_dcp(cfg):
+        import torch.distributed.checkpoint as dcp
+        sd = hfio.load_state_dict(cfg["hf_dir"])
+        dcp.save({"model": sd}, checkpoint_id=os.path.join(cfg["dcp_dir"], "release"), no_dist=True)
+        with open(os.path.join(cfg["dcp_dir"], "latest_checkpointed_iteration.txt"), "w") as f:
+            f.write("release")
+
+    @staticmethod
+    def dcp_to_hf(cfg):
+        import torch.distributed.checkpoint as dcp
+        from torch.distributed.checkpoint.format_utils import dcp_to_torch_save
+        src = cfg["dcp_dir"]
+        tr = os.path.join(src, "latest_checkpointed_iteration.txt")
+        if os.path.exists(tr):
+            tag = open(tr).read().strip()
+            src = os.path.join(src, tag if tag == "release" else f"iter_{int(tag):07d}")
+        tmp = os.path.join(cfg["save_hf_dir"], "_dcp_tmp.pt")
+        os.makedirs(cfg["save_hf_dir"], exist_ok=True)
+        dcp_to_torch_save(src, tmp)
+        sd = torch.load(tmp, map_location="cpu", weights_only=False)
+        os.remove(tmp)
+        sd = sd.get("model", sd)
+        hfio.save_sharded({k: v for k, v in sd.items() if isinstance(v, torch.Tensor)}, cfg["save_hf_dir"])
+
+
+@register
+class Qwen2_5_VLConverter(_VLMConverter):
+    glu_vit = True
+
+
+@register
+class Qwen2VLConverter(_VLMConverter):
+    glu_vit = False
+
+
+@register
+class WanConverter:
+    @staticmethod
+    def hf_to_mm(cfg):
+        from .wan import diffusers_to_mm
+        hfio.save_sharded(diffusers_to_mm(hfio.load_state_dict(cfg["source_path"])), cfg["target_path"])
+
+    @staticmethod
+    def mm_to_hf(cfg):
+        from .wan import mm_to_diffusers
+        hfio.save_sharded(mm_to_diffusers(hfio.load_state_dict(cfg["source_path"])), cfg["target_path"])
+
+
+def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if len(argv) < 2 or argv[0] in ("-h", "--help"):
+        print(__doc__)
+        print("converters:", ", ".join(sorted(CONVERTERS)))
+        return 0 if argv and argv[0] in ("-h", "--help") else 2
+    conv, cmd = argv[0], argv[1]
+    if conv not in CONVERTERS:
+        raise SystemExit(f"unknown converter {conv}; known: {sorted(CONVERTERS)}")
+    fn = getattr(CONVERTERS[conv], cmd, None)
+    if fn is None:
+        raise SystemExit(f"{conv} has no command {cmd}")
+    fn(parse_cfg(argv[2:]))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,217 @@
+"""HuggingFace-format weights: name maps, safetensors IO, load into / save from the sharding engine.
+
+Internal parameter names are the modules' own (``layers.3.qkv_proj.weight``); HuggingFace names differ in
+three ways that the operator list below undoes: prefixes (``model.language_model.`` / ``model.visual.`` in
+current transformers, ``model.`` / ``visual.`` in older checkpoints), un-fused projections (q/k/v and
+gate/up are separate tensors) and the Conv3d-shaped patch embedding.  Loading streams shard by shard and
+writes straight into each rank's slice of the flat buffers (no full model is ever materialised on one
+rank), the way the reference loads safetensors into sharded DTensors
+(mindspeed_mm/fsdp/checkpoint/hf_utils.py:103-292); saving gathers unit by unit and writes size-capped
+shards plus ``model.safetensors.index.json`` (hf_checkpointer.py:39-197).
+"""
+from __future__ import annotations
+
+import json
+import os
+import shutil
+from typing import Callable, Dict, Iterable, List, Optional, Tuple
+
+import torch
+
+from .operators import (ExpertStack, Merge, Operator, QKVMerge, Rename, RenamePrefix, Reshape, StateDict, apply_ops,
+                        revert_ops)
+
+INDEX = "model.safetensors.index.json"
+
+
+# ------------------------------------------------------------------------------------------ name maps
+def qwen25vl_ops(cfg) -> List[Operator]:
+    """HF Qwen2.5-VL -> internal names/layouts (``cfg``: models.qwen2_5_vl.Qwen25VLConfig)."""
+    t, v = cfg.text, cfg.vision
+    ffn, ffn_p = v.intermediate_size, (v.intermediate_size + 63) // 64 * 64
+
+    def pad_rows(x, rows):      # [f, ...] -> [rows, ...] zero padded
+        if x.shape[0] == rows:
+            return x
+        out = x.new_zeros((rows,) + tuple(x.shape[1:]))
+        out[:x.shape[0]] = x
+        return out
+
+    class VitFFNPad(Operator):
+        """Zero-pad the ViT FFN width (3420 -> 3456) after gate|up were merged; revert strips the pad."""
+
+        def apply(self, sd):
+            for k in list(sd.keys()):
+                if k.startswith("visual.blocks.") and ".mlp_gate_up." in k:
+                    g, u = torch.chunk(sd[k], 2, dim=0)
+                    sd[k] = torch.cat([pad_rows(g, ffn_p), pad_rows(u, ffn_p)])
+                elif k.startswith("visual.blocks.") and k.endswith("mlp_down.weight"):
+                    w = sd[k]
+                    if w.shape[1] != ffn_p:
+                        out = w.new_zeros(w.shape[0], ffn_p)
+                        out[:, :w.shape[1]] = w
+                        sd[k] = out
+
+        def revert(self, sd):
+            for k in list(sd.keys()):
+                if k.startswith("visual.blocks.") and ".mlp_gate_up." in k:
+                    g, u = torch.chunk(sd[k], 2, dim=0)
+                    sd[k] = torch.cat([g[:ffn], u[:ffn]])
+                elif k.startswith("visual.blocks.") and k.endswith("mlp_down.weight"):
+                    sd[k] = sd[k][:, :ffn].contiguous()
+
+    ops: List[Operator] = [
+        RenamePrefix("model.language_model.", "model."),       # current transformers layout -> classic
+        RenamePrefix("model.visual.", "visual."),
+        Rename("visual.patch_embed.proj.weight", "visual.patch_embed.proj.weight"),
+        Reshape("visual.patch_embed.proj.weight", lambda x: (x.shape[0], -1),
+                lambda x: (x.shape[0], v.in_channels, v.temporal_patch_size, v.patch_size, v.patch_size)),
+        Rename("visual.blocks.{i}.attn.qkv.weight", "visual.blocks.{i}.attn_qkv.weight"),
+        Rename("visual.blocks.{i}.attn.qkv.bias", "visual.blocks.{i}.attn_qkv.bias"),
+        Rename("visual.blocks.{i}.attn.proj.weight", "visual.blocks.{i}.attn_proj.weight"),
+        Rename("visual.blocks.{i}.attn.proj.bias", "visual.blocks.{i}.attn_proj.bias"),
+        Merge(["visual.blocks.{i}.mlp.gate_proj.weight", "visual.blocks.{i}.mlp.up_proj.weight"],
+              "visual.blocks.{i}.mlp_gate_up.weight"),
+        Merge(["visual.blocks.{i}.mlp.gate_proj.bias", "visual.blocks.{i}.mlp.up_proj.bias"],
+              "visual.blocks.{i}.mlp_gate_up.bias"),
+        Rename("visual.blocks.{i}.mlp.down_proj.weight", "visual.blocks.{i}.mlp_down.weight"),
+        Rename("visual.blocks.{i}.mlp.down_proj.bias", "visual.blocks.{i}.mlp_down.bias"),
+        VitFFNPad(),
+        Rename("visual.merger.mlp.0.weight", "visual.merger.fc1.weight"),
+        Rename("visual.merger.mlp.0.bias", "visual.merger.fc1.bias"),
+        Rename("visual.merger.mlp.2.weight", "visual.merger.fc2.weight"),
+        Rename("visual.merger.mlp.2.bias", "visual.merger.fc2.bias"),
+        Rename("model.embed_tokens.weight", "embed_tokens.weight"),
+        QKVMerge(["model.layers.{i}.self_attn.q_proj.weight", "model.layers.{i}.self_attn.k_proj.weight",
+                  "model.layers.{i}.self_attn.v_proj.weight"], "layers.{i}.qkv_proj.weight",
+                 t.num_attention_heads, t.num_key_value_heads, t.head_dim),
+        QKVMerge(["model.layers.{i}.self_attn.q_proj.bias", "model.layers.{i}.self_attn.k_proj.bias",
+                  "model.layers.{i}.self_attn.v_proj.bias"], "layers.{i}.qkv_proj.bias",
+                 t.num_attention_heads, t.num_key_value_heads, t.head_dim),
+        Rename("model.layers.{i}.self_attn.o_proj.weight", "layers.{i}.o_proj.weight"),
+        Merge(["model.layers.{i}.mlp.gate_proj.weight", "model.layers.{i}.mlp.up_proj.weight"],
+              "layers.{i}.gate_up_proj.weight"),
+        Rename("model.layers.{i}.mlp.down_proj.weight", "layers.{i}.down_proj.weight"),
+        Rename("model.layers.{i}.input_layernorm.weight", "layers.{i}.input_layernorm.weight"),
+        Rename("model.layers.{i}.post_attention_layernorm.weight", "layers.{i}.post_attention_layernorm.weight"),
+        Rename("model.norm.weight", "lm_head.norm.weight"),
+        Rename("lm_head.weight", "lm_head.weight"),
+    ]
+    return ops
+
+
+class _ModernPrefix(Operator):
+    """On the way back to HF, emit the current transformers prefixes."""
+
+    def apply(self, sd):
+        pass
+
+    def revert(self, sd):
+        for k in list(sd.keys()):
+            if k.startswith("model."):
+                sd["model.language_model." + k[len("model."):]] = sd.pop(k)
+            elif k.startswith("visual."):
+                sd["model." + k] = sd.pop(k)
+
+
+def to_internal(hf_sd: StateDict, ops: List[Operator]) -> StateDict:
+    return apply_ops(dict(hf_sd), ops)
+
+
+def to_hf(internal_sd: StateDict, ops: List[Operator], modern_prefix: bool = True) -> StateDict:
+    ops = [o for o in ops if not isinstance(o, RenamePrefix)]
+    sd = revert_ops(dict(internal_sd), ops)
+    if modern_prefix:
+        _ModernPrefix().revert(sd)
+    return sd
+
+
+# ------------------------------------------------------------------------------------------ safetensors IO
+def iter_safetensors(path: str) -> Iterable[Tuple[str, torch.Tensor]]:
+    """Yield (name, tensor) from a file, a sharded directory (index json) or a directory of *.safetensors."""
+    from safetensors import safe_open
+    files: List[str]
+    if os.path.isfile(path):
+        files = [path]
+    else:
+        idx = os.path.join(path, INDEX)
+        if os.path.exists(idx):
+            with open(idx) as f:
+                files = sorted({os.path.join(path, v) for v in json.load(f)["weight_map"].values()})
+        else:
+            files = sorted(os.path.join(path, f) for f in os.listdir(path) if f.endswith(".safetensors"))
+    for fp in files:
+        with safe_open(fp, framework="pt", device="cpu") as f:
+            for k in f.keys():
+                yield k, f.get_tensor(k)
+
+
+def load_state_dict(path: str) -> StateDict:
+    return dict(iter_safetensors(path))
+
+
+def save_sharded(sd: StateDict, out_dir: str, max_shard_bytes: int = 5 << 30, metadata: Optional[dict] = None) -> None:
+    from safetensors.torch import save_file
+    os.makedirs(out_dir, exist_ok=True)
+    shards: List[Dict[str, torch.Tensor]] = [{}]
+    size = 0
+    for k in sorted(sd):
+        t = sd[k].contiguous()
+        nb = t.numel() * t.element_size()
+        if size + nb > max_shard_bytes and shards[-1]:
+            shards.append({})
+            size = 0
+        shards[-1][k] = t
+        size += nb
+    weight_map, total = {}, 0
+    n = len(shards)
+    for i, sh in enumerate(shards):
+        name = "model.safetensors" if n == 1 else f"model-{i + 1:05d}-of-{n:05d}.safetensors"
+        save_file(sh, os.path.join(out_dir, name), metadata={"format": "pt"})
+        for k, t in sh.items():
+            weight_map[k] = name
+            total += t.numel() * t.element_size()
+    if n > 1:
+        with open(os.path.join(out_dir, INDEX), "w") as f:
+            json.dump({"metadata": {"total_size": total, **(metadata or {})}, "weight_map": weight_map}, f, indent=2)
+
+
+def is_hf_checkpoint(path: str) -> bool:
+    if not path or not os.path.isdir(path):
+        return False
+    return any(f.endswith(".safetensors") for f in os.listdir(path))
+
+
+# ------------------------------------------------------------------------------------------ engine bridges
+def load_hf_into_engine(engine, path: str, ops: List[Operator], strict: bool = True) -> List[str]:
+    """Fill the engine's shards from an HF checkpoint.  Returns missing internal names."""
+    sd = to_internal(load_state_dict(path), ops)
+
+    def getter(name, shape):
+        t = sd.get(name)
+        if t is None:
+            return None
+        if tuple(t.shape) != tuple(shape):
+            raise ValueError(f"shape mismatch for {name}: checkpoint {tuple(t.shape)} vs model {tuple(shape)}")
+        return t.to(engine.device)
+
+    missing = engine.load_full_params(getter)
+    if strict and missing:
+        raise KeyError(f"missing in checkpoint: {missing[:8]}{'...' if len(missing) > 8 else ''}")
+    return missing
+
+
+def save_engine_as_hf(engine, out_dir: str, ops: List[Operator], dtype: Optional[torch.dtype] = None,
+                      assets_from: Optional[str] = None, rank: int = 0) -> None:
+    """Gather unit by unit (all ranks participate); rank 0 writes the HF-named safetensors shards and copies
+    tokenizer / config assets from ``assets_from``."""
+    sd: StateDict = {}
+    for name, t in engine.named_full_params():
+        if rank == 0:
+            sd[name] = (t.to(dtype) if dtype else t).detach().cpu().clone()
+    if rank == 0:
+        save_sharded(to_hf(sd, ops), out_dir)
+        if assets_from and os.path.isdir(assets_from):
+            for f in os.listdir(assets_from):
+                if f.endswith((".json", ".txt", ".model", ".jinja")) and f != INDEX:
+                    shutil.copy(os.path.join(assets_from, f), os.path.join(out_dir, f))

@@ -1,0 +1,235 @@
+"""Checkpoint formats: operator algebra, HF <-> internal <-> Megatron round trips, resume, resharding,
+and numerical parity of the model against HuggingFace's Qwen2.5-VL on a tiny config."""
+import json
+import os
+
+import pytest
+import torch
+
+from mindspeed_mm_b200.api import stable_init_fn
+from mindspeed_mm_b200.checkpoint import hf as hfio
+from mindspeed_mm_b200.checkpoint import megatron as mm
+from mindspeed_mm_b200.checkpoint.convert_cli import main as mm_convert
+from mindspeed_mm_b200.checkpoint.operators import (ExpertStack, QKVMerge, concat_to_interleaved,
+                                                    interleaved_to_concat, merge_glu, split_glu)
+from mindspeed_mm_b200.checkpoint.sharded import DistributedCheckpointer
+from mindspeed_mm_b200.models.qwen2_5_vl import Qwen25VLConfig, Qwen25VLModel
+from mindspeed_mm_b200.parallel.fsdp import FSDPEngine, OptimConfig
+
+
+def small_cfg():
+    cfg = Qwen25VLConfig.tiny()
+    cfg.text.num_layers = 2
+    cfg.vision.depth = 2
+    cfg.vision.fullatt_block_indexes = (1,)
+    cfg.vision.intermediate_size = 300      # not a multiple of 64 -> exercises the FFN pad
+    return cfg
+
+
+def fake_hf_state(cfg, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    t, v = cfg.text, cfg.vision
+    sd = {}
+    R = lambda *s: torch.randn(*s, generator=g) * 0.05
+    sd["model.visual.patch_embed.proj.weight"] = R(v.hidden_size, 3, 2, 14, 14)
+    for i in range(v.depth):
+        p = f"model.visual.blocks.{i}."
+        sd[p + "norm1.weight"], sd[p + "norm2.weight"] = 1 + R(v.hidden_size), 1 + R(v.hidden_size)
+        sd[p + "attn.qkv.weight"], sd[p + "attn.qkv.bias"] = R(3 * v.hidden_size, v.hidden_size), R(3 * v.hidden_size)
+        sd[p + "attn.proj.weight"], sd[p + "attn.proj.bias"] = R(v.hidden_size, v.hidden_size), R(v.hidden_size)
+        for n in ("gate_proj", "up_proj"):
+            sd[p + f"mlp.{n}.weight"], sd[p + f"mlp.{n}.bias"] = R(v.intermediate_size, v.hidden_size), R(v.intermediate_size)
+        sd[p + "mlp.down_proj.weight"], sd[p + "mlp.down_proj.bias"] = R(v.hidden_size, v.intermediate_size), R(v.hidden_size)
+    m = v.hidden_size * 4
+    sd["model.visual.merger.ln_q.weight"] = 1 + R(v.hidden_size)
+    sd["model.visual.merger.mlp.0.weight"], sd["model.visual.merger.mlp.0.bias"] = R(m, m), R(m)
+    sd["model.visual.merger.mlp.2.weight"], sd["model.visual.merger.mlp.2.bias"] = R(v.out_hidden_size, m), R(v.out_hidden_size)
+    sd["model.language_model.embed_tokens.weight"] = R(t.vocab_size, t.hidden_size)
+    for i in range(t.num_layers):
+        p = f"model.language_model.layers.{i}."
+        for n, rows in (("q", t.num_attention_heads), ("k", t.num_key_value_heads), ("v", t.num_key_value_heads)):
+            sd[p + f"self_attn.{n}_proj.weight"] = R(rows * t.head_dim, t.hidden_size)
+            sd[p + f"self_attn.{n}_proj.bias"] = R(rows * t.head_dim)
+        sd[p + "self_attn.o_proj.weight"] = R(t.hidden_size, t.hidden_size)
+        sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"] = R(t.intermediate_size, t.hidden_size), R(t.intermediate_size, t.hidden_size)
+        sd[p + "mlp.down_proj.weight"] = R(t.hidden_size, t.intermediate_size)
+        sd[p + "input_layernorm.weight"], sd[p + "post_attention_layernorm.weight"] = 1 + R(t.hidden_size), 1 + R(t.hidden_size)
+    sd["model.language_model.norm.weight"] = 1 + R(t.hidden_size)
+    sd["lm_head.weight"] = R(t.vocab_size, t.hidden_size)
+    return sd
+
+
+def test_qkv_interleave_roundtrip():
+    q, k, v = torch.arange(8.).view(8, 1), 100 + torch.arange(4.).view(4, 1), 200 + torch.arange(4.).view(4, 1)
+    cat = torch.cat([q, k, v])
+    inter = concat_to_interleaved(cat, 2, [8, 4, 4])
+    assert inter.flatten().tolist() == [0, 1, 2, 3, 100, 101, 200, 201, 4, 5, 6, 7, 102, 103, 202, 203]
+    assert torch.equal(interleaved_to_concat(inter, 2, [4, 2, 2]), cat)
+
+
+def test_glu_split_merge():
+    t = torch.arange(16.).view(8, 2)
+    parts = split_glu(t, 2)
+    assert torch.equal(parts[0], torch.cat([t[0:2], t[4:6]]))
+    assert torch.equal(merge_glu(parts), t)
+
+
+def test_expert_stack():
+    sd = {f"l.0.experts.{e}.w": torch.full((2, 3), float(e)) for e in range(4)}
+    op = ExpertStack("l.{i}.experts.{e}.w", "l.{i}.experts.w_stacked")
+    op.apply(sd)
+    assert sd["l.0.experts.w_stacked"].shape == (4, 3, 2)
+    op.revert(sd)
+    assert torch.equal(sd["l.0.experts.2.w"], torch.full((2, 3), 2.0))
+
+
+def test_hf_internal_roundtrip_and_model_load():
+    cfg = small_cfg()
+    hf_sd = fake_hf_state(cfg)
+    ops = hfio.qwen25vl_ops(cfg)
+    internal = hfio.to_internal(hf_sd, ops)
+    with torch.device("meta"):
+        model = Qwen25VLModel(cfg)
+    names = {n: p.shape for n, p in model.named_parameters()}
+    assert set(names) == set(internal), (set(names) ^ set(internal))
+    for n, s in names.items():
+        assert tuple(internal[n].shape) == tuple(s), n
+    back = hfio.to_hf(internal, hfio.qwen25vl_ops(cfg))
+    assert set(back) == set(hf_sd)
+    for k in hf_sd:
+        assert torch.equal(back[k], hf_sd[k]), k
+
+
+def test_hf_mm_roundtrip_tp_pp(tmp_path):
+    cfg = small_cfg()
+    t, v = cfg.text, cfg.vision
+    hf_sd = fake_hf_state(cfg)
+    mk = lambda: mm.qwen25vl_mm_ops(t.num_attention_heads, t.num_key_value_heads, t.head_dim, v.num_heads)
+    stages = mm.hf_to_mm(hf_sd, mk(), tp=2, vit_layers=[2, 0], llm_layers=[1, 1])
+    assert len(stages) == 2 and len(stages[0]) == 2
+    s0, s1 = stages[0][0], stages[1][0]
+    assert "text_decoder.embedding.word_embeddings.weight" in s0 and "text_decoder.output_layer.weight" in s1
+    assert "text_decoder.decoder.layers.0.mlp.linear_fc1.weight" in s1          # renumbered from global layer 1
+    assert not any(k.startswith("image_encoder") for k in s1)
+    assert s0["text_decoder.decoder.layers.0.self_attention.linear_qkv.weight"].shape[0] == \
+        (t.num_attention_heads + 2 * t.num_key_value_heads) * t.head_dim // 2
+    mm.save_mm(stages, str(tmp_path / "mm"))
+    assert os.path.exists(tmp_path / "mm" / "release" / "mp_rank_01_001" / "model_optim_rng.pt")
+    assert open(tmp_path / "mm" / "latest_checkpointed_iteration.txt").read() == "release"
+    back = mm.mm_to_hf(mm.load_mm(str(tmp_path / "mm")), mk(), [2, 0], [1, 1])
+    assert set(back) == set(hf_sd)
+    for k in hf_sd:
+        assert torch.equal(back[k], hf_sd[k]), k
+
+
+def test_mm_convert_cli(tmp_path):
+    cfg = small_cfg()
+    t, v = cfg.text, cfg.vision
+    hf_dir = tmp_path / "hf"
+    hfio.save_sharded(fake_hf_state(cfg), str(hf_dir), max_shard_bytes=20 << 20)
+    assert os.path.exists(hf_dir / hfio.INDEX)
+    json.dump({"text_config": {"num_attention_heads": t.num_attention_heads, "num_key_value_heads": t.num_key_value_heads,
+                               "hidden_size": t.hidden_size, "num_hidden_layers": t.num_layers},
+               "vision_config": {"num_heads": v.num_heads, "depth": v.depth}}, open(hf_dir / "config.json", "w"))
+    assert mm_convert(["Qwen2_5_VLConverter", "hf_to_mm", "--cfg.mm_dir", str(tmp_path / "mm"), "--cfg.hf_config.hf_dir",
+                       str(hf_dir), "--cfg.parallel_config.llm_pp_layers", "[[1,1]]",
+                       "--cfg.parallel_config.vit_pp_layers", "[[2,0]]", "--cfg.parallel_config.tp_size", "2"]) == 0
+    assert mm_convert(["Qwen2_5_VLConverter", "resplit", "--cfg.source_dir", str(tmp_path / "mm"), "--cfg.target_dir",
+                       str(tmp_path / "mm2"), "--cfg.hf_config.hf_dir", str(hf_dir),
+                       "--cfg.source_parallel_config.llm_pp_layers", "[[1,1]]", "--cfg.source_parallel_config.vit_pp_layers",
+                       "[[2,0]]", "--cfg.source_parallel_config.tp_size", "2", "--cfg.target_parallel_config.llm_pp_layers",
+                       "[[2]]", "--cfg.target_parallel_config.vit_pp_layers", "[[2]]",
+                       "--cfg.target_parallel_config.tp_size", "1"]) == 0
+    assert mm_convert(["Qwen2_5_VLConverter", "mm_to_hf", "--cfg.save_hf_dir", str(tmp_path / "hf2"), "--cfg.mm_dir",
+                       str(tmp_path / "mm2"), "--cfg.hf_config.hf_dir", str(hf_dir)]) == 0
+    a, b = hfio.load_state_dict(str(hf_dir)), hfio.load_state_dict(str(tmp_path / "hf2"))
+    assert set(a) == set(b) and all(torch.equal(a[k], b[k]) for k in a)
+    assert mm_convert(["Qwen2_5_VLConverter", "hf_to_dcp", "--cfg.hf_dir", str(hf_dir), "--cfg.dcp_dir", str(tmp_path / "dcp")]) == 0
+    assert mm_convert(["Qwen2_5_VLConverter", "dcp_to_hf", "--cfg.hf_dir", str(hf_dir), "--cfg.dcp_dir", str(tmp_path / "dcp"),
+                       "--cfg.save_hf_dir", str(tmp_path / "hf3")]) == 0
+    c = hfio.load_state_dict(str(tmp_path / "hf3"))
+    assert set(a) == set(c) and all(torch.equal(a[k], c[k]) for k in a)
+
+
+def _engine(cfg, world_rank=(1, 0)):
+    with torch.device("meta"):
+        model = Qwen25VLModel(cfg)
+    eng = FSDPEngine(model.fsdp_units(), group=False, device="cpu", param_dtype=torch.float32, opt=OptimConfig(lr=1e-3))
+    eng.materialize(stable_init_fn(0.02, 0))
+    return model, eng
+
+
+def test_engine_hf_save_load_and_sharded_resume(tmp_path):
+    from bench import make_batches
+    cfg = small_cfg()
+    cfg.vision.intermediate_size = 320
+    model, eng = _engine(cfg)
+    batch = make_batches(cfg, 1, 512, 1, 1, 224, 0, pin=False)[0]
+
+    def step(m, e):
+        e.set_lr(1e-3)
+        ls, n = m(batch, run=e.run)
+        (ls / n).backward()
+        e.end_micro_step()
+        e.finish_step()
+        return float((ls / n).detach())
+
+    step(model, eng)
+    ck = DistributedCheckpointer(str(tmp_path / "ck"))
+    ck.save(1, eng, {"iteration": 1})
+    hfio.save_engine_as_hf(eng, str(tmp_path / "hf"), hfio.qwen25vl_ops(cfg))
+    l2 = step(model, eng)
+    # resume from the sharded checkpoint: same next loss
+    model2, eng2 = _engine(cfg)
+    extra = DistributedCheckpointer(str(tmp_path / "ck")).load(eng2)
+    assert extra["iteration"] == 1
+    assert abs(step(model2, eng2) - l2) < 1e-5
+    # weights-only load from the HF export reproduces the same forward loss
+    model3, eng3 = _engine(cfg)
+    assert hfio.load_hf_into_engine(eng3, str(tmp_path / "hf"), hfio.qwen25vl_ops(cfg)) == []
+    with torch.no_grad():
+        ls, n = model3(batch, run=eng3.run)
+    assert abs(float(ls / n) - l2) < 1e-4
+
+
+def test_parity_with_transformers_tiny():
+    tr = pytest.importorskip("transformers")
+    try:
+        from transformers import Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration
+    except Exception:  # noqa: BLE001
+        pytest.skip("transformers lacks Qwen2.5-VL")
+    cfg = small_cfg()
+    cfg.vision.intermediate_size = 320
+    t, v = cfg.text, cfg.vision
+    text_cfg = dict(vocab_size=t.vocab_size, hidden_size=t.hidden_size, intermediate_size=t.intermediate_size,
+                    num_hidden_layers=t.num_layers, num_attention_heads=t.num_attention_heads,
+                    num_key_value_heads=t.num_key_value_heads, rms_norm_eps=t.rms_norm_eps, rope_theta=t.rope_theta,
+                    rope_scaling={"type": "mrope", "mrope_section": list(t.mrope_section), "rope_type": "default"},
+                    max_position_embeddings=4096, tie_word_embeddings=False)
+    vis_cfg = dict(depth=v.depth, hidden_size=v.hidden_size, intermediate_size=v.intermediate_size, num_heads=v.num_heads,
+                   out_hidden_size=v.out_hidden_size, patch_size=14, spatial_merge_size=2, temporal_patch_size=2,
+                   window_size=112, fullatt_block_indexes=list(v.fullatt_block_indexes), in_channels=3)
+    try:
+        hcfg = Qwen2_5_VLConfig(text_config=text_cfg, vision_config=vis_cfg, image_token_id=cfg.image_token_id,
+                                video_token_id=cfg.video_token_id, vision_start_token_id=cfg.vision_start_token_id)
+        hcfg._attn_implementation = "eager"
+        hf = Qwen2_5_VLForConditionalGeneration(hcfg).float().eval()
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"cannot build HF tiny model on this transformers version: {e}")
+    hf_sd = {k: v_.detach().clone() for k, v_ in hf.state_dict().items()}
+    with torch.device("meta"):
+        model = Qwen25VLModel(cfg)
+    eng = FSDPEngine(model.fsdp_units(), group=False, device="cpu", param_dtype=torch.float32)
+    eng.materialize(stable_init_fn(0.02, 0))
+    internal = hfio.to_internal(hf_sd, hfio.qwen25vl_ops(cfg))
+    missing = eng.load_full_params(lambda n, s: internal.get(n))
+    assert missing == []
+    from bench import make_batches
+    batch = make_batches(cfg, 1, 384, 1, 1, 224, 0, pin=False)[0]
+    with torch.no_grad():
+        loss_sum, n = model(batch, run=eng.run)
+        out = hf(input_ids=batch["input_ids"][None], pixel_values=batch["pixel_values"],
+                 image_grid_thw=batch["image_grid_thw"], attention_mask=torch.ones(1, batch["n_tokens"], dtype=torch.long))
+        logits = out.logits[0].float()
+        ref = torch.nn.functional.cross_entropy(logits, batch["labels"], ignore_index=-100, reduction="sum")
+    assert abs(float(loss_sum) - float(ref)) / float(ref) < 2e-4, (float(loss_sum), float(ref))

@@ -1,0 +1,203 @@
+"""Ring attention: KV blocks travel around the context-parallel ring while every rank keeps its queries.
+
+Forward: at step s a rank attends its queries to the KV block that originated on rank (r - s) mod P, then
+merges (out, lse) with the running result (online softmax); the next block is received while the current one
+is computed (isend/irecv double buffering).  Backward replays the ring with the FINAL (out, lse): each block's
+dq is accumulated locally, dk/dv travel with their block and arrive home after P steps.
+Causal attention uses the zig-zag layout (rank r holds chunks r and 2P-1-r of 2P chunks) so that every rank
+does the same amount of work: own block -> causal; blocks from lower ranks -> all queries x first half of
+the keys; blocks from higher ranks -> second half of the queries x all keys.
+
+Reference: mindspeed_mm/fsdp/distributed/context_parallel/ring_context_parallel/ring_context_parallel.py:920-1218
+(forward/backward), utils.py:98-232 (RingP2P, forward_update).  Block kernels: fp32 PyTorch math on CPU,
+flash-attn's fwd/bwd entry points on the GPU library tier.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+# ------------------------------------------------------------------------------------------ block kernels
+def _block_fwd_ref(q, k, v, scale, causal) -> Tuple[torch.Tensor, torch.Tensor]:
+    """q [B,Sq,N,D], k/v [B,Sk,Nkv,D] -> out [B,Sq,N,D] (fp32), lse [B,N,Sq]."""
+    rep = q.shape[2] // k.shape[2]
+    qf, kf, vf = q.float().transpose(1, 2), k.float().transpose(1, 2), v.float().transpose(1, 2)
+    kf, vf = kf.repeat_interleave(rep, 1), vf.repeat_interleave(rep, 1)
+    s = qf @ kf.transpose(-1, -2) * scale
+    if causal:
+        sq, sk = s.shape[-2:]
+        s = s.masked_fill(~torch.ones(sq, sk, dtype=torch.bool, device=q.device).tril(sk - sq), float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    o = torch.exp(s - lse.unsqueeze(-1)) @ vf
+    return o.transpose(1, 2), lse
+
+
+def _block_bwd_ref(do, q, k, v, o, lse, scale, causal):
+    """Gradients of one block given the GLOBAL out / lse (so probabilities are globally normalised)."""
+    rep = q.shape[2] // k.shape[2]
+    qf, kf, vf = q.float().transpose(1, 2), k.float().transpose(1, 2), v.float().transpose(1, 2)
+    kr, vr = kf.repeat_interleave(rep, 1), vf.repeat_interleave(rep, 1)
+    dof, of = do.float().transpose(1, 2), o.float().transpose(1, 2)
+    s = qf @ kr.transpose(-1, -2) * scale
+    if causal:
+        sq, sk = s.shape[-2:]
+        s = s.masked_fill(~torch.ones(sq, sk, dtype=torch.bool, device=q.device).tril(sk - sq), float("-inf"))
+    p = torch.exp(s - lse.unsqueeze(-1))
+    dv = p.transpose(-1, -2) @ dof
+    dp = dof @ vr.transpose(-1, -2)
+    delta = (dof * of).sum(-1, keepdim=True)
+    ds = p * (dp - delta) * scale
+    dq = ds @ kr
+    dk = ds.transpose(-1, -2) @ qf
+    B, N, Sk, D = dk.shape
+    dk = dk.view(B, N // rep, rep, Sk, D).sum(2)
+    dv = dv.view(B, N // rep, rep, Sk, -1).sum(2)
+    return dq.transpose(1, 2), dk.transpose(1, 2), dv.transpose(1, 2)
+
+
+def _block_fwd(q, k, v, scale, causal):
+    if q.is_cuda:
+        from flash_attn.flash_attn_interface import _flash_attn_forward
+        out = _flash_attn_forward(q, k, v, 0.0, scale, causal=causal, window_size_left=-1, window_size_right=-1,
+                                  softcap=0.0, alibi_slopes=None, return_softmax=False)
+        return out[0].float(), out[1][..., :q.shape[1]]
+    return _block_fwd_ref(q, k, v, scale, causal)
+
+
+def _block_bwd(do, q, k, v, o, lse, scale, causal):
+    if q.is_cuda:
+        from flash_attn.flash_attn_interface import _flash_attn_backward
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        _flash_attn_backward(do.to(q.dtype).contiguous(), q, k, v, o.to(q.dtype).contiguous(), lse.contiguous(), dq, dk, dv,
+                             0.0, scale, causal, -1, -1, 0.0, None, False)
+        return dq.float(), dk.float(), dv.float()
+    return _block_bwd_ref(do, q, k, v, o, lse, scale, causal)
+
+
+def _merge(o, lse, o_b, lse_b):
+    """Online-softmax merge; o [B,S,N,D] fp32, lse [B,N,S]."""
+    if o is None:
+        return o_b, lse_b
+    new = torch.logaddexp(lse, lse_b)
+    w1 = torch.exp(lse - new).transpose(1, 2).unsqueeze(-1)
+    w2 = torch.exp(lse_b - new).transpose(1, 2).unsqueeze(-1)
+    return o * w1 + o_b * w2, new
+
+
+# ------------------------------------------------------------------------------------------ ring transport
+class RingP2P:
+    """Send to the next rank, receive from the previous one (batched isend/irecv), double buffered."""
+
+    def __init__(self, group):
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.next = dist.get_global_rank(group, (self.rank + 1) % self.world)
+        self.prev = dist.get_global_rank(group, (self.rank - 1) % self.world)
+        self._reqs = []
+
+    def exchange(self, send: torch.Tensor, reverse: bool = False) -> torch.Tensor:
+        recv = torch.empty_like(send)
+        dst, src = (self.prev, self.next) if reverse else (self.next, self.prev)
+        ops = [dist.P2POp(dist.isend, send.contiguous(), dst, self.group), dist.P2POp(dist.irecv, recv, src, self.group)]
+        if self.rank % 2:        # odd ranks post the receive first (avoids a send-send stall on CPU backends)
+            ops.reverse()
+        self._reqs = dist.batch_isend_irecv(ops)
+        return recv
+
+    def wait(self):
+        for r in self._reqs:
+            r.wait()
+        self._reqs = []
+
+
+def _step_plan(causal: bool, rank: int, src: int):
+    """(q slice, kv slice, causal flag) for the block from ``src``: slices are 'all', 'first', 'second' or None."""
+    if not causal:
+        return "all", "all", False
+    if src == rank:
+        return "all", "all", True
+    if src < rank:
+        return "all", "first", False
+    return "second", "all", False
+
+
+def _half(x, which, dim=1):
+    if which == "all":
+        return x
+    h = x.shape[dim] // 2
+    return x.narrow(dim, 0, h) if which == "first" else x.narrow(dim, h, h)
+
+
+class _RingAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, group, causal, scale):
+        ring = RingP2P(group)
+        P, r = ring.world, ring.rank
+        B, S, N, D = q.shape
+        out = torch.zeros(B, S, N, v.shape[-1], dtype=torch.float32, device=q.device)
+        lse = torch.full((B, N, S), float("-inf"), dtype=torch.float32, device=q.device)
+        kv = torch.stack([k, v]).contiguous()
+        for s in range(P):
+            nxt = ring.exchange(kv) if s < P - 1 else None
+            src = (r - s) % P
+            qs, ks, c = _step_plan(causal, r, src)
+            qb = _half(q, qs)
+            ob, lb = _block_fwd(qb.contiguous(), _half(kv[0], ks).contiguous(), _half(kv[1], ks).contiguous(), scale, c)
+            if qs == "all":
+                o2, l2 = _merge(out if s else None, lse if s else None, ob, lb)
+                out, lse = o2, l2
+            else:
+                h = S // 2
+                o2, l2 = _merge(out[:, h:], lse[..., h:], ob, lb)
+                out = torch.cat([out[:, :h], o2], 1)
+                lse = torch.cat([lse[..., :h], l2], -1)
+            if nxt is not None:
+                ring.wait()
+                kv = nxt
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.group, ctx.causal, ctx.scale = group, causal, scale
+        return out.to(q.dtype)
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, out, lse = ctx.saved_tensors
+        ring = RingP2P(ctx.group)
+        P, r = ring.world, ring.rank
+        S = q.shape[1]
+        dq = torch.zeros_like(q, dtype=torch.float32)
+        kv = torch.stack([k, v]).contiguous()
+        dkv = torch.zeros_like(kv, dtype=torch.float32)      # gradient of the block currently held
+        for s in range(P):
+            src = (r - s) % P
+            qs, ks, c = _step_plan(ctx.causal, r, src)
+            sl = slice(None) if qs == "all" else slice(S // 2, None)
+            dqb, dkb, dvb = _block_bwd(do[:, sl].contiguous(), q[:, sl].contiguous(), _half(kv[0], ks).contiguous(),
+                                       _half(kv[1], ks).contiguous(), out[:, sl].contiguous(), lse[..., sl].contiguous(),
+                                       ctx.scale, c)
+            dq[:, sl] += dqb
+            if ks == "all":
+                dkv[0] += dkb
+                dkv[1] += dvb
+            else:
+                h = kv.shape[2] // 2
+                dkv[0][:, :h] += dkb
+                dkv[1][:, :h] += dvb
+            # pass the block and its gradient on; after P hops both are back at the owner
+            both = torch.cat([kv.float(), dkv]).contiguous()
+            both = ring.exchange(both)
+            ring.wait()
+            kv, dkv = both[:2].to(k.dtype), both[2:]
+        return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None, None
+
+
+def ring_attention(q, k, v, group, causal: bool = False, softmax_scale: Optional[float] = None):
+    """q/k/v: [B, S_local, N, D] (zig-zag ordered when ``causal``).  Returns [B, S_local, N, D]."""
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if group is None or dist.get_world_size(group) == 1:
+        from ... import ops
+        return ops.attention_dense(q, k, v, causal, scale)
+    return _RingAttention.apply(q, k, v, group, causal, scale)

@@ -38,3 +38,17 @@ def test_gpu_world2(comm):
     assert "ok=True" in out
     if comm == "p2p":
         assert "p2p=True" in out
+
+
+def _run_script(nproc, script, *args, timeout=600):
+    port = 29000 + (os.getpid() % 400) + nproc
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, script), *args]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return r.stdout
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_context_parallel_attention_gloo(world):
+    assert "ok=True" in _run_script(world, "dist_cp_check.py")

@@ -1,2 +1,4 @@
 """Imports every built-in model file so that its ``@model_register`` decorators run."""
 from . import qwen2_5_vl  # noqa: F401
+from . import wan  # noqa: F401
+from .diffusion import flow_match  # noqa: F401

@@ -1,0 +1,146 @@
+"""Shared body of the Megatron-style entry scripts (``pretrain_vlm.py``, ``pretrain_sora.py`` ...).
+
+The reference's scripts each define ``model_provider / get_batch / loss_func / forward_step /
+train_valid_test_datasets_provider`` and hand them to ``pretrain()`` (pretrain_vlm.py:35-269,
+mindspeed_mm/training.py:86-346).  Here ``pretrain(kind)`` parses the same command line
+(flags + ``--mm-model/--mm-data/--mm-tool``), builds the model from ``args.mm.model``, maps the Megatron
+parallel flags onto the shared runtime (``--use-torch-fsdp2`` or plain data parallel -> sharding engine;
+``--tensor-model-parallel-size`` / ``--pipeline-model-parallel-size`` -> the TP / PP backends) and runs the same
+``TrainEngine`` loop as the native trainer, printing the same log line.
+"""
+from __future__ import annotations
+
+import os
+import sys
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..api import init_distributed, stable_init_fn
+from ..config.legacy import parse_legacy_args
+from ..parallel.fsdp import FSDPEngine, OptimConfig
+from ..parallel.state import init_parallel_state
+from .logging import print_rank0
+from .loss import build_loss
+from .lr_scheduler import LRSchedule
+from .tools import Profiler
+from .train_engine import TrainConfig, TrainEngine
+
+
+def model_provider(kind: str, args):
+    """Build the (meta-device) model named by ``args.mm.model``."""
+    mm = args.mm.model.to_dict()
+    if kind == "vlm":
+        from ..models.qwen2_5_vl import Qwen25VLConfig, Qwen25VLModel
+        cfg = Qwen25VLConfig.from_mm_json(mm)
+        with torch.device("meta"):
+            model = Qwen25VLModel(cfg)
+        ve = mm["image_encoder"]
+        if ve["vision_encoder"].get("freeze", False):
+            for n, p in model.visual.named_parameters():
+                if not n.startswith("merger"):
+                    p.requires_grad_(False)
+        if ve["vision_projector"].get("freeze", False):
+            for p in model.visual.merger.parameters():
+                p.requires_grad_(False)
+        return model
+    if kind == "sora":
+        from ..models.diffusion import FlowMatchScheduler
+        from ..models.wan import SoRAModel, WanConfig, WanDiT
+        pred = dict(mm["predictor"])
+        if pred.get("model_id") != "wandit":
+            from ..models.registry import build_model
+            net = build_model(pred["model_id"], pred)
+        else:
+            with torch.device("meta"):
+                net = WanDiT(WanConfig.from_mm_json(pred))
+        diff = {k: v for k, v in mm.get("diffusion", {}).items() if k != "model_id"}
+        return SoRAModel(net, FlowMatchScheduler(**diff), seed=args.seed)
+    raise ValueError(f"unknown entry kind {kind}")
+
+
+def datasets_provider(kind: str, args, model, ps):
+    """Synthetic datasets of the model's shapes unless ``args.mm.data`` names a registered dataset."""
+    from ..data.collate import PackedVLMCollator
+    from ..data.samplers import BaseRandomBatchSampler
+    from ..data.synthetic import (SyntheticVideoLatentDataset, SyntheticVideoLatentSpec, SyntheticVLMDataset,
+                                  SyntheticVLMSpec)
+    data = args.mm.data.to_dict() if hasattr(args.mm, "data") else {}
+    basic = data.get("dataset_param", {}).get("basic_parameters", {})
+    if kind == "vlm":
+        cfg = model.config
+        seq = int(args.seq_length or 1024)
+        ds = SyntheticVLMDataset(SyntheticVLMSpec(
+            seq_len=seq, images_per_sample=int(basic.get("images_per_sample", 1)), image_size=int(basic.get("image_size", 224)),
+            vocab_size=cfg.text.vocab_size, image_token_id=cfg.image_token_id,
+            vision_start_token_id=cfg.vision_start_token_id, seed=args.seed, num_samples=int(basic.get("num_samples", 1 << 20))))
+        v = cfg.vision
+        coll = PackedVLMCollator(cfg.image_token_id, cfg.vision_start_token_id, v.spatial_merge_size, v.patch_size,
+                                 v.window_size, v.hidden_size // v.num_heads)
+    else:
+        c = model.predictor.config
+        ds = SyntheticVideoLatentDataset(SyntheticVideoLatentSpec(
+            channels=c.in_dim, frames=int(basic.get("frames", 5)), height=int(basic.get("height", 16)),
+            width=int(basic.get("width", 16)), text_len=c.text_len, text_dim=c.text_dim, seed=args.seed,
+            num_samples=int(basic.get("num_samples", 1 << 20))))
+        coll = lambda ss: {k: torch.stack([s[k] for s in ss]) for k in ss[0]}   # noqa: E731
+    sampler = BaseRandomBatchSampler(len(ds), args.micro_batch_size, ps.get_dp_rank(), ps.get_dp_world_size(), seed=args.seed)
+
+    def gen():
+        for idx in sampler:
+            yield coll([ds[i] for i in idx])
+    return gen()
+
+
+def pretrain(kind: str, argv=None, device: Optional[str] = None):
+    args = parse_legacy_args(argv)
+    dev, rank, world = init_distributed(device)
+    torch.manual_seed(args.seed)
+    tp, pp, cp = args.tensor_model_parallel_size, args.pipeline_model_parallel_size, args.context_parallel_size
+    if tp > 1 or pp > 1:
+        from ..parallel.mcore import pretrain_mcore
+        return pretrain_mcore(kind, args, dev, rank, world)
+    uly = cp if args.context_parallel_algo in ("ulysses_cp_algo", "hybrid_cp_algo") else 1
+    if args.context_parallel_algo == "hybrid_cp_algo":
+        uly = int(getattr(args, "ulysses_degree_in_cp", None) or cp)
+    ps = init_parallel_state(world_size=world, device_type=dev.type, ulysses_parallel_size=uly,
+                             ring_attention_size=cp // uly)
+    model = model_provider(kind, args)
+    opt = OptimConfig(lr=args.lr, betas=(args.adam_beta1, args.adam_beta2), eps=args.adam_eps,
+                      weight_decay=args.weight_decay, clip_grad=args.clip_grad)
+    accum = max(1, args.global_batch_size // (args.micro_batch_size * ps.get_dp_world_size()))
+    engine = FSDPEngine(model.fsdp_units(), group=ps.get_fsdp_group() if world > 1 else False, device=dev,
+                        param_dtype=torch.bfloat16 if (args.bf16 and dev.type == "cuda") else torch.float32,
+                        opt=opt, grad_accum_steps=accum, no_recompute=("lm_head",) if kind == "vlm" else ())
+    std = getattr(getattr(model, "config", None), "init_std", 0.02)
+    engine.materialize(stable_init_fn(std, args.seed))
+    warm = args.lr_warmup_fraction or 0.0
+    sched = LRSchedule(lr=args.lr, train_iters=args.train_iters, lr_decay_style=args.lr_decay_style,
+                       lr_warmup_ratio=warm, lr_warmup_steps=int(getattr(args, "lr_warmup_iters", 0) or 0),
+                       lr_min=args.min_lr or 0.0)
+    loss_type = "per_token_loss" if args.calculate_per_token_loss else "default"
+    cfg = TrainConfig(train_iters=args.train_iters, micro_batch_size=args.micro_batch_size,
+                      gradient_accumulation_steps=accum, global_batch_size=args.global_batch_size,
+                      log_interval=args.log_interval, save_interval=args.save_interval or 0,
+                      exit_interval=int(args.exit_interval or 0), exit_duration_in_mins=float(args.exit_duration_in_mins or 0),
+                      log_tps=bool(args.log_tps))
+    ck = None
+    if args.save or args.load:
+        from ..checkpoint.sharded import DistributedCheckpointer
+        ck = DistributedCheckpointer(args.save, args.load, no_save_optim=args.no_save_optim, no_save_rng=args.no_save_rng)
+    prof_cfg = args.mm.tool.get("profile", None) if hasattr(args.mm, "tool") else None
+    prof = None
+    if prof_cfg is not None and getattr(prof_cfg, "enable", False):
+        sp = prof_cfg.static_param
+        prof = Profiler(True, getattr(prof_cfg, "ranks", [0]), sp.start_step, sp.end_step, sp.save_path)
+    te = TrainEngine(model, engine, build_loss(loss_type, ps.group("dp"), ps.get_dp_world_size()), sched, cfg,
+                     data_iter=datasets_provider(kind, args, model, ps), checkpointer=ck, profiler=prof,
+                     dp_group=ps.group("dp"), dp_world=ps.get_dp_world_size(), device=dev)
+    if ck and args.load:
+        te.load(load_optim=not args.no_load_optim, load_rng=not args.no_load_rng)
+    print_rank0(f"> parallel: {ps.describe()} | parameters: {engine.param_count() / 1e6:.1f} M")
+    hist = te.train()
+    if dist.is_initialized():
+        dist.barrier()
+    return hist

@@ -1,0 +1,202 @@
+"""Config-driven trainer for the native YAML schema.
+
+    torchrun --nproc-per-node N -m mindspeed_mm_b200.runtime.trainer config.yaml [a.b.c=value ...]
+
+Order of construction (reference: mindspeed_mm/fsdp/train/trainer.py:140-477): distributed init and seeds ->
+plugins -> parallel state -> model on the meta device (+ freeze, LoRA) -> sharding engine (materialise /
+load weights) -> optimizer hyper-parameters and LR schedule -> dataset, sampler, dataloader (optional
+preloader) -> checkpointers -> profiler / memory profiler / watchdog -> ``TrainEngine.train()``.
+"""
+from __future__ import annotations
+
+import json
+import os
+import random
+import sys
+from typing import Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..api import init_distributed, stable_init_fn
+from ..checkpoint import hf as hfio
+from ..checkpoint.sharded import DistributedCheckpointer
+from ..config.native import Arguments, load_config, match_modules
+from ..config.tree import get_dtype
+from ..models import registry
+from ..parallel.fsdp import FSDPEngine, OptimConfig
+from ..parallel.state import init_parallel_state
+from .logging import print_rank0
+from .loss import build_loss
+from .lr_scheduler import LRSchedule
+from .tools import MemoryProfiler, Profiler, Watchdog
+from .train_engine import TrainConfig, TrainEngine
+
+
+def set_seed(seed: int, deterministic: bool = False) -> None:
+    random.seed(seed)
+    np.random.seed(seed % (2 ** 32))
+    torch.manual_seed(seed)
+    if deterministic:
+        torch.use_deterministic_algorithms(True, warn_only=True)
+        os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
+
+
+class Trainer:
+    def __init__(self, args: Arguments, device: Optional[str] = None):
+        self.args = args
+        t = args.training
+        self.device, self.rank, self.world = init_distributed(device)
+        set_seed(t.seed, t.use_deter_comp or t.enable_full_determinism)
+        registry.import_plugin(t.plugin)
+        registry._ensure_builtin()
+        self.ps = init_parallel_state(world_size=self.world, device_type=self.device.type, **args.parallel.state_kwargs())
+        self.model = self.build_model()
+        self.engine = self.build_engine()
+        self.load_weights()
+        self.schedule = LRSchedule(lr=t.lr, train_iters=t.train_iters, lr_decay_style=t.lr_decay_style,
+                                   lr_warmup_ratio=t.lr_warmup_ratio, lr_min=t.lr_min, lr_start=t.lr_start,
+                                   lr_decay_ratio=t.lr_decay_ratio)
+        self.data_iter, self.val_iter_fn = self.build_data()
+        self.checkpointer = DistributedCheckpointer(t.save, t.load if t.load_format != "hf" else None, t.save_async,
+                                                    t.no_save_optim, t.no_save_rng) if (t.save or t.load) else None
+        cfg = TrainConfig(train_iters=t.train_iters, micro_batch_size=t.micro_batch_size,
+                          gradient_accumulation_steps=t.gradient_accumulation_steps or 1,
+                          global_batch_size=t.global_batch_size, log_interval=t.log_interval,
+                          save_interval=t.save_interval, val_interval=t.val_interval, exit_interval=t.exit_interval,
+                          exit_duration_in_mins=t.exit_duration_in_mins)
+        self.train_engine = TrainEngine(
+            self.model, self.engine, build_loss(args.features.loss_cfg.loss_type or "default", self.ps.group("dp"),
+                                                self.ps.get_dp_world_size()),
+            self.schedule, cfg, data_iter=self.data_iter, val_iter_fn=self.val_iter_fn, checkpointer=self.checkpointer,
+            profiler=Profiler.from_config(args.tools.profile),
+            memory_profiler=MemoryProfiler(**args.tools.memory_profile.model_dump()),
+            watchdog=Watchdog(t.watchdog_timeout_s).start() if t.watchdog_timeout_s else None,
+            dp_group=self.ps.group("dp"), dp_world=self.ps.get_dp_world_size(), device=self.device)
+        if self.checkpointer and t.load and t.load_format != "hf" and not hfio.is_hf_checkpoint(t.load):
+            self.train_engine.load(load_optim=not t.no_load_optim, load_rng=not t.no_load_rng)
+
+    # ------------------------------------------------------------------------------------------
+    def build_model(self):
+        m = self.args.model
+        cls = registry.model_register.get(m.model_id)
+        cfg = self._model_config(cls, m)
+        with torch.device("meta"):
+            model = cls(cfg)
+        names = [n for n, _ in model.named_modules()]
+        for n in match_modules(m.freeze, names):
+            for p in dict(model.named_modules())[n].parameters():
+                p.requires_grad_(False)
+        if self.args.training.lora.enable:
+            from ..tasks.lora import apply_lora
+            apply_lora(model, self.args.training.lora)
+        return model
+
+    def _model_config(self, cls, m):
+        extra = m.model_extra or {}
+        if "config" in extra:                         # inline model config in the YAML
+            return _config_from_dict(cls, extra["config"])
+        if m.model_name_or_path and os.path.exists(os.path.join(m.model_name_or_path, "config.json")):
+            with open(os.path.join(m.model_name_or_path, "config.json")) as f:
+                return _config_from_hf(cls, json.load(f))
+        return _config_from_dict(cls, {"preset": extra.get("preset", "tiny")})
+
+    def build_engine(self) -> FSDPEngine:
+        a, t, plan = self.args, self.args.training, self.args.parallel.fsdp_plan
+        opt = OptimConfig(lr=t.lr, betas=(t.adam_beta1, t.adam_beta2), eps=t.adam_eps, weight_decay=t.weight_decay,
+                          clip_grad=t.clip_grad)
+        if t.no_decay_params or t.no_decay_modules:
+            keys = tuple(t.no_decay_params) + tuple(t.no_decay_modules)
+            opt.no_decay = lambda n, p: p.dim() < 2 or any(k in n for k in keys)
+        units = self.model.fsdp_units()
+        if plan.apply_modules:
+            wanted = set(match_modules(plan.apply_modules, [n for n, _ in units]))
+            if wanted and wanted != {n for n, _ in units}:
+                print_rank0(f"fsdp_plan.apply_modules selects {len(wanted)} of {len(units)} units; "
+                            "the remaining units are sharded as well (every parameter must live in one unit)")
+        recompute = a.features.recompute or a.parallel.recompute
+        group = self.ps.get_fsdp_group() if self.world > 1 else False
+        return FSDPEngine(units, group=group, device=self.device, param_dtype=get_dtype(plan.param_dtype or "bf16")
+                          if self.device.type == "cuda" else torch.float32,
+                          reduce_dtype=get_dtype(plan.reduce_dtype or "fp32"), opt=opt, recompute=recompute,
+                          grad_accum_steps=t.gradient_accumulation_steps or 1,
+                          prefetch=max(plan.num_to_forward_prefetch or 0, plan.num_to_backward_prefetch or 0),
+                          comm=plan.comm)
+
+    def load_weights(self):
+        t = self.args.training
+        std = getattr(getattr(self.model, "config", None), "init_std", 0.02)
+        self.engine.materialize(stable_init_fn(std, t.seed))
+        path = t.load or self.args.model.model_name_or_path
+        fmt = t.load_format
+        if path and (fmt == "hf" or (fmt == "auto" and hfio.is_hf_checkpoint(path))):
+            ops = getattr(self.model, "hf_ops", None)
+            if ops is None and self.args.model.model_id == "qwen2_5vl":
+                ops = hfio.qwen25vl_ops(self.model.config)
+            if ops is not None:
+                hfio.load_hf_into_engine(self.engine, path, ops, strict=t.load_strict)
+
+    def build_data(self):
+        from ..data import build_dataloader
+        return build_dataloader(self.args, self.model, self.ps, self.device)
+
+    def train(self):
+        hist = self.train_engine.train()
+        t = self.args.training
+        if t.save and t.save_format == "hf" and self.args.model.model_id == "qwen2_5vl":
+            hfio.save_engine_as_hf(self.engine, os.path.join(t.save, "hf"), hfio.qwen25vl_ops(self.model.config),
+                                   get_dtype(t.save_ckpt_dtype) if t.save_ckpt_dtype else None,
+                                   self.args.model.model_name_or_path, self.rank)
+        if self.checkpointer:
+            self.checkpointer.wait()
+        return hist
+
+
+def _config_from_dict(cls, d: dict):
+    cfg_cls = _config_class(cls)
+    preset = d.get("preset")
+    cfg = getattr(cfg_cls, preset)() if preset and hasattr(cfg_cls, preset) else cfg_cls()
+    for k, v in d.items():
+        if k == "preset":
+            continue
+        if isinstance(v, dict) and hasattr(cfg, k):
+            sub = getattr(cfg, k)
+            for kk, vv in v.items():
+                setattr(sub, kk, tuple(vv) if isinstance(vv, list) else vv)
+        elif hasattr(cfg, k):
+            setattr(cfg, k, tuple(v) if isinstance(v, list) else v)
+    return cfg
+
+
+def _config_from_hf(cls, hf: dict):
+    cfg_cls = _config_class(cls)
+    if hasattr(cfg_cls, "from_hf"):
+        return cfg_cls.from_hf(hf)
+    return cfg_cls()
+
+
+def _config_class(cls):
+    import inspect
+    sig = inspect.signature(cls.__init__)
+    ann = list(sig.parameters.values())[1].annotation
+    if isinstance(ann, str):
+        mod = sys.modules[cls.__module__]
+        ann = getattr(mod, ann)
+    return ann
+
+
+def main(argv=None):
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if not argv:
+        raise SystemExit("usage: trainer.py config.yaml [key=value ...]")
+    args = load_config(argv[0], argv[1:])
+    tr = Trainer(args)
+    tr.train()
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

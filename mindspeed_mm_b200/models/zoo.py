@@ -2,3 +2,4 @@
 from . import qwen2_5_vl  # noqa: F401
 from . import wan  # noqa: F401
 from .diffusion import flow_match  # noqa: F401
+from . import qwen3_vl_moe  # noqa: F401

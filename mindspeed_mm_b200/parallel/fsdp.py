@@ -154,13 +154,14 @@ _EMPTY = _Empty()
 class Unit:
     def __init__(self, name: str, module: nn.Module, engine: "FSDPEngine"):
         self.name, self.module, self.engine = name, module, engine
-        named = [(f"{name}.{n}" if name else n, p) for n, p in module.named_parameters()]
+        named = [(f"{name}.{n}" if name else n, p) for n, p in module.named_parameters()
+                 if id(p) not in engine.exclude_params]
         train = [(n, p) for n, p in named if p.requires_grad]
         frozen = [(n, p) for n, p in named if not p.requires_grad]
         mk = lambda ps, tr: FlatGroup(ps, engine.rank, engine.world, engine.device, engine.param_dtype, tr, engine.opt)
         self.groups: List[FlatGroup] = ([mk(train, True)] if train else []) + ([mk(frozen, False)] if frozen else [])
         # shapes are recorded by the groups above; now swap in re-bindable placeholders
-        mapping = _to_flat_params(module, engine.device, engine.param_dtype)
+        mapping = _to_flat_params(module, engine.device, engine.param_dtype, engine.exclude_params)
         for g in self.groups:
             g.named_params = [(n, mapping[id(p)]) for n, p in g.named_params]
         self.unsharded = False
@@ -183,7 +184,7 @@ class FSDPEngine:
                  reduce_dtype: torch.dtype = torch.float32, opt: Optional[OptimConfig] = None,
                  recompute: bool = True, grad_accum_steps: int = 1, prefetch: int = 1,
                  comm: str = "auto", grad_divide: Optional[float] = None,
-                 no_recompute: Sequence[str] = ("lm_head",)):
+                 no_recompute: Sequence[str] = ("lm_head",), exclude_params: Sequence[nn.Parameter] = ()):
         self.group = group
         self.world = dist.get_world_size(group) if (dist.is_initialized() and group is not False) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
@@ -194,6 +195,7 @@ class FSDPEngine:
         self.grad_accum_steps = grad_accum_steps
         self.prefetch = prefetch
         self.grad_divide = float(grad_divide if grad_divide is not None else self.world)
+        self.exclude_params = {id(p) for p in exclude_params}    # owned by another engine (e.g. experts)
         self.units: List[Unit] = [Unit(n, m, self) for n, m in units]
         for i, u in enumerate(self.units):
             u.index = i
@@ -363,11 +365,11 @@ class FSDPEngine:
                 else:
                     gshard = self._reduce_scatter(g, flat)
                     if fused:
-                        self._adamw(g, gshard, 1.0)
+                        self._adamw(g, gshard, 1.0 / self.grad_divide if self.world == 1 else 1.0)
                     else:
                         if g.grad32 is None:
                             g.grad32 = torch.zeros(g.shard_numel, dtype=self.reduce_dtype, device=self.device)
-                        g.grad32.add_(gshard)
+                        g.grad32.add_(gshard, alpha=1.0 / self.grad_divide if self.world == 1 else 1.0)
 
     def _reduce_scatter(self, g: FlatGroup, flat: torch.Tensor) -> torch.Tensor:
         if self.world == 1:
@@ -497,7 +499,7 @@ class FSDPEngine:
         return sum(g.numel for u in self.units for g in u.groups)
 
 
-def _to_flat_params(module: nn.Module, device, dtype) -> dict:
+def _to_flat_params(module: nn.Module, device, dtype, exclude=()) -> dict:
     """Swap every parameter for a same-shaped placeholder of the flat buffer's device/dtype.
 
     The placeholder's storage is replaced by a view of the flat buffer in ``FlatGroup.bind``; the
@@ -507,7 +509,7 @@ def _to_flat_params(module: nn.Module, device, dtype) -> dict:
     mapping = {}
     for m in module.modules():
         for n, p in list(m._parameters.items()):
-            if p is None:
+            if p is None or id(p) in exclude:
                 continue
             if id(p) not in mapping:
                 mapping[id(p)] = nn.Parameter(torch.empty(0, dtype=dtype, device=device), requires_grad=p.requires_grad)
@@ -592,3 +594,91 @@ class _UnitFn(torch.autograd.Function):
         u.bwd_done = True
         grads = [t.grad if need else None for t, need in zip(tensors, ctx.needs)]
         return (None, None, None, None, *grads)
+
+
+class EngineMux:
+    """Two engines over one model: dense parameters (sharded over the FSDP group) and expert parameters
+    (sharded over the expert-FSDP group, gradients divided by the full data-parallel size).  The reference
+    builds the same split with a second ``fully_shard`` mesh and a second optimizer
+    (fsdp/distributed/expert_parallel/expert_fully_shard_parallel.py:22-57, fsdp/optimizer/optimizer.py:374-520).
+    Expert modules find their engine through ``module._fsdp_run``."""
+
+    def __init__(self, dense: FSDPEngine, expert: FSDPEngine):
+        self.dense, self.expert = dense, expert
+        for u in expert.units:
+            u.recompute = False
+            u.module._fsdp_run = expert.run
+        self.device, self.rank, self.world = dense.device, dense.rank, dense.world
+        self.group = dense.group
+
+    @property
+    def engines(self):
+        return (self.dense, self.expert)
+
+    def run(self, module, *a, **k):
+        return self.dense.run(module, *a, **k)
+
+    def materialize(self, init_fn):
+        for e in self.engines:
+            e.materialize(init_fn)
+
+    def set_lr(self, lr):
+        for e in self.engines:
+            e.set_lr(lr)
+
+    def end_micro_step(self):
+        for e in self.engines:
+            e.end_micro_step()
+
+    def finish_step(self, lr=None):
+        """Joint gradient clipping: the global norm combines both engines' squared norms."""
+        if self.dense.opt.clip_grad > 0:
+            return _joint_clip_finish(self.engines)
+        norms = [e.finish_step(lr) for e in self.engines]
+        return norms[0]
+
+    def named_full_params(self):
+        for e in self.engines:
+            yield from e.named_full_params()
+
+    def load_full_params(self, getter):
+        return sum((e.load_full_params(getter) for e in self.engines), [])
+
+    def sharded_state(self):
+        out = {}
+        for tag, e in zip(("dense", "expert"), self.engines):
+            out.update({f"{tag}/{k}": v for k, v in e.sharded_state().items()})
+        return out
+
+    def param_count(self):
+        return sum(e.param_count() for e in self.engines)
+
+
+def _joint_clip_finish(engines):
+    """Deferred update of several engines under ONE clip coefficient (EP params reduce over their own
+    groups first: fsdp/optimizer/clip_grad_norm.py:69-116)."""
+    total = None
+    for e in engines:
+        e.flush_pending()
+        if e.cuda:
+            torch.cuda.current_stream().wait_stream(e.comm_stream)
+        groups = [g for u in e.units for g in u.groups if g.trainable and g.grad32 is not None]
+        if not groups:
+            continue
+        sq = torch.stack([g.grad32.float().pow(2).sum() for g in groups]).sum() / (e.grad_accum_steps ** 2)
+        if e.world > 1:
+            dist.all_reduce(sq, group=e.group)
+        total = sq if total is None else total + sq
+    # expert shards differ across EP ranks: sum their squared norms over the whole world once
+    norm = total.sqrt()
+    clip = engines[0].opt.clip_grad
+    scale = torch.clamp(clip / (norm + 1e-6), max=1.0)
+    for e in engines:
+        for u in e.units:
+            for g in u.groups:
+                if g.trainable and g.grad32 is not None:
+                    e._adamw(g, g.grad32, scale / e.grad_accum_steps)
+                    g.grad32 = None
+        if e._p2p is not None:
+            e._p2p.step_barrier()
+    return norm

@@ -1,0 +1,92 @@
+"""Expert parallelism under gloo (run with torch.distributed.run): a tiny MoE VLM with ep = world gives the
+same losses as the single-process model holding all experts, for both dispatchers."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from bench import make_batches  # noqa: E402
+from mindspeed_mm_b200.api import stable_init_fn  # noqa: E402
+from mindspeed_mm_b200.models.qwen3_vl_moe import Qwen3VLMoEConfig, Qwen3VLMoEModel  # noqa: E402
+from mindspeed_mm_b200.parallel.fsdp import EngineMux, FSDPEngine, OptimConfig  # noqa: E402
+from mindspeed_mm_b200.parallel.state import init_parallel_state, reset_parallel_state  # noqa: E402
+
+
+def build(cfg, world, ep, group, dispatcher):
+    cfg.text.ep_dispatcher = dispatcher
+    ps = init_parallel_state(world_size=world, device_type="cpu", expert_parallel_size=ep)
+    with torch.device("meta"):
+        model = Qwen3VLMoEModel(cfg, ep_size=ep)
+    opt = OptimConfig(lr=1e-3)
+    ex = [p for _, m in model.expert_units() for p in m.parameters()]
+    dense = FSDPEngine(model.fsdp_units(), group=group, device="cpu", param_dtype=torch.float32, opt=opt, exclude_params=ex)
+    # ep == world: experts are not sharded any further; their gradients are divided by the world size
+    expert = FSDPEngine(model.expert_units(), group=False, device="cpu", param_dtype=torch.float32, opt=opt,
+                        grad_divide=world, no_recompute=())
+    mux = EngineMux(dense, expert)
+    mux.materialize(stable_init_fn(0.02, 0))
+    return model, mux
+
+
+def main():
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    cfg = Qwen3VLMoEConfig.tiny()
+    packs = [make_batches(cfg, 2, 384, 1, 1, 224, r, pin=False) for r in range(world)]
+    ok = True
+    # single-process twin with all experts (built first; its weights seed the EP runs)
+    reset_parallel_state()
+    ref_model, ref = build(cfg, 1, 1, False, "alltoall")
+    full = {n: t.detach().clone() for n, t in ref.named_full_params()}
+    ref.dense.grad_accum_steps = ref.expert.grad_accum_steps = world
+    ref.dense.deferred = ref.expert.deferred = True
+    ref_losses = []
+    for s in range(2):
+        ref.set_lr(1e-3)
+        ls = []
+        for r in range(world):
+            loss_sum, n = ref_model(packs[r][s], run=ref.run)
+            (loss_sum / n).backward()
+            ref.end_micro_step()
+            ls.append(float((loss_sum / n).detach()))
+        ref.finish_step()
+        ref_losses.append(sum(ls) / world)
+    for disp in ("alltoall", "allgather"):
+        reset_parallel_state()
+        model, mux = build(cfg, world, world, dist.group.WORLD, disp)
+        e_local = cfg.text.num_experts // world
+
+        def getter(name, shape):
+            t = full[name]
+            if ".mlp.experts." in name:
+                t = t[rank * e_local:(rank + 1) * e_local]
+            return t
+        assert mux.load_full_params(getter) == []
+        losses = []
+        for s in range(2):
+            mux.set_lr(1e-3)
+            loss_sum, n = model(packs[rank][s], run=mux.run)
+            loss = loss_sum / n
+            loss.backward()
+            mux.end_micro_step()
+            mux.finish_step()
+            t = loss.detach().clone()
+            dist.all_reduce(t)
+            losses.append(float(t) / world)
+        for a, b in zip(losses, ref_losses):
+            if abs(a - b) > 3e-5 * max(1, abs(b)):
+                ok = False
+        if rank == 0:
+            print(f"dist_moe_check world={world} dispatcher={disp} losses={losses} ref={ref_losses}", flush=True)
+    flag = torch.tensor([int(ok)])
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(f"dist_moe_check ok={bool(flag.item())}", flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -52,3 +52,7 @@ def _run_script(nproc, script, *args, timeout=600):
 @pytest.mark.parametrize("world", [2, 4])
 def test_context_parallel_attention_gloo(world):
     assert "ok=True" in _run_script(world, "dist_cp_check.py")
+
+
+def test_expert_parallel_gloo():
+    assert "ok=True" in _run_script(2, "dist_moe_check.py")

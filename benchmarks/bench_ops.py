@@ -117,6 +117,29 @@ def bench_elementwise(out, small):
     rec("adamw_shard", lambda: native.adamw_shard(p, m, v, g, p16, 1e-4, 0.9, 0.999, 1e-8, 0.0, 1, n, 1.0), n * 28.0)
 
 
+def bench_fmha(out, small):
+    import math
+    tf, _, src = peaks()
+    from flash_attn import flash_attn_varlen_func
+    cases = [("llm_causal_4x2048", [2048] * 4, 28, 4, True), ("dit_full_1x16384", [16384], 8, 8, False)]
+    if not small:
+        cases.append(("dit_full_1x75600_5heads", [75600], 5, 5, False))
+    for name, lens, nq, nkv, causal in cases:
+        T, D = sum(lens), 128
+        q = torch.randn(T, nq, D, device="cuda", dtype=torch.bfloat16)
+        k = torch.randn(T, nkv, D, device="cuda", dtype=torch.bfloat16)
+        v = torch.randn(T, nkv, D, device="cuda", dtype=torch.bfloat16)
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+        flops = sum(4.0 * l * l * D * nq for l in lens) * (0.5 if causal else 1.0)
+        sc = 1.0 / math.sqrt(D)
+        t = time_fn(lambda: native.fmha_forward(q, k, v, cu, cu, causal, sc))
+        tl = time_fn(lambda: flash_attn_varlen_func(q, k, v, cu, cu, max(lens), max(lens), causal=causal))
+        emit(dict(op="fmha_fwd", case=name, T=T, heads=nq, kv_heads=nkv, causal=causal, ms=round(t, 4),
+                  tflops=round(flops / t / 1e9, 1), frac_of_peak=round(flops / t / 1e9 / tf, 3), peak=src,
+                  flash_attn2_ms=round(tl, 4), flash_attn2_tflops=round(flops / tl / 1e9, 1), vs_flash_attn2=round(tl / t, 3)), out)
+        native.check_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ops", default="gemm,elementwise")
@@ -124,7 +147,7 @@ def main():
     ap.add_argument("--small", action="store_true")
     a = ap.parse_args()
     for op in a.ops.split(","):
-        {"gemm": bench_gemm, "elementwise": bench_elementwise}[op](a.out, a.small)
+        {"gemm": bench_gemm, "elementwise": bench_elementwise, "fmha": bench_fmha}[op](a.out, a.small)
 
 
 if __name__ == "__main__":

@@ -49,6 +49,8 @@ def _declare(L):
         "mm_adamw": [_p, _p, _p, _p, _i, _p, _ll, _ll, _f, _f, _f, _f, _f, _f, _f, _f, _p, _p],
         "mm_gemm_bf16": [_p, _p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _p, _p],
         "mm_ce_fwd_bwd": [_p, _ll, _p, _p, _i, _i, _i, _p],
+        "mm_fmha_max_tiles": [_i, _i],
+        "mm_fmha_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _f, _p, _p],
         "mm_p2p_flag_bytes": [],
         "mm_p2p_allgather": [_p, _p, _ll, _i, _i, _i, _p],
         "mm_p2p_rs_adamw": [_p, _p, _ll, _i, _i, _i, C.c_uint, _f, _p, _p, _p, _p, _ll, _f, _f, _f, _f, _f, _f, _f,
@@ -406,7 +408,63 @@ def linear(x, w, bias=None):
 
 # --------------------------------------------------------------------------- not yet native
 def fmha_supported(q, k, v) -> bool:
-    return False
+    return (os.environ.get("MM_B200_FMHA", "1") == "1" and q.dtype == torch.bfloat16 and q.shape[-1] == 128
+            and v.shape[-1] == 128 and q.shape[1] % k.shape[1] == 0)
+
+
+def _dense_heads(t):
+    """[T, N, D] with unit stride on D, D between heads and an 8-element aligned token stride (views into a
+    fused qkv tensor qualify); anything else is copied."""
+    T, N, D = t.shape
+    if t.stride(2) != 1 or t.stride(1) != D or t.stride(0) % 8 or t.data_ptr() % 16:
+        t = t.contiguous()
+    return t
+
+
+def fmha_forward(q, k, v, cu_q, cu_k, causal, scale):
+    """Returns (out [T, Nq, D] bf16, lse [Nq, T] fp32) from the tcgen05 kernel."""
+    q, k, v = _dense_heads(q), _dense_heads(k), _dense_heads(v)
+    T, Nq, D = q.shape
+    Tk, Nkv = k.shape[0], k.shape[1]
+    n_seqs = cu_q.numel() - 1
+    out = torch.empty(T, Nq, D, dtype=q.dtype, device=q.device)
+    lse = torch.empty(Nq, T, dtype=torch.float32, device=q.device)
+    plan = torch.empty(2 * lib().mm_fmha_max_tiles(T, n_seqs) + 1, dtype=torch.int32, device=q.device)
+    cu_q = cu_q.to(torch.int32)
+    cu_k = cu_k.to(torch.int32)
+    rc = lib().mm_fmha_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), cu_q.data_ptr(),
+                           cu_k.data_ptr(), plan.data_ptr(), T, Tk, n_seqs, Nq, Nkv, D, q.stride(0), k.stride(0),
+                           v.stride(0), int(causal), float(scale), status_word(q.device).data_ptr(), _st())
+    _check(rc, "fmha_fwd")
+    return out, lse
+
+
+class _FMHA(torch.autograd.Function):
+    """Forward: tcgen05 kernel.  Backward: flash-attn's varlen backward fed with this forward's out / lse
+    (library kernel, until the tcgen05 backward replaces it)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, causal, scale):
+        out, lse = fmha_forward(q, k, v, cu_q, cu_k, causal, scale)
+        ctx.save_for_backward(q, k, v, out, lse, cu_q, cu_k)
+        ctx.meta = (max_q, max_k, causal, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, do):
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
+        q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
+        max_q, max_k, causal, scale = ctx.meta
+        dq, dk, dv = torch.empty(q.shape, dtype=q.dtype, device=q.device), torch.empty(k.shape, dtype=k.dtype, device=k.device), \
+            torch.empty(v.shape, dtype=v.dtype, device=v.device)
+        _flash_attn_varlen_backward(do.contiguous(), q, k, v, out, lse, dq, dk, dv, cu_q.to(torch.int32), cu_k.to(torch.int32),
+                                    max_q, max_k, 0.0, scale, causal, -1, -1, 0.0, None, False)
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+def attention_varlen(q, k, v, cu_q, cu_k, max_q, max_k, causal, scale):
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    return _FMHA.apply(q, k, v, cu_q, cu_k, max_q, max_k, bool(causal), float(scale))
 
 
 def lce_supported(h, w) -> bool:

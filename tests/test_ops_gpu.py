@@ -198,3 +198,31 @@ def test_linear_cross_entropy(T, H, V):
     assert abs(float(loss / n) - float(lr / nr)) < 2e-2 * float(lr / nr)
     _close(h.grad, hr.grad, rtol=5e-2, atol=1e-5)
     _close(w.grad, wr.grad, rtol=5e-2, atol=1e-5)
+
+
+@pytest.mark.parametrize("lens,nq,nkv,causal", [([128], 1, 1, False), ([256, 128], 2, 1, False), ([300, 77, 513], 4, 2, True),
+                                                  ([2048, 2048], 28, 4, True), ([1000], 5, 5, False)])
+def test_fmha_forward_and_grad(lens, nq, nkv, causal):
+    from mindspeed_mm_b200.ops import native
+    torch.manual_seed(0)
+    T, D = sum(lens), 128
+    qkv = torch.randn(T, (nq + 2 * nkv) * D, device=DEV, dtype=torch.bfloat16)
+    q = qkv[:, :nq * D].view(T, nq, D)                       # strided views, like the model passes them
+    k = qkv[:, nq * D:(nq + nkv) * D].view(T, nkv, D)
+    v = qkv[:, (nq + nkv) * D:].view(T, nkv, D)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    out, lse = native.fmha_forward(q, k, v, cu, cu, causal, 1.0 / math.sqrt(D))
+    ro, rl = ref.attention_varlen(q.float(), k.float(), v.float(), cu.cpu(), cu.cpu(), causal, return_lse=True)
+    _close(out, ro, rtol=2e-2, atol=2e-2)
+    assert (lse - rl).abs().max().item() < 2e-2
+    # autograd path (native forward + backward fed with its out / lse)
+    qg, kg, vg = (t.detach().clone().requires_grad_() for t in (q, k, v))
+    o = ops.attention_varlen(qg, kg, vg, cu, cu, max(lens), max(lens), causal=causal)
+    do = torch.randn_like(o)
+    o.backward(do)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    orf = ref.attention_varlen(qr, kr, vr, cu.cpu(), cu.cpu(), causal)
+    orf.backward(do.float())
+    _close(qg.grad, qr.grad, rtol=3e-2, atol=3e-2)
+    _close(kg.grad, kr.grad, rtol=3e-2, atol=3e-2)
+    _close(vg.grad, vr.grad, rtol=3e-2, atol=3e-2)

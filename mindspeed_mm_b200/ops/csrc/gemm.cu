@@ -46,6 +46,18 @@ struct Params {
     const bf16* bias;
     int* status;
     int group_m;
+    // output routing (fused all-to-all / reduce-scatter push): where a 128 x 64 output slab goes
+    //   mode 0: C[m, n] of this GPU
+    //   mode 1: column blocks of width `blk` are dealt round-robin to `world` destinations (Ulysses head scatter):
+    //           dst = (n / blk) % world, column (n / (blk * world)) * blk + n % blk, row row_off + m
+    //   mode 2: row blocks of `blk` rows go to destination m / blk, stored at row rank * blk + m % blk
+    //           (every source has its own slot on the destination, which then sums the slots)
+    int mode, blk, world, rank, row_off;
+};
+
+constexpr int kMaxDst = 8;
+struct TMapSet {
+    CUtensorMap m[kMaxDst];
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int group_m, int& mb, int& nb) {
@@ -61,7 +73,7 @@ __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const __grid_constant__ CUtensorMap tmC, Params p) {
+            const __grid_constant__ TMapSet tmC, Params p) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -96,7 +108,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         fence_barrier_init();
         prefetch_tmap(&tmA);
         prefetch_tmap(&tmB);
-        prefetch_tmap(&tmC);
+        for (int d = 0; d < (p.mode ? p.world : 1); ++d) prefetch_tmap(&tmC.m[d]);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, C::kTmemCols);
@@ -243,7 +255,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 fence_proxy_async();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (issuer) {
-                    tma_store_2d(&tmC, buf, n0, mb * BM);
+                    if (p.mode == 0) {
+                        tma_store_2d(&tmC.m[0], buf, n0, mb * BM);
+                    } else if (p.mode == 1) {
+                        const int b = n0 / p.blk;
+                        tma_store_2d(&tmC.m[b % p.world], buf, (b / p.world) * p.blk + n0 % p.blk, p.row_off + mb * BM);
+                    } else {
+                        const int m0 = mb * BM;
+                        tma_store_2d(&tmC.m[m0 / p.blk], buf, n0, p.rank * p.blk + m0 % p.blk);
+                    }
                     tma_commit();
                 }
             }
@@ -266,19 +286,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
 }
 
+struct Route {
+    int mode = 0, blk = 0, world = 1, rank = 0, row_off = 0;
+    void* const* dst = nullptr;     // mode != 0: `world` destination base pointers (peer-mapped)
+    long long dst_rows = 0, dst_cols = 0;
+};
+
 template <int BN, bool A_MN, bool B_MN>
 int launch(const void* A, const void* B, void* Cc, const void* bias, int M, int N, int K, long long lda, long long ldb,
-           long long ldc, int* status, cudaStream_t st) {
+           long long ldc, int* status, cudaStream_t st, const Route& rt = Route()) {
     using C = Cfg<BN>;
-    CUtensorMap tA, tB, tC;
+    CUtensorMap tA, tB;
+    TMapSet tC;
     int r;
     // A_MN: memory is [K, M] -> rows=K, cols=M, box = 64 k-rows x 64 m ;  else rows=M, cols=K, box = 128 x 64
     r = A_MN ? make_tmap_2d(&tA, A, K, M, lda, BK, 64) : make_tmap_2d(&tA, A, M, K, lda, BM, BK);
     if (r) return 1000 + r;
     r = B_MN ? make_tmap_2d(&tB, B, K, N, ldb, BK, 64) : make_tmap_2d(&tB, B, N, K, ldb, BN, BK);
     if (r) return 2000 + r;
-    r = make_tmap_2d(&tC, Cc, M, N, ldc, BM, 64);
-    if (r) return 3000 + r;
+    if (rt.mode == 0) {
+        r = make_tmap_2d(&tC.m[0], Cc, M, N, ldc, BM, 64);
+        if (r) return 3000 + r;
+    } else {
+        if (rt.world > kMaxDst) return -5;
+        for (int d = 0; d < rt.world; ++d) {
+            r = make_tmap_2d(&tC.m[d], rt.dst[d], rt.dst_rows, rt.dst_cols, ldc, BM, 64);
+            if (r) return 3000 + r;
+        }
+    }
     auto kern = gemm_kernel<BN, A_MN, B_MN>;
     static bool done = false;
     if (!done) {
@@ -294,7 +329,7 @@ int launch(const void* A, const void* B, void* Cc, const void* bias, int M, int 
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     }
     const int tiles = m_blocks * n_blocks;
-    Params p{M, N, K, (const bf16*)bias, status, 8};
+    Params p{M, N, K, (const bf16*)bias, status, 8, rt.mode, rt.blk, rt.world, rt.rank, rt.row_off};
     const int grid = tiles < sms ? tiles : sms;
     kern<<<grid, kThreads, C::kSmem, st>>>(tA, tB, tC, p);
     return (int)cudaGetLastError();
@@ -319,4 +354,56 @@ MM_API int mm_gemm_bf16(const void* A, const void* B, void* C, const void* bias,
     }
     MM_DISPATCH(256)
 #undef MM_DISPATCH
+}
+
+
+// Routed output (the collective is the epilogue: slabs are written straight into the destinations' buffers over
+// NVLink).  K-major operands (y = x W^T + bias).  mode 1: all-to-all of column blocks (Ulysses head scatter),
+// requires blk % 64 == 0; mode 2: push of row blocks into per-source slots (first half of a reduce-scatter),
+// requires blk % 128 == 0.  dst[d]: base of destination d's [dst_rows, dst_cols] bf16 buffer with row pitch ldc.
+MM_API int mm_gemm_bf16_routed(const void* A, const void* B, const void* bias, int M, int N, int K, long long lda,
+                               long long ldb, void* const* dst, long long dst_rows, long long dst_cols, long long ldc,
+                               int mode, int blk, int world, int rank, int row_off, int* status, cudaStream_t st) {
+    if ((lda | ldb | ldc) % 8) return -1;
+    if (((uintptr_t)A | (uintptr_t)B) & 15) return -2;
+    if (mode == 1 && (blk % 64 || N % (blk * world))) return -3;
+    if (mode == 2 && (blk % 128 || M != blk * world)) return -3;
+    if (mode != 1 && mode != 2) return -4;
+    Route rt;
+    rt.mode = mode; rt.blk = blk; rt.world = world; rt.rank = rank; rt.row_off = row_off;
+    rt.dst = dst; rt.dst_rows = dst_rows; rt.dst_cols = dst_cols;
+    if (mode == 1 && blk % 256 == 0)
+        return launch<256, false, false>(A, B, nullptr, bias, M, N, K, lda, ldb, ldc, status, st, rt);
+    if (mode == 2 && N >= 256)
+        return launch<256, false, false>(A, B, nullptr, bias, M, N, K, lda, ldb, ldc, status, st, rt);
+    return launch<128, false, false>(A, B, nullptr, bias, M, N, K, lda, ldb, ldc, status, st, rt);
+}
+
+// out[r, :] = sum_s slots[s * rows + r, :]   (second half of the reduce-scatter: fold the per-source slots)
+namespace {
+__global__ void fold_slots_kernel(const bf16* __restrict__ slots, bf16* __restrict__ out, long long rows, int cols,
+                                  long long pitch, int world) {
+    const int cv = cols >> 3;
+    const long long total = rows * cv;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cv;
+        const int c = (int)(i - r * cv);
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int s = 0; s < world; ++s) {
+            float f[8];
+            unpack8(reinterpret_cast<const Vec8*>(slots + (s * rows + r) * pitch)[c], f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] += f[k];
+        }
+        reinterpret_cast<Vec8*>(out + r * cols)[c] = pack8(acc);
+    }
+}
+}  // namespace
+
+MM_API int mm_fold_slots(const void* slots, void* out, long long rows, int cols, long long pitch, int world, cudaStream_t st) {
+    if (cols % 8 || pitch % 8) return -1;
+    long long work = rows * (cols / 8);
+    int grid = (int)((work + 255) / 256 < 148 * 8 ? (work + 255) / 256 : 148 * 8);
+    fold_slots_kernel<<<grid < 1 ? 1 : grid, 256, 0, st>>>((const bf16*)slots, (bf16*)out, rows, cols, pitch, world);
+    return (int)cudaGetLastError();
 }

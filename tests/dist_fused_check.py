@@ -1,0 +1,113 @@
+"""Fused GEMM + collective kernels against GEMM followed by the NCCL collective (>= 2 GPUs; run with
+torch.distributed.run).  Also times both with CUDA events (max over ranks)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from mindspeed_mm_b200.comm.fused import RowParallelLinearRS, UlyssesQKVProjection  # noqa: E402
+from mindspeed_mm_b200.ops import native  # noqa: E402
+
+
+def timed(fn, iters=5):
+    for _ in range(2):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
+def main():
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, W = dist.get_rank(), dist.get_world_size()
+    g = dist.group.WORLD
+    ok = True
+    torch.manual_seed(0)
+    big = "--big" in sys.argv
+    # ---------------- Ulysses QKV: x_local [S_local, H] -> q|k|v of my heads over the full sequence
+    H = 5120 if big else 1024
+    S_local = (75600 // 8 // 128 * 128) if big else 512
+    xs = torch.randn(W, S_local, H, device="cuda", dtype=torch.bfloat16) * 0.5
+    w = (torch.randn(3 * H, H, device="cuda") * 0.03).to(torch.bfloat16)
+    b = torch.randn(3 * H, device="cuda", dtype=torch.bfloat16)
+    x = xs[rank].clone().requires_grad_()
+    wq = w.clone().requires_grad_()
+    proj = UlyssesQKVProjection(g, "cuda", S_local, 3 * H)
+    y = proj(x, wq, b)
+    # unfused reference: local GEMM, then all-to-all of head blocks
+    def unfused(xl, wl):
+        yl = native.gemm_nt(xl, wl, b)                                   # [S_local, 3H]
+        blk = H // W
+        send = yl.view(S_local, 3, W, blk).permute(2, 0, 1, 3).contiguous()    # [dst, S_local, 3, blk]
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=g)                      # [src, S_local, 3, blk]
+        return recv.reshape(W * S_local, 3 * blk)
+    ref = unfused(xs[rank], w)
+    err = (y.float() - ref.float()).abs().max().item()
+    if err > 1e-2:
+        ok = False
+        print(f"rank {rank} ulysses fwd err {err}")
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    # reference gradients through autograd of the unfused torch path
+    xr = xs[rank].clone().float().requires_grad_()
+    wr = w.clone().float().requires_grad_()
+    yl = torch.nn.functional.linear(xr, wr, b.float())
+    blk = H // W
+    send = yl.view(S_local, 3, W, blk).permute(2, 0, 1, 3).contiguous()
+    gsend = torch.empty_like(send)
+    dist.all_to_all_single(gsend, gy.float().view(W, S_local, 3, blk).contiguous(), group=g)
+    send.backward(gsend)
+    for name, a_, b_ in (("dx", x.grad, xr.grad), ("dw", wq.grad, wr.grad)):
+        e_ = (a_.float() - b_).abs().max().item() / (b_.abs().max().item() + 1e-6)
+        if e_ > 3e-2:
+            ok = False
+            print(f"rank {rank} ulysses {name} rel err {e_}")
+    t_f = timed(lambda: proj(xs[rank], w, b))
+    t_u = timed(lambda: unfused(xs[rank], w))
+    # ---------------- row-parallel linear + reduce-scatter
+    M, N, K = (8192, 8192, 29568 // 4 // 64 * 64) if big else (1024, 512, 768)
+    xa = torch.randn(M, K, device="cuda", dtype=torch.bfloat16) * 0.5
+    wa = (torch.randn(N, K, device="cuda") * 0.03).to(torch.bfloat16)
+    rs = RowParallelLinearRS(g, "cuda", M, N)
+    yo = rs(xa, wa)
+    part = native.gemm_nt(xa, wa).float()
+    refo = torch.empty(M // W, N, device="cuda")
+    dist.reduce_scatter_tensor(refo, part, group=g)
+    e2 = (yo.float() - refo).abs().max().item() / (refo.abs().max().item() + 1e-6)
+    if e2 > 2e-2:
+        ok = False
+        print(f"rank {rank} rs fwd rel err {e2}")
+    def unfused_rs():
+        p_ = native.gemm_nt(xa, wa)
+        o_ = torch.empty(M // W, N, device="cuda", dtype=torch.bfloat16)
+        dist.reduce_scatter_tensor(o_, p_, group=g)
+        return o_
+    t_rf = timed(lambda: rs(xa, wa))
+    t_ru = timed(unfused_rs)
+    native.check_status()
+    flag = torch.tensor([int(ok)], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(f"dist_fused_check world={W} ok={bool(flag.item())} ulysses_qkv fused {t_f:.3f} ms vs gemm+nccl_a2a {t_u:.3f} ms | "
+              f"rowparallel_rs fused {t_rf:.3f} ms vs gemm+nccl_rs {t_ru:.3f} ms (S_local={S_local}, H={H}; M={M},N={N},K={K})",
+              flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -56,3 +56,10 @@ def test_context_parallel_attention_gloo(world):
 
 def test_expert_parallel_gloo():
     assert "ok=True" in _run_script(2, "dist_moe_check.py")
+
+
+@pytest.mark.gpu
+def test_fused_gemm_collectives_2gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    assert "ok=True" in _run_script(2, "dist_fused_check.py")

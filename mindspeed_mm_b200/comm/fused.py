@@ -134,3 +134,122 @@ class RowParallelLinearRS:
 
     def __call__(self, x, w):
         return _RowParallelRSFn.apply(x.contiguous(), w, self)
+
+
+# ------------------------------------------------------------------------------------------ gather -> GEMM
+def _declare_gather():
+    L = native.lib()
+    p, i, ll, u = C.c_void_p, C.c_int, C.c_longlong, C.c_uint
+    L.mm_gemm_gather_bf16.argtypes = [p, p, p, p, i, i, i, ll, ll, ll, p, ll, i, i, i, i, i, i, p, u, p, p]
+    L.mm_gemm_gather_bf16.restype = i
+    return L
+
+
+class _GatherGemmBase:
+    def _launch(self, A, w, bias, out, src_ptrs, src_pitch, src_rows, src_cols, axis, extent):
+        L = _declare_gather()
+        self.epoch += 1
+        M, K = A.shape
+        rc = L.mm_gemm_gather_bf16(A.data_ptr(), w.data_ptr(), out.data_ptr(), None if bias is None else bias.data_ptr(),
+                                   M, w.shape[0], K, A.stride(0), w.stride(0), out.stride(0), src_ptrs, src_pitch, src_rows,
+                                   src_cols, axis, extent, self.world, self.rank, self.flags.data_ptr(), self.epoch,
+                                   native.status_word(A.device).data_ptr(), native._st())
+        native._check(rc, "gemm_gather")
+
+
+class _AllGatherLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, mod):
+        S_local, H = x.shape
+        mod.send.copy_(x)                                       # peers read my slab from here
+        mod.A[mod.rank * S_local:(mod.rank + 1) * S_local].copy_(x)
+        out = torch.empty(mod.A.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
+        mod.arena.barrier()                                     # every rank's send buffer is written
+        mod._launch(mod.A, w, bias, out, mod.send_ptrs, H, S_local, H, 0, S_local)
+        mod.arena.barrier()                                     # every rank is done reading my send buffer
+        ctx.save_for_backward(mod.A.clone(), w)
+        ctx.mod, ctx.has_bias = mod, bias is not None
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        A, w = ctx.saved_tensors
+        mod = ctx.mod
+        dA = native.gemm_nn(g.contiguous(), w)
+        dx = torch.empty(A.shape[0] // mod.world, A.shape[1], dtype=dA.dtype, device=dA.device)
+        dist.reduce_scatter_tensor(dx, dA, group=mod.group)
+        db = g.float().sum(0).to(g.dtype) if ctx.has_bias else None
+        return dx, native.gemm_tn(g.contiguous(), A), db, None
+
+
+class AllGatherLinear(_GatherGemmBase):
+    """Sequence-parallel all-gather fused into a column-parallel linear:
+    ``y = all_gather_rows(x_local) @ W_local^T (+ b)``, x_local [S/tp, H] (S/tp a multiple of 128) -> y [S, N/tp]."""
+
+    def __init__(self, group, device, S_local: int, H: int):
+        self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+        if S_local % 128:
+            raise ValueError("rows per rank must be a multiple of 128")
+        self.arena = SymmArena(S_local * H * 2 + 4096, group, torch.device(device))
+        off = self.arena.carve(S_local * H * 2)
+        self.send = self.arena.view(off, S_local * H, torch.bfloat16).view(S_local, H)
+        self.send_ptrs = self.arena.peer_ptrs(off)
+        self.A = torch.empty(S_local * self.world, H, dtype=torch.bfloat16, device=device)
+        self.flags = torch.zeros(8, dtype=torch.int32, device=device)
+        self.epoch = 0
+
+    def __call__(self, x, w, bias=None):
+        return _AllGatherLinearFn.apply(x.contiguous(), w, bias, self)
+
+
+class _UlyssesOutFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, o_heads, w, bias, mod):
+        S_full, cols = o_heads.shape
+        S_local = S_full // mod.world
+        mod.o_buf.copy_(o_heads)
+        mod.A[:, mod.rank * cols:(mod.rank + 1) * cols].copy_(o_heads[mod.rank * S_local:(mod.rank + 1) * S_local])
+        out = torch.empty(S_local, w.shape[0], dtype=o_heads.dtype, device=o_heads.device)
+        mod.arena.barrier()
+        mod._launch(mod.A, w, bias, out, mod.src_ptrs, cols, S_local, cols, 2, cols)
+        mod.arena.barrier()
+        ctx.save_for_backward(mod.A.clone(), w)
+        ctx.mod, ctx.has_bias = mod, bias is not None
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        A, w = ctx.saved_tensors
+        mod = ctx.mod
+        S_local, H = A.shape
+        cols = H // mod.world
+        dA = native.gemm_nn(g.contiguous(), w)                                  # [S_local, H]
+        send = dA.view(S_local, mod.world, cols).permute(1, 0, 2).contiguous()  # [dst head group, S_local, cols]
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=mod.group)                     # [src rows block, S_local, cols]
+        db = g.float().sum(0).to(g.dtype) if ctx.has_bias else None
+        return recv.reshape(mod.world * S_local, cols), native.gemm_tn(g.contiguous(), A), db, None
+
+
+class UlyssesOutProjection(_GatherGemmBase):
+    """Ulysses output projection with the head all-to-all fused into the GEMM's operand fetch:
+    o_heads [S_full, H/P] (this rank's heads, all tokens) -> y [S_local, N] = concat_heads(o)[my tokens] @ W^T (+ b)."""
+
+    def __init__(self, group, device, S_local: int, H: int):
+        self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+        cols = H // self.world
+        if cols % 64:
+            raise ValueError("per-rank head block must be a multiple of 64 columns")
+        S_full = S_local * self.world
+        self.arena = SymmArena(S_full * cols * 2 + 4096, group, torch.device(device))
+        off = self.arena.carve(S_full * cols * 2)
+        self.o_buf = self.arena.view(off, S_full * cols, torch.bfloat16).view(S_full, cols)
+        # every peer reads the rows of MY tokens out of ITS buffer: same offset on every peer
+        row_off = self.rank * S_local * cols * 2
+        self.src_ptrs = (C.c_void_p * self.world)(*[b + off + row_off for b in self.arena.peer_base])
+        self.A = torch.empty(S_local, H, dtype=torch.bfloat16, device=device)
+        self.flags = torch.zeros(8, dtype=torch.int32, device=device)
+        self.epoch = 0
+
+    def __call__(self, o_heads, w, bias=None):
+        return _UlyssesOutFn.apply(o_heads.contiguous(), w, bias, self)

@@ -7,7 +7,8 @@ import torch
 import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-from mindspeed_mm_b200.comm.fused import RowParallelLinearRS, UlyssesQKVProjection  # noqa: E402
+from mindspeed_mm_b200.comm.fused import (AllGatherLinear, RowParallelLinearRS, UlyssesOutProjection,  # noqa: E402
+                                           UlyssesQKVProjection)
 from mindspeed_mm_b200.ops import native  # noqa: E402
 
 
@@ -97,12 +98,53 @@ def main():
         return o_
     t_rf = timed(lambda: rs(xa, wa))
     t_ru = timed(unfused_rs)
+    # ---------------- sequence-parallel all-gather -> column-parallel GEMM
+    Sl, Hh, Nn = (1024, 8192, 29568 // 4 // 64 * 64 * 2) if big else (256, 512, 768)
+    xl = torch.randn(W, Sl, Hh, device="cuda", dtype=torch.bfloat16) * 0.5
+    wc = (torch.randn(Nn, Hh, device="cuda") * 0.03).to(torch.bfloat16)
+    agl = AllGatherLinear(g, "cuda", Sl, Hh)
+    for rep in range(2):                                  # second call exercises the epoch counters
+        ya = agl(xl[rank], wc)
+    refa = native.gemm_nt(xl.reshape(W * Sl, Hh), wc)
+    e3 = (ya.float() - refa.float()).abs().max().item() / (refa.float().abs().max().item() + 1e-6)
+    if e3 > 1e-2:
+        ok = False
+        print(f"rank {rank} allgather-linear rel err {e3}")
+    def unfused_ag():
+        full = torch.empty(W * Sl, Hh, device="cuda", dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(full, xl[rank], group=g)
+        return native.gemm_nt(full, wc)
+    t_af = timed(lambda: agl(xl[rank], wc))
+    t_au = timed(unfused_ag)
+    # ---------------- Ulysses output projection (heads come back from peers)
+    So, Ho = (S_local, H) if big else (256, 1024)
+    o_full = torch.randn(W * So, Ho, device="cuda", dtype=torch.bfloat16) * 0.5     # same on every rank (seeded)
+    wo = (torch.randn(Ho, Ho, device="cuda") * 0.03).to(torch.bfloat16)
+    cols = Ho // W
+    mine = o_full[:, rank * cols:(rank + 1) * cols].contiguous()                   # my heads, all tokens
+    uo = UlyssesOutProjection(g, "cuda", So, Ho)
+    for rep in range(2):
+        yu = uo(mine, wo)
+    refu = native.gemm_nt(o_full[rank * So:(rank + 1) * So].contiguous(), wo)
+    e4 = (yu.float() - refu.float()).abs().max().item() / (refu.float().abs().max().item() + 1e-6)
+    if e4 > 1e-2:
+        ok = False
+        print(f"rank {rank} ulysses-out rel err {e4}")
+    def unfused_uo():
+        send = mine.view(W, So, cols).contiguous()
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=g)
+        return native.gemm_nt(recv.permute(1, 0, 2).reshape(So, Ho), wo)
+    t_of = timed(lambda: uo(mine, wo))
+    t_ou = timed(unfused_uo)
     native.check_status()
     flag = torch.tensor([int(ok)], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
         print(f"dist_fused_check world={W} ok={bool(flag.item())} ulysses_qkv fused {t_f:.3f} ms vs gemm+nccl_a2a {t_u:.3f} ms | "
-              f"rowparallel_rs fused {t_rf:.3f} ms vs gemm+nccl_rs {t_ru:.3f} ms (S_local={S_local}, H={H}; M={M},N={N},K={K})",
+              f"rowparallel_rs fused {t_rf:.3f} ms vs gemm+nccl_rs {t_ru:.3f} ms | allgather_linear fused {t_af:.3f} ms vs "
+              f"nccl_ag+gemm {t_au:.3f} ms | ulysses_out fused {t_of:.3f} ms vs nccl_a2a+gemm {t_ou:.3f} ms "
+              f"(S_local={S_local}, H={H}; M={M},N={N},K={K})",
               flush=True)
     dist.barrier()
     dist.destroy_process_group()

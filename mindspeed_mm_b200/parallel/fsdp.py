@@ -351,6 +351,10 @@ class FSDPEngine:
         for g in u.groups:
             if not g.trainable:
                 continue
+            for _, prm in g.named_params:          # sequence-parallel replicas saw only a slice of the tokens
+                tpg = getattr(prm, "_tp_sum_group", None)
+                if tpg is not None and prm.grad is not None:
+                    dist.all_reduce(prm.grad, group=tpg)
             flat = g.flat_grads(self._p2p.grad_slot(g) if self._p2p is not None else None)
             if self.cuda:
                 self.comm_stream.wait_stream(torch.cuda.current_stream())
@@ -512,7 +516,9 @@ def _to_flat_params(module: nn.Module, device, dtype, exclude=()) -> dict:
             if p is None or id(p) in exclude:
                 continue
             if id(p) not in mapping:
-                mapping[id(p)] = nn.Parameter(torch.empty(0, dtype=dtype, device=device), requires_grad=p.requires_grad)
+                q = nn.Parameter(torch.empty(0, dtype=dtype, device=device), requires_grad=p.requires_grad)
+                q.__dict__.update(p.__dict__)            # keep tags such as _tp_sum_group
+                mapping[id(p)] = q
             m._parameters[n] = mapping[id(p)]
     return mapping
 

@@ -63,3 +63,7 @@ def test_fused_gemm_collectives_2gpu():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     assert "ok=True" in _run_script(2, "dist_fused_check.py")
+
+
+def test_tp_pp_backend_gloo():
+    assert "ok=True" in _run_script(4, "dist_mcore_check.py")

@@ -75,10 +75,7 @@ class FusedExperts(nn.Module):
         if ps.enabled("ep"):
             fn = epmod.ep_forward_allgather if self.c.ep_dispatcher == "allgather" else epmod.ep_forward_alltoall
             return fn(tokens, topk_ids, probs, self.gate_up_proj, self.down_proj, self.c.num_experts, ps.get_ep_group())
-        permuted, order = ops.moe_permute(tokens, topk_ids)
-        counts = torch.bincount(topk_ids.reshape(-1), minlength=self.c.num_experts).tolist()
-        y = epmod.experts_mlp(permuted, self.gate_up_proj, self.down_proj, counts)
-        return ops.moe_unpermute(y, order, probs)
+        return ops.moe_experts(tokens, topk_ids, probs, self.gate_up_proj, self.down_proj)
 
 
 class SparseMoeBlock(nn.Module):

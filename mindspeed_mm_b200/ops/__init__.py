@@ -225,6 +225,17 @@ class _GroupedGemmLoop(torch.autograd.Function):
         return dx, dw, None
 
 
+def moe_experts(tokens, topk_ids, probs, gate_up, down):
+    """Local routed experts (all experts of ``gate_up`` / ``down`` live on this rank)."""
+    if _native(tokens) and _nat().moe_supported(tokens, gate_up, down):
+        return _nat().moe_experts(tokens, topk_ids, probs, gate_up, down)
+    permuted, order = ref.moe_permute(tokens, topk_ids)
+    counts = torch.bincount(topk_ids.reshape(-1), minlength=gate_up.shape[0]).tolist()
+    h = grouped_gemm(permuted, gate_up, counts)
+    y = grouped_gemm(swiglu(h), down, counts)
+    return ref.moe_unpermute(y, order, probs)
+
+
 moe_permute = ref.moe_permute
 moe_unpermute = ref.moe_unpermute
 

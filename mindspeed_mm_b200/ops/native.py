@@ -51,6 +51,10 @@ def _declare(L):
         "mm_ce_fwd_bwd": [_p, _ll, _p, _p, _i, _i, _i, _p],
         "mm_fmha_max_tiles": [_i, _i],
         "mm_fmha_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _f, _p, _p],
+        "mm_grouped_gemm_max_tiles": [_i, _i, _i, _i, _i],
+        "mm_grouped_gemm_bf16": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p],
+        "mm_moe_permute": [_p, _p, _p, _i, _i, _p],
+        "mm_moe_unpermute": [_p, _p, _p, _p, _i, _i, _i, _p],
         "mm_p2p_flag_bytes": [],
         "mm_p2p_allgather": [_p, _p, _ll, _i, _i, _i, _p],
         "mm_p2p_rs_adamw": [_p, _p, _ll, _i, _i, _i, C.c_uint, _f, _p, _p, _p, _p, _ll, _f, _f, _f, _f, _f, _f, _f,
@@ -521,4 +525,117 @@ def linear_cross_entropy(h, w, labels, ignore_index=-100, chunk=8192):
 
 
 def grouped_gemm_supported(x, w) -> bool:
-    return False
+    return False      # the native MoE path works on the aligned layout: see moe_experts()
+
+
+# --------------------------------------------------------------------------- MoE on the aligned layout
+def moe_supported(tokens, gate_up, down) -> bool:
+    return (os.environ.get("MM_B200_MOE", "1") == "1" and tokens.dtype == torch.bfloat16 and tokens.shape[-1] % 128 == 0
+            and gate_up.shape[-1] % 256 == 0 and down.shape[-1] % 128 == 0)
+
+
+def aligned_routing(topk_ids, num_experts: int):
+    """Device-side plan of the aligned expert-major layout (no host sync): every expert's rows start at a
+    multiple of 128.  Returns (off [E+1] int32, row_of_pair [T*k] int32, src_of_row [R] int32 (-1 = pad), R)."""
+    T, k = topk_ids.shape
+    flat = topk_ids.reshape(-1)
+    order = torch.sort(flat, stable=True).indices
+    counts = torch.bincount(flat, minlength=num_experts)
+    padded = (counts + 127) // 128 * 128
+    off = torch.zeros(num_experts + 1, dtype=torch.int64, device=flat.device)
+    off[1:] = padded.cumsum(0)
+    ustart = torch.zeros(num_experts + 1, dtype=torch.int64, device=flat.device)
+    ustart[1:] = counts.cumsum(0)
+    sorted_e = flat[order]
+    rows = off[sorted_e] + (torch.arange(flat.numel(), device=flat.device) - ustart[sorted_e])
+    R = (T * k + num_experts * 127 + 127) // 128 * 128            # static upper bound of off[E]
+    row_of_pair = torch.empty(T * k, dtype=torch.int32, device=flat.device)
+    row_of_pair[order] = rows.to(torch.int32)
+    src_of_row = torch.full((R,), -1, dtype=torch.int32, device=flat.device)
+    src_of_row[rows] = (order // k).to(torch.int32)
+    return off.to(torch.int32), row_of_pair, src_of_row, R
+
+
+class _AlignedPermute(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tokens, src_of_row, row_of_pair, k):
+        R, H = src_of_row.numel(), tokens.shape[1]
+        out = torch.empty(R, H, dtype=tokens.dtype, device=tokens.device)
+        _check(lib().mm_moe_permute(tokens.contiguous().data_ptr(), src_of_row.data_ptr(), out.data_ptr(), R, H, _st()),
+               "moe_permute")
+        ctx.save_for_backward(row_of_pair)
+        ctx.k, ctx.T = k, tokens.shape[0]
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (row_of_pair,) = ctx.saved_tensors
+        ones = torch.ones(ctx.T * ctx.k, dtype=g.dtype, device=g.device)
+        out = torch.empty(ctx.T, g.shape[1], dtype=g.dtype, device=g.device)
+        _check(lib().mm_moe_unpermute(g.contiguous().data_ptr(), row_of_pair.data_ptr(), ones.data_ptr(), out.data_ptr(),
+                                      ctx.T, ctx.k, g.shape[1], _st()), "moe_unpermute")
+        return out, None, None, None
+
+
+class _AlignedUnpermute(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, row_of_pair, probs):
+        T, k = probs.shape
+        out = torch.empty(T, y.shape[1], dtype=y.dtype, device=y.device)
+        pc = probs.to(y.dtype).contiguous()
+        _check(lib().mm_moe_unpermute(y.contiguous().data_ptr(), row_of_pair.data_ptr(), pc.data_ptr(), out.data_ptr(), T, k,
+                                      y.shape[1], _st()), "moe_unpermute")
+        ctx.save_for_backward(y, row_of_pair, pc)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        y, row_of_pair, probs = ctx.saved_tensors
+        T, k = probs.shape
+        idx = row_of_pair.long()
+        ge = g.repeat_interleave(k, dim=0)                              # [T*k, H]
+        dy = torch.zeros_like(y)
+        dy[idx] = ge * probs.reshape(-1, 1)
+        dprobs = (ge.float() * y[idx].float()).sum(-1).view(T, k).to(probs.dtype)
+        return dy, None, dprobs
+
+
+def _grouped_raw(a, b, c, off, mode, K, N, E):
+    R = a.shape[0]
+    plan = torch.empty(3 * lib().mm_grouped_gemm_max_tiles(R, E, K, N, mode) + 1, dtype=torch.int32, device=a.device)
+    _check(lib().mm_grouped_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), off.data_ptr(), plan.data_ptr(), R, E, K, N,
+                                      mode, status_word(a.device).data_ptr(), _st()), "grouped_gemm")
+
+
+class _AlignedGroupedGemm(torch.autograd.Function):
+    """x [R, K] (aligned expert-major rows) x W [E, K, N] -> [R, N]; all three passes on tcgen05."""
+
+    @staticmethod
+    def forward(ctx, x, w, off):
+        E, K, N = w.shape
+        x = x.contiguous()
+        y = torch.empty(x.shape[0], N, dtype=x.dtype, device=x.device)
+        _grouped_raw(x, w, y, off, 0, K, N, E)
+        ctx.save_for_backward(x, w, off)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w, off = ctx.saved_tensors
+        E, K, N = w.shape
+        g = g.contiguous()
+        dx = torch.empty_like(x)
+        _grouped_raw(g, w, dx, off, 1, K, N, E)
+        dw = torch.zeros_like(w)
+        _grouped_raw(x, g, dw, off, 2, K, N, E)
+        return dx, dw, None
+
+
+def moe_experts(tokens, topk_ids, probs, gate_up, down):
+    """Routed SwiGLU experts: permute -> grouped GEMM -> SwiGLU -> grouped GEMM -> weighted un-permute."""
+    E = gate_up.shape[0]
+    off, row_of_pair, src_of_row, R = aligned_routing(topk_ids, E)
+    x = _AlignedPermute.apply(tokens, src_of_row, row_of_pair, topk_ids.shape[1])
+    h = _AlignedGroupedGemm.apply(x, gate_up, off)
+    y = _AlignedGroupedGemm.apply(swiglu(h), down, off)
+    return _AlignedUnpermute.apply(y, row_of_pair, probs)

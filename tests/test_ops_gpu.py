@@ -226,3 +226,30 @@ def test_fmha_forward_and_grad(lens, nq, nkv, causal):
     _close(qg.grad, qr.grad, rtol=3e-2, atol=3e-2)
     _close(kg.grad, kr.grad, rtol=3e-2, atol=3e-2)
     _close(vg.grad, vr.grad, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("T,k,E,H,F", [(512, 2, 8, 256, 128), (4096, 8, 128, 2048, 768), (300, 4, 16, 512, 256)])
+def test_moe_experts_native_vs_reference(T, k, E, H, F):
+    torch.manual_seed(0)
+    x = (torch.randn(T, H, device=DEV) * 0.5).to(torch.bfloat16).requires_grad_()
+    gu = (torch.randn(E, H, 2 * F, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_()
+    dn = (torch.randn(E, F, H, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_()
+    logits = torch.randn(T, E, device=DEV)
+    if E >= 16:
+        logits[:, 0] += 2.0              # skewed routing: one hot expert, some experts may stay empty
+        logits[:, E - 1] -= 30.0
+    p, ids = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+    p = (p / p.sum(-1, keepdim=True)).to(torch.bfloat16).requires_grad_()
+    y = ops.moe_experts(x, ids, p, gu, dn)
+    g = torch.randn_like(y)
+    y.backward(g)
+    ops.set_tier("library")
+    xr, gur, dnr, pr = (t.detach().float().requires_grad_() for t in (x, gu, dn, p))
+    yr = ops.moe_experts(xr, ids, pr, gur, dnr)
+    yr.backward(g.float())
+    ops.set_tier("native")
+    _close(y, yr, rtol=3e-2, atol=3e-2)
+    _close(x.grad, xr.grad, rtol=4e-2, atol=4e-2)
+    _close(gu.grad, gur.grad, rtol=4e-2, atol=4e-2)
+    _close(dn.grad, dnr.grad, rtol=4e-2, atol=4e-2)
+    _close(p.grad, pr.grad, rtol=4e-2, atol=4e-2)

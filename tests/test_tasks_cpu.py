@@ -1,0 +1,98 @@
+import math
+
+import torch
+
+from mindspeed_mm_b200.api import stable_init_fn
+from mindspeed_mm_b200.models.qwen2_5_vl import Qwen25VLConfig, Qwen25VLModel
+from mindspeed_mm_b200.models.wan import WanConfig, WanDiT
+from mindspeed_mm_b200.parallel.fsdp import FSDPEngine, OptimConfig
+from mindspeed_mm_b200.tasks import evaluation as ev
+from mindspeed_mm_b200.tasks import preference as pref
+from mindspeed_mm_b200.tasks.inference import VLMGenerator, WanPipeline
+from mindspeed_mm_b200.tasks.lora import apply_lora, lora_state_dict, merge_lora
+
+
+class _L:
+    rank, alpha, dropout = 4, 8, 0.0
+    target_modules = ["q_proj", "o_proj", "visual.blocks.{*}.attn_proj"]
+
+
+def _tiny():
+    cfg = Qwen25VLConfig.tiny()
+    cfg.text.num_layers = 1
+    cfg.vision.depth = 1
+    cfg.vision.fullatt_block_indexes = (0,)
+    return cfg
+
+
+def test_lora_trains_only_adapters_and_merges():
+    from bench import make_batches
+    cfg = _tiny()
+    with torch.device("meta"):
+        model = Qwen25VLModel(cfg)
+    wrapped = apply_lora(model, _L)
+    assert "layers.0.qkv_proj" in wrapped and "layers.0.o_proj" in wrapped and "visual.blocks.0.attn_proj" in wrapped
+    eng = FSDPEngine(model.fsdp_units(), group=False, device="cpu", param_dtype=torch.float32, opt=OptimConfig(lr=1e-2))
+    eng.materialize(stable_init_fn(0.02, 0))
+    before = {n: t.clone() for n, t in eng.named_full_params()}
+    batch = make_batches(cfg, 1, 300, 1, 1, 224, 0, pin=False)[0]
+    for _ in range(2):
+        eng.set_lr(1e-2)
+        ls, n = model(batch, run=eng.run)
+        (ls / n).backward()
+        eng.end_micro_step()
+        eng.finish_step()
+    after = dict(eng.named_full_params())
+    changed = {n for n in before if not torch.equal(before[n], after[n])}
+    assert changed and all("lora_" in n for n in changed), changed
+    sd = lora_state_dict(eng.named_full_params())
+    assert set(sd) == {n for n in before if "lora_" in n}
+    merged = merge_lora({n: t.clone() for n, t in eng.named_full_params()}, _L.alpha / _L.rank)
+    assert "layers.0.qkv_proj.weight" in merged and not any("lora" in k or ".base." in k for k in merged)
+    w0, a, b = after["layers.0.o_proj.base.weight"], after["layers.0.o_proj.lora_A"], after["layers.0.o_proj.lora_B"]
+    assert torch.allclose(merged["layers.0.o_proj.weight"], w0 + 2.0 * b @ a, atol=1e-6)
+
+
+def test_vlm_generate_and_wan_pipeline():
+    cfg = _tiny()
+    with torch.device("meta"):
+        model = Qwen25VLModel(cfg)
+    eng = FSDPEngine(model.fsdp_units(), group=False, device="cpu", param_dtype=torch.float32)
+    eng.materialize(stable_init_fn(0.02, 0))
+    gen = VLMGenerator(model, run=eng.run)
+    out = gen.generate(torch.randint(0, 1000, (12,)), max_new_tokens=3)
+    assert out.shape == (15,)
+    wc = WanConfig.tiny()
+    with torch.device("meta"):
+        dit = WanDiT(wc)
+    e2 = FSDPEngine(dit.fsdp_units(), group=False, device="cpu", param_dtype=torch.float32, no_recompute=())
+    e2.materialize(stable_init_fn(0.02, 0))
+    pipe = WanPipeline(dit, run=e2.run)
+    pipe.scheduler.set_timesteps(3)
+    vid = pipe(torch.randn(1, 16, 64), torch.zeros(1, 16, 64), frames=2, height=4, width=4)
+    assert vid.shape == (1, 16, 2, 4, 4) and torch.isfinite(vid).all()
+
+
+def test_preference_losses():
+    pc, pr, rc, rr = torch.tensor([-1.0]), torch.tensor([-3.0]), torch.tensor([-2.0]), torch.tensor([-2.0])
+    loss, cr, rj = pref.dpo_loss(pc, pr, rc, rr, beta=0.5)
+    assert abs(float(loss) - (-math.log(1 / (1 + math.exp(-1.0))))) < 1e-6 and float(cr) == 0.5 and float(rj) == -0.5
+    assert float(pref.dpo_loss(pc, pr, rc, rr, beta=0.5, loss_type="hinge")[0]) == 0.0
+    adv = pref.grpo_advantages(torch.tensor([1.0, 2.0, 3.0, 10.0, 10.0, 13.0]), 3)
+    assert abs(float(adv[:3].mean())) < 1e-6 and abs(float(adv[3:].mean())) < 1e-6
+    l0 = pref.grpo_loss(torch.zeros(4), torch.zeros(4), torch.tensor([1.0, -1.0, 2.0, -2.0]))
+    assert abs(float(l0)) < 1e-6                       # ratio 1: objective = -mean(adv) = 0
+    lp = pref.sde_step_logprob(torch.zeros(2, 4), torch.zeros(2, 4), torch.zeros(2, 4), 0.8, 0.7)
+    assert lp.shape == (2,) and torch.isfinite(lp).all()
+    assert float(pref.bradley_terry_loss(torch.tensor([2.0]), torch.tensor([0.0]))) < math.log(2)
+    lp_tok = torch.log(torch.tensor([0.5, 0.5, 0.25, 0.25, 0.25]))
+    s = pref.sequence_logprobs(lp_tok, torch.tensor([1, -100, 1, 1, 1]), torch.tensor([0, 2, 5]))
+    assert torch.allclose(s, torch.tensor([math.log(0.5), 3 * math.log(0.25)]))
+
+
+def test_eval_metrics():
+    assert ev.multiple_choice_match("The answer is (B).", "b") and not ev.multiple_choice_match("C", "B")
+    assert ev.relaxed_accuracy("10.2", "10") and not ev.relaxed_accuracy("12", "10")
+    assert ev.anls("hello wrld", ["hello world"]) > 0.8 and ev.anls("zzz", ["hello"]) == 0.0
+    r = ev.evaluate(lambda s: s["guess"], [{"guess": "A", "answer": "A"}, {"guess": "B", "answer": "C"}], "multiple_choice")
+    assert r == {"accuracy": 0.5, "n": 2}

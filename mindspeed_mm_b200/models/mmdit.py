@@ -1,0 +1,238 @@
+"""Dual-stream / single-stream MMDiT family: HunyuanVideo and FLUX.
+
+Both are "double blocks" (image and text tokens keep separate modulation, QKV and MLP weights but attend
+jointly) followed by "single blocks" (one stream over the concatenation, attention and MLP computed in
+parallel from one fused projection), adaLN-zero modulation from a pooled conditioning vector, QK-RMSNorm per
+head and RoPE on the image tokens only (3-D (t, h, w) split for video, 2-D for FLUX).
+HunyuanVideo: 20 double + 40 single blocks, 24 heads x 128, rope dims (16, 56, 56)
+(mindspeed_mm/models/predictor/dits/hunyuan_video_dit.py:104-200,645,1090,1394-1560).  FLUX.1: 19 double + 38
+single, 24 heads x 128, rope dims (16, 56, 56) over (id, h, w) (examples/diffusers/flux; trained natively here
+instead of through diffusers scripts).  Under Ulysses only the image tokens are sequence-sharded; text tokens
+are replicated and their heads are split, as the reference does for HunyuanVideo.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from .qwen2_5_vl import Linear, RMSNorm
+from .registry import model_register
+from .wan import sinusoidal_embedding
+
+
+@dataclass
+class MMDiTConfig:
+    in_channels: int = 16
+    out_channels: int = 16
+    patch_size: Sequence[int] = (1, 2, 2)
+    hidden_size: int = 3072
+    num_heads: int = 24
+    mlp_ratio: float = 4.0
+    num_double_blocks: int = 20
+    num_single_blocks: int = 40
+    text_dim: int = 4096
+    pooled_dim: int = 768
+    rope_dims: Sequence[int] = (16, 56, 56)
+    rope_theta: float = 256.0
+    guidance_embed: bool = True
+    eps: float = 1e-6
+    init_std: float = 0.02
+
+    @staticmethod
+    def hunyuan_video():
+        return MMDiTConfig()
+
+    @staticmethod
+    def flux_dev():
+        return MMDiTConfig(in_channels=64, out_channels=64, patch_size=(1, 1, 1), num_double_blocks=19, num_single_blocks=38,
+                           rope_theta=10000.0)
+
+    @staticmethod
+    def tiny():
+        return MMDiTConfig(in_channels=4, out_channels=4, hidden_size=64, num_heads=4, num_double_blocks=1,
+                           num_single_blocks=2, text_dim=32, pooled_dim=16, rope_dims=(4, 6, 6))
+
+
+def rope_nd(grid: Tuple[int, int, int], dims: Sequence[int], theta: float, device=None):
+    """cos/sin [prod(grid), sum(dims)/2] for interleaved-pair rotation; axis a uses dims[a] channels."""
+    outs = []
+    sizes = list(grid)
+    for a, (n, d) in enumerate(zip(sizes, dims)):
+        inv = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float64, device=device) / d))
+        ang = torch.outer(torch.arange(n, dtype=torch.float64, device=device), inv)
+        shape = [1, 1, 1, d // 2]
+        shape[a] = n
+        outs.append(ang.view(shape).expand(*sizes, d // 2))
+    ang = torch.cat(outs, -1).reshape(-1, sum(dims) // 2)
+    return ang.cos().float(), ang.sin().float()
+
+
+class Modulation(nn.Module):
+    def __init__(self, dim, n):
+        super().__init__()
+        self.n = n
+        self.lin = Linear(dim, n * dim)
+
+    def forward(self, vec):                       # vec [B, H] -> n x [B, 1, H]
+        return self.lin(F.silu(vec)).unsqueeze(1).chunk(self.n, dim=-1)
+
+
+class StreamParams(nn.Module):
+    """Per-stream weights of a double block."""
+
+    def __init__(self, c: MMDiTConfig):
+        super().__init__()
+        H, nh = c.hidden_size, c.num_heads
+        self.mod = Modulation(H, 6)
+        self.qkv = Linear(H, 3 * H)
+        self.q_norm, self.k_norm = RMSNorm(H // nh, c.eps), RMSNorm(H // nh, c.eps)
+        self.proj = Linear(H, H)
+        self.mlp_0 = Linear(H, int(H * c.mlp_ratio))
+        self.mlp_2 = Linear(int(H * c.mlp_ratio), H)
+
+
+def _heads(x, nh):
+    B, S, H = x.shape
+    return x.view(B, S, nh, H // nh)
+
+
+def _rope(x, cos, sin):
+    B, S, N, D = x.shape
+    return ops.rope_interleaved(x.reshape(B * S, N, D), cos.repeat(B, 1), sin.repeat(B, 1)).view(B, S, N, D)
+
+
+class DoubleBlock(nn.Module):
+    def __init__(self, c: MMDiTConfig):
+        super().__init__()
+        self.c = c
+        self.img, self.txt = StreamParams(c), StreamParams(c)
+
+    def forward(self, img, txt, vec, cos, sin):
+        c, nh = self.c, self.c.num_heads
+        im, tm = self.img.mod(vec), self.txt.mod(vec)
+        qkvs = []
+        for x, sp, m in ((img, self.img, im), (txt, self.txt, tm)):
+            h = ops.layer_norm_modulate(x, m[1], m[0], c.eps)
+            q, k, v = sp.qkv(h).chunk(3, dim=-1)
+            qkvs.append((sp.q_norm(_heads(q, nh)), sp.k_norm(_heads(k, nh)), _heads(v, nh)))
+        (qi, ki, vi), (qt, kt, vt) = qkvs
+        qi, ki = _rope(qi, cos, sin), _rope(ki, cos, sin)
+        q, k, v = torch.cat([qi, qt], 1), torch.cat([ki, kt], 1), torch.cat([vi, vt], 1)
+        o = ops.attention_dense(q, k, v)
+        S_img = img.shape[1]
+        oi, ot = o[:, :S_img].flatten(2), o[:, S_img:].flatten(2)
+        outs = []
+        for x, o_, sp, m in ((img, oi, self.img, im), (txt, ot, self.txt, tm)):
+            x = ops.gated_residual(x, sp.proj(o_), m[2])
+            y = sp.mlp_2(ops.gelu_tanh(sp.mlp_0(ops.layer_norm_modulate(x, m[4], m[3], c.eps))))
+            outs.append(ops.gated_residual(x, y, m[5]))
+        return outs[0], outs[1]
+
+
+class SingleBlock(nn.Module):
+    def __init__(self, c: MMDiTConfig):
+        super().__init__()
+        self.c = c
+        H, nh = c.hidden_size, c.num_heads
+        self.mlp_dim = int(H * c.mlp_ratio)
+        self.mod = Modulation(H, 3)
+        self.linear1 = Linear(H, 3 * H + self.mlp_dim)
+        self.linear2 = Linear(H + self.mlp_dim, H)
+        self.q_norm, self.k_norm = RMSNorm(H // nh, c.eps), RMSNorm(H // nh, c.eps)
+
+    def forward(self, x, vec, cos, sin, s_img: int):
+        c, nh = self.c, self.c.num_heads
+        m = self.mod(vec)
+        h = ops.layer_norm_modulate(x, m[1], m[0], c.eps)
+        qkv, mlp = self.linear1(h).split([3 * c.hidden_size, self.mlp_dim], dim=-1)
+        q, k, v = qkv.chunk(3, dim=-1)
+        q, k, v = self.q_norm(_heads(q, nh)), self.k_norm(_heads(k, nh)), _heads(v, nh)
+        q = torch.cat([_rope(q[:, :s_img], cos, sin), q[:, s_img:]], 1)
+        k = torch.cat([_rope(k[:, :s_img], cos, sin), k[:, s_img:]], 1)
+        o = ops.attention_dense(q, k, v).flatten(2)
+        y = self.linear2(torch.cat([o, ops.gelu_tanh(mlp)], dim=-1))
+        return ops.gated_residual(x, y, m[2])
+
+
+class MMDiTEmbed(nn.Module):
+    def __init__(self, c: MMDiTConfig):
+        super().__init__()
+        self.c = c
+        p = c.patch_size
+        self.img_in = Linear(c.in_channels * p[0] * p[1] * p[2], c.hidden_size)
+        self.txt_in = Linear(c.text_dim, c.hidden_size)
+        self.time_in_0, self.time_in_2 = Linear(256, c.hidden_size), Linear(c.hidden_size, c.hidden_size)
+        self.vector_in_0, self.vector_in_2 = Linear(c.pooled_dim, c.hidden_size), Linear(c.hidden_size, c.hidden_size)
+        if c.guidance_embed:
+            self.guidance_in_0, self.guidance_in_2 = Linear(256, c.hidden_size), Linear(c.hidden_size, c.hidden_size)
+
+    def forward(self, tokens, txt, t, pooled, guidance=None):
+        dt = self.img_in.weight.dtype
+        vec = self.time_in_2(F.silu(self.time_in_0(sinusoidal_embedding(t, 256).to(dt))))
+        vec = vec + self.vector_in_2(F.silu(self.vector_in_0(pooled.to(dt))))
+        if self.c.guidance_embed and guidance is not None:
+            vec = vec + self.guidance_in_2(F.silu(self.guidance_in_0(sinusoidal_embedding(guidance, 256).to(dt))))
+        return self.img_in(tokens.to(dt)), self.txt_in(txt.to(dt)), vec
+
+
+class MMDiTFinal(nn.Module):
+    def __init__(self, c: MMDiTConfig):
+        super().__init__()
+        self.c = c
+        p = c.patch_size
+        self.mod = Modulation(c.hidden_size, 2)
+        self.linear = Linear(c.hidden_size, c.out_channels * p[0] * p[1] * p[2])
+
+    def forward(self, x, vec):
+        m = self.mod(vec)
+        return self.linear(ops.layer_norm_modulate(x, m[1], m[0], self.c.eps))
+
+
+class MMDiT(nn.Module):
+    """``forward(latents [B,C,F,H,W], t [B], txt [B,L,text_dim], pooled [B,pooled_dim], guidance=None) -> velocity``."""
+
+    def __init__(self, config: MMDiTConfig):
+        super().__init__()
+        self.config = config
+        self.embed = MMDiTEmbed(config)
+        self.double_blocks = nn.ModuleList([DoubleBlock(config) for _ in range(config.num_double_blocks)])
+        self.single_blocks = nn.ModuleList([SingleBlock(config) for _ in range(config.num_single_blocks)])
+        self.final = MMDiTFinal(config)
+
+    def fsdp_units(self):
+        return [("embed", self.embed)] + [(f"double_blocks.{i}", b) for i, b in enumerate(self.double_blocks)] + \
+               [(f"single_blocks.{i}", b) for i, b in enumerate(self.single_blocks)] + [("final", self.final)]
+
+    def forward(self, latents, t, txt, pooled, guidance=None, run=None):
+        run = run or (lambda m, *a, **k: m(*a, **k))
+        c = self.config
+        B, C, Fr, Hh, Ww = latents.shape
+        pf, ph, pw = c.patch_size
+        grid = (Fr // pf, Hh // ph, Ww // pw)
+        x = latents.view(B, C, grid[0], pf, grid[1], ph, grid[2], pw).permute(0, 2, 4, 6, 1, 3, 5, 7).reshape(B, -1, C * pf * ph * pw)
+        img, text, vec = run(self.embed, x, txt, t, pooled, guidance)
+        cos, sin = rope_nd(grid, c.rope_dims, c.rope_theta, device=latents.device)
+        for blk in self.double_blocks:
+            img, text = run(blk, img, text, vec, cos, sin)
+        s_img = img.shape[1]
+        h = torch.cat([img, text], 1)
+        for blk in self.single_blocks:
+            h = run(blk, h, vec, cos, sin, s_img)
+        y = run(self.final, h[:, :s_img], vec)
+        y = y.view(B, grid[0], grid[1], grid[2], c.out_channels, pf, ph, pw).permute(0, 4, 1, 5, 2, 6, 3, 7)
+        return y.reshape(B, c.out_channels, Fr, Hh, Ww)
+
+
+@model_register.register("hunyuanvideodit")
+class HunyuanVideoDiT(MMDiT):
+    pass
+
+
+@model_register.register("flux")
+class FluxDiT(MMDiT):
+    pass

@@ -248,6 +248,19 @@ def gated_delta_rule(q, k, v, g, beta, scale=None, chunk: int = 64, initial_stat
     return ref.gated_delta_rule_chunked(q, k, v, g, beta, scale, chunk, initial_state)
 
 
+def gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk: int = 64, scale=None):
+    """Packed gated delta rule.  q, k: [T, H, K]; v: [T, H, V]; g, beta: [T, H]; the state restarts at every
+    ``cu_seqlens`` boundary.  Returns [T, H, V] (fp32)."""
+    if _native(q) and _nat().gdn_supported(q, v, chunk):
+        return _nat().gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk, scale)
+    outs = []
+    cu = [int(c) for c in cu_seqlens]
+    for a, b in zip(cu[:-1], cu[1:]):
+        o, _ = ref.gated_delta_rule_chunked(q[None, a:b], k[None, a:b], v[None, a:b], g[None, a:b], beta[None, a:b], scale, chunk)
+        outs.append(o[0])
+    return torch.cat(outs, 0)
+
+
 def status() -> dict:
     """Which ops have a native sm_100a implementation loaded (for logs and DESIGN tables)."""
     try:

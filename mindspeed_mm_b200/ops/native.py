@@ -639,3 +639,8 @@ def moe_experts(tokens, topk_ids, probs, gate_up, down):
     h = _AlignedGroupedGemm.apply(x, gate_up, off)
     y = _AlignedGroupedGemm.apply(swiglu(h), down, off)
     return _AlignedUnpermute.apply(y, row_of_pair, probs)
+
+
+# --------------------------------------------------------------------------- GDN
+def gdn_supported(q, v, chunk) -> bool:
+    return False

@@ -304,9 +304,12 @@ def gated_delta_rule_chunked(q, k, v, g, beta, scale=None, chunk: int = 64, init
     vb = v * beta.unsqueeze(-1)
     A = -(kb @ k.transpose(-1, -2) * decay).tril(-1)
     # (I - A)^-1 via row-wise forward substitution
+    rows = [A[..., 0, :]]                         # built out of place so that autograd can differentiate it
     for i in range(1, chunk):
-        A[..., i, :i] = A[..., i, :i] + (A[..., i, :i].unsqueeze(-1) * A[..., :i, :i]).sum(-2)
-    Tm = A + torch.eye(chunk, device=q.device)
+        a = A[..., i, :i]
+        prev = torch.stack(rows, dim=-2)[..., :i]
+        rows.append(F.pad(a + (a.unsqueeze(-1) * prev).sum(-2), (0, chunk - i)))
+    Tm = torch.stack(rows, dim=-2) + torch.eye(chunk, device=q.device)
     u = Tm @ vb
     w = Tm @ (kb * gc.exp().unsqueeze(-1))
     S = torch.zeros(B, H, K, V, device=q.device) if initial_state is None else initial_state.float().clone()

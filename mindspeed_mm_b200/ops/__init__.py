@@ -91,8 +91,17 @@ def rope_interleaved(x, cos, sin):
     return ref.rope_interleaved(x, cos, sin)
 
 
-l2_norm = ref.l2_norm
-gated_rms_norm = ref.gated_rms_norm
+def l2_norm(x, eps: float = 1e-6):
+    if _native(x) and x.dtype == torch.bfloat16 and x.shape[-1] <= 256:
+        return _nat().l2_norm(x, eps)
+    return ref.l2_norm(x, eps)
+
+
+def gated_rms_norm(x, z, weight, eps: float = 1e-6):
+    if (_native(x) and x.dtype == torch.float32 and z.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and x.shape[-1] <= 256 and not torch.is_grad_enabled()):
+        return _nat().gated_rms_norm_fwd(x, z, weight, eps)
+    return ref.gated_rms_norm(x, z, weight, eps)
 
 
 # --------------------------------------------------------------------------- GEMM
@@ -241,6 +250,8 @@ moe_unpermute = ref.moe_unpermute
 
 # --------------------------------------------------------------------------- GDN
 def causal_conv1d(x, weight, bias=None, activation="silu", cu_seqlens=None):
+    if _native(x) and bias is None and _nat().conv1d_supported(x, weight):
+        return _nat().causal_conv1d(x, weight, activation, cu_seqlens)
     return ref.causal_conv1d(x, weight, bias, activation, cu_seqlens)
 
 

@@ -1,0 +1,215 @@
+// Auxiliary kernels of the gated-delta-net layer on packed sequences:
+//   causal_conv1d (depthwise, kernel <= 8, optional SiLU, restarts at every sequence boundary) forward and backward,
+//   l2norm over the head dim (forward and backward), gated RMSNorm  y = rmsnorm(x) * w * silu(z)  (forward).
+// x is [T, D] bf16 with the channel dim contiguous: a thread owns 8 channels (16 bytes) and walks a strip of
+// tokens keeping the last K-1 inputs in registers, so every input is read once.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kMaxK = 8;
+constexpr int kStrip = 32;   // tokens per thread strip
+
+// seq_start[t] = first token index of the sequence token t belongs to (int32, precomputed from cu_seqlens)
+template <bool SILU>
+__global__ void conv1d_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const int* __restrict__ seq_start,
+                                  bf16* __restrict__ y, int T, int D, int K) {
+    const int dv = D >> 3;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= dv) return;
+    const int t0 = blockIdx.y * kStrip, t1 = min(T, t0 + kStrip);
+    float wk[kMaxK][8];
+    for (int k = 0; k < K; ++k)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) wk[k][j] = __bfloat162float(w[(size_t)(c * 8 + j) * K + k]);
+    float hist[kMaxK][8];     // hist[i] = x[t - (K-1) + i]; hist[K-1] is the current token
+    for (int i = 0; i < K - 1; ++i) {
+        const int t = t0 - (K - 1) + i;
+        if (t >= 0 && t >= seq_start[t0]) unpack8(reinterpret_cast<const Vec8*>(x + (size_t)t * D)[c], hist[i]);
+        else
+#pragma unroll
+            for (int j = 0; j < 8; ++j) hist[i][j] = 0.f;
+    }
+    for (int t = t0; t < t1; ++t) {
+        if (seq_start[t] == t)      // a new sequence starts here: forget the history
+            for (int i = 0; i < K - 1; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) hist[i][j] = 0.f;
+        unpack8(reinterpret_cast<const Vec8*>(x + (size_t)t * D)[c], hist[K - 1]);
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int k = 0; k < K; ++k)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += wk[k][j] * hist[k][j];
+        if (SILU)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = acc[j] / (1.f + __expf(-acc[j]));
+        reinterpret_cast<Vec8*>(y + (size_t)t * D)[c] = pack8(acc);
+        for (int i = 0; i < K - 1; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) hist[i][j] = hist[i + 1][j];
+    }
+}
+
+// dx[t] = sum_k w[k] * dpre[t + (K-1-k)] (same sequence only); dw partial per strip -> atomics in fp32.
+template <bool SILU>
+__global__ void conv1d_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const int* __restrict__ seq_start,
+                                  const int* __restrict__ seq_end, const bf16* __restrict__ dy, bf16* __restrict__ dx,
+                                  float* __restrict__ dw, int T, int D, int K) {
+    const int dv = D >> 3;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= dv) return;
+    const int t0 = blockIdx.y * kStrip, t1 = min(T, t0 + kStrip);
+    float wk[kMaxK][8], dwacc[kMaxK][8];
+    for (int k = 0; k < K; ++k)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            wk[k][j] = __bfloat162float(w[(size_t)(c * 8 + j) * K + k]);
+            dwacc[k][j] = 0.f;
+        }
+    // gradient of the pre-activation at token t (recomputes the forward conv when SiLU is fused)
+    auto dpre = [&](int t, float* out) {
+        float g[8];
+        unpack8(reinterpret_cast<const Vec8*>(dy + (size_t)t * D)[c], g);
+        if (SILU) {
+            float pre[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) pre[j] = 0.f;
+            for (int k = 0; k < K; ++k) {
+                const int s = t - (K - 1) + k;
+                if (s >= seq_start[t]) {
+                    float xv[8];
+                    unpack8(reinterpret_cast<const Vec8*>(x + (size_t)s * D)[c], xv);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) pre[j] += wk[k][j] * xv[j];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float sg = 1.f / (1.f + __expf(-pre[j]));
+                out[j] = g[j] * sg * (1.f + pre[j] * (1.f - sg));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) out[j] = g[j];
+        }
+    };
+    for (int t = t0; t < t1; ++t) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        float xv[8];
+        unpack8(reinterpret_cast<const Vec8*>(x + (size_t)t * D)[c], xv);
+        for (int k = 0; k < K; ++k) {
+            const int u = t + (K - 1 - k);       // output token that used x[t] with tap k
+            if (u < seq_end[t]) {
+                float d[8];
+                dpre(u, d);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    acc[j] += wk[k][j] * d[j];
+                    dwacc[k][j] += d[j] * xv[j];
+                }
+            }
+        }
+        reinterpret_cast<Vec8*>(dx + (size_t)t * D)[c] = pack8(acc);
+    }
+    for (int k = 0; k < K; ++k)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) atomicAdd(&dw[(size_t)(c * 8 + j) * K + k], dwacc[k][j]);
+}
+
+// ---- l2norm over the last dim (D <= 256, one warp per row)
+__global__ void l2norm_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, float* __restrict__ rnorm, long long rows,
+                                  int D, float eps) {
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    float v[8];
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) {
+        v[i >> 5] = __bfloat162float(x[row * D + i]);
+        ss += v[i >> 5] * v[i >> 5];
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss + eps);
+    if (lane == 0 && rnorm) rnorm[row] = r;
+    for (int i = lane; i < D; i += 32) y[row * D + i] = __float2bfloat16(v[i >> 5] * r);
+}
+
+__global__ void l2norm_bwd_kernel(const bf16* __restrict__ y, const bf16* __restrict__ dy, const float* __restrict__ rnorm,
+                                  bf16* __restrict__ dx, long long rows, int D) {
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    float yv[8], gv[8];
+    float dot = 0.f;
+    for (int i = lane; i < D; i += 32) {
+        yv[i >> 5] = __bfloat162float(y[row * D + i]);
+        gv[i >> 5] = __bfloat162float(dy[row * D + i]);
+        dot += yv[i >> 5] * gv[i >> 5];
+    }
+    dot = warp_sum(dot);
+    const float r = rnorm[row];
+    for (int i = lane; i < D; i += 32) dx[row * D + i] = __float2bfloat16(r * (gv[i >> 5] - yv[i >> 5] * dot));
+}
+
+// ---- gated RMSNorm forward: y = x * rsqrt(mean(x^2) + eps) * w * silu(z)   (rows of D <= 256)
+__global__ void gated_rmsnorm_fwd_kernel(const float* __restrict__ x, const bf16* __restrict__ z, const bf16* __restrict__ w,
+                                         bf16* __restrict__ y, long long rows, int D, float eps) {
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    float v[8];
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) {
+        v[i >> 5] = x[row * D + i];
+        ss += v[i >> 5] * v[i >> 5];
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / (float)D + eps);
+    for (int i = lane; i < D; i += 32) {
+        const float zz = __bfloat162float(z[row * D + i]);
+        y[row * D + i] = __float2bfloat16(v[i >> 5] * r * __bfloat162float(w[i]) * zz / (1.f + __expf(-zz)));
+    }
+}
+
+}  // namespace
+
+MM_API int mm_conv1d_fwd(const void* x, const void* w, const int* seq_start, void* y, int T, int D, int K, int silu, cudaStream_t st) {
+    if (D % 8 || K > kMaxK || K < 1) return -1;
+    dim3 grid((D / 8 + 127) / 128, (T + kStrip - 1) / kStrip);
+    if (silu) conv1d_fwd_kernel<true><<<grid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, seq_start, (bf16*)y, T, D, K);
+    else conv1d_fwd_kernel<false><<<grid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, seq_start, (bf16*)y, T, D, K);
+    return (int)cudaGetLastError();
+}
+
+// dw: fp32 [D, K], zeroed by the caller (accumulated with atomics).
+MM_API int mm_conv1d_bwd(const void* x, const void* w, const int* seq_start, const int* seq_end, const void* dy, void* dx,
+                         float* dw, int T, int D, int K, int silu, cudaStream_t st) {
+    if (D % 8 || K > kMaxK || K < 1) return -1;
+    dim3 grid((D / 8 + 127) / 128, (T + kStrip - 1) / kStrip);
+    if (silu) conv1d_bwd_kernel<true><<<grid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, seq_start, seq_end, (const bf16*)dy, (bf16*)dx, dw, T, D, K);
+    else conv1d_bwd_kernel<false><<<grid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, seq_start, seq_end, (const bf16*)dy, (bf16*)dx, dw, T, D, K);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_l2norm_fwd(const void* x, void* y, float* rnorm, long long rows, int D, float eps, cudaStream_t st) {
+    if (D > 256) return -1;
+    l2norm_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const bf16*)x, (bf16*)y, rnorm, rows, D, eps);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_l2norm_bwd(const void* y, const void* dy, const float* rnorm, void* dx, long long rows, int D, cudaStream_t st) {
+    if (D > 256) return -1;
+    l2norm_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const bf16*)y, (const bf16*)dy, rnorm, (bf16*)dx, rows, D);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_gated_rmsnorm_fwd(const float* x, const void* z, const void* w, void* y, long long rows, int D, float eps,
+                                cudaStream_t st) {
+    if (D > 256) return -1;
+    gated_rmsnorm_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(x, (const bf16*)z, (const bf16*)w, (bf16*)y, rows, D, eps);
+    return (int)cudaGetLastError();
+}

@@ -1,0 +1,208 @@
+"""Chunked gated delta rule on packed sequences: batched prologue + sequential state pass.
+
+The WY form splits the operator in two:
+
+* ``chunk_prologue`` -- everything local to a 64-token chunk (cumulative gates, the unit-triangular solve, ``u``,
+  ``w``, the decayed ``q`` / ``k`` and the masked intra-chunk attention).  It is plain batched PyTorch over all
+  chunks of all sequences at once, so autograd differentiates it.
+* ``state_pass`` -- the walk over the chunks of a sequence, each needing the state its predecessor left.  On a GPU
+  the forward is the tcgen05 kernel of ``csrc/gdn.cu`` (state resident in tensor memory); on CPU a PyTorch loop with
+  the same inputs and outputs.  Its backward is written by hand: only ``dS`` has to be walked backwards over the
+  chunks, every other gradient is a batched product of saved per-chunk states.
+
+Operator parity: fla ``chunk_gated_delta_rule`` as called by the reference's Qwen3.5 gated-delta-net block
+(fsdp/models/qwen3_5/modeling_qwen3_5.py) with ``cu_seqlens`` packing.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+CHUNK = 64
+
+
+# ------------------------------------------------------------------------------------------ chunk layout
+class ChunkLayout:
+    """Maps packed tokens [T] to chunk-padded slots [NC * 64]; chunks never straddle a sequence."""
+
+    def __init__(self, cu_seqlens: Sequence[int], device):
+        cu = [int(c) for c in cu_seqlens]
+        self.T = cu[-1]
+        slot_of_tok: List[torch.Tensor] = []
+        seq_chunks = [0]
+        pos: List[int] = []
+        seq_of: List[int] = []
+        for s, (a, b) in enumerate(zip(cu[:-1], cu[1:])):
+            n = (b - a + CHUNK - 1) // CHUNK
+            slot_of_tok.append(torch.arange(b - a) + seq_chunks[-1] * CHUNK)
+            pos += list(range(n))
+            seq_of += [s] * n
+            seq_chunks.append(seq_chunks[-1] + n)
+        self.NC = seq_chunks[-1]
+        self.nseq = len(cu) - 1
+        self.max_chunks = max(pos) + 1 if pos else 0
+        self.slot_of_tok = torch.cat(slot_of_tok).to(device) if slot_of_tok else torch.zeros(0, dtype=torch.long, device=device)
+        self.seq_chunks = torch.tensor(seq_chunks, dtype=torch.int32, device=device)
+        self.seq_chunks_host = seq_chunks
+        # chunks at position j of their sequence (and the sequences they belong to), for the backward walk
+        self.idx_at = [torch.tensor([c for c, pj in enumerate(pos) if pj == j], dtype=torch.long, device=device)
+                       for j in range(self.max_chunks)]
+        self.seq_at = [torch.tensor([seq_of[c] for c, pj in enumerate(pos) if pj == j], dtype=torch.long, device=device)
+                       for j in range(self.max_chunks)]
+
+    def scatter(self, x: torch.Tensor) -> torch.Tensor:
+        """[T, H, ...] -> [H, NC, 64, ...] with zero padding."""
+        out = x.new_zeros((self.NC * CHUNK,) + tuple(x.shape[1:]))
+        out = out.index_copy(0, self.slot_of_tok, x)
+        out = out.view((self.NC, CHUNK) + tuple(x.shape[1:]))
+        return out.movedim(2, 0)
+
+    def gather(self, y: torch.Tensor) -> torch.Tensor:
+        """[H, NC*64, V] -> [T, H, V]."""
+        return y.transpose(0, 1).index_select(0, self.slot_of_tok)
+
+
+# ------------------------------------------------------------------------------------------ prologue
+def chunk_prologue(q, k, v, g, beta, scale: float):
+    """Inputs [H, NC, 64, *] (fp32).  Returns W, Qg, Kd [H,NC,64,K], At [H,NC,64,64], U [H,NC,64,V], gamma [H,NC]."""
+    gc = g.cumsum(-1)
+    diff = gc.unsqueeze(-1) - gc.unsqueeze(-2)
+    tril = torch.ones(CHUNK, CHUNK, dtype=torch.bool, device=q.device).tril()
+    decay = torch.where(tril, diff, torch.full_like(diff, -float("inf"))).exp()
+    kb = k * beta.unsqueeze(-1)
+    A = (kb @ k.transpose(-1, -2) * decay).tril(-1)              # I + A is the unit-triangular system
+    eye = torch.eye(CHUNK, device=q.device, dtype=q.dtype)
+    Tm = torch.linalg.solve_triangular(eye + A, eye.expand_as(A), upper=False, unitriangular=True)
+    U = Tm @ (v * beta.unsqueeze(-1))
+    W = Tm @ (kb * gc.exp().unsqueeze(-1))
+    Qg = q * (scale * gc.exp()).unsqueeze(-1)
+    last = gc[..., -1:]
+    Kd = k * (last - gc).exp().unsqueeze(-1)
+    At = (q @ k.transpose(-1, -2)) * (decay * scale)
+    gamma = last.squeeze(-1).exp()
+    return W, Qg, Kd, At, U, gamma
+
+
+# ------------------------------------------------------------------------------------------ state pass
+def _state_pass_torch(W, Qg, Kd, At, U, gamma, layout: ChunkLayout):
+    """PyTorch state walk with the kernel's contract.  Shapes [H, NC, 64, *]; returns O, Vn, SprevT."""
+    H, NC, _, K = W.shape
+    V = U.shape[-1]
+    O = torch.empty(H, NC, CHUNK, V, dtype=torch.float32, device=W.device)
+    Vn = torch.empty_like(O)
+    SprevT = torch.empty(H, NC, V, K, dtype=torch.float32, device=W.device)
+    sc = layout.seq_chunks_host
+    Wf, Qf, Kf, Af, Uf = (t.float() for t in (W, Qg, Kd, At, U))
+    for s in range(layout.nseq):
+        S = torch.zeros(H, K, V, dtype=torch.float32, device=W.device)
+        for c in range(sc[s], sc[s + 1]):
+            SprevT[:, c] = S.transpose(-1, -2)
+            vn = Uf[:, c] - Wf[:, c] @ S
+            O[:, c] = Qf[:, c] @ S + Af[:, c] @ vn
+            Vn[:, c] = vn
+            S = S * gamma[:, c, None, None] + Kf[:, c].transpose(-1, -2) @ vn
+    return O, Vn, SprevT
+
+
+def _state_pass_native(W, Qg, Kd, At, U, gamma, layout: ChunkLayout, want_saved: bool):
+    from . import native
+    H, NC, _, K = W.shape
+    V = U.shape[-1]
+    dev = W.device
+    O = torch.empty(H, NC, CHUNK, V, dtype=torch.bfloat16, device=dev)
+    Vn = torch.empty_like(O) if want_saved else None
+    SprevT = torch.empty(H, NC, V, K, dtype=torch.bfloat16, device=dev) if want_saved else None
+    native._check(native.lib().mm_gdn_fwd(
+        W.data_ptr(), Qg.data_ptr(), Kd.data_ptr(), At.data_ptr(), U.data_ptr(), gamma.data_ptr(),
+        layout.seq_chunks.data_ptr(), O.data_ptr(), Vn.data_ptr() if want_saved else None,
+        SprevT.data_ptr() if want_saved else None, None, H, NC, layout.nseq,
+        native.status_word(dev).data_ptr(), native._st()), "gdn_fwd")
+    return O, Vn, SprevT
+
+
+class _StatePass(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, W, Qg, Kd, At, U, gamma, layout):
+        need = any(t.requires_grad for t in (W, Qg, Kd, At, U, gamma))
+        if W.is_cuda:
+            args = [t.to(torch.bfloat16).contiguous() for t in (W, Qg, Kd, At, U)]
+            gam = gamma.float().contiguous()
+            O, Vn, SprevT = _state_pass_native(*args, gam, layout, need)
+            saved = args + [gam]
+        else:
+            O, Vn, SprevT = _state_pass_torch(W, Qg, Kd, At, U, gamma, layout)
+            saved = [W, Qg, Kd, At, U, gamma]
+        if need:
+            ctx.save_for_backward(*saved[:4], saved[5], Vn, SprevT)
+        ctx.layout = layout
+        ctx.in_dtypes = [t.dtype for t in (W, Qg, Kd, At, U, gamma)]
+        return O
+
+    @staticmethod
+    def backward(ctx, dO):
+        W, Qg, Kd, At, gamma, Vn, SprevT = ctx.saved_tensors
+        lay: ChunkLayout = ctx.layout
+        H, NC, _, K = W.shape
+        V = Vn.shape[-1]
+        dev = W.device
+        cdt = W.dtype                       # bf16 on a GPU (tensor-core batched products), fp32 on CPU
+        dO = dO.to(cdt)
+        dVn = torch.empty(H, NC, CHUNK, V, dtype=cdt, device=dev)
+        dSn_all = torch.empty(H, NC, K, V, dtype=cdt, device=dev)     # gradient w.r.t. the state after each chunk
+        dS_seq = torch.zeros(H, lay.nseq, K, V, dtype=torch.float32, device=dev)
+        QgT_dO = Qg.transpose(-1, -2) @ dO                            # [H, NC, K, V]   batched once
+        AtT_dO = At.transpose(-1, -2) @ dO                            # [H, NC, 64, V]
+        for j in range(lay.max_chunks - 1, -1, -1):
+            idx, sidx = lay.idx_at[j], lay.seq_at[j]
+            dSn = dS_seq[:, sidx]                                     # fp32 [H, n, K, V]
+            dSn_c = dSn.to(cdt)
+            dSn_all[:, idx] = dSn_c
+            dvn = AtT_dO[:, idx] + Kd[:, idx] @ dSn_c
+            dVn[:, idx] = dvn
+            dS_prev = QgT_dO[:, idx].float() + gamma[:, idx, None, None] * dSn - (W[:, idx].transpose(-1, -2) @ dvn).float()
+            dS_seq[:, sidx] = dS_prev
+        dU = dVn
+        dW = -(dVn @ SprevT.to(cdt))                                  # [64, V] @ [V, K]
+        dQg = dO @ SprevT.to(cdt)
+        dAt = dO @ Vn.to(cdt).transpose(-1, -2)
+        dKd = Vn.to(cdt) @ dSn_all.transpose(-1, -2)
+        dgamma = (dSn_all.float() * SprevT.float().transpose(-1, -2)).sum((-1, -2))
+        outs = (dW, dQg, dKd, dAt, dU, dgamma)
+        return tuple(o.to(dt) for o, dt in zip(outs, ctx.in_dtypes)) + (None,)
+
+
+def state_pass(W, Qg, Kd, At, U, gamma, layout: ChunkLayout):
+    return _StatePass.apply(W, Qg, Kd, At, U, gamma, layout)
+
+
+# ------------------------------------------------------------------------------------------ public
+_layout_cache: dict = {}
+
+
+def _layout(cu_seqlens, device) -> ChunkLayout:
+    cu = cu_seqlens.tolist() if torch.is_tensor(cu_seqlens) else cu_seqlens
+    key = (tuple(int(c) for c in cu), str(device))
+    lay = _layout_cache.get(key)
+    if lay is None:
+        if len(_layout_cache) > 64:
+            _layout_cache.clear()
+        lay = _layout_cache[key] = ChunkLayout(key[0], device)
+    return lay
+
+
+def gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, scale: Optional[float] = None):
+    """q, k: [T, H, K]; v: [T, H, V]; g (log gate), beta: [T, H].  Returns [T, H, V] in ``v.dtype``."""
+    K = q.shape[-1]
+    scale = K ** -0.5 if scale is None else scale
+    lay = _layout(cu_seqlens, q.device)
+    qc, kc, vc = (lay.scatter(t.float()) for t in (q, k, v))
+    gcn, bc = (lay.scatter(t.float()) for t in (g, beta))
+    W, Qg, Kd, At, U, gamma = chunk_prologue(qc, kc, vc, gcn, bc, scale)
+    O = state_pass(W, Qg, Kd, At, U, gamma, lay)
+    H, NC = O.shape[:2]
+    return lay.gather(O.reshape(H, NC * CHUNK, -1)).to(v.dtype)
+
+
+def supported(q, v, chunk: int) -> bool:
+    return chunk == CHUNK and q.shape[-1] == 128 and v.shape[-1] == 128

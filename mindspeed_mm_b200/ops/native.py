@@ -55,6 +55,12 @@ def _declare(L):
         "mm_grouped_gemm_bf16": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p],
         "mm_moe_permute": [_p, _p, _p, _i, _i, _p],
         "mm_moe_unpermute": [_p, _p, _p, _p, _i, _i, _i, _p],
+        "mm_conv1d_fwd": [_p, _p, _p, _p, _i, _i, _i, _i, _p],
+        "mm_conv1d_bwd": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
+        "mm_l2norm_fwd": [_p, _p, _p, _ll, _i, _f, _p],
+        "mm_l2norm_bwd": [_p, _p, _p, _p, _ll, _i, _p],
+        "mm_gated_rmsnorm_fwd": [_p, _p, _p, _p, _ll, _i, _f, _p],
+        "mm_gdn_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p, _p],
         "mm_p2p_flag_bytes": [],
         "mm_p2p_allgather": [_p, _p, _ll, _i, _i, _i, _p],
         "mm_p2p_rs_adamw": [_p, _p, _ll, _i, _i, _i, C.c_uint, _f, _p, _p, _p, _p, _ll, _f, _f, _f, _f, _f, _f, _f,
@@ -642,5 +648,94 @@ def moe_experts(tokens, topk_ids, probs, gate_up, down):
 
 
 # --------------------------------------------------------------------------- GDN
+def _seq_bounds(cu_seqlens, T, device):
+    """Per-token first index and one-past-last index of its sequence (int32 [T] each)."""
+    if cu_seqlens is None:
+        return (torch.zeros(T, dtype=torch.int32, device=device), torch.full((T,), T, dtype=torch.int32, device=device))
+    cu = torch.as_tensor(cu_seqlens, device=device).to(torch.int64)
+    seg = torch.bucketize(torch.arange(T, device=device), cu[1:], right=True)
+    return cu[seg].int().contiguous(), cu[seg + 1].int().contiguous()
+
+
+class _CausalConv1d(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, cu_seqlens, silu):
+        T, D = x.shape
+        K = w.shape[-1]
+        x, w = x.contiguous(), w.contiguous()
+        start, end = _seq_bounds(cu_seqlens, T, x.device)
+        y = torch.empty_like(x)
+        _check(lib().mm_conv1d_fwd(x.data_ptr(), w.data_ptr(), start.data_ptr(), y.data_ptr(), T, D, K, int(silu), _st()),
+               "conv1d_fwd")
+        ctx.save_for_backward(x, w, start, end)
+        ctx.silu = silu
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, start, end = ctx.saved_tensors
+        T, D = x.shape
+        K = w.shape[-1]
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        dw = torch.zeros(D, K, dtype=torch.float32, device=x.device)
+        _check(lib().mm_conv1d_bwd(x.data_ptr(), w.data_ptr(), start.data_ptr(), end.data_ptr(), dy.data_ptr(),
+                                   dx.data_ptr(), dw.data_ptr(), T, D, K, int(ctx.silu), _st()), "conv1d_bwd")
+        return dx, dw.to(w.dtype), None, None
+
+
+def conv1d_supported(x, w) -> bool:
+    return x.dim() == 2 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 \
+        and w.shape[-1] <= 8
+
+
+def causal_conv1d(x, w, activation, cu_seqlens):
+    return _CausalConv1d.apply(x, w, cu_seqlens, activation == "silu")
+
+
+class _L2Norm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, eps):
+        D = x.shape[-1]
+        x2 = x.reshape(-1, D).contiguous()
+        y = torch.empty_like(x2)
+        r = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+        _check(lib().mm_l2norm_fwd(x2.data_ptr(), y.data_ptr(), r.data_ptr(), x2.shape[0], D, eps, _st()), "l2norm_fwd")
+        ctx.save_for_backward(y, r)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        y, r = ctx.saved_tensors
+        D = y.shape[-1]
+        dy2 = dy.reshape(-1, D).contiguous()
+        dx = torch.empty_like(y)
+        _check(lib().mm_l2norm_bwd(y.data_ptr(), dy2.data_ptr(), r.data_ptr(), dx.data_ptr(), y.shape[0], D, _st()),
+               "l2norm_bwd")
+        return dx.view(dy.shape), None
+
+
+def l2_norm(x, eps=1e-6):
+    return _L2Norm.apply(x, eps)
+
+
+def gated_rms_norm_fwd(x_f32, z, w, eps=1e-6):
+    """Inference-only fused ``rmsnorm(x) * w * silu(z)`` on an fp32 ``x`` (the delta-rule output)."""
+    D = x_f32.shape[-1]
+    x2 = x_f32.reshape(-1, D).contiguous()
+    z2 = z.reshape(-1, D).contiguous()
+    y = torch.empty(x2.shape, dtype=torch.bfloat16, device=x2.device)
+    _check(lib().mm_gated_rmsnorm_fwd(x2.data_ptr(), z2.data_ptr(), w.contiguous().data_ptr(), y.data_ptr(), x2.shape[0], D,
+                                      eps, _st()), "gated_rmsnorm_fwd")
+    return y.view(x_f32.shape)
+
+
 def gdn_supported(q, v, chunk) -> bool:
-    return False
+    from . import gdn
+    lib()
+    return _STATUS.get("mm_gdn_fwd", False) and gdn.supported(q, v, chunk)
+
+
+def gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk, scale):
+    from . import gdn
+    return gdn.gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, scale)

@@ -253,3 +253,68 @@ def test_moe_experts_native_vs_reference(T, k, E, H, F):
     _close(gu.grad, gur.grad, rtol=4e-2, atol=4e-2)
     _close(dn.grad, dnr.grad, rtol=4e-2, atol=4e-2)
     _close(p.grad, pr.grad, rtol=4e-2, atol=4e-2)
+
+
+@pytest.mark.parametrize("lens,D,K,silu", [([70, 200, 33], 512, 4, True), ([300], 1024, 4, False), ([5, 1, 64], 64, 3, True)])
+def test_causal_conv1d_fwd_bwd(lens, D, K, silu):
+    torch.manual_seed(0)
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    x = torch.randn(T, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (0.5 * torch.randn(D, K, device=DEV)).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(T, D, device=DEV, dtype=torch.bfloat16)
+    act = "silu" if silu else None
+    y = ops.causal_conv1d(x, w, None, act, cu)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = ref.causal_conv1d(xr, wr, None, act, cu.tolist())
+    yr.backward(dy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad)
+    _close(w.grad, wr.grad, rtol=3e-2)
+
+
+def test_l2norm_and_gated_rmsnorm():
+    torch.manual_seed(0)
+    x = torch.randn(777, 16, 128, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    dy = torch.randn_like(x)
+    y = ops.l2_norm(x)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    yr = ref.l2_norm(xr)
+    yr.backward(dy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad)
+    o = torch.randn(500, 8, 128, device=DEV)
+    z = torch.randn(500, 8, 128, device=DEV, dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(128, device=DEV)).to(torch.bfloat16)
+    with torch.no_grad():
+        _close(ops.gated_rms_norm(o, z, w, 1e-6), ref.gated_rms_norm(o, z.float(), w.float(), 1e-6))
+
+
+@pytest.mark.parametrize("lens,H", [([70, 200], 2), ([64], 1), ([1000, 130, 5], 4)])
+def test_gated_delta_rule_native(lens, H):
+    """tcgen05 state pass (+ hand-written backward) against the token-by-token fp32 recurrence."""
+    torch.manual_seed(0)
+    T, K, V = sum(lens), 128, 128
+    cu = [0] + [int(c) for c in torch.tensor(lens).cumsum(0)]
+    F = torch.nn.functional
+    q = F.normalize(torch.randn(T, H, K, device=DEV), dim=-1).requires_grad_()
+    k = F.normalize(torch.randn(T, H, K, device=DEV), dim=-1).requires_grad_()
+    v = torch.randn(T, H, V, device=DEV).requires_grad_()
+    g = (-0.5 * torch.rand(T, H, device=DEV)).requires_grad_()
+    beta = torch.rand(T, H, device=DEV).requires_grad_()
+    from mindspeed_mm_b200.ops import native
+    assert native.gdn_supported(q, v, 64)
+    o = ops.gated_delta_rule_varlen(q, k, v, g, beta, cu, chunk=64)
+    do = torch.randn_like(o)
+    grads = torch.autograd.grad(o, [q, k, v, g, beta], do)
+    outs = []
+    for a, b in zip(cu[:-1], cu[1:]):
+        oo, _ = ref.gated_delta_rule_recurrent(q[None, a:b], k[None, a:b], v[None, a:b], g[None, a:b], beta[None, a:b])
+        outs.append(oo[0])
+    o_ref = torch.cat(outs)
+    grads_ref = torch.autograd.grad(o_ref, [q, k, v, g, beta], do)
+    _close(o, o_ref, rtol=3e-2, atol=3e-3)
+    for a, b in zip(grads, grads_ref):
+        _close(a, b, rtol=5e-2, atol=5e-3)

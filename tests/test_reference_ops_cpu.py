@@ -172,3 +172,29 @@ def test_adamw_matches_torch():
         opt.step()
         ref.adamw_step(p, m, v, g, 1e-2, 0.9, 0.999, 1e-8, 0.1, step)
     assert torch.allclose(p, ref_p.data, atol=1e-6)
+
+
+def test_gdn_prologue_state_pass_and_hand_backward_match_recurrence():
+    """Batched prologue + state walk + hand-written backward == autograd of the token-by-token recurrence."""
+    import torch.nn.functional as F
+    from mindspeed_mm_b200.ops import gdn
+    torch.manual_seed(0)
+    T, H, K, V = 200, 2, 128, 128
+    cu = [0, 70, 200]
+    q = F.normalize(torch.randn(T, H, K), dim=-1).requires_grad_()
+    k = F.normalize(torch.randn(T, H, K), dim=-1).requires_grad_()
+    v = torch.randn(T, H, V).requires_grad_()
+    g = (-0.5 * torch.rand(T, H)).requires_grad_()
+    beta = torch.rand(T, H).requires_grad_()
+    o = gdn.gated_delta_rule_varlen(q, k, v, g, beta, cu)
+    outs = []
+    for a, b in zip(cu[:-1], cu[1:]):
+        oo, _ = ref.gated_delta_rule_recurrent(q[None, a:b], k[None, a:b], v[None, a:b], g[None, a:b], beta[None, a:b])
+        outs.append(oo[0])
+    o_ref = torch.cat(outs)
+    assert torch.allclose(o, o_ref, atol=1e-5)
+    do = torch.randn_like(o)
+    got = torch.autograd.grad(o, [q, k, v, g, beta], do)
+    want = torch.autograd.grad(o_ref, [q, k, v, g, beta], do)
+    for a, b in zip(got, want):
+        assert torch.allclose(a, b, atol=2e-5), (a - b).abs().max()

@@ -140,6 +140,46 @@ def bench_fmha(out, small):
         native.check_status()
 
 
+def bench_gdn(out, small):
+    """Gated delta rule, K = V = 128, chunk 64: the state-pass kernel alone, the whole operator (batched prologue
+    + kernel), forward + backward, and the PyTorch chunked oracle on the same GPU."""
+    from mindspeed_mm_b200.ops import gdn, reference as ref
+    import torch.nn.functional as F
+    cases = [("4x2048_h16", [2048] * 4, 16)] + ([] if small else [("2x8192_h32", [8192] * 2, 32)])
+    for name, lens, H in cases:
+        T = sum(lens)
+        cu = [0] + [int(c) for c in torch.tensor(lens).cumsum(0)]
+        q = F.normalize(torch.randn(T, H, 128, device="cuda"), dim=-1).bfloat16()
+        k = F.normalize(torch.randn(T, H, 128, device="cuda"), dim=-1).bfloat16()
+        v = torch.randn(T, H, 128, device="cuda", dtype=torch.bfloat16)
+        g = -0.5 * torch.rand(T, H, device="cuda")
+        beta = torch.rand(T, H, device="cuda")
+        lay = gdn._layout(cu, q.device)
+        with torch.no_grad():
+            pro = gdn.chunk_prologue(*(lay.scatter(t.float()) for t in (q, k, v, g, beta)), 128 ** -0.5)
+            args = [t.to(torch.bfloat16).contiguous() for t in pro[:5]] + [pro[5].float().contiguous()]
+            t_kernel = time_fn(lambda: gdn._state_pass_native(*args, lay, False))
+            t_fwd = time_fn(lambda: gdn.gated_delta_rule_varlen(q, k, v, g, beta, cu))
+            t_ref = time_fn(lambda: [ref.gated_delta_rule_chunked(q[None, a:b], k[None, a:b], v[None, a:b], g[None, a:b],
+                                                                  beta[None, a:b]) for a, b in zip(cu[:-1], cu[1:])],
+                            iters=3, warmup=1)
+        ins = [t.clone().requires_grad_() for t in (q, k, v, g, beta)]
+
+        def fb():
+            o = gdn.gated_delta_rule_varlen(*ins, cu)
+            o.backward(torch.ones_like(o))
+        t_fb = time_fn(fb, iters=5)
+        NC = lay.NC
+        # tensor-core work of the state pass per chunk and head: D1, D2 (2 x 2*128*64*128), O (2*128*64*64), S (2*128*64*128)
+        flops = NC * H * (3 * 2 * 128 * 64 * 128 + 2 * 128 * 64 * 64)
+        bytes_ = NC * H * 64 * (3 * 128 + 64 + 2 * 128) * 2          # W, Qg, Kd, At, U in; O out
+        emit(dict(op="gdn", case=name, T=T, heads=H, chunks=NC, state_pass_ms=round(t_kernel, 4),
+                  state_pass_tflops=round(flops / t_kernel / 1e9, 1), state_pass_gbs=round(bytes_ / t_kernel / 1e6, 1),
+                  fwd_ms=round(t_fwd, 3), fwd_bwd_ms=round(t_fb, 3), torch_chunked_fwd_ms=round(t_ref, 3),
+                  fwd_vs_torch_chunked=round(t_ref / t_fwd, 2)), out)
+        native.check_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ops", default="gemm,elementwise")
@@ -147,7 +187,7 @@ def main():
     ap.add_argument("--small", action="store_true")
     a = ap.parse_args()
     for op in a.ops.split(","):
-        {"gemm": bench_gemm, "elementwise": bench_elementwise, "fmha": bench_fmha}[op](a.out, a.small)
+        {"gemm": bench_gemm, "elementwise": bench_elementwise, "fmha": bench_fmha, "gdn": bench_gdn}[op](a.out, a.small)
 
 
 if __name__ == "__main__":

@@ -56,7 +56,10 @@ def model_provider(kind: str, args):
             with torch.device("meta"):
                 net = WanDiT(WanConfig.from_mm_json(pred))
         diff = {k: v for k, v in mm.get("diffusion", {}).items() if k != "model_id"}
-        return SoRAModel(net, FlowMatchScheduler(**diff), seed=args.seed)
+        from ..models.towers import build_ae, build_text_encoder
+        ae = None if mm.get("load_video_features", True) else build_ae(mm.get("ae"))
+        te = None if mm.get("load_text_features", True) else build_text_encoder(mm.get("text_encoder"))
+        return SoRAModel(net, FlowMatchScheduler(**diff), ae=ae, text_encoder=te, seed=args.seed)
     raise ValueError(f"unknown entry kind {kind}")
 
 

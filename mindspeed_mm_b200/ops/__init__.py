@@ -272,6 +272,11 @@ def gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk: int = 64, scale
     return torch.cat(outs, 0)
 
 
+def kda(q, k, v, g, beta, scale=None, chunk: int = 64, initial_state=None):
+    """Kimi delta attention (per-channel gate).  Chunked batched-GEMM form on every device."""
+    return ref.kda_chunked(q, k, v, g, beta, scale, chunk, initial_state)
+
+
 def status() -> dict:
     """Which ops have a native sm_100a implementation loaded (for logs and DESIGN tables)."""
     try:

@@ -325,6 +325,67 @@ def gated_delta_rule_chunked(q, k, v, g, beta, scale=None, chunk: int = 64, init
     return o, S
 
 
+def kda_recurrent(q, k, v, g, beta, scale=None, initial_state=None):
+    """Kimi delta attention, token by token: the delta rule with a per-channel gate.
+
+    q, k, g: [B,T,H,K] (g = log decay per key channel); v: [B,T,H,V]; beta: [B,T,H].
+    S_t = diag(exp(g_t)) S_{t-1};  S_t += k_t (beta_t (v_t - S_t^T k_t))^T;  o_t = S_t^T q_t * scale
+    (naive form of the reference: mindspeed_mm/fsdp/ops/kda/chunk_kda_naive.py).
+    """
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    scale = K ** -0.5 if scale is None else scale
+    q, k, v, g, beta = (t.float() for t in (q, k, v, g, beta))
+    S = torch.zeros(B, H, K, V, device=q.device) if initial_state is None else initial_state.float().clone()
+    outs = []
+    for t in range(T):
+        S = S * g[:, t].exp().unsqueeze(-1)
+        kv = torch.einsum("bhk,bhkv->bhv", k[:, t], S)
+        delta = (v[:, t] - kv) * beta[:, t][..., None]
+        S = S + torch.einsum("bhk,bhv->bhkv", k[:, t], delta)
+        outs.append(torch.einsum("bhk,bhkv->bhv", q[:, t] * scale, S))
+    return torch.stack(outs, 1), S
+
+
+def kda_chunked(q, k, v, g, beta, scale=None, chunk: int = 64, initial_state=None):
+    """Chunk-parallel KDA (WY form with per-channel decay); same math as :func:`kda_recurrent`.
+
+    Inside a chunk the pairwise decay exp(G_i - G_j) is applied per key channel by folding exp(G) into one operand
+    and exp(-G) into the other; ``g`` is accumulated from the chunk start, so the exponents stay bounded by the
+    chunk's total decay.
+    """
+    B, T0, H, K = q.shape
+    V = v.shape[-1]
+    scale = K ** -0.5 if scale is None else scale
+    pad = (-T0) % chunk
+    q, k, v, g, beta = (t.float() for t in (q, k, v, g, beta))
+    if pad:
+        q, k, v, g = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v, g))
+        beta = F.pad(beta, (0, 0, 0, pad))
+    n = (T0 + pad) // chunk
+    rs = lambda t: t.transpose(1, 2).reshape(B, H, n, chunk, -1)
+    q, k, v, g = rs(q) * scale, rs(k), rs(v), rs(g)
+    beta = beta.transpose(1, 2).reshape(B, H, n, chunk)
+    G = g.cumsum(-2)                                          # [B,H,n,C,K]
+    k_up, k_dn, q_up = k * G.exp(), k * (-G).exp(), q * G.exp()
+    eye = torch.eye(chunk, device=q.device)
+    A = ((k_up * beta.unsqueeze(-1)) @ k_dn.transpose(-1, -2)).tril(-1)
+    Tm = torch.linalg.solve_triangular(eye + A, eye.expand_as(A), upper=False, unitriangular=True)
+    u = Tm @ (v * beta.unsqueeze(-1))
+    w = Tm @ (k_up * beta.unsqueeze(-1))
+    attn = (q_up @ k_dn.transpose(-1, -2)).tril()
+    last = G[..., -1:, :]                                     # [B,H,n,1,K]
+    k_tail = k * (last - G).exp()
+    S = torch.zeros(B, H, K, V, device=q.device) if initial_state is None else initial_state.float().clone()
+    outs = []
+    for c in range(n):
+        v_new = u[:, :, c] - w[:, :, c] @ S
+        outs.append(q_up[:, :, c] @ S + attn[:, :, c] @ v_new)
+        S = S * last[:, :, c].transpose(-1, -2).exp() + k_tail[:, :, c].transpose(-1, -2) @ v_new
+    o = torch.stack(outs, 2).reshape(B, H, n * chunk, V).transpose(1, 2)[:, :T0]
+    return o, S
+
+
 # --------------------------------------------------------------------------- optimizer
 def adamw_step(p32, m, v, grad, lr, beta1, beta2, eps, wd, step, grad_scale: float = 1.0, p16=None):
     """One decoupled-weight-decay Adam update on fp32 master weights (in place)."""

@@ -67,3 +67,8 @@ def test_fused_gemm_collectives_2gpu():
 
 def test_tp_pp_backend_gloo():
     assert "ok=True" in _run_script(4, "dist_mcore_check.py")
+
+
+@pytest.mark.parametrize("wide", [False, True])
+def test_u_shaped_disaggregated_pipeline_gloo(wide):
+    assert "ok=True" in _run_script(3, "dist_ldt_check.py", *(["--wide"] if wide else []))

@@ -198,3 +198,17 @@ def test_gdn_prologue_state_pass_and_hand_backward_match_recurrence():
     want = torch.autograd.grad(o_ref, [q, k, v, g, beta], do)
     for a, b in zip(got, want):
         assert torch.allclose(a, b, atol=2e-5), (a - b).abs().max()
+
+
+def test_kda_chunked_matches_recurrent():
+    torch.manual_seed(0)
+    B, T, H, K, V = 2, 150, 2, 32, 16
+    q = F.normalize(torch.randn(B, T, H, K), dim=-1)
+    k = F.normalize(torch.randn(B, T, H, K), dim=-1)
+    v = torch.randn(B, T, H, V)
+    g = -0.1 * torch.rand(B, T, H, K)
+    beta = torch.rand(B, T, H)
+    o1, s1 = ref.kda_recurrent(q, k, v, g, beta)
+    o2, s2 = ref.kda_chunked(q, k, v, g, beta, chunk=64)
+    assert torch.allclose(o1, o2, atol=2e-4), (o1 - o2).abs().max()
+    assert torch.allclose(s1, s2, atol=2e-4)

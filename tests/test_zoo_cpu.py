@@ -60,3 +60,46 @@ def test_qwen35_gdn_layer_is_causal_and_packed():
     x3[5] += 1.0                                # a token of sequence 0 must not leak into sequence 1
     y3 = layer(x3, cu)
     assert torch.allclose(y[17:], y3[17:], atol=1e-5) and not torch.allclose(y[5:17], y3[5:17])
+
+
+def _composable_batch(cfg):
+    from mindspeed_mm_b200.data.collate import PackedVLMCollator
+    from mindspeed_mm_b200.data.synthetic import SyntheticVLMDataset, SyntheticVLMSpec
+    ds = SyntheticVLMDataset(SyntheticVLMSpec(seq_len=96, images_per_sample=1, image_size=56, vocab_size=1024,
+                                              image_token_id=1023, vision_start_token_id=1021,
+                                              temporal_patch=1 if cfg.vision_kind == "vit" else 2))
+    b = PackedVLMCollator(1023, 1021, vit_head_dim=32)([ds[0], ds[1]])
+    if cfg.vision_kind is None:
+        b.pop("pixel_values")
+    if cfg.audio is not None:
+        b["audio_features"] = [torch.randn(16, 40)]
+        b["input_ids"][5:15] = cfg.audio_token_id
+    return b
+
+
+def test_composable_presets_cover_the_reference_zoo_and_train():
+    """Every remaining model id of the reference's zoo resolves to a switch setting that runs forward + backward
+    with gradients on all parameters."""
+    from mindspeed_mm_b200.models import zoo  # noqa: F401
+    from mindspeed_mm_b200.models.composable import PRESETS, ComposableLM
+    from mindspeed_mm_b200.models.registry import model_register
+    for mid, cfg in PRESETS.items():
+        assert mid in model_register
+        torch.manual_seed(0)
+        m = ComposableLM(cfg)
+        m.init_weights(0)
+        loss, n = m(_composable_batch(cfg))
+        (loss / n).backward()
+        assert torch.isfinite(loss) and all(p.grad is not None for p in m.parameters()), mid
+
+
+def test_composable_from_hf_config_switches():
+    from mindspeed_mm_b200.models.composable import from_hf_config
+    hf = {"model_type": "kimi_k2", "text_config": {
+        "num_hidden_layers": 4, "hidden_size": 64, "num_attention_heads": 4, "vocab_size": 100, "kv_lora_rank": 16,
+        "q_lora_rank": 24, "qk_nope_head_dim": 8, "qk_rope_head_dim": 8, "v_head_dim": 8, "n_routed_experts": 8,
+        "num_experts_per_tok": 2, "moe_intermediate_size": 32, "n_shared_experts": 1, "first_k_dense_replace": 1},
+        "vision_config": {"hidden_size": 32, "intermediate_size": 64, "num_hidden_layers": 2, "num_attention_heads": 2}}
+    c = from_hf_config(hf)
+    assert c.text.mixers == ("mla",) * 4 and c.text.ffns == ("dense", "moe", "moe", "moe")
+    assert c.vision_kind == "vit" and c.text.shared_expert_intermediate_size == 32 and c.text.rope == "rope1d"

@@ -72,7 +72,9 @@ class VLMTrainerSpec:
     gradient_accumulation_steps: int = 1
     param_dtype: torch.dtype = torch.bfloat16
     reduce_dtype: torch.dtype = torch.float32
-    recompute: bool = True
+    recompute: object = True          # True / False / "auto" / int = number of decoder layers to recompute
+    tokens_per_micro_batch: int = 8192   # used by recompute="auto" to size the activation budget
+    activation_reserve_gb: float = 20.0  # memory kept free for workspaces when recompute="auto"
     loss_type: str = "default"
     seed: int = 0
     comm: str = "auto"
@@ -91,9 +93,12 @@ def build_vlm_trainer(spec: VLMTrainerSpec, device=None, data_iter=None, checkpo
     opt = OptimConfig(lr=spec.lr, weight_decay=spec.weight_decay, clip_grad=spec.clip_grad)
     engine = FSDPEngine(model.fsdp_units(), group=ps.get_fsdp_group() if world > 1 else False, device=dev,
                         param_dtype=spec.param_dtype, reduce_dtype=spec.reduce_dtype, opt=opt,
-                        recompute=spec.recompute, grad_accum_steps=spec.gradient_accumulation_steps, comm=spec.comm)
+                        recompute=spec.recompute is not False, grad_accum_steps=spec.gradient_accumulation_steps,
+                        comm=spec.comm)
     # python's hash() of str is salted per process: use a stable digest instead
     engine.materialize(stable_init_fn(spec.model.init_std, spec.seed))
+    if spec.recompute == "auto" or (isinstance(spec.recompute, int) and not isinstance(spec.recompute, bool)):
+        plan_recompute(engine, spec, world)
     sched = LRSchedule(lr=spec.lr, train_iters=spec.train_iters, lr_decay_style=spec.lr_decay_style,
                        lr_warmup_ratio=spec.lr_warmup_ratio)
     loss_fn = build_loss(spec.loss_type, ps.group("dp"), ps.get_dp_world_size())
@@ -101,6 +106,41 @@ def build_vlm_trainer(spec: VLMTrainerSpec, device=None, data_iter=None, checkpo
                       gradient_accumulation_steps=spec.gradient_accumulation_steps, log_interval=spec.log_interval)
     return TrainEngine(model, engine, loss_fn, sched, cfg, data_iter=data_iter, checkpointer=checkpointer,
                        dp_group=ps.group("dp"), dp_world=ps.get_dp_world_size(), device=dev)
+
+
+def decoder_layer_activation_bytes(t, tokens: int) -> int:
+    """Bytes autograd keeps for one decoder layer when it is not recomputed: the inputs of both norms and of the
+    four GEMMs, the rotated q/k, the attention output and the SwiGLU input (bf16), plus fp32 row statistics."""
+    qkv = (t.num_attention_heads + 2 * t.num_key_value_heads) * t.head_dim
+    rot = (t.num_attention_heads + t.num_key_value_heads) * t.head_dim
+    per_token = 2 * (5 * t.hidden_size + qkv + rot + 3 * t.intermediate_size) + 4 * (2 + t.num_attention_heads)
+    return per_token * tokens
+
+
+def plan_recompute(engine: FSDPEngine, spec: VLMTrainerSpec, world: int) -> int:
+    """Keep the autograd graph of as many decoder layers as the free device memory allows (the last layers first:
+    their backward runs first) and recompute the rest.  Returns the number of layers left on recompute.  All ranks
+    take the minimum so that they run the same plan."""
+    layers = [u for u in engine.units if u.name.startswith("layers.")]
+    if isinstance(spec.recompute, int) and not isinstance(spec.recompute, bool):
+        keep = max(0, len(layers) - spec.recompute)
+    elif engine.device.type == "cuda":
+        free, _ = torch.cuda.mem_get_info(engine.device)
+        per_layer = decoder_layer_activation_bytes(spec.model.text, spec.tokens_per_micro_batch) * 1.1
+        # a layer that keeps its graph also keeps its gathered bf16 weights and gradients until its update
+        per_layer += 0 if world == 1 else 4 * sum(g.padded for g in layers[0].groups)
+        keep = int(max(0.0, free - spec.activation_reserve_gb * 2 ** 30) // per_layer)
+        if world > 1:
+            k = torch.tensor([keep], device=engine.device)
+            dist.all_reduce(k, op=dist.ReduceOp.MIN)
+            keep = int(k.item())
+    else:
+        keep = 0
+    keep = min(keep, len(layers))
+    for u in layers[len(layers) - keep:]:
+        u.recompute = False
+    engine.recompute_plan = {"decoder_layers": len(layers), "recomputed": len(layers) - keep}
+    return len(layers) - keep
 
 
 def stable_init_fn(std: float = 0.02, seed: int = 0):

@@ -300,6 +300,8 @@ class FSDPEngine:
             self.wait_unshard(u)
             self._prefetch_forward(u)
             u.pending_reduce = u.trainable
+            if u.trainable:
+                self._hook_backward_done(u, args, kwargs)
             return module(*args, **kwargs)
         tensors, spec = _split_args(args, kwargs)
         outs = _UnitFn.apply(self, u, spec, self._dummy, *tensors)
@@ -337,14 +339,38 @@ class FSDPEngine:
             self._exec_pos = {id(u): i for i, u in enumerate(self._exec_order)}
 
     # ------------------------------------------------------------------ gradient reduce + update
-    def flush_pending(self) -> None:
+    def _hook_backward_done(self, u: Unit, args, kwargs) -> None:
+        """A unit that keeps its graph has finished its backward once the gradient of its (first differentiable)
+        input exists.  Its reduce + update is issued when the *next* unit reports done (one unit of slack, so a
+        weight-gradient node scheduled after the input gradient cannot be missed); the last one is picked up by
+        ``flush_pending``.  Units without a differentiable input are reduced by ``flush_pending`` only."""
+        for t in list(args) + list(kwargs.values()):
+            if isinstance(t, torch.Tensor) and t.requires_grad:
+                t.register_hook(lambda g, u=u: self._unit_backward_done(u))
+                return
+
+    def _unit_backward_done(self, u: Unit) -> None:
+        prev, self._done_wait = getattr(self, "_done_wait", None), u
+        if prev is not None and prev is not u and prev.pending_reduce:
+            self._reduce_pending(prev)
+
+    def _reduce_pending(self, u: Unit) -> None:
+        u.pending_reduce = False
+        u.bwd_done = True
+        if any(p.grad is not None for g in u.groups for _, p in g.named_params):
+            self.reduce_and_update(u)
+        self.reshard(u)
+
+    def flush_pending(self, after: Optional[Unit] = None) -> None:
+        """Reduce every graph-keeping unit whose backward is over: all of them (``after`` None, end of the step) or
+        those that ran after ``after`` in the forward (their backward precedes ``after``'s)."""
+        pos = self._exec_pos if self._order_known else {id(u): i for i, u in enumerate(self.units)}
+        lo = pos.get(id(after), -1) if after is not None else -1
         for u in self.units:
-            if u.pending_reduce:
-                u.pending_reduce = False
-                u.bwd_done = True
-                if any(p.grad is not None for g in u.groups for _, p in g.named_params):
-                    self.reduce_and_update(u)
-                self.reshard(u)
+            if u.pending_reduce and pos.get(id(u), 1 << 30) > lo:
+                self._reduce_pending(u)
+        if after is None:
+            self._done_wait = None
 
     def reduce_and_update(self, u: Unit) -> None:
         last_micro = (self.micro_step + 1) % self.grad_accum_steps == 0
@@ -582,7 +608,7 @@ class _UnitFn(torch.autograd.Function):
     def backward(ctx, *gouts):
         engine, u = ctx.engine, ctx.u
         tensors = [t.detach().requires_grad_(need) for t, need in zip(ctx.saved_tensors, ctx.needs)]
-        engine.flush_pending()
+        engine.flush_pending(after=u)
         engine.unshard(u)
         engine.wait_unshard(u)
         engine._prefetch_backward(u)

@@ -36,12 +36,15 @@ def main():
     ap.add_argument("--comm", default="auto")
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--clip", type=float, default=0.0)
+    ap.add_argument("--recompute-layers", type=int, default=-1,
+                    help=">= 0: recompute only that many decoder layers, keep the graph of the rest")
     a = ap.parse_args()
     cuda = a.device == "cuda"
     dtype = torch.bfloat16 if cuda else torch.float32
     cfg = small_cfg()
     spec = VLMTrainerSpec(model=cfg, lr=1e-3, lr_warmup_ratio=0.0, lr_decay_style="constant", param_dtype=dtype,
-                          clip_grad=a.clip, comm=a.comm, log_interval=0, weight_decay=0.01)
+                          clip_grad=a.clip, comm=a.comm, log_interval=0, weight_decay=0.01,
+                          recompute=True if a.recompute_layers < 0 else a.recompute_layers)
     tr = build_vlm_trainer(spec, device=a.device)
     rank, world = dist.get_rank(), dist.get_world_size()
     packs = [make_batches(cfg, a.steps, 512, 1, 1, 224, r, pin=False) for r in range(world)]

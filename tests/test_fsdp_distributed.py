@@ -24,6 +24,13 @@ def test_gloo_world2_matches_single_process():
     assert "ok=True" in out
 
 
+@pytest.mark.parametrize("layers", [0, 1])
+def test_gloo_world2_graph_kept_for_some_layers(layers):
+    """Layers that keep their autograd graph (no recompute) are reduced by their backward-done hooks."""
+    out = _run(2, "--device", "cpu", "--steps", "2", "--recompute-layers", str(layers))
+    assert "ok=True" in out
+
+
 def test_gloo_world2_with_clipping():
     out = _run(2, "--device", "cpu", "--steps", "2", "--clip", "0.5")
     assert "ok=True" in out
@@ -72,3 +79,7 @@ def test_tp_pp_backend_gloo():
 @pytest.mark.parametrize("wide", [False, True])
 def test_u_shaped_disaggregated_pipeline_gloo(wide):
     assert "ok=True" in _run_script(3, "dist_ldt_check.py", *(["--wide"] if wide else []))
+
+
+def test_hybrid_usp_and_fpdt_attention_gloo():
+    assert "ok=True" in _run_script(4, "dist_usp_check.py")

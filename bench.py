@@ -130,7 +130,7 @@ def main():
     ap.add_argument("--model", default="qwen2_5_vl_7b", choices=["qwen2_5_vl_7b", "tiny"])
     ap.add_argument("--seq-len", type=int, default=8192)
     ap.add_argument("--comm", default="auto", choices=["auto", "p2p", "nccl"])
-    ap.add_argument("--recompute", default="full", choices=["full", "auto", "none"],
+    ap.add_argument("--recompute", default="auto", choices=["full", "auto", "none"],
                     help="auto: keep the graph of as many decoder layers as free memory allows")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override decoder depth (invalidates the number)")
     args = ap.parse_args()
@@ -200,7 +200,8 @@ def main():
     plan = getattr(trainer.engine, "recompute_plan", None)
     recompute_note = ("full per decoder layer" if args.recompute == "full" else "none" if args.recompute == "none" else
                       f"memory-budgeted: {plan['recomputed']} of {plan['decoder_layers']} decoder layers recomputed, "
-                      f"ViT blocks recomputed" if plan else "full per decoder layer")
+                      f"{plan['vision_recomputed']} of {plan['vision_blocks']} ViT blocks recomputed"
+                      if plan else "full per decoder layer")
     peak_gb = torch.cuda.max_memory_allocated() / 2 ** 30
     if rank == 0:
         value = tokens_per_step / (ms_dev / 1e3)

@@ -74,6 +74,7 @@ class VLMTrainerSpec:
     reduce_dtype: torch.dtype = torch.float32
     recompute: object = True          # True / False / "auto" / int = number of decoder layers to recompute
     tokens_per_micro_batch: int = 8192   # used by recompute="auto" to size the activation budget
+    patches_per_micro_batch: int = 8192  # vision patches per micro-batch, same purpose
     activation_reserve_gb: float = 20.0  # memory kept free for workspaces when recompute="auto"
     loss_type: str = "default"
     seed: int = 0
@@ -117,6 +118,11 @@ def decoder_layer_activation_bytes(t, tokens: int) -> int:
     return per_token * tokens
 
 
+def vision_block_activation_bytes(v, patches: int) -> int:
+    inter = -(-v.intermediate_size // 64) * 64
+    return (2 * (5 * v.hidden_size + 3 * v.hidden_size + 2 * v.hidden_size + 3 * inter) + 4 * (2 + v.num_heads)) * patches
+
+
 def plan_recompute(engine: FSDPEngine, spec: VLMTrainerSpec, world: int) -> int:
     """Keep the autograd graph of as many decoder layers as the free device memory allows (the last layers first:
     their backward runs first) and recompute the rest.  Returns the number of layers left on recompute.  All ranks
@@ -140,6 +146,21 @@ def plan_recompute(engine: FSDPEngine, spec: VLMTrainerSpec, world: int) -> int:
     for u in layers[len(layers) - keep:]:
         u.recompute = False
     engine.recompute_plan = {"decoder_layers": len(layers), "recomputed": len(layers) - keep}
+    blocks = [u for u in engine.units if u.name.startswith("visual.blocks.") and u.trainable]
+    engine.recompute_plan.update(vision_blocks=len(blocks), vision_recomputed=len(blocks))
+    if spec.recompute == "auto" and keep == len(layers) and blocks and engine.device.type == "cuda":
+        left = free - spec.activation_reserve_gb * 2 ** 30 - keep * per_layer
+        per_block = vision_block_activation_bytes(spec.model.vision, spec.patches_per_micro_batch) * 1.1
+        per_block += 0 if world == 1 else 4 * sum(g.padded for g in blocks[0].groups)
+        kb = int(max(0.0, left) // per_block)
+        if world > 1:
+            k = torch.tensor([kb], device=engine.device)
+            dist.all_reduce(k, op=dist.ReduceOp.MIN)
+            kb = int(k.item())
+        kb = min(kb, len(blocks))
+        for u in blocks[len(blocks) - kb:]:
+            u.recompute = False
+        engine.recompute_plan["vision_recomputed"] = len(blocks) - kb
     return len(layers) - keep
 
 

@@ -19,6 +19,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--top", type=int, default=40)
     ap.add_argument("--out", default="")
+    ap.add_argument("--recompute", default="auto", choices=["full", "auto", "none"])
     a = ap.parse_args()
     from bench import make_batches
     from mindspeed_mm_b200 import ops
@@ -30,7 +31,8 @@ def main():
     cfg = Qwen25VLConfig.qwen2_5_vl_7b()
     if a.layers:
         cfg.text.num_layers = a.layers
-    tr = build_vlm_trainer(VLMTrainerSpec(model=cfg, lr=1e-5, log_interval=0))
+    tr = build_vlm_trainer(VLMTrainerSpec(model=cfg, lr=1e-5, log_interval=0,
+                                         recompute={"full": True, "none": False, "auto": "auto"}[a.recompute]))
     b = to_device(make_batches(cfg, 1, 8192, 4, 2, 448, 0, pin=True)[0], tr.device)
     for _ in range(2):
         tr.train_step([b])

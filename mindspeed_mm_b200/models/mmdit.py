@@ -53,6 +53,13 @@ class MMDiTConfig:
                            rope_theta=10000.0)
 
     @staticmethod
+    def sd3_medium():
+        """Stable Diffusion 3: dual-stream blocks only, 2x2 patches of 16-channel latents, no guidance embedding."""
+        return MMDiTConfig(in_channels=16, out_channels=16, patch_size=(1, 2, 2), hidden_size=1536, num_heads=24,
+                           num_double_blocks=24, num_single_blocks=0, text_dim=4096, pooled_dim=2048,
+                           rope_dims=(0, 32, 32), rope_theta=10000.0, guidance_embed=False)
+
+    @staticmethod
     def tiny():
         return MMDiTConfig(in_channels=4, out_channels=4, hidden_size=64, num_heads=4, num_double_blocks=1,
                            num_single_blocks=2, text_dim=32, pooled_dim=16, rope_dims=(4, 6, 6))
@@ -235,4 +242,11 @@ class HunyuanVideoDiT(MMDiT):
 
 @model_register.register("flux")
 class FluxDiT(MMDiT):
+    pass
+
+
+@model_register.register("sd3")
+class SD3DiT(MMDiT):
+    """Dual-stream-only MMDiT (the reference fine-tunes SD3 / SD3.5 through diffusers scripts,
+    examples/diffusers/sd3/); same blocks with ``num_single_blocks = 0``."""
     pass

@@ -77,3 +77,58 @@ class WanPipeline:
         lat = self.scheduler.sample(fn, lat, prompt_embeds.to(device, dtype),
                                     None if negative_prompt_embeds is None else negative_prompt_embeds.to(device, dtype))
         return self.vae_decode(lat) if self.vae_decode is not None else lat
+
+
+def wan_i2v_condition(first_frame, vae, clip_vision=None, frames: int = 81, last_frame=None):
+    """Image-to-video conditioning of Wan (mindspeed_mm/utils/extra_processor/wan_i2v_processor.py): the first
+    (and optionally last) frame padded with zeros to ``frames`` is VAE-encoded, a 4-channel mask marks which latent
+    frames are given (the first pixel frame repeated 4x so that it folds onto one latent frame), and the CLIP
+    penultimate-layer tokens of the image feed the DiT's image cross-attention.
+
+    first_frame: [B, 3, H, W] in [-1, 1].  Returns ``(y [B, 4 + z, 1 + (frames-1)/4, H/8, W/8], clip_feature)``."""
+    B, _, H, W = first_frame.shape
+    video = torch.zeros(B, 3, frames, H, W, dtype=first_frame.dtype, device=first_frame.device)
+    video[:, :, 0] = first_frame
+    mask = torch.zeros(B, frames, H // 8, W // 8, dtype=first_frame.dtype, device=first_frame.device)
+    mask[:, 0] = 1
+    if last_frame is not None:
+        video[:, :, -1] = last_frame
+        mask[:, -1] = 1
+    lat = vae.encode(video)
+    mask = torch.cat([mask[:, :1].repeat(1, 4, 1, 1), mask[:, 1:]], dim=1)          # 4 + (frames - 1)
+    mask = mask.view(B, mask.shape[1] // 4, 4, H // 8, W // 8).transpose(1, 2)      # [B, 4, T_lat, h, w]
+    clip = None
+    if clip_vision is not None:
+        img = torch.nn.functional.interpolate(first_frame.float(), size=(clip_vision.c.image_size,) * 2, mode="bicubic",
+                                              align_corners=False)
+        mean = torch.tensor([0.48145466, 0.4578275, 0.40821073], device=img.device).view(1, 3, 1, 1)
+        std = torch.tensor([0.26862954, 0.26130258, 0.27577711], device=img.device).view(1, 3, 1, 1)
+        clip = clip_vision.encode(((img * 0.5 + 0.5) - mean) / std)
+    return torch.cat([mask, lat], dim=1), clip
+
+
+class MMDiTPipeline:
+    """Text-to-image / text-to-video sampling for the dual/single-stream DiTs (FLUX, SD3, HunyuanVideo):
+    flow-matching Euler steps with an optional distilled-guidance input and classifier-free guidance
+    (mindspeed_mm/tasks/inference/pipeline/hunyuanvideo_pipeline.py, flux pipelines of the diffusers examples)."""
+
+    def __init__(self, dit, scheduler: Optional[FlowMatchScheduler] = None, vae_decode: Optional[Callable] = None,
+                 run: Optional[Callable] = None, embedded_guidance: Optional[float] = None):
+        self.dit, self.vae_decode, self.run, self.embedded_guidance = dit, vae_decode, run, embedded_guidance
+        self.scheduler = scheduler or FlowMatchScheduler(num_inference_timesteps=28, shift=3.0, sigma_min=0.0,
+                                                         extra_one_step=True, guidance_scale=1.0)
+
+    @torch.no_grad()
+    def __call__(self, txt, pooled, negative=None, frames: int = 1, height: int = 64, width: int = 64, generator=None,
+                 device="cpu", dtype=torch.float32):
+        c = self.dit.config
+        B = txt.shape[0]
+        lat = torch.randn(B, c.in_channels, frames, height, width, generator=generator, dtype=torch.float32).to(device, dtype)
+        g = None if self.embedded_guidance is None else torch.full((B,), self.embedded_guidance, device=device, dtype=dtype)
+
+        def fn(x, t, cond):
+            te, po = cond
+            return self.dit(x, t, te, po, g, run=self.run)
+        neg = None if negative is None else (negative[0].to(device, dtype), negative[1].to(device, dtype))
+        lat = self.scheduler.sample(fn, lat, (txt.to(device, dtype), pooled.to(device, dtype)), neg)
+        return self.vae_decode(lat) if self.vae_decode is not None else lat

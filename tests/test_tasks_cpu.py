@@ -96,3 +96,28 @@ def test_eval_metrics():
     assert ev.anls("hello wrld", ["hello world"]) > 0.8 and ev.anls("zzz", ["hello"]) == 0.0
     r = ev.evaluate(lambda s: s["guess"], [{"guess": "A", "answer": "A"}, {"guess": "B", "answer": "C"}], "multiple_choice")
     assert r == {"accuracy": 0.5, "n": 2}
+
+
+def test_wan_i2v_condition_and_mmdit_pipeline():
+    import torch
+    from mindspeed_mm_b200.models.ae.wan_vae import WanVAE, WanVAEConfig
+    from mindspeed_mm_b200.models.diffusion import FlowMatchScheduler
+    from mindspeed_mm_b200.models.encoders import CLIPVisionConfig, CLIPVisionEncoder
+    from mindspeed_mm_b200.models.mmdit import MMDiT, MMDiTConfig
+    from mindspeed_mm_b200.tasks.inference import MMDiTPipeline, wan_i2v_condition
+    torch.manual_seed(0)
+    vae = WanVAE(WanVAEConfig.tiny()).eval()
+    clip = CLIPVisionEncoder(CLIPVisionConfig.tiny()).eval()
+    y, feat = wan_i2v_condition(torch.rand(1, 3, 32, 32) * 2 - 1, vae, clip, frames=9)
+    assert y.shape == (1, 4 + 4, 3, 4, 4) and feat.shape == (1, 5, 64)
+    assert y[0, :4, 0].min() == 1 and y[0, :4, 1:].max() == 0          # only the first latent frame is given
+
+    cfg = MMDiTConfig.tiny()
+    dit = MMDiT(cfg)
+    for p in dit.parameters():
+        torch.nn.init.normal_(p, std=0.02)
+    pipe = MMDiTPipeline(dit, FlowMatchScheduler(num_inference_timesteps=3, shift=3.0, sigma_min=0.0, extra_one_step=True),
+                         embedded_guidance=3.5)
+    out = pipe(torch.randn(1, 6, cfg.text_dim), torch.randn(1, cfg.pooled_dim), frames=1, height=8, width=8,
+               generator=torch.Generator().manual_seed(0))
+    assert out.shape == (1, cfg.in_channels, 1, 8, 8) and torch.isfinite(out).all()

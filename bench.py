@@ -121,12 +121,114 @@ def make_batches(cfg, n_batches, seq_len, samples_per_pack, images_per_sample, i
     return [col([ds[b * samples_per_pack + i] for i in range(samples_per_pack)]) for b in range(n_batches)]
 
 
+def run_wan(args):
+    """Second headline workload: Wan2.1-14B text-to-video DiT training step, Ulysses sequence parallel over all N
+    GPUs of the job (one sample per SP group), parameters / optimizer state ZeRO-3 sharded over the same ranks.
+    Latents 16 x 21 x 90 x 160 (75600 tokens), umT5 context 512 x 4096, synthetic N(0,1) features, bf16, activation
+    checkpointing per block, AdamW.  value = samples/s of the whole job."""
+    from mindspeed_mm_b200 import ops
+    from mindspeed_mm_b200.api import init_distributed, stable_init_fn
+    from mindspeed_mm_b200.models.diffusion import FlowMatchScheduler
+    from mindspeed_mm_b200.models.wan import SoRAModel, WanConfig, WanDiT
+    from mindspeed_mm_b200.ops import native
+    from mindspeed_mm_b200.parallel.fsdp import FSDPEngine, OptimConfig
+    from mindspeed_mm_b200.parallel.state import init_parallel_state
+
+    ops.set_tier("native" if args.impl == "native" else "library")
+    dev, rank, world = init_distributed(None)
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    small = args.model == "tiny"
+    cfg = WanConfig.tiny() if small else WanConfig.wan2_1_14b()
+    if args.layers:
+        cfg.num_layers = args.layers
+    ps = init_parallel_state(world_size=world, device_type=dev.type, ulysses_parallel_size=world)
+    with torch.device("meta"):
+        net = WanDiT(cfg)
+    model = SoRAModel(net, FlowMatchScheduler(shift=5.0, sigma_min=0.0, extra_one_step=True), seed=0)
+    engine = FSDPEngine(model.fsdp_units(), group=ps.get_fsdp_group() if world > 1 else False, device=dev,
+                        param_dtype=torch.bfloat16, opt=OptimConfig(lr=1e-5, weight_decay=0.01), no_recompute=(),
+                        comm=args.comm)
+    engine.materialize(stable_init_fn(0.02, 0))
+    shape = (1, cfg.in_dim, 3, 8, 8) if small else (1, cfg.in_dim, 21, 90, 160)
+    g = torch.Generator().manual_seed(7)            # the same sample on every rank of the SP group
+    host = [dict(latents=torch.randn(shape, generator=g).to(torch.bfloat16).pin_memory(),
+                 prompt=torch.randn(1, cfg.text_len, cfg.text_dim, generator=g).to(torch.bfloat16).pin_memory())
+            for _ in range(2)]
+    on_dev = [{k: v.to(dev) for k, v in b.items()} for b in host]
+    h2d = sum(v.numel() * v.element_size() for v in host[0].values())
+    tokens = shape[2] * (shape[3] // 2) * (shape[4] // 2)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one(b):
+        engine.set_lr(1e-5)
+        loss = model(b, run=engine.run)
+        loss.backward()
+        engine.end_micro_step()
+        engine.finish_step()
+        return loss
+
+    def region(batches, steps, e2e):
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = native.LAUNCHES
+        s.record()
+        last = None
+        for i in range(steps):
+            b = batches[i % len(batches)]
+            if e2e:
+                b = {k: v.to(dev, non_blocking=True) for k, v in b.items()}
+            loss = one(b)
+            if e2e:
+                last = float(loss.detach())
+        e.record()
+        barrier()
+        ms = torch.tensor([s.elapsed_time(e)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms) / steps, native.LAUNCHES - l0, last
+
+    region(on_dev, max(args.warmup, 3) - 1, False)
+    region(host, 1, True)
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms_dev, launches, _ = region(on_dev, args.steps, False)
+    ms_e2e, _, loss = region(host, args.steps, True)
+    clocks = sampler.stop()
+    if args.impl == "native":
+        native.check_status()
+    if rank == 0:
+        out = {"metric": "Wan2.1-14B T2V samples/s", "value": round(1e3 / ms_dev, 4), "unit": "samples/s", "n_gpus": world,
+               "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_dev, 1),
+               "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+               "data": "synthetic (random-init weights, N(0,1) latents and text context)", "impl": args.impl,
+               "config": {"model": "Wan2.1-14B T2V" if not small else "tiny", "global_batch": 1, "seq_len": tokens,
+                          "parallelism": f"ulysses_sp{world} x zero3_{world}", "latent": list(shape[1:]),
+                          "recompute": "activation checkpointing per block", "optimizer": "AdamW fused into backward",
+                          "l2": "inputs_larger_than_L2 (28 GB of bf16 weights streamed every step)",
+                          "baseline_note": "the reference publishes no Wan2.1-14B number"},
+               "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1), "clocks": clocks,
+               "e2e": {"value": round(1e3 / ms_e2e, 4), "unit": "samples/s", "ms_per_step": round(ms_e2e, 1),
+                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": loss},
+               "gpu_launches": launches}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "library", "reference"])
+    ap.add_argument("--workload", default="vlm", choices=["vlm", "wan"],
+                    help="vlm: Qwen2.5-VL-7B FSDP2 tokens/s (default, the driver's line); wan: Wan2.1-14B T2V samples/s")
     ap.add_argument("--model", default="qwen2_5_vl_7b", choices=["qwen2_5_vl_7b", "tiny"])
     ap.add_argument("--seq-len", type=int, default=8192)
     ap.add_argument("--comm", default="auto", choices=["auto", "p2p", "nccl"])
@@ -137,6 +239,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload == "wan":
+        return run_wan(args)
 
     from mindspeed_mm_b200 import ops
     from mindspeed_mm_b200.api import VLMTrainerSpec, build_vlm_trainer

@@ -83,3 +83,7 @@ def test_u_shaped_disaggregated_pipeline_gloo(wide):
 
 def test_hybrid_usp_and_fpdt_attention_gloo():
     assert "ok=True" in _run_script(4, "dist_usp_check.py")
+
+
+def test_wan_fsdp_ulysses_matches_single_process_gloo():
+    assert "ok=True" in _run_script(2, "dist_wan_check.py")

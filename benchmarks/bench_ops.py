@@ -117,7 +117,7 @@ def bench_elementwise(out, small):
     rec("adamw_shard", lambda: native.adamw_shard(p, m, v, g, p16, 1e-4, 0.9, 0.999, 1e-8, 0.0, 1, n, 1.0), n * 28.0)
 
 
-def bench_fmha(out, small):
+def bench_fmha(out_file, small):
     import math
     tf, _, src = peaks()
     from flash_attn import flash_attn_varlen_func
@@ -134,9 +134,21 @@ def bench_fmha(out, small):
         sc = 1.0 / math.sqrt(D)
         t = time_fn(lambda: native.fmha_forward(q, k, v, cu, cu, causal, sc))
         tl = time_fn(lambda: flash_attn_varlen_func(q, k, v, cu, cu, max(lens), max(lens), causal=causal))
+        # backward: tcgen05 dQ + dK/dV kernels against flash-attn's backward, both fed with the native forward's out / lse
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
+        out, lse = native.fmha_forward(q, k, v, cu, cu, causal, sc)
+        do = torch.randn_like(out)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        tb = time_fn(lambda: native.fmha_backward(do, q, k, v, out, lse, cu, cu, causal, sc), iters=5)
+        tbl = time_fn(lambda: _flash_attn_varlen_backward(do, q, k, v, out, lse, dq, dk, dv, cu, cu, max(lens), max(lens), 0.0,
+                                                          sc, causal, -1, -1, 0.0, None, False), iters=5)
+        emit(dict(op="fmha_bwd", case=name, T=T, heads=nq, kv_heads=nkv, causal=causal, ms=round(tb, 4),
+                  tflops=round(2.5 * flops / tb / 1e9, 1), frac_of_peak=round(2.5 * flops / tb / 1e9 / tf, 3), peak=src,
+                  flash_attn2_ms=round(tbl, 4), flash_attn2_tflops=round(2.5 * flops / tbl / 1e9, 1),
+                  vs_flash_attn2=round(tbl / tb, 3)), out_file)
         emit(dict(op="fmha_fwd", case=name, T=T, heads=nq, kv_heads=nkv, causal=causal, ms=round(t, 4),
                   tflops=round(flops / t / 1e9, 1), frac_of_peak=round(flops / t / 1e9 / tf, 3), peak=src,
-                  flash_attn2_ms=round(tl, 4), flash_attn2_tflops=round(flops / tl / 1e9, 1), vs_flash_attn2=round(tl / t, 3)), out)
+                  flash_attn2_ms=round(tl, 4), flash_attn2_tflops=round(flops / tl / 1e9, 1), vs_flash_attn2=round(tl / t, 3)), out_file)
         native.check_status()
 
 

@@ -164,6 +164,32 @@ def plan_recompute(engine: FSDPEngine, spec: VLMTrainerSpec, world: int) -> int:
     return len(layers) - keep
 
 
+def wan_block_activation_bytes(c, tokens_local: int) -> int:
+    """Bytes autograd keeps for one Wan DiT block (self-attention incl. the Ulysses-exchanged q/k/v/o, cross-attention,
+    GELU FFN) when it is not recomputed."""
+    return 2 * (23 * c.hidden_size + 2 * c.ffn_dim) * tokens_local
+
+
+def plan_recompute_units(engine: FSDPEngine, prefix: str, per_unit_bytes: float, reserve_gb: float = 20.0) -> dict:
+    """Generic form of :func:`plan_recompute`: keep the graph of as many ``prefix*`` units (last ones first) as the
+    free device memory allows."""
+    units = [u for u in engine.units if u.name.startswith(prefix)]
+    keep = 0
+    if engine.device.type == "cuda" and units:
+        free, _ = torch.cuda.mem_get_info(engine.device)
+        per = per_unit_bytes * 1.1 + (0 if engine.world == 1 else 4 * sum(g.padded for g in units[0].groups))
+        keep = int(max(0.0, free - reserve_gb * 2 ** 30) // per)
+        if engine.world > 1:
+            k = torch.tensor([keep], device=engine.device)
+            dist.all_reduce(k, op=dist.ReduceOp.MIN, group=engine.group)
+            keep = int(k.item())
+    keep = min(keep, len(units))
+    for u in units[len(units) - keep:]:
+        u.recompute = False
+    engine.recompute_plan = {"units": len(units), "recomputed": len(units) - keep}
+    return engine.recompute_plan
+
+
 def stable_init_fn(std: float = 0.02, seed: int = 0):
     import zlib
 

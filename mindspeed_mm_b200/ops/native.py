@@ -51,6 +51,9 @@ def _declare(L):
         "mm_ce_fwd_bwd": [_p, _ll, _p, _p, _i, _i, _i, _p],
         "mm_fmha_max_tiles": [_i, _i],
         "mm_fmha_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _f, _p, _p],
+        "mm_fmha_bwd_max_tiles": [_i, _i],
+        "mm_fmha_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _f,
+                        _p, _p],
         "mm_grouped_gemm_max_tiles": [_i, _i, _i, _i, _i],
         "mm_grouped_gemm_bf16": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p],
         "mm_moe_permute": [_p, _p, _p, _i, _i, _p],
@@ -449,9 +452,38 @@ def fmha_forward(q, k, v, cu_q, cu_k, causal, scale):
     return out, lse
 
 
+FMHA_BWD = os.environ.get("MM_B200_FMHA_BWD", "native")     # "native" (tcgen05 kernels) or "flash" (flash-attn library)
+
+
+def fmha_backward(do, q, k, v, out, lse, cu_q, cu_k, causal, scale):
+    """dq, dk, dv from the tcgen05 backward kernels (dQ kernel + dK/dV kernel, no atomics)."""
+    q, k, v = _dense_heads(q), _dense_heads(k), _dense_heads(v)
+    do, out = do.contiguous(), out.contiguous()
+    T, Nq, D = q.shape
+    Tk, Nkv = k.shape[0], k.shape[1]
+    n_seqs = cu_q.numel() - 1
+    dev = q.device
+    dq = torch.empty(T, Nq, D, dtype=q.dtype, device=dev)
+    dk = torch.empty(Tk, Nkv, D, dtype=q.dtype, device=dev)
+    dv = torch.empty(Tk, Nkv, D, dtype=q.dtype, device=dev)
+    delta = torch.empty(Nq, T, dtype=torch.float32, device=dev)
+    L = lib()
+    plan = torch.empty(2 * (L.mm_fmha_bwd_max_tiles(T, n_seqs) + L.mm_fmha_bwd_max_tiles(Tk, n_seqs)) + 2,
+                       dtype=torch.int32, device=dev)
+    cu_q, cu_k = cu_q.to(torch.int32), cu_k.to(torch.int32)
+    rc = L.mm_fmha_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                       delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu_q.data_ptr(), cu_k.data_ptr(),
+                       plan.data_ptr(), T, Tk, n_seqs, Nq, Nkv, D, q.stride(0), k.stride(0), v.stride(0), int(causal),
+                       float(scale), status_word(dev).data_ptr(), _st())
+    _check(rc, "fmha_bwd")
+    global LAUNCHES
+    LAUNCHES += 4
+    return dq, dk, dv
+
+
 class _FMHA(torch.autograd.Function):
-    """Forward: tcgen05 kernel.  Backward: flash-attn's varlen backward fed with this forward's out / lse
-    (library kernel, until the tcgen05 backward replaces it)."""
+    """Forward and backward: tcgen05 kernels (``MM_B200_FMHA_BWD=flash`` switches the backward to flash-attn's
+    varlen backward fed with this forward's out / lse, for comparison)."""
 
     @staticmethod
     def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, causal, scale):
@@ -465,6 +497,9 @@ class _FMHA(torch.autograd.Function):
         from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
         q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
         max_q, max_k, causal, scale = ctx.meta
+        if FMHA_BWD == "native" and _STATUS.get("mm_fmha_bwd", False):
+            dq, dk, dv = fmha_backward(do, q, k, v, out, lse, cu_q, cu_k, causal, scale)
+            return dq, dk, dv, None, None, None, None, None, None
         dq, dk, dv = torch.empty(q.shape, dtype=q.dtype, device=q.device), torch.empty(k.shape, dtype=k.dtype, device=k.device), \
             torch.empty(v.shape, dtype=v.dtype, device=v.device)
         _flash_attn_varlen_backward(do.contiguous(), q, k, v, out, lse, dq, dk, dv, cu_q.to(torch.int32), cu_k.to(torch.int32),

@@ -228,6 +228,25 @@ def test_fmha_forward_and_grad(lens, nq, nkv, causal):
     _close(vg.grad, vr.grad, rtol=3e-2, atol=3e-2)
 
 
+def test_fmha_backward_cross_attention_shapes():
+    """q and k/v of different lengths (DiT cross-attention to 512 text tokens), non-causal, tcgen05 backward."""
+    torch.manual_seed(0)
+    B, Sq, Sk, N, D = 2, 700, 512, 3, 128
+    q = torch.randn(B, Sq, N, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(B, Sk, N, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(B, Sk, N, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    o = ops.attention_dense(q, k, v)
+    do = torch.randn_like(o)
+    o.backward(do)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    orf = ref.attention_dense(qr, kr, vr)
+    orf.backward(do.float())
+    _close(o, orf)
+    _close(q.grad, qr.grad, rtol=3e-2, atol=3e-2)
+    _close(k.grad, kr.grad, rtol=3e-2, atol=3e-2)
+    _close(v.grad, vr.grad, rtol=3e-2, atol=3e-2)
+
+
 @pytest.mark.parametrize("T,k,E,H,F", [(512, 2, 8, 256, 128), (4096, 8, 128, 2048, 768), (300, 4, 16, 512, 256)])
 def test_moe_experts_native_vs_reference(T, k, E, H, F):
     torch.manual_seed(0)

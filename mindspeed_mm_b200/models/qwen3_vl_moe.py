@@ -73,7 +73,11 @@ class FusedExperts(nn.Module):
     def forward(self, tokens, topk_ids, probs):
         ps = get_parallel_state()
         if ps.enabled("ep"):
-            fn = epmod.ep_forward_allgather if self.c.ep_dispatcher == "allgather" else epmod.ep_forward_alltoall
+            kind = self.c.ep_dispatcher
+            if kind in ("p2p", "mc2") and not (tokens.is_cuda and tokens.dtype == torch.bfloat16 and ops.get_tier() == "native"):
+                kind = "alltoall"                      # the peer-memory dispatcher is GPU / bf16 only
+            fn = {"allgather": epmod.ep_forward_allgather, "p2p": epmod.ep_forward_p2p,
+                  "mc2": epmod.ep_forward_p2p}.get(kind, epmod.ep_forward_alltoall)
             return fn(tokens, topk_ids, probs, self.gate_up_proj, self.down_proj, self.c.num_experts, ps.get_ep_group())
         return ops.moe_experts(tokens, topk_ids, probs, self.gate_up_proj, self.down_proj)
 

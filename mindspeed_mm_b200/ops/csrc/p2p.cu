@@ -222,6 +222,34 @@ __global__ void p2p_wait_done_kernel(void* my_flags, int slot, uint32_t seq, int
     }
 }
 
+// ------------------------------------------------------------------------------------------ MoE row exchange
+// Expert-parallel dispatch / combine as direct peer memory traffic: a token row goes straight from the sender's
+// activation tensor into its slot of the destination rank's expert slab (and back), so the all-to-all and the
+// permute are one pass over the data.  Row maps are computed on the host side of the op from the exchanged
+// per-expert histograms.  One warp moves one row with 16-byte accesses.
+//   scatter: peer[dst_rank[i]][dst_row[i]] = src[src_row[i]]            (push)
+//   gather : out[i] = peer[dst_rank[i]][dst_row[i]]                      (pull)
+__global__ void __launch_bounds__(256) p2p_scatter_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ src_row,
+                                                               const int* __restrict__ dst_rank,
+                                                               const int* __restrict__ dst_row, Peers bufs, int n, int row_vec) {
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (i >= n) return;
+    const int lane = threadIdx.x & 31;
+    const uint4* s = src + (size_t)src_row[i] * row_vec;
+    uint4* d = reinterpret_cast<uint4*>(bufs.p[dst_rank[i]]) + (size_t)dst_row[i] * row_vec;
+    for (int v = lane; v < row_vec; v += 32) d[v] = s[v];
+}
+
+__global__ void __launch_bounds__(256) p2p_gather_rows_kernel(uint4* __restrict__ out, const int* __restrict__ dst_rank,
+                                                              const int* __restrict__ dst_row, Peers bufs, int n, int row_vec) {
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (i >= n) return;
+    const int lane = threadIdx.x & 31;
+    const uint4* s = reinterpret_cast<const uint4*>(bufs.p[dst_rank[i]]) + (size_t)dst_row[i] * row_vec;
+    uint4* d = out + (size_t)i * row_vec;
+    for (int v = lane; v < row_vec; v += 32) d[v] = ld_stream(s + v);
+}
+
 Peers make_peers(void* const* ptrs, int world) {
     Peers P;
     for (int i = 0; i < kMaxPeers; ++i) P.p[i] = i < world ? ptrs[i] : nullptr;
@@ -263,5 +291,23 @@ MM_API int mm_p2p_rs(void* const* grad_ptrs, void* const* flag_ptrs, long long s
 
 MM_API int mm_p2p_wait_done(void* my_flags, int slot, unsigned seq, int world, int rank, int* status, cudaStream_t st) {
     p2p_wait_done_kernel<<<1, 32, 0, st>>>(my_flags, slot, seq, world, rank, status);
+    return (int)cudaGetLastError();
+}
+
+// src: [*, H] bf16 local; src_row / dst_rank / dst_row: int32 [n] on the device; buf_ptrs[p]: rank p's slab (peer-mapped).
+MM_API int mm_p2p_scatter_rows(const void* src, const int* src_row, const int* dst_rank, const int* dst_row,
+                               void* const* buf_ptrs, int n, int H, int world, cudaStream_t st) {
+    if (world > kMaxPeers || H % 8) return -1;
+    if (n == 0) return 0;
+    p2p_scatter_rows_kernel<<<(n + 7) / 8, 256, 0, st>>>((const uint4*)src, src_row, dst_rank, dst_row, make_peers(buf_ptrs, world),
+                                                         n, H / 8);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_p2p_gather_rows(void* out, const int* dst_rank, const int* dst_row, void* const* buf_ptrs, int n, int H,
+                              int world, cudaStream_t st) {
+    if (world > kMaxPeers || H % 8) return -1;
+    if (n == 0) return 0;
+    p2p_gather_rows_kernel<<<(n + 7) / 8, 256, 0, st>>>((uint4*)out, dst_rank, dst_row, make_peers(buf_ptrs, world), n, H / 8);
     return (int)cudaGetLastError();
 }

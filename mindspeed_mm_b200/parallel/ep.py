@@ -158,3 +158,145 @@ def load_balancing_loss(router_logits: torch.Tensor, topk_ids: torch.Tensor, num
     frac = torch.zeros(num_experts, device=p.device).index_add_(0, topk_ids.reshape(-1), torch.ones(topk_ids.numel(), device=p.device))
     frac = frac / topk_ids.numel() * k
     return num_experts * (frac / k * p.mean(0)).sum() * k
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Peer-memory dispatcher ("mc2" in the reference's naming: fused communication + expert GEMM input layout,
+# fsdp/ops/moe_ops/gemm_mc2.py, ep_dispatcher.py:319-397).  A token row travels once: straight from the sender's
+# activation tensor into its row of the destination rank's 128-aligned expert slab over NVLink, and the expert
+# outputs are pulled back the same way.  All-to-all, permute and the alignment padding are one pass.
+class P2PDispatcher:
+    """Symmetric-memory slabs + row maps for one EP group.  ``capacity_factor`` bounds the rows a rank can receive
+    (relative to a perfectly balanced routing); above it the caller falls back to the all-to-all dispatcher."""
+
+    _instances: dict = {}
+
+    @classmethod
+    def get(cls, group, hidden: int, device, pairs: int, e_local: int, capacity_factor: float = 2.0):
+        key = (id(group), hidden, str(device))
+        inst = cls._instances.get(key)
+        need = int(pairs * capacity_factor) + 128 * e_local
+        if inst is None or inst.cap_rows < need:
+            inst = cls._instances[key] = cls(group, hidden, device, need)
+        return inst
+
+    def __init__(self, group, hidden: int, device, cap_rows: int):
+        from ..comm.symm import SymmArena
+        self.group, self.H = group, hidden
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.cap_rows = (cap_rows + 127) // 128 * 128
+        nbytes = self.cap_rows * hidden * 2
+        self.arena = SymmArena(2 * nbytes + 8192, group, torch.device(device))
+        self.off_in, self.off_out = self.arena.carve(nbytes), self.arena.carve(nbytes)
+        self.buf_in = self.arena.view(self.off_in, self.cap_rows * hidden, torch.bfloat16).view(self.cap_rows, hidden)
+        self.buf_out = self.arena.view(self.off_out, self.cap_rows * hidden, torch.bfloat16).view(self.cap_rows, hidden)
+        self.ptrs_in, self.ptrs_out = self.arena.peer_ptrs(self.off_in), self.arena.peer_ptrs(self.off_out)
+
+    # -- kernels -------------------------------------------------------------------------------------------------
+    def push(self, src, src_row, dst_rank, dst_row, R: int, pad_rows):
+        """Rows of ``src`` -> peers' incoming slabs; returns this rank's slab [R, H] (pad rows zero)."""
+        from ..ops import native
+        self.arena.barrier()
+        native._check(native.lib().mm_p2p_scatter_rows(src.data_ptr(), src_row.data_ptr(), dst_rank.data_ptr(),
+                                                       dst_row.data_ptr(), self.ptrs_in, src_row.numel(), self.H,
+                                                       self.world, native._st()), "p2p_scatter_rows")
+        self.arena.barrier()
+        x = self.buf_in[:R].clone()
+        if pad_rows.numel():
+            x.index_fill_(0, pad_rows, 0)
+        return x
+
+    def pull(self, y, dst_rank, dst_row):
+        """Publishes ``y`` [R, H] as this rank's outgoing slab and fetches the rows (dst_rank, dst_row) from peers."""
+        from ..ops import native
+        n = dst_rank.numel()
+        out = torch.empty(n, self.H, dtype=torch.bfloat16, device=y.device)
+        self.buf_out[: y.shape[0]].copy_(y)
+        self.arena.barrier()
+        native._check(native.lib().mm_p2p_gather_rows(out.data_ptr(), dst_rank.data_ptr(), dst_row.data_ptr(), self.ptrs_out,
+                                                      n, self.H, self.world, native._st()), "p2p_gather_rows")
+        self.arena.barrier()
+        return out
+
+
+class _P2PPush(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tokens, disp, plan):
+        ctx.disp, ctx.plan = disp, plan
+        return disp.push(tokens.contiguous(), plan["pair_token"], plan["dst_rank"], plan["dst_row"], plan["R"], plan["pad_rows"])
+
+    @staticmethod
+    def backward(ctx, g):
+        plan = ctx.plan
+        pairs = ctx.disp.pull(g.contiguous(), plan["dst_rank"], plan["dst_row"])          # [T*k, H]
+        return pairs.view(plan["T"], plan["k"], -1).sum(1), None, None
+
+
+class _P2PPull(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, disp, plan):
+        ctx.disp, ctx.plan = disp, plan
+        return disp.pull(y.contiguous(), plan["dst_rank"], plan["dst_row"])
+
+    @staticmethod
+    def backward(ctx, g):
+        plan = ctx.plan
+        return ctx.disp.push(g.contiguous(), plan["pair_index"], plan["dst_rank"], plan["dst_row"], plan["R"],
+                             plan["pad_rows"]), None, None
+
+
+def p2p_plan(topk_ids: torch.Tensor, num_experts: int, group):
+    """Row maps of the peer-memory dispatch.  Returns (plan dict, max rows any rank receives)."""
+    ep, rank = dist.get_world_size(group), dist.get_rank(group)
+    e_local = num_experts // ep
+    T, k = topk_ids.shape
+    dev = topk_ids.device
+    flat = topk_ids.reshape(-1)
+    hist = torch.bincount(flat, minlength=num_experts)
+    allh = torch.empty(ep * num_experts, dtype=hist.dtype, device=dev)
+    dist.all_gather_into_tensor(allh, hist, group=group)
+    allh = allh.view(ep, num_experts)
+    tot = allh.sum(0)                                              # rows per global expert
+    padded = (tot + 127) // 128 * 128
+    per_rank = padded.view(ep, e_local)
+    off = torch.zeros(ep, e_local + 1, dtype=torch.int64, device=dev)
+    off[:, 1:] = per_rank.cumsum(1)                                # slab offsets on every destination rank
+    before_me = allh[:rank].sum(0)                                 # rows of earlier source ranks inside each expert's slab
+    start_me = off[:, :-1].reshape(-1) + before_me                 # [E]: first row of MY block in expert e's slab
+    order = torch.sort(flat, stable=True).indices
+    ustart = torch.zeros(num_experts + 1, dtype=torch.int64, device=dev)
+    ustart[1:] = hist.cumsum(0)
+    sorted_e = flat[order]
+    within = torch.empty_like(flat)
+    within[order] = torch.arange(flat.numel(), device=dev) - ustart[sorted_e]
+    my_off = off[rank]
+    my_tot = tot.view(ep, e_local)[rank]
+    # pad rows of my slabs: [off[e] + tot[e], off[e + 1])
+    R_all = off[:, -1]
+    R_max, R = int(R_all.max()), int(R_all[rank])                  # one host sync per layer, like the all-to-all splits
+    ar = torch.arange(R, device=dev)
+    e_of_row = torch.bucketize(ar, my_off[1:], right=True).clamp(max=e_local - 1)
+    pad_rows = ar[ar >= (my_off[:-1] + my_tot)[e_of_row]]
+    plan = dict(T=T, k=k, R=R, off=my_off.to(torch.int32), pad_rows=pad_rows,
+                dst_rank=(flat // e_local).to(torch.int32), dst_row=(start_me[flat] + within).to(torch.int32),
+                pair_token=(torch.arange(flat.numel(), device=dev) // k).to(torch.int32),
+                pair_index=torch.arange(flat.numel(), device=dev, dtype=torch.int32))
+    return plan, R_max
+
+
+def ep_forward_p2p(tokens, topk_ids, probs, gate_up, down, num_experts: int, group, capacity_factor: float = 2.0):
+    """Peer-memory dispatcher (GPU, bf16).  Falls back to the all-to-all dispatcher when a rank would receive more
+    rows than the slabs hold; every rank sees the same histogram, so all ranks take the same branch."""
+    from ..ops import native
+    T, k = topk_ids.shape
+    ep = dist.get_world_size(group)
+    e_local = num_experts // ep
+    disp = P2PDispatcher.get(group, tokens.shape[1], tokens.device, T * k, e_local, capacity_factor)
+    plan, R_max = p2p_plan(topk_ids, num_experts, group)
+    if R_max > disp.cap_rows:
+        return ep_forward_alltoall(tokens, topk_ids, probs, gate_up, down, num_experts, group)
+    x = _P2PPush.apply(tokens, disp, plan)
+    h = native._AlignedGroupedGemm.apply(x, gate_up, plan["off"])
+    y = native._AlignedGroupedGemm.apply(ops.swiglu(h), down, plan["off"])
+    pairs = _P2PPull.apply(y, disp, plan)
+    return native._AlignedUnpermute.apply(pairs, plan["pair_index"], probs)

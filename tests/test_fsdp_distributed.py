@@ -87,3 +87,10 @@ def test_hybrid_usp_and_fpdt_attention_gloo():
 
 def test_wan_fsdp_ulysses_matches_single_process_gloo():
     assert "ok=True" in _run_script(2, "dist_wan_check.py")
+
+
+@pytest.mark.gpu
+def test_moe_peer_memory_dispatcher_matches_alltoall():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    assert "ok=True" in _run_script(2, "dist_moe_p2p_check.py")

@@ -89,7 +89,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 // ============================================================================================== dQ
 constexpr int kSmemDq = 7 * kTile + 1024 + 1024;
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const BwdParams p) {
     if ((int)blockIdx.x >= *p.n_tiles) return;     // whole CTA leaves before any barrier or TMEM allocation
@@ -137,11 +137,11 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             mbar_init(&v_full[i], 1);
             mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1);
-            mbar_init(&s_empty[i], 128);
+            mbar_init(&s_empty[i], 256);
         }
         mbar_init(dp_full, 1);
-        mbar_init(dp_empty, 128);
-        mbar_init(ds_full, 128);
+        mbar_init(dp_empty, 256);
+        mbar_init(ds_full, 256);
         mbar_init(ds_empty, 1);
         mbar_init(dq_full, 1);
         *abort_flag = 0;
@@ -236,33 +236,33 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             if (!ok) atomicExch(p.status, MM_TIMEOUT_MMA);
         }
     } else {
+        // two warpgroups of 128 threads: both own all 128 query rows, each takes 64 of the 128 key columns of a tile
+        const int half = (warp - 2) >> 2;
         const int qd = warp & 3;
         const int row = qd * 32 + lane;
         const int qi = q0 + row;
         const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
-        const bool row_ok = live && qi < q_len;
+        const bool row_ok = qi < q_len;
         const size_t stat = (size_t)head * p.T + q_begin + min(qi, max(q_len - 1, 0));
-        const float lse2 = live && n_kv > 0 ? p.lse[stat] * kLog2e : 0.f;
-        const float dlt = live && n_kv > 0 ? p.delta[stat] : 0.f;
+        const float lse2 = n_kv > 0 ? p.lse[stat] * kLog2e : 0.f;
+        const float dlt = n_kv > 0 ? p.delta[stat] : 0.f;
         bool ok = true;
         for (int j = 0; j < n_kv; ++j) {
             const int st = j & 1;
             const uint32_t ph = (j >> 1) & 1;
             if (!mbar_wait(&s_full[st], ph, abort_flag)) { ok = false; break; }
             fence_after_sync();
-            uint32_t r[128];
-            const uint32_t t_row = tS + st * 128 + lane_off;
+            uint32_t r[64];
+            const uint32_t t_row = tS + st * 128 + half * 64 + lane_off;
             tmem_ld_32x32(t_row, r);
             tmem_ld_32x32(t_row + 32, r + 32);
-            tmem_ld_32x32(t_row + 64, r + 64);
-            tmem_ld_32x32(t_row + 96, r + 96);
             tmem_wait_ld();
             fence_before_sync();
             mbar_arrive(&s_empty[st]);
-            const int kbase = j * 128;
+            const int kbase = j * 128 + half * 64;
             const int limit = !row_ok ? -1 : (p.causal ? min(k_len - 1, qi + diag) : k_len - 1);
 #pragma unroll
-            for (int i = 0; i < 128; ++i) {
+            for (int i = 0; i < 64; ++i) {
                 const float pr = exp2f(__uint_as_float(r[i]) * p.scale_log2 - lse2);
                 r[i] = __float_as_uint(kbase + i > limit ? 0.f : pr);
             }
@@ -270,9 +270,9 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             fence_after_sync();
             if (j > 0 && !mbar_wait(ds_empty, (j - 1) & 1, abort_flag)) { ok = false; break; }
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t d[32];
-                tmem_ld_32x32(tdP + lane_off + c * 32, d);
+                tmem_ld_32x32(tdP + half * 64 + lane_off + c * 32, d);
                 tmem_wait_ld();
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
@@ -285,8 +285,8 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     w.y = pack2(f[2], f[3]);
                     w.z = pack2(f[4], f[5]);
                     w.w = pack2(f[6], f[7]);
-                    const int gg = c * 4 + g;      // 16-byte group of 8 keys: atom gg / 8, chunk gg % 8
-                    *reinterpret_cast<uint4*>(sdS + (gg >> 3) * kAtom + row * 128 + (((gg & 7) ^ (row & 7)) << 4)) = w;
+                    const int gg = c * 4 + g;      // 16-byte group of 8 keys inside this warpgroup's 64-key atom
+                    *reinterpret_cast<uint4*>(sdS + half * kAtom + row * 128 + ((gg ^ (row & 7)) << 4)) = w;
                 }
             }
             fence_before_sync();
@@ -294,13 +294,13 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             fence_proxy_async();
             mbar_arrive(ds_full);
         }
+        bf16* dst = p.dq + ((size_t)(q_begin + qi) * p.Nq + head) * HD + half * 64;
         if (ok && n_kv > 0 && mbar_wait(dq_full, 0, abort_flag)) {
             fence_after_sync();
-            bf16* dst = p.dq + ((size_t)(q_begin + qi) * p.Nq + head) * HD;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t d[32];
-                tmem_ld_32x32(tdQ + lane_off + c * 32, d);
+                tmem_ld_32x32(tdQ + half * 64 + lane_off + c * 32, d);
                 tmem_wait_ld();
                 if (row_ok) {
 #pragma unroll
@@ -314,9 +314,8 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     }
                 }
             }
-        } else if (live && n_kv == 0 && row_ok) {
-            bf16* dst = p.dq + ((size_t)(q_begin + qi) * p.Nq + head) * HD;
-            for (int g = 0; g < 16; ++g) reinterpret_cast<uint4*>(dst)[g] = make_uint4(0, 0, 0, 0);
+        } else if (n_kv == 0 && row_ok) {
+            for (int g = 0; g < 8; ++g) reinterpret_cast<uint4*>(dst)[g] = make_uint4(0, 0, 0, 0);
         }
         if (!ok && lane == 0) atomicExch(p.status, MM_TIMEOUT_EPI);
     }
@@ -338,7 +337,7 @@ constexpr int kQAtom = BQ2 * 128;          // 8 KiB
 constexpr int kPTile = 128 * BQ2 * 2;      // 16 KiB: P^T / dS^T, one swizzle atom of 128 rows
 constexpr int kSmemDkv = 2 * kTile + 4 * kQTile + 2 * kPTile + 2048 + 1024;
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const BwdParams p) {
     if ((int)blockIdx.x >= *p.n_tiles) return;
@@ -383,9 +382,9 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], 1);
             mbar_init(&st_full[i], 1);
-            mbar_init(&st_empty[i], 128);
+            mbar_init(&st_empty[i], 256);
         }
-        mbar_init(pds_full, 128);
+        mbar_init(pds_full, 256);
         mbar_init(pds_empty, 1);
         mbar_init(acc_full, 1);
         *abort_flag = 0;
@@ -470,49 +469,56 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (!ok) atomicExch(p.status, MM_TIMEOUT_MMA);
         }
     } else {
+        // two warpgroups of 128 threads: both own all 128 key rows, each takes 32 of the 64 query columns of a tile
+        const int half = (warp - 2) >> 2;
         const int qd = warp & 3;
         const int row = qd * 32 + lane;                  // key row inside the tile
-        const int tid = row;
+        const int tid2 = (warp - 2) * 32 + lane;         // 0..255
         const int kj = kv0 + row;                        // key index inside its sequence
         const bool row_ok = kj < k_len;
         const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
+        // per-column statistics (lse for threads 0..63, delta for 64..127) are fetched one tile ahead
+        auto load_stat = [&](int it) -> float {
+            if (tid2 >= 128) return 0.f;
+            const int head = kv_head * G + it / per_head;
+            const int qi = min((i_min + it % per_head) * BQ2 + (tid2 & 63), q_len - 1);
+            const size_t idx = (size_t)head * p.T + q_begin + qi;
+            return tid2 < 64 ? p.lse[idx] * kLog2e : p.delta[idx];
+        };
+        float pre = n_it > 0 ? load_stat(0) : 0.f;
         bool ok = true;
         for (int it = 0; it < n_it; ++it) {
             const int st = it & 1;
             const uint32_t ph = (it >> 1) & 1;
-            const int head = kv_head * G + it / per_head;
             const int qbase = (i_min + it % per_head) * BQ2;
-            {   // per-column statistics of this query tile
-                const int c = tid & 63;
-                const int qi = min(qbase + c, q_len - 1);
-                const size_t idx = (size_t)head * p.T + q_begin + qi;
-                if (tid < 64) s_lse[st * BQ2 + c] = p.lse[idx] * kLog2e;
-                else s_dlt[st * BQ2 + c] = p.delta[idx];
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (tid2 < 64) s_lse[st * BQ2 + tid2] = pre;
+            else if (tid2 < 128) s_dlt[st * BQ2 + tid2 - 64] = pre;
+            if (it + 1 < n_it) pre = load_stat(it + 1);
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             if (!mbar_wait(&st_full[st], ph, abort_flag)) { ok = false; break; }
             fence_after_sync();
-            uint32_t s[64], d[64];
-            tmem_ld_32x32(tST + st * BQ2 + lane_off, s);
-            tmem_ld_32x32(tST + st * BQ2 + lane_off + 32, s + 32);
-            tmem_ld_32x32(tdPT + st * BQ2 + lane_off, d);
-            tmem_ld_32x32(tdPT + st * BQ2 + lane_off + 32, d + 32);
+            uint32_t s[32], d[32];
+            tmem_ld_32x32(tST + st * BQ2 + half * 32 + lane_off, s);
+            tmem_ld_32x32(tdPT + st * BQ2 + half * 32 + lane_off, d);
             tmem_wait_ld();
             fence_before_sync();
             mbar_arrive(&st_empty[st]);
             // visible query columns for this key: qi < q_len and (not causal or kj <= qi + diag)
             const int c_lo = !row_ok ? BQ2 : (p.causal ? max(0, kj - diag - qbase) : 0);
             const int c_hi = min(BQ2, q_len - qbase);
+            const float* ls = s_lse + st * BQ2 + half * 32;
+            const float* dl = s_dlt + st * BQ2 + half * 32;
 #pragma unroll
-            for (int c = 0; c < BQ2; ++c) {
-                const float pr = exp2f(__uint_as_float(s[c]) * p.scale_log2 - s_lse[st * BQ2 + c]);
-                const float pv = (c >= c_lo && c < c_hi) ? pr : 0.f;
+            for (int c = 0; c < 32; ++c) {
+                const int cc = half * 32 + c;
+                const float pr = exp2f(__uint_as_float(s[c]) * p.scale_log2 - ls[c]);
+                const float pv = (cc >= c_lo && cc < c_hi) ? pr : 0.f;
                 s[c] = __float_as_uint(pv);
-                d[c] = __float_as_uint(pv * (__uint_as_float(d[c]) - s_dlt[st * BQ2 + c]));
+                d[c] = __float_as_uint(pv * (__uint_as_float(d[c]) - dl[c]));
             }
             if (it > 0 && !mbar_wait(pds_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
+            for (int g = 0; g < 4; ++g) {
                 uint4 w, x;
                 w.x = pack2(__uint_as_float(s[8 * g + 0]), __uint_as_float(s[8 * g + 1]));
                 w.y = pack2(__uint_as_float(s[8 * g + 2]), __uint_as_float(s[8 * g + 3]));
@@ -522,22 +528,22 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 x.y = pack2(__uint_as_float(d[8 * g + 2]), __uint_as_float(d[8 * g + 3]));
                 x.z = pack2(__uint_as_float(d[8 * g + 4]), __uint_as_float(d[8 * g + 5]));
                 x.w = pack2(__uint_as_float(d[8 * g + 6]), __uint_as_float(d[8 * g + 7]));
-                const int off = row * 128 + ((g ^ (row & 7)) << 4);
+                const int off = row * 128 + (((half * 4 + g) ^ (row & 7)) << 4);
                 *reinterpret_cast<uint4*>(sP + off) = w;
                 *reinterpret_cast<uint4*>(sdS + off) = x;
             }
             fence_proxy_async();
             mbar_arrive(pds_full);
         }
-        bf16* dvp = p.dv + ((size_t)(k_begin + kj) * p.Nkv + kv_head) * HD;
-        bf16* dkp = p.dk + ((size_t)(k_begin + kj) * p.Nkv + kv_head) * HD;
+        bf16* dvp = p.dv + ((size_t)(k_begin + kj) * p.Nkv + kv_head) * HD + half * 64;
+        bf16* dkp = p.dk + ((size_t)(k_begin + kj) * p.Nkv + kv_head) * HD + half * 64;
         if (ok && n_it > 0 && mbar_wait(acc_full, 0, abort_flag)) {
             fence_after_sync();
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t a[32], b[32];
-                tmem_ld_32x32(tdV + lane_off + c * 32, a);
-                tmem_ld_32x32(tdK + lane_off + c * 32, b);
+                tmem_ld_32x32(tdV + half * 64 + lane_off + c * 32, a);
+                tmem_ld_32x32(tdK + half * 64 + lane_off + c * 32, b);
                 tmem_wait_ld();
                 if (row_ok) {
 #pragma unroll
@@ -557,7 +563,7 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 }
             }
         } else if (n_it == 0 && row_ok) {
-            for (int g = 0; g < 16; ++g) {
+            for (int g = 0; g < 8; ++g) {
                 reinterpret_cast<uint4*>(dvp)[g] = make_uint4(0, 0, 0, 0);
                 reinterpret_cast<uint4*>(dkp)[g] = make_uint4(0, 0, 0, 0);
             }
@@ -613,11 +619,11 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
     if (cudaFuncSetAttribute(fmha_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkv) != cudaSuccess) return -3;
     BwdParams p{cu_q, cu_k, q_seq, q_r0, q_n, lse, delta, (bf16*)dq, (bf16*)dk, (bf16*)dv, T, Tk, Nq, Nkv, causal, scale,
                 scale * kLog2e, status};
-    fmha_bwd_dq_kernel<<<dim3(mq, Nq), 192, kSmemDq, st>>>(tQ, tK, tV, tdO, p);
+    fmha_bwd_dq_kernel<<<dim3(mq, Nq), 320, kSmemDq, st>>>(tQ, tK, tV, tdO, p);
     BwdParams pk = p;
     pk.tile_seq = k_seq;
     pk.tile_r0 = k_r0;
     pk.n_tiles = k_n;
-    fmha_bwd_dkv_kernel<<<dim3(mk, Nkv), 192, kSmemDkv, st>>>(tQ64, tK, tV, tdO64, pk);
+    fmha_bwd_dkv_kernel<<<dim3(mk, Nkv), 320, kSmemDkv, st>>>(tQ64, tK, tV, tdO64, pk);
     return (int)cudaGetLastError();
 }

@@ -48,7 +48,7 @@ class TPPlan(_Base):
 
 class EPPlan(_Base):
     apply_modules: List[str] = Field(default_factory=list)
-    dispatcher: Literal["alltoall", "allgather", "mc2", "fused"] = "alltoall"
+    dispatcher: Literal["alltoall", "allgather", "mc2", "p2p", "fused"] = "alltoall"
     apply_efsdp_modules: List[str] = Field(default_factory=list)
     use_npu_fused_ops: bool = True          # accepted for recipe compatibility; ignored
 

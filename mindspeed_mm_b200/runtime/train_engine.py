@@ -74,7 +74,12 @@ class TrainEngine:
             loss = self.loss_fn(loss_sum, n_valid)
         else:
             loss, n_valid = out, None
-        loss.backward()
+        total = loss
+        aux_fn = getattr(self.model, "aux_loss", None)          # MoE router load-balancing term
+        aux = aux_fn() if callable(aux_fn) else None
+        if aux is not None:
+            total = loss + aux.to(loss.dtype)
+        total.backward()
         self.engine.end_micro_step()
         return dict(loss=loss.detach(), n_valid=n_valid)
 

@@ -82,6 +82,10 @@ class Trainer:
         m = self.args.model
         cls = registry.model_register.get(m.model_id)
         cfg = self._model_config(cls, m)
+        text = getattr(cfg, "text", None)
+        if text is not None and hasattr(text, "ep_dispatcher"):
+            d = self.args.parallel.ep_plan.dispatcher
+            text.ep_dispatcher = "p2p" if d in ("mc2", "fused") else d
         with torch.device("meta"):
             model = cls(cfg)
         names = [n for n, _ in model.named_modules()]
@@ -117,12 +121,24 @@ class Trainer:
                             "the remaining units are sharded as well (every parameter must live in one unit)")
         recompute = a.features.recompute or a.parallel.recompute
         group = self.ps.get_fsdp_group() if self.world > 1 else False
-        return FSDPEngine(units, group=group, device=self.device, param_dtype=get_dtype(plan.param_dtype or "bf16")
-                          if self.device.type == "cuda" else torch.float32,
-                          reduce_dtype=get_dtype(plan.reduce_dtype or "fp32"), opt=opt, recompute=recompute,
-                          grad_accum_steps=t.gradient_accumulation_steps or 1,
-                          prefetch=max(plan.num_to_forward_prefetch or 0, plan.num_to_backward_prefetch or 0),
-                          comm=plan.comm)
+        common = dict(device=self.device, param_dtype=get_dtype(plan.param_dtype or "bf16")
+                      if self.device.type == "cuda" else torch.float32,
+                      reduce_dtype=get_dtype(plan.reduce_dtype or "fp32"), opt=opt,
+                      grad_accum_steps=t.gradient_accumulation_steps or 1)
+        prefetch = max(plan.num_to_forward_prefetch or 0, plan.num_to_backward_prefetch or 0)
+        expert_units = self.model.expert_units() if hasattr(self.model, "expert_units") else []
+        if not expert_units:
+            return FSDPEngine(units, group=group, recompute=recompute, prefetch=prefetch, comm=plan.comm, **common)
+        # MoE: dense parameters over the FSDP group; expert parameters over the expert-FSDP group (size 1 when
+        # ep == ranks per stage), their gradients divided by the full data-parallel size.
+        from ..parallel.fsdp import EngineMux
+        ex = [p for _, m in expert_units for p in m.parameters()]
+        dense = FSDPEngine(units, group=group, recompute=recompute, prefetch=prefetch, comm=plan.comm, exclude_params=ex,
+                           **common)
+        eg = self.ps.group("efsdp") if self.ps.size("efsdp") > 1 else False
+        expert = FSDPEngine(expert_units, group=eg, grad_divide=self.ps.get_dp_world_size(), no_recompute=(),
+                            comm="nccl", **common)
+        return EngineMux(dense, expert)
 
     def load_weights(self):
         t = self.args.training

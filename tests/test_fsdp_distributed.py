@@ -94,3 +94,15 @@ def test_moe_peer_memory_dispatcher_matches_alltoall():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     assert "ok=True" in _run_script(2, "dist_moe_p2p_check.py")
+
+
+def test_native_trainer_moe_recipe_with_expert_parallel_gloo():
+    """examples/qwen3vl/tiny_moe_native.yaml end to end: dense engine + expert engine (EngineMux), EP = 2."""
+    root = os.path.dirname(HERE)
+    port = 29300 + (os.getpid() % 300)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), "-m", "mindspeed_mm_b200.runtime.trainer",
+           os.path.join(root, "examples", "qwen3vl", "tiny_moe_native.yaml")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=root, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "iteration        3/       3" in r.stdout + r.stderr

@@ -41,6 +41,7 @@ struct BwdParams {
     int T, Tk, Nq, Nkv, causal;
     float scale, scale_log2;
     int* status;
+    int split;              // dK/dV kernel: 1 = one CTA per QUERY head writing partial dk / dv [Tk, Nq, 128]
 };
 
 // delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (t, h)
@@ -366,8 +367,11 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seq = p.tile_seq[blockIdx.x];
     const int kv0 = p.tile_r0[blockIdx.x];
-    const int kv_head = blockIdx.y;
-    const int G = p.Nq / p.Nkv;
+    const int Gfull = p.Nq / p.Nkv;
+    const int kv_head = p.split ? blockIdx.y / Gfull : blockIdx.y;
+    const int head0 = p.split ? blockIdx.y : kv_head * Gfull;     // first query head this CTA walks
+    const int G = p.split ? 1 : Gfull;                              // ... and how many
+    const int out_heads = p.split ? p.Nq : p.Nkv, out_head = blockIdx.y;
     const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
     const int k_begin = p.cu_k[seq], k_len = p.cu_k[seq + 1] - k_begin;
     const int diag = k_len - q_len;
@@ -414,7 +418,7 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             for (int it = 0; it < n_it; ++it) {
                 const int st = it & 1;
                 const uint32_t ph = (it >> 1) & 1;
-                const int head = kv_head * G + it / per_head;
+                const int head = head0 + it / per_head;
                 const int row = q_begin + (i_min + it % per_head) * BQ2;
                 if (!mbar_wait(&empty[st], ph ^ 1, abort_flag)) { atomicExch(p.status, MM_TIMEOUT_TMA); break; }
                 mbar_expect_tx(&full[st], 2 * kQTile);
@@ -480,7 +484,7 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // per-column statistics (lse for threads 0..63, delta for 64..127) are fetched one tile ahead
         auto load_stat = [&](int it) -> float {
             if (tid2 >= 128) return 0.f;
-            const int head = kv_head * G + it / per_head;
+            const int head = head0 + it / per_head;
             const int qi = min((i_min + it % per_head) * BQ2 + (tid2 & 63), q_len - 1);
             const size_t idx = (size_t)head * p.T + q_begin + qi;
             return tid2 < 64 ? p.lse[idx] * kLog2e : p.delta[idx];
@@ -535,8 +539,8 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             fence_proxy_async();
             mbar_arrive(pds_full);
         }
-        bf16* dvp = p.dv + ((size_t)(k_begin + kj) * p.Nkv + kv_head) * HD + half * 64;
-        bf16* dkp = p.dk + ((size_t)(k_begin + kj) * p.Nkv + kv_head) * HD + half * 64;
+        bf16* dvp = p.dv + ((size_t)(k_begin + kj) * out_heads + out_head) * HD + half * 64;
+        bf16* dkp = p.dk + ((size_t)(k_begin + kj) * out_heads + out_head) * HD + half * 64;
         if (ok && n_it > 0 && mbar_wait(acc_full, 0, abort_flag)) {
             fence_after_sync();
 #pragma unroll
@@ -587,11 +591,12 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 MM_API int mm_fmha_bwd_max_tiles(int T, int n_seqs) { return T / 128 + n_seqs + 1; }
 
 // q, dO, o: [T, Nq, 128]; k, v: [Tk, Nkv, 128] (token strides q_ts / k_ts / v_ts elements, heads dense; dO and o dense);
-// lse: [Nq, T] fp32 from the forward; outputs dq [T, Nq, 128], dk / dv [Tk, Nkv, 128] dense bf16.
+// lse: [Nq, T] fp32 from the forward; outputs dq [T, Nq, 128], dk / dv [Tk, Nkv, 128] dense bf16
+// (split_heads = 1: dk / dv are per-query-head partials [Tk, Nq, 128] that the caller sums over each GQA group).
 MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
                        float* delta, void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, int* plan, int T, int Tk,
                        int n_seqs, int Nq, int Nkv, int D, long long q_ts, long long k_ts, long long v_ts, int causal,
-                       float scale, int* status, cudaStream_t st) {
+                       float scale, int split_heads, int* status, cudaStream_t st) {
     if (D != HD || Nq % Nkv || (q_ts | k_ts | v_ts) % 8) return -1;
     if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o | (uintptr_t)dO | (uintptr_t)dq | (uintptr_t)dk |
          (uintptr_t)dv) & 15)
@@ -618,12 +623,12 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
     if (cudaFuncSetAttribute(fmha_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDq) != cudaSuccess) return -3;
     if (cudaFuncSetAttribute(fmha_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkv) != cudaSuccess) return -3;
     BwdParams p{cu_q, cu_k, q_seq, q_r0, q_n, lse, delta, (bf16*)dq, (bf16*)dk, (bf16*)dv, T, Tk, Nq, Nkv, causal, scale,
-                scale * kLog2e, status};
+                scale * kLog2e, status, split_heads};
     fmha_bwd_dq_kernel<<<dim3(mq, Nq), 320, kSmemDq, st>>>(tQ, tK, tV, tdO, p);
     BwdParams pk = p;
     pk.tile_seq = k_seq;
     pk.tile_r0 = k_r0;
     pk.n_tiles = k_n;
-    fmha_bwd_dkv_kernel<<<dim3(mk, Nkv), 320, kSmemDkv, st>>>(tQ64, tK, tV, tdO64, pk);
+    fmha_bwd_dkv_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkv, st>>>(tQ64, tK, tV, tdO64, pk);
     return (int)cudaGetLastError();
 }

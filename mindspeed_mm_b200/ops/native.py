@@ -53,7 +53,7 @@ def _declare(L):
         "mm_fmha_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _f, _p, _p],
         "mm_fmha_bwd_max_tiles": [_i, _i],
         "mm_fmha_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _f,
-                        _p, _p],
+                        _i, _p, _p],
         "mm_grouped_gemm_max_tiles": [_i, _i, _i, _i, _i],
         "mm_grouped_gemm_bf16": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p],
         "mm_moe_permute": [_p, _p, _p, _i, _i, _p],
@@ -466,8 +466,10 @@ def fmha_backward(do, q, k, v, out, lse, cu_q, cu_k, causal, scale):
     n_seqs = cu_q.numel() - 1
     dev = q.device
     dq = torch.empty(T, Nq, D, dtype=q.dtype, device=dev)
-    dk = torch.empty(Tk, Nkv, D, dtype=q.dtype, device=dev)
-    dv = torch.empty(Tk, Nkv, D, dtype=q.dtype, device=dev)
+    # GQA: one dK/dV CTA per QUERY head (more, shorter CTAs); the group's partials are summed afterwards
+    split = Nq != Nkv
+    dk = torch.empty(Tk, Nq if split else Nkv, D, dtype=q.dtype, device=dev)
+    dv = torch.empty(Tk, Nq if split else Nkv, D, dtype=q.dtype, device=dev)
     delta = torch.empty(Nq, T, dtype=torch.float32, device=dev)
     L = lib()
     plan = torch.empty(2 * (L.mm_fmha_bwd_max_tiles(T, n_seqs) + L.mm_fmha_bwd_max_tiles(Tk, n_seqs)) + 2,
@@ -476,10 +478,14 @@ def fmha_backward(do, q, k, v, out, lse, cu_q, cu_k, causal, scale):
     rc = L.mm_fmha_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), do.data_ptr(), lse.data_ptr(),
                        delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu_q.data_ptr(), cu_k.data_ptr(),
                        plan.data_ptr(), T, Tk, n_seqs, Nq, Nkv, D, q.stride(0), k.stride(0), v.stride(0), int(causal),
-                       float(scale), status_word(dev).data_ptr(), _st())
+                       float(scale), int(split), status_word(dev).data_ptr(), _st())
     _check(rc, "fmha_bwd")
     global LAUNCHES
     LAUNCHES += 4
+    if split:
+        G = Nq // Nkv
+        dk = dk.view(Tk, Nkv, G, D).float().sum(2).to(q.dtype)
+        dv = dv.view(Tk, Nkv, G, D).float().sum(2).to(q.dtype)
     return dq, dk, dv
 
 

@@ -250,6 +250,22 @@ __global__ void __launch_bounds__(256) p2p_gather_rows_kernel(uint4* __restrict_
     for (int v = lane; v < row_vec; v += 32) d[v] = ld_stream(s + v);
 }
 
+// ------------------------------------------------------------------------------------------ plain peer copy
+// dst <- src for `n_vec` 16-byte vectors; either side may be a peer-mapped address (pull or push).  Used by ring
+// attention to bring the next K/V block into local memory while the current block is being computed.
+__global__ void __launch_bounds__(256) p2p_copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, long long n_vec) {
+    const long long stride = (long long)gridDim.x * blockDim.x * 4;
+    for (long long i = (long long)blockIdx.x * blockDim.x * 4 + threadIdx.x; i < n_vec; i += stride) {
+        uint4 r[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (i + u * 256 < n_vec) r[u] = ld_stream(src + i + u * 256);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (i + u * 256 < n_vec) dst[i + u * 256] = r[u];
+    }
+}
+
 Peers make_peers(void* const* ptrs, int world) {
     Peers P;
     for (int i = 0; i < kMaxPeers; ++i) P.p[i] = i < world ? ptrs[i] : nullptr;
@@ -309,5 +325,12 @@ MM_API int mm_p2p_gather_rows(void* out, const int* dst_rank, const int* dst_row
     if (world > kMaxPeers || H % 8) return -1;
     if (n == 0) return 0;
     p2p_gather_rows_kernel<<<(n + 7) / 8, 256, 0, st>>>((uint4*)out, dst_rank, dst_row, make_peers(buf_ptrs, world), n, H / 8);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_p2p_copy(void* dst, const void* src, long long nbytes, int ctas, cudaStream_t st) {
+    if (nbytes % 16 || ((uintptr_t)dst | (uintptr_t)src) & 15) return -1;
+    if (nbytes == 0) return 0;
+    p2p_copy_kernel<<<ctas, 256, 0, st>>>((uint4*)dst, (const uint4*)src, nbytes / 16);
     return (int)cudaGetLastError();
 }

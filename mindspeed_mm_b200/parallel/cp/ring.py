@@ -59,7 +59,23 @@ def _block_bwd_ref(do, q, k, v, o, lse, scale, causal):
     return dq.transpose(1, 2), dk.transpose(1, 2), dv.transpose(1, 2)
 
 
+def _native_ok(q, k):
+    from ... import ops
+    return ops.get_tier() == "native" and q.dtype == torch.bfloat16 and q.shape[-1] == 128 and k.shape[-1] == 128
+
+
+def _cu(B, S, device):
+    return torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=device)
+
+
 def _block_fwd(q, k, v, scale, causal):
+    if q.is_cuda and _native_ok(q, k):
+        from ...ops import native
+        B, Sq, N, D = q.shape
+        Sk = k.shape[1]
+        o, lse = native.fmha_forward(q.reshape(B * Sq, N, D), k.reshape(B * Sk, -1, D), v.reshape(B * Sk, -1, D),
+                                     _cu(B, Sq, q.device), _cu(B, Sk, q.device), causal, scale)
+        return o.view(B, Sq, N, D).float(), lse.view(N, B, Sq).transpose(0, 1)
     if q.is_cuda:
         from flash_attn.flash_attn_interface import _flash_attn_forward
         out = _flash_attn_forward(q, k, v, 0.0, scale, causal=causal, window_size_left=-1, window_size_right=-1,
@@ -69,6 +85,16 @@ def _block_fwd(q, k, v, scale, causal):
 
 
 def _block_bwd(do, q, k, v, o, lse, scale, causal):
+    if q.is_cuda and _native_ok(q, k):
+        from ...ops import native
+        B, Sq, N, D = q.shape
+        Sk = k.shape[1]
+        dq, dk, dv = native.fmha_backward(do.to(q.dtype).reshape(B * Sq, N, D), q.reshape(B * Sq, N, D),
+                                          k.reshape(B * Sk, -1, D), v.reshape(B * Sk, -1, D),
+                                          o.to(q.dtype).reshape(B * Sq, N, D),
+                                          lse.transpose(0, 1).reshape(N, B * Sq).contiguous(), _cu(B, Sq, q.device),
+                                          _cu(B, Sk, q.device), causal, scale)
+        return dq.view(B, Sq, N, D).float(), dk.view(B, Sk, -1, D).float(), dv.view(B, Sk, -1, D).float()
     if q.is_cuda:
         from flash_attn.flash_attn_interface import _flash_attn_backward
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
@@ -114,6 +140,83 @@ class RingP2P:
         self._reqs = []
 
 
+class PeerRing:
+    """Ring transport over NVLink peer memory: every rank publishes its K/V block in a symmetric-memory arena; the
+    block needed at the next step is pulled into a local double buffer by a copy kernel on a side stream while the
+    current block is being computed, and gradient contributions are pushed straight into a per-writer slot of the
+    owner's arena (summed by the owner after one barrier).  No send / recv pairs, no NCCL."""
+
+    _cache: dict = {}
+
+    @classmethod
+    def get(cls, group, shape, dtype, device):
+        key = (id(group), tuple(shape), dtype, str(device))
+        inst = cls._cache.get(key)
+        if inst is None:
+            if len(cls._cache) > 4:
+                cls._cache.clear()
+            inst = cls._cache[key] = cls(group, shape, dtype, device)
+        return inst
+
+    def __init__(self, group, shape, dtype, device):
+        from ...comm.symm import SymmArena
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.shape, self.dtype = tuple(shape), dtype
+        n = 1
+        for d in shape:
+            n *= d
+        self.nbytes = n * torch.empty(0, dtype=dtype).element_size()
+        self.arena = SymmArena((1 + self.world) * self.nbytes + 8192, group, torch.device(device))
+        self.kv_off = self.arena.carve(self.nbytes)
+        self.slot_off = [self.arena.carve(self.nbytes) for _ in range(self.world)]
+        self.kv = self.arena.view(self.kv_off, n, dtype).view(shape)
+        self.slots = [self.arena.view(o, n, dtype).view(shape) for o in self.slot_off]
+        self.local = [torch.empty(shape, dtype=dtype, device=device) for _ in range(2)]
+        self.side = torch.cuda.Stream(device)
+
+    def publish(self, kv):
+        self.arena.barrier()            # nobody still reads the previous contents
+        self.kv.copy_(kv)
+        self.arena.barrier()
+
+    def _copy(self, dst_ptr, src_ptr, stream):
+        from ...ops import native
+        native._check(native.lib().mm_p2p_copy(dst_ptr, src_ptr, self.nbytes, 64, stream.cuda_stream), "p2p_copy")
+
+    def fetch_async(self, src_rank: int, buf: int) -> torch.Tensor:
+        """Start pulling rank ``src_rank``'s published block into local buffer ``buf`` on the side stream."""
+        self.side.wait_stream(torch.cuda.current_stream())
+        self._copy(self.local[buf].data_ptr(), self.arena.peer_base[src_rank] + self.kv_off, self.side)
+        return self.local[buf]
+
+    def wait(self):
+        torch.cuda.current_stream().wait_stream(self.side)
+
+    def push_grad_async(self, owner: int, dkv: torch.Tensor):
+        """Write this rank's gradient contribution for ``owner``'s block into slot[self.rank] of the owner's arena."""
+        dkv = dkv.to(self.dtype).contiguous()
+        self.side.wait_stream(torch.cuda.current_stream())
+        dkv.record_stream(self.side)
+        self._copy(self.arena.peer_base[owner] + self.slot_off[self.rank], dkv.data_ptr(), self.side)
+
+    def reduce_grads(self, own: torch.Tensor, writers) -> torch.Tensor:
+        self.wait()
+        self.arena.barrier()            # every contribution has landed
+        total = own.float()
+        for w in writers:
+            total = total + self.slots[w].float()
+        return total
+
+
+def _peer_ring_enabled(q) -> bool:
+    import os
+    if not q.is_cuda or os.environ.get("MM_B200_RING", "peer") != "peer":
+        return False
+    from ... import ops
+    return ops.get_tier() == "native"
+
+
 def _step_plan(causal: bool, rank: int, src: int):
     """(q slice, kv slice, causal flag) for the block from ``src``: slices are 'all', 'first', 'second' or None."""
     if not causal:
@@ -135,14 +238,20 @@ def _half(x, which, dim=1):
 class _RingAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, group, causal, scale):
-        ring = RingP2P(group)
+        peer = _peer_ring_enabled(q)
+        kv = torch.stack([k, v]).contiguous()
+        ring = PeerRing.get(group, kv.shape, kv.dtype, q.device) if peer else RingP2P(group)
         P, r = ring.world, ring.rank
         B, S, N, D = q.shape
         out = torch.zeros(B, S, N, v.shape[-1], dtype=torch.float32, device=q.device)
         lse = torch.full((B, N, S), float("-inf"), dtype=torch.float32, device=q.device)
-        kv = torch.stack([k, v]).contiguous()
+        if peer:
+            ring.publish(kv)
         for s in range(P):
-            nxt = ring.exchange(kv) if s < P - 1 else None
+            if peer:
+                nxt = ring.fetch_async((r - s - 1) % P, (s + 1) & 1) if s < P - 1 else None
+            else:
+                nxt = ring.exchange(kv) if s < P - 1 else None
             src = (r - s) % P
             qs, ks, c = _step_plan(causal, r, src)
             qb = _half(q, qs)
@@ -165,6 +274,8 @@ class _RingAttention(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do):
         q, k, v, out, lse = ctx.saved_tensors
+        if _peer_ring_enabled(q):
+            return _ring_backward_peer(ctx, do, q, k, v, out, lse)
         ring = RingP2P(ctx.group)
         P, r = ring.world, ring.rank
         S = q.shape[1]
@@ -192,6 +303,43 @@ class _RingAttention(torch.autograd.Function):
             ring.wait()
             kv, dkv = both[:2].to(k.dtype), both[2:]
         return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None, None
+
+
+def _ring_backward_peer(ctx, do, q, k, v, out, lse):
+    """Backward over peer memory: blocks are pulled like in the forward; each rank pushes its dK / dV contribution
+    for a remote block into the owner's arena and the owner sums the P - 1 slots after one barrier."""
+    kv = torch.stack([k, v]).contiguous()
+    ring = PeerRing.get(ctx.group, kv.shape, kv.dtype, q.device)
+    P, r = ring.world, ring.rank
+    S = q.shape[1]
+    dq = torch.zeros_like(q, dtype=torch.float32)
+    own = torch.zeros_like(kv, dtype=torch.float32)
+    ring.publish(kv)
+    cur = kv
+    for s in range(P):
+        nxt = ring.fetch_async((r - s - 1) % P, (s + 1) & 1) if s < P - 1 else None
+        src = (r - s) % P
+        qs, ks, c = _step_plan(ctx.causal, r, src)
+        sl = slice(None) if qs == "all" else slice(S // 2, None)
+        dqb, dkb, dvb = _block_bwd(do[:, sl].contiguous(), q[:, sl].contiguous(), _half(cur[0], ks).contiguous(),
+                                   _half(cur[1], ks).contiguous(), out[:, sl].contiguous(), lse[..., sl].contiguous(),
+                                   ctx.scale, c)
+        dq[:, sl] += dqb
+        contrib = own if src == r else torch.zeros_like(kv, dtype=torch.float32)
+        if ks == "all":
+            contrib[0] += dkb
+            contrib[1] += dvb
+        else:
+            h = kv.shape[2] // 2
+            contrib[0][:, :h] += dkb
+            contrib[1][:, :h] += dvb
+        if src != r:
+            ring.push_grad_async(src, contrib)
+        if nxt is not None:
+            ring.wait()
+            cur = nxt
+    total = ring.reduce_grads(own, [w for w in range(P) if w != r])
+    return dq.to(q.dtype), total[0].to(k.dtype), total[1].to(v.dtype), None, None, None
 
 
 def ring_attention(q, k, v, group, causal: bool = False, softmax_scale: Optional[float] = None):

@@ -106,3 +106,11 @@ def test_native_trainer_moe_recipe_with_expert_parallel_gloo():
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=root, env=dict(os.environ, OMP_NUM_THREADS="1"))
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "iteration        3/       3" in r.stdout + r.stderr
+
+
+@pytest.mark.gpu
+def test_ring_attention_over_peer_memory_2gpu():
+    """Ring attention with K/V blocks pulled over NVLink peer memory and tcgen05 block kernels (forward + backward)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    assert "ok=True" in _run_script(2, "dist_cp_check.py", "--cuda")

@@ -585,6 +585,8 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
 }
 
+#include "fmha_bwd_pp.cuh"
+
 }  // namespace
 
 // Scratch: plan = 2 * (2 * max_tiles + 1) ints with max_tiles = mm_fmha_bwd_max_tiles; delta = Nq * T floats.
@@ -596,7 +598,7 @@ MM_API int mm_fmha_bwd_max_tiles(int T, int n_seqs) { return T / 128 + n_seqs + 
 MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
                        float* delta, void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, int* plan, int T, int Tk,
                        int n_seqs, int Nq, int Nkv, int D, long long q_ts, long long k_ts, long long v_ts, int causal,
-                       float scale, int split_heads, int* status, cudaStream_t st) {
+                       float scale, int split_heads, int variant, int* status, cudaStream_t st) {
     if (D != HD || Nq % Nkv || (q_ts | k_ts | v_ts) % 8) return -1;
     if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o | (uintptr_t)dO | (uintptr_t)dq | (uintptr_t)dk |
          (uintptr_t)dv) & 15)
@@ -624,11 +626,22 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
     if (cudaFuncSetAttribute(fmha_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkv) != cudaSuccess) return -3;
     BwdParams p{cu_q, cu_k, q_seq, q_r0, q_n, lse, delta, (bf16*)dq, (bf16*)dk, (bf16*)dv, T, Tk, Nq, Nkv, causal, scale,
                 scale * kLog2e, status, split_heads};
-    fmha_bwd_dq_kernel<<<dim3(mq, Nq), 320, kSmemDq, st>>>(tQ, tK, tV, tdO, p);
     BwdParams pk = p;
     pk.tile_seq = k_seq;
     pk.tile_r0 = k_r0;
     pk.n_tiles = k_n;
+    if (variant == 1) {      // ping-pong schedule: 64-wide inner tiles, deeper rings, one warpgroup per in-flight tile
+        CUtensorMap tK64, tV64;
+        if ((r = make_tmap_3d(&tK64, k, HD, Nkv, Tk, HD, k_ts, 64, 1, BK))) return 7000 + r;
+        if ((r = make_tmap_3d(&tV64, v, HD, Nkv, Tk, HD, v_ts, 64, 1, BK))) return 8000 + r;
+        if (cudaFuncSetAttribute(fmha_bwd_dq_pp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDqPP) != cudaSuccess ||
+            cudaFuncSetAttribute(fmha_bwd_dkv_pp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkvPP) != cudaSuccess)
+            return -3;
+        fmha_bwd_dq_pp_kernel<<<dim3(mq, Nq), 320, kSmemDqPP, st>>>(tQ, tK64, tV64, tdO, p);
+        fmha_bwd_dkv_pp_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkvPP, st>>>(tQ64, tK, tV, tdO64, pk);
+        return (int)cudaGetLastError();
+    }
+    fmha_bwd_dq_kernel<<<dim3(mq, Nq), 320, kSmemDq, st>>>(tQ, tK, tV, tdO, p);
     fmha_bwd_dkv_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkv, st>>>(tQ64, tK, tV, tdO64, pk);
     return (int)cudaGetLastError();
 }

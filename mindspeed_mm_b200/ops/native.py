@@ -53,7 +53,7 @@ def _declare(L):
         "mm_fmha_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _f, _p, _p],
         "mm_fmha_bwd_max_tiles": [_i, _i],
         "mm_fmha_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _f,
-                        _i, _p, _p],
+                        _i, _i, _p, _p],
         "mm_grouped_gemm_max_tiles": [_i, _i, _i, _i, _i],
         "mm_grouped_gemm_bf16": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p],
         "mm_moe_permute": [_p, _p, _p, _i, _i, _p],
@@ -455,6 +455,8 @@ def fmha_forward(q, k, v, cu_q, cu_k, causal, scale):
     return out, lse
 
 
+# 0: both warpgroups share a 128-wide tile (faster as measured); 1: ping-pong schedule over 64-wide tiles
+FMHA_BWD_VARIANT = int(os.environ.get("MM_B200_FMHA_BWD_VARIANT", "0"))
 FMHA_BWD = os.environ.get("MM_B200_FMHA_BWD", "native")     # "native" (tcgen05 kernels) or "flash" (flash-attn library)
 
 
@@ -479,7 +481,7 @@ def fmha_backward(do, q, k, v, out, lse, cu_q, cu_k, causal, scale):
     rc = L.mm_fmha_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), do.data_ptr(), lse.data_ptr(),
                        delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu_q.data_ptr(), cu_k.data_ptr(),
                        plan.data_ptr(), T, Tk, n_seqs, Nq, Nkv, D, q.stride(0), k.stride(0), v.stride(0), int(causal),
-                       float(scale), int(split), status_word(dev).data_ptr(), _st())
+                       float(scale), int(split), FMHA_BWD_VARIANT, status_word(dev).data_ptr(), _st())
     _check(rc, "fmha_bwd")
     global LAUNCHES
     LAUNCHES += 4

@@ -630,14 +630,16 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
     pk.tile_seq = k_seq;
     pk.tile_r0 = k_r0;
     pk.n_tiles = k_n;
-    if (variant == 1) {      // ping-pong schedule: 64-wide inner tiles, deeper rings, one warpgroup per in-flight tile
+    if (variant == 1 || variant == 2) {      // ping-pong schedule (2: dS through tensor memory, TS-form dQ product): 64-wide inner tiles, deeper rings, one warpgroup per in-flight tile
         CUtensorMap tK64, tV64;
         if ((r = make_tmap_3d(&tK64, k, HD, Nkv, Tk, HD, k_ts, 64, 1, BK))) return 7000 + r;
         if ((r = make_tmap_3d(&tV64, v, HD, Nkv, Tk, HD, v_ts, 64, 1, BK))) return 8000 + r;
-        if (cudaFuncSetAttribute(fmha_bwd_dq_pp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDqPP) != cudaSuccess ||
+        if (cudaFuncSetAttribute(fmha_bwd_dq_pp_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDqPP) != cudaSuccess ||
+            cudaFuncSetAttribute(fmha_bwd_dq_pp_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDqPP) != cudaSuccess ||
             cudaFuncSetAttribute(fmha_bwd_dkv_pp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkvPP) != cudaSuccess)
             return -3;
-        fmha_bwd_dq_pp_kernel<<<dim3(mq, Nq), 320, kSmemDqPP, st>>>(tQ, tK64, tV64, tdO, p);
+        if (variant == 2) fmha_bwd_dq_pp_kernel<true><<<dim3(mq, Nq), 320, kSmemDqPP, st>>>(tQ, tK64, tV64, tdO, p);
+        else fmha_bwd_dq_pp_kernel<false><<<dim3(mq, Nq), 320, kSmemDqPP, st>>>(tQ, tK64, tV64, tdO, p);
         fmha_bwd_dkv_pp_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkvPP, st>>>(tQ64, tK, tV, tdO64, pk);
         return (int)cudaGetLastError();
     }

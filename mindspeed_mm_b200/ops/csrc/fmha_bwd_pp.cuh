@@ -22,6 +22,9 @@ constexpr int kDsTile = 128 * BK * 2;      // 16 KiB: dS / P^T / dS^T tile (one 
 constexpr int kStagesDq = 4;
 constexpr int kSmemDqPP = 2 * kTile + 2 * kStagesDq * kKTile + 2 * kDsTile + 1024 + 1024;
 
+// kTS: dS is handed to the dQ product through tensor memory (written over the tile's dP columns with tcgen05.st and
+// consumed as the A operand of a TS-form MMA) instead of through swizzled shared memory.
+template <bool kTS>
 __global__ void __launch_bounds__(320, 1)
 fmha_bwd_dq_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const BwdParams p) {
@@ -146,16 +149,20 @@ fmha_bwd_dq_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const int st = j % kStagesDq, b = j & 1;
                 const uint32_t bph = (j >> 1) & 1;
                 // S / dP of tile j + 2 go into the buffers tile j's warpgroup has just emptied into registers
-                if (j + 2 < n_kv && !(ok = issue_s_dp(j + 2))) break;
+                if (!kTS && j + 2 < n_kv && !(ok = issue_s_dp(j + 2))) break;
                 if (!mbar_wait(&ds_full[b], bph, abort_flag)) { ok = false; break; }
                 fence_after_sync();
                 const uint32_t ka = smem_u32(sK + st * kKTile), dsa = smem_u32(sdS + b * kDsTile);
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k)
-                    mma_ss(tdQ, smem_desc_sw128(dsa + k * 32, 16, 1024), smem_desc_sw128(ka + k * 2048, kKAtom, 1024), idesc_dq,
-                           (j | k) ? 1u : 0u);
+                for (int k = 0; k < BK / 16; ++k) {
+                    const uint64_t db = smem_desc_sw128(ka + k * 2048, kKAtom, 1024);
+                    if (kTS) mma_ts(tdQ, tdP + b * BK + k * 8, db, idesc_dq, (j | k) ? 1u : 0u);
+                    else mma_ss(tdQ, smem_desc_sw128(dsa + k * 32, 16, 1024), db, idesc_dq, (j | k) ? 1u : 0u);
+                }
                 mma_commit(&ds_empty[b]);
                 mma_commit(&k_empty[st]);
+                // TS: dS(j) sits in dP[b]'s columns; the in-order tensor pipe runs dP(j + 2) after dQ(j)
+                if (kTS && j + 2 < n_kv && !(ok = issue_s_dp(j + 2))) break;
             }
             if (ok) mma_commit(dq_full);
             if (!ok) atomicExch(p.status, MM_TIMEOUT_MMA);
@@ -192,6 +199,16 @@ fmha_bwd_dq_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const float pr = exp2f(__uint_as_float(r[i]) * p.scale_log2 - lse2);
                 const float pv = kbase + i > limit ? 0.f : pr;
                 r[i] = __float_as_uint(pv * (__uint_as_float(d[i]) - dlt));
+            }
+            if (kTS) {
+                // 64 keys -> 32 columns of bf16 pairs over the first half of this tile's dP columns
+#pragma unroll
+                for (int i = 0; i < 32; ++i) d[i] = pack2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                tmem_st_32x32(tdP + wg * BK + lane_off, d);
+                tmem_wait_st();
+                fence_before_sync();
+                mbar_arrive(&ds_full[wg]);
+                continue;
             }
             if (j >= 2 && !mbar_wait(&ds_empty[wg], ((j >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
 #pragma unroll

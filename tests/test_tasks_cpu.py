@@ -173,3 +173,34 @@ def test_posttrain_trainers_take_a_step():
     vd = VLMDPOTrainer(lm, lm_ref, beta=0.1, optimizer=torch.optim.SGD(lm.parameters(), lr=1e-2))
     r = vd.train_step(batch)
     assert abs(r["loss"] - 0.6931) < 1e-3
+
+
+def test_task_entry_points_on_tiny_configs(tmp_path):
+    """inference / evaluation / post-training entry functions behind the root scripts."""
+    import json
+    import os
+    import torch
+    from mindspeed_mm_b200.runtime import task_entry as te
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = json.load(open(os.path.join(root, "examples", "wan2.1", "pretrain_model_tiny.json")))
+    cfg.update(prompts=[[1, 2, 3]], frames=3, height=8, width=8, save_path=str(tmp_path))
+    vids = te.inference_sora(cfg)
+    assert vids[0].shape == (1, 16, 3, 8, 8) and os.path.exists(tmp_path / "sample_0000.pt")
+    assert te.evaluate_gen(cfg)["num_samples"] == 1
+
+    def pairs():
+        while True:
+            yield dict(latents_win=torch.randn(1, 16, 3, 8, 8), latents_lose=torch.randn(1, 16, 3, 8, 8),
+                       prompt=torch.randn(1, 16, 64))
+    assert abs(te.posttrain_sora_dpo(cfg, pairs(), steps=1)[0]["loss"] - 0.6931) < 1e-3
+    r = te.posttrain_flux_dancegrpo({"predictor": {"preset": "tiny"}, "grpo": {"num_steps": 3, "group_size": 2}},
+                                    [(torch.randn(1, 4, 32), torch.randn(1, 16))], lambda x, c: -x.flatten(1).pow(2).mean(1), steps=1)
+    assert r[0]["reward_std"] > 0
+    out = te.inference_vlm({"model": {"preset": "tiny"}, "prompts": [{"text": "hello"}], "max_new_tokens": 2})
+    assert len(out) == 1
+    (tmp_path / "q.jsonl").write_text(json.dumps({"question": "2+2?", "answer": "4"}) + "\n")
+    res = te.evaluate_vlm({"dataset": str(tmp_path / "q.jsonl"), "metric": "exact_match"}, predict=lambda s: "4")
+    assert list(res.values())[0] == 1.0 or res.get("accuracy", res.get("exact_match", 0)) == 1.0
+    video = torch.rand(3, 4, 16, 16) * 2 - 1
+    te.write_video(video, str(tmp_path / "v.mp4"), fps=4)
+    assert os.path.getsize(tmp_path / "v.mp4") > 0

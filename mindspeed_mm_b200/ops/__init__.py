@@ -125,6 +125,15 @@ def attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max
         if _TIER == "native" and _nat().fmha_supported(q, k, v):
             return _nat().attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
                                            causal, softmax_scale)
+        D = q.shape[-1]
+        if _TIER == "native" and q.dtype == torch.bfloat16 and D < 128 and D % 8 == 0 and v.shape[-1] == D:
+            # smaller heads (ViT: 80) ride the 128-wide tcgen05 kernels zero-padded; the scale stays 1/sqrt(D)
+            pad = 128 - D
+            qp, kp, vp = (F.pad(t, (0, pad)) for t in (q, k, v))
+            if _nat().fmha_supported(qp, kp, vp):
+                scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
+                o = _nat().attention_varlen(qp, kp, vp, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, scale)
+                return o[..., :D]
         return _library_attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
                                          causal, softmax_scale)
     return ref.attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, causal, softmax_scale)

@@ -228,6 +228,28 @@ def test_fmha_forward_and_grad(lens, nq, nkv, causal):
     _close(vg.grad, vr.grad, rtol=3e-2, atol=3e-2)
 
 
+def test_attention_head_dim_80_padded_onto_native_kernels():
+    """ViT heads (D = 80) with window-sized segments: zero-padded to 128 and run by the tcgen05 forward / backward."""
+    from mindspeed_mm_b200.ops import native
+    torch.manual_seed(0)
+    lens = [64] * 20 + [37, 256]
+    T, N, D = sum(lens), 16, 80
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    q, k, v = (torch.randn(T, N, D, device=DEV, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+    before = native.LAUNCHES
+    o = ops.attention_varlen(q, k, v, cu, cu, max(lens), max(lens), causal=False)
+    do = torch.randn_like(o)
+    o.backward(do)
+    assert native.LAUNCHES > before
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    orf = ref.attention_varlen(qr, kr, vr, cu.cpu(), cu.cpu(), False)
+    orf.backward(do.float())
+    _close(o, orf)
+    _close(q.grad, qr.grad, rtol=3e-2, atol=3e-2)
+    _close(k.grad, kr.grad, rtol=3e-2, atol=3e-2)
+    _close(v.grad, vr.grad, rtol=3e-2, atol=3e-2)
+
+
 def test_fmha_backward_cross_attention_shapes():
     """q and k/v of different lengths (DiT cross-attention to 512 text tokens), non-causal, tcgen05 backward."""
     torch.manual_seed(0)

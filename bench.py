@@ -113,7 +113,7 @@ def make_batches(cfg, n_batches, seq_len, samples_per_pack, images_per_sample, i
     ds = SyntheticVLMDataset(SyntheticVLMSpec(
         seq_len=per, images_per_sample=images_per_sample, image_size=image_size, vocab_size=cfg.text.vocab_size,
         image_token_id=cfg.image_token_id, vision_start_token_id=cfg.vision_start_token_id, seed=1234 + rank,
-        pixel_dtype=torch.bfloat16))
+        pixel_dtype=torch.bfloat16, patch=cfg.vision.patch_size, merge=cfg.vision.spatial_merge_size))
     col = PackedVLMCollator(cfg.image_token_id, cfg.vision_start_token_id, merge=cfg.vision.spatial_merge_size,
                             patch=cfg.vision.patch_size, window_size=cfg.vision.window_size,
                             vit_head_dim=cfg.vision.hidden_size // cfg.vision.num_heads,
@@ -234,13 +234,113 @@ def run_wan(args):
     return 0
 
 
+def run_moe(args):
+    """Third workload: Qwen3-VL-30B-A3B (128 experts, top-8) finetune step, 8192 packed tokens per GPU.  Dense parameters
+    ZeRO-3 over all ranks, experts expert-parallel over all ranks (16 experts per rank on 8 GPUs) with the
+    peer-memory dispatcher; AdamW in backward; activation checkpointing per layer.  value = tokens/s of the job."""
+    from mindspeed_mm_b200 import ops
+    from mindspeed_mm_b200.api import init_distributed, stable_init_fn
+    from mindspeed_mm_b200.data.collate import batch_nbytes, to_device
+    from mindspeed_mm_b200.models.qwen3_vl_moe import Qwen3VLMoEConfig, Qwen3VLMoEModel
+    from mindspeed_mm_b200.ops import native
+    from mindspeed_mm_b200.parallel.fsdp import EngineMux, FSDPEngine, OptimConfig
+    from mindspeed_mm_b200.parallel.state import init_parallel_state
+
+    ops.set_tier("native" if args.impl == "native" else "library")
+    dev, rank, world = init_distributed(None)
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    small = args.model == "tiny"
+    cfg = Qwen3VLMoEConfig.tiny() if small else Qwen3VLMoEConfig.qwen3_vl_30b_a3b()
+    if args.layers:
+        cfg.text.num_layers = args.layers
+    cfg.text.ep_dispatcher = args.dispatcher
+    ps = init_parallel_state(world_size=world, device_type=dev.type, expert_parallel_size=world)
+    with torch.device("meta"):
+        model = Qwen3VLMoEModel(cfg, ep_size=world)
+    opt = OptimConfig(lr=1e-5, weight_decay=0.0)
+    ex = [p for _, m in model.expert_units() for p in m.parameters()]
+    dense = FSDPEngine(model.fsdp_units(), group=ps.get_fsdp_group() if world > 1 else False, device=dev,
+                       param_dtype=torch.bfloat16, opt=opt, exclude_params=ex, comm=args.comm)
+    expert = FSDPEngine(model.expert_units(), group=False, device=dev, param_dtype=torch.bfloat16, opt=opt,
+                        grad_divide=world, no_recompute=())
+    mux = EngineMux(dense, expert)
+    mux.materialize(stable_init_fn(0.02, 0))
+    seq = args.seq_len if not small else 512
+    host = make_batches(cfg, 2, seq, 4 if not small else 1, 2 if not small else 1, 448 if not small else 224, rank, pin=True)
+    on_dev = [to_device(b, dev) for b in host]
+    tokens_per_step = host[0]["n_tokens"] * world
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one(b):
+        mux.set_lr(1e-5)
+        loss_sum, n = model(b, run=mux.run)
+        loss = loss_sum / n
+        loss.backward()
+        mux.end_micro_step()
+        mux.finish_step()
+        return loss
+
+    def region(batches, steps, e2e):
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = native.LAUNCHES
+        s.record()
+        last = None
+        for i in range(steps):
+            b = batches[i % len(batches)]
+            if e2e:
+                b = to_device(b, dev)
+            loss = one(b)
+            if e2e:
+                last = float(loss.detach())
+        e.record()
+        barrier()
+        ms = torch.tensor([s.elapsed_time(e)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms) / steps, native.LAUNCHES - l0, last
+
+    region(on_dev, max(args.warmup, 3) - 1, False)
+    region(host, 1, True)
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms_dev, launches, _ = region(on_dev, args.steps, False)
+    ms_e2e, _, loss = region(host, args.steps, True)
+    clocks = sampler.stop()
+    if args.impl == "native":
+        native.check_status()
+    if rank == 0:
+        out = {"metric": "Qwen3-VL-30B-A3B MoE tokens/s", "value": round(tokens_per_step / (ms_dev / 1e3), 1), "unit": "tokens/s",
+               "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_dev, 2),
+               "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+               "data": "synthetic (random-init weights, random text ids, U[0,1] images)", "impl": args.impl,
+               "config": {"model": "Qwen3-VL-30B-A3B" if not small else "tiny", "global_batch": world, "seq_len": seq,
+                          "parallelism": f"zero3_{world} (dense) x ep{world} (experts)", "dispatcher": args.dispatcher,
+                          "recompute": "activation checkpointing per layer",
+                          "l2": "inputs_larger_than_L2 (expert weights + optimizer state are streamed every step)"},
+               "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1), "clocks": clocks,
+               "e2e": {"value": round(tokens_per_step / (ms_e2e / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 2),
+                       "h2d_bytes_per_step": batch_nbytes(host[0]), "d2h_bytes_per_step": 4, "last_loss": loss},
+               "gpu_launches": launches}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "library", "reference"])
-    ap.add_argument("--workload", default="vlm", choices=["vlm", "wan"],
+    ap.add_argument("--dispatcher", default="p2p", choices=["p2p", "alltoall", "allgather"], help="MoE workload only")
+    ap.add_argument("--workload", default="vlm", choices=["vlm", "wan", "moe"],
                     help="vlm: Qwen2.5-VL-7B FSDP2 tokens/s (default, the driver's line); wan: Wan2.1-14B T2V samples/s")
     ap.add_argument("--model", default="qwen2_5_vl_7b", choices=["qwen2_5_vl_7b", "tiny"])
     ap.add_argument("--seq-len", type=int, default=8192)
@@ -254,6 +354,8 @@ def main():
         return run_reference(args)
     if args.workload == "wan":
         return run_wan(args)
+    if args.workload == "moe":
+        return run_moe(args)
 
     from mindspeed_mm_b200 import ops
     from mindspeed_mm_b200.api import VLMTrainerSpec, build_vlm_trainer

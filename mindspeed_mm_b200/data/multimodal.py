@@ -393,3 +393,63 @@ class FeatureDataset(Dataset):
             if k in d:
                 out[k] = d[k]
         return out
+
+
+@data_register.register("t2v")
+@data_register.register("i2v")
+class VideoTextDataset(Dataset):
+    """Raw video (or image) + caption records for generative training without pre-extracted features
+    (mindspeed_mm/data/datasets/t2v_dataset.py): ``{"path": ..., "cap": ...}`` in json / jsonl.  Frames are sampled
+    uniformly, resized so that the short side covers the target, centre-cropped and scaled to [-1, 1]; the caption
+    is tokenised (ids padded to ``text_len``).  The frozen VAE / text encoder of ``SoRAModel`` consume the result."""
+
+    def __init__(self, dataset_param=None, model=None, *, files=None, data_folder: str = "", num_frames: int = 17,
+                 height: int = 256, width: int = 256, tokenizer=None, text_len: int = 512):
+        if dataset_param is not None:
+            basic = dict(getattr(dataset_param, "basic_parameters", None) or {})
+            pre = dict(getattr(dataset_param, "preprocess_parameters", None) or {})
+            files = files or basic.get("data_path")
+            files = [files] if isinstance(files, str) else list(files)
+            data_folder = basic.get("data_folder", data_folder)
+            num_frames = int(pre.get("num_frames", num_frames))
+            height, width = int(pre.get("max_height", height)), int(pre.get("max_width", width))
+            text_len = int(pre.get("text_len", text_len))
+            tp = (pre.get("tokenizer_config") or {}).get("from_pretrained")
+            if tokenizer is None and tp and os.path.exists(tp):
+                from transformers import AutoTokenizer
+                tokenizer = AutoTokenizer.from_pretrained(tp)
+        self.records: List[dict] = []
+        for f in files:
+            self.records += _read_records(f)
+        self.folder, self.T, self.H, self.W, self.text_len = data_folder, num_frames, height, width, text_len
+        self.tok = tokenizer or ByteTokenizer()
+
+    def __len__(self):
+        return len(self.records)
+
+    def _frames(self, path: str) -> torch.Tensor:
+        p = path if os.path.isabs(path) or not self.folder else os.path.join(self.folder, path)
+        if p.lower().endswith((".png", ".jpg", ".jpeg", ".bmp", ".webp")):
+            from PIL import Image
+            import numpy as np
+            x = torch.from_numpy(np.asarray(Image.open(p).convert("RGB")).copy()).permute(2, 0, 1).float()[None] / 255.0
+        else:
+            x = read_video_frames(p, self.T)
+        _, _, h, w = x.shape
+        s = max(self.H / h, self.W / w)
+        nh, nw = max(self.H, round(h * s)), max(self.W, round(w * s))
+        x = torch.nn.functional.interpolate(x, size=(nh, nw), mode="bilinear", align_corners=False, antialias=True)
+        top, left = (nh - self.H) // 2, (nw - self.W) // 2
+        x = x[:, :, top:top + self.H, left:left + self.W]
+        if x.shape[0] < self.T and x.shape[0] > 1:
+            x = torch.cat([x, x[-1:].repeat(self.T - x.shape[0], 1, 1, 1)], 0)
+        return (x * 2 - 1).permute(1, 0, 2, 3).contiguous()           # [3, T, H, W]
+
+    def __getitem__(self, i):
+        r = self.records[i]
+        cap = r.get("cap") or r.get("caption") or r.get("text") or ""
+        cap = cap[0] if isinstance(cap, list) else cap
+        ids = list(self.tok.encode(cap))[: self.text_len]
+        mask = [1] * len(ids) + [0] * (self.text_len - len(ids))
+        ids = ids + [0] * (self.text_len - len(ids))
+        return dict(video=self._frames(r["path"]), prompt_ids=torch.tensor(ids), prompt_mask=torch.tensor(mask))

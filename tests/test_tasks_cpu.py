@@ -204,3 +204,29 @@ def test_task_entry_points_on_tiny_configs(tmp_path):
     video = torch.rand(3, 4, 16, 16) * 2 - 1
     te.write_video(video, str(tmp_path / "v.mp4"), fps=4)
     assert os.path.getsize(tmp_path / "v.mp4") > 0
+
+
+def test_ae_trainer_and_video_text_dataset(tmp_path):
+    import json
+    import numpy as np
+    import torch
+    from mindspeed_mm_b200.data.multimodal import VideoTextDataset, read_video_frames
+    from mindspeed_mm_b200.models.ae.wan_vae import WanVAE, WanVAEConfig
+    from mindspeed_mm_b200.runtime.task_entry import write_video
+    from mindspeed_mm_b200.tasks.ae_train import AETrainer, NLayerDiscriminator3D, VAELoss
+    torch.manual_seed(0)
+    write_video(torch.rand(3, 9, 48, 64) * 2 - 1, str(tmp_path / "clip.mp4"), fps=8)
+    (tmp_path / "d.jsonl").write_text(json.dumps({"path": "clip.mp4", "cap": "a test clip"}) + "\n")
+    ds = VideoTextDataset(files=[str(tmp_path / "d.jsonl")], data_folder=str(tmp_path), num_frames=5, height=32, width=32,
+                          text_len=16)
+    s = ds[0]
+    assert s["video"].shape == (3, 5, 32, 32) and s["prompt_ids"].shape == (16,) and int(s["prompt_mask"].sum()) == 11
+    assert -1.0 <= float(s["video"].min()) and float(s["video"].max()) <= 1.0
+    vae = WanVAE(WanVAEConfig.tiny())
+    tr = AETrainer(vae, VAELoss(kl_weight=1e-4, disc_weight=0.5, disc_start=1),
+                   NLayerDiscriminator3D(3, base=8, n_layers=2), lr=1e-3)
+    video = s["video"][None]
+    l0 = tr.train_step(video)
+    l1 = tr.train_step(video)
+    assert "d_loss" not in l0 and "d_loss" in l1 and "g_loss" in l1
+    assert all(v == v for v in l1.values())

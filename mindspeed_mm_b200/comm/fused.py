@@ -65,7 +65,7 @@ class _UlyssesQKVFn(torch.autograd.Function):
         dy = recv.permute(1, 2, 0, 3).reshape(S_local, n_slots * W * blk)   # column = (slot * W + dst) * blk + c
         dx = native.gemm_nn(dy, w)
         dw = native.gemm_tn(dy, x)
-        db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias else None
+        db = torch.sum(dy, 0, dtype=torch.float32).to(dy.dtype) if ctx.has_bias else None
         return dx, dw, db, None
 
 
@@ -178,7 +178,7 @@ class _AllGatherLinearFn(torch.autograd.Function):
         dA = native.gemm_nn(g.contiguous(), w)
         dx = torch.empty(A.shape[0] // mod.world, A.shape[1], dtype=dA.dtype, device=dA.device)
         dist.reduce_scatter_tensor(dx, dA, group=mod.group)
-        db = g.float().sum(0).to(g.dtype) if ctx.has_bias else None
+        db = torch.sum(g, 0, dtype=torch.float32).to(g.dtype) if ctx.has_bias else None
         return dx, native.gemm_tn(g.contiguous(), A), db, None
 
 
@@ -227,7 +227,7 @@ class _UlyssesOutFn(torch.autograd.Function):
         send = dA.view(S_local, mod.world, cols).permute(1, 0, 2).contiguous()  # [dst head group, S_local, cols]
         recv = torch.empty_like(send)
         dist.all_to_all_single(recv, send, group=mod.group)                     # [src rows block, S_local, cols]
-        db = g.float().sum(0).to(g.dtype) if ctx.has_bias else None
+        db = torch.sum(g, 0, dtype=torch.float32).to(g.dtype) if ctx.has_bias else None
         return recv.reshape(mod.world * S_local, cols), native.gemm_tn(g.contiguous(), A), db, None
 
 

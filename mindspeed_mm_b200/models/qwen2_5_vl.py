@@ -235,8 +235,8 @@ class Linear(nn.Module):
         self.weight = nn.Parameter(torch.empty(out_features, in_features))
         self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
 
-    def forward(self, x):
-        return ops.linear(x, self.weight, self.bias)
+    def forward(self, x, value_unused_in_backward: bool = False):
+        return ops.linear(x, self.weight, self.bias, value_unused_in_backward)
 
 
 class VisionBlock(nn.Module):
@@ -271,7 +271,8 @@ class VisionBlock(nn.Module):
         k = ops.rope_rotate_half(qkv[:, 1], cos, sin)
         o = ops.attention_varlen(q, k, qkv[:, 2], cu_seqlens, cu_seqlens, max_seqlen, max_seqlen, causal=False)
         x = x + self.attn_proj(o.reshape(T, -1))
-        x = x + self.mlp_down(ops.swiglu(self.mlp_gate_up(self.norm2(x))))
+        # the block's last product only feeds the residual add: its value is not needed when the block is recomputed
+        x = x + self.mlp_down(ops.swiglu(self.mlp_gate_up(self.norm2(x))), value_unused_in_backward=True)
         return x
 
 
@@ -371,7 +372,8 @@ class DecoderLayer(nn.Module):
         o = ops.attention_varlen(q, k, v.view(T, self.nkv, self.hd), cu_seqlens, cu_seqlens,
                                  max_seqlen, max_seqlen, causal=True)
         x = x + self.o_proj(o.reshape(T, -1))
-        x = x + self.down_proj(ops.linear_swiglu(self.post_attention_layernorm(x), self.gate_up_proj.weight))
+        x = x + self.down_proj(ops.linear_swiglu(self.post_attention_layernorm(x), self.gate_up_proj.weight),
+                               value_unused_in_backward=True)
         return x
 
 

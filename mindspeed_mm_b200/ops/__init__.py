@@ -106,10 +106,29 @@ def gated_rms_norm(x, z, weight, eps: float = 1e-6):
 
 
 # --------------------------------------------------------------------------- GEMM
-def linear(x, weight, bias=None):
-    """``x @ weight.T + bias`` (weight is [out, in], K-major for both operands)."""
+_RECOMPUTING = False
+
+
+class recompute_region:
+    """Marks the re-forward of a checkpointed unit (entered by the sharding engine's backward)."""
+
+    def __enter__(self):
+        global _RECOMPUTING
+        self.prev, _RECOMPUTING = _RECOMPUTING, True
+
+    def __exit__(self, *exc):
+        global _RECOMPUTING
+        _RECOMPUTING = self.prev
+
+
+def linear(x, weight, bias=None, value_unused_in_backward: bool = False):
+    """``x @ weight.T + bias`` (weight is [out, in], K-major for both operands).
+
+    ``value_unused_in_backward``: the caller promises that nothing downstream inside the checkpointed unit needs the
+    VALUE of this product for its gradient (it only feeds a residual add).  During a recompute the native tier then
+    skips the GEMM and returns an uninitialised tensor; gradients are unaffected."""
     if _native(x) and x.dtype == torch.bfloat16 and _nat().gemm_supported(x, weight):
-        return _nat().linear(x, weight, bias)
+        return _nat().linear(x, weight, bias, value_unused_in_backward and _RECOMPUTING)
     return F.linear(x, weight, bias)
 
 

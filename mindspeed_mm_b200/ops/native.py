@@ -393,12 +393,16 @@ _BWD_NATIVE = os.environ.get("MM_B200_GEMM_BWD", "1") == "1"
 
 class _Linear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, bias):
+    def forward(ctx, x, w, bias, skip_value=False):
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
         ctx.shape = shape
+        if skip_value:
+            # re-forward of a checkpointed unit whose last linear feeds only a residual add: the gradient needs the
+            # operands, not the product, so the GEMM is not run again
+            return torch.empty(*shape[:-1], w.shape[0], dtype=x.dtype, device=x.device)
         y = gemm_nt(x2, w, bias)
         return y.view(*shape[:-1], w.shape[0])
 
@@ -414,12 +418,12 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = gemm_tn(dy2, x2) if _BWD_NATIVE else dy2.t() @ x2
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy2.float().sum(0).to(dy2.dtype)
-        return dx, dw, db
+            db = torch.sum(dy2, 0, dtype=torch.float32).to(dy2.dtype)
+        return dx, dw, db, None
 
 
-def linear(x, w, bias=None):
-    return _Linear.apply(x, w, bias)
+def linear(x, w, bias=None, skip_value=False):
+    return _Linear.apply(x, w, bias, skip_value)
 
 
 # --------------------------------------------------------------------------- not yet native

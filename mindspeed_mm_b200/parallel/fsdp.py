@@ -613,7 +613,7 @@ class _UnitFn(torch.autograd.Function):
         engine.wait_unshard(u)
         engine._prefetch_backward(u)
         args, kwargs = _join_args(ctx.spec, tensors)
-        with torch.enable_grad():
+        with torch.enable_grad(), ops.recompute_region():
             out = u.module(*args, **kwargs)
         outs = tuple(out) if isinstance(out, (tuple, list)) else (out,)
         pairs = [(o, g) for o, g in zip(outs, gouts)

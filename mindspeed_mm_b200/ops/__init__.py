@@ -121,6 +121,25 @@ class recompute_region:
         _RECOMPUTING = self.prev
 
 
+_ACT_CACHE = None      # (list, "record" | "replay") while a checkpointed unit runs under the sharding engine
+
+
+class activation_cache:
+    """Lets expensive, small-output ops (attention: out + log-sum-exp) keep their result across a checkpointed unit's
+    first forward and its re-forward: ``record`` appends results to ``store``, ``replay`` hands them back in order."""
+
+    def __init__(self, store: list, mode: str):
+        self.store, self.mode = store, mode
+
+    def __enter__(self):
+        global _ACT_CACHE
+        self.prev, _ACT_CACHE = _ACT_CACHE, (self.store, self.mode)
+
+    def __exit__(self, *exc):
+        global _ACT_CACHE
+        _ACT_CACHE = self.prev
+
+
 def linear(x, weight, bias=None, value_unused_in_backward: bool = False):
     """``x @ weight.T + bias`` (weight is [out, in], K-major for both operands).
 
@@ -144,7 +163,7 @@ def attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max
     if q.is_cuda:
         if _TIER == "native" and _nat().fmha_supported(q, k, v):
             return _nat().attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
-                                           causal, softmax_scale)
+                                           causal, softmax_scale, _ACT_CACHE)
         D = q.shape[-1]
         if (_TIER == "native" and _PAD_SMALL_HEADS and q.dtype == torch.bfloat16 and D < 128 and D % 8 == 0
                 and v.shape[-1] == D):

@@ -501,10 +501,11 @@ class _FMHA(torch.autograd.Function):
     varlen backward fed with this forward's out / lse, for comparison)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, causal, scale):
-        out, lse = fmha_forward(q, k, v, cu_q, cu_k, causal, scale)
+    def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, causal, scale, precomputed=None):
+        out, lse = precomputed if precomputed is not None else fmha_forward(q, k, v, cu_q, cu_k, causal, scale)
         ctx.save_for_backward(q, k, v, out, lse, cu_q, cu_k)
         ctx.meta = (max_q, max_k, causal, scale)
+        ctx.lse_out = lse
         return out
 
     @staticmethod
@@ -514,16 +515,27 @@ class _FMHA(torch.autograd.Function):
         max_q, max_k, causal, scale = ctx.meta
         if FMHA_BWD == "native" and _STATUS.get("mm_fmha_bwd", False):
             dq, dk, dv = fmha_backward(do, q, k, v, out, lse, cu_q, cu_k, causal, scale)
-            return dq, dk, dv, None, None, None, None, None, None
+            return dq, dk, dv, None, None, None, None, None, None, None
         dq, dk, dv = torch.empty(q.shape, dtype=q.dtype, device=q.device), torch.empty(k.shape, dtype=k.dtype, device=k.device), \
             torch.empty(v.shape, dtype=v.dtype, device=v.device)
         _flash_attn_varlen_backward(do.contiguous(), q, k, v, out, lse, dq, dk, dv, cu_q.to(torch.int32), cu_k.to(torch.int32),
                                     max_q, max_k, 0.0, scale, causal, -1, -1, 0.0, None, False)
-        return dq, dk, dv, None, None, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None, None, None
 
 
-def attention_varlen(q, k, v, cu_q, cu_k, max_q, max_k, causal, scale):
+def attention_varlen(q, k, v, cu_q, cu_k, max_q, max_k, causal, scale, cache=None):
+    """``cache`` = (store, mode) from :class:`ops.activation_cache`: under ``record`` (the no-grad first forward of a
+    checkpointed unit) the output and log-sum-exp are kept, under ``replay`` (its re-forward) they are reused and the
+    forward kernel is not run again."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if cache is not None:
+        store, mode = cache
+        if mode == "record" and not torch.is_grad_enabled():
+            out, lse = fmha_forward(q, k, v, cu_q, cu_k, bool(causal), float(scale))
+            store.append((out, lse))
+            return out
+        if mode == "replay" and store:
+            return _FMHA.apply(q, k, v, cu_q, cu_k, max_q, max_k, bool(causal), float(scale), store.pop(0))
     return _FMHA.apply(q, k, v, cu_q, cu_k, max_q, max_k, bool(causal), float(scale))
 
 

@@ -593,7 +593,8 @@ class _UnitFn(torch.autograd.Function):
         engine.wait_unshard(u)
         engine._prefetch_forward(u)
         args, kwargs = _join_args(spec, tensors)
-        with torch.no_grad():
+        ctx.act_cache = []
+        with torch.no_grad(), ops.activation_cache(ctx.act_cache, "record"):
             out = u.module(*args, **kwargs)
         engine.reshard(u)
         ctx.save_for_backward(*tensors)
@@ -613,8 +614,9 @@ class _UnitFn(torch.autograd.Function):
         engine.wait_unshard(u)
         engine._prefetch_backward(u)
         args, kwargs = _join_args(ctx.spec, tensors)
-        with torch.enable_grad(), ops.recompute_region():
+        with torch.enable_grad(), ops.recompute_region(), ops.activation_cache(ctx.act_cache, "replay"):
             out = u.module(*args, **kwargs)
+        ctx.act_cache = None
         outs = tuple(out) if isinstance(out, (tuple, list)) else (out,)
         pairs = [(o, g) for o, g in zip(outs, gouts)
                  if isinstance(o, torch.Tensor) and o.requires_grad and g is not None]

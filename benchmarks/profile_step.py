@@ -20,6 +20,7 @@ def main():
     ap.add_argument("--top", type=int, default=40)
     ap.add_argument("--out", default="")
     ap.add_argument("--recompute", default="auto", choices=["full", "auto", "none"])
+    ap.add_argument("--shapes", action="store_true", help="also list the costliest aten ops grouped by input shapes")
     a = ap.parse_args()
     from bench import make_batches
     from mindspeed_mm_b200 import ops
@@ -38,7 +39,7 @@ def main():
         tr.train_step([b])
     torch.cuda.synchronize()
     from torch.profiler import ProfilerActivity, profile
-    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU], record_shapes=a.shapes) as prof:
         tr.train_step([b])
         torch.cuda.synchronize()
     evs = [e for e in prof.key_averages() if e.device_time_total > 0 and e.device_type.name == "CUDA"]
@@ -49,6 +50,12 @@ def main():
     lines = [f"total CUDA kernel time {tot / 1e3:.1f} ms (impl={a.impl}, layers={cfg.text.num_layers})"]
     for e in evs[:a.top]:
         lines.append(f"{e.device_time_total / 1e3:9.2f} ms {100 * e.device_time_total / tot:5.1f}% n={e.count:5d}  {e.key[:110]}")
+    if a.shapes:
+        ops_ = [e for e in prof.key_averages(group_by_input_shape=True) if e.device_time_total > 0 and e.key.startswith("aten::")]
+        ops_.sort(key=lambda e: -e.device_time_total)
+        lines.append("-- aten ops by input shape (device time includes children)")
+        for e in ops_[:40]:
+            lines.append(f"{e.device_time_total / 1e3:9.2f} ms n={e.count:5d}  {e.key:28s} {str(e.input_shapes)[:120]}")
     txt = "\n".join(lines)
     print(txt)
     if a.out:

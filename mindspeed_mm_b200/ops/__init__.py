@@ -126,7 +126,8 @@ _ACT_CACHE = None      # (list, "record" | "replay") while a checkpointed unit r
 
 class activation_cache:
     """Lets expensive, small-output ops (attention: out + log-sum-exp) keep their result across a checkpointed unit's
-    first forward and its re-forward: ``record`` appends results to ``store``, ``replay`` hands them back in order."""
+    first forward and its re-forward: ``record`` appends results to ``store``, ``replay`` hands them back in order.
+    Same purpose as the reference's skip-recompute flash attention (fsdp/ops/flash_attn/skip_recompute_flash_attn.py:38,135)."""
 
     def __init__(self, store: list, mode: str):
         self.store, self.mode = store, mode

@@ -416,7 +416,15 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = (gemm_nn(dy2, w) if _BWD_NATIVE else dy2 @ w).view(ctx.shape)
         if ctx.needs_input_grad[1]:
-            dw = gemm_tn(dy2, x2) if _BWD_NATIVE else dy2.t() @ x2
+            tgt = getattr(w, "_grad_flat", None)
+            if tgt is not None and _BWD_NATIVE and w.grad is None:
+                # the sharding engine offered this parameter's slice of the unit's flat gradient buffer: write the
+                # weight gradient there (a fresh view each time, so autograd can adopt it as .grad without a copy)
+                flat, off, numel, shape = tgt
+                w._grad_flat = None                      # a second use of the same weight falls back to a new tensor
+                dw = gemm_tn(dy2, x2, out=flat[off:off + numel].view(shape))
+            else:
+                dw = gemm_tn(dy2, x2) if _BWD_NATIVE else dy2.t() @ x2
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = torch.sum(dy2, 0, dtype=torch.float32).to(dy2.dtype)
         return dx, dw, db, None
@@ -491,8 +499,8 @@ def fmha_backward(do, q, k, v, out, lse, cu_q, cu_k, causal, scale):
     LAUNCHES += 4
     if split:
         G = Nq // Nkv
-        dk = dk.view(Tk, Nkv, G, D).float().sum(2).to(q.dtype)
-        dv = dv.view(Tk, Nkv, G, D).float().sum(2).to(q.dtype)
+        dk = torch.sum(dk.view(Tk, Nkv, G, D), 2, dtype=torch.float32).to(q.dtype)
+        dv = torch.sum(dv.view(Tk, Nkv, G, D), 2, dtype=torch.float32).to(q.dtype)
     return dq, dk, dv
 
 

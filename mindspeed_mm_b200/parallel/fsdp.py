@@ -123,14 +123,16 @@ class FlatGroup:
         """Copy the parameters' ``.grad`` into one flat buffer (pads zero) and drop the originals."""
         g = out if out is not None else torch.empty(self.padded, dtype=self.dtype, device=self.device)
         views, srcs, prev_end = [], [], 0
+        base, esz = g.data_ptr(), g.element_size()
         for (n, p), off, shape, numel in zip(self.named_params, self.offsets, self.shapes, self.numels):
             if off > prev_end:
                 g[prev_end:off].zero_()
             if p.grad is None:
                 g[off:off + numel].zero_()
-            else:
+            elif p.grad.data_ptr() != base + off * esz or p.grad.dtype != g.dtype:
                 views.append(g[off:off + numel].view(shape))
                 srcs.append(p.grad)
+            # else: the weight-gradient GEMM already wrote this slice of the flat buffer (see offer_grad_buffer)
             prev_end = off + numel
         if prev_end < self.padded:
             g[prev_end:].zero_()
@@ -138,7 +140,17 @@ class FlatGroup:
             torch._foreach_copy_(views, srcs)
         for _, p in self.named_params:
             p.grad = None
+            p._grad_flat = None
         return g
+
+    def offer_grad_buffer(self) -> torch.Tensor:
+        """Allocate this group's flat gradient buffer BEFORE the unit's backward and tell every parameter where its
+        slice lives, so that a weight-gradient GEMM can write there directly (``ops.native._Linear.backward``);
+        ``flat_grads(out=buffer)`` then skips the copy for the slices that were filled in place."""
+        flat = torch.empty(self.padded, dtype=self.dtype, device=self.device)
+        for (n, p), off, shape, numel in zip(self.named_params, self.offsets, self.shapes, self.numels):
+            p._grad_flat = (flat, off, numel, shape) if p.requires_grad else None
+        return flat
 
 
 class _Empty(dict):
@@ -381,7 +393,9 @@ class FSDPEngine:
                 tpg = getattr(prm, "_tp_sum_group", None)
                 if tpg is not None and prm.grad is not None:
                     dist.all_reduce(prm.grad, group=tpg)
-            flat = g.flat_grads(self._p2p.grad_slot(g) if self._p2p is not None else None)
+            offered = getattr(u, "_offered", None)
+            flat = g.flat_grads(self._p2p.grad_slot(g) if self._p2p is not None else
+                                (offered.pop(id(g), None) if offered else None))
             if self.cuda:
                 self.comm_stream.wait_stream(torch.cuda.current_stream())
                 flat.record_stream(self.comm_stream)
@@ -613,6 +627,8 @@ class _UnitFn(torch.autograd.Function):
         engine.unshard(u)
         engine.wait_unshard(u)
         engine._prefetch_backward(u)
+        if u.trainable and engine._p2p is None and engine.cuda:
+            u._offered = {id(g): g.offer_grad_buffer() for g in u.groups if g.trainable}
         args, kwargs = _join_args(ctx.spec, tensors)
         with torch.enable_grad(), ops.recompute_region(), ops.activation_cache(ctx.act_cache, "replay"):
             out = u.module(*args, **kwargs)

@@ -143,11 +143,12 @@ class FlatGroup:
             p._grad_flat = None
         return g
 
-    def offer_grad_buffer(self) -> torch.Tensor:
+    def offer_grad_buffer(self, flat: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Allocate this group's flat gradient buffer BEFORE the unit's backward and tell every parameter where its
         slice lives, so that a weight-gradient GEMM can write there directly (``ops.native._Linear.backward``);
         ``flat_grads(out=buffer)`` then skips the copy for the slices that were filled in place."""
-        flat = torch.empty(self.padded, dtype=self.dtype, device=self.device)
+        if flat is None:
+            flat = torch.empty(self.padded, dtype=self.dtype, device=self.device)
         for (n, p), off, shape, numel in zip(self.named_params, self.offsets, self.shapes, self.numels):
             p._grad_flat = (flat, off, numel, shape) if p.requires_grad else None
         return flat
@@ -314,7 +315,16 @@ class FSDPEngine:
             u.pending_reduce = u.trainable
             if u.trainable:
                 self._hook_backward_done(u, args, kwargs)
-            return module(*args, **kwargs)
+            out = module(*args, **kwargs)
+            if u.trainable and self.cuda and self._p2p is None:
+                # offer the flat gradient buffer when this unit's backward is about to start (its output gradient
+                # exists); with peer-memory slots the buffer is taken late instead, so that a slot is not held while
+                # the previous unit's reduce-scatter is still reading the other one
+                first = next((t for t in (out if isinstance(out, (tuple, list)) else (out,))
+                              if isinstance(t, torch.Tensor) and t.requires_grad), None)
+                if first is not None:
+                    first.register_hook(lambda g, u=u: self._offer_buffers(u))
+            return out
         tensors, spec = _split_args(args, kwargs)
         outs = _UnitFn.apply(self, u, spec, self._dummy, *tensors)
         return outs[0] if len(outs) == 1 and not u._tuple_out else outs
@@ -361,6 +371,9 @@ class FSDPEngine:
                 t.register_hook(lambda g, u=u: self._unit_backward_done(u))
                 return
 
+    def _offer_buffers(self, u: Unit) -> None:
+        u._offered = {id(g): g.offer_grad_buffer() for g in u.groups if g.trainable}
+
     def _unit_backward_done(self, u: Unit) -> None:
         prev, self._done_wait = getattr(self, "_done_wait", None), u
         if prev is not None and prev is not u and prev.pending_reduce:
@@ -394,8 +407,10 @@ class FSDPEngine:
                 if tpg is not None and prm.grad is not None:
                     dist.all_reduce(prm.grad, group=tpg)
             offered = getattr(u, "_offered", None)
-            flat = g.flat_grads(self._p2p.grad_slot(g) if self._p2p is not None else
-                                (offered.pop(id(g), None) if offered else None))
+            buf = offered.pop(id(g), None) if offered else None
+            if buf is None and self._p2p is not None:
+                buf = self._p2p.grad_slot(g)
+            flat = g.flat_grads(buf)
             if self.cuda:
                 self.comm_stream.wait_stream(torch.cuda.current_stream())
                 flat.record_stream(self.comm_stream)
@@ -627,8 +642,10 @@ class _UnitFn(torch.autograd.Function):
         engine.unshard(u)
         engine.wait_unshard(u)
         engine._prefetch_backward(u)
-        if u.trainable and engine._p2p is None and engine.cuda:
-            u._offered = {id(g): g.offer_grad_buffer() for g in u.groups if g.trainable}
+        if u.trainable and engine.cuda:
+            # with peer-memory collectives the buffer is the next gradient slot of the symmetric arena
+            u._offered = {id(g): g.offer_grad_buffer(engine._p2p.grad_slot(g) if engine._p2p is not None else None)
+                          for g in u.groups if g.trainable}
         args, kwargs = _join_args(ctx.spec, tensors)
         with torch.enable_grad(), ops.recompute_region(), ops.activation_cache(ctx.act_cache, "replay"):
             out = u.module(*args, **kwargs)

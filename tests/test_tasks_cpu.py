@@ -230,3 +230,24 @@ def test_ae_trainer_and_video_text_dataset(tmp_path):
     l1 = tr.train_step(video)
     assert "d_loss" not in l0 and "d_loss" in l1 and "g_loss" in l1
     assert all(v == v for v in l1.values())
+
+
+def test_feature_extraction_roundtrip_into_feature_dataset(tmp_path):
+    import json
+    import torch
+    from mindspeed_mm_b200.data.multimodal import FeatureDataset, VideoTextDataset
+    from mindspeed_mm_b200.models.towers import build_ae, build_text_encoder
+    from mindspeed_mm_b200.runtime.task_entry import write_video
+    from mindspeed_mm_b200.tasks.feature_extraction import extract_features
+    torch.manual_seed(0)
+    write_video(torch.rand(3, 9, 32, 32) * 2 - 1, str(tmp_path / "a.mp4"), fps=8)
+    (tmp_path / "d.jsonl").write_text(json.dumps({"path": "a.mp4", "cap": "clip"}) + "\n")
+    ds = VideoTextDataset(files=[str(tmp_path / "d.jsonl")], data_folder=str(tmp_path), num_frames=5, height=16, width=16, text_len=8)
+    ae = build_ae({"model_id": "wan_video_vae", "base_dim": 8, "z_dim": 4, "dim_mult": [1, 2, 2, 2], "num_res_blocks": 1,
+                   "latents_mean": [0] * 4, "latents_std": [1] * 4})
+    te = build_text_encoder({"model_id": "UMT5", "vocab_size": 300, "d_model": 32, "d_kv": 8, "d_ff": 64, "num_layers": 1, "num_heads": 4})
+    out = tmp_path / "feat"
+    assert extract_features(ds, ae, te, str(out), i2v=True) == 1
+    fd = FeatureDataset(index=str(out / "index_rank0.jsonl"), data_folder=str(out))
+    s = fd[0]
+    assert s["latents"].shape == (4, 2, 2, 2) and s["prompt"].shape == (8, 32) and s["first_frame_latents"].shape == (4, 1, 2, 2)

@@ -41,12 +41,14 @@ def extract_features(dataset, ae, text_encoder, out_dir: str, device="cpu", dtyp
 
 
 def main(argv=None):
-    from ..config.tree import ConfigNode
+    from types import SimpleNamespace
     from ..data.multimodal import VideoTextDataset
     from ..models.towers import build_ae, build_text_encoder
     argv = list(sys.argv[1:] if argv is None else argv)
     model = json.load(open(argv[0]))
-    data = ConfigNode(json.load(open(argv[1])))
+    dp = json.load(open(argv[1])).get("dataset_param", {})
+    data = SimpleNamespace(dataset_param=SimpleNamespace(basic_parameters=dp.get("basic_parameters", {}),
+                                                       preprocess_parameters=dp.get("preprocess_parameters", {})))
     dev = "cuda" if torch.cuda.is_available() else "cpu"
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     if dev == "cuda":

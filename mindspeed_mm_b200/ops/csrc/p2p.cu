@@ -36,11 +36,16 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// true when *flag >= want (sequence numbers only grow); false after ~2^34 cycles.
+// Limit of every peer-flag wait in cycles (default 2^34, about 9 s); mm_p2p_set_wait_limit changes it, e.g. so that a
+// test of the time-out path finishes in a fraction of a second.
+__device__ long long g_wait_limit = 1LL << 34;
+
+// true when *flag >= want (sequence numbers only grow); false once the limit has passed.
 __device__ bool wait_flag_geq(const uint32_t* flag, uint32_t want) {
     const long long t0 = clock64();
+    const long long limit = g_wait_limit;
     while ((int32_t)(ld_acquire_sys(flag) - want) < 0) {
-        if (clock64() - t0 > (1LL << 34)) return false;
+        if (clock64() - t0 > limit) return false;
         __nanosleep(200);
     }
     return true;
@@ -333,4 +338,10 @@ MM_API int mm_p2p_copy(void* dst, const void* src, long long nbytes, int ctas, c
     if (nbytes == 0) return 0;
     p2p_copy_kernel<<<ctas, 256, 0, st>>>((uint4*)dst, (const uint4*)src, nbytes / 16);
     return (int)cudaGetLastError();
+}
+
+// cycles <= 0 restores the default.  Applies to kernels launched afterwards on the current device.
+MM_API int mm_p2p_set_wait_limit(long long cycles) {
+    const long long v = cycles > 0 ? cycles : (1LL << 34);
+    return (int)cudaMemcpyToSymbol(g_wait_limit, &v, sizeof(v));
 }

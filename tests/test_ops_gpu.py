@@ -361,3 +361,27 @@ def test_gated_delta_rule_native(lens, H):
     _close(o, o_ref, rtol=3e-2, atol=3e-3)
     for a, b in zip(grads, grads_ref):
         _close(a, b, rtol=5e-2, atol=5e-3)
+
+
+def test_peer_flag_wait_runs_out_and_reports_status():
+    """Failure detection on the device without a fault: a wait on a flag that nothing sets gives up after its limit,
+    the kernel returns, the status word says which kind of wait expired, and the context stays usable."""
+    from mindspeed_mm_b200.ops import native
+    L = native.lib()
+    dev = torch.device(DEV)
+    flags = torch.zeros(L.mm_p2p_flag_bytes() // 4, dtype=torch.int32, device=dev)
+    assert L.mm_p2p_set_wait_limit(1 << 27) == 0                     # ~70 ms at 1.9 GHz
+    try:
+        native.status_word(dev).zero_()
+        rc = L.mm_p2p_wait_done(flags.data_ptr(), 0, 1, 2, 0, native.status_word(dev).data_ptr(), native._st())
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert int(native.status_word(dev).item()) == 4              # MM_TIMEOUT_PEER
+        with pytest.raises(RuntimeError):
+            native.check_status(dev)
+    finally:
+        assert L.mm_p2p_set_wait_limit(0) == 0
+    x = torch.randn(64, 512, device=dev, dtype=torch.bfloat16)
+    w = torch.ones(512, device=dev, dtype=torch.bfloat16)
+    _close(ops.rms_norm(x, w), ref.rms_norm(x.float(), w.float()))
+    assert int(native.status_word(dev).item()) == 0

@@ -144,3 +144,39 @@ class Watchdog:
                 dist.destroy_process_group()
         finally:
             os._exit(3)
+
+
+class PeerHeartbeat:
+    """Failure detection between ranks on the host: every rank publishes ``hb/<rank> = (iteration, wall time)`` in
+    a key-value store after each step and checks its peers before the next launch.  A peer whose last beat is older
+    than ``timeout_s`` (or that announced ``leave()``) is reported, so the survivors stop BEFORE issuing another
+    collective instead of hanging in it.  The store is any ``torch.distributed.Store`` (TCPStore in production,
+    HashStore in single-process tests)."""
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 60.0):
+        self.store, self.rank, self.world, self.timeout_s = store, rank, world, timeout_s
+        self.beat(-1)
+
+    def beat(self, iteration: int) -> None:
+        self.store.set(f"hb/{self.rank}", f"{iteration}:{time.time():.3f}")
+
+    def leave(self, reason: str = "exit") -> None:
+        """A rank that stops on purpose (between steps, with nothing in flight) says so."""
+        self.store.set(f"hb/{self.rank}", f"left:{reason}")
+
+    def failed_peers(self) -> list:
+        """Ranks that left or whose heartbeat is stale."""
+        now, bad = time.time(), []
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            try:
+                v = self.store.get(f"hb/{r}").decode()
+            except Exception:  # noqa: BLE001 - key never written: the rank never joined
+                bad.append((r, "never joined"))
+                continue
+            if v.startswith("left:"):
+                bad.append((r, v[5:]))
+            elif now - float(v.split(":")[1]) > self.timeout_s:
+                bad.append((r, f"no heartbeat for {now - float(v.split(':')[1]):.1f}s"))
+        return bad

@@ -114,3 +114,14 @@ def test_ring_attention_over_peer_memory_2gpu():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     assert "ok=True" in _run_script(2, "dist_cp_check.py", "--cuda")
+
+
+@pytest.mark.parametrize("mode", ["heartbeat", "timeout"])
+def test_rank_leaving_between_steps_is_detected_on_the_host(mode):
+    """Fault injection on the host under gloo: the survivor stops through the heartbeat store, or its next
+    collective fails after the short process-group timeout."""
+    port = 29100 + (os.getpid() % 300)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "dist_failure_check.py"), mode]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=180, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert f"detected={mode} ok=True" in r.stdout + r.stderr, r.stdout[-2000:] + r.stderr[-2000:]

@@ -42,6 +42,8 @@ struct BwdParams {
     float scale, scale_log2;
     int* status;
     int split;              // dK/dV kernel: 1 = one CTA per QUERY head writing partial dk / dv [Tk, Nq, 128]
+    int dbg;                // timing experiments only (results are wrong when non-zero): 1 no exp2, 2 no dS math and
+                            // shared stores, 4 no S / dP products, 8 no dQ product
 };
 
 // delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (t, h)
@@ -195,40 +197,52 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag) || !mbar_wait(&k_full[st], ph, abort_flag)) return false;
                 fence_after_sync();
                 const uint32_t ka = smem_u32(sK + st * kTile);
+                if (!(p.dbg & 4)) {
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k) {
-                    const uint32_t off = (k >> 2) * kAtom + (k & 3) * 32;
-                    mma_ss(tS + st * 128, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024), idesc_kk,
-                           k ? 1u : 0u);
+                    for (int k = 0; k < HD / 16; ++k) {
+                        const uint32_t off = (k >> 2) * kAtom + (k & 3) * 32;
+                        mma_ss(tS + st * 128, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024), idesc_kk,
+                               k ? 1u : 0u);
+                    }
                 }
                 mma_commit(&s_full[st]);
                 return true;
             };
-            if (ok) ok = issue_s(0);
-            for (int j = 0; j < n_kv && ok; ++j) {
+            auto issue_dp = [&](int j) -> bool {
                 const int st = j & 1;
                 const uint32_t ph = (j >> 1) & 1;
-                // dP_j = dO V_j^T
-                if (!mbar_wait(dp_empty, (j & 1) ^ 1, abort_flag) || !mbar_wait(&v_full[st], ph, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(dp_empty, (j & 1) ^ 1, abort_flag) || !mbar_wait(&v_full[st], ph, abort_flag)) return false;
                 fence_after_sync();
                 const uint32_t va = smem_u32(sV + st * kTile);
+                if (!(p.dbg & 4)) {
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k) {
-                    const uint32_t off = (k >> 2) * kAtom + (k & 3) * 32;
-                    mma_ss(tdP, smem_desc_sw128(doa + off, 16, 1024), smem_desc_sw128(va + off, 16, 1024), idesc_kk, k ? 1u : 0u);
+                    for (int k = 0; k < HD / 16; ++k) {
+                        const uint32_t off = (k >> 2) * kAtom + (k & 3) * 32;
+                        mma_ss(tdP, smem_desc_sw128(doa + off, 16, 1024), smem_desc_sw128(va + off, 16, 1024), idesc_kk, k ? 1u : 0u);
+                    }
                 }
                 mma_commit(dp_full);
                 mma_commit(&v_empty[st]);
-                if (j + 1 < n_kv && !(ok = issue_s(j + 1))) break;
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            if (ok) ok = issue_dp(0);
+            for (int j = 0; j < n_kv && ok; ++j) {
+                const int st = j & 1;
+                // S and dP of the next tile run on the tensor pipe while the threads work on tile j; dP's single
+                // buffer is free as soon as the threads have pulled dP(j) into registers
+                if (j + 1 < n_kv && !(ok = issue_s(j + 1) && issue_dp(j + 1))) break;
                 // dQ += dS_j K_j
                 if (!mbar_wait(ds_full, j & 1, abort_flag)) { ok = false; break; }
                 fence_after_sync();
                 const uint32_t ka = smem_u32(sK + st * kTile);
+                if (!(p.dbg & 8)) {
 #pragma unroll
-                for (int k = 0; k < 128 / 16; ++k) {
-                    const uint64_t da = smem_desc_sw128(dsa + (k >> 2) * kAtom + (k & 3) * 32, 16, 1024);
-                    const uint64_t db = smem_desc_sw128(ka + k * 2048, kAtom, 1024);
-                    mma_ss(tdQ, da, db, idesc_kn, (j | k) ? 1u : 0u);
+                    for (int k = 0; k < 128 / 16; ++k) {
+                        const uint64_t da = smem_desc_sw128(dsa + (k >> 2) * kAtom + (k & 3) * 32, 16, 1024);
+                        const uint64_t db = smem_desc_sw128(ka + k * 2048, kAtom, 1024);
+                        mma_ss(tdQ, da, db, idesc_kn, (j | k) ? 1u : 0u);
+                    }
                 }
                 mma_commit(ds_empty);
                 mma_commit(&k_empty[st]);
@@ -251,47 +265,39 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int j = 0; j < n_kv; ++j) {
             const int st = j & 1;
             const uint32_t ph = (j >> 1) & 1;
-            if (!mbar_wait(&s_full[st], ph, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(&s_full[st], ph, abort_flag) || !mbar_wait(dp_full, j & 1, abort_flag)) { ok = false; break; }
             fence_after_sync();
-            uint32_t r[64];
+            uint32_t r[64], d[64];
             const uint32_t t_row = tS + st * 128 + half * 64 + lane_off;
             tmem_ld_32x32(t_row, r);
             tmem_ld_32x32(t_row + 32, r + 32);
+            tmem_ld_32x32(tdP + half * 64 + lane_off, d);
+            tmem_ld_32x32(tdP + half * 64 + lane_off + 32, d + 32);
             tmem_wait_ld();
             fence_before_sync();
             mbar_arrive(&s_empty[st]);
+            mbar_arrive(dp_empty);
             const int kbase = j * 128 + half * 64;
             const int limit = !row_ok ? -1 : (p.causal ? min(k_len - 1, qi + diag) : k_len - 1);
+            if (!(p.dbg & 1)) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                const float pr = exp2f(__uint_as_float(r[i]) * p.scale_log2 - lse2);
-                r[i] = __float_as_uint(kbase + i > limit ? 0.f : pr);
-            }
-            if (!mbar_wait(dp_full, j & 1, abort_flag)) { ok = false; break; }
-            fence_after_sync();
-            if (j > 0 && !mbar_wait(ds_empty, (j - 1) & 1, abort_flag)) { ok = false; break; }
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t d[32];
-                tmem_ld_32x32(tdP + half * 64 + lane_off + c * 32, d);
-                tmem_wait_ld();
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    uint4 w;
-                    float f[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        f[i] = __uint_as_float(r[c * 32 + g * 8 + i]) * (__uint_as_float(d[g * 8 + i]) - dlt);
-                    w.x = pack2(f[0], f[1]);
-                    w.y = pack2(f[2], f[3]);
-                    w.z = pack2(f[4], f[5]);
-                    w.w = pack2(f[6], f[7]);
-                    const int gg = c * 4 + g;      // 16-byte group of 8 keys inside this warpgroup's 64-key atom
-                    *reinterpret_cast<uint4*>(sdS + half * kAtom + row * 128 + ((gg ^ (row & 7)) << 4)) = w;
+                for (int i = 0; i < 64; ++i) {
+                    const float pr = exp2f(__uint_as_float(r[i]) * p.scale_log2 - lse2);
+                    r[i] = __float_as_uint(kbase + i > limit ? 0.f : pr * (__uint_as_float(d[i]) - dlt));
                 }
             }
-            fence_before_sync();
-            mbar_arrive(dp_empty);
+            if (j > 0 && !mbar_wait(ds_empty, (j - 1) & 1, abort_flag)) { ok = false; break; }
+            if (!(p.dbg & 2)) {
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    uint4 w;
+                    w.x = pack2(__uint_as_float(r[8 * g + 0]), __uint_as_float(r[8 * g + 1]));
+                    w.y = pack2(__uint_as_float(r[8 * g + 2]), __uint_as_float(r[8 * g + 3]));
+                    w.z = pack2(__uint_as_float(r[8 * g + 4]), __uint_as_float(r[8 * g + 5]));
+                    w.w = pack2(__uint_as_float(r[8 * g + 6]), __uint_as_float(r[8 * g + 7]));
+                    *reinterpret_cast<uint4*>(sdS + half * kAtom + row * 128 + ((g ^ (row & 7)) << 4)) = w;
+                }
+            }
             fence_proxy_async();
             mbar_arrive(ds_full);
         }
@@ -336,7 +342,8 @@ constexpr int BQ2 = 64;
 constexpr int kQTile = BQ2 * HD * 2;       // 16 KiB: a 64-row tile of Q / dO
 constexpr int kQAtom = BQ2 * 128;          // 8 KiB
 constexpr int kPTile = 128 * BQ2 * 2;      // 16 KiB: P^T / dS^T, one swizzle atom of 128 rows
-constexpr int kSmemDkv = 2 * kTile + 4 * kQTile + 2 * kPTile + 2048 + 1024;
+constexpr int kRing = 3;                   // Q_i / dO_i ring depth (the TMEM buffers of S^T / dP^T stay double)
+constexpr int kSmemDkv = 2 * kTile + 2 * kRing * kQTile + 2 * kPTile + 2048 + 1024;
 
 __global__ void __launch_bounds__(320, 1)
 fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -346,22 +353,22 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sK = smem;
     uint8_t* sV = sK + kTile;
-    uint8_t* sQ = sV + kTile;            // [2]
-    uint8_t* sdO = sQ + 2 * kQTile;      // [2]
-    uint8_t* sP = sdO + 2 * kQTile;
+    uint8_t* sQ = sV + kTile;            // [kRing]
+    uint8_t* sdO = sQ + kRing * kQTile;  // [kRing]
+    uint8_t* sP = sdO + kRing * kQTile;
     uint8_t* sdS = sP + kPTile;
     float* s_lse = reinterpret_cast<float*>(sdS + kPTile);    // [2][64]
     float* s_dlt = s_lse + 2 * BQ2;                            // [2][64]
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_dlt + 2 * BQ2);
     uint64_t* kv_full = bars + 0;
-    uint64_t* full = bars + 1;        // [2]  Q_i / dO_i landed
-    uint64_t* empty = bars + 3;       // [2]
-    uint64_t* st_full = bars + 5;     // [2]  S^T / dP^T ready
-    uint64_t* st_empty = bars + 7;    // [2]
-    uint64_t* pds_full = bars + 9;
-    uint64_t* pds_empty = bars + 10;
-    uint64_t* acc_full = bars + 11;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    uint64_t* full = bars + 1;        // [kRing]  Q_i / dO_i landed
+    uint64_t* empty = bars + 1 + kRing;   // [kRing]
+    uint64_t* st_full = bars + 1 + 2 * kRing;     // [2]  S^T / dP^T ready
+    uint64_t* st_empty = st_full + 2;             // [2]
+    uint64_t* pds_full = st_full + 4;
+    uint64_t* pds_empty = st_full + 5;
+    uint64_t* acc_full = st_full + 6;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(st_full + 7);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -382,9 +389,11 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     if (threadIdx.x == 0) {
         mbar_init(kv_full, 1);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kRing; ++i) {
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
             mbar_init(&st_full[i], 1);
             mbar_init(&st_empty[i], 256);
         }
@@ -416,8 +425,8 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             tma_load_3d(sV, &tmV, kv_full, 0, kv_head, k_begin + kv0);
             tma_load_3d(sV + kAtom, &tmV, kv_full, 64, kv_head, k_begin + kv0);
             for (int it = 0; it < n_it; ++it) {
-                const int st = it & 1;
-                const uint32_t ph = (it >> 1) & 1;
+                const int st = it % kRing;
+                const uint32_t ph = (it / kRing) & 1;
                 const int head = head0 + it / per_head;
                 const int row = q_begin + (i_min + it % per_head) * BQ2;
                 if (!mbar_wait(&empty[st], ph ^ 1, abort_flag)) { atomicExch(p.status, MM_TIMEOUT_TMA); break; }
@@ -435,11 +444,11 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             bool ok = mbar_wait(kv_full, 0, abort_flag);
             const uint32_t ka = smem_u32(sK), va = smem_u32(sV), pa = smem_u32(sP), dsa = smem_u32(sdS);
             auto issue_t = [&](int it) -> bool {
-                const int st = it & 1;
-                const uint32_t ph = (it >> 1) & 1;
-                if (!mbar_wait(&st_empty[st], ph ^ 1, abort_flag) || !mbar_wait(&full[st], ph, abort_flag)) return false;
+                const int st = it & 1, rs = it % kRing;
+                const uint32_t ph = (it >> 1) & 1, rph = (it / kRing) & 1;
+                if (!mbar_wait(&st_empty[st], ph ^ 1, abort_flag) || !mbar_wait(&full[rs], rph, abort_flag)) return false;
                 fence_after_sync();
-                const uint32_t qa = smem_u32(sQ + st * kQTile), doa = smem_u32(sdO + st * kQTile);
+                const uint32_t qa = smem_u32(sQ + rs * kQTile), doa = smem_u32(sdO + rs * kQTile);
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
                     const uint32_t aoff = (k >> 2) * kAtom + (k & 3) * 32;
@@ -454,11 +463,11 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             };
             if (ok) ok = issue_t(0);
             for (int it = 0; it < n_it && ok; ++it) {
-                const int st = it & 1;
+                const int rs = it % kRing;
                 if (it + 1 < n_it && !(ok = issue_t(it + 1))) break;
                 if (!mbar_wait(pds_full, it & 1, abort_flag)) { ok = false; break; }
                 fence_after_sync();
-                const uint32_t qa = smem_u32(sQ + st * kQTile), doa = smem_u32(sdO + st * kQTile);
+                const uint32_t qa = smem_u32(sQ + rs * kQTile), doa = smem_u32(sdO + rs * kQTile);
 #pragma unroll
                 for (int k = 0; k < BQ2 / 16; ++k) {
                     mma_ss(tdV, smem_desc_sw128(pa + k * 32, 16, 1024), smem_desc_sw128(doa + k * 2048, kQAtom, 1024), idesc_acc,
@@ -467,7 +476,7 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                            (it | k) ? 1u : 0u);
                 }
                 mma_commit(pds_empty);
-                mma_commit(&empty[st]);
+                mma_commit(&empty[rs]);
             }
             if (ok) mma_commit(acc_full);
             if (!ok) atomicExch(p.status, MM_TIMEOUT_MMA);
@@ -599,6 +608,8 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
                        float* delta, void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, int* plan, int T, int Tk,
                        int n_seqs, int Nq, int Nkv, int D, long long q_ts, long long k_ts, long long v_ts, int causal,
                        float scale, int split_heads, int variant, int* status, cudaStream_t st) {
+    const int dbg = variant >> 8;        // timing experiments (see BwdParams::dbg)
+    variant &= 0xff;
     if (D != HD || Nq % Nkv || (q_ts | k_ts | v_ts) % 8) return -1;
     if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o | (uintptr_t)dO | (uintptr_t)dq | (uintptr_t)dk |
          (uintptr_t)dv) & 15)
@@ -625,7 +636,7 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
     if (cudaFuncSetAttribute(fmha_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDq) != cudaSuccess) return -3;
     if (cudaFuncSetAttribute(fmha_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkv) != cudaSuccess) return -3;
     BwdParams p{cu_q, cu_k, q_seq, q_r0, q_n, lse, delta, (bf16*)dq, (bf16*)dk, (bf16*)dv, T, Tk, Nq, Nkv, causal, scale,
-                scale * kLog2e, status, split_heads};
+                scale * kLog2e, status, split_heads, dbg};
     BwdParams pk = p;
     pk.tile_seq = k_seq;
     pk.tile_r0 = k_r0;
@@ -643,7 +654,7 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
         fmha_bwd_dkv_pp_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkvPP, st>>>(tQ64, tK, tV, tdO64, pk);
         return (int)cudaGetLastError();
     }
-    fmha_bwd_dq_kernel<<<dim3(mq, Nq), 320, kSmemDq, st>>>(tQ, tK, tV, tdO, p);
-    fmha_bwd_dkv_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkv, st>>>(tQ64, tK, tV, tdO64, pk);
+    if (!(dbg & 32)) fmha_bwd_dq_kernel<<<dim3(mq, Nq), 320, kSmemDq, st>>>(tQ, tK, tV, tdO, p);
+    if (!(dbg & 16)) fmha_bwd_dkv_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkv, st>>>(tQ64, tK, tV, tdO64, pk);
     return (int)cudaGetLastError();
 }

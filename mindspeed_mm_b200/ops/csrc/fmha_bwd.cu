@@ -42,8 +42,6 @@ struct BwdParams {
     float scale, scale_log2;
     int* status;
     int split;              // dK/dV kernel: 1 = one CTA per QUERY head writing partial dk / dv [Tk, Nq, 128]
-    int dbg;                // timing experiments only (results are wrong when non-zero): 1 no exp2, 2 no dS math and
-                            // shared stores, 4 no S / dP products, 8 no dQ product
 };
 
 // delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (t, h)
@@ -90,7 +88,8 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 }
 
 // ============================================================================================== dQ
-constexpr int kSmemDq = 7 * kTile + 1024 + 1024;
+constexpr int kRingK = 3;                 // K ring depth of the dQ kernel (V stays 2 deep: it is released right after dP)
+constexpr int kSmemDq = (2 + kRingK + 2) * kTile + 1024 + 1024;
 
 __global__ void __launch_bounds__(320, 1)
 fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -100,23 +99,21 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;
     uint8_t* sdO = sQ + kTile;
-    uint8_t* sK = sdO + kTile;          // [2]
-    uint8_t* sV = sK + 2 * kTile;       // [2]
-    uint8_t* sdS = sV + 2 * kTile;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + kTile);
+    uint8_t* sK = sdO + kTile;              // [kRingK]
+    uint8_t* sV = sK + kRingK * kTile;      // [2]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * kTile);
     uint64_t* q_full = bars + 0;
-    uint64_t* k_full = bars + 1;     // [2]
-    uint64_t* k_empty = bars + 3;    // [2]
-    uint64_t* v_full = bars + 5;     // [2]
-    uint64_t* v_empty = bars + 7;    // [2]
-    uint64_t* s_full = bars + 9;     // [2]
-    uint64_t* s_empty = bars + 11;   // [2]
-    uint64_t* dp_full = bars + 13;
-    uint64_t* dp_empty = bars + 14;
-    uint64_t* ds_full = bars + 15;
-    uint64_t* ds_empty = bars + 16;
-    uint64_t* dq_full = bars + 17;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+    uint64_t* k_full = bars + 1;              // [kRingK]
+    uint64_t* k_empty = k_full + kRingK;      // [kRingK]
+    uint64_t* v_full = k_empty + kRingK;      // [2]
+    uint64_t* v_empty = v_full + 2;           // [2]
+    uint64_t* s_full = v_full + 4;            // [2]
+    uint64_t* s_empty = v_full + 6;           // [2]
+    uint64_t* dp_full = v_full + 8;
+    uint64_t* dp_empty = v_full + 9;
+    uint64_t* ds_full = v_full + 10;
+    uint64_t* dq_full = v_full + 11;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(v_full + 12);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -134,9 +131,11 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kRingK; ++i) {
             mbar_init(&k_full[i], 1);
             mbar_init(&k_empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
             mbar_init(&v_full[i], 1);
             mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1);
@@ -145,7 +144,6 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_init(dp_full, 1);
         mbar_init(dp_empty, 256);
         mbar_init(ds_full, 256);
-        mbar_init(ds_empty, 1);
         mbar_init(dq_full, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -172,13 +170,13 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             tma_load_3d(sdO, &tmdO, q_full, 0, head, q_begin + q0);
             tma_load_3d(sdO + kAtom, &tmdO, q_full, 64, head, q_begin + q0);
             for (int j = 0; j < n_kv; ++j) {
-                const int st = j & 1;
-                const uint32_t ph = (j >> 1) & 1;
+                const int st = j & 1, ks = j % kRingK;
+                const uint32_t ph = (j >> 1) & 1, kph = (j / kRingK) & 1;
                 const int row = k_begin + j * 128;
-                if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) { atomicExch(p.status, MM_TIMEOUT_TMA); break; }
-                mbar_expect_tx(&k_full[st], kTile);
-                tma_load_3d(sK + st * kTile, &tmK, &k_full[st], 0, kv_head, row);
-                tma_load_3d(sK + st * kTile + kAtom, &tmK, &k_full[st], 64, kv_head, row);
+                if (!mbar_wait(&k_empty[ks], kph ^ 1, abort_flag)) { atomicExch(p.status, MM_TIMEOUT_TMA); break; }
+                mbar_expect_tx(&k_full[ks], kTile);
+                tma_load_3d(sK + ks * kTile, &tmK, &k_full[ks], 0, kv_head, row);
+                tma_load_3d(sK + ks * kTile + kAtom, &tmK, &k_full[ks], 64, kv_head, row);
                 if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) { atomicExch(p.status, MM_TIMEOUT_TMA); break; }
                 mbar_expect_tx(&v_full[st], kTile);
                 tma_load_3d(sV + st * kTile, &tmV, &v_full[st], 0, kv_head, row);
@@ -190,20 +188,18 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             constexpr uint32_t idesc_kk = idesc_bf16(128, 128, 0, 0);     // both operands K-major
             constexpr uint32_t idesc_kn = idesc_bf16(128, 128, 0, 1);     // B = K_j as [N = d, K = kv]: MN-major
             bool ok = mbar_wait(q_full, 0, abort_flag);
-            const uint32_t qa = smem_u32(sQ), doa = smem_u32(sdO), dsa = smem_u32(sdS);
+            const uint32_t qa = smem_u32(sQ), doa = smem_u32(sdO);
             auto issue_s = [&](int j) -> bool {
-                const int st = j & 1;
-                const uint32_t ph = (j >> 1) & 1;
-                if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag) || !mbar_wait(&k_full[st], ph, abort_flag)) return false;
+                const int st = j & 1, ks = j % kRingK;
+                const uint32_t ph = (j >> 1) & 1, kph = (j / kRingK) & 1;
+                if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag) || !mbar_wait(&k_full[ks], kph, abort_flag)) return false;
                 fence_after_sync();
-                const uint32_t ka = smem_u32(sK + st * kTile);
-                if (!(p.dbg & 4)) {
+                const uint32_t ka = smem_u32(sK + ks * kTile);
 #pragma unroll
-                    for (int k = 0; k < HD / 16; ++k) {
-                        const uint32_t off = (k >> 2) * kAtom + (k & 3) * 32;
-                        mma_ss(tS + st * 128, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024), idesc_kk,
-                               k ? 1u : 0u);
-                    }
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (k >> 2) * kAtom + (k & 3) * 32;
+                    mma_ss(tS + st * 128, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024), idesc_kk,
+                           k ? 1u : 0u);
                 }
                 mma_commit(&s_full[st]);
                 return true;
@@ -214,12 +210,10 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 if (!mbar_wait(dp_empty, (j & 1) ^ 1, abort_flag) || !mbar_wait(&v_full[st], ph, abort_flag)) return false;
                 fence_after_sync();
                 const uint32_t va = smem_u32(sV + st * kTile);
-                if (!(p.dbg & 4)) {
 #pragma unroll
-                    for (int k = 0; k < HD / 16; ++k) {
-                        const uint32_t off = (k >> 2) * kAtom + (k & 3) * 32;
-                        mma_ss(tdP, smem_desc_sw128(doa + off, 16, 1024), smem_desc_sw128(va + off, 16, 1024), idesc_kk, k ? 1u : 0u);
-                    }
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (k >> 2) * kAtom + (k & 3) * 32;
+                    mma_ss(tdP, smem_desc_sw128(doa + off, 16, 1024), smem_desc_sw128(va + off, 16, 1024), idesc_kk, k ? 1u : 0u);
                 }
                 mma_commit(dp_full);
                 mma_commit(&v_empty[st]);
@@ -235,17 +229,18 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 // dQ += dS_j K_j
                 if (!mbar_wait(ds_full, j & 1, abort_flag)) { ok = false; break; }
                 fence_after_sync();
-                const uint32_t ka = smem_u32(sK + st * kTile);
-                if (!(p.dbg & 8)) {
+                const int ks = j % kRingK;
+                const uint32_t ka = smem_u32(sK + ks * kTile);
+                {
+                    // dS(j) sits in the columns of S[st] that the row threads emptied into registers: keys 0..63 in
+                    // columns 0..31, keys 64..127 in columns 64..95 (bf16 pairs); TS-form product
 #pragma unroll
                     for (int k = 0; k < 128 / 16; ++k) {
-                        const uint64_t da = smem_desc_sw128(dsa + (k >> 2) * kAtom + (k & 3) * 32, 16, 1024);
                         const uint64_t db = smem_desc_sw128(ka + k * 2048, kAtom, 1024);
-                        mma_ss(tdQ, da, db, idesc_kn, (j | k) ? 1u : 0u);
+                        mma_ts(tdQ, tS + st * 128 + (k >> 2) * 64 + (k & 3) * 8, db, idesc_kn, (j | k) ? 1u : 0u);
                     }
                 }
-                mma_commit(ds_empty);
-                mma_commit(&k_empty[st]);
+                mma_commit(&k_empty[ks]);
             }
             if (ok) mma_commit(dq_full);
             if (!ok) atomicExch(p.status, MM_TIMEOUT_MMA);
@@ -279,26 +274,16 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             mbar_arrive(dp_empty);
             const int kbase = j * 128 + half * 64;
             const int limit = !row_ok ? -1 : (p.causal ? min(k_len - 1, qi + diag) : k_len - 1);
-            if (!(p.dbg & 1)) {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    const float pr = exp2f(__uint_as_float(r[i]) * p.scale_log2 - lse2);
-                    r[i] = __float_as_uint(kbase + i > limit ? 0.f : pr * (__uint_as_float(d[i]) - dlt));
-                }
+            for (int i = 0; i < 64; ++i) {
+                const float pr = exp2f(__uint_as_float(r[i]) * p.scale_log2 - lse2);
+                r[i] = __float_as_uint(kbase + i > limit ? 0.f : pr * (__uint_as_float(d[i]) - dlt));
             }
-            if (j > 0 && !mbar_wait(ds_empty, (j - 1) & 1, abort_flag)) { ok = false; break; }
-            if (!(p.dbg & 2)) {
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    uint4 w;
-                    w.x = pack2(__uint_as_float(r[8 * g + 0]), __uint_as_float(r[8 * g + 1]));
-                    w.y = pack2(__uint_as_float(r[8 * g + 2]), __uint_as_float(r[8 * g + 3]));
-                    w.z = pack2(__uint_as_float(r[8 * g + 4]), __uint_as_float(r[8 * g + 5]));
-                    w.w = pack2(__uint_as_float(r[8 * g + 6]), __uint_as_float(r[8 * g + 7]));
-                    *reinterpret_cast<uint4*>(sdS + half * kAtom + row * 128 + ((g ^ (row & 7)) << 4)) = w;
-                }
-            }
-            fence_proxy_async();
+            for (int i = 0; i < 32; ++i) d[i] = pack2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+            tmem_st_32x32(t_row, d);             // over the first 32 of the 64 fp32 columns this thread just read
+            tmem_wait_st();
+            fence_before_sync();
             mbar_arrive(ds_full);
         }
         bf16* dst = p.dq + ((size_t)(q_begin + qi) * p.Nq + head) * HD + half * 64;
@@ -342,8 +327,8 @@ constexpr int BQ2 = 64;
 constexpr int kQTile = BQ2 * HD * 2;       // 16 KiB: a 64-row tile of Q / dO
 constexpr int kQAtom = BQ2 * 128;          // 8 KiB
 constexpr int kPTile = 128 * BQ2 * 2;      // 16 KiB: P^T / dS^T, one swizzle atom of 128 rows
-constexpr int kRing = 3;                   // Q_i / dO_i ring depth (the TMEM buffers of S^T / dP^T stay double)
-constexpr int kSmemDkv = 2 * kTile + 2 * kRing * kQTile + 2 * kPTile + 2048 + 1024;
+constexpr int kRing = 4;                   // Q_i / dO_i ring depth (the TMEM buffers of S^T / dP^T stay double)
+constexpr int kSmemDkv = 2 * kTile + 2 * kRing * kQTile + 2048 + 1024;
 
 __global__ void __launch_bounds__(320, 1)
 fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -355,9 +340,7 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     uint8_t* sV = sK + kTile;
     uint8_t* sQ = sV + kTile;            // [kRing]
     uint8_t* sdO = sQ + kRing * kQTile;  // [kRing]
-    uint8_t* sP = sdO + kRing * kQTile;
-    uint8_t* sdS = sP + kPTile;
-    float* s_lse = reinterpret_cast<float*>(sdS + kPTile);    // [2][64]
+    float* s_lse = reinterpret_cast<float*>(sdO + kRing * kQTile);    // [2][64]
     float* s_dlt = s_lse + 2 * BQ2;                            // [2][64]
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_dlt + 2 * BQ2);
     uint64_t* kv_full = bars + 0;
@@ -366,9 +349,8 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     uint64_t* st_full = bars + 1 + 2 * kRing;     // [2]  S^T / dP^T ready
     uint64_t* st_empty = st_full + 2;             // [2]
     uint64_t* pds_full = st_full + 4;
-    uint64_t* pds_empty = st_full + 5;
-    uint64_t* acc_full = st_full + 6;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(st_full + 7);
+    uint64_t* acc_full = st_full + 5;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(st_full + 6);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -398,7 +380,6 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             mbar_init(&st_empty[i], 256);
         }
         mbar_init(pds_full, 256);
-        mbar_init(pds_empty, 1);
         mbar_init(acc_full, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -442,7 +423,7 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             constexpr uint32_t idesc_t = idesc_bf16(128, BQ2, 0, 0);       // S^T, dP^T: N = 64 query rows
             constexpr uint32_t idesc_acc = idesc_bf16(128, 128, 0, 1);     // dV, dK: B = dO_i / Q_i as [N = d, K = q]
             bool ok = mbar_wait(kv_full, 0, abort_flag);
-            const uint32_t ka = smem_u32(sK), va = smem_u32(sV), pa = smem_u32(sP), dsa = smem_u32(sdS);
+            const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
             auto issue_t = [&](int it) -> bool {
                 const int st = it & 1, rs = it % kRing;
                 const uint32_t ph = (it >> 1) & 1, rph = (it / kRing) & 1;
@@ -468,14 +449,15 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 if (!mbar_wait(pds_full, it & 1, abort_flag)) { ok = false; break; }
                 fence_after_sync();
                 const uint32_t qa = smem_u32(sQ + rs * kQTile), doa = smem_u32(sdO + rs * kQTile);
+                // P^T / dS^T sit in the S^T / dP^T columns the row threads emptied (queries 0..31 in columns 0..15,
+                // queries 32..63 in columns 32..47, bf16 pairs): TS-form products, no shared-memory round trip
+                const int sb = it & 1;
 #pragma unroll
                 for (int k = 0; k < BQ2 / 16; ++k) {
-                    mma_ss(tdV, smem_desc_sw128(pa + k * 32, 16, 1024), smem_desc_sw128(doa + k * 2048, kQAtom, 1024), idesc_acc,
-                           (it | k) ? 1u : 0u);
-                    mma_ss(tdK, smem_desc_sw128(dsa + k * 32, 16, 1024), smem_desc_sw128(qa + k * 2048, kQAtom, 1024), idesc_acc,
-                           (it | k) ? 1u : 0u);
+                    const uint32_t acol = sb * BQ2 + (k >> 1) * 32 + (k & 1) * 8;
+                    mma_ts(tdV, tST + acol, smem_desc_sw128(doa + k * 2048, kQAtom, 1024), idesc_acc, (it | k) ? 1u : 0u);
+                    mma_ts(tdK, tdPT + acol, smem_desc_sw128(qa + k * 2048, kQAtom, 1024), idesc_acc, (it | k) ? 1u : 0u);
                 }
-                mma_commit(pds_empty);
                 mma_commit(&empty[rs]);
             }
             if (ok) mma_commit(acc_full);
@@ -529,23 +511,17 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 s[c] = __float_as_uint(pv);
                 d[c] = __float_as_uint(pv * (__uint_as_float(d[c]) - dl[c]));
             }
-            if (it > 0 && !mbar_wait(pds_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
+            uint32_t pw[16], dw[16];
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                uint4 w, x;
-                w.x = pack2(__uint_as_float(s[8 * g + 0]), __uint_as_float(s[8 * g + 1]));
-                w.y = pack2(__uint_as_float(s[8 * g + 2]), __uint_as_float(s[8 * g + 3]));
-                w.z = pack2(__uint_as_float(s[8 * g + 4]), __uint_as_float(s[8 * g + 5]));
-                w.w = pack2(__uint_as_float(s[8 * g + 6]), __uint_as_float(s[8 * g + 7]));
-                x.x = pack2(__uint_as_float(d[8 * g + 0]), __uint_as_float(d[8 * g + 1]));
-                x.y = pack2(__uint_as_float(d[8 * g + 2]), __uint_as_float(d[8 * g + 3]));
-                x.z = pack2(__uint_as_float(d[8 * g + 4]), __uint_as_float(d[8 * g + 5]));
-                x.w = pack2(__uint_as_float(d[8 * g + 6]), __uint_as_float(d[8 * g + 7]));
-                const int off = row * 128 + (((half * 4 + g) ^ (row & 7)) << 4);
-                *reinterpret_cast<uint4*>(sP + off) = w;
-                *reinterpret_cast<uint4*>(sdS + off) = x;
+            for (int i = 0; i < 16; ++i) {
+                pw[i] = pack2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+                dw[i] = pack2(__uint_as_float(d[2 * i]), __uint_as_float(d[2 * i + 1]));
             }
-            fence_proxy_async();
+            // over the first 16 of the 32 fp32 columns this thread has just read from each accumulator
+            tmem_st_32x16(tST + st * BQ2 + half * 32 + lane_off, pw);
+            tmem_st_32x16(tdPT + st * BQ2 + half * 32 + lane_off, dw);
+            tmem_wait_st();
+            fence_before_sync();
             mbar_arrive(pds_full);
         }
         bf16* dvp = p.dv + ((size_t)(k_begin + kj) * out_heads + out_head) * HD + half * 64;
@@ -608,8 +584,6 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
                        float* delta, void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, int* plan, int T, int Tk,
                        int n_seqs, int Nq, int Nkv, int D, long long q_ts, long long k_ts, long long v_ts, int causal,
                        float scale, int split_heads, int variant, int* status, cudaStream_t st) {
-    const int dbg = variant >> 8;        // timing experiments (see BwdParams::dbg)
-    variant &= 0xff;
     if (D != HD || Nq % Nkv || (q_ts | k_ts | v_ts) % 8) return -1;
     if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o | (uintptr_t)dO | (uintptr_t)dq | (uintptr_t)dk |
          (uintptr_t)dv) & 15)
@@ -636,7 +610,7 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
     if (cudaFuncSetAttribute(fmha_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDq) != cudaSuccess) return -3;
     if (cudaFuncSetAttribute(fmha_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkv) != cudaSuccess) return -3;
     BwdParams p{cu_q, cu_k, q_seq, q_r0, q_n, lse, delta, (bf16*)dq, (bf16*)dk, (bf16*)dv, T, Tk, Nq, Nkv, causal, scale,
-                scale * kLog2e, status, split_heads, dbg};
+                scale * kLog2e, status, split_heads};
     BwdParams pk = p;
     pk.tile_seq = k_seq;
     pk.tile_r0 = k_r0;
@@ -654,7 +628,22 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
         fmha_bwd_dkv_pp_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkvPP, st>>>(tQ64, tK, tV, tdO64, pk);
         return (int)cudaGetLastError();
     }
-    if (!(dbg & 32)) fmha_bwd_dq_kernel<<<dim3(mq, Nq), 320, kSmemDq, st>>>(tQ, tK, tV, tdO, p);
-    if (!(dbg & 16)) fmha_bwd_dkv_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkv, st>>>(tQ64, tK, tV, tdO64, pk);
+    if (variant == 4) {      // dQ with Q / dO / dS in tensor memory over 64-key steps
+        CUtensorMap tK64, tV64;
+        if ((r = make_tmap_3d(&tK64, k, HD, Nkv, Tk, HD, k_ts, 64, 1, BK))) return 7000 + r;
+        if ((r = make_tmap_3d(&tV64, v, HD, Nkv, Tk, HD, v_ts, 64, 1, BK))) return 8000 + r;
+        if (cudaFuncSetAttribute(fmha_bwd_dq_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDqTs) != cudaSuccess)
+            return -3;
+        fmha_bwd_dq_ts_kernel<<<dim3(mq, Nq), 320, kSmemDqTs, st>>>(tQ, tK64, tV64, tdO, p);
+    } else {
+        fmha_bwd_dq_kernel<<<dim3(mq, Nq), 320, kSmemDq, st>>>(tQ, tK, tV, tdO, p);
+    }
+    if (variant == 3) {      // dK/dV with every A operand in tensor memory (TS-form products)
+        if (cudaFuncSetAttribute(fmha_bwd_dkv_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkvTs) != cudaSuccess)
+            return -3;
+        fmha_bwd_dkv_ts_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkvTs, st>>>(tQ64, tK, tV, tdO64, pk);
+        return (int)cudaGetLastError();
+    }
+    fmha_bwd_dkv_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkv, st>>>(tQ64, tK, tV, tdO64, pk);
     return (int)cudaGetLastError();
 }

@@ -2,11 +2,12 @@
 // head dim 128, bf16 in / bf16 out + fp32 log-sum-exp (for ring merging and for the backward pass).
 //
 // One CTA = one 128-row query tile of one head.  It walks the 128-key tiles of its sequence:
-//   warp 0      TMA producer: Q once, then K_j / V_j into 2-stage rings (128B-swizzled boxes of 64 x 128)
+//   warp 0      TMA producer: Q once, then K_j / V_j into 3-stage rings (128B-swizzled boxes of 64 x 128)
 //   warp 1      MMA issuer:   S_j = Q K_j^T  -> TMEM S[j&1]      (issued one tile ahead of the softmax)
-//                             O_j = P_j V_j  -> TMEM O[j&1]      (fresh accumulator per tile)
+//                             O_j = P_j V_j  -> TMEM O[j&1]      (fresh accumulator per tile; P_j is the A operand
+//                                                                 read from tensor memory)
 //   warps 2-5   softmax:      thread = query row; pulls its 128-column row of S into registers in one go, writes
-//                             P_j (bf16) into swizzled smem as the A operand of the PV MMA, keeps m / l
+//                             P_j (bf16 pairs) back over the first 64 columns of S[j&1], keeps m / l
 //   warps 6-9   accumulate:   O_acc = O_acc * 2^(m_old - m_new) + O_j in registers (reads O_j from TMEM),
 //                             final normalise, bf16 store
 // TMEM: S double buffer (2 x 128 cols) + O double buffer (2 x 128 cols) = 512 columns.
@@ -22,7 +23,8 @@ constexpr int BQ = 128, BKV = 128, HD = 128;
 constexpr int kThreads = 320;
 constexpr int kTileBytes = BQ * HD * 2;   // 32 KiB: Q, K, V and P tiles all have this size
 constexpr int kAtomBytes = 128 * 128;     // one 64-element-wide swizzle atom of 128 rows
-constexpr int kSmem = 6 * kTileBytes + 4096 + 1024;   // Q + 2K + 2V + P + (barriers, alpha ring, l) + align
+constexpr int kRing = 3;                  // K and V ring depth
+constexpr int kSmem = (1 + 2 * kRing) * kTileBytes + 2048 + 1024;   // Q + 3K + 3V + (barriers, alpha ring, l) + align = 227 KB
 
 struct FmhaParams {
     const int* cu_q;
@@ -61,26 +63,23 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + kTileBytes;
-    uint8_t* sV = sK + 2 * kTileBytes;
-    uint8_t* sP = sV + 2 * kTileBytes;
-    uint8_t* aux = sP + kTileBytes;
+    uint8_t* sV = sK + kRing * kTileBytes;
+    uint8_t* aux = sV + kRing * kTileBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(aux);
     uint64_t* q_full = bars + 0;
-    uint64_t* k_full = bars + 1;    // [2]
-    uint64_t* k_empty = bars + 3;   // [2]
-    uint64_t* v_full = bars + 5;    // [2]
-    uint64_t* v_empty = bars + 7;   // [2]
-    uint64_t* s_full = bars + 9;    // [2]
-    uint64_t* s_empty = bars + 11;  // [2]
-    uint64_t* p_full = bars + 13;
-    uint64_t* p_empty = bars + 14;
-    uint64_t* o_full = bars + 15;   // [2]
-    uint64_t* o_empty = bars + 17;  // [2]
-    uint64_t* fin = bars + 19;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    uint64_t* k_full = bars + 1;    // [kRing]
+    uint64_t* k_empty = bars + 4;   // [kRing]
+    uint64_t* v_full = bars + 7;    // [kRing]
+    uint64_t* v_empty = bars + 10;  // [kRing]
+    uint64_t* s_full = bars + 13;   // [2]
+    uint64_t* p_full = bars + 15;   // [2]
+    uint64_t* o_full = bars + 17;   // [2]
+    uint64_t* o_empty = bars + 19;  // [2]
+    uint64_t* fin = bars + 21;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* alpha_ring = reinterpret_cast<float*>(aux + 256);   // [4][128]
-    float* l_final = alpha_ring + 4 * 128;                      // [128]
+    float* alpha_ring = reinterpret_cast<float*>(aux + 256);   // [2][128]
+    float* l_final = alpha_ring + 2 * 128;                      // [128]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seq = p.tile_seq[blockIdx.x];
@@ -96,18 +95,18 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kRing; ++i) {
             mbar_init(&k_full[i], 1);
             mbar_init(&k_empty[i], 1);
             mbar_init(&v_full[i], 1);
             mbar_init(&v_empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
             mbar_init(&s_full[i], 1);
-            mbar_init(&s_empty[i], 128);
+            mbar_init(&p_full[i], 128);
             mbar_init(&o_full[i], 1);
             mbar_init(&o_empty[i], 128);
         }
-        mbar_init(p_full, 128);
-        mbar_init(p_empty, 1);
         mbar_init(fin, 128);
         *abort_flag = 0;
         fence_barrier_init();
@@ -132,8 +131,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tma_load_3d(sQ, &tmQ, q_full, 0, head, q_begin + q0);
             tma_load_3d(sQ + kAtomBytes, &tmQ, q_full, 64, head, q_begin + q0);
             for (int j = 0; j < n_kv; ++j) {
-                const int st = j & 1;
-                const uint32_t ph = (j >> 1) & 1;
+                const int st = j % kRing;
+                const uint32_t ph = (j / kRing) & 1;
                 const int row = k_begin + j * BKV;
                 if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) { atomicExch(p.status, MM_TIMEOUT_TMA); break; }
                 mbar_expect_tx(&k_full[st], kTileBytes);
@@ -152,12 +151,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             constexpr uint32_t idesc_pv = idesc_bf16(BQ, HD, 0, 1);
             bool ok = mbar_wait(q_full, 0, abort_flag);
             auto issue_qk = [&](int j) -> bool {
-                const int st = j & 1;
-                const uint32_t ph = (j >> 1) & 1;
-                if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag)) return false;
-                if (!mbar_wait(&k_full[st], ph, abort_flag)) return false;
+                // S[j & 1] was last read by the PV product of tile j - 2 (as P), which this thread issued earlier:
+                // the tensor pipe runs its instructions in order, so no barrier guards the overwrite.
+                const int st = j & 1, rs = j % kRing;
+                if (!mbar_wait(&k_full[rs], (j / kRing) & 1, abort_flag)) return false;
                 fence_after_sync();
-                const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + st * kTileBytes);
+                const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + rs * kTileBytes);
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
                     const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
@@ -165,28 +164,27 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                            idesc_qk, k ? 1u : 0u);
                 }
                 mma_commit(&s_full[st]);
-                mma_commit(&k_empty[st]);
+                mma_commit(&k_empty[rs]);
                 return true;
             };
             if (ok) ok = issue_qk(0);
             for (int j = 0; j < n_kv && ok; ++j) {
                 if (j + 1 < n_kv) ok = issue_qk(j + 1);
                 if (!ok) break;
-                const int st = j & 1;
+                const int st = j & 1, rs = j % kRing;
                 const uint32_t ph = (j >> 1) & 1;
-                if (!mbar_wait(&o_empty[st], ph ^ 1, abort_flag) || !mbar_wait(&v_full[st], ph, abort_flag) ||
-                    !mbar_wait(p_full, j & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&o_empty[st], ph ^ 1, abort_flag) || !mbar_wait(&v_full[rs], (j / kRing) & 1, abort_flag) ||
+                    !mbar_wait(&p_full[st], ph, abort_flag)) { ok = false; break; }
                 fence_after_sync();
-                const uint32_t pa = smem_u32(sP), va = smem_u32(sV + st * kTileBytes);
+                // P comes from tensor memory: bf16 pairs in the first 64 columns of S[st], 8 columns per K = 16 step
+                const uint32_t va = smem_u32(sV + rs * kTileBytes);
 #pragma unroll
                 for (int k = 0; k < BKV / 16; ++k) {
-                    const uint64_t da = smem_desc_sw128(pa + (k >> 2) * kAtomBytes + (k & 3) * 32, 16, 1024);
                     const uint64_t db = smem_desc_sw128(va + k * 2048, kAtomBytes, 1024);
-                    mma_ss(tO + st * 128, da, db, idesc_pv, k ? 1u : 0u);
+                    mma_ts(tO + st * 128, tS + st * 128 + k * 8, db, idesc_pv, k ? 1u : 0u);
                 }
                 mma_commit(&o_full[st]);
-                mma_commit(&v_empty[st]);
-                mma_commit(p_empty);
+                mma_commit(&v_empty[rs]);
             }
             if (!ok) atomicExch(p.status, MM_TIMEOUT_MMA);
         }
@@ -213,8 +211,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             tmem_ld_32x32(t_row + 64, r + 64);
             tmem_ld_32x32(t_row + 96, r + 96);
             tmem_wait_ld();
-            fence_before_sync();
-            mbar_arrive(&s_empty[st]);     // S[st] may be overwritten by the QK MMA of tile j+2
             float mx = -INFINITY;
             if (need_mask) {
 #pragma unroll
@@ -235,7 +231,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const float m_new = fmaxf(m, mx);
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
             const float alpha = exp2f(m - m_use);        // m = -inf on the first tile -> 0
-            alpha_ring[(j & 3) * 128 + row] = alpha;
+            // The accumulate warps must be done with tile j - 2 before its alpha slot is reused and before
+            // p_full[st], which they wait on too, can complete again.
+            if (j >= 2 && !mbar_wait(&o_empty[st], ((j - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
+            alpha_ring[st * 128 + row] = alpha;
             m = m_new;
             float sum = 0.f;
 #pragma unroll
@@ -245,24 +244,18 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 r[i] = __float_as_uint(e);
             }
             l = l * alpha + sum;
-            // P buffer must have been consumed by the previous PV MMA
-            if (j > 0 && !mbar_wait(p_empty, (j - 1) & 1, abort_flag)) { ok = false; break; }
+            // P goes back into tensor memory as bf16 pairs over the first 64 columns of the S buffer just read; the
+            // PV product takes it from there as its A operand.
 #pragma unroll
-            for (int g = 0; g < 16; ++g) {
-                uint4 v;
-                bf162 t0 = __floats2bfloat162_rn(__uint_as_float(r[8 * g + 0]), __uint_as_float(r[8 * g + 1]));
-                bf162 t1 = __floats2bfloat162_rn(__uint_as_float(r[8 * g + 2]), __uint_as_float(r[8 * g + 3]));
-                bf162 t2 = __floats2bfloat162_rn(__uint_as_float(r[8 * g + 4]), __uint_as_float(r[8 * g + 5]));
-                bf162 t3 = __floats2bfloat162_rn(__uint_as_float(r[8 * g + 6]), __uint_as_float(r[8 * g + 7]));
-                v.x = *reinterpret_cast<uint32_t*>(&t0);
-                v.y = *reinterpret_cast<uint32_t*>(&t1);
-                v.z = *reinterpret_cast<uint32_t*>(&t2);
-                v.w = *reinterpret_cast<uint32_t*>(&t3);
-                // 16 chunks of 8 keys: atom = g / 8, 16-byte chunk inside the atom's 128-byte row = g % 8
-                *reinterpret_cast<uint4*>(sP + (g >> 3) * kAtomBytes + row * 128 + (((g & 7) ^ (row & 7)) << 4)) = v;
+            for (int i = 0; i < 64; ++i) {
+                bf162 t = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                r[i] = *reinterpret_cast<uint32_t*>(&t);
             }
-            fence_proxy_async();
-            mbar_arrive(p_full);
+            tmem_st_32x32(t_row, r);
+            tmem_st_32x32(t_row + 32, r + 32);
+            tmem_wait_st();
+            fence_before_sync();
+            mbar_arrive(&p_full[st]);
         }
         l_final[row] = l;
         if (ok && qi < q_len && n_kv > 0)
@@ -281,9 +274,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int j = 0; j < n_kv; ++j) {
             const int st = j & 1;
             const uint32_t ph = (j >> 1) & 1;
-            if (!mbar_wait(p_full, j & 1, abort_flag) || !mbar_wait(&o_full[st], ph, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(&p_full[st], ph, abort_flag) || !mbar_wait(&o_full[st], ph, abort_flag)) { ok = false; break; }
             fence_after_sync();
-            const float alpha = alpha_ring[(j & 3) * 128 + row];
+            const float alpha = alpha_ring[st * 128 + row];
             const uint32_t t_row = tO + st * 128 + ((uint32_t)(qd * 32) << 16);
 #pragma unroll
             for (int c = 0; c < 2; ++c) {

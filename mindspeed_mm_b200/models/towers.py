@@ -23,13 +23,55 @@ def _load_safetensors_dir(path: str) -> Dict[str, torch.Tensor]:
     return sd
 
 
+def _build_kl_family(mid: str, block: dict):
+    """The KL / VQ autoencoders other than Wan's (``models/ae/kl_vae.py``), selected by the reference's ``model_id``s."""
+    from .ae import kl_vae as K
+    mid = mid.lower()
+    cfg_keys = {k: block[k] for k in ("in_channels", "out_channels", "base", "ch_mult", "num_res_blocks", "z_channels",
+                                      "temporal_down", "kt", "mid_attention", "scale_factor", "shift_factor") if k in block}
+    if "ch" in block:
+        cfg_keys.setdefault("base", block["ch"])
+    tiling = {k: block[k] for k in ("tile_sample_min", "tile_overlap", "tile_frames") if k in block}
+    if mid in ("flux_vae", "fluxvae"):
+        return K.AutoencoderKL2D(K.KLVAEConfig.flux(**{k: v for k, v in cfg_keys.items() if k not in ("z_channels", "scale_factor", "shift_factor", "kt")}))
+    if mid in ("vae", "autoencoderkl", "autoencoder_kl", "diffusers_ae", "sd3_vae", "sd_vae"):
+        preset = K.KLVAEConfig.sd3 if "sd3" in mid or block.get("z_channels", 16) == 16 else K.KLVAEConfig.sd
+        base = preset()
+        for k, v in cfg_keys.items():
+            setattr(base, k, tuple(v) if isinstance(v, list) else v)
+        base.kt = 1
+        return K.AutoencoderKL2D(base)
+    if mid in ("casualvae", "causalvae", "contextparallelcasualvae", "autoencoder_kl_hunyuanvideo", "hunyuanvideo_vae",
+               "hunyuanvideo_15_vae", "stepvideovae", "stepvideo_vae", "vae3d", "vae_temporal"):
+        preset = K.KLVAEConfig.hunyuan_video if "hunyuan" in mid else K.KLVAEConfig.open_sora_plan
+        base = preset()
+        for k, v in cfg_keys.items():
+            setattr(base, k, tuple(v) if isinstance(v, list) else v)
+        vae = K.CausalVAE3D(base, **tiling)
+        vae.enable_tiling(bool(block.get("use_tiling", block.get("enable_tiling", False))))
+        return vae
+    if mid in ("wfvae", "wf_vae"):
+        return K.WFVAE(**{k: block[k] for k in ("base", "z_channels", "in_channels", "num_res_blocks", "energy_flow", "scale_factor",
+                                                "shift_factor", "mid_attention") if k in block})
+    if mid in ("movq", "movqvae"):
+        return K.MOVQ(**{k: block[k] for k in ("z_channels", "in_channels", "base", "ch_mult", "num_res_blocks", "n_embed",
+                                               "embed_dim", "mid_attention") if k in block})
+    return None
+
+
 def build_ae(block: Optional[dict], device="cpu", dtype=torch.float32):
     if not block:
         return None
     mid = block.get("model_id", "wan_video_vae")
     if mid not in ("wan_video_vae", "wan_vae", "autoencoder_kl_wan"):
-        from .registry import build_model
-        return build_model(mid, block)
+        vae = _build_kl_family(mid, block)
+        if vae is None:
+            from .registry import build_model
+            return build_model(mid, block)
+        src = block.get("from_pretrained")
+        if src and os.path.exists(src):
+            vae.load_state_dict(_load_safetensors_dir(src), strict=False)
+        return vae.to(device=device, dtype=dtype).eval().requires_grad_(False)
     from .ae.wan_vae import WanVAE, WanVAEConfig
     keys = {k: block[k] for k in ("base_dim", "z_dim", "dim_mult", "num_res_blocks", "attn_scales", "temporal_downsample",
                                   "latents_mean", "latents_std") if k in block}

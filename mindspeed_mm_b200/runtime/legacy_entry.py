@@ -46,7 +46,7 @@ def model_provider(kind: str, args):
                 p.requires_grad_(False)
         return model
     if kind == "sora":
-        from ..models.diffusion import FlowMatchScheduler
+        from ..models.diffusion import build_scheduler
         from ..models.wan import SoRAModel, WanConfig, WanDiT
         pred = dict(mm["predictor"])
         if pred.get("model_id") != "wandit":
@@ -55,11 +55,10 @@ def model_provider(kind: str, args):
         else:
             with torch.device("meta"):
                 net = WanDiT(WanConfig.from_mm_json(pred))
-        diff = {k: v for k, v in mm.get("diffusion", {}).items() if k != "model_id"}
         from ..models.towers import build_ae, build_text_encoder
         ae = None if mm.get("load_video_features", True) else build_ae(mm.get("ae"))
         te = None if mm.get("load_text_features", True) else build_text_encoder(mm.get("text_encoder"))
-        return SoRAModel(net, FlowMatchScheduler(**diff), ae=ae, text_encoder=te, seed=args.seed)
+        return SoRAModel(net, build_scheduler(mm.get("diffusion", {})), ae=ae, text_encoder=te, seed=args.seed)
     raise ValueError(f"unknown entry kind {kind}")
 
 

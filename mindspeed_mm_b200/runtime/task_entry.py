@@ -97,7 +97,7 @@ def evaluate_vlm(cfg: dict, device="cpu", predict: Optional[Callable[[dict], str
 
 # ------------------------------------------------------------------------------------------ video generation
 def build_sora_for_inference(cfg: dict, device="cpu", dtype=torch.float32):
-    from ..models.diffusion import FlowMatchScheduler
+    from ..models.diffusion import build_scheduler
     from ..models.towers import build_ae, build_text_encoder
     from ..models.wan import WanConfig, WanDiT
     pred = dict(cfg["predictor"])
@@ -108,8 +108,7 @@ def build_sora_for_inference(cfg: dict, device="cpu", dtype=torch.float32):
         dit = build_model(pred["model_id"], pred)
     for p in dit.parameters():
         torch.nn.init.normal_(p, std=0.02)
-    diff = {k: v for k, v in cfg.get("diffusion", {}).items() if k != "model_id"}
-    sched = FlowMatchScheduler(**diff)
+    sched = build_scheduler(cfg.get("diffusion", {}))
     ae = build_ae(cfg.get("ae"), device, dtype)
     te = build_text_encoder(cfg.get("text_encoder"), device, dtype)
     return dit.to(device=device, dtype=dtype).eval(), sched, ae, te
@@ -180,7 +179,7 @@ def posttrain_sora_dpo(cfg: dict, data_iter, device="cpu", steps: int = 1) -> Li
 
 
 def posttrain_flux_dancegrpo(cfg: dict, prompts, reward_fn, device="cpu", steps: int = 1) -> List[Dict[str, float]]:
-    from ..models.diffusion import FlowMatchScheduler
+    from ..models.diffusion import build_scheduler
     from ..models.mmdit import MMDiT, MMDiTConfig
     from ..tasks.posttrain import FlowGRPOTrainer
     pred = dict(cfg.get("predictor", {}))
@@ -190,7 +189,7 @@ def posttrain_flux_dancegrpo(cfg: dict, prompts, reward_fn, device="cpu", steps:
     for p in dit.parameters():
         torch.nn.init.normal_(p, std=0.02)
     opt = torch.optim.AdamW(dit.parameters(), lr=float(cfg.get("lr", 1e-5)))
-    sched = FlowMatchScheduler(**{k: v for k, v in cfg.get("diffusion", {}).items() if k != "model_id"})
+    sched = build_scheduler(cfg.get("diffusion", {}))
     g = cfg.get("grpo", {})
     tr = FlowGRPOTrainer(lambda x, t, c: dit(x, t, c[0].expand(x.shape[0], -1, -1), c[1].expand(x.shape[0], -1)), sched, reward_fn,
                          group_size=int(g.get("group_size", 4)), num_steps=int(g.get("num_steps", 8)), eta=float(g.get("eta", 0.3)),

@@ -1,0 +1,102 @@
+"""KL / VQ autoencoder family: wavelet identities, shape contracts, causal blocks, tiling, factory ids."""
+import torch
+
+from mindspeed_mm_b200.models.ae.kl_vae import (MOVQ, WFVAE, AutoencoderKL2D, CausalVAE3D, Conv, DiagonalGaussian, Down, KLVAEConfig,
+                                                VectorQuantizer, _blend, haar, inverse_haar)
+from mindspeed_mm_b200.models.towers import build_ae
+
+
+def test_haar_is_orthonormal_and_low_band_first():
+    torch.manual_seed(0)
+    x = torch.randn(2, 3, 4, 8, 6)
+    w = haar(x, (2, 3, 4))
+    assert w.shape == (2, 24, 2, 4, 3)
+    assert torch.allclose(inverse_haar(w, (2, 3, 4)), x, atol=1e-5)
+    assert torch.allclose(w.pow(2).sum(), x.pow(2).sum(), rtol=1e-5)            # energy preserved
+    blocks = x.reshape(2, 3, 2, 2, 4, 2, 3, 2).sum((3, 5, 7)) / (2 ** 1.5)
+    assert torch.allclose(w[:, :3], blocks, atol=1e-5)
+    w2 = haar(x, (3, 4))
+    assert w2.shape == (2, 12, 4, 4, 3) and torch.allclose(inverse_haar(w2, (3, 4)), x, atol=1e-5)
+
+
+def test_causal_conv_and_down_do_not_see_the_future():
+    torch.manual_seed(0)
+    conv, down = Conv(4, 4), Down(4, time=True)
+    x = torch.randn(1, 4, 9, 8, 8)
+    y = x.clone()
+    y[:, :, 5:] += 1.0
+    assert torch.equal(conv(x)[:, :, :5], conv(y)[:, :, :5])
+    dx, dy = down(x), down(y)
+    assert dx.shape == (1, 4, 5, 4, 4)
+    assert torch.equal(dx[:, :, :3], dy[:, :, :3]) and not torch.equal(dx[:, :, 3:], dy[:, :, 3:])
+
+
+def test_causal_vae_shapes_image_path_and_posterior():
+    torch.manual_seed(0)
+    v = CausalVAE3D(KLVAEConfig.tiny(scale_factor=0.5, shift_factor=0.1)).eval()
+    assert v.compression() == (4, 4, 4)
+    x = torch.randn(1, 3, 9, 16, 16)
+    z = v.encode(x)
+    assert z.shape == (1, 4, 3, 4, 4)
+    assert v.decode(z).shape == x.shape
+    img = torch.randn(2, 3, 16, 16)
+    zi = v.encode(img)
+    assert zi.shape == (2, 4, 4, 4) and v.decode(zi).shape == img.shape
+    rec, post = v(x, sample_posterior=True, generator=torch.Generator().manual_seed(0))
+    assert rec.shape == x.shape and post.kl().shape == (1,) and float(post.kl().detach()) >= 0
+    g = DiagonalGaussian(torch.zeros(1, 8, 1, 2, 2))
+    assert float(g.kl()) == 0 and torch.equal(g.mode(), torch.zeros(1, 4, 1, 2, 2))
+
+
+def test_tiling_matches_shapes_and_blend_is_identity_on_constants():
+    torch.manual_seed(0)
+    a, b = torch.full((1, 1, 1, 4, 6), 2.0), torch.full((1, 1, 1, 4, 6), 2.0)
+    assert torch.equal(_blend(a, b, 4, 3), b)
+    ramp = _blend(torch.zeros(1, 1, 1, 1, 4), torch.ones(1, 1, 1, 1, 4), 4, 3)[0, 0, 0, 0]
+    assert (ramp[1:] >= ramp[:-1]).all() and float(ramp[-1]) == 1 and 0 < float(ramp[0]) < 1
+    v = CausalVAE3D(KLVAEConfig.tiny(), tile_sample_min=16, tile_overlap=0.25, tile_frames=5).eval()
+    x = torch.randn(1, 3, 9, 32, 32)
+    full = v.encode(x)
+    v.enable_tiling()
+    tiled = v.encode(x)
+    assert tiled.shape == full.shape and torch.isfinite(tiled).all()
+    out = v.decode(tiled)
+    assert out.shape == x.shape and torch.isfinite(out).all()
+
+
+def test_wfvae_and_movq_and_image_vae():
+    torch.manual_seed(0)
+    wf = WFVAE(base=16, z_channels=4, num_res_blocks=1, energy_flow=8).eval()
+    x = torch.randn(1, 3, 9, 32, 32)
+    z = wf.encode(x)
+    assert z.shape == (1, 4, 3, 4, 4)
+    rec, post = wf(x, sample_posterior=False)
+    assert rec.shape == x.shape
+    rec.mean().backward()
+    assert wf.in_flow3[0].conv.weight.grad is not None and wf.out_flow2[1].conv.weight.grad is not None
+    assert wf.get_last_layer().shape[0] == 24
+    m = MOVQ(base=16, ch_mult=(1, 2, 2), num_res_blocks=1, n_embed=32).eval()
+    img = torch.randn(2, 3, 16, 16)
+    idx = m.encode(img)
+    assert idx.shape == (2, 4, 4) and idx.dtype == torch.long and int(idx.max()) < 32
+    assert m.decode_codes(idx).shape == img.shape
+    vq = VectorQuantizer(8, 2)
+    pts = vq.embedding.weight.detach()[[3, 5]].t().reshape(1, 2, 1, 2).clone().requires_grad_()
+    ids, q, commit = vq(pts)
+    assert ids.flatten().tolist() == [3, 5] and float(commit) < 1e-12
+    q.sum().backward()
+    assert torch.equal(pts.grad, torch.ones_like(pts))                              # straight-through
+    k = AutoencoderKL2D(KLVAEConfig(base=16, ch_mult=(1, 2, 2, 2), num_res_blocks=1, kt=1, z_channels=4, scale_factor=0.36, shift_factor=0.1)).eval()
+    zk = k.encode(img)
+    assert zk.shape == (2, 4, 2, 2) and k.decode(zk).shape == img.shape
+    assert sum(p.numel() for n, p in k.named_parameters() if "conv.weight" in n and p.shape[2] != 1) == 0   # no temporal taps
+
+
+def test_factory_ids():
+    tiny = dict(base=16, ch_mult=[1, 2, 2], num_res_blocks=1, z_channels=4)
+    assert isinstance(build_ae(dict(model_id="casualvae", temporal_down=[True, True], **tiny)), CausalVAE3D)
+    assert isinstance(build_ae(dict(model_id="autoencoder_kl_hunyuanvideo", temporal_down=[True, True], use_tiling=True, **tiny)), CausalVAE3D)
+    assert isinstance(build_ae(dict(model_id="flux_vae", base=16, ch_mult=[1, 2, 2, 2], num_res_blocks=1)), AutoencoderKL2D)
+    assert isinstance(build_ae(dict(model_id="vae", temporal_down=[False, False], **tiny)), AutoencoderKL2D)
+    assert isinstance(build_ae(dict(model_id="wfvae", base=16, z_channels=4, num_res_blocks=1, energy_flow=8)), WFVAE)
+    assert isinstance(build_ae(dict(model_id="movq", base=16, ch_mult=[1, 2, 2], num_res_blocks=1, n_embed=16)), MOVQ)

@@ -6,3 +6,4 @@ from . import qwen3_vl_moe  # noqa: F401
 from . import qwen3_5  # noqa: F401
 from . import mmdit  # noqa: F401
 from . import composable  # noqa: F401
+from . import wan_variants  # noqa: F401

@@ -80,3 +80,70 @@ def test_wan_name_maps_roundtrip():
     assert set(back) == set(internal)
     for k in internal:
         assert torch.equal(back[k], internal[k]), k
+
+
+# ------------------------------------------------------------------------------------------------- Wan variants
+def test_wan22_per_token_timesteps_match_uniform_when_equal():
+    from mindspeed_mm_b200.models.wan_variants import Wan22Config, Wan22DiT
+    torch.manual_seed(0)
+    cfg = Wan22Config.tiny(per_token_timestep=True)
+    m = Wan22DiT(cfg)
+    for p in m.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    lat = torch.randn(1, 16, 3, 4, 4)
+    prompt = torch.randn(1, 16, 64)
+    t = torch.tensor([400.0])
+    uniform = m(lat, t, prompt)
+    per_tok = m(lat, t[:, None].expand(1, 3 * 2 * 2), prompt)
+    assert torch.allclose(uniform, per_tok, atol=1e-4)
+    clean_first = m(lat, t, prompt, first_frame_clean=True)
+    assert not torch.allclose(uniform, clean_first, atol=1e-4)
+    tt = m.ti2v_timesteps(lat, t)
+    assert tt.shape == (1, 12) and tt[0, :4].tolist() == [0, 0, 0, 0] and tt[0, 4:].tolist() == [400.0] * 8
+
+
+def test_wan22_moe_ffn_and_expert_pair():
+    from mindspeed_mm_b200.models.wan_variants import Wan22Config, Wan22DiT, WanExpertPair
+    torch.manual_seed(0)
+    m = Wan22DiT(Wan22Config.tiny(moe_num_experts=4, moe_top_k=2))
+    for p in m.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    lat, prompt = torch.randn(1, 16, 2, 4, 4), torch.randn(1, 16, 64)
+    out = m(lat, torch.tensor([100.0]), prompt)
+    assert out.shape == lat.shape
+    out.mean().backward()
+    assert m.blocks[0].moe.gate_up.grad is not None and m.blocks[0].moe.router.weight.grad is not None
+    assert not hasattr(m.blocks[0], "ffn_0")
+    pair = WanExpertPair(Wan22Config.tiny())
+    assert pair.expert_for(torch.tensor([900.0])) is pair.high_noise and pair.expert_for(torch.tensor([100.0])) is pair.low_noise
+    lo, hi = pair.scheduler_boundaries("high")
+    assert lo == 0.0 and abs(hi - 0.4167) < 1e-3
+    assert abs(WanExpertPair(Wan22Config.tiny(model_type="i2v")).scheduler_boundaries("low")[0] - 0.357) < 1e-3
+    names = [n for n, _ in pair.fsdp_units()]
+    assert names[0].startswith("high_noise.") and names[-1].startswith("low_noise.")
+    assert pair(lat, torch.tensor([900.0]), prompt).shape == lat.shape
+
+
+def test_vace_hints_start_as_identity_and_train_only_the_branch():
+    from mindspeed_mm_b200.models.wan import WanDiT
+    from mindspeed_mm_b200.models.wan_variants import VaceConfig, VaceWanDiT
+    torch.manual_seed(0)
+    cfg = VaceConfig.tiny()
+    m = VaceWanDiT(cfg)
+    for n, p in m.named_parameters():
+        if "after_proj" not in n and "before_proj" not in n:
+            torch.nn.init.normal_(p, std=0.05)
+    lat, prompt = torch.randn(1, 16, 2, 4, 4), torch.randn(1, 16, 64)
+    ctrl = torch.randn(1, 20, 2, 4, 4)
+    t = torch.tensor([300.0])
+    base = m(lat, t, prompt)
+    with_ctrl = m(lat, t, prompt, vace_context=ctrl)
+    assert torch.allclose(base, with_ctrl, atol=1e-6)                 # zero-initialised projections: no effect at start
+    torch.nn.init.normal_(m.vace_blocks[0].after_proj.weight, std=0.05)
+    moved = m(lat, t, prompt, vace_context=ctrl, vace_scale=2.0)
+    assert not torch.allclose(base, moved, atol=1e-5)
+    m.freeze_trunk()
+    moved = m(lat, t, prompt, vace_context=ctrl)
+    moved.mean().backward()
+    assert all((p.grad is None) == (not n.startswith("vace_")) or not p.requires_grad for n, p in m.named_parameters())
+    assert m.vace_patch_embedding.weight.grad is not None and m.blocks[0].ffn_0.weight.grad is None

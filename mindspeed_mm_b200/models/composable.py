@@ -361,10 +361,12 @@ class ComposableLM(Qwen25VLModel):
     def forward(self, batch: dict, run=None):
         run = run or (lambda m, *a, **k: m(*a, **k))
         cfg, t = self.config, self.config.text
-        ids = batch["input_ids"]
-        x = run(self.embed_tokens, ids)
-        if t.embed_scale:
-            x = x * math.sqrt(t.hidden_size)
+        ids = batch.get("input_ids")
+        x = batch.get("inputs_embeds")            # callers that build their own token embeddings (speech LMs)
+        if x is None:
+            x = run(self.embed_tokens, ids)
+            if t.embed_scale:
+                x = x * math.sqrt(t.hidden_size)
         pv = batch.get("pixel_values")
         if self.visual is not None and pv is not None and pv.numel() > 0:
             if isinstance(self.visual, VisionTransformer):
@@ -397,6 +399,8 @@ class ComposableLM(Qwen25VLModel):
         cos, sin = cos.to(x.dtype), sin.to(x.dtype)
         for layer in self.layers:
             x = run(layer, x, cos, sin, batch["cu_seqlens"], batch["max_seqlen"])
+        if batch.get("return_hidden"):
+            return x                              # pre-norm hidden states [T, H]
         return run(self.lm_head, x, batch.get("labels"))
 
 

@@ -7,3 +7,5 @@ from . import qwen3_5  # noqa: F401
 from . import mmdit  # noqa: F401
 from . import composable  # noqa: F401
 from . import wan_variants  # noqa: F401
+from . import ltx2  # noqa: F401
+from . import speech_lm  # noqa: F401

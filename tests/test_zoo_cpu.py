@@ -103,3 +103,48 @@ def test_composable_from_hf_config_switches():
     c = from_hf_config(hf)
     assert c.text.mixers == ("mla",) * 4 and c.text.ffns == ("dense", "moe", "moe", "moe")
     assert c.vision_kind == "vit" and c.text.shared_expert_intermediate_size == 32 and c.text.rope == "rope1d"
+
+
+def test_ltx2_joint_audio_video_block():
+    from mindspeed_mm_b200.models.ltx2 import LTX2Config, LTX2Model, fractional_rope
+    torch.manual_seed(0)
+    cfg = LTX2Config.tiny()
+    m = LTX2Model(cfg)
+    for p in m.parameters():
+        if p.dim() > 1:
+            torch.nn.init.normal_(p, std=0.05)
+        else:
+            torch.nn.init.normal_(p, std=0.02)
+    for n, p in m.named_parameters():
+        if n.endswith("q_norm") or n.endswith("k_norm"):
+            torch.nn.init.ones_(p)
+    B, Sv, Sa, L = 2, 12, 5, 7
+    vpos = torch.stack([torch.arange(Sv) // 4, (torch.arange(Sv) // 2) % 2, torch.arange(Sv) % 2]).float()[None].expand(B, -1, -1)
+    apos = torch.arange(Sa).float()[None, None].expand(B, -1, -1)
+    vt = torch.full((B, Sv), 500.0)
+    vt[:, :4] = 0.0                                                     # a clean conditioning frame
+    args = dict(video_latent=torch.randn(B, Sv, 8), video_timesteps=vt, video_positions=vpos, context=torch.randn(B, L, 24),
+                context_mask=torch.tensor([[1] * 7, [1] * 4 + [0] * 3]).bool(), video_target_velocity=torch.randn(B, Sv, 8),
+                audio_latent=torch.randn(B, Sa, 6), audio_timesteps=torch.full((B, Sa), 300.0), audio_positions=apos,
+                audio_target_velocity=torch.randn(B, Sa, 6), loss_mask=(vt > 0))
+    out = m(**args)
+    assert out["video_pred"].shape == (B, Sv, 8) and out["audio_pred"].shape == (B, Sa, 6) and torch.isfinite(out["loss"])
+    out["loss"].backward()
+    blk = m.transformer_blocks[0]
+    assert blk.audio_to_video_attn.to_k.weight.grad is not None and blk.video_to_audio_attn.to_q.weight.grad is not None
+    assert blk.scale_shift_table_a2v_ca_audio.grad is not None
+    # padded context positions do not matter
+    args2 = dict(args)
+    ctx = args["context"].clone()
+    ctx[1, 4:] += 10.0
+    args2["context"] = ctx
+    with torch.no_grad():
+        a, b = m(**args)["video_pred"], m(**args2)["video_pred"]
+    assert torch.allclose(a[1], b[1], atol=1e-5)
+    # video-only call works and differs from the joint one (the audio stream feeds the video stream)
+    with torch.no_grad():
+        solo = m(**{k: v for k, v in args.items() if not k.startswith("audio")})
+    assert solo["audio_pred"] is None and not torch.allclose(solo["video_pred"], a, atol=1e-5)
+    cos, sin = fractional_rope(vpos, 16, 10000.0, (20, 2048, 2048))
+    assert cos.shape == (B, Sv, 8) and torch.allclose(cos ** 2 + sin ** 2, torch.ones_like(cos), atol=1e-5)
+    assert [n for n, _ in m.fsdp_units()][:3] == ["video_io", "audio_io", "transformer_blocks.0"]

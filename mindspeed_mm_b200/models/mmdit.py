@@ -42,10 +42,23 @@ class MMDiTConfig:
     guidance_embed: bool = True
     eps: float = 1e-6
     init_std: float = 0.02
+    # block-sparse self-attention over the latent canvas (HunyuanVideo-1.5): dict(tile=(6, 8, 8), kernel=(3, 3, 3), topk=8,
+    # mode="ssta"); None = dense
+    sparse_attention: Optional[dict] = None
 
     @staticmethod
     def hunyuan_video():
         return MMDiTConfig()
+
+    @staticmethod
+    def hunyuan_video_15(**kw):
+        """HunyuanVideo-1.5 (mindspeed_mm/models/predictor/dits/hunyuan_video_15_dit.py:698): dual-stream blocks only, 32-channel
+        latents with 1 x 1 x 1 patches, selective sliding-tile attention."""
+        d = dict(in_channels=32, out_channels=32, patch_size=(1, 1, 1), hidden_size=2048, num_heads=16, num_double_blocks=54,
+                 num_single_blocks=0, text_dim=3584, rope_dims=(16, 56, 56), guidance_embed=False,
+                 sparse_attention=dict(tile=(6, 8, 8), kernel=(3, 3, 3), topk=8, mode="ssta"))
+        d.update(kw)
+        return MMDiTConfig(**d)
 
     @staticmethod
     def flux_dev():
@@ -108,6 +121,17 @@ def _heads(x, nh):
     return x.view(B, S, nh, H // nh)
 
 
+def _attend(c: "MMDiTConfig", q, k, v, s_img: int, grid):
+    """Joint attention over [image tokens, text tokens]; block-sparse on the image canvas when the config asks for it."""
+    sp = c.sparse_attention
+    if not sp or grid is None:
+        return ops.attention_dense(q, k, v)
+    from ..ops.sparse_attention import ssta_attention
+    return ssta_attention(q, k, v, grid, tuple(sp.get("tile", (6, 8, 8))), tuple(sp.get("kernel", (1, 1, 1))), int(sp.get("topk", 1)),
+                          text_len=q.shape[1] - s_img, mode=sp.get("mode", "ssta"), pad=sp.get("pad", "zero"),
+                          share_heads=sp.get("share_heads", True))[0]
+
+
 def _rope(x, cos, sin):
     B, S, N, D = x.shape
     return ops.rope_interleaved(x.reshape(B * S, N, D), cos.repeat(B, 1), sin.repeat(B, 1)).view(B, S, N, D)
@@ -119,7 +143,7 @@ class DoubleBlock(nn.Module):
         self.c = c
         self.img, self.txt = StreamParams(c), StreamParams(c)
 
-    def forward(self, img, txt, vec, cos, sin):
+    def forward(self, img, txt, vec, cos, sin, grid=None):
         c, nh = self.c, self.c.num_heads
         im, tm = self.img.mod(vec), self.txt.mod(vec)
         qkvs = []
@@ -130,8 +154,8 @@ class DoubleBlock(nn.Module):
         (qi, ki, vi), (qt, kt, vt) = qkvs
         qi, ki = _rope(qi, cos, sin), _rope(ki, cos, sin)
         q, k, v = torch.cat([qi, qt], 1), torch.cat([ki, kt], 1), torch.cat([vi, vt], 1)
-        o = ops.attention_dense(q, k, v)
         S_img = img.shape[1]
+        o = _attend(c, q, k, v, S_img, grid)
         oi, ot = o[:, :S_img].flatten(2), o[:, S_img:].flatten(2)
         outs = []
         for x, o_, sp, m in ((img, oi, self.img, im), (txt, ot, self.txt, tm)):
@@ -152,7 +176,7 @@ class SingleBlock(nn.Module):
         self.linear2 = Linear(H + self.mlp_dim, H)
         self.q_norm, self.k_norm = RMSNorm(H // nh, c.eps), RMSNorm(H // nh, c.eps)
 
-    def forward(self, x, vec, cos, sin, s_img: int):
+    def forward(self, x, vec, cos, sin, s_img: int, grid=None):
         c, nh = self.c, self.c.num_heads
         m = self.mod(vec)
         h = ops.layer_norm_modulate(x, m[1], m[0], c.eps)
@@ -161,7 +185,7 @@ class SingleBlock(nn.Module):
         q, k, v = self.q_norm(_heads(q, nh)), self.k_norm(_heads(k, nh)), _heads(v, nh)
         q = torch.cat([_rope(q[:, :s_img], cos, sin), q[:, s_img:]], 1)
         k = torch.cat([_rope(k[:, :s_img], cos, sin), k[:, s_img:]], 1)
-        o = ops.attention_dense(q, k, v).flatten(2)
+        o = _attend(c, q, k, v, s_img, grid).flatten(2)
         y = self.linear2(torch.cat([o, ops.gelu_tanh(mlp)], dim=-1))
         return ops.gated_residual(x, y, m[2])
 
@@ -225,11 +249,11 @@ class MMDiT(nn.Module):
         img, text, vec = run(self.embed, x, txt, t, pooled, guidance)
         cos, sin = rope_nd(grid, c.rope_dims, c.rope_theta, device=latents.device)
         for blk in self.double_blocks:
-            img, text = run(blk, img, text, vec, cos, sin)
+            img, text = run(blk, img, text, vec, cos, sin, grid)
         s_img = img.shape[1]
         h = torch.cat([img, text], 1)
         for blk in self.single_blocks:
-            h = run(blk, h, vec, cos, sin, s_img)
+            h = run(blk, h, vec, cos, sin, s_img, grid)
         y = run(self.final, h[:, :s_img], vec)
         y = y.view(B, grid[0], grid[1], grid[2], c.out_channels, pf, ph, pw).permute(0, 4, 1, 5, 2, 6, 3, 7)
         return y.reshape(B, c.out_channels, Fr, Hh, Ww)
@@ -237,6 +261,12 @@ class MMDiT(nn.Module):
 
 @model_register.register("hunyuanvideodit")
 class HunyuanVideoDiT(MMDiT):
+    pass
+
+
+@model_register.register("hunyuanvideo15dit")
+class HunyuanVideo15DiT(MMDiT):
+    """HunyuanVideo-1.5: ``MMDiTConfig.hunyuan_video_15()``; attention over the canvas is block-sparse (``ops/sparse_attention.py``)."""
     pass
 
 

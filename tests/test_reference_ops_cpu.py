@@ -212,3 +212,40 @@ def test_kda_chunked_matches_recurrent():
     o2, s2 = ref.kda_chunked(q, k, v, g, beta, chunk=64)
     assert torch.allclose(o1, o2, atol=2e-4), (o1 - o2).abs().max()
     assert torch.allclose(s1, s2, atol=2e-4)
+
+
+# ------------------------------------------------------------------------------------------------- block-sparse attention
+def test_sta_mask_window_is_clamped_at_borders():
+    from mindspeed_mm_b200.ops.sparse_attention import sta_block_mask, tile_order
+    m = sta_block_mask((1, 4, 4), (1, 3, 3))
+    assert m.shape == (16, 16) and (m.sum(1) == 9).all()                 # every tile sees a full 3 x 3 window
+    assert m[0].nonzero().flatten().tolist() == [0, 1, 2, 4, 5, 6, 8, 9, 10]     # corner tile: window shifted inwards
+    assert m[5].nonzero().flatten().tolist() == [0, 1, 2, 4, 5, 6, 8, 9, 10]
+    assert sta_block_mask((2, 2, 2), (3, 3, 3)).all()
+    perm = tile_order((2, 4, 4), (1, 2, 2))
+    assert perm[:4].tolist() == [0, 1, 4, 5] and sorted(perm.tolist()) == list(range(32))
+
+
+def test_ssta_equals_dense_when_every_block_is_selected_and_is_sparse_otherwise():
+    from mindspeed_mm_b200.ops import reference as R
+    from mindspeed_mm_b200.ops.sparse_attention import ssta_attention
+    torch.manual_seed(0)
+    B, N, D = 2, 2, 16
+    canvas, tile, text = (2, 4, 4), (1, 2, 2), 4
+    S = 2 * 4 * 4 + text
+    q, k, v = (torch.randn(B, S, N, D) for _ in range(3))
+    dense = R.attention_dense(q, k, v)
+    full, density = ssta_attention(q, k, v, canvas, tile, kernel=(5, 5, 5), topk=1, text_len=text)
+    assert density == 1.0 and torch.allclose(full, dense, atol=1e-5)
+    sparse, density = ssta_attention(q, k, v, canvas, tile, kernel=(1, 1, 1), topk=2, text_len=text)
+    assert 0 < density < 1 and sparse.shape == dense.shape and not torch.allclose(sparse, dense, atol=1e-3)
+    # text rows see everything in every mode
+    assert torch.allclose(sparse[:, -text:], dense[:, -text:], atol=1e-5)
+    # window-only mode and per-head selection run and differ from each other
+    sta, d_sta = ssta_attention(q, k, v, canvas, tile, kernel=(1, 3, 3), text_len=text, mode="sta")
+    per_head, _ = ssta_attention(q, k, v, canvas, tile, kernel=(1, 1, 1), topk=2, text_len=text, share_heads=False)
+    assert d_sta < 1 and sta.shape == per_head.shape == dense.shape
+    # a canvas that is not a multiple of the tile is padded and cropped back
+    q2, k2, v2 = (torch.randn(1, 3 * 3 * 5, N, D) for _ in range(3))
+    out, _ = ssta_attention(q2, k2, v2, (3, 3, 5), (2, 2, 2), kernel=(1, 1, 1), topk=1)
+    assert out.shape == q2.shape and torch.isfinite(out).all()

@@ -101,3 +101,40 @@ def test_qwen3tts_talker_and_code_predictor():
     assert codes.shape == (5, G) and torch.equal(codes[:, 0], code0)
     names = [n for n, _ in m.fsdp_units()]
     assert "code_predictor.backbone.layers.0" in names and "backbone.layers.1" in names and "speaker_encoder" in names
+
+
+def test_audio_codec_rvq_and_roundtrip_shapes():
+    from mindspeed_mm_b200.models.audio_codec import (AudioCodec, AudioCodecConfig, CausalConv1d, ResidualVQ, VectorQuantize,
+                                                      multi_scale_mel_loss)
+    torch.manual_seed(0)
+    # residual quantisation: every extra codebook lowers the reconstruction error
+    rvq = ResidualVQ(4, 8, 64, ema_decay=None).eval()
+    x = torch.randn(2, 8, 50)
+    errs = [float((rvq(x, n)[0] - x).pow(2).mean()) for n in (1, 2, 4)]
+    assert errs[0] > errs[1] > errs[2]
+    codes = rvq.encode(x)
+    assert codes.shape == (2, 4, 50) and torch.allclose(rvq.decode(codes), rvq(x)[0], atol=1e-5)
+    # straight-through gradient and EMA update that moves the codebook toward the data
+    vq = VectorQuantize(8, 16, ema_decay=0.5).train()
+    xin = (torch.randn(2, 8, 40) * 3 + 5).requires_grad_()
+    before = (vq.codebook.mean(0) - 5).abs().mean()
+    q, idx, commit = vq(xin)
+    q.sum().backward()
+    assert torch.allclose(xin.grad, torch.ones_like(xin)) and idx.shape == (2, 40)
+    assert (vq.codebook.mean(0) - 5).abs().mean() < before
+    conv = CausalConv1d(1, 1, 5, stride=2)
+    a = torch.randn(1, 1, 40)
+    b = a.clone()
+    b[..., 30:] += 1
+    assert torch.equal(conv(a)[..., :15], conv(b)[..., :15])                     # output t depends on inputs <= 2t
+    cfg = AudioCodecConfig.tiny()
+    codec = AudioCodec(cfg)
+    assert cfg.hop == 16
+    wav = torch.randn(2, 1, 16 * 10 + 5)
+    rec, codes, commit = codec(wav)
+    assert rec.shape == wav.shape and codes.shape == (2, 4, 11) and torch.isfinite(commit)
+    (multi_scale_mel_loss(rec, wav, 16000, ffts=(64, 128), n_mels=10) + commit).backward()
+    assert codec.encoder[0].conv.weight.grad is not None and codec.decoder[-1].conv.weight.grad is not None
+    codec.eval()
+    c2 = codec.encode(wav)
+    assert c2.shape == (2, 4, 11) and codec.decode(c2).shape[-1] >= wav.shape[-1]

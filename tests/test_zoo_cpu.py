@@ -148,3 +148,24 @@ def test_ltx2_joint_audio_video_block():
     cos, sin = fractional_rope(vpos, 16, 10000.0, (20, 2048, 2048))
     assert cos.shape == (B, Sv, 8) and torch.allclose(cos ** 2 + sin ** 2, torch.ones_like(cos), atol=1e-5)
     assert [n for n, _ in m.fsdp_units()][:3] == ["video_io", "audio_io", "transformer_blocks.0"]
+
+
+def test_hunyuan_video_15_sparse_attention_path():
+    from mindspeed_mm_b200.models.mmdit import HunyuanVideo15DiT, MMDiTConfig
+    torch.manual_seed(0)
+    base = dict(in_channels=4, out_channels=4, hidden_size=64, num_heads=4, num_double_blocks=2, text_dim=32, pooled_dim=16,
+                rope_dims=(4, 6, 6))
+    lat, txt, pooled = torch.randn(1, 4, 2, 4, 4), torch.randn(1, 4, 32), torch.randn(1, 16)
+    t = torch.tensor([500.0])
+    outs = {}
+    for name, sp in (("dense", None), ("all", dict(tile=(1, 2, 2), kernel=(5, 5, 5), topk=1)), ("sparse", dict(tile=(1, 2, 2), kernel=(1, 1, 1), topk=1))):
+        torch.manual_seed(1)
+        m = HunyuanVideo15DiT(MMDiTConfig.hunyuan_video_15(sparse_attention=sp, **base))
+        for p in m.parameters():
+            torch.nn.init.normal_(p, std=0.05)
+        outs[name] = m(lat, t, txt, pooled)
+    assert outs["dense"].shape == lat.shape
+    assert torch.allclose(outs["dense"], outs["all"], atol=1e-4)          # a window that covers the canvas is dense attention
+    assert not torch.allclose(outs["dense"], outs["sparse"], atol=1e-4)
+    full = MMDiTConfig.hunyuan_video_15()
+    assert full.num_single_blocks == 0 and full.sparse_attention["tile"] == (6, 8, 8)

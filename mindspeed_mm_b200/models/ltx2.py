@@ -217,6 +217,7 @@ class LTX2Model(nn.Module):
     """``forward(video_latent [B, Sv, Cv], video_timesteps [B, Sv], video_positions [B, 3, Sv], context [B, L, Cc],
     video_target_velocity, audio_latent / audio_timesteps / audio_positions [B, 1, Sa] / audio_target_velocity, context_mask,
     loss_mask)`` -> dict(loss, video_pred, audio_pred); without targets only the predictions are filled."""
+    config_class = LTX2Config
 
     def __init__(self, config: Optional[LTX2Config] = None):
         super().__init__()

@@ -226,6 +226,7 @@ class MMDiTFinal(nn.Module):
 
 class MMDiT(nn.Module):
     """``forward(latents [B,C,F,H,W], t [B], txt [B,L,text_dim], pooled [B,pooled_dim], guidance=None) -> velocity``."""
+    config_class = MMDiTConfig
 
     def __init__(self, config: MMDiTConfig):
         super().__init__()

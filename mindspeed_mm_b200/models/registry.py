@@ -59,9 +59,40 @@ def import_plugin(paths) -> None:
             importlib.import_module(p.replace("/", "."))
 
 
+def config_from_dict(cfg_cls, d: dict):
+    """Builds a dataclass config from a json / yaml block: unknown keys (``model_id``, ``from_pretrained`` ...) are dropped,
+    lists become tuples, nested dataclass fields are built recursively, and ``preset: name`` starts from the class's
+    ``name()`` factory with the remaining keys as overrides."""
+    import dataclasses
+    fields = {f.name: f for f in dataclasses.fields(cfg_cls)}
+    known = {}
+    for k, v in d.items():
+        if k not in fields:
+            continue
+        sub = fields[k].type if isinstance(fields[k].type, type) else None
+        if sub is None and isinstance(fields[k].default_factory, type):
+            sub = fields[k].default_factory
+        if isinstance(v, dict) and sub is not None and dataclasses.is_dataclass(sub):
+            v = config_from_dict(sub, v)
+        known[k] = tuple(v) if isinstance(v, list) else v
+    preset = d.get("preset")
+    if preset and hasattr(cfg_cls, preset):
+        base = getattr(cfg_cls, preset)()
+        return dataclasses.replace(base, **known)
+    return cfg_cls(**known)
+
+
 def build_model(model_id: str, config, **kw):
+    """Instantiates a registered model.  Classes that declare ``config_class`` accept the raw config block (a dict or an
+    attribute tree with ``to_dict``) in place of the dataclass."""
     _ensure_builtin()
-    return model_register.get(model_id)(config, **kw)
+    obj = model_register.get(model_id)
+    cfg_cls = getattr(obj, "config_class", None)
+    if cfg_cls is not None and config is not None and not isinstance(config, cfg_cls):
+        raw = config.to_dict() if hasattr(config, "to_dict") else config
+        if isinstance(raw, dict):
+            config = config_from_dict(cfg_cls, raw)
+    return obj(config, **kw)
 
 
 _BUILTIN_DONE = False

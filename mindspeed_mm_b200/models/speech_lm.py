@@ -112,6 +112,7 @@ class MultiCodebookConfig:
 class MultiCodebookLM(_Wrapped):
     """``batch``: ``input_ids`` [T, 1 + n_vq], ``labels`` [T, 1 + n_vq] (already shifted, -100 ignored), ``cu_seqlens``,
     ``max_seqlen``.  Returns the weighted loss, or the list of per-channel logits when there are no labels."""
+    config_class = MultiCodebookConfig
 
     def __init__(self, config: Optional[MultiCodebookConfig] = None):
         super().__init__()
@@ -235,6 +236,7 @@ class CosyVoice3Config:
 class CosyVoice3LM(_Wrapped):
     """Special speech ids: ``sos = S``, ``eos = S + 1``, ``task_id = S + 2``, ``fill = S + 3`` (S = speech_token_size); the speech
     table and the output head have S + 200 rows, every id >= S stops generation."""
+    config_class = CosyVoice3Config
 
     def __init__(self, config: Optional[CosyVoice3Config] = None):
         super().__init__()
@@ -489,6 +491,7 @@ class Qwen3TTSTalker(_Wrapped):
     ``labels`` [T] (code 0 to predict, -100 elsewhere), ``speaker_pos`` [n_seq] (row that receives the speaker embedding),
     ``ref_mels`` [n_seq, frames, n_mels] or ``speaker_embedding`` [n_seq, H], ``cu_seqlens``, ``max_seqlen``.
     """
+    config_class = Qwen3TTSConfig
 
     def __init__(self, config: Optional[Qwen3TTSConfig] = None):
         super().__init__()

@@ -237,6 +237,7 @@ class WanHead(nn.Module):
 @model_register.register("wandit")
 class WanDiT(nn.Module):
     """``forward(latents [B,C,F,H,W], timestep [B], prompt [B,L,text_dim], clip_feature=None) -> [B,C,F,H,W]``."""
+    config_class = WanConfig
 
     def __init__(self, config: WanConfig):
         super().__init__()

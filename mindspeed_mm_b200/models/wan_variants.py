@@ -122,6 +122,7 @@ class Wan22Head(WanHead):
 @model_register.register("wan2_2")
 class Wan22DiT(WanDiT):
     """Wan2.2 trunk.  ``timestep`` is ``[B]`` or, for TI2V, ``[B, tokens]``; ``ti2v_timesteps`` builds the latter."""
+    config_class = Wan22Config
 
     def __init__(self, config: Wan22Config):
         nn.Module.__init__(self)
@@ -150,6 +151,7 @@ class WanExpertPair(nn.Module):
     ``boundary`` is the switch point as a fraction of the training timesteps (0.875 text-to-video, 0.9 image-to-video).
     Training touches one expert per step (the scheduler's timestep boundaries pick the range); sampling routes each call
     by its timestep, so the pair behaves as a single ``model(latents, t, prompt)``."""
+    config_class = Wan22Config
 
     def __init__(self, config: Wan22Config, boundary: Optional[float] = None, num_train_timesteps: int = 1000):
         super().__init__()
@@ -222,6 +224,7 @@ class VaceBlock(nn.Module):
 class VaceWanDiT(WanDiT):
     """``forward(latents, timestep, prompt, vace_context=[B, vace_in_dim, F, H, W], vace_scale=1.0)``.  The trunk may be
     frozen (``freeze_trunk``) so that only the control branch trains, as the reference's VACE recipe does."""
+    config_class = VaceConfig
 
     def __init__(self, config: VaceConfig):
         super().__init__(config)

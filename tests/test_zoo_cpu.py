@@ -169,3 +169,47 @@ def test_hunyuan_video_15_sparse_attention_path():
     assert not torch.allclose(outs["dense"], outs["sparse"], atol=1e-4)
     full = MMDiTConfig.hunyuan_video_15()
     assert full.num_single_blocks == 0 and full.sparse_attention["tile"] == (6, 8, 8)
+
+
+def test_video_dit_families():
+    from mindspeed_mm_b200.models.registry import build_model
+    from mindspeed_mm_b200.models.video_dits import (CrossDiT, JointDiT, VideoDiTConfig, grouped_self_attention, sparse_1d_groups)
+    from mindspeed_mm_b200.ops import reference as R
+    torch.manual_seed(0)
+    g = sparse_1d_groups(10, 4, contiguous=False)
+    assert g.shape == (4, 3) and g[0].tolist() == [0, 4, 8] and g[3].tolist() == [3, 7, -1]
+    assert sparse_1d_groups(10, 4, contiguous=True)[0].tolist() == [0, 1, 2]
+    q, k, v = (torch.randn(2, 10, 2, 8) for _ in range(3))
+    o = grouped_self_attention(q, k, v, g)
+    ref0 = R.attention_dense(q[:, [0, 4, 8]], k[:, [0, 4, 8]], v[:, [0, 4, 8]])
+    ref3 = R.attention_dense(q[:, [3, 7]], k[:, [3, 7]], v[:, [3, 7]])
+    assert torch.allclose(o[:, [0, 4, 8]], ref0, atol=1e-5) and torch.allclose(o[:, [3, 7]], ref3, atol=1e-5)
+    lat, text, t = torch.randn(2, 4, 2, 4, 4), torch.randn(2, 5, 32), torch.tensor([10.0, 900.0])
+    mask = torch.tensor([[1, 1, 1, 1, 1], [1, 1, 0, 0, 0]]).bool()
+
+    def init(m):
+        for p in m.parameters():
+            torch.nn.init.normal_(p, std=0.05)
+        return m
+
+    for kw in (dict(), dict(sparse_n=2), dict(skip_connections=True, num_layers=4), dict(learn_sigma=True), dict(text_dim_2=12)):
+        m = init(CrossDiT(VideoDiTConfig.tiny(**kw)))
+        out = m(lat, t, text, mask, text_2=torch.randn(2, 1, 12) if kw.get("text_dim_2") else None)
+        assert out.shape == (2, 8 if kw.get("learn_sigma") else 4, 2, 4, 4)
+        out.mean().backward()
+        if kw.get("skip_connections"):
+            assert m.blocks[3].skip_proj.weight.grad is not None and m.blocks[0].skip_proj is None
+    # masked text positions do not influence the result
+    m = init(CrossDiT(VideoDiTConfig.tiny())).eval()
+    text2 = text.clone()
+    text2[1, 2:] += 5.0
+    with torch.no_grad():
+        assert torch.allclose(m(lat, t, text, mask)[1], m(lat, t, text2, mask)[1], atol=1e-5)
+    j = init(JointDiT(VideoDiTConfig.tiny()))
+    out = j(lat, t, text)
+    assert out.shape == lat.shape
+    out.mean().backward()
+    assert j.blocks[0].ada.weight.grad is not None
+    assert isinstance(build_model("satdit", dict(hidden_size=64, num_heads=4, num_layers=1, text_dim=32, in_channels=4, out_channels=4)), JointDiT)
+    sparse = build_model("sparseummdit", dict(hidden_size=64, num_heads=4, num_layers=2, text_dim=32, in_channels=4, out_channels=4))
+    assert isinstance(sparse, CrossDiT) and sparse.config.skip_connections and sparse.config.sparse_n == 4

@@ -213,3 +213,57 @@ def test_video_dit_families():
     assert isinstance(build_model("satdit", dict(hidden_size=64, num_heads=4, num_layers=1, text_dim=32, in_channels=4, out_channels=4)), JointDiT)
     sparse = build_model("sparseummdit", dict(hidden_size=64, num_heads=4, num_layers=2, text_dim=32, in_channels=4, out_channels=4))
     assert isinstance(sparse, CrossDiT) and sparse.config.skip_connections and sparse.config.sparse_n == 4
+
+
+def test_bagel_mot_routes_tokens_to_their_parameter_set():
+    from mindspeed_mm_b200.models.omni import BagelConfig, BagelMoT, bagel_attention_mask
+    torch.manual_seed(0)
+    m = BagelMoT(BagelConfig.tiny())
+    for n, p in m.named_parameters():
+        if p.dim() > 1:
+            torch.nn.init.normal_(p, std=0.05)
+        elif "norm" in n:
+            torch.nn.init.ones_(p)
+    # sample 0: 3 text, 2 vit, 3 text ; sample 1: 2 text, 4 latent tokens
+    T = 14
+    text_rows = torch.tensor([0, 1, 2, 5, 6, 7, 8, 9])
+    batch = dict(input_ids=torch.randint(1, 100, (T,)), text_rows=text_rows, vit_rows=torch.tensor([3, 4]), vit_embeds=torch.randn(2, 24),
+                 latent_rows=torch.tensor([10, 11, 12, 13]), latents=torch.randn(4, 16), latent_pos=torch.tensor([0, 1, 8, 9]),
+                 timesteps=torch.full((4,), 0.4), noise=torch.randn(4, 16), position_ids=torch.cat([torch.arange(8), torch.arange(6)]),
+                 cu_seqlens=torch.tensor([0, 8, 14], dtype=torch.int32), max_seqlen=8,
+                 attention_masks=[bagel_attention_mask(["causal", "full", "causal"], [3, 2, 3]), bagel_attention_mask(["causal", "noise"], [2, 4])])
+    labels = torch.full((T,), -100)
+    labels[[0, 1, 5, 6, 8]] = torch.randint(0, 100, (5,))
+    batch["labels"] = labels
+    out = m(batch)
+    assert torch.isfinite(out["loss"]) and out["ce"] is not None and out["mse"] is not None
+    out["loss"].backward()
+    l0 = m.layers[0]
+    assert l0.und.qkv.weight.grad.abs().sum() > 0 and l0.gen.qkv.weight.grad.abs().sum() > 0
+    assert m.vae2llm.weight.grad is not None and m.latent_pos_embed.grad[[0, 1, 8, 9]].abs().sum() > 0
+    # text-only batch: the generation parameter set receives no gradient
+    m.zero_grad()
+    text_only = dict(input_ids=batch["input_ids"][:8], text_rows=torch.arange(8), labels=labels[:8].clone(), position_ids=torch.arange(8),
+                     cu_seqlens=torch.tensor([0, 8], dtype=torch.int32), max_seqlen=8)
+    text_only["labels"][3:5] = 7
+    m(text_only)["loss"].backward()
+    assert l0.gen.qkv.weight.grad is None or float(l0.gen.qkv.weight.grad.abs().sum()) == 0
+    mask = bagel_attention_mask(["causal", "noise", "causal"], [2, 2, 2])
+    assert mask[2, 3] and mask[3, 2] and not mask[4, 2] and mask[4, 0] and not mask[0, 1]
+
+
+def test_reward_model_bradley_terry():
+    from mindspeed_mm_b200.models.omni import RewardModelBT
+    torch.manual_seed(0)
+    rm = RewardModelBT()
+    rm.backbone.init_weights()
+    torch.nn.init.normal_(rm.rm_head.weight, std=0.1)
+    T = 12
+    batch = dict(input_ids=torch.randint(0, 1000, (T,)), position_ids=torch.cat([torch.arange(3), torch.arange(3), torch.arange(4), torch.arange(2)])[None].expand(3, -1),
+                 cu_seqlens=torch.tensor([0, 3, 6, 10, 12], dtype=torch.int32), max_seqlen=4)
+    r = rm.rewards(batch)
+    assert r.shape == (4,)
+    loss = rm(batch)
+    loss.backward()
+    assert rm.rm_head.weight.grad is not None and 0 <= float(rm.last_accuracy) <= 1
+    assert "backbone.lm_head" not in [n for n, _ in rm.fsdp_units()]

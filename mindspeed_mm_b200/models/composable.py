@@ -452,6 +452,12 @@ PRESETS: Dict[str, ComposableConfig] = {
                                            shared_expert_intermediate_size=64), "vit", vit=_tiny_vit(128), **_IDS),
     "mimov2_5": ComposableConfig(_tiny_text(qk_norm=True, ffns=("moe", "moe")), "qwen_window", _tiny_qwen_vit(128), **_IDS),
     "minimax_m3_vl": ComposableConfig(_tiny_text(qk_norm=True, rope="rope1d", ffns=("moe", "moe")), "vit", vit=_tiny_vit(128), **_IDS),
+    # Chameleon-style autoregressive image generation: image patches are MOVQ code indices inside the text vocabulary
+    "lumina_mgpt2": ComposableConfig(_tiny_text(qk_norm=True, rope="rope1d"), None, **_IDS),
+    # LLaVA-style assembly (plain ViT + projector + dense decoder) and DeepSeek-VL2 (plain ViT + MLA attention + routed experts)
+    "llava": ComposableConfig(_tiny_text(rope="rope1d"), "vit", vit=_tiny_vit(128), **_IDS),
+    "deepseekvl2": ComposableConfig(_tiny_text(rope="rope1d", mixers=("mla", "mla"), ffns=("dense", "moe"),
+                                               shared_expert_intermediate_size=64), "vit", vit=_tiny_vit(128), **_IDS),
     "longcat_next": ComposableConfig(_tiny_text(rope="rope1d", mixers=("mla", "mla"), ffns=("moe", "moe")), "vit",
                                      vit=_tiny_vit(128), **_IDS),
 }

@@ -132,3 +132,66 @@ class MMDiTPipeline:
         neg = None if negative is None else (negative[0].to(device, dtype), negative[1].to(device, dtype))
         lat = self.scheduler.sample(fn, lat, (txt.to(device, dtype), pooled.to(device, dtype)), neg)
         return self.vae_decode(lat) if self.vae_decode is not None else lat
+
+
+class TextToVideoPipeline:
+    """Sampling loop shared by the cross-attention and joint-sequence video DiTs (``models/video_dits.py``) with any scheduler
+    of ``models/diffusion``: CogVideoX (zero-SNR v-prediction + dynamic guidance), Open-Sora-Plan (linear-quadratic flow
+    schedule), StepVideo and HunyuanVideo style discrete flow matching, Open-Sora rectified flow, DDPM / DDIM
+    (mindspeed_mm/tasks/inference/pipeline/{cogvideox,opensoraplan,stepvideo,hunyuanvideo}_pipeline.py).
+
+    ``dit(latents, t, text, text_mask)`` is the denoiser; schedulers receive it wrapped as ``model(x, t, **kwargs)`` with
+    the positive prompt in ``model_kwargs`` and the negative prompt in ``negative_kwargs``."""
+
+    PRESETS = {
+        "cogvideox": dict(model_id="cogvideo_diffusion", num_inference_steps=50, guidance_scale=6.0),
+        "opensoraplan": dict(model_id="opensoraplan_v1_5", num_inference_steps=50, guidance_scale=4.5),
+        "stepvideo": dict(model_id="flow_match_discrete", num_inference_timesteps=50, shift=13.0, guidance_scale=9.0),
+        "hunyuanvideo": dict(model_id="flow_match_discrete", num_inference_timesteps=50, shift=7.0, guidance_scale=1.0,
+                             embedded_guidance_scale=6.0),
+        "opensora": dict(model_id="rflow", num_inference_steps=30, cfg_scale=7.0),
+    }
+
+    def __init__(self, dit, scheduler=None, vae_decode: Optional[Callable] = None, text_encode: Optional[Callable] = None,
+                 run: Optional[Callable] = None, preset: Optional[str] = None):
+        from ..models.diffusion import build_scheduler
+        self.dit, self.vae_decode, self.text_encode, self.run = dit, vae_decode, text_encode, run
+        self.scheduler = scheduler if scheduler is not None else build_scheduler(self.PRESETS[preset or "stepvideo"])
+
+    def _model(self, x, t, text=None, text_mask=None, **extra):
+        if text.shape[0] != x.shape[0]:
+            text = text.expand(x.shape[0], -1, -1) if text.shape[0] == 1 else text.repeat(x.shape[0] // text.shape[0], 1, 1)
+            if text_mask is not None:
+                text_mask = text_mask.expand(x.shape[0], -1) if text_mask.shape[0] == 1 else text_mask.repeat(x.shape[0] // text_mask.shape[0], 1)
+        kw = {"run": self.run} if self.run is not None else {}
+        return self.dit(x, t.reshape(-1).expand(x.shape[0]) if t.numel() == 1 else t, text, text_mask, **kw)
+
+    @torch.no_grad()
+    def __call__(self, prompt_embeds, negative_prompt_embeds=None, prompt_mask=None, negative_mask=None, frames: int = 13,
+                 height: int = 32, width: int = 32, generator=None, device="cpu", dtype=torch.float32, **sample_kw):
+        if self.text_encode is not None and not isinstance(prompt_embeds, torch.Tensor):
+            prompt_embeds = self.text_encode(prompt_embeds)
+        B = prompt_embeds.shape[0]
+        C = self.dit.config.in_channels
+        lat = torch.randn(B, C, frames, height, width, generator=generator, dtype=torch.float32).to(device, dtype)
+        pos = dict(text=prompt_embeds.to(device, dtype), text_mask=prompt_mask)
+        neg = None if negative_prompt_embeds is None else dict(text=negative_prompt_embeds.to(device, dtype), text_mask=negative_mask)
+        sched = self.scheduler
+        if type(sched).__name__ in ("RFlow", "GaussianDiffusion", "DDPM", "IDDPM"):
+            # these samplers run cond / uncond as one doubled batch
+            text = pos["text"] if neg is None else torch.cat([pos["text"], neg["text"]])
+            mask = None
+            if prompt_mask is not None:
+                mask = prompt_mask if neg is None else torch.cat([prompt_mask, negative_mask if negative_mask is not None else prompt_mask])
+            guided = neg is not None
+            if not guided:
+                sample_kw.setdefault("guidance_scale", 1.0)
+            fn = (lambda x, t, **kw: self._model(x, t, text=text if x.shape[0] == text.shape[0] else pos["text"],
+                                                 text_mask=mask if mask is None or x.shape[0] == mask.shape[0] else prompt_mask))
+            if type(sched).__name__ == "RFlow" and not guided:
+                fn = (lambda x, t, **kw: self._model(x, t, text=torch.cat([pos["text"], pos["text"]]), text_mask=None if prompt_mask is None
+                                                     else torch.cat([prompt_mask, prompt_mask])))
+            lat = sched.sample(fn, lat, model_kwargs={}, **sample_kw)
+        else:
+            lat = sched.sample(self._model, lat, model_kwargs=pos, negative_kwargs=neg, **sample_kw)
+        return self.vae_decode(lat) if self.vae_decode is not None else lat

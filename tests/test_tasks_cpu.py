@@ -251,3 +251,28 @@ def test_feature_extraction_roundtrip_into_feature_dataset(tmp_path):
     fd = FeatureDataset(index=str(out / "index_rank0.jsonl"), data_folder=str(out))
     s = fd[0]
     assert s["latents"].shape == (4, 2, 2, 2) and s["prompt"].shape == (8, 32) and s["first_frame_latents"].shape == (4, 1, 2, 2)
+
+
+def test_text_to_video_pipeline_over_scheduler_families():
+    import torch
+    from mindspeed_mm_b200.models.diffusion import build_scheduler
+    from mindspeed_mm_b200.models.video_dits import CrossDiT, JointDiT, VideoDiTConfig
+    from mindspeed_mm_b200.tasks.inference import TextToVideoPipeline
+    torch.manual_seed(0)
+    dit = CrossDiT(VideoDiTConfig.tiny())
+    for p in dit.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    text, neg = torch.randn(1, 5, 32), torch.zeros(1, 5, 32)
+    for cfg in (dict(model_id="flow_match_discrete", shift=7.0, guidance_scale=3.0), dict(model_id="opensoraplan_v1_5", guidance_scale=2.0),
+                dict(model_id="cogvideo_diffusion"), dict(model_id="rflow", num_inference_steps=3, use_timestep_transform=False),
+                dict(model_id="iddpm", num_inference_steps=3, learn_sigma=False)):
+        pipe = TextToVideoPipeline(dit, build_scheduler(cfg))
+        kw = {} if cfg["model_id"] in ("rflow", "iddpm") else dict(num_inference_steps=4 if cfg["model_id"] != "opensoraplan_v1_5" else 4)
+        out = pipe(text, neg, frames=2, height=4, width=4, generator=torch.Generator().manual_seed(0), **kw)
+        assert out.shape == (1, 4, 2, 4, 4) and torch.isfinite(out).all(), cfg
+    joint = JointDiT(VideoDiTConfig.tiny())
+    for p in joint.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    pipe = TextToVideoPipeline(joint, preset="cogvideox", vae_decode=lambda z: z * 2)
+    out = pipe(text, frames=2, height=4, width=4, generator=torch.Generator().manual_seed(0), num_inference_steps=3)
+    assert out.shape == (1, 4, 2, 4, 4)

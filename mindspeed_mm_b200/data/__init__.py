@@ -54,6 +54,9 @@ def build_dataset(dataset_param, model=None):
             basic.setdefault("image_token_id", cfg.image_token_id)
             basic.setdefault("vision_start_token_id", cfg.vision_start_token_id)
         return cls(SyntheticVLMSpec(**basic))
+    if kind == "synthetic_speech":
+        from .synthetic import SyntheticSpeechSpec
+        return cls(SyntheticSpeechSpec(**basic))
     if kind == "synthetic_video_latents":
         from .synthetic import SyntheticVideoLatentSpec
         return cls(SyntheticVideoLatentSpec(**basic))
@@ -64,6 +67,8 @@ def build_collator(args, model, pin: bool):
     cp = args.data.dataloader_param.collate_param
     name = (cp.collator_id or cp.model_name or "").lower()
     cfg = getattr(model, "config", None)
+    if hasattr(model, "collate"):                 # models with their own sequence layout (speech LMs) pack their samples
+        return model.collate
     if "qwen2" in name or "vl" in name or args.data.dataset_param.dataset_type == "synthetic_vlm":
         from .collate import PackedVLMCollator
         v = cfg.vision

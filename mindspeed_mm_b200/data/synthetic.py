@@ -117,3 +117,36 @@ class SyntheticVideoLatentDataset(Dataset):
             latents=torch.randn(s.channels, s.frames, s.height, s.width, generator=g).to(s.dtype),
             prompt=torch.randn(s.text_len, s.text_dim, generator=g).to(s.dtype),
             prompt_mask=torch.ones(s.text_len, dtype=torch.bool))
+
+
+# ------------------------------------------------------------------------------------------------- speech
+@dataclass
+class SyntheticSpeechSpec:
+    """Utterances for the speech-token LMs: a text id list, a codec frame matrix and a reference mel clip."""
+    num_samples: int = 64
+    text_len: int = 12
+    frames: int = 20
+    n_codebooks: int = 4
+    text_vocab: int = 100
+    audio_vocab: int = 32
+    n_mels: int = 20
+    ref_frames: int = 30
+    seed: int = 0
+
+
+@data_register.register("synthetic_speech")
+class SyntheticSpeechDataset(Dataset):
+    def __init__(self, spec: SyntheticSpeechSpec):
+        self.spec = spec
+
+    def __len__(self):
+        return self.spec.num_samples
+
+    def __getitem__(self, i):
+        s = self.spec
+        g = torch.Generator().manual_seed(s.seed * 1_000_003 + i)
+        n_text = int(torch.randint(max(2, s.text_len // 2), s.text_len + 1, (1,), generator=g))
+        n_frames = int(torch.randint(max(2, s.frames // 2), s.frames + 1, (1,), generator=g))
+        return dict(text=torch.randint(1, s.text_vocab, (n_text,), generator=g),
+                    codes=torch.randint(0, s.audio_vocab, (n_frames, s.n_codebooks), generator=g),
+                    ref_mel=torch.randn(s.ref_frames, s.n_mels, generator=g))

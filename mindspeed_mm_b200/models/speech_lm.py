@@ -157,6 +157,30 @@ class MultiCodebookLM(_Wrapped):
         self.last_channel_losses = torch.stack(parts)
         return total / sum(cw)
 
+    def collate(self, samples: Sequence[dict], audio_slot: int = 0) -> dict:
+        """Utterances (``text`` ids, ``codes`` [frames, >= n_vq]) -> one packed batch: text rows carry the text id and padding
+        codes, audio rows carry ``audio_slot`` in the text channel and the delayed codes; labels are the inputs shifted
+        by one row inside each utterance (padding codes are not predicted)."""
+        c = self.config
+        pad = c.audio_vocab_size
+        rows, labels, cu = [], [], [0]
+        for smp in samples:
+            text, codes = smp["text"].long(), smp["codes"][:, : c.n_vq].long()
+            delayed = apply_delay_pattern(codes, pad)
+            t_rows = torch.cat([text[:, None], torch.full((text.numel(), c.n_vq), pad)], 1)
+            a_rows = torch.cat([torch.full((delayed.shape[0], 1), audio_slot), delayed], 1)
+            seq = torch.cat([t_rows, a_rows])
+            lab = torch.cat([seq[1:], torch.full((1, c.n_vq + 1), IGNORE)])
+            lab[:, 1:][lab[:, 1:] == pad] = IGNORE
+            lab[: text.numel() - 1, 1:] = IGNORE
+            lab[text.numel() - 1:, 0] = IGNORE               # inside the audio span only the code channels are trained
+            rows.append(seq)
+            labels.append(lab)
+            cu.append(cu[-1] + seq.shape[0])
+        lens = [b - a for a, b in zip(cu[:-1], cu[1:])]
+        return dict(input_ids=torch.cat(rows), labels=torch.cat(labels), cu_seqlens=torch.tensor(cu, dtype=torch.int32),
+                    max_seqlen=max(lens))
+
     @torch.no_grad()
     def generate_codes(self, prompt_ids: torch.Tensor, steps: int, pad_code: Optional[int] = None, temperature: float = 0.0,
                        generator=None) -> torch.Tensor:
@@ -245,11 +269,11 @@ class CosyVoice3LM(_Wrapped):
         S, H = c.speech_token_size, c.text.hidden_size
         self.sos, self.eos, self.task_id, self.fill = S, S + 1, S + 2, S + 3
         self.speech_embedding = Embedding(S + 200, H)
-        self.llm_decoder = nn.Parameter(torch.empty(S + 200, H))
+        self.llm_decoder = Embedding(S + 200, H)       # output table (rows = speech ids incl. the special ones)
         self.rng = random.Random(0)
 
     def _extra_units(self):
-        return [("speech_embedding", self.speech_embedding)]
+        return [("speech_embedding", self.speech_embedding), ("llm_decoder", self.llm_decoder)]
 
     # ------------------------------------------------------------------ sequence building
     def build_sample(self, text: Sequence[int], speech: Sequence[int], instruct: Sequence[int] = (), bistream: bool = False):
@@ -298,6 +322,12 @@ class CosyVoice3LM(_Wrapped):
                     labels=torch.tensor(tgt, device=device), cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=device),
                     max_seqlen=max(lens), n_samples=len(samples))
 
+    def collate(self, samples: Sequence[dict]) -> dict:
+        """Dataset rows (``text`` ids, ``codes`` whose first codebook is the speech token stream, optional ``instruct``)."""
+        S = self.config.speech_token_size
+        return self.pack([dict(text=s["text"].tolist(), speech=(s["codes"][:, 0] % S).tolist(),
+                               instruct=s["instruct"].tolist() if "instruct" in s else ()) for s in samples])
+
     # ------------------------------------------------------------------ model
     def embed(self, ids, is_speech, run=None):
         run = run or (lambda m, *a, **k: m(*a, **k))
@@ -312,15 +342,15 @@ class CosyVoice3LM(_Wrapped):
         h = self.backbone.lm_head.norm(h)
         labels = batch.get("labels")
         if labels is None:
-            return ops.linear(h, self.llm_decoder)
+            return ops.linear(h, self.llm_decoder.weight)
         if c.lsm_weight == 0.0 and c.length_normalized_loss:
-            loss = _ce_mean(h, self.llm_decoder, labels)
+            loss = _ce_mean(h, self.llm_decoder.weight, labels)
         else:
-            loss = label_smoothing_loss(ops.linear(h, self.llm_decoder), labels, c.lsm_weight, c.length_normalized_loss,
+            loss = label_smoothing_loss(ops.linear(h, self.llm_decoder.weight), labels, c.lsm_weight, c.length_normalized_loss,
                                         batch.get("n_samples", 1))
         with torch.no_grad():
             keep = labels != IGNORE
-            pred = ops.linear(h[keep], self.llm_decoder).argmax(-1)
+            pred = ops.linear(h[keep], self.llm_decoder.weight).argmax(-1)
             self.last_accuracy = (pred == labels[keep]).float().mean() if bool(keep.any()) else h.new_zeros(())
         return loss
 
@@ -329,7 +359,7 @@ class CosyVoice3LM(_Wrapped):
                  min_len: int = 0, generator=None, **sampling) -> List[int]:
         kinds = ["s"] + ["t"] * (len(instruct) + len(text)) + ["s"] + ["s"] * len(prompt_speech)
         ids = [self.sos] + list(instruct) + list(text) + [self.task_id] + list(prompt_speech)
-        dev = self.llm_decoder.device
+        dev = self.llm_decoder.weight.device
         out: List[int] = []
         for step in range(max_len):
             T = len(ids)
@@ -444,7 +474,8 @@ class CodePredictor(_Wrapped):
         self.heads = nn.ParameterList(nn.Parameter(torch.empty(V, Hp)) for _ in range(G - 1))
 
     def _extra_units(self):
-        return [("codec_embedding", self.codec_embedding)]
+        return [("codec_embedding", self.codec_embedding), ("small_to_mtp_projection", self.small_to_mtp_projection),
+                ("heads", self.heads)]
 
     def frame_hidden(self, frame_inputs: torch.Tensor, run=None) -> torch.Tensor:
         """``frame_inputs`` [N, L <= G, Ht] -> normed hidden [N, L, Hp]; every frame is its own causal sequence."""
@@ -507,7 +538,7 @@ class Qwen3TTSTalker(_Wrapped):
 
     def _extra_units(self):
         return [("text_embedding", self.text_embedding), ("text_projection", self.text_projection),
-                ("speaker_encoder", self.speaker_encoder)] + \
+                ("speaker_encoder", self.speaker_encoder), ("speaker_proj", self.speaker_proj)] + \
                [(f"code_predictor.{n}", m) for n, m in self.code_predictor.fsdp_units()]
 
     @torch.no_grad()
@@ -554,6 +585,15 @@ class Qwen3TTSTalker(_Wrapped):
             self.last_sub_talker_loss = sub.detach()
             loss = loss + c.sub_talker_weight * sub
         return loss
+
+    def collate(self, samples: Sequence[dict]) -> dict:
+        """Dataset rows (``text``, ``codes`` [frames, G], ``ref_mel``).  The last three ids of the codec vocabulary serve as
+        bos / eos / pad."""
+        c = self.config
+        V = c.talker.vocab_size
+        built = [self.build_sample(s["text"].tolist(), s["codes"][:, : c.num_code_groups].long() % (V - 3), V - 3, V - 2, V - 1)
+                 for s in samples]
+        return self.pack(built, ref_mels=torch.stack([s["ref_mel"] for s in samples]))
 
     @staticmethod
     def build_sample(text_ids: Sequence[int], codes: torch.Tensor, bos: int, eos: int, pad: int, speaker_slot: bool = True) -> dict:

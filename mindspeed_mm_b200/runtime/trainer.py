@@ -194,6 +194,8 @@ def _config_from_hf(cls, hf: dict):
 
 def _config_class(cls):
     import inspect
+    if getattr(cls, "config_class", None) is not None:
+        return cls.config_class
     sig = inspect.signature(cls.__init__)
     ann = list(sig.parameters.values())[1].annotation
     if isinstance(ann, str):

@@ -53,7 +53,7 @@ def test_cosyvoice3_layouts_loss_and_sampling():
     assert batch["cu_seqlens"].tolist() == [0, 9, 17]
     loss = c(batch)
     loss.backward()
-    assert c.speech_embedding.weight.grad is not None and c.llm_decoder.grad is not None
+    assert c.speech_embedding.weight.grad is not None and c.llm_decoder.weight.grad is not None
     # label smoothing: equals plain CE at 0 smoothing
     logits, target = torch.randn(6, 11), torch.tensor([1, 2, IGNORE, 4, 5, 0])
     ce = torch.nn.functional.cross_entropy(logits, target, ignore_index=IGNORE)

@@ -54,6 +54,9 @@ def build_dataset(dataset_param, model=None):
             basic.setdefault("image_token_id", cfg.image_token_id)
             basic.setdefault("vision_start_token_id", cfg.vision_start_token_id)
         return cls(SyntheticVLMSpec(**basic))
+    if kind == "synthetic_av_latents":
+        from .synthetic import SyntheticAVLatentSpec
+        return cls(SyntheticAVLatentSpec(**basic))
     if kind == "synthetic_speech":
         from .synthetic import SyntheticSpeechSpec
         return cls(SyntheticSpeechSpec(**basic))

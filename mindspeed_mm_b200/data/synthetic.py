@@ -150,3 +150,50 @@ class SyntheticSpeechDataset(Dataset):
         return dict(text=torch.randint(1, s.text_vocab, (n_text,), generator=g),
                     codes=torch.randint(0, s.audio_vocab, (n_frames, s.n_codebooks), generator=g),
                     ref_mel=torch.randn(s.ref_frames, s.n_mels, generator=g))
+
+
+# ------------------------------------------------------------------------------------------------- audio + video latents
+@dataclass
+class SyntheticAVLatentSpec:
+    """Pre-encoded joint audio-video samples in the layout of the LTX-2 trainer: patchified video latents with (t, h, w)
+    positions, audio latents with time positions, text features, flow-matching targets at one sigma per sample."""
+    num_samples: int = 32
+    grid: Sequence[int] = (3, 4, 4)
+    video_channels: int = 8
+    audio_tokens: int = 6
+    audio_channels: int = 6
+    text_len: int = 7
+    text_dim: int = 24
+    first_frame_clean: bool = True
+    seed: int = 0
+
+
+@data_register.register("synthetic_av_latents")
+class SyntheticAVLatentDataset(Dataset):
+    def __init__(self, spec: SyntheticAVLatentSpec):
+        self.spec = spec
+
+    def __len__(self):
+        return self.spec.num_samples
+
+    def __getitem__(self, i):
+        s = self.spec
+        g = torch.Generator().manual_seed(s.seed * 1_000_003 + i)
+        t, h, w = s.grid
+        n = t * h * w
+        idx = torch.arange(n)
+        pos = torch.stack([idx // (h * w), (idx // w) % h, idx % w]).float()
+        clean, noise = torch.randn(n, s.video_channels, generator=g), torch.randn(n, s.video_channels, generator=g)
+        sigma = float(torch.rand(1, generator=g))
+        sig = torch.full((n,), sigma)
+        mask = torch.ones(n, dtype=torch.bool)
+        if s.first_frame_clean:
+            sig[: h * w] = 0.0
+            mask[: h * w] = False
+        a_clean, a_noise = torch.randn(s.audio_tokens, s.audio_channels, generator=g), torch.randn(s.audio_tokens, s.audio_channels, generator=g)
+        return dict(video_latent=(1 - sig[:, None]) * clean + sig[:, None] * noise, video_timesteps=sig * 1000.0, video_positions=pos,
+                    video_target_velocity=noise - clean, loss_mask=mask,
+                    audio_latent=(1 - sigma) * a_clean + sigma * a_noise, audio_timesteps=torch.full((s.audio_tokens,), sigma * 1000.0),
+                    audio_positions=torch.arange(s.audio_tokens).float()[None] * (t / max(s.audio_tokens, 1)),
+                    audio_target_velocity=a_noise - a_clean,
+                    context=torch.randn(s.text_len, s.text_dim, generator=g), context_mask=torch.ones(s.text_len, dtype=torch.bool))

@@ -76,7 +76,7 @@ class FlowMatchScheduler:
         t = timestep.detach().float().cpu().reshape(-1)[0]
         return self.weights[torch.argmin((self.timesteps - t).abs())]
 
-    def training_losses(self, model_output, x_start, noise, t, reduction: str = "mean"):
+    def training_losses(self, model_output, x_start, noise, t, reduction: str = "mean", **_):
         target = noise - x_start
         loss = torch.nn.functional.mse_loss(model_output.float(), target.float(), reduction=reduction)
         return loss * self.training_weight(t).to(loss.device)

@@ -235,6 +235,9 @@ class LTX2Model(nn.Module):
     def forward(self, video_latent=None, video_timesteps=None, video_positions=None, context=None, video_target_velocity=None,
                 context_mask=None, loss_mask=None, audio_latent=None, audio_timesteps=None, audio_positions=None,
                 audio_target_velocity=None, audio_context=None, audio_context_mask=None, run=None, **_):
+        if isinstance(video_latent, dict):
+            # engine convention ``model(batch, run=...)``: unpack the batch and hand back the scalar loss
+            return self.forward(**video_latent, run=run)["loss"]
         run = run or (lambda m, *a, **k: m(*a, **k))
         c = self.config
         vx = ax = v = a = None

@@ -306,5 +306,8 @@ class SoRAModel(nn.Module):
             noise = torch.randn(latents.shape, generator=self.generator, dtype=torch.float32).to(latents.device, latents.dtype)
             x_t, noise, t = self.scheduler.q_sample(latents, noise=noise, generator=self.generator,
                                                     first_frame_latents=batch.get("first_frame_latents"))
-        pred = self.predictor(x_t, t.expand(latents.shape[0]), prompt, batch.get("clip_feature"), run=run)
-        return self.scheduler.training_losses(pred, latents, noise, t)
+        # fourth input: CLIP image tokens for the Wan image-to-video trunks, the prompt mask for the cross-attention DiTs
+        extra = batch["clip_feature"] if "clip_feature" in batch else batch.get("prompt_mask")
+        pred = self.predictor(x_t, t.expand(latents.shape[0]), prompt, extra, run=run)
+        loss = self.scheduler.training_losses(pred, latents, noise=noise, t=t, x_t=x_t)
+        return loss.mean() if loss.dim() else loss

@@ -586,29 +586,39 @@ class _null:
         return False
 
 
+def _flatten_arg(a, tensors):
+    """Replaces every tensor inside ``a`` (also inside dicts / lists / tuples) by its index into ``tensors``."""
+    if isinstance(a, torch.Tensor):
+        tensors.append(a)
+        return ("t", len(tensors) - 1)
+    if isinstance(a, dict):
+        return ("d", {k: _flatten_arg(v, tensors) for k, v in a.items()})
+    if isinstance(a, (list, tuple)) and any(isinstance(v, (torch.Tensor, dict, list, tuple)) for v in a):
+        return ("l", type(a), [_flatten_arg(v, tensors) for v in a])
+    return ("c", a)
+
+
+def _unflatten_arg(spec, tensors):
+    kind = spec[0]
+    if kind == "t":
+        return tensors[spec[1]]
+    if kind == "c":
+        return spec[1]
+    if kind == "d":
+        return {k: _unflatten_arg(v, tensors) for k, v in spec[1].items()}
+    return spec[1](_unflatten_arg(v, tensors) for v in spec[2])
+
+
 def _split_args(args, kwargs):
-    tensors, spec = [], []
-    for a in args:
-        if isinstance(a, torch.Tensor):
-            spec.append(("t", len(tensors)))
-            tensors.append(a)
-        else:
-            spec.append(("c", a))
-    kspec = {}
-    for k, a in kwargs.items():
-        if isinstance(a, torch.Tensor):
-            kspec[k] = ("t", len(tensors))
-            tensors.append(a)
-        else:
-            kspec[k] = ("c", a)
+    tensors: list = []
+    spec = [_flatten_arg(a, tensors) for a in args]
+    kspec = {k: _flatten_arg(a, tensors) for k, a in kwargs.items()}
     return tensors, (spec, kspec)
 
 
 def _join_args(spec, tensors):
     a_spec, k_spec = spec
-    args = [tensors[v] if k == "t" else v for k, v in a_spec]
-    kwargs = {n: (tensors[v] if k == "t" else v) for n, (k, v) in k_spec.items()}
-    return args, kwargs
+    return [_unflatten_arg(v, tensors) for v in a_spec], {n: _unflatten_arg(v, tensors) for n, v in k_spec.items()}
 
 
 class _UnitFn(torch.autograd.Function):

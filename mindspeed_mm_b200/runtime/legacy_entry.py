@@ -51,7 +51,8 @@ def model_provider(kind: str, args):
         pred = dict(mm["predictor"])
         if pred.get("model_id") != "wandit":
             from ..models.registry import build_model
-            net = build_model(pred["model_id"], pred)
+            with torch.device("meta"):
+                net = build_model(pred["model_id"], pred)
         else:
             with torch.device("meta"):
                 net = WanDiT(WanConfig.from_mm_json(pred))

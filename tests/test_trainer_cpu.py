@@ -109,7 +109,7 @@ def test_trainer_runs_speech_lm_recipes(capsys):
     import pytest
     from mindspeed_mm_b200.runtime.trainer import Trainer
     for rel in ("examples/moss_tts/finetune_moss_tts_delay_tiny.yaml", "examples/cosyvoice3/finetune_cosyvoice3_tiny.yaml",
-                "examples/qwen3tts/finetune_qwen3tts_tiny.yaml"):
+                "examples/qwen3tts/finetune_qwen3tts_tiny.yaml", "examples/ltx2/finetune_ltx2_tiny.yaml"):
         args = load_config(os.path.join(ROOT, rel), ["training.train_iters=3"], world_size=1)
         hist = Trainer(args, device="cpu").train()
         assert len(hist) == 3 and all(h["loss"] == h["loss"] and h["loss"] > 0 for h in hist), rel

@@ -147,3 +147,29 @@ def test_vace_hints_start_as_identity_and_train_only_the_branch():
     moved.mean().backward()
     assert all((p.grad is None) == (not n.startswith("vace_")) or not p.requires_grad for n, p in m.named_parameters())
     assert m.vace_patch_embedding.weight.grad is not None and m.blocks[0].ffn_0.weight.grad is None
+
+
+def test_generation_recipes_build_and_step_through_the_sora_wrapper():
+    import json
+    import os
+    from mindspeed_mm_b200.models.diffusion import build_scheduler
+    from mindspeed_mm_b200.models.registry import build_model
+    from mindspeed_mm_b200.models.wan import SoRAModel
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for rel in ("wan2.2/pretrain_model_ti2v_tiny.json", "vace/pretrain_model_tiny.json", "cogvideox/pretrain_model_tiny.json",
+                "opensoraplan/pretrain_model_tiny.json", "stepvideo/pretrain_model_tiny.json"):
+        mm = json.load(open(os.path.join(root, "examples", rel)))
+        torch.manual_seed(0)
+        net = build_model(mm["predictor"]["model_id"], mm["predictor"])
+        for p in net.parameters():
+            torch.nn.init.normal_(p, std=0.05)
+        model = SoRAModel(net, build_scheduler(mm["diffusion"]), seed=0)
+        batch = dict(latents=torch.randn(2, 16, 2, 4, 4), prompt=torch.randn(2, 6, 64))
+        loss = model(batch)
+        assert loss.dim() == 0 and torch.isfinite(loss), rel
+        loss.backward()
+        assert any(p.grad is not None and p.grad.abs().sum() > 0 for p in net.parameters()), rel
+    big = json.load(open(os.path.join(root, "examples/wan2.2/pretrain_model_a14b_high_noise.json")))
+    sched = build_scheduler(big["diffusion"])
+    _, _, t = sched.q_sample(torch.zeros(1, 16, 1, 2, 2), generator=torch.Generator().manual_seed(0))
+    assert float(t) >= 875.0                       # the high-noise expert only ever sees t above the boundary

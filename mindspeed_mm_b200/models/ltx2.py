@@ -199,6 +199,10 @@ class _StreamIO(nn.Module):
         self.out_table = nn.Parameter(torch.randn(2, dim) / dim ** 0.5)
         self.proj_out = Linear(dim, in_ch)
 
+    def forward(self, mode: str, *args):
+        """One sharding unit, two entry points: ``("prepare", latent, timesteps, context)`` and ``("output", x, emb, eps)``."""
+        return self.prepare(*args) if mode == "prepare" else self.output(*args)
+
     def prepare(self, latent, timesteps, context):
         x = self.patchify_proj(latent.to(self.patchify_proj.weight.dtype))
         temb, emb = self.adaln(timesteps)
@@ -243,7 +247,7 @@ class LTX2Model(nn.Module):
         vx = ax = v = a = None
         hd_v, hd_a = c.dim // c.num_heads, c.audio_dim // c.audio_heads
         if video_latent is not None and self.video_io is not None:
-            vx, v = self.video_io.prepare(video_latent, video_timesteps, context)
+            vx, v = run(self.video_io, "prepare", video_latent, video_timesteps, context)
             v["context_mask"] = context_mask
             v["pe"] = fractional_rope(video_positions, c.dim // c.num_heads, c.rope_theta, c.rope_axes)
             # the audio <-> video attentions share only the time axis; as keys of the audio queries the video tokens
@@ -254,7 +258,7 @@ class LTX2Model(nn.Module):
         if audio_latent is not None and self.audio_io is not None:
             if audio_timesteps is None or audio_positions is None:
                 raise ValueError("audio_timesteps and audio_positions are required with audio_latent")
-            ax, a = self.audio_io.prepare(audio_latent, audio_timesteps, audio_context if audio_context is not None else context)
+            ax, a = run(self.audio_io, "prepare", audio_latent, audio_timesteps, audio_context if audio_context is not None else context)
             a["context_mask"] = audio_context_mask if audio_context_mask is not None else context_mask
             a["pe"] = fractional_rope(audio_positions, c.audio_dim // c.audio_heads, c.rope_theta, (c.audio_rope_max,))
             a["cross_pe"] = fractional_rope(audio_positions[:, :1], hd_a, c.rope_theta, c.rope_axes[:1])
@@ -264,7 +268,7 @@ class LTX2Model(nn.Module):
         out = dict(loss=None, video_pred=None, audio_pred=None)
         losses = []
         if vx is not None:
-            out["video_pred"] = self.video_io.output(vx, v["emb"], c.norm_eps)
+            out["video_pred"] = run(self.video_io, "output", vx, v["emb"], c.norm_eps)
             if video_target_velocity is not None:
                 err = (out["video_pred"].float() - video_target_velocity.float()) ** 2
                 if loss_mask is not None:
@@ -273,7 +277,7 @@ class LTX2Model(nn.Module):
                 else:
                     losses.append(err.mean())
         if ax is not None:
-            out["audio_pred"] = self.audio_io.output(ax, a["emb"], c.norm_eps)
+            out["audio_pred"] = run(self.audio_io, "output", ax, a["emb"], c.norm_eps)
             if audio_target_velocity is not None:
                 losses.append(((out["audio_pred"].float() - audio_target_velocity.float()) ** 2).mean())
         if losses:

@@ -157,19 +157,12 @@ class BagelMoT(nn.Module):
     def __init__(self, config: Optional[BagelConfig] = None):
         super().__init__()
         self.config = c = config or BagelConfig.tiny()
-        H = c.hidden_size
-        self.embed_tokens = Embedding(c.vocab_size, H)
+        self.embed_tokens = Embedding(c.vocab_size, c.hidden_size)
         self.layers = nn.ModuleList(MoTLayer(c) for _ in range(c.num_layers))
-        self.norm, self.norm_gen = RMSNorm(H, c.eps), RMSNorm(H, c.eps)
-        self.lm_head = nn.Parameter(torch.empty(c.vocab_size, H))
-        pd = c.latent_channels * c.latent_patch ** 2
-        self.vae2llm, self.llm2vae = Linear(pd, H), Linear(H, pd)
-        self.time_1, self.time_2 = Linear(c.freq_dim, H), Linear(H, H)
-        self.latent_pos_embed = nn.Parameter(torch.zeros(c.max_latent_size ** 2, H))
-        self.connector_1, self.connector_2 = Linear(c.vit_dim, H), Linear(H, H)
+        self.io = _BagelIO(c)
 
     def fsdp_units(self):
-        return [("embed_tokens", self.embed_tokens)] + [(f"layers.{i}", l) for i, l in enumerate(self.layers)]
+        return [("embed_tokens", self.embed_tokens), ("io", self.io)] + [(f"layers.{i}", l) for i, l in enumerate(self.layers)]
 
     def forward(self, batch: dict, run=None):
         run = run or (lambda m, *a, **k: m(*a, **k))
@@ -182,8 +175,7 @@ class BagelMoT(nn.Module):
         x = x.index_copy(0, text_rows, run(self.embed_tokens, batch["input_ids"][text_rows]))
         und_rows = [text_rows]
         if batch.get("vit_rows") is not None and batch["vit_rows"].numel():
-            v = self.connector_2(ops.gelu_tanh(self.connector_1(batch["vit_embeds"].to(dt))))
-            x = x.index_copy(0, batch["vit_rows"], v)
+            x = x.index_copy(0, batch["vit_rows"], run(self.io, "vit", batch["vit_embeds"].to(dt)))
             und_rows.append(batch["vit_rows"])
         lat_rows = batch.get("latent_rows")
         target = None
@@ -195,8 +187,7 @@ class BagelMoT(nn.Module):
             sig = batch["timesteps"].to(dt)[:, None]
             noisy = (1 - sig) * clean + sig * noise
             target = (noise - clean).float()
-            temb = self.time_2(F.silu(self.time_1(sinusoidal_embedding(batch["timesteps"].float() * 1000.0, c.freq_dim).to(dt))))
-            x = x.index_copy(0, lat_rows, self.vae2llm(noisy) + temb + self.latent_pos_embed[batch["latent_pos"]].to(dt))
+            x = x.index_copy(0, lat_rows, run(self.io, "latent", noisy, batch["timesteps"], batch["latent_pos"]))
         else:
             lat_rows = torch.zeros(0, dtype=torch.long, device=dev)
         idx_und = torch.cat(und_rows).sort().values
@@ -210,20 +201,63 @@ class BagelMoT(nn.Module):
         total = x.new_zeros((), dtype=torch.float32)
         labels = batch.get("labels")
         if labels is not None:
-            h = self.norm(x[text_rows])
-            s, n = ops.linear_cross_entropy(h, self.lm_head, labels[text_rows])
-            out["ce"] = s / n.clamp(min=1).to(s.dtype)
+            out["ce"] = run(self.io, "ce", x[text_rows], labels[text_rows])
             total = total + c.ce_weight * out["ce"]
         if target is not None:
-            pred = self.llm2vae(self.norm_gen(x[idx_gen])).float()
+            pred = run(self.io, "velocity", x[idx_gen]).float()
             out["mse"] = ((pred - target) ** 2).mean()
             out["pred_velocity"] = pred
             total = total + c.mse_weight * out["mse"]
         out["loss"] = total
-        return out
+        return total if batch.get("loss_only") else out
+
+
+class _BagelIO(nn.Module):
+    """Everything around the decoder stack, as one sharding unit with several entry points: ViT connector, latent
+    input path (projection + timestep embedding + 2-D position table), text head with cross entropy, latent output head."""
+
+    def __init__(self, c: BagelConfig):
+        super().__init__()
+        self.c = c
+        H = c.hidden_size
+        self.norm, self.norm_gen = RMSNorm(H, c.eps), RMSNorm(H, c.eps)
+        self.lm_head = nn.Parameter(torch.empty(c.vocab_size, H))
+        pd = c.latent_channels * c.latent_patch ** 2
+        self.vae2llm, self.llm2vae = Linear(pd, H), Linear(H, pd)
+        self.time_1, self.time_2 = Linear(c.freq_dim, H), Linear(H, H)
+        self.latent_pos_embed = nn.Parameter(torch.zeros(c.max_latent_size ** 2, H))
+        self.connector_1, self.connector_2 = Linear(c.vit_dim, H), Linear(H, H)
+
+    def forward(self, mode: str, *a):
+        if mode == "vit":
+            return self.connector_2(ops.gelu_tanh(self.connector_1(a[0])))
+        if mode == "latent":
+            noisy, timesteps, pos = a
+            dt = noisy.dtype
+            temb = self.time_2(F.silu(self.time_1(sinusoidal_embedding(timesteps.float() * 1000.0, self.c.freq_dim).to(dt))))
+            return self.vae2llm(noisy) + temb + self.latent_pos_embed[pos].to(dt)
+        if mode == "ce":
+            s, n = ops.linear_cross_entropy(self.norm(a[0]), self.lm_head, a[1])
+            return s / n.clamp(min=1).to(s.dtype)
+        if mode == "velocity":
+            return self.llm2vae(self.norm_gen(a[0]))
+        raise ValueError(mode)
 
 
 # ------------------------------------------------------------------------------------------------- reward model
+class _ValueHead(nn.Module):
+    """Final norm of the decoder (its vocabulary table is dropped) followed by the linear value head."""
+
+    def __init__(self, lm_head: nn.Module, hidden: int, output_dim: int):
+        super().__init__()
+        self.lm_head = lm_head
+        self.lm_head.weight = None
+        self.rm_head = nn.Linear(hidden, output_dim, bias=False)
+
+    def forward(self, h):
+        return self.rm_head(self.lm_head.norm(h).to(self.rm_head.weight.dtype))
+
+
 @model_register.register("qwen2vl_reward")
 class RewardModelBT(nn.Module):
     """``forward(batch)``: packed VLM batch whose sequences alternate chosen, rejected; the value head is read at the last
@@ -236,15 +270,16 @@ class RewardModelBT(nn.Module):
             backbone = build_preset("qwen2vl")
         self.backbone = backbone
         self.reward_token_id = reward_token_id
-        self.rm_head = nn.Linear(backbone.config.text.hidden_size, output_dim, bias=False)
+        self.value_head = _ValueHead(backbone.lm_head, backbone.config.text.hidden_size, output_dim)
 
     def fsdp_units(self):
-        return [(f"backbone.{n}", m) for n, m in self.backbone.fsdp_units() if n != "lm_head"]
+        return [(f"backbone.{n}", m) for n, m in self.backbone.fsdp_units() if n != "lm_head"] + [("value_head", self.value_head)]
 
     def rewards(self, batch: dict, run=None) -> torch.Tensor:
+        run = run or (lambda m, *a, **k: m(*a, **k))
         b = {k: v for k, v in batch.items() if k != "labels"}
         b["return_hidden"] = True
-        h = self.backbone.lm_head.norm(self.backbone(b, run))
+        h = self.backbone(b, run)
         cu = batch["cu_seqlens"].long()
         rows = cu[1:] - 1
         if self.reward_token_id is not None:
@@ -255,7 +290,7 @@ class RewardModelBT(nn.Module):
                 mine = hit[seq_of == s]
                 if mine.numel():
                     rows[s] = mine[-1]
-        return self.rm_head(h[rows].float().to(self.rm_head.weight.dtype)).squeeze(-1)
+        return run(self.value_head, h[rows]).squeeze(-1)
 
     def forward(self, batch: dict, run=None):
         from ..tasks.preference import bradley_terry_loss

@@ -52,6 +52,57 @@ def _positions(cu: torch.Tensor, total: int, device) -> torch.Tensor:
     return torch.arange(total, device=device) - starts
 
 
+class SummedEmbeddings(nn.Module):
+    """``n`` embedding tables looked up by the columns of an id matrix: ``forward(ids [T, n])`` returns the sum [T, D],
+    ``forward(ids, stack=True)`` the separate rows [T, n, D]."""
+
+    def __init__(self, n: int, vocab: int, dim: int):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(n, vocab, dim))
+
+    def forward(self, ids, stack: bool = False):
+        n, V, D = self.weight.shape
+        flat = self.weight.view(n * V, D)
+        e = F.embedding(ids + torch.arange(ids.shape[1], device=ids.device) * V, flat)      # [T, k, D], k <= n
+        return e if stack else e.sum(1)
+
+
+class NormedHeads(nn.Module):
+    """The decoder's final norm followed by one or several output tables.  Owns the backbone's ``lm_head`` module (so
+    that norm and tables are gathered together as one sharding unit) plus ``extra`` tables of its own.
+
+    ``forward(h, labels [T, n_tables] or None, drop_last)``: returns the per-table mean cross entropies [n_tables] (tables
+    whose label column is all -100 give 0) or, without labels, the list of logits.  ``drop_last[i]`` removes the last
+    row of table i from the prediction (an input-only padding id)."""
+
+    def __init__(self, lm_head: nn.Module, extra: Sequence[Tuple[int, int]] = (), use_lm_table: bool = True):
+        super().__init__()
+        self.lm_head = lm_head
+        self.use_lm_table = use_lm_table
+        if not use_lm_table:
+            self.lm_head.weight = None
+        self.extra = nn.ParameterList(nn.Parameter(torch.empty(v, d)) for v, d in extra)
+
+    def tables(self, drop_last: Sequence[bool] = ()):
+        ws = ([self.lm_head.weight] if self.use_lm_table else []) + list(self.extra)
+        return [w[:-1] if i < len(drop_last) and drop_last[i] else w for i, w in enumerate(ws)]
+
+    def forward(self, h, labels=None, drop_last: Sequence[bool] = (), return_normed: bool = False):
+        hn = self.lm_head.norm(h)
+        ws = self.tables(drop_last)
+        if labels is None:
+            out = [ops.linear(hn, w) for w in ws]
+            return (out, hn) if return_normed else out
+        if labels.dim() == 1:
+            labels = labels[:, None]
+        losses = []
+        for k, w in enumerate(ws):
+            lab = labels[:, k]
+            losses.append(_ce_mean(hn, w, lab) if bool((lab != IGNORE).any()) else hn.new_zeros((), dtype=torch.float32))
+        out = torch.stack(losses)
+        return (out, hn) if return_normed else out
+
+
 class _Wrapped(nn.Module):
     """Common plumbing: ``self.backbone`` + extra tables / heads, exposed to the sharding engine as units."""
 
@@ -61,7 +112,8 @@ class _Wrapped(nn.Module):
         return []
 
     def fsdp_units(self):
-        return self._extra_units() + [(f"backbone.{n}", m) for n, m in self.backbone.fsdp_units()]
+        # the backbone's lm_head belongs to this model's ``heads`` unit
+        return self._extra_units() + [(f"backbone.{n}", m) for n, m in self.backbone.fsdp_units() if n != "lm_head"]
 
     def hidden(self, embeds, batch: dict, run=None):
         b = {k: v for k, v in batch.items() if k not in ("labels", "input_ids")}
@@ -119,43 +171,32 @@ class MultiCodebookLM(_Wrapped):
         self.config = c = config or MultiCodebookConfig.tiny()
         self.backbone = _text_lm(c.text)
         H = c.text.hidden_size
-        self.emb_ext = nn.ModuleList(Embedding(c.audio_vocab_size + 1, H) for _ in range(c.n_vq))
-        self.audio_heads = nn.ParameterList(nn.Parameter(torch.empty(c.audio_vocab_size + 1, H)) for _ in range(c.n_vq))
+        self.emb_ext = SummedEmbeddings(c.n_vq, c.audio_vocab_size + 1, H)
+        self.heads = NormedHeads(self.backbone.lm_head, [(c.audio_vocab_size + 1, H)] * c.n_vq)
 
     def _extra_units(self):
-        return [("emb_ext", self.emb_ext), ("audio_heads", self.audio_heads)]
+        return [("emb_ext", self.emb_ext), ("heads", self.heads)]
 
     def embed(self, ids, run=None):
         run = run or (lambda m, *a, **k: m(*a, **k))
-        x = run(self.backbone.embed_tokens, ids[:, 0])
-        for k, emb in enumerate(self.emb_ext):
-            x = x + emb(ids[:, k + 1])
-        return x
+        return run(self.backbone.embed_tokens, ids[:, 0]) + run(self.emb_ext, ids[:, 1:])
 
     def forward(self, batch: dict, run=None):
         c = self.config
         ids = batch["input_ids"]
         if ids.dim() != 2 or ids.shape[1] != c.n_vq + 1:
             raise ValueError("input_ids must be [tokens, 1 + n_vq]")
+        run = run or (lambda m, *a, **k: m(*a, **k))
         h = self.hidden(self.embed(ids, run), batch, run)
-        h = self.backbone.lm_head.norm(h)
         # the last index of every audio table is an input-only padding code: it is never predicted
-        weights = [self.backbone.lm_head.weight] + [w[:-1] for w in self.audio_heads]
+        drop = [False] + [True] * c.n_vq
         labels = batch.get("labels")
         if labels is None:
-            return [ops.linear(h, w) for w in weights]
-        cw = list(c.channel_loss_weight or [1.0] * len(weights))
-        total, parts = h.new_zeros((), dtype=torch.float32), []
-        for k, w in enumerate(weights):
-            lab = labels[:, k]
-            if bool((lab != IGNORE).any()):
-                lk = _ce_mean(h, w, lab)
-                parts.append(lk.detach())
-                total = total + cw[k] * lk
-            else:
-                parts.append(h.new_zeros((), dtype=torch.float32))
-        self.last_channel_losses = torch.stack(parts)
-        return total / sum(cw)
+            return run(self.heads, h, None, drop)
+        parts = run(self.heads, h, labels, drop)
+        cw = torch.tensor(list(c.channel_loss_weight or [1.0] * (c.n_vq + 1)), dtype=parts.dtype, device=parts.device)
+        self.last_channel_losses = parts.detach()
+        return (parts * cw).sum() / cw.sum()
 
     def collate(self, samples: Sequence[dict], audio_slot: int = 0) -> dict:
         """Utterances (``text`` ids, ``codes`` [frames, >= n_vq]) -> one packed batch: text rows carry the text id and padding
@@ -269,11 +310,13 @@ class CosyVoice3LM(_Wrapped):
         S, H = c.speech_token_size, c.text.hidden_size
         self.sos, self.eos, self.task_id, self.fill = S, S + 1, S + 2, S + 3
         self.speech_embedding = Embedding(S + 200, H)
-        self.llm_decoder = Embedding(S + 200, H)       # output table (rows = speech ids incl. the special ones)
+        # output table over the speech ids (incl. the special ones) behind the decoder's final norm; the text-vocabulary
+        # table of the backbone is dropped
+        self.heads = NormedHeads(self.backbone.lm_head, [(S + 200, H)], use_lm_table=False)
         self.rng = random.Random(0)
 
     def _extra_units(self):
-        return [("speech_embedding", self.speech_embedding), ("llm_decoder", self.llm_decoder)]
+        return [("speech_embedding", self.speech_embedding), ("heads", self.heads)]
 
     # ------------------------------------------------------------------ sequence building
     def build_sample(self, text: Sequence[int], speech: Sequence[int], instruct: Sequence[int] = (), bistream: bool = False):
@@ -331,35 +374,35 @@ class CosyVoice3LM(_Wrapped):
     # ------------------------------------------------------------------ model
     def embed(self, ids, is_speech, run=None):
         run = run or (lambda m, *a, **k: m(*a, **k))
-        text_vocab = self.backbone.embed_tokens.weight.shape[0]
+        text_vocab = self.config.text.vocab_size
         te = run(self.backbone.embed_tokens, torch.where(is_speech, torch.zeros_like(ids), ids).clamp(max=text_vocab - 1))
         se = run(self.speech_embedding, torch.where(is_speech, ids, torch.zeros_like(ids)))
         return torch.where(is_speech[:, None], se, te)
 
     def forward(self, batch: dict, run=None):
         c = self.config
+        run = run or (lambda m, *a, **k: m(*a, **k))
         h = self.hidden(self.embed(batch["input_ids"], batch["is_speech"], run), batch, run)
-        h = self.backbone.lm_head.norm(h)
         labels = batch.get("labels")
         if labels is None:
-            return ops.linear(h, self.llm_decoder.weight)
+            return run(self.heads, h)[0]
         if c.lsm_weight == 0.0 and c.length_normalized_loss:
-            loss = _ce_mean(h, self.llm_decoder.weight, labels)
-        else:
-            loss = label_smoothing_loss(ops.linear(h, self.llm_decoder.weight), labels, c.lsm_weight, c.length_normalized_loss,
-                                        batch.get("n_samples", 1))
-        with torch.no_grad():
-            keep = labels != IGNORE
-            pred = ops.linear(h[keep], self.llm_decoder.weight).argmax(-1)
-            self.last_accuracy = (pred == labels[keep]).float().mean() if bool(keep.any()) else h.new_zeros(())
-        return loss
+            return run(self.heads, h, labels)[0]
+        return label_smoothing_loss(run(self.heads, h)[0], labels, c.lsm_weight, c.length_normalized_loss, batch.get("n_samples", 1))
+
+    @torch.no_grad()
+    def accuracy(self, batch: dict) -> torch.Tensor:
+        """Share of label positions whose arg-max prediction is right (the reference logs it next to the loss)."""
+        logits = self.forward({k: v for k, v in batch.items() if k != "labels"})
+        keep = batch["labels"] != IGNORE
+        return (logits[keep].argmax(-1) == batch["labels"][keep]).float().mean()
 
     @torch.no_grad()
     def generate(self, text: Sequence[int], prompt_speech: Sequence[int] = (), instruct: Sequence[int] = (), max_len: int = 64,
                  min_len: int = 0, generator=None, **sampling) -> List[int]:
         kinds = ["s"] + ["t"] * (len(instruct) + len(text)) + ["s"] + ["s"] * len(prompt_speech)
         ids = [self.sos] + list(instruct) + list(text) + [self.task_id] + list(prompt_speech)
-        dev = self.llm_decoder.weight.device
+        dev = self.speech_embedding.weight.device
         out: List[int] = []
         for step in range(max_len):
             T = len(ids)
@@ -460,6 +503,28 @@ class Qwen3TTSConfig:
         return Qwen3TTSConfig(**d)
 
 
+class _FrameHeads(nn.Module):
+    """Heads of the code predictor: final norm, then head i - 1 reads position i of every frame sequence."""
+
+    def __init__(self, lm_head: nn.Module, n_heads: int, vocab: int, dim: int):
+        super().__init__()
+        self.lm_head = lm_head
+        self.lm_head.weight = None
+        self.weight = nn.Parameter(torch.empty(n_heads, vocab, dim))
+
+    def forward(self, h, codec_ids=None, position: Optional[int] = None):
+        """``h`` [N, L, D].  With ``codec_ids`` [N, G]: mean CE over heads 1 .. G-1.  With ``position`` i: logits of head i - 1
+        at the last position."""
+        hn = self.lm_head.norm(h)
+        if codec_ids is None:
+            return ops.linear(hn[:, -1], self.weight[position - 1])
+        G = codec_ids.shape[1]
+        total = hn.new_zeros((), dtype=torch.float32)
+        for i in range(1, G):
+            total = total + _ce_mean(hn[:, i], self.weight[i - 1], codec_ids[:, i])
+        return total / (G - 1)
+
+
 class CodePredictor(_Wrapped):
     """Per-frame decoder over the codebook axis: inputs [talker hidden, emb(code 0), ..., emb(code G-2)] (all in the
     talker's width, projected down), position i + 1 predicts code i + 1 with its own head."""
@@ -469,32 +534,34 @@ class CodePredictor(_Wrapped):
         G, Ht, Hp, V = c.num_code_groups, c.talker.hidden_size, c.predictor.hidden_size, c.predictor.vocab_size
         self.G = G
         self.backbone = _text_lm(c.predictor)
-        self.codec_embedding = nn.ModuleList(Embedding(V, Ht) for _ in range(G - 1))     # tables of codes 1 .. G-1
-        self.small_to_mtp_projection = nn.Linear(Ht, Hp) if Ht != Hp else nn.Identity()
-        self.heads = nn.ParameterList(nn.Parameter(torch.empty(V, Hp)) for _ in range(G - 1))
+        self.backbone.embed_tokens = None                                  # inputs are always embeddings
+        self.codec_embedding = SummedEmbeddings(G - 1, V, Ht)              # tables of codes 1 .. G-1
+        self.small_to_mtp_projection = nn.Linear(Ht, Hp)
+        self.heads = _FrameHeads(self.backbone.lm_head, G - 1, V, Hp)
 
     def _extra_units(self):
         return [("codec_embedding", self.codec_embedding), ("small_to_mtp_projection", self.small_to_mtp_projection),
                 ("heads", self.heads)]
 
+    def fsdp_units(self):
+        return [(n, m) for n, m in super().fsdp_units() if m is not None]
+
     def frame_hidden(self, frame_inputs: torch.Tensor, run=None) -> torch.Tensor:
-        """``frame_inputs`` [N, L <= G, Ht] -> normed hidden [N, L, Hp]; every frame is its own causal sequence."""
+        """``frame_inputs`` [N, L <= G, Ht] -> hidden [N, L, Hp]; every frame is its own causal sequence."""
+        run = run or (lambda m, *a, **k: m(*a, **k))
         N, L, _ = frame_inputs.shape
-        x = self.small_to_mtp_projection(frame_inputs).reshape(N * L, -1)
+        x = run(self.small_to_mtp_projection, frame_inputs).reshape(N * L, -1)
         cu = torch.arange(0, (N + 1) * L, L, dtype=torch.int32, device=x.device)
-        h = self.hidden(x, dict(cu_seqlens=cu, max_seqlen=L), run)
-        return self.backbone.lm_head.norm(h).reshape(N, L, -1)
+        return self.hidden(x, dict(cu_seqlens=cu, max_seqlen=L), run).reshape(N, L, -1)
 
     def loss(self, talker_hidden, codec_ids, code0_embed, run=None):
         """``talker_hidden`` [N, Ht], ``codec_ids`` [N, G], ``code0_embed`` [N, Ht] (from the talker's own codec table)."""
-        G = self.G
-        seq = [talker_hidden[:, None], code0_embed[:, None]] + \
-              [self.codec_embedding[i - 1](codec_ids[:, i])[:, None] for i in range(1, G - 1)]
+        run = run or (lambda m, *a, **k: m(*a, **k))
+        seq = [talker_hidden[:, None], code0_embed[:, None]]
+        if self.G > 2:
+            seq.append(run(self.codec_embedding, codec_ids[:, 1:self.G - 1], True))
         h = self.frame_hidden(torch.cat(seq, 1), run)                                     # [N, G, Hp]
-        total = h.new_zeros((), dtype=torch.float32)
-        for i in range(1, G):
-            total = total + _ce_mean(h[:, i], self.heads[i - 1], codec_ids[:, i])
-        return total / (G - 1)
+        return run(self.heads, h, codec_ids)
 
     @torch.no_grad()
     def generate(self, talker_hidden, code0, code0_embed, temperature: float = 0.0, generator=None):
@@ -502,14 +569,39 @@ class CodePredictor(_Wrapped):
         seq = torch.cat([talker_hidden[:, None], code0_embed[:, None]], 1)
         codes = [code0]
         for i in range(1, self.G):
-            h = self.frame_hidden(seq)[:, -1]
-            lg = ops.linear(h, self.heads[i - 1]).float()
+            lg = self.heads(self.frame_hidden(seq), None, i).float()
             nxt = lg.argmax(-1) if temperature <= 0 else torch.multinomial(F.softmax(lg / temperature, -1).cpu(), 1,
                                                                             generator=generator)[:, 0].to(lg.device)
             codes.append(nxt)
             if i < self.G - 1:
-                seq = torch.cat([seq, self.codec_embedding[i - 1](nxt)[:, None]], 1)
+                V = self.codec_embedding.weight.shape[1]
+                emb = F.embedding(nxt + (i - 1) * V, self.codec_embedding.weight.view(-1, self.codec_embedding.weight.shape[2]))
+                seq = torch.cat([seq, emb[:, None]], 1)
         return torch.stack(codes, 1)
+
+
+class _TextFrontEnd(nn.Module):
+    """Text id -> talker width: embedding in the text model's width followed by a two-layer projection."""
+
+    def __init__(self, vocab, text_hidden, hidden):
+        super().__init__()
+        self.embedding = Embedding(vocab, text_hidden)
+        self.fc1, self.fc2 = nn.Linear(text_hidden, text_hidden), nn.Linear(text_hidden, hidden)
+
+    def forward(self, ids):
+        return self.fc2(F.silu(self.fc1(self.embedding(ids))))
+
+
+class _SpeakerFrontEnd(nn.Module):
+    def __init__(self, c: "Qwen3TTSConfig", hidden):
+        super().__init__()
+        self.encoder = SpeakerEncoder(c.n_mels, c.speaker_channels, c.speaker_dim)
+        self.proj = nn.Linear(c.speaker_dim, hidden)
+
+    def forward(self, mels=None, embedding=None):
+        if embedding is None:
+            embedding = self.encoder(mels).detach()            # the reference trains with a frozen speaker embedding
+        return self.proj(embedding)
 
 
 @model_register.register("qwen3tts")
@@ -520,7 +612,7 @@ class Qwen3TTSTalker(_Wrapped):
     this position: control ids in the prefix, code 0 of the previous frame inside the audio span), ``codec_in_mask`` [T],
     ``codec_ids`` [T, G] + ``codec_mask`` [T] (positions that carry a full frame whose codes 1.. are added to the input),
     ``labels`` [T] (code 0 to predict, -100 elsewhere), ``speaker_pos`` [n_seq] (row that receives the speaker embedding),
-    ``ref_mels`` [n_seq, frames, n_mels] or ``speaker_embedding`` [n_seq, H], ``cu_seqlens``, ``max_seqlen``.
+    ``ref_mels`` [n_seq, frames, n_mels] or ``speaker_embedding`` [n_seq, speaker_dim], ``cu_seqlens``, ``max_seqlen``.
     """
     config_class = Qwen3TTSConfig
 
@@ -529,16 +621,13 @@ class Qwen3TTSTalker(_Wrapped):
         self.config = c = config or Qwen3TTSConfig.tiny()
         H = c.talker.hidden_size
         self.backbone = _text_lm(c.talker)                      # embed_tokens = codec embedding, lm_head = codec head
-        self.text_embedding = Embedding(c.text_vocab_size, c.text_hidden_size)
-        self.text_projection = nn.Sequential(nn.Linear(c.text_hidden_size, c.text_hidden_size), nn.SiLU(),
-                                             nn.Linear(c.text_hidden_size, H))
+        self.text_front = _TextFrontEnd(c.text_vocab_size, c.text_hidden_size, H)
+        self.speaker_front = _SpeakerFrontEnd(c, H)
+        self.heads = NormedHeads(self.backbone.lm_head)
         self.code_predictor = CodePredictor(c)
-        self.speaker_encoder = SpeakerEncoder(c.n_mels, c.speaker_channels, c.speaker_dim)
-        self.speaker_proj = nn.Linear(c.speaker_dim, H) if c.speaker_dim != H else nn.Identity()
 
     def _extra_units(self):
-        return [("text_embedding", self.text_embedding), ("text_projection", self.text_projection),
-                ("speaker_encoder", self.speaker_encoder), ("speaker_proj", self.speaker_proj)] + \
+        return [("text_front", self.text_front), ("speaker_front", self.speaker_front), ("heads", self.heads)] + \
                [(f"code_predictor.{n}", m) for n, m in self.code_predictor.fsdp_units()]
 
     @torch.no_grad()
@@ -549,30 +638,27 @@ class Qwen3TTSTalker(_Wrapped):
     def embed(self, batch, run=None):
         run = run or (lambda m, *a, **k: m(*a, **k))
         dt = self.backbone.embed_tokens.weight.dtype
-        x = self.text_projection(run(self.text_embedding, batch["text_ids"])) * batch["text_mask"][:, None].to(dt)
+        x = run(self.text_front, batch["text_ids"]) * batch["text_mask"][:, None].to(dt)
         x = x + run(self.backbone.embed_tokens, batch["codec_in"]) * batch["codec_in_mask"][:, None].to(dt)
-        spk = batch.get("speaker_embedding")
-        if spk is None and batch.get("ref_mels") is not None:
-            spk = self.speaker_encoder(batch["ref_mels"].to(dt)).detach()
-        if spk is not None:
-            x = x.index_copy(0, batch["speaker_pos"], x[batch["speaker_pos"]] * 0 + self.speaker_proj(spk.to(dt)))
+        if batch.get("speaker_embedding") is not None or batch.get("ref_mels") is not None:
+            mels = batch["ref_mels"].to(dt) if batch.get("ref_mels") is not None else None
+            emb = batch["speaker_embedding"].to(dt) if batch.get("speaker_embedding") is not None else None
+            x = x.index_copy(0, batch["speaker_pos"], run(self.speaker_front, mels, emb).to(x.dtype))
         cm = batch["codec_mask"]
         if bool(cm.any()):
-            add = x.new_zeros(int(cm.sum()), x.shape[1])
-            frames = batch["codec_ids"][cm]
-            for i in range(1, self.config.num_code_groups):
-                add = add + self.code_predictor.codec_embedding[i - 1](frames[:, i])
-            x = x.index_add(0, cm.nonzero(as_tuple=True)[0], add)
+            add = run(self.code_predictor.codec_embedding, batch["codec_ids"][cm][:, 1:])
+            x = x.index_add(0, cm.nonzero(as_tuple=True)[0], add.to(x.dtype))
         return x
 
     def forward(self, batch: dict, run=None):
+        run = run or (lambda m, *a, **k: m(*a, **k))
         c = self.config
         h = self.hidden(self.embed(batch, run), batch, run)
         labels = batch.get("labels")
-        hn = self.backbone.lm_head.norm(h)
         if labels is None:
-            return ops.linear(hn, self.backbone.lm_head.weight)
-        loss = _ce_mean(hn, self.backbone.lm_head.weight, labels)
+            return run(self.heads, h)[0]
+        parts, hn = run(self.heads, h, labels, (), True)
+        loss = parts[0]
         # the position that predicts code 0 of a frame also conditions that frame's remaining codebooks
         has_frame = labels != IGNORE
         if batch.get("eos_rows") is not None:
@@ -580,7 +666,7 @@ class Qwen3TTSTalker(_Wrapped):
         pred_pos = has_frame.nonzero(as_tuple=True)[0]
         frames = batch.get("label_codec_ids")
         if frames is not None and pred_pos.numel():
-            code0_embed = self.backbone.embed_tokens(frames[:, 0])
+            code0_embed = run(self.backbone.embed_tokens, frames[:, 0])
             sub = self.code_predictor.loss(hn[pred_pos], frames, code0_embed, run)
             self.last_sub_talker_loss = sub.detach()
             loss = loss + c.sub_talker_weight * sub

@@ -213,6 +213,7 @@ class _Final(nn.Module):
 
 class CrossDiT(nn.Module):
     """``forward(latents [B, C, F, H, W], t [B], text [B, L, text_dim], text_mask=None, text_2=None) -> prediction``."""
+    cond_input = "prompt_mask"          # which batch entry the generic training wrapper passes as the fourth argument
 
     def __init__(self, config: VideoDiTConfig):
         super().__init__()
@@ -273,6 +274,8 @@ class JointBlock(nn.Module):
 
 
 class JointDiT(nn.Module):
+    cond_input = "prompt_mask"
+
     def __init__(self, config: VideoDiTConfig):
         super().__init__()
         self.config = c = config
@@ -282,7 +285,8 @@ class JointDiT(nn.Module):
         self.final = _Final(c)
 
     def fsdp_units(self):
-        return [("embed", self.embed)] + [(f"blocks.{i}", b) for i, b in enumerate(self.blocks)] + [("final", self.final)]
+        return [("embed", self.embed)] + [(f"blocks.{i}", b) for i, b in enumerate(self.blocks)] + \
+               [("norm_final", self.norm_final), ("final", self.final)]
 
     def forward(self, latents, t, text, text_mask=None, run=None, **_):
         run = run or (lambda m, *a, **k: m(*a, **k))
@@ -293,7 +297,7 @@ class JointDiT(nn.Module):
         h = torch.cat([ctx, x], 1)
         for blk in self.blocks:
             h = run(blk, h, temb, n_text, cos, sin)
-        h = self.norm_final(h)[:, n_text:]
+        h = run(self.norm_final, h)[:, n_text:]
         return run(self.final, h, temb, grid)
 
 

@@ -307,7 +307,7 @@ class SoRAModel(nn.Module):
             x_t, noise, t = self.scheduler.q_sample(latents, noise=noise, generator=self.generator,
                                                     first_frame_latents=batch.get("first_frame_latents"))
         # fourth input: CLIP image tokens for the Wan image-to-video trunks, the prompt mask for the cross-attention DiTs
-        extra = batch["clip_feature"] if "clip_feature" in batch else batch.get("prompt_mask")
+        extra = batch.get(getattr(self.predictor, "cond_input", "clip_feature"))
         pred = self.predictor(x_t, t.expand(latents.shape[0]), prompt, extra, run=run)
         loss = self.scheduler.training_losses(pred, latents, noise=noise, t=t, x_t=x_t)
         return loss.mean() if loss.dim() else loss

@@ -233,6 +233,10 @@ class VaceWanDiT(WanDiT):
         self.vace_blocks = nn.ModuleList([VaceBlock(config, i == 0) for i in range(len(config.vace_layers))])
         self.vace_to_trunk = {layer: i for i, layer in enumerate(config.vace_layers)}
 
+    def fsdp_units(self):
+        return super().fsdp_units() + [("vace_patch_embedding", self.vace_patch_embedding)] + \
+               [(f"vace_blocks.{i}", b) for i, b in enumerate(self.vace_blocks)]
+
     def freeze_trunk(self):
         for name, p in self.named_parameters():
             p.requires_grad_(name.startswith("vace_"))
@@ -249,7 +253,7 @@ class VaceWanDiT(WanDiT):
         hints = []
         if vace_context is not None:
             tok, _ = self.embeddings.patchify(vace_context.to(x.dtype))
-            ctrl = self.vace_patch_embedding(tok)
+            ctrl = run(self.vace_patch_embedding, tok)
             if ctrl.shape[1] < x.shape[1]:                                       # shorter control clips are zero-padded
                 ctrl = F.pad(ctrl, (0, 0, 0, x.shape[1] - ctrl.shape[1]))
             for vb in self.vace_blocks:

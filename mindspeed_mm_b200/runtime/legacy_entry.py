@@ -83,9 +83,11 @@ def datasets_provider(kind: str, args, model, ps):
                                  v.window_size, v.hidden_size // v.num_heads)
     else:
         c = model.predictor.config
+        channels = getattr(c, "in_dim", None) or getattr(c, "in_channels")       # Wan names it in_dim, the other DiTs in_channels
         ds = SyntheticVideoLatentDataset(SyntheticVideoLatentSpec(
-            channels=c.in_dim, frames=int(basic.get("frames", 5)), height=int(basic.get("height", 16)),
-            width=int(basic.get("width", 16)), text_len=c.text_len, text_dim=c.text_dim, seed=args.seed,
+            channels=channels, frames=int(basic.get("frames", 5)), height=int(basic.get("height", 16)),
+            width=int(basic.get("width", 16)), text_len=int(getattr(c, "text_len", basic.get("text_len", 16))),
+            text_dim=c.text_dim, seed=args.seed,
             num_samples=int(basic.get("num_samples", 1 << 20))))
         coll = lambda ss: {k: torch.stack([s[k] for s in ss]) for k in ss[0]}   # noqa: E731
     sampler = BaseRandomBatchSampler(len(ds), args.micro_batch_size, ps.get_dp_rank(), ps.get_dp_world_size(), seed=args.seed)

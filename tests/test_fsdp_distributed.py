@@ -125,3 +125,8 @@ def test_rank_leaving_between_steps_is_detected_on_the_host(mode):
            "--master-port", str(port), os.path.join(HERE, "dist_failure_check.py"), mode]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=180, env=dict(os.environ, OMP_NUM_THREADS="1"))
     assert f"detected={mode} ok=True" in r.stdout + r.stderr, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_model_families_sharded_step_matches_single_process_gloo():
+    """Speech LMs, LTX-2, Bagel, reward model, CogVideoX-style DiT, VACE, Wan2.2 with routed experts under ZeRO-3 at world 2."""
+    assert "ok=True" in _run_script(2, "dist_zoo_check.py")

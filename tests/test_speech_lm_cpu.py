@@ -27,11 +27,11 @@ def test_multicodebook_channel_losses_and_masked_pad_code():
     cl = m.last_channel_losses
     assert float(cl[3]) == 0 and torch.allclose(loss, (cl[0] + 2 * cl[1] + 2 * cl[2]) / 7.0, atol=1e-5)
     loss.backward()
-    assert m.emb_ext[2].weight.grad is not None and m.audio_heads[2].grad is None or float(m.audio_heads[2].grad.abs().sum()) == 0
+    assert m.emb_ext.weight.grad is not None and m.heads.extra[2].grad is None and float(m.heads.extra[0].grad.abs().sum()) > 0
     logits = m(dict(input_ids=ids, cu_seqlens=b["cu_seqlens"], max_seqlen=7))
     assert logits[0].shape == (T, 1024) and logits[1].shape == (T, 32)      # pad code (index 32) is not predicted
     names = [n for n, _ in m.fsdp_units()]
-    assert "emb_ext" in names and "backbone.layers.0" in names and "backbone.lm_head" in names
+    assert "emb_ext" in names and "backbone.layers.0" in names and "heads" in names and "backbone.lm_head" not in names
     codes = m.eval().generate_codes(ids[:4], steps=3)
     assert codes.shape == (3, 3) and int(codes.max()) < 32
 
@@ -53,7 +53,7 @@ def test_cosyvoice3_layouts_loss_and_sampling():
     assert batch["cu_seqlens"].tolist() == [0, 9, 17]
     loss = c(batch)
     loss.backward()
-    assert c.speech_embedding.weight.grad is not None and c.llm_decoder.weight.grad is not None
+    assert c.speech_embedding.weight.grad is not None and c.heads.extra[0].grad is not None and c.backbone.lm_head.weight is None
     # label smoothing: equals plain CE at 0 smoothing
     logits, target = torch.randn(6, 11), torch.tensor([1, 2, IGNORE, 4, 5, 0])
     ce = torch.nn.functional.cross_entropy(logits, target, ignore_index=IGNORE)
@@ -76,7 +76,7 @@ def test_qwen3tts_talker_and_code_predictor():
     cfg = Qwen3TTSConfig.tiny()
     m = Qwen3TTSTalker(cfg)
     m.init_weights()
-    for p in m.speaker_encoder.parameters():
+    for p in m.speaker_front.encoder.parameters():
         torch.nn.init.normal_(p, std=0.05)
     G = cfg.num_code_groups
     s1 = m.build_sample([5, 6, 7], torch.randint(0, 60, (4, G)), bos=61, eos=62, pad=63)
@@ -89,9 +89,9 @@ def test_qwen3tts_talker_and_code_predictor():
     loss = m(batch)
     assert torch.isfinite(loss) and float(m.last_sub_talker_loss) > 0
     loss.backward()
-    assert m.code_predictor.heads[0].grad is not None and m.code_predictor.codec_embedding[1].weight.grad is not None
-    assert m.text_projection[0].weight.grad is not None
-    assert all(p.grad is None for p in m.speaker_encoder.parameters())            # speaker embedding is detached
+    assert m.code_predictor.heads.weight.grad is not None and m.code_predictor.codec_embedding.weight.grad is not None
+    assert m.text_front.fc1.weight.grad is not None
+    assert all(p.grad is None for p in m.speaker_front.encoder.parameters()) and m.speaker_front.proj.weight.grad is not None            # speaker embedding is detached
     spk = SpeakerEncoder(20, 32, 16)(torch.randn(3, 25, 20))
     assert spk.shape == (3, 16)
     with torch.no_grad():
@@ -100,7 +100,7 @@ def test_qwen3tts_talker_and_code_predictor():
         codes = m.code_predictor.generate(hid, code0, m.backbone.embed_tokens(code0))
     assert codes.shape == (5, G) and torch.equal(codes[:, 0], code0)
     names = [n for n, _ in m.fsdp_units()]
-    assert "code_predictor.backbone.layers.0" in names and "backbone.layers.1" in names and "speaker_encoder" in names
+    assert "code_predictor.backbone.layers.0" in names and "backbone.layers.1" in names and "speaker_front" in names
 
 
 def test_audio_codec_rvq_and_roundtrip_shapes():

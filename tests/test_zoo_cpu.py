@@ -240,7 +240,7 @@ def test_bagel_mot_routes_tokens_to_their_parameter_set():
     out["loss"].backward()
     l0 = m.layers[0]
     assert l0.und.qkv.weight.grad.abs().sum() > 0 and l0.gen.qkv.weight.grad.abs().sum() > 0
-    assert m.vae2llm.weight.grad is not None and m.latent_pos_embed.grad[[0, 1, 8, 9]].abs().sum() > 0
+    assert m.io.vae2llm.weight.grad is not None and m.io.latent_pos_embed.grad[[0, 1, 8, 9]].abs().sum() > 0
     # text-only batch: the generation parameter set receives no gradient
     m.zero_grad()
     text_only = dict(input_ids=batch["input_ids"][:8], text_rows=torch.arange(8), labels=labels[:8].clone(), position_ids=torch.arange(8),
@@ -257,7 +257,7 @@ def test_reward_model_bradley_terry():
     torch.manual_seed(0)
     rm = RewardModelBT()
     rm.backbone.init_weights()
-    torch.nn.init.normal_(rm.rm_head.weight, std=0.1)
+    torch.nn.init.normal_(rm.value_head.rm_head.weight, std=0.1)
     T = 12
     batch = dict(input_ids=torch.randint(0, 1000, (T,)), position_ids=torch.cat([torch.arange(3), torch.arange(3), torch.arange(4), torch.arange(2)])[None].expand(3, -1),
                  cu_seqlens=torch.tensor([0, 3, 6, 10, 12], dtype=torch.int32), max_seqlen=4)
@@ -265,5 +265,5 @@ def test_reward_model_bradley_terry():
     assert r.shape == (4,)
     loss = rm(batch)
     loss.backward()
-    assert rm.rm_head.weight.grad is not None and 0 <= float(rm.last_accuracy) <= 1
+    assert rm.value_head.rm_head.weight.grad is not None and 0 <= float(rm.last_accuracy) <= 1
     assert "backbone.lm_head" not in [n for n, _ in rm.fsdp_units()]

@@ -6,17 +6,13 @@
 //   warp 1      MMA issuer:   S_j = Q K_j^T  -> TMEM S[j&1]      (issued one tile ahead of the softmax)
 //                             O_j = P_j V_j  -> TMEM O[j&1]      (fresh accumulator per tile; P_j is the A operand
 //                                                                 read from tensor memory)
-//   warps 2-9   two compute warpgroups; thread = (query row, half): warpgroup h owns key columns [64h, 64h+64) of S
-//               and head-dim columns [64h, 64h+64) of O.  Per tile: pull its 64 columns of S, exchange the row
-//               maximum with the other half through a shared-memory atomic max + one named barrier, exp2, write
-//               P_j (bf16 pairs) back over the first 64 columns of S[j&1]; then fold O_{j-1} into its register
-//               accumulator: O_acc = O_acc * 2^(m_old - m_new) + O_j.  Final normalise, bf16 store.
-//               Two warps per scheduler hide each other's TMEM / special-function latency; the exp2 work of a
-//               tile (16384 per 128 x 128) is spread over 256 threads.
+//   warps 2-5   softmax:      thread = query row; pulls its 128-column row of S into registers in one go, writes
+//                             P_j (bf16 pairs) back over the first 64 columns of S[j&1], keeps m / l
+//   warps 6-9   accumulate:   O_acc = O_acc * 2^(m_old - m_new) + O_j in registers (reads O_j from TMEM),
+//                             final normalise, bf16 store
 // TMEM: S double buffer (2 x 128 cols) + O double buffer (2 x 128 cols) = 512 columns.
 // Rescaling lives in registers, so TMEM is never read-modify-written and the tensor core runs QK of tile j+1
-// while the softmax of tile j is in flight.  All mbarrier waits are bounded (tc05::mbar_wait); a thread whose wait
-// gave up keeps taking part in the named barriers so that nobody is left waiting for it.
+// while the softmax of tile j is in flight.  All mbarrier waits are bounded (tc05::mbar_wait).
 #include "tc05.cuh"
 
 namespace {
@@ -42,19 +38,6 @@ struct FmhaParams {
     float scale_log2;   // softmax scale * log2(e)
     int* status;
 };
-
-constexpr int kOrdNegInf = (int)0x807fffff;   // float_to_ordered(-inf)
-
-// Order-preserving map float -> int (so that an integer atomic max is a float max) and back.
-__device__ __forceinline__ int float_to_ordered(float f) {
-    const int i = __float_as_int(f);
-    return i >= 0 ? i : i ^ 0x7fffffff;
-}
-__device__ __forceinline__ float ordered_to_float(int i) { return __int_as_float(i >= 0 ? i : i ^ 0x7fffffff); }
-
-__device__ __forceinline__ void named_barrier_sync(int id, int count) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
 
 __global__ void fmha_plan_kernel(const int* cu_q, int n_seqs, int* tile_seq, int* tile_q0, int* n_tiles, int max_tiles) {
     if (threadIdx.x || blockIdx.x) return;
@@ -92,10 +75,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint64_t* p_full = bars + 15;   // [2]
     uint64_t* o_full = bars + 17;   // [2]
     uint64_t* o_empty = bars + 19;  // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+    uint64_t* fin = bars + 21;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* maxbuf = reinterpret_cast<int*>(aux + 256);            // [3][128] row maxima as ordered ints, rotating
-    float* l_half = reinterpret_cast<float*>(aux + 256);        // [2][128], reuses maxbuf after the key loop
+    float* alpha_ring = reinterpret_cast<float*>(aux + 256);   // [2][128]
+    float* l_final = alpha_ring + 2 * 128;                      // [128]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seq = p.tile_seq[blockIdx.x];
@@ -119,10 +103,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], 256);
+            mbar_init(&p_full[i], 128);
             mbar_init(&o_full[i], 1);
-            mbar_init(&o_empty[i], 256);
+            mbar_init(&o_empty[i], 128);
         }
+        mbar_init(fin, 128);
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tmap(&tmQ);
@@ -133,7 +118,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
-    for (int i = threadIdx.x; i < 3 * 128; i += kThreads) maxbuf[i] = kOrdNegInf;
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
@@ -204,110 +188,114 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             }
             if (!ok) atomicExch(p.status, MM_TIMEOUT_MMA);
         }
-    } else {
-        // ------------------------------------------------------------------------------ compute (warps 2..9)
-        const int half = warp >= 6 ? 1 : 0;              // which 64 key columns of S / 64 head-dim columns of O
-        const int qd = warp & 3;                         // TMEM lane quarter this warp may touch
+    } else if (warp < 6) {
+        // ------------------------------------------------------------------------------ softmax (warps 2..5)
+        const int qd = warp & 3;
         const int row = qd * 32 + lane;
         const int qi = q0 + row;                         // query index inside its sequence
-        const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
-        float m = -INFINITY, l = 0.f, alpha_pending = 0.f;
-        float acc[64];
-#pragma unroll
-        for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+        float m = -INFINITY, l = 0.f;
         bool ok = true;
-        auto fold = [&](int jj) {                        // O_acc = O_acc * alpha_jj + O_jj for this thread's 64 columns
-            const int sb = jj & 1;
-            if (ok && !mbar_wait(&o_full[sb], (jj >> 1) & 1, abort_flag)) ok = false;
-            if (!ok) return;
-            fence_after_sync();
-            uint32_t o[64];
-            const uint32_t t_o = tO + sb * 128 + half * 64 + lane_off;
-            tmem_ld_32x32(t_o, o);
-            tmem_ld_32x32(t_o + 32, o + 32);
-            tmem_wait_ld();
-            fence_before_sync();
-            mbar_arrive(&o_empty[sb]);
-#pragma unroll
-            for (int i = 0; i < 64; ++i) acc[i] = acc[i] * alpha_pending + __uint_as_float(o[i]);
-        };
         for (int j = 0; j < n_kv; ++j) {
             const int st = j & 1;
             const uint32_t ph = (j >> 1) & 1;
-            if (ok && !mbar_wait(&s_full[st], ph, abort_flag)) ok = false;
-            uint32_t r[64];
-            const uint32_t t_s = tS + st * 128 + lane_off;
-            const int kbase = j * BKV + half * 64;
-            if (ok) {
-                fence_after_sync();
-                tmem_ld_32x32(t_s + half * 64, r);
-                tmem_ld_32x32(t_s + half * 64 + 32, r + 32);
-                tmem_wait_ld();
-                const bool need_mask = (kbase + 64 > k_len) || (p.causal && kbase + 63 > q0 + diag);
-                const int limit = p.causal ? min(k_len - 1, qi + diag) : k_len - 1;   // last visible key index
-                float mx = -INFINITY;
-                if (need_mask) {
+            if (!mbar_wait(&s_full[st], ph, abort_flag)) { ok = false; break; }
+            fence_after_sync();
+            const uint32_t t_row = tS + st * 128 + ((uint32_t)(qd * 32) << 16);
+            const int kbase = j * BKV;
+            const bool need_mask = (kbase + BKV > k_len) || (p.causal && kbase + BKV - 1 > q0 + diag);
+            const int limit = p.causal ? min(k_len - 1, qi + diag) : k_len - 1;   // last visible key index
+            // one TMEM round trip: the whole 128-column row of S lands in registers, then S[st] is released
+            uint32_t r[128];
+            tmem_ld_32x32(t_row, r);
+            tmem_ld_32x32(t_row + 32, r + 32);
+            tmem_ld_32x32(t_row + 64, r + 64);
+            tmem_ld_32x32(t_row + 96, r + 96);
+            tmem_wait_ld();
+            float mx = -INFINITY;
+            if (need_mask) {
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        float sv = __uint_as_float(r[i]) * p.scale_log2;
-                        if (kbase + i > limit) sv = -INFINITY;
-                        r[i] = __float_as_uint(sv);
-                        mx = fmaxf(mx, sv);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        const float sv = __uint_as_float(r[i]) * p.scale_log2;
-                        r[i] = __float_as_uint(sv);
-                        mx = fmaxf(mx, sv);
-                    }
+                for (int i = 0; i < 128; ++i) {
+                    float s = __uint_as_float(r[i]) * p.scale_log2;
+                    if (kbase + i > limit) s = -INFINITY;
+                    r[i] = __float_as_uint(s);
+                    mx = fmaxf(mx, s);
                 }
-                atomicMax(&maxbuf[(j % 3) * 128 + row], float_to_ordered(mx));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 128; ++i) {
+                    const float s = __uint_as_float(r[i]) * p.scale_log2;
+                    r[i] = __float_as_uint(s);
+                    mx = fmaxf(mx, s);
+                }
             }
-            // Both halves of every row have read their S columns and published their maximum.  After this barrier
-            // the P columns may overwrite S, and the slot of tile j - 1 (next used by tile j + 2) may be reset.
-            named_barrier_sync(1, 256);
-            if (half == 0) maxbuf[((j + 2) % 3) * 128 + row] = kOrdNegInf;
-            if (ok) {
-                const float mx_all = ordered_to_float(maxbuf[(j % 3) * 128 + row]);
-                const float m_new = fmaxf(m, mx_all);
-                const float m_use = m_new == -INFINITY ? 0.f : m_new;
-                const float alpha = exp2f(m - m_use);        // m = -inf on the first tile -> 0
-                m = m_new;
-                float sum = 0.f;
+            const float m_new = fmaxf(m, mx);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = exp2f(m - m_use);        // m = -inf on the first tile -> 0
+            // The accumulate warps must be done with tile j - 2 before its alpha slot is reused and before
+            // p_full[st], which they wait on too, can complete again.
+            if (j >= 2 && !mbar_wait(&o_empty[st], ((j - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
+            alpha_ring[st * 128 + row] = alpha;
+            m = m_new;
+            float sum = 0.f;
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    const float e = exp2f(__uint_as_float(r[i]) - m_use);
-                    sum += e;
-                    r[i] = __float_as_uint(e);
-                }
-                l = l * alpha + sum;
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    bf162 t = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                    r[i] = *reinterpret_cast<uint32_t*>(&t);
-                }
-                // P: bf16 pairs over the first 64 columns of S[st]; this half's 64 keys are columns [32 half, 32 half + 32)
-                tmem_st_32x32(t_s + half * 32, r);
-                tmem_wait_st();
-                fence_before_sync();
-                mbar_arrive(&p_full[st]);
-                if (j > 0) fold(j - 1);                      // uses alpha of tile j - 1
-                alpha_pending = alpha;
+            for (int i = 0; i < 128; ++i) {
+                const float e = exp2f(__uint_as_float(r[i]) - m_use);
+                sum += e;
+                r[i] = __float_as_uint(e);
             }
+            l = l * alpha + sum;
+            // P goes back into tensor memory as bf16 pairs over the first 64 columns of the S buffer just read; the
+            // PV product takes it from there as its A operand.
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+                bf162 t = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                r[i] = *reinterpret_cast<uint32_t*>(&t);
+            }
+            tmem_st_32x32(t_row, r);
+            tmem_st_32x32(t_row + 32, r + 32);
+            tmem_wait_st();
+            fence_before_sync();
+            mbar_arrive(&p_full[st]);
         }
-        if (n_kv > 0) fold(n_kv - 1);
-        named_barrier_sync(1, 256);                          // maxbuf is free: reuse it for the two partial row sums
-        l_half[half * 128 + row] = l;
-        named_barrier_sync(1, 256);
-        if (ok && qi < q_len && n_kv > 0) {
-            const float lsum = l_half[row] + l_half[128 + row];
-            const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-            if (half == 0)
-                p.lse[(size_t)head * p.T + q_begin + qi] = (m == -INFINITY) ? -INFINITY : m * 0.6931471805599453f + logf(lsum);
-            bf16* dst = p.o + ((size_t)(q_begin + qi) * p.Nq + head) * HD + half * 64;
+        l_final[row] = l;
+        if (ok && qi < q_len && n_kv > 0)
+            p.lse[(size_t)head * p.T + q_begin + qi] = (m == -INFINITY) ? -INFINITY : m * 0.6931471805599453f + logf(l);
+        mbar_arrive(fin);
+        if (!ok && lane == 0) atomicExch(p.status, MM_TIMEOUT_EPI);
+    } else {
+        // ------------------------------------------------------------------------------ accumulate (warps 6..9)
+        const int qd = warp & 3;
+        const int row = qd * 32 + lane;
+        const int qi = q0 + row;
+        float acc[HD];
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
+        for (int i = 0; i < HD; ++i) acc[i] = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_kv; ++j) {
+            const int st = j & 1;
+            const uint32_t ph = (j >> 1) & 1;
+            if (!mbar_wait(&p_full[st], ph, abort_flag) || !mbar_wait(&o_full[st], ph, abort_flag)) { ok = false; break; }
+            fence_after_sync();
+            const float alpha = alpha_ring[st * 128 + row];
+            const uint32_t t_row = tO + st * 128 + ((uint32_t)(qd * 32) << 16);
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t r[64];
+                tmem_ld_32x32(t_row + c * 64, r);
+                tmem_ld_32x32(t_row + c * 64 + 32, r + 32);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 64; ++i) acc[c * 64 + i] = acc[c * 64 + i] * alpha + __uint_as_float(r[i]);
+            }
+            fence_before_sync();
+            mbar_arrive(&o_empty[st]);
+        }
+        if (ok && mbar_wait(fin, 0, abort_flag) && qi < q_len && n_kv > 0) {
+            const float lsum = l_final[row];
+            const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+            bf16* dst = p.o + ((size_t)(q_begin + qi) * p.Nq + head) * HD;
+#pragma unroll
+            for (int g = 0; g < HD / 8; ++g) {
                 float f[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) f[i] = acc[g * 8 + i] * inv;
@@ -327,7 +315,18 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
 }
 
+#include "fmha_fwd_split.cuh"
+
+int g_fwd_variant = 0;   // 0: default kernel, 1: split-softmax kernel (fmha_fwd_split.cuh)
+
 }  // namespace
+
+// Selects the forward kernel for later calls (0 = default, 1 = split softmax).  Returns the previous value.
+MM_API int mm_fmha_set_fwd_variant(int v) {
+    const int prev = g_fwd_variant;
+    g_fwd_variant = v;
+    return prev;
+}
 
 // Scratch needed by the planner: 2 * max_tiles + 1 ints, max_tiles = T / 128 + n_seqs.
 MM_API int mm_fmha_max_tiles(int T, int n_seqs) { return T / BQ + n_seqs + 1; }
@@ -352,12 +351,17 @@ MM_API int mm_fmha_fwd(const void* q, const void* k, const void* v, void* o, flo
     static bool done = false;
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(fmha_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(fmha_fwd_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
     FmhaParams p{cu_q, cu_k, tile_seq, tile_q0, n_tiles, (bf16*)o, lse, T, Nq, Nkv, causal,
                  scale * 1.4426950408889634f, status};
     dim3 grid(max_tiles, Nq);
-    fmha_fwd_kernel<<<grid, kThreads, kSmem, st>>>(tQ, tK, tV, p);
+    if (g_fwd_variant == 1)
+        fmha_fwd_split_kernel<<<grid, kThreads, kSmem, st>>>(tQ, tK, tV, p);
+    else
+        fmha_fwd_kernel<<<grid, kThreads, kSmem, st>>>(tQ, tK, tV, p);
     return (int)cudaGetLastError();
 }

@@ -1,0 +1,280 @@
+// Forward flash-attention kernel, "split" variant: included by fmha_fwd.cu inside its namespace (shares FmhaParams, the
+// tile constants and the planner with the default kernel).
+//
+// Same producer / MMA-issuer warps and TMEM layout as the default kernel, but both compute warpgroups run the softmax:
+//   warps 2-9   thread = (query row, half): warpgroup h owns key columns [64h, 64h+64) of S and head-dim columns
+//               [64h, 64h+64) of O.  Per tile: pull its 64 columns of S, exchange the row maximum with the other half
+//               through a shared-memory atomic max + one named barrier, exp2, write P_j (bf16 pairs) back over the
+//               first 64 columns of S[j&1]; then fold O_{j-1} into its register accumulator.
+// Two warps per scheduler hide each other's TMEM / special-function latency, and the exp2 work of a tile (16384 per
+// 128 x 128) is spread over 256 threads.  A thread whose bounded wait gave up keeps taking part in the named barriers,
+// so nobody is left waiting for it.
+
+constexpr int kOrdNegInf = (int)0x807fffff;   // float_to_ordered(-inf)
+
+// Order-preserving map float -> int (so that an integer atomic max is a float max) and back.
+__device__ __forceinline__ int float_to_ordered(float f) {
+    const int i = __float_as_int(f);
+    return i >= 0 ? i : i ^ 0x7fffffff;
+}
+__device__ __forceinline__ float ordered_to_float(int i) { return __int_as_float(i >= 0 ? i : i ^ 0x7fffffff); }
+
+__device__ __forceinline__ void named_barrier_sync(int id, int count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, FmhaParams p) {
+    if ((int)blockIdx.x >= *p.n_tiles) return;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sQ = smem;
+    uint8_t* sK = sQ + kTileBytes;
+    uint8_t* sV = sK + kRing * kTileBytes;
+    uint8_t* aux = sV + kRing * kTileBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aux);
+    uint64_t* q_full = bars + 0;
+    uint64_t* k_full = bars + 1;    // [kRing]
+    uint64_t* k_empty = bars + 4;   // [kRing]
+    uint64_t* v_full = bars + 7;    // [kRing]
+    uint64_t* v_empty = bars + 10;  // [kRing]
+    uint64_t* s_full = bars + 13;   // [2]
+    uint64_t* p_full = bars + 15;   // [2]
+    uint64_t* o_full = bars + 17;   // [2]
+    uint64_t* o_empty = bars + 19;  // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* maxbuf = reinterpret_cast<int*>(aux + 256);            // [3][128] row maxima as ordered ints, rotating
+    float* l_half = reinterpret_cast<float*>(aux + 256);        // [2][128], reuses maxbuf after the key loop
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = p.tile_seq[blockIdx.x];
+    const int q0 = p.tile_q0[blockIdx.x];
+    const int head = blockIdx.y;
+    const int kv_head = head / (p.Nq / p.Nkv);
+    const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
+    const int k_begin = p.cu_k[seq], k_len = p.cu_k[seq + 1] - k_begin;
+    const int diag = k_len - q_len;   // causal: key j visible to query i iff j <= i + diag
+    int kv_end = k_len;
+    if (p.causal) kv_end = min(k_len, q0 + BQ + diag);
+    const int n_kv = (kv_end + BKV - 1) / BKV;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < kRing; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&k_empty[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&v_empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 256);
+            mbar_init(&o_full[i], 1);
+            mbar_init(&o_empty[i], 256);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tmQ);
+        prefetch_tmap(&tmK);
+        prefetch_tmap(&tmV);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    for (int i = threadIdx.x; i < 3 * 128; i += kThreads) maxbuf[i] = kOrdNegInf;
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tS = tmem_base, tO = tmem_base + 256;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------------------ TMA producer
+        if (lane == 0 && n_kv > 0) {
+            mbar_expect_tx(q_full, kTileBytes);
+            tma_load_3d(sQ, &tmQ, q_full, 0, head, q_begin + q0);
+            tma_load_3d(sQ + kAtomBytes, &tmQ, q_full, 64, head, q_begin + q0);
+            for (int j = 0; j < n_kv; ++j) {
+                const int st = j % kRing;
+                const uint32_t ph = (j / kRing) & 1;
+                const int row = k_begin + j * BKV;
+                if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag)) { atomicExch(p.status, MM_TIMEOUT_TMA); break; }
+                mbar_expect_tx(&k_full[st], kTileBytes);
+                tma_load_3d(sK + st * kTileBytes, &tmK, &k_full[st], 0, kv_head, row);
+                tma_load_3d(sK + st * kTileBytes + kAtomBytes, &tmK, &k_full[st], 64, kv_head, row);
+                if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag)) { atomicExch(p.status, MM_TIMEOUT_TMA); break; }
+                mbar_expect_tx(&v_full[st], kTileBytes);
+                tma_load_3d(sV + st * kTileBytes, &tmV, &v_full[st], 0, kv_head, row);
+                tma_load_3d(sV + st * kTileBytes + kAtomBytes, &tmV, &v_full[st], 64, kv_head, row);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && n_kv > 0) {
+            constexpr uint32_t idesc_qk = idesc_bf16(BQ, BKV, 0, 0);
+            constexpr uint32_t idesc_pv = idesc_bf16(BQ, HD, 0, 1);
+            bool ok = mbar_wait(q_full, 0, abort_flag);
+            auto issue_qk = [&](int j) -> bool {
+                // S[j & 1] was last read by the PV product of tile j - 2 (as P), which this thread issued earlier:
+                // the tensor pipe runs its instructions in order, so no barrier guards the overwrite.
+                const int st = j & 1, rs = j % kRing;
+                if (!mbar_wait(&k_full[rs], (j / kRing) & 1, abort_flag)) return false;
+                fence_after_sync();
+                const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + rs * kTileBytes);
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
+                    mma_ss(tS + st * 128, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024),
+                           idesc_qk, k ? 1u : 0u);
+                }
+                mma_commit(&s_full[st]);
+                mma_commit(&k_empty[rs]);
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < n_kv && ok; ++j) {
+                if (j + 1 < n_kv) ok = issue_qk(j + 1);
+                if (!ok) break;
+                const int st = j & 1, rs = j % kRing;
+                const uint32_t ph = (j >> 1) & 1;
+                if (!mbar_wait(&o_empty[st], ph ^ 1, abort_flag) || !mbar_wait(&v_full[rs], (j / kRing) & 1, abort_flag) ||
+                    !mbar_wait(&p_full[st], ph, abort_flag)) { ok = false; break; }
+                fence_after_sync();
+                // P comes from tensor memory: bf16 pairs in the first 64 columns of S[st], 8 columns per K = 16 step
+                const uint32_t va = smem_u32(sV + rs * kTileBytes);
+#pragma unroll
+                for (int k = 0; k < BKV / 16; ++k) {
+                    const uint64_t db = smem_desc_sw128(va + k * 2048, kAtomBytes, 1024);
+                    mma_ts(tO + st * 128, tS + st * 128 + k * 8, db, idesc_pv, k ? 1u : 0u);
+                }
+                mma_commit(&o_full[st]);
+                mma_commit(&v_empty[rs]);
+            }
+            if (!ok) atomicExch(p.status, MM_TIMEOUT_MMA);
+        }
+    } else {
+        // ------------------------------------------------------------------------------ compute (warps 2..9)
+        const int half = warp >= 6 ? 1 : 0;              // which 64 key columns of S / 64 head-dim columns of O
+        const int qd = warp & 3;                         // TMEM lane quarter this warp may touch
+        const int row = qd * 32 + lane;
+        const int qi = q0 + row;                         // query index inside its sequence
+        const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
+        float m = -INFINITY, l = 0.f, alpha_pending = 0.f;
+        float acc[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+        bool ok = true;
+        auto fold = [&](int jj) {                        // O_acc = O_acc * alpha_jj + O_jj for this thread's 64 columns
+            const int sb = jj & 1;
+            if (ok && !mbar_wait(&o_full[sb], (jj >> 1) & 1, abort_flag)) ok = false;
+            if (!ok) return;
+            fence_after_sync();
+            uint32_t o[64];
+            const uint32_t t_o = tO + sb * 128 + half * 64 + lane_off;
+            tmem_ld_32x32(t_o, o);
+            tmem_ld_32x32(t_o + 32, o + 32);
+            tmem_wait_ld();
+            fence_before_sync();
+            mbar_arrive(&o_empty[sb]);
+#pragma unroll
+            for (int i = 0; i < 64; ++i) acc[i] = acc[i] * alpha_pending + __uint_as_float(o[i]);
+        };
+        for (int j = 0; j < n_kv; ++j) {
+            const int st = j & 1;
+            const uint32_t ph = (j >> 1) & 1;
+            if (ok && !mbar_wait(&s_full[st], ph, abort_flag)) ok = false;
+            uint32_t r[64];
+            const uint32_t t_s = tS + st * 128 + lane_off;
+            const int kbase = j * BKV + half * 64;
+            if (ok) {
+                fence_after_sync();
+                tmem_ld_32x32(t_s + half * 64, r);
+                tmem_ld_32x32(t_s + half * 64 + 32, r + 32);
+                tmem_wait_ld();
+                const bool need_mask = (kbase + 64 > k_len) || (p.causal && kbase + 63 > q0 + diag);
+                const int limit = p.causal ? min(k_len - 1, qi + diag) : k_len - 1;   // last visible key index
+                float mx = -INFINITY;
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        float sv = __uint_as_float(r[i]) * p.scale_log2;
+                        if (kbase + i > limit) sv = -INFINITY;
+                        r[i] = __float_as_uint(sv);
+                        mx = fmaxf(mx, sv);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const float sv = __uint_as_float(r[i]) * p.scale_log2;
+                        r[i] = __float_as_uint(sv);
+                        mx = fmaxf(mx, sv);
+                    }
+                }
+                atomicMax(&maxbuf[(j % 3) * 128 + row], float_to_ordered(mx));
+            }
+            // Both halves of every row have read their S columns and published their maximum.  After this barrier
+            // the P columns may overwrite S, and the slot of tile j - 1 (next used by tile j + 2) may be reset.
+            named_barrier_sync(1, 256);
+            if (half == 0) maxbuf[((j + 2) % 3) * 128 + row] = kOrdNegInf;
+            if (ok) {
+                const float mx_all = ordered_to_float(maxbuf[(j % 3) * 128 + row]);
+                const float m_new = fmaxf(m, mx_all);
+                const float m_use = m_new == -INFINITY ? 0.f : m_new;
+                const float alpha = exp2f(m - m_use);        // m = -inf on the first tile -> 0
+                m = m_new;
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    const float e = exp2f(__uint_as_float(r[i]) - m_use);
+                    sum += e;
+                    r[i] = __float_as_uint(e);
+                }
+                l = l * alpha + sum;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    bf162 t = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                    r[i] = *reinterpret_cast<uint32_t*>(&t);
+                }
+                // P: bf16 pairs over the first 64 columns of S[st]; this half's 64 keys are columns [32 half, 32 half + 32)
+                tmem_st_32x32(t_s + half * 32, r);
+                tmem_wait_st();
+                fence_before_sync();
+                mbar_arrive(&p_full[st]);
+                if (j > 0) fold(j - 1);                      // uses alpha of tile j - 1
+                alpha_pending = alpha;
+            }
+        }
+        if (n_kv > 0) fold(n_kv - 1);
+        named_barrier_sync(1, 256);                          // maxbuf is free: reuse it for the two partial row sums
+        l_half[half * 128 + row] = l;
+        named_barrier_sync(1, 256);
+        if (ok && qi < q_len && n_kv > 0) {
+            const float lsum = l_half[row] + l_half[128 + row];
+            const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+            if (half == 0)
+                p.lse[(size_t)head * p.T + q_begin + qi] = (m == -INFINITY) ? -INFINITY : m * 0.6931471805599453f + logf(lsum);
+            bf16* dst = p.o + ((size_t)(q_begin + qi) * p.Nq + head) * HD + half * 64;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                float f[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = acc[g * 8 + i] * inv;
+                reinterpret_cast<Vec8*>(dst)[g] = pack8(f);
+            }
+        }
+        if (!ok && lane == 0) atomicExch(p.status, MM_TIMEOUT_EPI);
+    }
+
+    if (*abort_flag)
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        fence_after_sync();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+

@@ -17,6 +17,8 @@ from . import build as _build
 
 _LIB = None
 _STATUS: dict = {}
+# forward attention kernel: 0 = default, 1 = split-softmax variant (csrc/fmha_fwd_split.cuh)
+FMHA_FWD_VARIANT = int(os.environ.get("MM_B200_FMHA_FWD_VARIANT", "0"))
 LAUNCHES = 0  # native kernel launches issued through this module (bench reports it)
 
 _p, _i, _ll, _f = C.c_void_p, C.c_int, C.c_longlong, C.c_float
@@ -30,6 +32,8 @@ def lib():
             raise RuntimeError(f"native op library not built: {path} (run python -m mindspeed_mm_b200.ops.build)")
         _LIB = C.CDLL(path)
         _declare(_LIB)
+        if FMHA_FWD_VARIANT:
+            _LIB.mm_fmha_set_fwd_variant(FMHA_FWD_VARIANT)
     return _LIB
 
 
@@ -50,6 +54,7 @@ def _declare(L):
         "mm_gemm_bf16": [_p, _p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _p, _p],
         "mm_ce_fwd_bwd": [_p, _ll, _p, _p, _i, _i, _i, _p],
         "mm_fmha_max_tiles": [_i, _i],
+        "mm_fmha_set_fwd_variant": [_i],
         "mm_fmha_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _f, _p, _p],
         "mm_fmha_bwd_max_tiles": [_i, _i],
         "mm_fmha_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _f,

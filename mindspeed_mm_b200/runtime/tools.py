@@ -180,3 +180,26 @@ class PeerHeartbeat:
             elif now - float(v.split(":")[1]) > self.timeout_s:
                 bad.append((r, f"no heartbeat for {now - float(v.split(':')[1]):.1f}s"))
         return bad
+
+
+def estimate_training_memory(n_params: float, shard_world: int = 1, tp: int = 1, param_bytes: int = 2, grad_bytes: int = 4,
+                             optimizer_bytes: int = 12, activation_bytes_per_layer: float = 0.0, n_layers: int = 0,
+                             recompute_layers: int = 0, layer_input_bytes: float = 0.0, largest_unit_params: float = 0.0,
+                             workspace_gb: float = 2.0, reserve_gb: float = 2.0) -> dict:
+    """Back-of-envelope memory model of one rank, in GiB (the reference ships the same kind of estimate as a script:
+    mindspeed_mm/tools/mem_analysis.py).
+
+    static  = sharded bf16 parameters + sharded fp32 master / Adam moments (``optimizer_bytes`` per parameter) + the
+              gradient shard; ZeRO-3 additionally keeps two gathered units and one full-size gradient buffer of the
+              largest unit alive (prefetch + compute).
+    active  = saved activations of the layers that keep their graph + only the layer inputs of the recomputed ones.
+    """
+    gib = float(1 << 30)
+    shard = n_params / max(tp, 1) / max(shard_world, 1)
+    static = shard * (param_bytes + grad_bytes + optimizer_bytes) / gib
+    gathered = largest_unit_params / max(tp, 1) * (2 * param_bytes + grad_bytes) / gib if shard_world > 1 else 0.0
+    kept = max(n_layers - recompute_layers, 0)
+    active = (kept * activation_bytes_per_layer + recompute_layers * layer_input_bytes) / gib
+    total = static + gathered + active + workspace_gb + reserve_gb
+    return dict(static_gb=static, gathered_units_gb=gathered, activation_gb=active, workspace_gb=workspace_gb,
+                reserve_gb=reserve_gb, total_gb=total)

@@ -101,3 +101,13 @@ def test_flops_accounting_7b():
     # ~2 * 7.6e9 params * 8192 tokens plus attention and the ViT
     assert 1.2e14 < f < 1.7e14
     assert abs(mfu(training_flops(f), 0.6, 1, 1648.3) - training_flops(f) / 0.6 / 1648.3e12) < 1e-12
+
+
+def test_memory_estimate_breakdown():
+    from mindspeed_mm_b200.runtime.tools import estimate_training_memory
+    one = estimate_training_memory(7.6e9, shard_world=1, n_layers=28, activation_bytes_per_layer=1.5e9, workspace_gb=0, reserve_gb=0)
+    assert abs(one["static_gb"] - 7.6e9 * 18 / 2 ** 30) < 1e-6 and one["gathered_units_gb"] == 0
+    eight = estimate_training_memory(7.6e9, shard_world=8, n_layers=28, activation_bytes_per_layer=1.5e9, recompute_layers=28,
+                                     layer_input_bytes=8192 * 3584 * 2, largest_unit_params=5.4e8, workspace_gb=0, reserve_gb=0)
+    assert abs(eight["static_gb"] * 8 - one["static_gb"]) < 1e-6 and eight["gathered_units_gb"] > 0
+    assert eight["activation_gb"] < one["activation_gb"] / 10 and eight["total_gb"] < 40

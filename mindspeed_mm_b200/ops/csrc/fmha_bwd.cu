@@ -274,13 +274,20 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             mbar_arrive(dp_empty);
             const int kbase = j * 128 + half * 64;
             const int limit = !row_ok ? -1 : (p.causal ? min(k_len - 1, qi + diag) : k_len - 1);
+            // packed fp32 math (two columns per instruction): dS = exp2(S * scale - lse) * (dP - delta)
+            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-dlt, -dlt);
+            const bool tile_masked = kbase + 63 > limit;         // some column of this row is hidden (or the row is padding)
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                const float pr = exp2f(__uint_as_float(r[i]) * p.scale_log2 - lse2);
-                r[i] = __float_as_uint(kbase + i > limit ? 0.f : pr * (__uint_as_float(d[i]) - dlt));
+            for (int i = 0; i < 32; ++i) {
+                const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), sc2, nl2);
+                const float2 g = __fadd2_rn(make_float2(__uint_as_float(d[2 * i]), __uint_as_float(d[2 * i + 1])), nd2);
+                float2 ds = __fmul2_rn(make_float2(exp2f(x.x), exp2f(x.y)), g);
+                if (tile_masked) {
+                    if (kbase + 2 * i > limit) ds.x = 0.f;
+                    if (kbase + 2 * i + 1 > limit) ds.y = 0.f;
+                }
+                d[i] = pack2(ds.x, ds.y);
             }
-#pragma unroll
-            for (int i = 0; i < 32; ++i) d[i] = pack2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
             tmem_st_32x32(t_row, d);             // over the first 32 of the 64 fp32 columns this thread just read
             tmem_wait_st();
             fence_before_sync();
@@ -571,6 +578,7 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 }
 
 #include "fmha_bwd_pp.cuh"
+#include "fmha_bwd_dkv128.cuh"
 
 }  // namespace
 
@@ -642,6 +650,12 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
         if (cudaFuncSetAttribute(fmha_bwd_dkv_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkvTs) != cudaSuccess)
             return -3;
         fmha_bwd_dkv_ts_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkvTs, st>>>(tQ64, tK, tV, tdO64, pk);
+        return (int)cudaGetLastError();
+    }
+    if (variant == 5) {      // dK/dV over 128-row query steps: all four products at N = 128
+        if (cudaFuncSetAttribute(fmha_bwd_dkv128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkv128) != cudaSuccess)
+            return -3;
+        fmha_bwd_dkv128_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkv128, st>>>(tQ, tK, tV, tdO, pk);
         return (int)cudaGetLastError();
     }
     fmha_bwd_dkv_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkv, st>>>(tQ64, tK, tV, tdO64, pk);

@@ -19,6 +19,12 @@ __device__ __forceinline__ int float_to_ordered(float f) {
 }
 __device__ __forceinline__ float ordered_to_float(int i) { return __int_as_float(i >= 0 ? i : i ^ 0x7fffffff); }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 __device__ __forceinline__ void named_barrier_sync(int id, int count) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
@@ -179,8 +185,14 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tmem_wait_ld();
             fence_before_sync();
             mbar_arrive(&o_empty[sb]);
+            const float2 a2 = make_float2(alpha_pending, alpha_pending);
 #pragma unroll
-            for (int i = 0; i < 64; ++i) acc[i] = acc[i] * alpha_pending + __uint_as_float(o[i]);
+            for (int i = 0; i < 32; ++i) {                // packed fp32: one instruction per two columns
+                const float2 v = __ffma2_rn(make_float2(acc[2 * i], acc[2 * i + 1]), a2,
+                                            make_float2(__uint_as_float(o[2 * i]), __uint_as_float(o[2 * i + 1])));
+                acc[2 * i] = v.x;
+                acc[2 * i + 1] = v.y;
+            }
         };
         for (int j = 0; j < n_kv; ++j) {
             const int st = j & 1;
@@ -196,23 +208,22 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 tmem_wait_ld();
                 const bool need_mask = (kbase + 64 > k_len) || (p.causal && kbase + 63 > q0 + diag);
                 const int limit = p.causal ? min(k_len - 1, qi + diag) : k_len - 1;   // last visible key index
-                float mx = -INFINITY;
+                // the maximum is taken over the raw scores (the softmax scale is positive); scale and shift are folded
+                // into one fused multiply-add in front of the exponential
                 if (need_mask) {
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        float sv = __uint_as_float(r[i]) * p.scale_log2;
-                        if (kbase + i > limit) sv = -INFINITY;
-                        r[i] = __float_as_uint(sv);
-                        mx = fmaxf(mx, sv);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        const float sv = __uint_as_float(r[i]) * p.scale_log2;
-                        r[i] = __float_as_uint(sv);
-                        mx = fmaxf(mx, sv);
-                    }
+                    for (int i = 0; i < 64; ++i)
+                        if (kbase + i > limit) r[i] = 0xff800000u;       // -inf
                 }
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 64; i += 8) {         // four independent chains of three-input maxima
+                    mx0 = max3(mx0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                    mx1 = max3(mx1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                    mx2 = max3(mx2, __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+                    mx3 = max3(mx3, __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+                }
+                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
                 atomicMax(&maxbuf[(j % 3) * 128 + row], float_to_ordered(mx));
             }
             // Both halves of every row have read their S columns and published their maximum.  After this barrier
@@ -225,19 +236,21 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const float m_use = m_new == -INFINITY ? 0.f : m_new;
                 const float alpha = exp2f(m - m_use);        // m = -inf on the first tile -> 0
                 m = m_new;
-                float sum = 0.f;
+                const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), ng2 = make_float2(-m_use, -m_use);
+                float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    const float e = exp2f(__uint_as_float(r[i]) - m_use);
-                    sum += e;
-                    r[i] = __float_as_uint(e);
+                for (int i = 0; i < 32; i += 2) {         // two packed chains: exp2(s * scale - m), running sums, bf16 pairs
+                    const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), sc2, ng2);
+                    const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(r[2 * i + 2]), __uint_as_float(r[2 * i + 3])), sc2, ng2);
+                    const float2 e0 = make_float2(exp2f(x0.x), exp2f(x0.y));
+                    const float2 e1 = make_float2(exp2f(x1.x), exp2f(x1.y));
+                    sum_a = __fadd2_rn(sum_a, e0);
+                    sum_b = __fadd2_rn(sum_b, e1);
+                    bf162 t0 = __floats2bfloat162_rn(e0.x, e0.y), t1 = __floats2bfloat162_rn(e1.x, e1.y);
+                    r[i] = *reinterpret_cast<uint32_t*>(&t0);
+                    r[i + 1] = *reinterpret_cast<uint32_t*>(&t1);
                 }
-                l = l * alpha + sum;
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    bf162 t = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                    r[i] = *reinterpret_cast<uint32_t*>(&t);
-                }
+                l = l * alpha + ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
                 // P: bf16 pairs over the first 64 columns of S[st]; this half's 64 keys are columns [32 half, 32 half + 32)
                 tmem_st_32x32(t_s + half * 32, r);
                 tmem_wait_st();

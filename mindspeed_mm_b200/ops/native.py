@@ -17,8 +17,8 @@ from . import build as _build
 
 _LIB = None
 _STATUS: dict = {}
-# forward attention kernel: 0 = default, 1 = split-softmax variant (csrc/fmha_fwd_split.cuh)
-FMHA_FWD_VARIANT = int(os.environ.get("MM_B200_FMHA_FWD_VARIANT", "0"))
+# forward attention kernel: 1 = split-softmax kernel (csrc/fmha_fwd_split.cuh, default), 0 = one softmax warpgroup
+FMHA_FWD_VARIANT = int(os.environ.get("MM_B200_FMHA_FWD_VARIANT", "1"))
 LAUNCHES = 0  # native kernel launches issued through this module (bench reports it)
 
 _p, _i, _ll, _f = C.c_void_p, C.c_int, C.c_longlong, C.c_float
@@ -32,8 +32,7 @@ def lib():
             raise RuntimeError(f"native op library not built: {path} (run python -m mindspeed_mm_b200.ops.build)")
         _LIB = C.CDLL(path)
         _declare(_LIB)
-        if FMHA_FWD_VARIANT:
-            _LIB.mm_fmha_set_fwd_variant(FMHA_FWD_VARIANT)
+        _LIB.mm_fmha_set_fwd_variant(FMHA_FWD_VARIANT)
     return _LIB
 
 
@@ -474,7 +473,9 @@ def fmha_forward(q, k, v, cu_q, cu_k, causal, scale):
 
 
 # 0: both warpgroups share a 128-wide tile (faster as measured); 1: ping-pong schedule over 64-wide tiles
-FMHA_BWD_VARIANT = int(os.environ.get("MM_B200_FMHA_BWD_VARIANT", "0"))
+# backward kernels: 5 = dQ kernel + dK/dV kernel over 128-row query steps (default); 0 = dK/dV over 64-row steps;
+# 1-4 = the ping-pong / all-TS experiments kept for reference
+FMHA_BWD_VARIANT = int(os.environ.get("MM_B200_FMHA_BWD_VARIANT", "5"))
 FMHA_BWD = os.environ.get("MM_B200_FMHA_BWD", "native")     # "native" (tcgen05 kernels) or "flash" (flash-attn library)
 
 

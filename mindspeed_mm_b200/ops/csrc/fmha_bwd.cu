@@ -579,6 +579,7 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
 #include "fmha_bwd_pp.cuh"
 #include "fmha_bwd_dkv128.cuh"
+#include "fmha_bwd_dq128ts.cuh"
 
 }  // namespace
 
@@ -643,6 +644,10 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
         if (cudaFuncSetAttribute(fmha_bwd_dq_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDqTs) != cudaSuccess)
             return -3;
         fmha_bwd_dq_ts_kernel<<<dim3(mq, Nq), 320, kSmemDqTs, st>>>(tQ, tK64, tV64, tdO, p);
+    } else if (variant == 6) {      // dQ with Q / dO resident in tensor memory, 128-key steps, deeper K / V rings
+        if (cudaFuncSetAttribute(fmha_bwd_dq128ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDq6) != cudaSuccess)
+            return -3;
+        fmha_bwd_dq128ts_kernel<<<dim3(mq, Nq), 320, kSmemDq6, st>>>(tQ, tK, tV, tdO, p);
     } else {
         fmha_bwd_dq_kernel<<<dim3(mq, Nq), 320, kSmemDq, st>>>(tQ, tK, tV, tdO, p);
     }
@@ -652,7 +657,7 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
         fmha_bwd_dkv_ts_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkvTs, st>>>(tQ64, tK, tV, tdO64, pk);
         return (int)cudaGetLastError();
     }
-    if (variant == 5) {      // dK/dV over 128-row query steps: all four products at N = 128
+    if (variant == 5 || variant == 6) {      // dK/dV over 128-row query steps: all four products at N = 128
         if (cudaFuncSetAttribute(fmha_bwd_dkv128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkv128) != cudaSuccess)
             return -3;
         fmha_bwd_dkv128_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkv128, st>>>(tQ, tK, tV, tdO, pk);

@@ -13,7 +13,7 @@
 // the row threads' other phase: while they turn S_{i+1} into P_{i+1}, the pipe runs dK_i and dP_{i+1}; while they turn
 // dP_{i+1} into dS_{i+1}, it runs dV_{i+1} and S_{i+2}.
 //
-//   warp 0      TMA: K, V once; Q_i and dO_i into separate 2-deep rings (Q is released by dK_i, dO by dV_i)
+//   warp 0      TMA: K, V once; Q_i into a 3-deep and dO_i into a 2-deep ring (Q is released by dK_i, dO by dV_i)
 //   warp 1      MMA issuer
 //   warps 2-9   row threads: thread = (key row, half): 64 of the 128 query columns.  Phase 1: P = exp2(S * scale -
 //               lse), masked, kept in registers and written as bf16 pairs over the first 32 of its own 64 S^T columns.
@@ -21,7 +21,9 @@
 // TMEM: S^T 128 | dP^T 128 | dV 128 | dK 128 = 512 columns.  Every mbarrier wait is bounded; a thread whose wait gave
 // up keeps taking part in the named barrier of the statistics exchange, so nobody is left waiting for it.
 
-constexpr int kSmemDkv128 = 2 * kTile + 4 * kTile + 4 * 128 * 4 + 256 + 1024;    // K, V, 2 x Q, 2 x dO, stats, barriers, align
+constexpr int kRingQ128 = 3;    // Q_i is needed first (S^T_i) and released last (dK_i): it gets the deeper ring
+constexpr int kRingDO128 = 2;
+constexpr int kSmemDkv128 = (2 + kRingQ128 + kRingDO128) * kTile + 2 * 128 * 4 + 256 + 1024;    // K, V, Q ring, dO ring, stats, barriers, align
 
 __global__ void __launch_bounds__(320, 1)
 fmha_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -32,22 +34,22 @@ fmha_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sK = smem;
     uint8_t* sV = sK + kTile;
-    uint8_t* sQ = sV + kTile;             // [2]
-    uint8_t* sdO = sQ + 2 * kTile;        // [2]
-    float* s_lse = reinterpret_cast<float*>(sdO + 2 * kTile);     // [2][128]
-    float* s_dlt = s_lse + 2 * BQ;                                 // [2][128]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_dlt + 2 * BQ);
+    uint8_t* sQ = sV + kTile;                     // [kRingQ128]
+    uint8_t* sdO = sQ + kRingQ128 * kTile;        // [kRingDO128]
+    float* s_lse = reinterpret_cast<float*>(sdO + kRingDO128 * kTile);     // [128]
+    float* s_dlt = s_lse + BQ;                                              // [128]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_dlt + BQ);
     uint64_t* kv_full = bars + 0;
-    uint64_t* q_full = bars + 1;      // [2]
-    uint64_t* q_empty = bars + 3;     // [2]
-    uint64_t* do_full = bars + 5;     // [2]
-    uint64_t* do_empty = bars + 7;    // [2]
-    uint64_t* s_full = bars + 9;
-    uint64_t* dp_full = bars + 10;
-    uint64_t* p_full = bars + 11;
-    uint64_t* ds_full = bars + 12;
-    uint64_t* acc_full = bars + 13;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    uint64_t* q_full = bars + 1;                  // [kRingQ128]
+    uint64_t* q_empty = q_full + kRingQ128;       // [kRingQ128]
+    uint64_t* do_full = q_empty + kRingQ128;      // [kRingDO128]
+    uint64_t* do_empty = do_full + kRingDO128;    // [kRingDO128]
+    uint64_t* s_full = do_empty + kRingDO128;
+    uint64_t* dp_full = s_full + 1;
+    uint64_t* p_full = s_full + 2;
+    uint64_t* ds_full = s_full + 3;
+    uint64_t* acc_full = s_full + 4;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 5);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -68,9 +70,11 @@ fmha_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
     if (threadIdx.x == 0) {
         mbar_init(kv_full, 1);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kRingQ128; ++i) {
             mbar_init(&q_full[i], 1);
             mbar_init(&q_empty[i], 1);
+        }
+        for (int i = 0; i < kRingDO128; ++i) {
             mbar_init(&do_full[i], 1);
             mbar_init(&do_empty[i], 1);
         }
@@ -105,18 +109,18 @@ fmha_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             tma_load_3d(sV, &tmV, kv_full, 0, kv_head, k_begin + kv0);
             tma_load_3d(sV + kAtom, &tmV, kv_full, 64, kv_head, k_begin + kv0);
             for (int it = 0; it < n_it; ++it) {
-                const int rs = it & 1;
-                const uint32_t ph = (it >> 1) & 1;
+                const int qs = it % kRingQ128, ds = it % kRingDO128;
+                const uint32_t qph = (it / kRingQ128) & 1, dph = (it / kRingDO128) & 1;
                 const int head = head0 + it / per_head;
                 const int row = q_begin + (i_min + it % per_head) * BQ;
-                if (!mbar_wait(&q_empty[rs], ph ^ 1, abort_flag)) { atomicExch(p.status, MM_TIMEOUT_TMA); break; }
-                mbar_expect_tx(&q_full[rs], kTile);
-                tma_load_3d(sQ + rs * kTile, &tmQ, &q_full[rs], 0, head, row);
-                tma_load_3d(sQ + rs * kTile + kAtom, &tmQ, &q_full[rs], 64, head, row);
-                if (!mbar_wait(&do_empty[rs], ph ^ 1, abort_flag)) { atomicExch(p.status, MM_TIMEOUT_TMA); break; }
-                mbar_expect_tx(&do_full[rs], kTile);
-                tma_load_3d(sdO + rs * kTile, &tmdO, &do_full[rs], 0, head, row);
-                tma_load_3d(sdO + rs * kTile + kAtom, &tmdO, &do_full[rs], 64, head, row);
+                if (!mbar_wait(&q_empty[qs], qph ^ 1, abort_flag)) { atomicExch(p.status, MM_TIMEOUT_TMA); break; }
+                mbar_expect_tx(&q_full[qs], kTile);
+                tma_load_3d(sQ + qs * kTile, &tmQ, &q_full[qs], 0, head, row);
+                tma_load_3d(sQ + qs * kTile + kAtom, &tmQ, &q_full[qs], 64, head, row);
+                if (!mbar_wait(&do_empty[ds], dph ^ 1, abort_flag)) { atomicExch(p.status, MM_TIMEOUT_TMA); break; }
+                mbar_expect_tx(&do_full[ds], kTile);
+                tma_load_3d(sdO + ds * kTile, &tmdO, &do_full[ds], 0, head, row);
+                tma_load_3d(sdO + ds * kTile + kAtom, &tmdO, &do_full[ds], 64, head, row);
             }
         }
     } else if (warp == 1) {
@@ -126,9 +130,10 @@ fmha_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             constexpr uint32_t idesc_acc = idesc_bf16(128, 128, 0, 1);     // dV, dK: B = dO_i / Q_i read as [N = d, K = q]
             bool ok = mbar_wait(kv_full, 0, abort_flag);
             const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
-            auto issue_t = [&](int it, uint32_t a_base, const uint8_t* b_tiles, uint64_t* landed, uint32_t tdst, uint64_t* done) -> bool {
-                const int rs = it & 1;
-                if (!mbar_wait(&landed[rs], (it >> 1) & 1, abort_flag)) return false;
+            auto issue_t = [&](int it, uint32_t a_base, const uint8_t* b_tiles, uint64_t* landed, int ring, uint32_t tdst,
+                               uint64_t* done) -> bool {
+                const int rs = it % ring;
+                if (!mbar_wait(&landed[rs], (it / ring) & 1, abort_flag)) return false;
                 fence_after_sync();
                 const uint32_t ba = smem_u32(b_tiles + rs * kTile);
 #pragma unroll
@@ -141,26 +146,26 @@ fmha_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             };
             // bf16 pairs of query columns [64 h, 64 h + 64) live in the first 32 columns of half h's 64-column region
             auto a_col = [](int k) -> uint32_t { return (uint32_t)((k >> 2) * 64 + (k & 3) * 8); };
-            if (ok) ok = issue_t(0, ka, sQ, q_full, tST, s_full);
-            if (ok) ok = issue_t(0, va, sdO, do_full, tdPT, dp_full);
+            if (ok) ok = issue_t(0, ka, sQ, q_full, kRingQ128, tST, s_full);
+            if (ok) ok = issue_t(0, va, sdO, do_full, kRingDO128, tdPT, dp_full);
             for (int it = 0; it < n_it && ok; ++it) {
-                const int rs = it & 1;
+                const int qs = it % kRingQ128, ds = it % kRingDO128;
                 const uint32_t par = it & 1;
                 if (!mbar_wait(p_full, par, abort_flag)) { ok = false; break; }
                 fence_after_sync();
-                const uint32_t doa = smem_u32(sdO + rs * kTile), qa = smem_u32(sQ + rs * kTile);
+                const uint32_t doa = smem_u32(sdO + ds * kTile), qa = smem_u32(sQ + qs * kTile);
 #pragma unroll
                 for (int k = 0; k < BQ / 16; ++k)
                     mma_ts(tdV, tST + a_col(k), smem_desc_sw128(doa + k * 2048, kAtom, 1024), idesc_acc, (it | k) ? 1u : 0u);
-                mma_commit(&do_empty[rs]);
-                if (it + 1 < n_it && !(ok = issue_t(it + 1, ka, sQ, q_full, tST, s_full))) break;
+                mma_commit(&do_empty[ds]);
+                if (it + 1 < n_it && !(ok = issue_t(it + 1, ka, sQ, q_full, kRingQ128, tST, s_full))) break;
                 if (!mbar_wait(ds_full, par, abort_flag)) { ok = false; break; }
                 fence_after_sync();
 #pragma unroll
                 for (int k = 0; k < BQ / 16; ++k)
                     mma_ts(tdK, tdPT + a_col(k), smem_desc_sw128(qa + k * 2048, kAtom, 1024), idesc_acc, (it | k) ? 1u : 0u);
-                mma_commit(&q_empty[rs]);
-                if (it + 1 < n_it && !(ok = issue_t(it + 1, va, sdO, do_full, tdPT, dp_full))) break;
+                mma_commit(&q_empty[qs]);
+                if (it + 1 < n_it && !(ok = issue_t(it + 1, va, sdO, do_full, kRingDO128, tdPT, dp_full))) break;
             }
             if (ok) mma_commit(acc_full);
             if (!ok) atomicExch(p.status, MM_TIMEOUT_MMA);
@@ -184,11 +189,12 @@ fmha_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         float pre = n_it > 0 ? load_stat(0) : 0.f;
         bool ok = true;
         for (int it = 0; it < n_it; ++it) {
-            const int st = it & 1;
             const uint32_t par = it & 1;
             const int qbase = (i_min + it % per_head) * BQ;
-            if (tid2 < 128) s_lse[st * BQ + tid2] = pre;
-            else s_dlt[st * BQ + tid2 - 128] = pre;
+            // the statistics buffer is single: everybody must be done with tile it - 1 before it is overwritten
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (tid2 < 128) s_lse[tid2] = pre;
+            else s_dlt[tid2 - 128] = pre;
             if (it + 1 < n_it) pre = load_stat(it + 1);
             asm volatile("bar.sync 1, 256;" ::: "memory");
             if (ok && !mbar_wait(s_full, par, abort_flag)) ok = false;
@@ -202,8 +208,8 @@ fmha_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             // visible query columns for this key: qi < q_len and (not causal or kj <= qi + diag)
             const int c_lo = !row_ok ? BQ : (p.causal ? max(0, kj - diag - qbase) : 0);
             const int c_hi = min(BQ, q_len - qbase);
-            const float* ls = s_lse + st * BQ + half * 64;
-            const float* dl = s_dlt + st * BQ + half * 64;
+            const float* ls = s_lse + half * 64;
+            const float* dl = s_dlt + half * 64;
             // packed fp32 math (two query columns per instruction): P = exp2(S^T * scale - lse)
             const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
             const bool col_masked = c_lo > half * 64 || c_hi < half * 64 + 64;

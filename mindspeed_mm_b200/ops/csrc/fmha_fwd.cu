@@ -37,6 +37,8 @@ struct FmhaParams {
     int T, Nq, Nkv, causal;
     float scale_log2;   // softmax scale * log2(e)
     int* status;
+    int flags;          // split kernel: bits 1-2 = share of exponentials on the FMA pipe (0 none, 1 a quarter, 2 half);
+                        // bit 0 = timing experiment only (no row-maximum exchange: wrong results)
 };
 
 __global__ void fmha_plan_kernel(const int* cu_q, int n_seqs, int* tile_seq, int* tile_q0, int* n_tiles, int max_tiles) {
@@ -317,7 +319,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
 #include "fmha_fwd_split.cuh"
 
-int g_fwd_variant = 0;   // 0: default kernel, 1: split-softmax kernel (fmha_fwd_split.cuh)
+int g_fwd_variant = 0;   // low 4 bits: 0 = one-softmax-warpgroup kernel, 1 = split-softmax kernel; higher bits: FmhaParams::flags
 
 }  // namespace
 
@@ -357,9 +359,10 @@ MM_API int mm_fmha_fwd(const void* q, const void* k, const void* v, void* o, flo
         done = true;
     }
     FmhaParams p{cu_q, cu_k, tile_seq, tile_q0, n_tiles, (bf16*)o, lse, T, Nq, Nkv, causal,
-                 scale * 1.4426950408889634f, status};
+                 scale * 1.4426950408889634f, status, 0};
     dim3 grid(max_tiles, Nq);
-    if (g_fwd_variant == 1)
+    p.flags = g_fwd_variant >> 4;
+    if ((g_fwd_variant & 15) == 1)
         fmha_fwd_split_kernel<<<grid, kThreads, kSmem, st>>>(tQ, tK, tV, p);
     else
         fmha_fwd_kernel<<<grid, kThreads, kSmem, st>>>(tQ, tK, tV, p);

@@ -25,6 +25,24 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
+// 2^x for two values at once on the FMA pipe instead of the special-function unit: round-to-nearest split x = n + f
+// with the 1.5 * 2^23 trick, cubic for 2^f on [-0.5, 0.5] (relative error 6e-4, below bf16 resolution), n added to the
+// exponent field.  Inputs are clamped to -126, so masked (-inf) entries come out as 2^-126 instead of 0.
+__device__ __forceinline__ float2 exp2_fma2(float2 x) {
+    const float2 magic = make_float2(12582912.f, 12582912.f);
+    x.x = fmaxf(x.x, -126.f);
+    x.y = fmaxf(x.y, -126.f);
+    const float2 t = __fadd2_rn(x, magic);
+    const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+    const float2 f = __fadd2_rn(x, make_float2(-n.x, -n.y));
+    float2 pl = __ffma2_rn(make_float2(0.0555041f, 0.0555041f), f, make_float2(0.2402265f, 0.2402265f));
+    pl = __ffma2_rn(pl, f, make_float2(0.6931472f, 0.6931472f));
+    pl = __ffma2_rn(pl, f, make_float2(1.f, 1.f));
+    return make_float2(__int_as_float(__float_as_int(pl.x) + (__float_as_int(t.x) << 23)),
+                       __int_as_float(__float_as_int(pl.y) + (__float_as_int(t.y) << 23)));
+}
+
+
 __device__ __forceinline__ void named_barrier_sync(int id, int count) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
@@ -169,6 +187,7 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const int qi = q0 + row;                         // query index inside its sequence
         const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
         float m = -INFINITY, l = 0.f, alpha_pending = 0.f;
+        const int poly_mode = (p.flags >> 1) & 3;
         float acc[64];
 #pragma unroll
         for (int i = 0; i < 64; ++i) acc[i] = 0.f;
@@ -201,12 +220,12 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             uint32_t r[64];
             const uint32_t t_s = tS + st * 128 + lane_off;
             const int kbase = j * BKV + half * 64;
+            const bool need_mask = (kbase + 64 > k_len) || (p.causal && kbase + 63 > q0 + diag);
             if (ok) {
                 fence_after_sync();
                 tmem_ld_32x32(t_s + half * 64, r);
                 tmem_ld_32x32(t_s + half * 64 + 32, r + 32);
                 tmem_wait_ld();
-                const bool need_mask = (kbase + 64 > k_len) || (p.causal && kbase + 63 > q0 + diag);
                 const int limit = p.causal ? min(k_len - 1, qi + diag) : k_len - 1;   // last visible key index
                 // the maximum is taken over the raw scores (the softmax scale is positive); scale and shift are folded
                 // into one fused multiply-add in front of the exponential
@@ -224,11 +243,12 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     mx3 = max3(mx3, __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
                 }
                 const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
-                atomicMax(&maxbuf[(j % 3) * 128 + row], float_to_ordered(mx));
+                if (!(p.flags & 1)) atomicMax(&maxbuf[(j % 3) * 128 + row], float_to_ordered(mx));
+                else maxbuf[(j % 3) * 128 + row] = float_to_ordered(mx);
             }
             // Both halves of every row have read their S columns and published their maximum.  After this barrier
             // the P columns may overwrite S, and the slot of tile j - 1 (next used by tile j + 2) may be reset.
-            named_barrier_sync(1, 256);
+            if (!(p.flags & 1)) named_barrier_sync(1, 256);
             if (half == 0) maxbuf[((j + 2) % 3) * 128 + row] = kOrdNegInf;
             if (ok) {
                 const float mx_all = ordered_to_float(maxbuf[(j % 3) * 128 + row]);
@@ -242,7 +262,9 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 for (int i = 0; i < 32; i += 2) {         // two packed chains: exp2(s * scale - m), running sums, bf16 pairs
                     const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), sc2, ng2);
                     const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(r[2 * i + 2]), __uint_as_float(r[2 * i + 3])), sc2, ng2);
-                    const float2 e0 = make_float2(exp2f(x0.x), exp2f(x0.y));
+                    // unmasked tiles hand a share of the exponentials to the FMA pipe to unload the special-function unit
+                    const bool poly = poly_mode != 0 && !need_mask && (poly_mode == 2 || ((i >> 1) & 1) == 0);
+                    const float2 e0 = poly ? exp2_fma2(x0) : make_float2(exp2f(x0.x), exp2f(x0.y));
                     const float2 e1 = make_float2(exp2f(x1.x), exp2f(x1.y));
                     sum_a = __fadd2_rn(sum_a, e0);
                     sum_b = __fadd2_rn(sum_b, e1);

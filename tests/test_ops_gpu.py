@@ -228,6 +228,35 @@ def test_fmha_forward_and_grad(lens, nq, nkv, causal):
     _close(vg.grad, vr.grad, rtol=3e-2, atol=3e-2)
 
 
+@pytest.mark.parametrize("fwd_variant,bwd_variant", [(0, 0), (1, 6), (0, 5)])
+def test_fmha_kernel_variants_agree_with_reference(fwd_variant, bwd_variant):
+    """The non-default forward / backward kernels stay correct: GQA + causal, ragged packing."""
+    from mindspeed_mm_b200.ops import native
+    torch.manual_seed(0)
+    lens, nq, nkv, D = [300, 129, 700], 4, 2, 128
+    T = sum(lens)
+    q, k, v = (torch.randn(T, n, D, device=DEV, dtype=torch.bfloat16) for n in (nq, nkv, nkv))
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    prev_f = native.lib().mm_fmha_set_fwd_variant(fwd_variant)
+    prev_b, native.FMHA_BWD_VARIANT = native.FMHA_BWD_VARIANT, bwd_variant
+    try:
+        qg, kg, vg = (t.detach().clone().requires_grad_() for t in (q, k, v))
+        o = ops.attention_varlen(qg, kg, vg, cu, cu, max(lens), max(lens), causal=True)
+        do = torch.randn_like(o)
+        o.backward(do)
+        native.check_status()
+    finally:
+        native.lib().mm_fmha_set_fwd_variant(prev_f)
+        native.FMHA_BWD_VARIANT = prev_b
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    orf = ref.attention_varlen(qr, kr, vr, cu.cpu(), cu.cpu(), True)
+    orf.backward(do.float())
+    _close(o, orf, rtol=2e-2, atol=2e-2)
+    _close(qg.grad, qr.grad, rtol=3e-2, atol=3e-2)
+    _close(kg.grad, kr.grad, rtol=3e-2, atol=3e-2)
+    _close(vg.grad, vr.grad, rtol=3e-2, atol=3e-2)
+
+
 def test_attention_head_dim_80_padded_onto_native_kernels():
     """ViT heads (D = 80) with window-sized segments: zero-padded to 128 and run by the tcgen05 forward / backward."""
     from mindspeed_mm_b200.ops import native

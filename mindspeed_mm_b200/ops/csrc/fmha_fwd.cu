@@ -37,8 +37,6 @@ struct FmhaParams {
     int T, Nq, Nkv, causal;
     float scale_log2;   // softmax scale * log2(e)
     int* status;
-    int flags;          // split kernel: bits 1-2 = share of exponentials on the FMA pipe (0 none, 1 a quarter, 2 half);
-                        // bit 0 = timing experiment only (no row-maximum exchange: wrong results)
 };
 
 __global__ void fmha_plan_kernel(const int* cu_q, int n_seqs, int* tile_seq, int* tile_q0, int* n_tiles, int max_tiles) {
@@ -319,7 +317,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
 #include "fmha_fwd_split.cuh"
 
-int g_fwd_variant = 0;   // low 4 bits: 0 = one-softmax-warpgroup kernel, 1 = split-softmax kernel; higher bits: FmhaParams::flags
+int g_fwd_variant = 0;   // 0: one softmax warpgroup; 1 / 2: split-softmax kernel with 2 / 4 compute warpgroups (fmha_fwd_split.cuh)
 
 }  // namespace
 
@@ -354,16 +352,23 @@ MM_API int mm_fmha_fwd(const void* q, const void* k, const void* v, void* o, flo
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(fmha_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
         if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(fmha_fwd_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+            e = cudaFuncSetAttribute(fmha_fwd_split_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(fmha_fwd_split_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(fmha_fwd_split_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
     FmhaParams p{cu_q, cu_k, tile_seq, tile_q0, n_tiles, (bf16*)o, lse, T, Nq, Nkv, causal,
-                 scale * 1.4426950408889634f, status, 0};
+                 scale * 1.4426950408889634f, status};
     dim3 grid(max_tiles, Nq);
-    p.flags = g_fwd_variant >> 4;
-    if ((g_fwd_variant & 15) == 1)
-        fmha_fwd_split_kernel<<<grid, kThreads, kSmem, st>>>(tQ, tK, tV, p);
+    if (g_fwd_variant == 1)
+        fmha_fwd_split_kernel<2><<<grid, 64 + 256, kSmem, st>>>(tQ, tK, tV, p);
+    else if (g_fwd_variant == 2)
+        fmha_fwd_split_kernel<4><<<grid, 64 + 512, kSmem, st>>>(tQ, tK, tV, p);
+    else if (g_fwd_variant == 3)
+        fmha_fwd_split_kernel<2, true><<<grid, 64 + 256, kSmem, st>>>(tQ, tK, tV, p);
     else
         fmha_fwd_kernel<<<grid, kThreads, kSmem, st>>>(tQ, tK, tV, p);
     return (int)cudaGetLastError();

@@ -25,29 +25,16 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
-// 2^x for two values at once on the FMA pipe instead of the special-function unit: round-to-nearest split x = n + f
-// with the 1.5 * 2^23 trick, cubic for 2^f on [-0.5, 0.5] (relative error 6e-4, below bf16 resolution), n added to the
-// exponent field.  Inputs are clamped to -126, so masked (-inf) entries come out as 2^-126 instead of 0.
-__device__ __forceinline__ float2 exp2_fma2(float2 x) {
-    const float2 magic = make_float2(12582912.f, 12582912.f);
-    x.x = fmaxf(x.x, -126.f);
-    x.y = fmaxf(x.y, -126.f);
-    const float2 t = __fadd2_rn(x, magic);
-    const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
-    const float2 f = __fadd2_rn(x, make_float2(-n.x, -n.y));
-    float2 pl = __ffma2_rn(make_float2(0.0555041f, 0.0555041f), f, make_float2(0.2402265f, 0.2402265f));
-    pl = __ffma2_rn(pl, f, make_float2(0.6931472f, 0.6931472f));
-    pl = __ffma2_rn(pl, f, make_float2(1.f, 1.f));
-    return make_float2(__int_as_float(__float_as_int(pl.x) + (__float_as_int(t.x) << 23)),
-                       __int_as_float(__float_as_int(pl.y) + (__float_as_int(t.y) << 23)));
-}
-
-
 __device__ __forceinline__ void named_barrier_sync(int id, int count) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+// PARTS compute warpgroups (2 or 4): each owns 128 / PARTS key columns of S and as many head-dim columns of O.
+// SKEW (two warpgroups only): warpgroup 1 folds O_{j-1} first and starts its exponentials only when warpgroup 0 has
+// finished its own, so that the two warps of a scheduler use the special-function unit one after the other and each
+// one's loads / maxima / conversions / folds overlap the other's exponentials instead of all idling together.
+template <int PARTS, bool SKEW = false>
+__global__ void __launch_bounds__(64 + 128 * PARTS, 1)
 fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, FmhaParams p) {
     if ((int)blockIdx.x >= *p.n_tiles) return;
@@ -67,10 +54,14 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     uint64_t* p_full = bars + 15;   // [2]
     uint64_t* o_full = bars + 17;   // [2]
     uint64_t* o_empty = bars + 19;  // [2]
+    uint64_t* a_done = bars + 22;   // [2]  warpgroup 0 finished its exponentials of the tile in S[st] (SKEW only)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* maxbuf = reinterpret_cast<int*>(aux + 256);            // [3][128] row maxima as ordered ints, rotating
-    float* l_half = reinterpret_cast<float*>(aux + 256);        // [2][128], reuses maxbuf after the key loop
+    float* l_sum = reinterpret_cast<float*>(aux + 256);         // [128], reuses maxbuf after the key loop
+    constexpr int C = 128 / PARTS;                               // columns per compute thread
+    constexpr int kCompute = 128 * PARTS;                        // compute threads
+    constexpr int kAll = 64 + kCompute;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seq = p.tile_seq[blockIdx.x];
@@ -94,9 +85,10 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], 256);
+            mbar_init(&p_full[i], kCompute);
             mbar_init(&o_full[i], 1);
-            mbar_init(&o_empty[i], 256);
+            mbar_init(&o_empty[i], kCompute);
+            mbar_init(&a_done[i], 128);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -108,7 +100,7 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
-    for (int i = threadIdx.x; i < 3 * 128; i += kThreads) maxbuf[i] = kOrdNegInf;
+    for (int i = threadIdx.x; i < 3 * 128; i += kAll) maxbuf[i] = kOrdNegInf;
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
@@ -181,32 +173,31 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
     } else {
         // ------------------------------------------------------------------------------ compute (warps 2..9)
-        const int half = warp >= 6 ? 1 : 0;              // which 64 key columns of S / 64 head-dim columns of O
+        const int half = (warp - 2) >> 2;                // which C key columns of S / C head-dim columns of O
         const int qd = warp & 3;                         // TMEM lane quarter this warp may touch
         const int row = qd * 32 + lane;
         const int qi = q0 + row;                         // query index inside its sequence
         const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
         float m = -INFINITY, l = 0.f, alpha_pending = 0.f;
-        const int poly_mode = (p.flags >> 1) & 3;
-        float acc[64];
+        float acc[C];
 #pragma unroll
-        for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+        for (int i = 0; i < C; ++i) acc[i] = 0.f;
         bool ok = true;
         auto fold = [&](int jj) {                        // O_acc = O_acc * alpha_jj + O_jj for this thread's 64 columns
             const int sb = jj & 1;
             if (ok && !mbar_wait(&o_full[sb], (jj >> 1) & 1, abort_flag)) ok = false;
             if (!ok) return;
             fence_after_sync();
-            uint32_t o[64];
-            const uint32_t t_o = tO + sb * 128 + half * 64 + lane_off;
+            uint32_t o[C];
+            const uint32_t t_o = tO + sb * 128 + half * C + lane_off;
             tmem_ld_32x32(t_o, o);
-            tmem_ld_32x32(t_o + 32, o + 32);
+            if constexpr (C == 64) tmem_ld_32x32(t_o + 32, o + 32);
             tmem_wait_ld();
             fence_before_sync();
             mbar_arrive(&o_empty[sb]);
             const float2 a2 = make_float2(alpha_pending, alpha_pending);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {                // packed fp32: one instruction per two columns
+            for (int i = 0; i < C / 2; ++i) {             // packed fp32: one instruction per two columns
                 const float2 v = __ffma2_rn(make_float2(acc[2 * i], acc[2 * i + 1]), a2,
                                             make_float2(__uint_as_float(o[2 * i]), __uint_as_float(o[2 * i + 1])));
                 acc[2 * i] = v.x;
@@ -217,38 +208,37 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const int st = j & 1;
             const uint32_t ph = (j >> 1) & 1;
             if (ok && !mbar_wait(&s_full[st], ph, abort_flag)) ok = false;
-            uint32_t r[64];
+            uint32_t r[C];
             const uint32_t t_s = tS + st * 128 + lane_off;
-            const int kbase = j * BKV + half * 64;
-            const bool need_mask = (kbase + 64 > k_len) || (p.causal && kbase + 63 > q0 + diag);
+            const int kbase = j * BKV + half * C;
             if (ok) {
                 fence_after_sync();
-                tmem_ld_32x32(t_s + half * 64, r);
-                tmem_ld_32x32(t_s + half * 64 + 32, r + 32);
+                tmem_ld_32x32(t_s + half * C, r);
+                if constexpr (C == 64) tmem_ld_32x32(t_s + half * C + 32, r + 32);
                 tmem_wait_ld();
+                const bool need_mask = (kbase + C > k_len) || (p.causal && kbase + C - 1 > q0 + diag);
                 const int limit = p.causal ? min(k_len - 1, qi + diag) : k_len - 1;   // last visible key index
                 // the maximum is taken over the raw scores (the softmax scale is positive); scale and shift are folded
                 // into one fused multiply-add in front of the exponential
                 if (need_mask) {
 #pragma unroll
-                    for (int i = 0; i < 64; ++i)
+                    for (int i = 0; i < C; ++i)
                         if (kbase + i > limit) r[i] = 0xff800000u;       // -inf
                 }
                 float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 64; i += 8) {         // four independent chains of three-input maxima
+                for (int i = 0; i < C; i += 8) {          // four independent chains of three-input maxima
                     mx0 = max3(mx0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
                     mx1 = max3(mx1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
                     mx2 = max3(mx2, __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
                     mx3 = max3(mx3, __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
                 }
                 const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
-                if (!(p.flags & 1)) atomicMax(&maxbuf[(j % 3) * 128 + row], float_to_ordered(mx));
-                else maxbuf[(j % 3) * 128 + row] = float_to_ordered(mx);
+                atomicMax(&maxbuf[(j % 3) * 128 + row], float_to_ordered(mx));
             }
             // Both halves of every row have read their S columns and published their maximum.  After this barrier
             // the P columns may overwrite S, and the slot of tile j - 1 (next used by tile j + 2) may be reset.
-            if (!(p.flags & 1)) named_barrier_sync(1, 256);
+            named_barrier_sync(1, kCompute);
             if (half == 0) maxbuf[((j + 2) % 3) * 128 + row] = kOrdNegInf;
             if (ok) {
                 const float mx_all = ordered_to_float(maxbuf[(j % 3) * 128 + row]);
@@ -256,15 +246,19 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const float m_use = m_new == -INFINITY ? 0.f : m_new;
                 const float alpha = exp2f(m - m_use);        // m = -inf on the first tile -> 0
                 m = m_new;
+                if constexpr (SKEW) {
+                    if (half == 1) {
+                        if (j > 0) fold(j - 1);
+                        if (ok && !mbar_wait(&a_done[st], ph, abort_flag)) ok = false;
+                    }
+                }
                 const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), ng2 = make_float2(-m_use, -m_use);
                 float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {         // two packed chains: exp2(s * scale - m), running sums, bf16 pairs
+                for (int i = 0; i < C / 2; i += 2) {      // two packed chains: exp2(s * scale - m), running sums, bf16 pairs
                     const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), sc2, ng2);
                     const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(r[2 * i + 2]), __uint_as_float(r[2 * i + 3])), sc2, ng2);
-                    // unmasked tiles hand a share of the exponentials to the FMA pipe to unload the special-function unit
-                    const bool poly = poly_mode != 0 && !need_mask && (poly_mode == 2 || ((i >> 1) & 1) == 0);
-                    const float2 e0 = poly ? exp2_fma2(x0) : make_float2(exp2f(x0.x), exp2f(x0.y));
+                    const float2 e0 = make_float2(exp2f(x0.x), exp2f(x0.y));
                     const float2 e1 = make_float2(exp2f(x1.x), exp2f(x1.y));
                     sum_a = __fadd2_rn(sum_a, e0);
                     sum_b = __fadd2_rn(sum_b, e1);
@@ -273,27 +267,37 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     r[i + 1] = *reinterpret_cast<uint32_t*>(&t1);
                 }
                 l = l * alpha + ((sum_a.x + sum_a.y) + (sum_b.x + sum_b.y));
-                // P: bf16 pairs over the first 64 columns of S[st]; this half's 64 keys are columns [32 half, 32 half + 32)
-                tmem_st_32x32(t_s + half * 32, r);
+                // P: bf16 pairs over the first 64 columns of S[st]; this part's C keys are columns [C / 2 * part, + C / 2)
+                if constexpr (C == 64) tmem_st_32x32(t_s + half * 32, r);
+                else tmem_st_32x16(t_s + half * 16, r);
                 tmem_wait_st();
                 fence_before_sync();
                 mbar_arrive(&p_full[st]);
-                if (j > 0) fold(j - 1);                      // uses alpha of tile j - 1
+                if constexpr (SKEW) {
+                    if (half == 0) {
+                        mbar_arrive(&a_done[st]);
+                        if (j > 0) fold(j - 1);
+                    }
+                } else {
+                    if (j > 0) fold(j - 1);                  // uses alpha of tile j - 1
+                }
                 alpha_pending = alpha;
             }
         }
         if (n_kv > 0) fold(n_kv - 1);
-        named_barrier_sync(1, 256);                          // maxbuf is free: reuse it for the two partial row sums
-        l_half[half * 128 + row] = l;
-        named_barrier_sync(1, 256);
+        named_barrier_sync(1, kCompute);                     // maxbuf is free: reuse it for the row sums
+        if (half == 0) l_sum[row] = 0.f;
+        named_barrier_sync(1, kCompute);
+        atomicAdd(&l_sum[row], l);
+        named_barrier_sync(1, kCompute);
         if (ok && qi < q_len && n_kv > 0) {
-            const float lsum = l_half[row] + l_half[128 + row];
+            const float lsum = l_sum[row];
             const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
             if (half == 0)
                 p.lse[(size_t)head * p.T + q_begin + qi] = (m == -INFINITY) ? -INFINITY : m * 0.6931471805599453f + logf(lsum);
-            bf16* dst = p.o + ((size_t)(q_begin + qi) * p.Nq + head) * HD + half * 64;
+            bf16* dst = p.o + ((size_t)(q_begin + qi) * p.Nq + head) * HD + half * C;
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
+            for (int g = 0; g < C / 8; ++g) {
                 float f[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) f[i] = acc[g * 8 + i] * inv;

@@ -497,7 +497,9 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             else if (tid2 < 128) s_dlt[st * BQ2 + tid2 - 64] = pre;
             if (it + 1 < n_it) pre = load_stat(it + 1);
             asm volatile("bar.sync 1, 256;" ::: "memory");
-            if (!mbar_wait(&st_full[st], ph, abort_flag)) { ok = false; break; }
+            // a thread whose wait gave up keeps walking the loop for the named barrier above, so nobody waits for it
+            if (ok && !mbar_wait(&st_full[st], ph, abort_flag)) ok = false;
+            if (!ok) continue;
             fence_after_sync();
             uint32_t s[32], d[32];
             tmem_ld_32x32(tST + st * BQ2 + half * 32 + lane_off, s);

@@ -30,10 +30,7 @@ __device__ __forceinline__ void named_barrier_sync(int id, int count) {
 }
 
 // PARTS compute warpgroups (2 or 4): each owns 128 / PARTS key columns of S and as many head-dim columns of O.
-// SKEW (two warpgroups only): warpgroup 1 folds O_{j-1} first and starts its exponentials only when warpgroup 0 has
-// finished its own, so that the two warps of a scheduler use the special-function unit one after the other and each
-// one's loads / maxima / conversions / folds overlap the other's exponentials instead of all idling together.
-template <int PARTS, bool SKEW = false>
+template <int PARTS>
 __global__ void __launch_bounds__(64 + 128 * PARTS, 1)
 fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, FmhaParams p) {
@@ -54,7 +51,6 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     uint64_t* p_full = bars + 15;   // [2]
     uint64_t* o_full = bars + 17;   // [2]
     uint64_t* o_empty = bars + 19;  // [2]
-    uint64_t* a_done = bars + 22;   // [2]  warpgroup 0 finished its exponentials of the tile in S[st] (SKEW only)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* maxbuf = reinterpret_cast<int*>(aux + 256);            // [3][128] row maxima as ordered ints, rotating
@@ -88,7 +84,6 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             mbar_init(&p_full[i], kCompute);
             mbar_init(&o_full[i], 1);
             mbar_init(&o_empty[i], kCompute);
-            mbar_init(&a_done[i], 128);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -246,12 +241,6 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const float m_use = m_new == -INFINITY ? 0.f : m_new;
                 const float alpha = exp2f(m - m_use);        // m = -inf on the first tile -> 0
                 m = m_new;
-                if constexpr (SKEW) {
-                    if (half == 1) {
-                        if (j > 0) fold(j - 1);
-                        if (ok && !mbar_wait(&a_done[st], ph, abort_flag)) ok = false;
-                    }
-                }
                 const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), ng2 = make_float2(-m_use, -m_use);
                 float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
 #pragma unroll
@@ -273,14 +262,7 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 tmem_wait_st();
                 fence_before_sync();
                 mbar_arrive(&p_full[st]);
-                if constexpr (SKEW) {
-                    if (half == 0) {
-                        mbar_arrive(&a_done[st]);
-                        if (j > 0) fold(j - 1);
-                    }
-                } else {
-                    if (j > 0) fold(j - 1);                  // uses alpha of tile j - 1
-                }
+                if (j > 0) fold(j - 1);                      // uses alpha of tile j - 1
                 alpha_pending = alpha;
             }
         }

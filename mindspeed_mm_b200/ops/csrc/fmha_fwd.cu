@@ -355,6 +355,8 @@ MM_API int mm_fmha_fwd(const void* q, const void* k, const void* v, void* o, flo
             e = cudaFuncSetAttribute(fmha_fwd_split_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(fmha_fwd_split_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(fmha_fwd_split_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
 
         if (e != cudaSuccess) return (int)e;
         done = true;
@@ -366,6 +368,8 @@ MM_API int mm_fmha_fwd(const void* q, const void* k, const void* v, void* o, flo
         fmha_fwd_split_kernel<2><<<grid, 64 + 256, kSmem, st>>>(tQ, tK, tV, p);
     else if (g_fwd_variant == 2)
         fmha_fwd_split_kernel<4><<<grid, 64 + 512, kSmem, st>>>(tQ, tK, tV, p);
+    else if (g_fwd_variant == 3)
+        fmha_fwd_split_kernel<2, true><<<grid, 64 + 256, kSmem, st>>>(tQ, tK, tV, p);
 
     else
         fmha_fwd_kernel<<<grid, kThreads, kSmem, st>>>(tQ, tK, tV, p);

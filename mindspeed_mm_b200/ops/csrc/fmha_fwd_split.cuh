@@ -30,7 +30,12 @@ __device__ __forceinline__ void named_barrier_sync(int id, int count) {
 }
 
 // PARTS compute warpgroups (2 or 4): each owns 128 / PARTS key columns of S and as many head-dim columns of O.
-template <int PARTS>
+// LAZY: O is accumulated across key tiles by the tensor core itself (one TMEM accumulator, no per-tile fold in
+// registers).  The reference maximum of a row is only moved when the running maximum has grown by more than 2^8
+// since it was set; only then the row threads rescale their O columns in tensor memory (rare after the first tiles).
+// P = exp2(S * scale - m_ref) is therefore at most 2^8, well inside bf16 / fp32 range, and the result is exact because
+// l, the LSE and O all refer to the same m_ref.
+template <int PARTS, bool LAZY = false>
 __global__ void __launch_bounds__(64 + 128 * PARTS, 1)
 fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, FmhaParams p) {
@@ -151,7 +156,7 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 if (!ok) break;
                 const int st = j & 1, rs = j % kRing;
                 const uint32_t ph = (j >> 1) & 1;
-                if (!mbar_wait(&o_empty[st], ph ^ 1, abort_flag) || !mbar_wait(&v_full[rs], (j / kRing) & 1, abort_flag) ||
+                if ((!LAZY && !mbar_wait(&o_empty[st], ph ^ 1, abort_flag)) || !mbar_wait(&v_full[rs], (j / kRing) & 1, abort_flag) ||
                     !mbar_wait(&p_full[st], ph, abort_flag)) { ok = false; break; }
                 fence_after_sync();
                 // P comes from tensor memory: bf16 pairs in the first 64 columns of S[st], 8 columns per K = 16 step
@@ -159,7 +164,8 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
                 for (int k = 0; k < BKV / 16; ++k) {
                     const uint64_t db = smem_desc_sw128(va + k * 2048, kAtomBytes, 1024);
-                    mma_ts(tO + st * 128, tS + st * 128 + k * 8, db, idesc_pv, k ? 1u : 0u);
+                    if constexpr (LAZY) mma_ts(tO, tS + st * 128 + k * 8, db, idesc_pv, (j | k) ? 1u : 0u);
+                    else mma_ts(tO + st * 128, tS + st * 128 + k * 8, db, idesc_pv, k ? 1u : 0u);
                 }
                 mma_commit(&o_full[st]);
                 mma_commit(&v_empty[rs]);
@@ -237,9 +243,38 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             if (half == 0) maxbuf[((j + 2) % 3) * 128 + row] = kOrdNegInf;
             if (ok) {
                 const float mx_all = ordered_to_float(maxbuf[(j % 3) * 128 + row]);
-                const float m_new = fmaxf(m, mx_all);
+                float m_new = fmaxf(m, mx_all);
+                if constexpr (LAZY) {
+                    const bool grow = m_new > m + 8.f;           // also true for the first finite maximum (m = -inf)
+                    if (!grow) m_new = m;
+                    if (__any_sync(__activemask(), grow) && j > 0) {
+                        // rescale this thread's O columns in tensor memory; PV_{j-1} must have landed, PV_j is not issued
+                        // before every thread has arrived on p_full
+                        const int sb = (j - 1) & 1;
+                        if (!mbar_wait(&o_full[sb], ((j - 1) >> 1) & 1, abort_flag)) ok = false;
+                        if (ok) {
+                            fence_after_sync();
+                            const float a = grow ? exp2f(m - (m_new == -INFINITY ? 0.f : m_new)) : 1.f;
+                            const float2 a2 = make_float2(a, a);
+                            uint32_t o[C];
+                            const uint32_t t_o = tO + half * C + lane_off;
+                            tmem_ld_32x32(t_o, o);
+                            if constexpr (C == 64) tmem_ld_32x32(t_o + 32, o + 32);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < C / 2; ++i) {
+                                const float2 v = __fmul2_rn(make_float2(__uint_as_float(o[2 * i]), __uint_as_float(o[2 * i + 1])), a2);
+                                o[2 * i] = __float_as_uint(v.x);
+                                o[2 * i + 1] = __float_as_uint(v.y);
+                            }
+                            tmem_st_32x32(t_o, o);
+                            if constexpr (C == 64) tmem_st_32x32(t_o + 32, o + 32);
+                            tmem_wait_st();
+                        }
+                    }
+                }
                 const float m_use = m_new == -INFINITY ? 0.f : m_new;
-                const float alpha = exp2f(m - m_use);        // m = -inf on the first tile -> 0
+                const float alpha = exp2f(m - m_use);        // m = -inf on the first tile -> 0; 1 when the reference stays
                 m = m_new;
                 const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), ng2 = make_float2(-m_use, -m_use);
                 float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
@@ -262,11 +297,31 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 tmem_wait_st();
                 fence_before_sync();
                 mbar_arrive(&p_full[st]);
-                if (j > 0) fold(j - 1);                      // uses alpha of tile j - 1
-                alpha_pending = alpha;
+                if constexpr (!LAZY) {
+                    if (j > 0) fold(j - 1);                  // uses alpha of tile j - 1
+                    alpha_pending = alpha;
+                }
             }
         }
-        if (n_kv > 0) fold(n_kv - 1);
+        if constexpr (LAZY) {
+            // the accumulator of all tiles sits in tensor memory: take it once
+            if (n_kv > 0) {
+                const int sb = (n_kv - 1) & 1;
+                if (ok && !mbar_wait(&o_full[sb], ((n_kv - 1) >> 1) & 1, abort_flag)) ok = false;
+                if (ok) {
+                    fence_after_sync();
+                    uint32_t o[C];
+                    const uint32_t t_o = tO + half * C + lane_off;
+                    tmem_ld_32x32(t_o, o);
+                    if constexpr (C == 64) tmem_ld_32x32(t_o + 32, o + 32);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < C; ++i) acc[i] = __uint_as_float(o[i]);
+                }
+            }
+        } else {
+            if (n_kv > 0) fold(n_kv - 1);
+        }
         named_barrier_sync(1, kCompute);                     // maxbuf is free: reuse it for the row sums
         if (half == 0) l_sum[row] = 0.f;
         named_barrier_sync(1, kCompute);

@@ -17,8 +17,10 @@ from . import build as _build
 
 _LIB = None
 _STATUS: dict = {}
-# forward attention kernel: 1 = split-softmax kernel (csrc/fmha_fwd_split.cuh, default), 0 = one softmax warpgroup
-FMHA_FWD_VARIANT = int(os.environ.get("MM_B200_FMHA_FWD_VARIANT", "1"))
+# forward attention kernel (csrc/fmha_fwd_split.cuh): 3 = split softmax, O accumulated in tensor memory with lazy
+# rescaling (default); 1 = split softmax with a per-tile fold in registers; 2 = the same with four compute warpgroups;
+# 0 = one softmax warpgroup (csrc/fmha_fwd.cu)
+FMHA_FWD_VARIANT = int(os.environ.get("MM_B200_FMHA_FWD_VARIANT", "3"))
 LAUNCHES = 0  # native kernel launches issued through this module (bench reports it)
 
 _p, _i, _ll, _f = C.c_void_p, C.c_int, C.c_longlong, C.c_float

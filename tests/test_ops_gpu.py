@@ -228,7 +228,7 @@ def test_fmha_forward_and_grad(lens, nq, nkv, causal):
     _close(vg.grad, vr.grad, rtol=3e-2, atol=3e-2)
 
 
-@pytest.mark.parametrize("fwd_variant,bwd_variant", [(0, 0), (1, 6), (0, 5)])
+@pytest.mark.parametrize("fwd_variant,bwd_variant", [(0, 0), (1, 6), (2, 5), (3, 5)])
 def test_fmha_kernel_variants_agree_with_reference(fwd_variant, bwd_variant):
     """The non-default forward / backward kernels stay correct: GQA + causal, ragged packing."""
     from mindspeed_mm_b200.ops import native

@@ -100,6 +100,7 @@ class SyntheticVideoLatentSpec:
     num_samples: int = 1 << 30
     seed: int = 0
     dtype: torch.dtype = torch.float32
+    pooled_dim: int = 0          # > 0: also emit ``added_cond`` = pooled prompt embedding + six size / crop numbers (SDXL)
 
 
 @data_register.register("synthetic_video_latents")
@@ -113,10 +114,15 @@ class SyntheticVideoLatentDataset(Dataset):
     def __getitem__(self, i):
         s = self.spec
         g = torch.Generator().manual_seed(s.seed * 1_000_003 + i)
-        return dict(
+        out = dict(
             latents=torch.randn(s.channels, s.frames, s.height, s.width, generator=g).to(s.dtype),
             prompt=torch.randn(s.text_len, s.text_dim, generator=g).to(s.dtype),
             prompt_mask=torch.ones(s.text_len, dtype=torch.bool))
+        if s.pooled_dim:
+            px = (8.0 * s.height, 8.0 * s.width)
+            out["added_cond"] = torch.cat([torch.randn(s.pooled_dim, generator=g),
+                                           torch.tensor([*px, 0.0, 0.0, *px])]).to(s.dtype)
+        return out
 
 
 # ------------------------------------------------------------------------------------------------- speech

@@ -112,13 +112,13 @@ class GaussianDiffusion:
                  timestep_respacing: Union[str, Sequence[int], None] = None, noise_schedule: str = "linear",
                  use_kl: bool = False, sigma_small: bool = False, predict_xstart: bool = False, learn_sigma: bool = True,
                  rescale_learned_sigmas: bool = False, prediction_type: Optional[str] = None, snr_gamma: Optional[float] = None,
-                 cfg_scale: float = 4.0, cfg_channels: Optional[int] = 3, **_):
+                 cfg_scale: float = 4.0, cfg_channels: Optional[int] = 3, beta_start: float = 1e-4, beta_end: float = 2e-2, **_):
         self.num_train_steps = num_train_steps
         self.loss_type = "rescaled_kl" if use_kl else ("rescaled_mse" if rescale_learned_sigmas else "mse")
         self.mean_type = prediction_type or ("x0" if predict_xstart else "epsilon")        # epsilon | x0 | v
         self.var_type = "learned_range" if learn_sigma else ("fixed_small" if sigma_small else "fixed_large")
         self.snr_gamma, self.cfg_scale, self.cfg_channels = snr_gamma, cfg_scale, cfg_channels
-        base = beta_schedule(noise_schedule, num_train_steps)
+        base = beta_schedule(noise_schedule, num_train_steps, beta_start, beta_end)
         if num_inference_steps is not None:
             timestep_respacing = str(num_inference_steps)
         keep = space_timesteps(num_train_steps, timestep_respacing if timestep_respacing else [num_train_steps])

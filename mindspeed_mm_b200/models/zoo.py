@@ -11,3 +11,4 @@ from . import ltx2  # noqa: F401
 from . import speech_lm  # noqa: F401
 from . import video_dits  # noqa: F401
 from . import omni  # noqa: F401
+from . import sdxl_unet  # noqa: F401

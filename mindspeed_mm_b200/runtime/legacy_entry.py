@@ -88,6 +88,7 @@ def datasets_provider(kind: str, args, model, ps):
             channels=channels, frames=int(basic.get("frames", 5)), height=int(basic.get("height", 16)),
             width=int(basic.get("width", 16)), text_len=int(getattr(c, "text_len", basic.get("text_len", 16))),
             text_dim=c.text_dim, seed=args.seed,
+            pooled_dim=int(c.pooled_dim) if getattr(model.predictor, "cond_input", "") == "added_cond" else 0,
             num_samples=int(basic.get("num_samples", 1 << 20))))
         coll = lambda ss: {k: torch.stack([s[k] for s in ss]) for k in ss[0]}   # noqa: E731
     sampler = BaseRandomBatchSampler(len(ds), args.micro_batch_size, ps.get_dp_rank(), ps.get_dp_world_size(), seed=args.seed)

@@ -24,6 +24,7 @@ def cases():
     from mindspeed_mm_b200.models.diffusion import build_scheduler
     from mindspeed_mm_b200.models.ltx2 import LTX2Config, LTX2Model
     from mindspeed_mm_b200.models.omni import BagelConfig, BagelMoT, RewardModelBT
+    from mindspeed_mm_b200.models.sdxl_unet import SDXLConfig, SDXLUNet
     from mindspeed_mm_b200.models.speech_lm import CosyVoice3LM, MultiCodebookLM, Qwen3TTSTalker
     from mindspeed_mm_b200.models.video_dits import JointDiT, VideoDiTConfig
     from mindspeed_mm_b200.models.wan import SoRAModel
@@ -59,6 +60,9 @@ def cases():
         ("reward", RewardModelBT, lambda m: rm_batch),
         ("satdit", sora(lambda: JointDiT(VideoDiTConfig.tiny(in_channels=16, out_channels=16, text_dim=64)), dict(model_id="cogvideo_diffusion")),
          lambda m: lat),
+        ("sdxl", sora(lambda: SDXLUNet(SDXLConfig.tiny()), dict(model_id="ddpm", learn_sigma=False, noise_schedule="scaled_linear")),
+         lambda m: dict(latents=torch.randn(2, 4, 1, 8, 8), prompt=torch.randn(2, 6, 48),
+                        added_cond=torch.cat([torch.randn(2, 24), torch.tensor([[64.0, 64.0, 0.0, 0.0, 64.0, 64.0]] * 2)], 1))),
         ("vace", sora(lambda: VaceWanDiT(VaceConfig.tiny()), dict(model_id="wan_flow_match_scheduler")),
          lambda m: dict(lat)),
         ("wan2_2_moe", sora(lambda: Wan22DiT(Wan22Config.tiny(moe_num_experts=2, per_token_timestep=True)), dict(model_id="wan_flow_match_scheduler")),

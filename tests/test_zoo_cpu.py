@@ -267,3 +267,37 @@ def test_reward_model_bradley_terry():
     loss.backward()
     assert rm.value_head.rm_head.weight.grad is not None and 0 <= float(rm.last_accuracy) <= 1
     assert "backbone.lm_head" not in [n for n, _ in rm.fsdp_units()]
+
+
+def test_sdxl_unet_matches_published_size_and_trains_through_the_sora_wrapper():
+    import json
+    import os
+    from mindspeed_mm_b200.models.diffusion import build_scheduler
+    from mindspeed_mm_b200.models.registry import build_model
+    from mindspeed_mm_b200.models.sdxl_unet import SDXLConfig, SDXLUNet, compute_time_ids
+    from mindspeed_mm_b200.models.wan import SoRAModel
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    full = json.load(open(os.path.join(root, "examples/sdxl/pretrain_model.json")))
+    with torch.device("meta"):
+        big = build_model("sdxl_unet", full["predictor"])
+    assert sum(p.numel() for p in big.parameters()) == 2_567_463_684          # the released SDXL-base denoiser
+    tiny = json.load(open(os.path.join(root, "examples/sdxl/pretrain_model_tiny.json")))
+    torch.manual_seed(0)
+    net = build_model("sdxl_unet", tiny["predictor"])
+    assert isinstance(net, SDXLUNet)
+    sched = build_scheduler(tiny["diffusion"])
+    assert abs(float(sched.betas[0]) - 0.00085) < 1e-9 and abs(float(sched.betas[-1]) - 0.012) < 1e-9
+    model = SoRAModel(net, sched, seed=0)
+    ids = compute_time_ids((64, 64), (0, 0), (64, 64))
+    added = torch.cat([torch.randn(2, 24), ids[None].expand(2, -1)], 1)
+    batch = dict(latents=torch.randn(2, 4, 1, 8, 8), prompt=torch.randn(2, 5, 48), added_cond=added)
+    loss = model(batch)
+    assert loss.dim() == 0 and torch.isfinite(loss)
+    loss.backward()
+    assert all(p.grad is not None for p in net.parameters())
+    # the size conditioning is live: another crop offset changes the prediction
+    x, t = torch.randn(1, 4, 8, 8), torch.tensor([500])
+    a0 = torch.cat([torch.zeros(1, 24), compute_time_ids((64, 64), (0, 0), (64, 64))[None]], 1)
+    a1 = torch.cat([torch.zeros(1, 24), compute_time_ids((64, 64), (16, 0), (64, 64))[None]], 1)
+    p = torch.randn(1, 5, 48)
+    assert (net(x, t, p, a0) - net(x, t, p, a1)).abs().max() > 0

@@ -83,6 +83,8 @@ class ComposableConfig:
     vision_start_token_id: int = 151652
     audio_token_id: int = 151646
     init_std: float = 0.02
+    tile_format: bool = False                   # any-resolution tiles: line-break and view-separator embeddings
+    global_view_pos: str = "head"               # head | tail: where the global view sits relative to the local grid
 
 
 # ------------------------------------------------------------------------------------------ blocks
@@ -293,6 +295,40 @@ class PlainViT(nn.Module):
         return self.merger_fc2(F.gelu(self.merger_fc1(x)))
 
 
+class TileFormatter(nn.Module):
+    """Lays the per-view features of any-resolution images out as the prompt expects them: the global view row by row
+    with a learned line-break vector after every row, a learned separator, then the local views stitched into one
+    ``(tiles_h * h) x (tiles_w * w)`` map, again with a line break per row (reference:
+    mindspeed_mm/models/deepseekvl_model.py:313-428, ``tile_tag == "2D"``).  ``data/anyres.py`` emits the placeholder
+    tokens in the same order."""
+
+    def __init__(self, dim: int, global_view_pos: str = "head"):
+        super().__init__()
+        self.image_newline = nn.Parameter(torch.empty(dim))
+        self.view_separator = nn.Parameter(torch.empty(dim))
+        self.global_view_pos = global_view_pos
+
+    def forward(self, feats, spatial_crop):
+        """feats [n_views * h * w, D] (views of all images in order: global, then local row-major);
+        spatial_crop [n_images, 2] = (tiles_w, tiles_h).  -> [sum of image_token_count, D]."""
+        crops = spatial_crop.tolist()
+        n_views = sum(1 + tw * th for tw, th in crops)
+        D = feats.shape[-1]
+        hw = feats.shape[0] // max(n_views, 1)
+        h = w = int(round(hw ** 0.5))
+        f = feats.view(n_views, h, w, D)
+        nl = self.image_newline.to(feats.dtype)
+        sep = self.view_separator.to(feats.dtype)[None]
+        out, at = [], 0
+        for tw, th in crops:
+            g = torch.cat([f[at], nl.expand(h, 1, D)], 1).reshape(-1, D)
+            loc = f[at + 1: at + 1 + tw * th].view(th, tw, h, w, D).permute(0, 2, 1, 3, 4).reshape(th * h, tw * w, D)
+            loc = torch.cat([loc, nl.expand(th * h, 1, D)], 1).reshape(-1, D)
+            out += [g, sep, loc] if self.global_view_pos == "head" else [loc, sep, g]
+            at += 1 + tw * th
+        return torch.cat(out)
+
+
 class AudioTower(nn.Module):
     def __init__(self, c: WhisperConfig, window: int, out_dim: int):
         super().__init__()
@@ -320,6 +356,7 @@ class ComposableLM(Qwen25VLModel):
         elif config.vision_kind == "vit":
             self.visual = PlainViT(config.vit)
         self.audio = AudioTower(config.audio, config.audio_window, t.hidden_size) if config.audio is not None else None
+        self.tile_format = TileFormatter(t.hidden_size, config.global_view_pos) if config.tile_format else None
         self.embed_tokens = Embedding(t.vocab_size, t.hidden_size)
         self.layers = nn.ModuleList(ComposableLayer(t, m, f, t.num_experts // ep_size if f == "moe" else None)
                                     for m, f in zip(mixers, ffns))
@@ -335,6 +372,10 @@ class ComposableLM(Qwen25VLModel):
                 m.post_init()
             if isinstance(m, ScaledRMSNorm):
                 m.weight.zero_()
+            if isinstance(m, TileFormatter):
+                g = torch.Generator(device="cpu").manual_seed(seed + 17)
+                for p in (m.image_newline, m.view_separator):
+                    p.copy_(torch.randn(p.shape, generator=g) * self.config.init_std)
 
     def fsdp_units(self) -> List[Tuple[str, nn.Module]]:
         units: List[Tuple[str, nn.Module]] = [("embed_tokens", self.embed_tokens)]
@@ -344,6 +385,8 @@ class ComposableLM(Qwen25VLModel):
             units += [("visual.merger", self.visual.merger)]
         elif self.visual is not None:
             units += [("visual", self.visual)]
+        if self.tile_format is not None:
+            units += [("tile_format", self.tile_format)]
         if self.audio is not None:
             units += [("audio", self.audio)]
         units += [(f"layers.{i}", l) for i, l in enumerate(self.layers)]
@@ -380,6 +423,8 @@ class ComposableLM(Qwen25VLModel):
                 v = run(vis.merger, v).index_select(0, plan["reverse"])
             else:
                 v = run(self.visual, pv.to(x.dtype), batch["image_grid_thw"])
+            if self.tile_format is not None and batch.get("spatial_crop") is not None:
+                v = run(self.tile_format, v, batch["spatial_crop"])
             pos = batch.get("image_positions")
             if pos is None:
                 pos = (ids == cfg.image_token_id).nonzero(as_tuple=True)[0]
@@ -457,7 +502,7 @@ PRESETS: Dict[str, ComposableConfig] = {
     # LLaVA-style assembly (plain ViT + projector + dense decoder) and DeepSeek-VL2 (plain ViT + MLA attention + routed experts)
     "llava": ComposableConfig(_tiny_text(rope="rope1d"), "vit", vit=_tiny_vit(128), **_IDS),
     "deepseekvl2": ComposableConfig(_tiny_text(rope="rope1d", mixers=("mla", "mla"), ffns=("dense", "moe"),
-                                               shared_expert_intermediate_size=64), "vit", vit=_tiny_vit(128), **_IDS),
+                                               shared_expert_intermediate_size=64), "vit", vit=_tiny_vit(128), tile_format=True, **_IDS),
     "longcat_next": ComposableConfig(_tiny_text(rope="rope1d", mixers=("mla", "mla"), ffns=("moe", "moe")), "vit",
                                      vit=_tiny_vit(128), **_IDS),
 }

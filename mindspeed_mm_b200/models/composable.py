@@ -442,11 +442,27 @@ class ComposableLM(Qwen25VLModel):
             p1 = pos_ids[0] if pos_ids.dim() == 2 else pos_ids
             cos, sin = ops.ref.mrope_cos_sin(p1[None].expand(3, -1), rope_dim, t.rope_theta, (rope_dim // 2, 0, 0))
         cos, sin = cos.to(x.dtype), sin.to(x.dtype)
+        trace = batch.get("collect_hidden")       # a list: receives the embeddings and every layer's output
+        if trace is not None:
+            trace.append(x)
         for layer in self.layers:
             x = run(layer, x, cos, sin, batch["cu_seqlens"], batch["max_seqlen"])
+            if trace is not None:
+                trace.append(x)
         if batch.get("return_hidden"):
             return x                              # pre-norm hidden states [T, H]
         return run(self.lm_head, x, batch.get("labels"))
+
+
+    def hidden_states(self, batch: dict, run=None) -> List[torch.Tensor]:
+        """Embeddings followed by the output of every layer (pre final norm), each [T, H]: what prompt encoders that read
+        an inner layer of a language model need."""
+        trace: List[torch.Tensor] = []
+        self.forward({**batch, "collect_hidden": trace, "return_hidden": True}, run=run)
+        return trace
+
+    def final_norm(self, h):
+        return self.lm_head.norm(h)
 
 
 # ------------------------------------------------------------------------------------------ presets

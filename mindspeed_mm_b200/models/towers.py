@@ -87,6 +87,20 @@ def _one_text_encoder(block: dict):
     mid = str(block.get("model_id", "UMT5")).lower()
     src = block.get("from_pretrained")
     have = bool(src) and os.path.exists(src)
+    if "glyph" in mid or "byt5" in mid:
+        # byte-level T5 over the quoted spans of the prompt (mindspeed_mm/models/text_encoder/hunyuan15_glyph_text_encoder.py)
+        from .prompt_encoders import ByteTokenizer, GlyphByT5Encoder, GlyphEncoderConfig
+        from .registry import config_from_dict
+        cfg = config_from_dict(GlyphEncoderConfig, {k: v for k, v in block.items() if k not in ("model_id", "from_pretrained")})
+        return GlyphByT5Encoder(cfg, ByteTokenizer())
+    if "mllm" in mid:
+        # decoder-only LM read at an inner layer behind an instruction template
+        # (mindspeed_mm/models/text_encoder/hunyuan15_mllm_text_encoder.py:63-121)
+        from .prompt_encoders import TEMPLATES, DecoderPromptEncoder
+        from .registry import build_model
+        lm = build_model(block.get("lm_model_id", "llava"), block.get("lm_config"))
+        tpl = block.get("template") or TEMPLATES.get(block.get("template_id", "encode-video"))
+        return DecoderPromptEncoder(lm, tpl, int(block.get("hidden_state_skip_layer", 2)), bool(block.get("apply_final_norm", False)))
     if "t5" in mid:
         cfg = T5Config(**{k: block[k] for k in ("vocab_size", "d_model", "d_kv", "d_ff", "num_layers", "num_heads",
                                                 "num_buckets", "max_distance") if k in block},

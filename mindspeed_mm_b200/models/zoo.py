@@ -12,3 +12,4 @@ from . import speech_lm  # noqa: F401
 from . import video_dits  # noqa: F401
 from . import omni  # noqa: F401
 from . import sdxl_unet  # noqa: F401
+from . import prompt_encoders  # noqa: F401

@@ -134,3 +134,14 @@ class BucketBatchSampler(_Resumable):
 
 SAMPLERS = {"BaseRandomBatchSampler": BaseRandomBatchSampler, "LengthGroupedSampler": LengthGroupedSampler,
             "BucketBatchSampler": BucketBatchSampler, "StatefulDistributedSampler": StatefulDistributedSampler}
+
+
+def _late():
+    """The bucketed-video, padded and grouped-length samplers live in ``video_buckets.py``; listed here under the names the
+    recipes use (``sampler_type``)."""
+    from .video_buckets import GroupedLengthSampler, PaddedDistributedSampler, VariableVideoBatchSampler
+    SAMPLERS.update({"VariableVideoBatchSampler": VariableVideoBatchSampler, "AESampler": PaddedDistributedSampler,
+                     "LuminaMetaLenDistSampler": GroupedLengthSampler})
+
+
+_late()

@@ -1,6 +1,6 @@
 """Per-kernel timing on one GPU: CUDA events, >=3 warm-ups, L2 flushed between timed iterations.
 
-    python benchmarks/bench_ops.py [--ops gemm,rmsnorm,...] [--out FILE] [--small]
+    python benchmarks/bench_ops.py [--ops gemm,gemm_swiglu,elementwise,fmha,gdn] [--out FILE] [--small]
 
 Prints one JSON line per case: achieved TFLOP/s or GB/s and the fraction of the measured peaks in
 MEASURED_PEAKS.json (fallback 1590 TFLOP/s / 6650 GB/s when the file is absent).  ``--small`` keeps
@@ -79,6 +79,25 @@ def bench_gemm(out, small):
                       tflops=round(flops / t / 1e9, 1), frac_of_peak=round(flops / t / 1e9 / tf, 3), peak=src,
                       cublas_ms=round(tl, 4), cublas_tflops=round(flops / tl / 1e9, 1),
                       vs_cublas=round(tl / t, 3)), out)
+        native.check_status()
+
+
+def bench_gemm_swiglu(out, small):
+    """gate/up projection + SwiGLU: one kernel with the activation as the epilogue against GEMM followed by the activation
+    kernel (the decoder MLP of Qwen2.5-VL-7B, and the ViT-sized one)."""
+    tf, _, src = peaks()
+    shapes = [("llm_mlp", 8192, 18944, 3584)] if small else [("llm_mlp", 8192, 18944, 3584), ("mlp_5120", 8192, 13824, 5120)]
+    for name, M, F, K in shapes:
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = (torch.randn(2 * F, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+        flops = 4.0 * M * F * K
+        with torch.no_grad():
+            t_f = time_fn(lambda: native.gemm_swiglu(x, w))
+            t_u = time_fn(lambda: native.swiglu(native.gemm_nt(x, w)))
+            t_l = time_fn(lambda: native.swiglu(x @ w.t()))
+        emit(dict(op="gemm_swiglu_bf16", case=name, M=M, F=F, K=K, fused_ms=round(t_f, 4),
+                  fused_tflops=round(flops / t_f / 1e9, 1), frac_of_peak=round(flops / t_f / 1e9 / tf, 3), peak=src,
+                  gemm_then_act_ms=round(t_u, 4), cublas_then_act_ms=round(t_l, 4), vs_two_kernels=round(t_u / t_f, 3)), out)
         native.check_status()
 
 
@@ -199,7 +218,7 @@ def main():
     ap.add_argument("--small", action="store_true")
     a = ap.parse_args()
     for op in a.ops.split(","):
-        {"gemm": bench_gemm, "elementwise": bench_elementwise, "fmha": bench_fmha, "gdn": bench_gdn}[op](a.out, a.small)
+        {"gemm": bench_gemm, "gemm_swiglu": bench_gemm_swiglu, "elementwise": bench_elementwise, "fmha": bench_fmha, "gdn": bench_gdn}[op](a.out, a.small)
 
 
 if __name__ == "__main__":

@@ -153,7 +153,13 @@ def linear(x, weight, bias=None, value_unused_in_backward: bool = False):
 
 
 def linear_swiglu(x, weight_gate_up):
-    """``swiglu(x @ W_gate_up.T)`` with the activation folded into the GEMM epilogue on the native tier."""
+    """``swiglu(x @ W_gate_up.T)``.  On the native tier a pass that keeps no graph (the first forward of a recomputed
+    unit, inference) runs one kernel with the activation as the GEMM epilogue; a pass that will be differentiated keeps
+    the pre-activation for the backward and runs GEMM and activation kernels."""
+    if _native(x) and x.dtype == torch.bfloat16 and \
+            not (torch.is_grad_enabled() and (x.requires_grad or weight_gate_up.requires_grad)) and \
+            _nat().gemm_swiglu_supported(x, weight_gate_up):
+        return _nat().gemm_swiglu(x, weight_gate_up)
     return swiglu(linear(x, weight_gate_up))
 
 

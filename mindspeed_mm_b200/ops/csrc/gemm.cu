@@ -70,7 +70,10 @@ __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks
     nb = r / gm;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+// SWIGLU (BN = 256, K-major operands, no bias): B is the fused [2F, K] gate/up weight, p.N = F.  A tile's accumulator holds
+// 128 gate columns (weight rows nb*128 ..) next to the 128 up columns of the same features (rows F + nb*128 ..); the
+// epilogue writes silu(gate) * up, so the [M, 2F] pre-activation never reaches memory.
+template <int BN, bool A_MN, bool B_MN, bool SWIGLU = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ TMapSet tmC, Params p) {
@@ -91,7 +94,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int m_blocks = (p.M + BM - 1) / BM;
-    const int n_blocks = (p.N + BN - 1) / BN;
+    const int n_blocks = SWIGLU ? p.N / 128 : (p.N + BN - 1) / BN;
     const int n_tiles = m_blocks * n_blocks;
     const int k_blocks = (p.K + BK - 1) / BK;
 
@@ -144,7 +147,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         for (int j = 0; j < BM / 64; ++j)
                             tma_load_2d(a + j * (BK * 128), &tmA, &full[stage], mb * BM + j * 64, kb * BK);
                     }
-                    if constexpr (!B_MN) {
+                    if constexpr (SWIGLU) {
+                        tma_load_2d(b, &tmB, &full[stage], kb * BK, nb * 128);
+                        tma_load_2d(b + 128 * 128, &tmB, &full[stage], kb * BK, p.N + nb * 128);
+                    } else if constexpr (!B_MN) {
                         tma_load_2d(b, &tmB, &full[stage], kb * BK, nb * BN);
                     } else {
 #pragma unroll
@@ -221,17 +227,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (*epi_stop) break;
             fence_after_sync();
             const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+            constexpr int kSlabs = SWIGLU ? 2 : BN / 64;
 #pragma unroll 1
-            for (int slab = 0; slab < BN / 64; ++slab, ++slab_count) {
+            for (int slab = 0; slab < kSlabs; ++slab, ++slab_count) {
                 uint8_t* buf = sC + (slab_count & 1) * (BM * 128);
                 if (issuer) tma_wait_read<1>();  // the store that last read this buffer has drained
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 uint32_t r[64];
-                tmem_ld_32x32(t_row + slab * 64, r);
-                tmem_ld_32x32(t_row + slab * 64 + 32, r + 32);
-                tmem_wait_ld();
-                const int n0 = nb * BN + slab * 64;
-                if (p.bias != nullptr) {
+                if constexpr (SWIGLU) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t u[32];
+                        tmem_ld_32x32(t_row + slab * 64 + h * 32, r + h * 32);
+                        tmem_ld_32x32(t_row + 128 + slab * 64 + h * 32, u);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) {
+                            const float g = __uint_as_float(r[h * 32 + c]);
+                            r[h * 32 + c] = __float_as_uint(__fdividef(g, 1.f + __expf(-g)) * __uint_as_float(u[c]));
+                        }
+                    }
+                } else {
+                    tmem_ld_32x32(t_row + slab * 64, r);
+                    tmem_ld_32x32(t_row + slab * 64 + 32, r + 32);
+                    tmem_wait_ld();
+                }
+                const int n0 = (SWIGLU ? nb * 128 : nb * BN) + slab * 64;
+                if (!SWIGLU && p.bias != nullptr) {
 #pragma unroll
                     for (int c = 0; c < 64; ++c) {
                         const int n = n0 + c;
@@ -292,7 +314,7 @@ struct Route {
     long long dst_rows = 0, dst_cols = 0;
 };
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool SWIGLU = false>
 int launch(const void* A, const void* B, void* Cc, const void* bias, int M, int N, int K, long long lda, long long ldb,
            long long ldc, int* status, cudaStream_t st, const Route& rt = Route()) {
     using C = Cfg<BN>;
@@ -302,7 +324,10 @@ int launch(const void* A, const void* B, void* Cc, const void* bias, int M, int 
     // A_MN: memory is [K, M] -> rows=K, cols=M, box = 64 k-rows x 64 m ;  else rows=M, cols=K, box = 128 x 64
     r = A_MN ? make_tmap_2d(&tA, A, K, M, lda, BK, 64) : make_tmap_2d(&tA, A, M, K, lda, BM, BK);
     if (r) return 1000 + r;
-    r = B_MN ? make_tmap_2d(&tB, B, K, N, ldb, BK, 64) : make_tmap_2d(&tB, B, N, K, ldb, BN, BK);
+    if (SWIGLU)
+        r = make_tmap_2d(&tB, B, 2LL * N, K, ldb, 128, BK);      // gate and up halves are fetched as two 128-row boxes
+    else
+        r = B_MN ? make_tmap_2d(&tB, B, K, N, ldb, BK, 64) : make_tmap_2d(&tB, B, N, K, ldb, BN, BK);
     if (r) return 2000 + r;
     if (rt.mode == 0) {
         r = make_tmap_2d(&tC.m[0], Cc, M, N, ldc, BM, 64);
@@ -314,14 +339,14 @@ int launch(const void* A, const void* B, void* Cc, const void* bias, int M, int 
             if (r) return 3000 + r;
         }
     }
-    auto kern = gemm_kernel<BN, A_MN, B_MN>;
+    auto kern = gemm_kernel<BN, A_MN, B_MN, SWIGLU>;
     static bool done = false;
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
-    const int m_blocks = (M + BM - 1) / BM, n_blocks = (N + BN - 1) / BN;
+    const int m_blocks = (M + BM - 1) / BM, n_blocks = SWIGLU ? N / 128 : (N + BN - 1) / BN;
     static int sms = 0;
     if (!sms) {
         int dev = 0;
@@ -354,6 +379,16 @@ MM_API int mm_gemm_bf16(const void* A, const void* B, void* C, const void* bias,
     }
     MM_DISPATCH(256)
 #undef MM_DISPATCH
+}
+
+
+// C[M, F] = silu(A W_gate^T) * (A W_up^T) with W = [W_gate; W_up] stored as one [2F, K] matrix.  F % 128 == 0.
+MM_API int mm_gemm_swiglu_bf16(const void* A, const void* W, void* C, int M, int F, int K, long long lda, long long ldw,
+                               long long ldc, int* status, cudaStream_t st) {
+    if ((lda | ldw | ldc) % 8) return -1;
+    if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)C) & 15) return -2;
+    if (M <= 0 || F <= 0 || K <= 0 || F % 128) return -3;
+    return launch<256, false, false, true>(A, W, C, nullptr, M, F, K, lda, ldw, ldc, status, st);
 }
 
 

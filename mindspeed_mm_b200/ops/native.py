@@ -53,6 +53,7 @@ def _declare(L):
         "mm_gated_residual": [_p, _p, _p, _p, _ll, _i, _i, _p],
         "mm_adamw": [_p, _p, _p, _p, _i, _p, _ll, _ll, _f, _f, _f, _f, _f, _f, _f, _f, _p, _p],
         "mm_gemm_bf16": [_p, _p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _p, _p],
+        "mm_gemm_swiglu_bf16": [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _p, _p],
         "mm_ce_fwd_bwd": [_p, _ll, _p, _p, _i, _i, _i, _p],
         "mm_fmha_max_tiles": [_i, _i],
         "mm_fmha_set_fwd_variant": [_i],
@@ -365,6 +366,28 @@ def gemm_nt(a, b, bias=None, out=None):
         out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
     _gemm_raw(a, b, out, bias, M, N, K, a.stride(0), b.stride(0), out.stride(0), 0, 0)
     return out
+
+
+def gemm_swiglu_supported(x, w) -> bool:
+    return gemm_supported(x, w) and w.shape[0] % 256 == 0 and os.environ.get("MM_B200_GEMM_SWIGLU", "1") == "1"
+
+
+def gemm_swiglu(x, w):
+    """``silu(x W_gate^T) * (x W_up^T)`` for the fused ``w = [W_gate; W_up]`` ([2F, K]) in one kernel: the activation is the
+    GEMM epilogue and the [T, 2F] pre-activation is never written.  No autograd: for passes that keep no graph."""
+    shape = x.shape
+    a = x.reshape(-1, shape[-1])
+    if not _ok2d(a):
+        a = a.contiguous()
+    if not _ok2d(w):
+        w = w.contiguous()
+    M, K = a.shape
+    F = w.shape[0] // 2
+    out = torch.empty(M, F, dtype=torch.bfloat16, device=a.device)
+    st = status_word(a.device)
+    _check(lib().mm_gemm_swiglu_bf16(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, F, K, a.stride(0), w.stride(0),
+                                     out.stride(0), st.data_ptr(), _st()), "gemm_swiglu_bf16")
+    return out.view(*shape[:-1], F)
 
 
 def gemm_nn(a, b, out=None):

@@ -18,12 +18,28 @@ import torch
 _LOGGER = None
 
 
+class _StdoutHandler(logging.StreamHandler):
+    """Writes to whatever ``sys.stdout`` is at the time of the record (redirections made after the logger was created,
+    e.g. by a launcher or a test harness, are honoured)."""
+
+    def __init__(self):
+        logging.Handler.__init__(self)
+
+    @property
+    def stream(self):
+        return sys.stdout
+
+    @stream.setter
+    def stream(self, _value):
+        pass
+
+
 def get_logger(name: str = "mm_b200") -> logging.Logger:
     global _LOGGER
     if _LOGGER is None:
         lg = logging.getLogger(name)
         if not lg.handlers:
-            h = logging.StreamHandler(sys.stdout)
+            h = _StdoutHandler()
             h.setFormatter(logging.Formatter("%(message)s"))
             lg.addHandler(h)
         lg.setLevel(os.environ.get("MM_B200_LOGLEVEL", "INFO"))

@@ -300,6 +300,65 @@ def test_fmha_backward_cross_attention_shapes():
     _close(v.grad, vr.grad, rtol=3e-2, atol=3e-2)
 
 
+@pytest.mark.parametrize("M,K,F", [(300, 512, 256), (1024, 3584, 2048), (4100, 1024, 1152)])
+def test_gemm_with_swiglu_epilogue_matches_reference(M, K, F):
+    """Passes without a graph run the GEMM with the activation as its epilogue; a differentiated pass gives the same values."""
+    from mindspeed_mm_b200.ops import native
+    torch.manual_seed(0)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = (torch.randn(2 * F, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    assert native.gemm_swiglu_supported(x, w)
+    with torch.no_grad():
+        fused = ops.linear_swiglu(x, w)
+    gu = x.float() @ w.float().t()
+    want = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    assert fused.shape == (M, F)
+    _close(fused, want)
+    xg = x.clone().requires_grad_()
+    two_kernel = ops.linear_swiglu(xg, w)
+    assert two_kernel.requires_grad
+    _close(fused, two_kernel, rtol=1e-2, atol=1e-2)
+    # 3-D input keeps its leading dims
+    with torch.no_grad():
+        assert ops.linear_swiglu(x.view(2, M // 2, K), w).shape == (2, M // 2, F)
+
+
+def test_sliding_tile_attention_on_native_kernels_matches_masked_reference():
+    """Block-sparse attention gathers the selected key blocks and runs the packed variable-length kernel; the oracle is a
+    dense fp32 softmax under the token-level mask built from the same block mask."""
+    from mindspeed_mm_b200.ops.sparse_attention import ssta_attention, sta_block_mask, tile_order
+    torch.manual_seed(0)
+    B, N, D = 1, 4, 128
+    canvas, tile, kernel, text = (2, 8, 8), (1, 4, 4), (1, 3, 1), 16
+    S = 2 * 8 * 8 + text
+    q, k, v = (torch.randn(B, S, N, D, device=DEV, dtype=torch.bfloat16) * 0.5 for _ in range(3))
+    q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
+    out, density = ssta_attention(q, k, v, canvas, tile, kernel=kernel, text_len=text, mode="sta")
+    assert 0 < density < 1
+    dy = torch.randn_like(out)
+    out.backward(dy)
+    # oracle
+    block = 16
+    tiles = (2, 2, 2)
+    n_img = 8
+    bm = torch.ones(n_img + 1, n_img + 1, dtype=torch.bool)
+    bm[:n_img, :n_img] = sta_block_mask(tiles, kernel)
+    perm = tile_order(canvas, tile)
+    blk_of = torch.empty(S, dtype=torch.long)
+    blk_of[perm] = torch.arange(n_img * block) // block
+    blk_of[n_img * block:] = n_img
+    tok_mask = bm[blk_of][:, blk_of].to(DEV)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    sc = torch.einsum("bqnd,bknd->bnqk", qr, kr) / math.sqrt(D)
+    sc = sc.masked_fill(~tok_mask, float("-inf"))
+    ref_out = torch.einsum("bnqk,bknd->bqnd", sc.softmax(-1), vr)
+    ref_out.backward(dy.float())
+    _close(out, ref_out)
+    _close(q.grad, qr.grad)
+    _close(k.grad, kr.grad)
+    _close(v.grad, vr.grad)
+
+
 @pytest.mark.parametrize("T,k,E,H,F", [(512, 2, 8, 256, 128), (4096, 8, 128, 2048, 768), (300, 4, 16, 512, 256)])
 def test_moe_experts_native_vs_reference(T, k, E, H, F):
     torch.manual_seed(0)

@@ -90,7 +90,10 @@ def test_composable_presets_cover_the_reference_zoo_and_train():
         m.init_weights(0)
         loss, n = m(_composable_batch(cfg))
         (loss / n).backward()
-        assert torch.isfinite(loss) and all(p.grad is not None for p in m.parameters()), mid
+        # the line-break / separator vectors of tiled images only take part when a batch carries tile grids
+        # (tests/test_anyres_cpu.py trains them)
+        assert torch.isfinite(loss) and all(p.grad is not None for n_, p in m.named_parameters()
+                                            if not n_.startswith("tile_format.")), mid
 
 
 def test_composable_from_hf_config_switches():

@@ -14,6 +14,7 @@ from torch.utils.data import DataLoader
 
 from .registry import data_register
 from . import synthetic  # noqa: F401  (registers the synthetic datasets)
+from . import anyres  # noqa: F401  (registers the tiled conversation dataset)
 
 
 class _StatefulIter:

@@ -178,3 +178,95 @@ def views_to_patch_rows(views: torch.Tensor, patch: int, merge: int = 2, tempora
     x = x.permute(0, 3, 6, 4, 7, 2, 1, 5, 8).reshape(n * gh * gw, C * temporal * patch * patch)
     grid = torch.tensor([[1, gh, gw]] * n, dtype=torch.long).view(-1, 3)
     return x, grid
+
+
+# ------------------------------------------------------------------------------------------------- dataset + collator
+class TiledConversationDataset(torch.utils.data.Dataset):
+    """ShareGPT / messages records with ``<image>`` tags -> tiled SFT samples (``build_sft_sample``).  Registered as
+    ``deepseekvl2`` (mindspeed_mm/data/datasets/deepseekvl2_dataset.py builds the same fields through the processor's
+    ``process_one``).  ``image_loader(path) -> PIL image or [3, H, W] tensor``."""
+
+    def __init__(self, dataset_param=None, model=None, *, files=None, dataset_dir: str = "", tokenizer=None,
+                 spec: AnyResSpec = None, cutoff_len: int = 4096, image_loader=None, bos_id: int = None, eos_id: int = None):
+        import os
+        from .multimodal import ByteTokenizer, _read_records
+        if dataset_param is not None:
+            basic = dict(getattr(dataset_param, "basic_parameters", None) or {})
+            files = files or basic.get("dataset") or basic.get("data_path")
+            dataset_dir = basic.get("dataset_dir", dataset_dir)
+            cutoff_len = int(basic.get("cutoff_len", cutoff_len))
+        files = [files] if isinstance(files, str) else list(files)
+        self.records = []
+        for f in files:
+            self.records += _read_records(f if os.path.isabs(f) or not dataset_dir else os.path.join(dataset_dir, f))
+        self.dir, self.cutoff = dataset_dir, cutoff_len
+        self.tok = tokenizer or ByteTokenizer()
+        cfg = getattr(model, "config", None)
+        if spec is None:
+            vit = getattr(cfg, "vit", None)
+            size = (vit.patch_size * vit.merge * 4) if vit is not None else 384
+            spec = AnyResSpec(image_size=size, patch_size=vit.patch_size if vit else 16, downsample_ratio=vit.merge if vit else 2,
+                              candidates=candidate_grid(size, 9), image_token_id=getattr(cfg, "image_token_id", 100003))
+        self.spec, self.bos_id, self.eos_id = spec, bos_id, eos_id
+        self.image_loader = image_loader or self._load
+
+    def _load(self, p: str):
+        import os
+        from PIL import Image
+        return Image.open(p if os.path.isabs(p) or not self.dir else os.path.join(self.dir, p))
+
+    def _encode(self, s: str) -> List[int]:
+        try:
+            return list(self.tok.encode(s, add_special_tokens=False))      # transformers tokenizers
+        except TypeError:
+            return list(self.tok.encode(s))
+
+    def __len__(self):
+        return len(self.records)
+
+    def __getitem__(self, i):
+        from .multimodal import normalise_messages
+        rec = self.records[i]
+        msgs = [m for m in normalise_messages(rec) if m["role"] != "system"]
+        turns = [(msgs[k]["content"], msgs[k + 1]["content"]) for k in range(0, len(msgs) - 1, 2)]
+        paths = rec.get("images") or ([rec["image"]] if rec.get("image") else [])
+        s = build_sft_sample(turns, [self.image_loader(p) for p in paths], self._encode, self.spec, self.bos_id, self.eos_id)
+        if s["input_ids"].numel() > self.cutoff:          # cut text only after the last image placeholder
+            last_img = int(s["images_seq_mask"].nonzero().max()) + 1 if s["images_seq_mask"].any() else 0
+            keep = max(self.cutoff, last_img)
+            for k in ("input_ids", "labels", "images_seq_mask"):
+                s[k] = s[k][:keep]
+        return s
+
+
+def _register():
+    from .registry import data_register
+    data_register.register("deepseekvl2")(TiledConversationDataset)
+
+
+_register()
+
+
+class TiledPackCollator:
+    """Packs tiled samples into one token stream for the composable model: shifted labels, per-sample positions,
+    ``cu_seqlens``, the ViT patch rows of every view and the tile grid of every image."""
+
+    def __init__(self, patch: int, merge: int = 2, temporal: int = 1, ignore_id: int = -100):
+        self.patch, self.merge, self.temporal, self.ignore = patch, merge, temporal, ignore_id
+
+    def __call__(self, samples: Sequence[dict]) -> dict:
+        ids, labels, pos, lens, views, crops = [], [], [], [], [], []
+        for s in samples:
+            n = s["input_ids"].numel()
+            ids.append(s["input_ids"])
+            lab = torch.full((n,), self.ignore, dtype=torch.long)
+            lab[:-1] = s["labels"][1:]                                  # next-token targets inside the sample
+            labels.append(lab)
+            pos.append(torch.arange(n))
+            lens.append(n)
+            views.append(s["views"])
+            crops.append(s["spatial_crop"])
+        rows, grid = views_to_patch_rows(torch.cat(views), self.patch, self.merge, self.temporal)
+        cu = torch.tensor([0] + lens, dtype=torch.int32).cumsum(0).to(torch.int32)
+        return dict(input_ids=torch.cat(ids), labels=torch.cat(labels), position_ids=torch.cat(pos), cu_seqlens=cu,
+                    max_seqlen=max(lens), pixel_values=rows, image_grid_thw=grid, spatial_crop=torch.cat(crops))

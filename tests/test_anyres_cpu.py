@@ -92,3 +92,42 @@ def test_tile_formatter_layout_and_model_step():
     assert torch.isfinite(loss)
     loss.backward()
     assert model.tile_format.image_newline.grad.abs().sum() > 0 and model.tile_format.view_separator.grad.abs().sum() > 0
+
+
+def test_tiled_dataset_and_pack_collator_feed_the_model(tmp_path):
+    import json
+    from mindspeed_mm_b200.data.anyres import TiledConversationDataset, TiledPackCollator
+    from mindspeed_mm_b200.data.registry import data_register
+    from mindspeed_mm_b200.models.composable import PRESETS, ComposableLM
+    assert data_register.get("deepseekvl2") is TiledConversationDataset
+    recs = [{"conversations": [{"from": "human", "value": "<image>\nwhat is this?"}, {"from": "gpt", "value": "a chart"}],
+             "images": ["a.png"]},
+            {"messages": [{"role": "user", "content": "hello"}, {"role": "assistant", "content": "hi there"}]}]
+    (tmp_path / "d.json").write_text(json.dumps(recs))
+    cfg = PRESETS["deepseekvl2"]
+    torch.manual_seed(0)
+    model = ComposableLM(cfg)
+    with torch.no_grad():
+        model.init_weights(0)
+
+    class Tok:                                       # ids stay clear of the special ids at the top of the tiny vocabulary
+        def encode(self, s):
+            return [3 + ord(c) % 200 for c in s]
+
+    ds = TiledConversationDataset(files=str(tmp_path / "d.json"), model=model, tokenizer=Tok(),
+                                  image_loader=lambda p: torch.rand(3, 50, 120), bos_id=1, eos_id=2)
+    assert len(ds) == 2
+    a, b = ds[0], ds[1]
+    assert a["spatial_crop"].shape == (1, 2) and b["spatial_crop"].shape == (0, 2) and b["views"].shape[0] == 0
+    n_img = int(a["images_seq_mask"].sum())
+    assert n_img == anyres.image_token_count(ds.spec, *a["spatial_crop"][0].tolist())
+    batch = TiledPackCollator(cfg.vit.patch_size, cfg.vit.merge, cfg.vit.temporal_patch_size)([a, b])
+    T = a["input_ids"].numel() + b["input_ids"].numel()
+    assert batch["input_ids"].numel() == T and batch["cu_seqlens"].tolist() == [0, a["input_ids"].numel(), T]
+    assert batch["labels"][a["input_ids"].numel() - 1] == -100            # no target crosses the sample boundary
+    assert int((batch["labels"] != -100).sum()) == len("a chart") + 1 + len("hi there") + 1
+    out = model(batch)
+    loss = out[0] / out[1] if isinstance(out, tuple) else out
+    assert torch.isfinite(loss)
+    loss.backward()
+    assert model.tile_format.image_newline.grad.abs().sum() > 0

@@ -306,3 +306,98 @@ class GlyphByT5Encoder(nn.Module):
         pairs = [self.tokenize(p, **kw) for p in prompts]
         dev = self.t5.embed.weight.device
         return self.encode(torch.cat([p[0] for p in pairs]).to(dev), torch.cat([p[1] for p in pairs]).to(dev))
+
+
+# ------------------------------------------------------------------------------------------------ StepVideo text encoder
+def alibi_slopes(n_heads: int) -> torch.Tensor:
+    """Geometric slopes 2^(-8 i / n) for the largest power of two n <= heads, the rest interleaved from the 2n series."""
+    import math
+    n = 2 ** math.floor(math.log2(n_heads))
+    s = torch.pow(torch.tensor(2.0 ** (-8.0 / n)), torch.arange(1, n + 1, dtype=torch.float32))
+    if n < n_heads:
+        extra = torch.pow(torch.tensor(2.0 ** (-4.0 / n)), torch.arange(1, 1 + 2 * (n_heads - n), 2, dtype=torch.float32))
+        s = torch.cat([s, extra])
+    return s
+
+
+def sqrt_alibi_bias(seq_len: int, n_heads: int) -> torch.Tensor:
+    """[heads, L, L] additive causal bias: ``-slope_h * sqrt(i - j)`` for j <= i, -inf above the diagonal."""
+    i = torch.arange(seq_len)
+    dist = (i[:, None] - i[None, :]).clamp(min=0).float().sqrt()
+    bias = -dist[None] * alibi_slopes(n_heads).view(-1, 1, 1)
+    return bias.masked_fill(i[None, :] > i[:, None], float("-inf"))
+
+
+@dataclass
+class StepLLMConfig:
+    """Sizes come from the checkpoint's ``config.json`` (the reference reads them there too); the defaults only fix the
+    field names and a plausible shape."""
+    hidden_size: int = 6144
+    num_attention_heads: int = 48
+    num_attention_groups: int = 8
+    num_layers: int = 48
+    ffn_hidden_size: int = 16896
+    vocab_size: int = 65536
+    eps: float = 1e-5
+    ffn_multiple_of: int = 256
+
+    @classmethod
+    def tiny(cls, **kw):
+        return cls(**{**dict(hidden_size=96, num_attention_heads=6, num_attention_groups=2, num_layers=2, ffn_hidden_size=100,
+                             vocab_size=128, ffn_multiple_of=16), **kw})
+
+
+class _StepBlock(nn.Module):
+    def __init__(self, c: StepLLMConfig):
+        super().__init__()
+        self.h, self.g, self.d = c.num_attention_heads, c.num_attention_groups, c.hidden_size // c.num_attention_heads
+        ff = (c.ffn_hidden_size + c.ffn_multiple_of - 1) // c.ffn_multiple_of * c.ffn_multiple_of
+        self.attention_norm = nn.Parameter(torch.ones(c.hidden_size))
+        self.ffn_norm = nn.Parameter(torch.ones(c.hidden_size))
+        self.wqkv = nn.Linear(c.hidden_size, c.hidden_size + 2 * self.d * self.g, bias=False)
+        self.wo = nn.Linear(c.hidden_size, c.hidden_size, bias=False)
+        self.w1 = nn.Linear(c.hidden_size, 2 * ff, bias=False)
+        self.w2 = nn.Linear(ff, c.hidden_size, bias=False)
+        self.eps = c.eps
+
+    def forward(self, x, bias):
+        from .. import ops
+        B, L, H = x.shape
+        q, kv = self.wqkv(ops.rms_norm(x, self.attention_norm, self.eps)).split([H, 2 * self.d * self.g], -1)
+        k, v = kv.view(B, L, self.g, 2 * self.d).chunk(2, -1)
+        rep = self.h // self.g
+        q = q.view(B, L, self.h, self.d).transpose(1, 2)
+        k = k.repeat_interleave(rep, 2).transpose(1, 2)
+        v = v.repeat_interleave(rep, 2).transpose(1, 2)
+        a = torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=bias.to(q.dtype))
+        x = x + self.wo(a.transpose(1, 2).reshape(B, L, H))
+        g, u = self.w1(ops.rms_norm(x, self.ffn_norm, self.eps)).chunk(2, -1)
+        return x + self.w2(torch.nn.functional.silu(g) * u)
+
+
+@model_register.register("stepllm")
+class StepLLMEncoder(nn.Module):
+    """Decoder-only prompt encoder of StepVideo: no rotary or learned positions -- order comes from a causal bias that
+    grows with the square root of the distance -- grouped-query attention, SwiGLU feed-forward, RMSNorm; the output is the
+    last block's hidden state without a final norm (mindspeed_mm/models/text_encoder/stepllm_text_encoder.py:36-272)."""
+    config_class = StepLLMConfig
+
+    def __init__(self, config: StepLLMConfig = None):
+        super().__init__()
+        c = self.config = config or StepLLMConfig()
+        self.tok_embeddings = nn.Embedding(c.vocab_size, c.hidden_size)
+        self.layers = nn.ModuleList(_StepBlock(c) for _ in range(c.num_layers))
+        for p in self.parameters():
+            p.requires_grad_(False)
+
+    def forward(self, input_ids, attention_mask=None):
+        x = self.tok_embeddings(input_ids)
+        bias = sqrt_alibi_bias(input_ids.shape[1], self.config.num_attention_heads).to(x.device)[None]
+        for blk in self.layers:
+            x = blk(x, bias)
+        return x
+
+    @torch.no_grad()
+    def encode(self, input_ids, attention_mask=None):
+        h = self(input_ids, attention_mask)
+        return h, (attention_mask if attention_mask is not None else torch.ones_like(input_ids))

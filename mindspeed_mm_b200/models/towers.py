@@ -93,6 +93,10 @@ def _one_text_encoder(block: dict):
         from .registry import config_from_dict
         cfg = config_from_dict(GlyphEncoderConfig, {k: v for k, v in block.items() if k not in ("model_id", "from_pretrained")})
         return GlyphByT5Encoder(cfg, ByteTokenizer())
+    if "stepllm" in mid or "step_llm" in mid:
+        from .prompt_encoders import StepLLMConfig, StepLLMEncoder
+        from .registry import config_from_dict
+        return StepLLMEncoder(config_from_dict(StepLLMConfig, {k: v for k, v in block.items() if k not in ("model_id", "from_pretrained")}))
     if "mllm" in mid:
         # decoder-only LM read at an inner layer behind an instruction template
         # (mindspeed_mm/models/text_encoder/hunyuan15_mllm_text_encoder.py:63-121)

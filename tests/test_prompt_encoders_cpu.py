@@ -91,3 +91,32 @@ def test_text_encoder_builder_knows_both_branches():
     ids = [torch.randint(3, 100, (2, 10)), torch.randint(3, 100, (2, 24))]
     (h, m), (g, gm) = te.encode(ids, [torch.ones(2, 10, dtype=torch.long), torch.ones(2, 24, dtype=torch.long)])
     assert h.shape == (2, 8, 128) and m.shape == (2, 8) and g.shape == (2, 24, 32) and gm.shape == (2, 24)
+
+
+def test_stepllm_encoder_bias_and_causality():
+    s = pe.alibi_slopes(8)
+    assert torch.allclose(s, torch.tensor([2.0 ** -(i + 1) for i in range(8)]))
+    s6 = pe.alibi_slopes(6)                                          # 4 from the power-of-two series, 2 interleaved
+    assert s6.shape == (6,) and torch.allclose(s6[:4], torch.tensor([0.25, 0.0625, 0.015625, 0.00390625]))
+    assert torch.allclose(s6[4:], torch.tensor([0.5, 0.125]))
+    b = pe.sqrt_alibi_bias(5, 2)
+    assert b.shape == (2, 5, 5) and b[0, 0, 1] == float("-inf") and b[0, 2, 2] == 0
+    assert abs(float(b[0, 4, 0]) + float(pe.alibi_slopes(2)[0]) * 2.0) < 1e-6      # sqrt(4) = 2
+    from mindspeed_mm_b200.models.registry import build_model
+    torch.manual_seed(0)
+    m = build_model("stepllm", {"preset": "tiny"})
+    for p in m.parameters():
+        if p.dim() > 1:
+            torch.nn.init.normal_(p, std=0.1)
+    ids = torch.randint(0, 128, (2, 9))
+    h, mask = m.encode(ids)
+    assert h.shape == (2, 9, 96) and mask.shape == (2, 9)
+    ids2 = ids.clone()
+    ids2[:, 6:] = (ids2[:, 6:] + 1) % 128
+    h2, _ = m.encode(ids2)
+    assert torch.allclose(h[:, :6], h2[:, :6], atol=1e-6) and not torch.allclose(h[:, 6:], h2[:, 6:])
+    # without positions in the embeddings, order still matters through the bias
+    perm = torch.tensor([1, 0, 2, 3, 4, 5, 6, 7, 8])
+    assert not torch.allclose(m.encode(ids[:, perm])[0][:, 8], h[:, 8], atol=1e-5)
+    # feed-forward width is rounded up to the configured multiple
+    assert m.layers[0].w2.in_features == 112 and m.layers[0].wqkv.out_features == 96 + 2 * 16 * 2

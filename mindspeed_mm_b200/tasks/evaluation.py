@@ -50,16 +50,29 @@ def anls(pred: str, answers: List[str], threshold: float = 0.5) -> float:
     return best
 
 
+def _anls_any(pred: str, answer) -> float:
+    return anls(pred, list(answer) if isinstance(answer, (list, tuple)) else [answer])
+
+
 METRICS: Dict[str, Callable] = {"multiple_choice": multiple_choice_match, "exact_match": exact_match,
-                                "relaxed_accuracy": relaxed_accuracy}
+                                "relaxed_accuracy": relaxed_accuracy, "anls": _anls_any}
 
 
 def evaluate(predict: Callable[[dict], str], samples: Iterable[dict], metric: str = "exact_match") -> Dict[str, float]:
     fn = METRICS[metric]
-    hit = n = 0
+    hit, n = 0.0, 0
+    cats: Dict[str, List[float]] = {}
     for s in samples:
-        hit += int(fn(predict(s), s["answer"]))
+        score = float(fn(predict(s), s["answer"]))
+        hit += score
         n += 1
+        if "category" in s:
+            c = cats.setdefault(s["category"], [0.0, 0])
+            c[0] += score
+            c[1] += 1
+    if cats and not (dist.is_initialized() and dist.get_world_size() > 1):
+        per = {k: v[0] / v[1] for k, v in sorted(cats.items())}
+        return {"accuracy": hit / max(n, 1), "n": n, "per_category": per}
     t = torch.tensor([hit, n], dtype=torch.float64)
     if dist.is_initialized() and dist.get_world_size() > 1:
         if torch.cuda.is_available() and dist.get_backend() == "nccl":

@@ -16,6 +16,7 @@ import torch
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from mindspeed_mm_b200 import ops  # noqa: E402
 from mindspeed_mm_b200.ops import native  # noqa: E402
+from mindspeed_mm_b200.ops import reference as ref  # noqa: E402
 
 
 def peaks():
@@ -134,6 +135,49 @@ def bench_elementwise(out, small):
     g = torch.randn(n, device="cuda", dtype=torch.bfloat16)
     p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
     rec("adamw_shard", lambda: native.adamw_shard(p, m, v, g, p16, 1e-4, 0.9, 0.999, 1e-8, 0.0, 1, n, 1.0), n * 28.0)
+    # DiT-side ops: adaLN modulate and gated residual on [B, S, H] with per-sample [B, 1, H] vectors; rotary on [T, N, D]
+    Hd = 5120
+    xd = torch.randn(1, T, Hd, device="cuda", dtype=torch.bfloat16)
+    sc, sh, gt = (torch.randn(1, 1, Hd, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+    yd = torch.randn_like(xd)
+    rec("layer_norm_modulate", lambda: ops.layer_norm_modulate(xd, sc, sh, 1e-6), 2 * xd.numel() * 2,
+        lambda: ref.layer_norm_modulate(xd, sc, sh, 1e-6))
+    rec("gated_residual", lambda: ops.gated_residual(xd, yd, gt), 3 * xd.numel() * 2, lambda: ref.gated_residual(xd, yd, gt))
+    q = torch.randn(T, 28, 128, device="cuda", dtype=torch.bfloat16)
+    ang = torch.randn(T, 64, device="cuda")
+    cos, sin = torch.cat([ang.cos()] * 2, -1).to(torch.bfloat16), torch.cat([ang.sin()] * 2, -1).to(torch.bfloat16)
+    rec("rope_rotate_half", lambda: ops.rope_rotate_half(q, cos, sin), 2 * q.numel() * 2, lambda: ref.rope_rotate_half(q, cos, sin))
+
+
+def bench_lce(out, small):
+    """Fused final projection + cross entropy, forward and backward, against materialised logits."""
+    tf, _, src = peaks()
+    T, H, V = (4096, 3584, 32768) if small else (8192, 3584, 152064)
+    h = (torch.randn(T, H, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(V, H, device="cuda") * 0.02).to(torch.bfloat16).requires_grad_()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    ops.set_tier("native")
+
+    def mine():
+        loss, n = ops.linear_cross_entropy(h, w, labels)
+        torch.autograd.grad(loss / n, (h, w))
+
+    def plain():
+        loss = torch.nn.functional.cross_entropy((h @ w.t()).float(), labels)
+        torch.autograd.grad(loss, (h, w))
+
+    torch.cuda.reset_peak_memory_stats()
+    base = torch.cuda.memory_allocated()
+    t = time_fn(mine, iters=5)
+    mem = (torch.cuda.max_memory_allocated() - base) / 2 ** 30
+    torch.cuda.reset_peak_memory_stats()
+    tb = time_fn(plain, iters=5)
+    mem_b = (torch.cuda.max_memory_allocated() - base) / 2 ** 30
+    flops = 3 * 2.0 * T * H * V
+    emit(dict(op="linear_cross_entropy_fwd_bwd", T=T, H=H, V=V, ms=round(t, 3), tflops=round(flops / t / 1e9, 1),
+              frac_of_peak=round(flops / t / 1e9 / tf, 3), peak=src, extra_mem_gb=round(mem, 2), torch_ms=round(tb, 3),
+              torch_extra_mem_gb=round(mem_b, 2), vs_torch=round(tb / t, 2)), out)
+    native.check_status()
 
 
 def bench_fmha(out_file, small):
@@ -218,7 +262,7 @@ def main():
     ap.add_argument("--small", action="store_true")
     a = ap.parse_args()
     for op in a.ops.split(","):
-        {"gemm": bench_gemm, "gemm_swiglu": bench_gemm_swiglu, "elementwise": bench_elementwise, "fmha": bench_fmha, "gdn": bench_gdn}[op](a.out, a.small)
+        {"gemm": bench_gemm, "gemm_swiglu": bench_gemm_swiglu, "elementwise": bench_elementwise, "lce": bench_lce, "fmha": bench_fmha, "gdn": bench_gdn}[op](a.out, a.small)
 
 
 if __name__ == "__main__":

@@ -168,3 +168,31 @@ def parse_legacy_args(argv: Optional[Sequence[str]] = None, check_paths: bool = 
 def merge_mm_args(args) -> None:
     if not hasattr(args, "mm") or args.mm is None:
         args.mm = MMConfig({"model": args.mm_model, "data": args.mm_data, "tool": args.mm_tool})
+
+
+def load_fsdp2_config(path: str) -> dict:
+    """The separate sharding YAML of the Megatron-style FSDP2 recipes (``--use-torch-fsdp2 --fsdp2-config-path``; schema:
+    mindspeed_mm/models/transformers/base_model.py:220-283).  Returns the keys the engine uses, normalised:
+    ``sharding_size`` (int or None = all data ranks), ``param_dtype`` / ``reduce_dtype`` (torch dtypes or None),
+    ``reshard_after_forward`` (bool), ``recompute_modules`` / ``sub_modules_to_wrap`` (lists of patterns, kept for
+    reporting: the unit list comes from the model's ``fsdp_units()``), ``offload_to_cpu`` (bool)."""
+    import torch
+    import yaml
+    with open(path) as f:
+        raw = yaml.safe_load(f) or {}
+    dt = {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "fp16": torch.float16, "float16": torch.float16,
+          "fp32": torch.float32, "float32": torch.float32, None: None}
+    size = raw.get("sharding_size")
+    out = {
+        "sharding_size": None if size in (None, "auto", -1) else int(size),
+        "param_dtype": dt[raw.get("param_dtype")],
+        "reduce_dtype": dt[raw.get("reduce_dtype")],
+        "reshard_after_forward": bool(raw.get("reshard_after_forward", True)),
+        "sub_modules_to_wrap": list(raw.get("sub_modules_to_wrap") or []),
+        "recompute_modules": list(raw.get("recompute_modules") or []),
+        "offload_to_cpu": bool(raw.get("offload_to_cpu", False)),
+    }
+    unknown = sorted(set(raw) - set(out) - {"ignored_modules", "num_to_forward_prefetch", "num_to_backward_prefetch",
+                                           "output_dtype", "cast_forward_inputs"})
+    out["unknown_keys"] = unknown
+    return out

@@ -116,8 +116,22 @@ def pretrain(kind: str, argv=None, device: Optional[str] = None):
     opt = OptimConfig(lr=args.lr, betas=(args.adam_beta1, args.adam_beta2), eps=args.adam_eps,
                       weight_decay=args.weight_decay, clip_grad=args.clip_grad)
     accum = max(1, args.global_batch_size // (args.micro_batch_size * ps.get_dp_world_size()))
+    param_dtype = torch.bfloat16 if (args.bf16 and dev.type == "cuda") else torch.float32
+    extra = {}
+    if getattr(args, "fsdp2_config_path", None):
+        from ..config.legacy import load_fsdp2_config
+        f2 = load_fsdp2_config(args.fsdp2_config_path)
+        if f2["param_dtype"] is not None and dev.type == "cuda":
+            param_dtype = f2["param_dtype"]
+        if f2["reduce_dtype"] is not None:
+            extra["reduce_dtype"] = f2["reduce_dtype"]
+        if f2["sharding_size"] not in (None, world):
+            print_rank0(f"fsdp2 config asks for sharding_size={f2['sharding_size']}; sharding over the whole data-parallel group "
+                        f"({world} ranks) instead")
+        if f2["unknown_keys"]:
+            print_rank0(f"fsdp2 config keys without effect here: {f2['unknown_keys']}")
     engine = FSDPEngine(model.fsdp_units(), group=ps.get_fsdp_group() if world > 1 else False, device=dev,
-                        param_dtype=torch.bfloat16 if (args.bf16 and dev.type == "cuda") else torch.float32,
+                        param_dtype=param_dtype, **extra,
                         opt=opt, grad_accum_steps=accum, no_recompute=("lm_head",) if kind == "vlm" else ())
     std = getattr(getattr(model, "config", None), "init_std", 0.02)
     engine.materialize(stable_init_fn(std, args.seed))

@@ -73,6 +73,10 @@ def build_collator(args, model, pin: bool):
     cfg = getattr(model, "config", None)
     if hasattr(model, "collate"):                 # models with their own sequence layout (speech LMs) pack their samples
         return model.collate
+    if args.data.dataset_param.dataset_type == "deepseekvl2" or "deepseek" in name:
+        from .anyres import TiledPackCollator
+        vit = cfg.vit
+        return TiledPackCollator(vit.patch_size, vit.merge, vit.temporal_patch_size)
     if "qwen2" in name or "vl" in name or args.data.dataset_param.dataset_type == "synthetic_vlm":
         from .collate import PackedVLMCollator
         v = cfg.vision

@@ -131,3 +131,26 @@ def test_tiled_dataset_and_pack_collator_feed_the_model(tmp_path):
     assert torch.isfinite(loss)
     loss.backward()
     assert model.tile_format.image_newline.grad.abs().sum() > 0
+
+
+def test_trainer_runs_the_tiled_recipe(tmp_path, capsys):
+    import json
+    import os
+    from PIL import Image
+    from mindspeed_mm_b200.config import load_config
+    from mindspeed_mm_b200.runtime.trainer import Trainer
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    Image.new("RGB", (120, 50), (10, 200, 30)).save(tmp_path / "a.png")
+    recs = [{"messages": [{"role": "user", "content": "<image>\nwhat is this?"}, {"role": "assistant", "content": "a green card"}],
+             "images": ["a.png"]}] * 4
+    (tmp_path / "d.json").write_text(json.dumps(recs))
+    args = load_config(os.path.join(root, "examples/deepseekvl2/tiny_native.yaml"),
+                       [f"data.dataset_param.basic_parameters.dataset={tmp_path}/d.json",
+                        f"data.dataset_param.basic_parameters.dataset_dir={tmp_path}", "training.train_iters=2"], world_size=1)
+    hist = Trainer(args, device="cpu").train()
+    assert len(hist) == 2 and all(h["loss"] == h["loss"] for h in hist)
+    # the shipped text-only demo file runs as well
+    args = load_config(os.path.join(root, "examples/deepseekvl2/tiny_native.yaml"),
+                       [f"data.dataset_param.basic_parameters.dataset={root}/examples/deepseekvl2/demo.json", "training.train_iters=1"],
+                       world_size=1)
+    assert len(Trainer(args, device="cpu").train()) == 1

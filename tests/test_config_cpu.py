@@ -12,7 +12,9 @@ from mindspeed_mm_b200.config import (ConfigNode, MMConfig, load_config, module_
 from mindspeed_mm_b200.config.security import check_path
 from mindspeed_mm_b200.models.qwen2_5_vl import Qwen25VLConfig
 
-REF = "/root/reference/examples"
+# the reference's recipe folder: next to this repository unless MM_REFERENCE_EXAMPLES points elsewhere
+REF = os.environ.get("MM_REFERENCE_EXAMPLES") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference", "examples")
 HERE = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 

@@ -84,26 +84,11 @@ class ClockSampler(threading.Thread):
 
 
 def run_reference(args):
-    """The reference arm: the unmodified reference from baseline/_ref through its own public entry point."""
-    why = None
-    ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    if not os.path.isdir(os.path.join(ref_dir, "mindspeed_mm")):
-        why = "reference not installed under baseline/_ref (offline pip install did not produce the package)"
-    else:
-        sys.path.insert(0, ref_dir)
-        os.environ.setdefault("NON_MEGATRON", "true")
-        try:
-            import importlib
-            importlib.import_module("mindspeed_mm.fsdp.train.trainer")
-        except Exception as e:  # noqa: BLE001
-            why = ("reference trainer cannot be imported unmodified on this image: "
-                   f"{type(e).__name__}: {str(e).splitlines()[0][:160]}")
-        if why is None:
-            why = ("reference native-FSDP path refuses torch versions other than 2.7.1/2.9.0 "
-                   "(fsdp/ops/fully_shard/fully_shard.py:840-847); image has torch " + torch.__version__)
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
-    return 0
+    """The reference arm: the unmodified reference from baseline/_ref through its own native trainer
+    (``baseline/reference_arm.py``).  Nothing of this repository's package is imported on this path."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm
+    return reference_arm.run(args, ClockSampler)
 
 
 def make_batches(cfg, n_batches, seq_len, samples_per_pack, images_per_sample, image_size, rank, pin):

@@ -209,7 +209,7 @@ def run_wan(args):
                "peak_mem_gb": round(peak_gb, 1), "clocks": clocks,
                "e2e": {"value": round(1e3 / ms_e2e, 4), "unit": "samples/s", "ms_per_step": round(ms_e2e, 1),
                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": loss},
-               "gpu_launches": launches}
+               "gpu_launches": launches, "library_fallbacks": ops.library_fallbacks()}
         if alt is not None:
             out["memory_budgeted_recompute"] = alt
         print(json.dumps(out), flush=True)
@@ -248,7 +248,7 @@ def run_moe(args):
                        param_dtype=torch.bfloat16, opt=opt, exclude_params=ex, comm=args.comm)
     expert = FSDPEngine(model.expert_units(), group=False, device=dev, param_dtype=torch.bfloat16, opt=opt,
                         grad_divide=world, no_recompute=())
-    mux = EngineMux(dense, expert)
+    mux = EngineMux(dense, expert, ep_group=ps.group("ep") if world > 1 else None)
     mux.materialize(stable_init_fn(0.02, 0))
     seq = args.seq_len if not small else 512
     host = make_batches(cfg, 2, seq, 4 if not small else 1, 2 if not small else 1, 448 if not small else 224, rank, pin=True)
@@ -310,7 +310,7 @@ def run_moe(args):
                "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1), "clocks": clocks,
                "e2e": {"value": round(tokens_per_step / (ms_e2e / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 2),
                        "h2d_bytes_per_step": batch_nbytes(host[0]), "d2h_bytes_per_step": 4, "last_loss": loss},
-               "gpu_launches": launches}
+               "gpu_launches": launches, "library_fallbacks": ops.library_fallbacks()}
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()
@@ -449,6 +449,7 @@ def main():
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 2),
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": loss},
             "gpu_launches": launches,
+            "library_fallbacks": ops.library_fallbacks(),
         }
         if alt is not None:
             out["memory_budgeted_recompute"] = alt

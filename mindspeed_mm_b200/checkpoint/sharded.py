@@ -40,24 +40,45 @@ def write_tracker(root: str, iteration: int) -> None:
     os.replace(tmp, os.path.join(root, TRACKER))
 
 
+def _global_rank_world(engine):
+    if dist.is_initialized():
+        return dist.get_rank(), dist.get_world_size()
+    return engine.rank, engine.world
+
+
+def _sub_engines(engine):
+    """(tag, engine) pairs: one for a plain sharding engine, ``dense/`` + ``expert/`` for an ``EngineMux``."""
+    subs = getattr(engine, "engines", None)
+    if subs is None:
+        return [("", engine)]
+    return list(zip(("dense/", "expert/"), subs))
+
+
 class DistributedCheckpointer:
+    """One shard file per global rank.  A record of a flat group carries the rank / size of the sharding group it was
+    cut for (the dense engine shards over the FSDP group, an expert engine over the expert-FSDP group), so dense and
+    expert records of one file may belong to groups of different sizes."""
+
     def __init__(self, save_dir: Optional[str], load_dir: Optional[str] = None, save_async: bool = False,
-                 no_save_optim: bool = False, no_save_rng: bool = False, keep_last: int = 0):
+                 no_save_optim: bool = False, no_save_rng: bool = False, keep_last: int = 0,
+                 async_wait_s: float = 600.0):
         self.save_dir, self.load_dir = save_dir, load_dir or save_dir
         self.save_async, self.no_save_optim, self.no_save_rng, self.keep_last = \
             save_async, no_save_optim, no_save_rng, keep_last
+        self.async_wait_s = async_wait_s
         self._inflight: Optional[threading.Thread] = None
         self._error: Optional[BaseException] = None
 
     # ------------------------------------------------------------------ save
     def save(self, iteration: int, engine, extra_state: Optional[dict] = None) -> str:
         self.wait()
-        rank, world = engine.rank, engine.world
+        rank, world = _global_rank_world(engine)
         d = iter_dir(self.save_dir, iteration)
         os.makedirs(d, exist_ok=True)
         state = {}
         for key, s in engine.sharded_state().items():
-            rec = dict(shard16=s["shard16"].detach().cpu().clone(), step=s["step"], numel=s["numel"], world=world)
+            rec = dict(shard16=s["shard16"].detach().cpu().clone(), step=s["step"], numel=s["numel"],
+                       world=s["world"], rank=s.get("rank", 0))
             if s["master"] is not None:
                 rec["master"] = s["master"].detach().cpu().clone()
                 if not self.no_save_optim:
@@ -68,23 +89,42 @@ class DistributedCheckpointer:
         if self.no_save_rng:
             extra.pop("torch_rng", None)
             extra.pop("cuda_rng", None)
+        shard_name = f"shard_{rank:05d}_of_{world:05d}.pt"
+
+        def atomic_save(obj, path):
+            torch.save(obj, path + ".tmp")
+            os.replace(path + ".tmp", path)          # a file that exists is complete
 
         def write():
             try:
-                torch.save(state, os.path.join(d, f"shard_{rank:05d}_of_{world:05d}.pt"))
-                torch.save(extra, os.path.join(d, f"extra_state_{rank:05d}.pt"))
+                atomic_save(extra, os.path.join(d, f"extra_state_{rank:05d}.pt"))
                 if rank == 0:
                     with open(os.path.join(d, "meta.json"), "w") as f:
                         json.dump({"iteration": iteration, "world_size": world,
                                    "groups": {k: v["numel"] for k, v in state.items()}}, f)
+                atomic_save(state, os.path.join(d, shard_name))      # last: its presence means "this rank is done"
             except BaseException as e:  # noqa: BLE001
                 self._error = e
 
+        def all_written() -> bool:
+            import time
+            t0 = time.time()
+            want = [os.path.join(d, f"shard_{r:05d}_of_{world:05d}.pt") for r in range(world)]
+            while time.time() - t0 < self.async_wait_s:
+                if all(os.path.exists(w) for w in want):
+                    return True
+                time.sleep(0.05)
+            return False
+
         def finish():
             write()
-            # every rank must have written before the tracker moves
-            if dist.is_initialized() and world > 1 and not self.save_async:
-                dist.barrier(group=engine.group if engine.group else None)
+            # every rank must have written before the tracker moves: a collective barrier on the caller's thread for a
+            # synchronous save; a background save must not issue collectives, so rank 0 watches for the files instead
+            if world > 1:
+                if not self.save_async:
+                    dist.barrier()
+                elif rank == 0 and not all_written():
+                    self._error = self._error or TimeoutError(f"not every rank wrote its shard of {d}")
             if rank == 0 and self._error is None:
                 write_tracker(self.save_dir, iteration)
                 self._prune()
@@ -125,16 +165,17 @@ class DistributedCheckpointer:
         if iteration is None:
             return None
         d = iter_dir(root, iteration)
-        files = sorted(f for f in os.listdir(d) if f.startswith("shard_"))
+        files = sorted(f for f in os.listdir(d) if f.startswith("shard_") and f.endswith(".pt"))
         if not files:
             raise FileNotFoundError(f"no shard files in {d}")
+        rank, world = _global_rank_world(engine)
         old_world = int(files[0].split("_of_")[1].split(".")[0])
-        if old_world == engine.world:
-            st = torch.load(os.path.join(d, files[engine.rank]), map_location="cpu", weights_only=False)
-            self._apply(engine, st, load_optim)
+        if old_world == world:
+            st = torch.load(os.path.join(d, files[rank]), map_location="cpu", weights_only=False)
+            engine.load_sharded_state(st, load_optim=load_optim)
         else:
             self._load_resharded(engine, d, files, load_optim)
-        ex = os.path.join(d, f"extra_state_{engine.rank:05d}.pt")
+        ex = os.path.join(d, f"extra_state_{rank:05d}.pt")
         if not os.path.exists(ex):
             ex = os.path.join(d, "extra_state_00000.pt")
         extra = torch.load(ex, map_location="cpu", weights_only=False) if os.path.exists(ex) else {}
@@ -144,36 +185,37 @@ class DistributedCheckpointer:
         return extra
 
     @staticmethod
-    def _apply(engine, st: Dict[str, dict], load_optim: bool) -> None:
-        for u in engine.units:
-            for gi, g in enumerate(u.groups):
-                s = st[f"{u.name}#{gi}"]
-                g.shard16.copy_(s["shard16"])
-                if g.trainable:
-                    g.master.copy_(s.get("master", s["shard16"]))
-                    if load_optim and "exp_avg" in s:
-                        g.exp_avg.copy_(s["exp_avg"])
-                        g.exp_avg_sq.copy_(s["exp_avg_sq"])
-                        g.step_count = s["step"]
-
-    @staticmethod
     def _load_resharded(engine, d: str, files: List[str], load_optim: bool) -> None:
-        """Concatenate the old shards of each flat group and cut this rank's new slice out of them."""
+        """The job has a different number of ranks than the one that saved.  A group that was sharded over ALL ranks
+        (then and now) is rebuilt by concatenating the old slices in rank order and cutting this rank's new slice.
+        Groups sharded over a sub-group (experts under expert parallelism, tensor / pipeline parallel shards) hold
+        different parameters on different ranks, so they cannot be re-cut: that is refused."""
         olds = [torch.load(os.path.join(d, f), map_location="cpu", weights_only=False) for f in files]
-        for u in engine.units:
-            for gi, g in enumerate(u.groups):
-                key = f"{u.name}#{gi}"
+        _, world = _global_rank_world(engine)
+        for tag, e in _sub_engines(engine):
+            if e.world != world:
+                raise ValueError(f"checkpoint was written by {len(files)} ranks and the '{tag or 'model'}' parameters are "
+                                 f"sharded over a sub-group of {e.world}: reload with the original layout, or convert "
+                                 f"through the full (HF) format")
+            st = {}
+            for u in e.units:
+                for gi, g in enumerate(u.groups):
+                    key = f"{tag}{u.name}#{gi}"
+                    if any(o[key].get("world", len(files)) != len(files) for o in olds):
+                        raise ValueError(f"{key} was not sharded over all {len(files)} ranks of the saving job")
 
-                def rebuild(field):
-                    flat = torch.cat([o[key][field] for o in olds])[:g.numel]
-                    out = torch.zeros(g.padded, dtype=flat.dtype)
-                    out[:g.numel] = flat
-                    return out[g.rank * g.shard_numel:(g.rank + 1) * g.shard_numel]
+                    def rebuild(field, g=g, key=key):
+                        flat = torch.cat([o[key][field] for o in olds])[:g.numel]
+                        out = torch.zeros(g.padded, dtype=flat.dtype)
+                        out[:g.numel] = flat
+                        return out[g.rank * g.shard_numel:(g.rank + 1) * g.shard_numel]
 
-                g.shard16.copy_(rebuild("shard16"))
-                if g.trainable:
-                    g.master.copy_(rebuild("master" if "master" in olds[0][key] else "shard16"))
-                    if load_optim and "exp_avg" in olds[0][key]:
-                        g.exp_avg.copy_(rebuild("exp_avg"))
-                        g.exp_avg_sq.copy_(rebuild("exp_avg_sq"))
-                        g.step_count = olds[0][key]["step"]
+                    first = olds[0][key]
+                    rec = dict(shard16=rebuild("shard16"), world=e.world, rank=e.rank, step=first["step"], master=None,
+                               exp_avg=None, exp_avg_sq=None)
+                    if g.trainable:
+                        rec["master"] = rebuild("master" if "master" in first else "shard16")
+                        if load_optim and "exp_avg" in first:
+                            rec["exp_avg"], rec["exp_avg_sq"] = rebuild("exp_avg"), rebuild("exp_avg_sq")
+                    st[f"{u.name}#{gi}"] = rec
+            e.load_sharded_state(st, load_optim=load_optim)

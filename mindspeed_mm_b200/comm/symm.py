@@ -13,8 +13,9 @@ NVLink; nothing on this path calls NCCL.  The reference delegates the same two c
 Host-side protocol per gradient publication (slot = unit parity, seq grows by one per use of the slot):
   compute stream: wait_done(slot, previous seq)  -> copy gradients into the slot
   comm stream   : rs kernel = publish ready[slot]=seq -> wait peers' ready -> reduce(+update) -> write done flags
-``finish_step`` ends with a device-side barrier over the arena's signal pad, so a rank never gathers a
-shard that its owner has not finished updating.
+``finish_step`` ends with a device-side barrier of the arena (``p2p_barrier_kernel``: sequence flags in the arena,
+bounded wait, time-out reported through the status word), so a rank never gathers a shard that its owner has not
+finished updating.
 """
 from __future__ import annotations
 
@@ -40,7 +41,7 @@ class SymmArena:
         import torch.distributed._symmetric_memory as symm
         self.group, self.device = group, device
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        self.nbytes = _round_up(nbytes, ALIGN_BYTES)
+        self.nbytes = _round_up(nbytes, ALIGN_BYTES) + ALIGN_BYTES       # + the barrier block carved below
         self.buf = symm.empty(self.nbytes, dtype=torch.uint8, device=device)
         self.handle = symm.rendezvous(self.buf, group)
         self.peer_base: List[int] = [int(p) for p in self.handle.buffer_ptrs]
@@ -48,6 +49,10 @@ class SymmArena:
             raise RuntimeError("symmetric memory: local base pointer mismatch")
         self.buf.zero_()
         self._cursor = 0
+        # barrier block: one sequence flag per rank, written by the peers (see p2p_barrier_kernel)
+        self._bar_off = self.carve(native.lib().mm_p2p_barrier_bytes())
+        self._bar_ptrs = self.peer_ptrs(self._bar_off)
+        self._bar_seq = 0
 
     def carve(self, nbytes: int) -> int:
         off = self._cursor
@@ -66,7 +71,21 @@ class SymmArena:
         return arr
 
     def barrier(self):
-        self.handle.barrier()
+        """Stream-ordered barrier over the ranks of the arena, with a bounded device wait: a peer that never arrives
+        makes the kernel write MM_TIMEOUT_PEER into the status word (``native.check_status`` raises on the host) and
+        return; the context stays usable."""
+        self._bar_seq += 1
+        rc = native.lib().mm_p2p_barrier(self._bar_ptrs, self.world, self.rank, self._bar_seq,
+                                         native.status_word(self.device).data_ptr(), native._st())
+        native._check(rc, "p2p_barrier")
+
+    def host_barrier(self):
+        """Everything queued so far on this device is finished on every rank, and visible to the peers' kernels:
+        device synchronize, process-group barrier, arena barrier.  Used after parameter loads that write the shards
+        in the arena from the host side (no collective orders them against a peer's first gather)."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        self.barrier()
 
 
 class P2PCollectives:
@@ -79,7 +98,7 @@ class P2PCollectives:
         flag_bytes = native.lib().mm_p2p_flag_bytes()
         slot_bytes = _round_up(max(g.padded for g in groups) * 2, ALIGN_BYTES)
         shard_bytes = sum(_round_up(g.shard_numel * 2, ALIGN_BYTES) for g in groups)
-        total = _round_up(flag_bytes, ALIGN_BYTES) + 2 * slot_bytes + shard_bytes + ALIGN_BYTES
+        total = _round_up(flag_bytes, ALIGN_BYTES) + 2 * slot_bytes + shard_bytes + 2 * ALIGN_BYTES
         self.arena = SymmArena(total, engine.group, engine.device)
         a = self.arena
         self.flag_off = a.carve(flag_bytes)
@@ -96,9 +115,7 @@ class P2PCollectives:
             g.shard16 = new
             self.shard_ptrs[id(g)] = a.peer_ptrs(off)
         self._next_slot = 0
-        torch.cuda.synchronize(engine.device)
-        dist.barrier(group=engine.group)
-        a.barrier()
+        a.host_barrier()
 
     # ------------------------------------------------------------------ all-gather
     def all_gather(self, g, full: torch.Tensor) -> None:
@@ -146,4 +163,7 @@ class P2PCollectives:
 
     def step_barrier(self):
         self.arena.barrier()
+
+    def sync_after_load(self):
+        self.arena.host_barrier()
 

@@ -244,10 +244,10 @@ class ViTBlock(nn.Module):
     def __init__(self, c: PlainViTConfig):
         super().__init__()
         self.heads = c.num_heads
-        self.ln1 = nn.LayerNorm(c.hidden_size, eps=c.eps)
+        self.ln1 = ops.LayerNorm(c.hidden_size, eps=c.eps)
         self.qkv = Linear(c.hidden_size, 3 * c.hidden_size, bias=True)
         self.proj = Linear(c.hidden_size, c.hidden_size, bias=True)
-        self.ln2 = nn.LayerNorm(c.hidden_size, eps=c.eps)
+        self.ln2 = ops.LayerNorm(c.hidden_size, eps=c.eps)
         self.fc1 = Linear(c.hidden_size, c.intermediate_size, bias=True)
         self.fc2 = Linear(c.intermediate_size, c.hidden_size, bias=True)
 
@@ -271,7 +271,7 @@ class PlainViT(nn.Module):
         self.blocks = nn.ModuleList(ViTBlock(c) for _ in range(c.num_layers))
         self.merger = nn.Sequential()
         m2 = c.merge ** 2
-        self.merger_norm = nn.LayerNorm(c.hidden_size * m2, eps=c.eps)
+        self.merger_norm = ops.LayerNorm(c.hidden_size * m2, eps=c.eps)
         self.merger_fc1 = Linear(c.hidden_size * m2, c.out_hidden_size, bias=True)
         self.merger_fc2 = Linear(c.out_hidden_size, c.out_hidden_size, bias=True)
 
@@ -292,7 +292,7 @@ class PlainViT(nn.Module):
         for blk in self.blocks:
             x = blk(x, cu, mx)
         x = self.merger_norm(x.view(-1, x.shape[-1] * self.cfg.merge ** 2))
-        return self.merger_fc2(F.gelu(self.merger_fc1(x)))
+        return self.merger_fc2(ops.gelu(self.merger_fc1(x)))
 
 
 class TileFormatter(nn.Module):

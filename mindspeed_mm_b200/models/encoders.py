@@ -50,10 +50,10 @@ class CLIPVisionEncoder(nn.Module):
         self.class_embedding = nn.Parameter(torch.zeros(c.hidden_size))
         self.patch_embedding = nn.Conv2d(3, c.hidden_size, c.patch_size, stride=c.patch_size, bias=False)
         self.position_embedding = nn.Embedding(n + 1, c.hidden_size)
-        self.pre_ln = nn.LayerNorm(c.hidden_size, eps=c.eps)
+        self.pre_ln = ops.LayerNorm(c.hidden_size, eps=c.eps)
         self.layers = nn.ModuleList(CLIPLayer(c.hidden_size, c.intermediate_size, c.num_heads, c.act, c.eps)
                                     for _ in range(c.num_layers))
-        self.post_ln = nn.LayerNorm(c.hidden_size, eps=c.eps)
+        self.post_ln = ops.LayerNorm(c.hidden_size, eps=c.eps)
 
     def forward(self, pixels, output_layer: int = -1):
         """pixels [B,3,H,W] -> (hidden states of layer ``output_layer`` [B,1+N,H], pooled class token)."""
@@ -120,12 +120,12 @@ class WhisperLayer(nn.Module):
         super().__init__()
         self.heads = c.num_heads
         d = c.d_model
-        self.ln1 = nn.LayerNorm(d, eps=c.eps)
+        self.ln1 = ops.LayerNorm(d, eps=c.eps)
         self.q = nn.Linear(d, d)
         self.k = nn.Linear(d, d, bias=False)
         self.v = nn.Linear(d, d)
         self.out = nn.Linear(d, d)
-        self.ln2 = nn.LayerNorm(d, eps=c.eps)
+        self.ln2 = ops.LayerNorm(d, eps=c.eps)
         self.fc1 = nn.Linear(d, c.ffn_dim)
         self.fc2 = nn.Linear(c.ffn_dim, d)
 
@@ -138,7 +138,7 @@ class WhisperLayer(nn.Module):
         v = ops.linear(h, self.v.weight, self.v.bias).view(T, self.heads, -1)
         o = ops.attention_varlen(q, k, v, cu_seqlens, cu_seqlens, max_len, max_len, causal=False)
         x = x + ops.linear(o.reshape(T, d), self.out.weight, self.out.bias)
-        return x + ops.linear(F.gelu(ops.linear(self.ln2(x), self.fc1.weight, self.fc1.bias)), self.fc2.weight, self.fc2.bias)
+        return x + ops.linear(ops.gelu(ops.linear(self.ln2(x), self.fc1.weight, self.fc1.bias)), self.fc2.weight, self.fc2.bias)
 
 
 class WhisperEncoder(nn.Module):
@@ -149,12 +149,12 @@ class WhisperEncoder(nn.Module):
         self.conv2 = nn.Conv1d(c.d_model, c.d_model, 3, stride=2, padding=1)
         self.register_buffer("positions", sinusoid_positions(c.max_source_positions, c.d_model), persistent=False)
         self.layers = nn.ModuleList(WhisperLayer(c) for _ in range(c.num_layers))
-        self.ln_post = nn.LayerNorm(c.d_model, eps=c.eps)
+        self.ln_post = ops.LayerNorm(c.d_model, eps=c.eps)
 
     def embed(self, mel):
         """mel [B, n_mels, frames] -> [B, frames/2, d] with positions added."""
-        x = F.gelu(self.conv1(mel))
-        x = F.gelu(self.conv2(x)).transpose(1, 2)
+        x = ops.gelu(self.conv1(mel))
+        x = ops.gelu(self.conv2(x)).transpose(1, 2)
         return x + self.positions[: x.shape[1]].to(x.dtype)
 
     def forward(self, mel):

@@ -287,7 +287,7 @@ class PatchMerger(nn.Module):
 
     def forward(self, x):
         x = self.ln_q(x).view(-1, x.shape[-1] * self.unit)
-        return self.fc2(F.gelu(self.fc1(x)))
+        return self.fc2(ops.gelu(self.fc1(x)))
 
 
 class VisionPatchEmbed(nn.Module):

@@ -107,7 +107,7 @@ class Attention(nn.Module):
 class TransformerLayer(nn.Module):
     def __init__(self, dim, ctx_dim, head_dim):
         super().__init__()
-        self.norm1, self.norm2, self.norm3 = nn.LayerNorm(dim), nn.LayerNorm(dim), nn.LayerNorm(dim)
+        self.norm1, self.norm2, self.norm3 = ops.LayerNorm(dim), ops.LayerNorm(dim), ops.LayerNorm(dim)
         self.attn1 = Attention(dim, dim, head_dim)
         self.attn2 = Attention(dim, ctx_dim, head_dim)
         self.ff_in = nn.Linear(dim, dim * 8)                   # GEGLU: value and gate halves
@@ -117,7 +117,7 @@ class TransformerLayer(nn.Module):
         x = x + self.attn1(self.norm1(x))
         x = x + self.attn2(self.norm2(x), ctx)
         a, g = self.ff_in(self.norm3(x)).chunk(2, -1)
-        return x + self.ff_out(a * F.gelu(g))
+        return x + self.ff_out(a * ops.gelu(g))
 
 
 class SpatialTransformer(nn.Module):

@@ -187,7 +187,7 @@ def _act(name: str, x):
     if name == "quick_gelu":
         return x * torch.sigmoid(1.702 * x)
     if name == "gelu":
-        return F.gelu(x)
+        return ops.gelu(x)
     return ops.gelu_tanh(x)
 
 
@@ -195,10 +195,10 @@ class CLIPLayer(nn.Module):
     def __init__(self, hidden, inter, heads, act, eps):
         super().__init__()
         self.heads, self.act, self.eps = heads, act, eps
-        self.ln1 = nn.LayerNorm(hidden, eps=eps)
+        self.ln1 = ops.LayerNorm(hidden, eps=eps)
         self.qkv = nn.Linear(hidden, 3 * hidden)
         self.out = nn.Linear(hidden, hidden)
-        self.ln2 = nn.LayerNorm(hidden, eps=eps)
+        self.ln2 = ops.LayerNorm(hidden, eps=eps)
         self.fc1 = nn.Linear(hidden, inter)
         self.fc2 = nn.Linear(inter, hidden)
 
@@ -219,7 +219,7 @@ class CLIPTextEncoder(nn.Module):
         self.position_embedding = nn.Embedding(c.max_positions, c.hidden_size)
         self.layers = nn.ModuleList(CLIPLayer(c.hidden_size, c.intermediate_size, c.num_heads, c.act, c.eps)
                                     for _ in range(c.num_layers))
-        self.final_ln = nn.LayerNorm(c.hidden_size, eps=c.eps)
+        self.final_ln = ops.LayerNorm(c.hidden_size, eps=c.eps)
 
     def forward(self, input_ids):
         B, L = input_ids.shape

@@ -281,7 +281,7 @@ class JointDiT(nn.Module):
         self.config = c = config
         self.embed = _Embed(c, 1)
         self.blocks = nn.ModuleList(JointBlock(c) for _ in range(c.num_layers))
-        self.norm_final = nn.LayerNorm(c.hidden_size, eps=c.eps)
+        self.norm_final = ops.LayerNorm(c.hidden_size, eps=c.eps)
         self.final = _Final(c)
 
     def fsdp_units(self):

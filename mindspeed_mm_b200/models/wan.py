@@ -208,7 +208,7 @@ class WanEmbeddings(nn.Module):
         ctx = self.text_embedding_2(ops.gelu_tanh(self.text_embedding_1(prompt.to(dtype))))
         n_img = 0
         if clip_feature is not None:
-            img = self.img_emb_norm2(self.img_emb_fc2(F.gelu(self.img_emb_fc1(self.img_emb_norm1(clip_feature.to(dtype))))))
+            img = self.img_emb_norm2(self.img_emb_fc2(ops.gelu(self.img_emb_fc1(self.img_emb_norm1(clip_feature.to(dtype))))))
             ctx = torch.cat([img, ctx], dim=1)
             n_img = img.shape[1]
         return x, times, time_emb, ctx, n_img

@@ -24,7 +24,10 @@ import torch.nn.functional as F
 from . import reference as ref
 
 _TIER = os.environ.get("MM_B200_TIER", "native")
-_PAD_SMALL_HEADS = os.environ.get("MM_B200_PAD_SMALL_HEADS", "0") == "1"
+_STRICT = os.environ.get("MM_B200_STRICT", "0") == "1"
+# op name -> number of calls that were handed CUDA tensors on the native tier and did NOT run a kernel of this
+# package (library or eager PyTorch instead).  Benchmarks print it; ``set_strict(True)`` turns a count into an error.
+FALLBACKS: dict = {}
 
 
 def set_tier(tier: str) -> None:
@@ -36,6 +39,30 @@ def set_tier(tier: str) -> None:
 
 def get_tier() -> str:
     return _TIER
+
+
+def set_strict(on: bool = True) -> None:
+    """Strict mode: on the native tier an op that would leave this package's kernels raises instead."""
+    global _STRICT
+    _STRICT = bool(on)
+
+
+def library_fallbacks(reset: bool = False) -> dict:
+    out = dict(FALLBACKS)
+    if reset:
+        FALLBACKS.clear()
+    return out
+
+
+def _fallback(op: str, x: torch.Tensor, why: str = "") -> None:
+    """Record (or, in strict mode, refuse) a non-native execution of ``op``; only CUDA tensors on the native tier
+    count: CPU runs and the explicit library tier are not fallbacks."""
+    if not (x.is_cuda and _TIER == "native"):
+        return
+    if _STRICT:
+        raise RuntimeError(f"ops.{op}: no native kernel for this call ({why or 'unsupported shape / dtype'}); "
+                           f"strict mode refuses the library / eager path")
+    FALLBACKS[op] = FALLBACKS.get(op, 0) + 1
 
 
 def _native(x: torch.Tensor) -> bool:
@@ -51,50 +78,73 @@ def _nat():
 def rms_norm(x, weight, eps: float = 1e-6):
     if _native(x) and x.dtype == torch.bfloat16:
         return _nat().rms_norm(x, weight, eps)
+    _fallback("rms_norm", x, str(x.dtype))
     return ref.rms_norm(x, weight, eps)
 
 
 def layer_norm(x, weight=None, bias=None, eps: float = 1e-6):
+    """LayerNorm over the last dim with optional affine.  Native tier: the LayerNorm-modulate kernel with
+    ``scale = weight - 1`` and ``shift = bias`` (``LN(x) * (1 + scale) + shift``), rows flattened to one batch."""
+    if _native(x) and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192:
+        return _nat().layer_norm(x, weight, bias, eps)
+    _fallback("layer_norm", x, f"{x.dtype} H={x.shape[-1]}")
     return ref.layer_norm(x, weight, bias, eps)
 
 
 def layer_norm_modulate(x, scale, shift, eps: float = 1e-6):
     if _native(x) and x.dtype == torch.bfloat16:
         return _nat().layer_norm_modulate(x, scale, shift, eps)
+    _fallback("layer_norm_modulate", x, str(x.dtype))
     return ref.layer_norm_modulate(x, scale, shift, eps)
 
 
 def gated_residual(x, y, gate):
     if _native(x) and x.dtype == torch.bfloat16:
         return _nat().gated_residual(x, y, gate)
+    _fallback("gated_residual", x, str(x.dtype))
     return ref.gated_residual(x, y, gate)
 
 
 def swiglu(gate_up, clamp: Optional[float] = None):
     if _native(gate_up) and gate_up.dtype == torch.bfloat16 and clamp is None:
         return _nat().swiglu(gate_up)
+    _fallback("swiglu", gate_up, "clamp" if clamp is not None else str(gate_up.dtype))
     return ref.swiglu(gate_up, clamp)
 
 
 def gelu_tanh(x):
+    if _native(x) and x.dtype == torch.bfloat16 and x.numel() % 8 == 0:
+        return _nat().gelu(x, tanh=True)
+    _fallback("gelu_tanh", x, str(x.dtype))
     return F.gelu(x, approximate="tanh")
+
+
+def gelu(x):
+    """Exact (erf) GELU."""
+    if _native(x) and x.dtype == torch.bfloat16 and x.numel() % 8 == 0:
+        return _nat().gelu(x, tanh=False)
+    _fallback("gelu", x, str(x.dtype))
+    return F.gelu(x)
 
 
 def rope_rotate_half(x, cos, sin):
     if _native(x) and x.dtype == torch.bfloat16:
         return _nat().rope(x, cos, sin, interleaved=False)
+    _fallback("rope_rotate_half", x, str(x.dtype))
     return ref.rope_rotate_half(x, cos, sin)
 
 
 def rope_interleaved(x, cos, sin):
     if _native(x) and x.dtype == torch.bfloat16:
         return _nat().rope(x, cos, sin, interleaved=True)
+    _fallback("rope_interleaved", x, str(x.dtype))
     return ref.rope_interleaved(x, cos, sin)
 
 
 def l2_norm(x, eps: float = 1e-6):
     if _native(x) and x.dtype == torch.bfloat16 and x.shape[-1] <= 256:
         return _nat().l2_norm(x, eps)
+    _fallback("l2_norm", x, f"{x.dtype} D={x.shape[-1]}")
     return ref.l2_norm(x, eps)
 
 
@@ -102,6 +152,7 @@ def gated_rms_norm(x, z, weight, eps: float = 1e-6):
     if (_native(x) and x.dtype == torch.float32 and z.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
             and x.shape[-1] <= 256 and not torch.is_grad_enabled()):
         return _nat().gated_rms_norm_fwd(x, z, weight, eps)
+    _fallback("gated_rms_norm", x, "training pass or unsupported dtype")
     return ref.gated_rms_norm(x, z, weight, eps)
 
 
@@ -149,6 +200,7 @@ def linear(x, weight, bias=None, value_unused_in_backward: bool = False):
     skips the GEMM and returns an uninitialised tensor; gradients are unaffected."""
     if _native(x) and x.dtype == torch.bfloat16 and _nat().gemm_supported(x, weight):
         return _nat().linear(x, weight, bias, value_unused_in_backward and _RECOMPUTING)
+    _fallback("linear", x, f"{x.dtype} {tuple(x.shape)} x {tuple(weight.shape)}")
     return F.linear(x, weight, bias)
 
 
@@ -171,18 +223,7 @@ def attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max
         if _TIER == "native" and _nat().fmha_supported(q, k, v):
             return _nat().attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
                                            causal, softmax_scale, _ACT_CACHE)
-        D = q.shape[-1]
-        if (_TIER == "native" and _PAD_SMALL_HEADS and q.dtype == torch.bfloat16 and D < 128 and D % 8 == 0
-                and v.shape[-1] == D):
-            # smaller heads (ViT: 80) can ride the 128-wide tcgen05 kernels zero-padded; the scale stays 1/sqrt(D).
-            # Off by default: measured on the Qwen2.5-VL-7B step the 1.6x padded work costs more (+27 ms per step)
-            # than the library kernel specialised for the narrow head.
-            pad = 128 - D
-            qp, kp, vp = (F.pad(t, (0, pad)) for t in (q, k, v))
-            if _nat().fmha_supported(qp, kp, vp):
-                scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
-                o = _nat().attention_varlen(qp, kp, vp, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, scale)
-                return o[..., :D]
+        _fallback("attention_varlen", q, f"{q.dtype} D={q.shape[-1]}")
         return _library_attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
                                          causal, softmax_scale)
     return ref.attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, causal, softmax_scale)
@@ -222,6 +263,7 @@ def linear_cross_entropy(h, weight, labels, ignore_index: int = -100, chunk: int
     """
     if _native(h) and h.dtype == torch.bfloat16 and _nat().lce_supported(h, weight):
         return _nat().linear_cross_entropy(h, weight, labels, ignore_index)
+    _fallback("linear_cross_entropy", h, str(h.dtype))
     return _ChunkedLinearCE.apply(h, weight, labels, ignore_index, chunk), (labels != ignore_index).sum()
 
 
@@ -260,6 +302,7 @@ class _ChunkedLinearCE(torch.autograd.Function):
 def grouped_gemm(x, w, counts):
     if _native(x) and x.dtype == torch.bfloat16 and _nat().grouped_gemm_supported(x, w):
         return _nat().grouped_gemm(x, w, counts)
+    _fallback("grouped_gemm", x, str(x.dtype))
     return _GroupedGemmLoop.apply(x, w, counts)
 
 
@@ -296,6 +339,7 @@ def moe_experts(tokens, topk_ids, probs, gate_up, down):
     """Local routed experts (all experts of ``gate_up`` / ``down`` live on this rank)."""
     if _native(tokens) and _nat().moe_supported(tokens, gate_up, down):
         return _nat().moe_experts(tokens, topk_ids, probs, gate_up, down)
+    _fallback("moe_experts", tokens, str(tokens.dtype))
     permuted, order = ref.moe_permute(tokens, topk_ids)
     counts = torch.bincount(topk_ids.reshape(-1), minlength=gate_up.shape[0]).tolist()
     h = grouped_gemm(permuted, gate_up, counts)
@@ -310,10 +354,12 @@ moe_unpermute = ref.moe_unpermute
 def causal_conv1d(x, weight, bias=None, activation="silu", cu_seqlens=None):
     if _native(x) and bias is None and _nat().conv1d_supported(x, weight):
         return _nat().causal_conv1d(x, weight, activation, cu_seqlens)
+    _fallback("causal_conv1d", x, "bias or unsupported shape")
     return ref.causal_conv1d(x, weight, bias, activation, cu_seqlens)
 
 
 def gated_delta_rule(q, k, v, g, beta, scale=None, chunk: int = 64, initial_state=None):
+    _fallback("gated_delta_rule", q, "batched form: use gated_delta_rule_varlen for the kernel path")
     return ref.gated_delta_rule_chunked(q, k, v, g, beta, scale, chunk, initial_state)
 
 
@@ -322,6 +368,7 @@ def gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk: int = 64, scale
     ``cu_seqlens`` boundary.  Returns [T, H, V] (fp32)."""
     if _native(q) and _nat().gdn_supported(q, v, chunk):
         return _nat().gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk, scale)
+    _fallback("gated_delta_rule_varlen", q, f"K={q.shape[-1]} V={v.shape[-1]} chunk={chunk}")
     outs = []
     cu = [int(c) for c in cu_seqlens]
     for a, b in zip(cu[:-1], cu[1:]):
@@ -332,6 +379,7 @@ def gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk: int = 64, scale
 
 def kda(q, k, v, g, beta, scale=None, chunk: int = 64, initial_state=None):
     """Kimi delta attention (per-channel gate).  Chunked batched-GEMM form on every device."""
+    _fallback("kda", q, "no dedicated kernel")
     return ref.kda_chunked(q, k, v, g, beta, scale, chunk, initial_state)
 
 
@@ -341,3 +389,13 @@ def status() -> dict:
         return _nat().status()
     except Exception as e:  # extension absent on a CPU box
         return {"loaded": False, "why": str(e)}
+
+
+class LayerNorm(torch.nn.LayerNorm):
+    """``torch.nn.LayerNorm`` (same parameters and state-dict keys) whose forward goes through :func:`layer_norm`,
+    i.e. the LayerNorm kernel of this package on the native tier."""
+
+    def forward(self, x):
+        if len(self.normalized_shape) != 1:
+            return super().forward(x)
+        return layer_norm(x, self.weight, self.bias, self.eps)

@@ -196,6 +196,51 @@ __global__ void swiglu_bwd_kernel(const bf16* __restrict__ in, const bf16* __res
     }
 }
 
+// ------------------------------------------------------------------------------------------ GELU
+// tanh form: 0.5 x (1 + tanh(c (x + 0.044715 x^3))), c = sqrt(2/pi); exact form: 0.5 x (1 + erf(x / sqrt 2)).
+// The backward recomputes the activation's derivative from the saved input (one read of x and dy, one write).
+template <bool TANH>
+__device__ __forceinline__ float gelu_f(float x) {
+    if (TANH) {
+        const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+        return 0.5f * x * (1.f + tanhf(u));
+    }
+    return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
+}
+template <bool TANH>
+__device__ __forceinline__ float gelu_df(float x) {
+    if (TANH) {
+        const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+        const float t = tanhf(u);
+        return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * 0.7978845608028654f * (1.f + 3.f * 0.044715f * x * x);
+    }
+    return 0.5f * (1.f + erff(x * 0.7071067811865476f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
+
+template <bool TANH>
+__global__ void gelu_fwd_kernel(const Vec8* __restrict__ in, Vec8* __restrict__ out, long long nvec) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+        float a[8];
+        unpack8(in[i], a);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) a[k] = gelu_f<TANH>(a[k]);
+        out[i] = pack8(a);
+    }
+}
+
+template <bool TANH>
+__global__ void gelu_bwd_kernel(const Vec8* __restrict__ in, const Vec8* __restrict__ dout, Vec8* __restrict__ din,
+                                long long nvec) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+        float a[8], g[8];
+        unpack8(in[i], a);
+        unpack8(dout[i], g);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) a[k] = g[k] * gelu_df<TANH>(a[k]);
+        din[i] = pack8(a);
+    }
+}
+
 // ------------------------------------------------------------------------------------------ RoPE
 // x: [T, N, D] with row stride `xs` elements between tokens (heads contiguous); out contiguous.
 // half-rotation: cos/sin [T, D] (bf16): o1 = x1*c1 - x2*s1 ; o2 = x2*c2 + x1*s2  (sign flips for bwd)
@@ -514,6 +559,25 @@ MM_API int mm_swiglu_fwd(const void* in, void* out, long long T, int F, cudaStre
 MM_API int mm_swiglu_bwd(const void* in, const void* dout, void* din, long long T, int F, cudaStream_t st) {
     if (F % 8) return -1;
     swiglu_bwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, st>>>((const bf16*)in, (const bf16*)dout, (bf16*)din, T, F);
+    return (int)cudaGetLastError();
+}
+
+// in / out / dout / din: contiguous bf16, n elements (multiple of 8, 16-byte aligned); tanh_form selects the approximation.
+MM_API int mm_gelu_fwd(const void* in, void* out, long long n, int tanh_form, cudaStream_t st) {
+    if (n % 8 || (((uintptr_t)in | (uintptr_t)out) & 15)) return -1;
+    if (n == 0) return 0;
+    if (tanh_form) gelu_fwd_kernel<true><<<grid_for(n / 8, 256), 256, 0, st>>>((const Vec8*)in, (Vec8*)out, n / 8);
+    else gelu_fwd_kernel<false><<<grid_for(n / 8, 256), 256, 0, st>>>((const Vec8*)in, (Vec8*)out, n / 8);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_gelu_bwd(const void* in, const void* dout, void* din, long long n, int tanh_form, cudaStream_t st) {
+    if (n % 8 || (((uintptr_t)in | (uintptr_t)dout | (uintptr_t)din) & 15)) return -1;
+    if (n == 0) return 0;
+    if (tanh_form)
+        gelu_bwd_kernel<true><<<grid_for(n / 8, 256), 256, 0, st>>>((const Vec8*)in, (const Vec8*)dout, (Vec8*)din, n / 8);
+    else
+        gelu_bwd_kernel<false><<<grid_for(n / 8, 256), 256, 0, st>>>((const Vec8*)in, (const Vec8*)dout, (Vec8*)din, n / 8);
     return (int)cudaGetLastError();
 }
 

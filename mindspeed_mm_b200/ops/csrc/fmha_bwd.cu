@@ -39,6 +39,7 @@ struct BwdParams {
     bf16* dk;               // [Tk, Nkv, 128]
     bf16* dv;
     int T, Tk, Nq, Nkv, causal;
+    int D;                  // head dim of the tensors in global memory (<= HD); shared-memory tiles stay HD wide
     float scale, scale_log2;
     int* status;
     int split;              // dK/dV kernel: 1 = one CTA per QUERY head writing partial dk / dv [Tk, Nq, 128]
@@ -46,12 +47,15 @@ struct BwdParams {
 
 // delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (t, h)
 __global__ void fmha_delta_kernel(const bf16* __restrict__ o, const bf16* __restrict__ dO, float* __restrict__ delta, int T,
-                                  int Nq) {
+                                  int Nq, int D) {
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= (long long)T * Nq) return;
     const int lane = threadIdx.x & 31;
-    const uint2 a = reinterpret_cast<const uint2*>(o + row * HD)[lane];
-    const uint2 b = reinterpret_cast<const uint2*>(dO + row * HD)[lane];
+    uint2 a = make_uint2(0, 0), b = make_uint2(0, 0);
+    if (lane * 4 < D) {                     // D is a multiple of 8: a lane's four elements are all inside or all outside
+        a = reinterpret_cast<const uint2*>(o + row * D)[lane];
+        b = reinterpret_cast<const uint2*>(dO + row * D)[lane];
+    }
     const bf162* pa = reinterpret_cast<const bf162*>(&a);
     const bf162* pb = reinterpret_cast<const bf162*>(&b);
     float s = 0.f;
@@ -293,7 +297,7 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             fence_before_sync();
             mbar_arrive(ds_full);
         }
-        bf16* dst = p.dq + ((size_t)(q_begin + qi) * p.Nq + head) * HD + half * 64;
+        bf16* dst = p.dq + ((size_t)(q_begin + qi) * p.Nq + head) * p.D + half * 64;
         if (ok && n_kv > 0 && mbar_wait(dq_full, 0, abort_flag)) {
             fence_after_sync();
 #pragma unroll
@@ -309,12 +313,13 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                         w.y = pack2(__uint_as_float(d[g * 8 + 2]) * p.scale, __uint_as_float(d[g * 8 + 3]) * p.scale);
                         w.z = pack2(__uint_as_float(d[g * 8 + 4]) * p.scale, __uint_as_float(d[g * 8 + 5]) * p.scale);
                         w.w = pack2(__uint_as_float(d[g * 8 + 6]) * p.scale, __uint_as_float(d[g * 8 + 7]) * p.scale);
-                        reinterpret_cast<uint4*>(dst)[c * 4 + g] = w;
+                        if (half * 64 + c * 32 + g * 8 < p.D) reinterpret_cast<uint4*>(dst)[c * 4 + g] = w;
                     }
                 }
             }
         } else if (n_kv == 0 && row_ok) {
-            for (int g = 0; g < 8; ++g) reinterpret_cast<uint4*>(dst)[g] = make_uint4(0, 0, 0, 0);
+            for (int g = 0; g < 8; ++g)
+                if (half * 64 + g * 8 < p.D) reinterpret_cast<uint4*>(dst)[g] = make_uint4(0, 0, 0, 0);
         }
         if (!ok && lane == 0) atomicExch(p.status, MM_TIMEOUT_EPI);
     }
@@ -533,8 +538,8 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             fence_before_sync();
             mbar_arrive(pds_full);
         }
-        bf16* dvp = p.dv + ((size_t)(k_begin + kj) * out_heads + out_head) * HD + half * 64;
-        bf16* dkp = p.dk + ((size_t)(k_begin + kj) * out_heads + out_head) * HD + half * 64;
+        bf16* dvp = p.dv + ((size_t)(k_begin + kj) * out_heads + out_head) * p.D + half * 64;
+        bf16* dkp = p.dk + ((size_t)(k_begin + kj) * out_heads + out_head) * p.D + half * 64;
         if (ok && n_it > 0 && mbar_wait(acc_full, 0, abort_flag)) {
             fence_after_sync();
 #pragma unroll
@@ -555,16 +560,19 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         x.y = pack2(__uint_as_float(b[g * 8 + 2]) * p.scale, __uint_as_float(b[g * 8 + 3]) * p.scale);
                         x.z = pack2(__uint_as_float(b[g * 8 + 4]) * p.scale, __uint_as_float(b[g * 8 + 5]) * p.scale);
                         x.w = pack2(__uint_as_float(b[g * 8 + 6]) * p.scale, __uint_as_float(b[g * 8 + 7]) * p.scale);
-                        reinterpret_cast<uint4*>(dvp)[c * 4 + g] = w;
-                        reinterpret_cast<uint4*>(dkp)[c * 4 + g] = x;
+                        if (half * 64 + c * 32 + g * 8 < p.D) {
+                            reinterpret_cast<uint4*>(dvp)[c * 4 + g] = w;
+                            reinterpret_cast<uint4*>(dkp)[c * 4 + g] = x;
+                        }
                     }
                 }
             }
         } else if (n_it == 0 && row_ok) {
-            for (int g = 0; g < 8; ++g) {
-                reinterpret_cast<uint4*>(dvp)[g] = make_uint4(0, 0, 0, 0);
-                reinterpret_cast<uint4*>(dkp)[g] = make_uint4(0, 0, 0, 0);
-            }
+            for (int g = 0; g < 8; ++g)
+                if (half * 64 + g * 8 < p.D) {
+                    reinterpret_cast<uint4*>(dvp)[g] = make_uint4(0, 0, 0, 0);
+                    reinterpret_cast<uint4*>(dkp)[g] = make_uint4(0, 0, 0, 0);
+                }
         }
         if (!ok && lane == 0) atomicExch(p.status, MM_TIMEOUT_EPI);
     }
@@ -579,23 +587,23 @@ fmha_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
 }
 
-#include "fmha_bwd_pp.cuh"
 #include "fmha_bwd_dkv128.cuh"
-#include "fmha_bwd_dq128ts.cuh"
 
 }  // namespace
 
 // Scratch: plan = 2 * (2 * max_tiles + 1) ints with max_tiles = mm_fmha_bwd_max_tiles; delta = Nq * T floats.
 MM_API int mm_fmha_bwd_max_tiles(int T, int n_seqs) { return T / 128 + n_seqs + 1; }
 
-// q, dO, o: [T, Nq, 128]; k, v: [Tk, Nkv, 128] (token strides q_ts / k_ts / v_ts elements, heads dense; dO and o dense);
-// lse: [Nq, T] fp32 from the forward; outputs dq [T, Nq, 128], dk / dv [Tk, Nkv, 128] dense bf16
-// (split_heads = 1: dk / dv are per-query-head partials [Tk, Nq, 128] that the caller sums over each GQA group).
+// q, dO, o: [T, Nq, D]; k, v: [Tk, Nkv, D] (token strides q_ts / k_ts / v_ts elements, heads dense; dO and o dense); D <= 128,
+// a multiple of 8 (narrower heads read zeros beyond D through the tensor maps' out-of-range fill);
+// lse: [Nq, T] fp32 from the forward; outputs dq [T, Nq, D], dk / dv [Tk, Nkv, D] dense bf16
+// (split_heads = 1: dk / dv are per-query-head partials [Tk, Nq, D] that the caller sums over each GQA group).
+// variant 0: dK/dV kernel over 64-row query steps (fallback); anything else: 128-row query steps (default).
 MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
                        float* delta, void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, int* plan, int T, int Tk,
                        int n_seqs, int Nq, int Nkv, int D, long long q_ts, long long k_ts, long long v_ts, int causal,
                        float scale, int split_heads, int variant, int* status, cudaStream_t st) {
-    if (D != HD || Nq % Nkv || (q_ts | k_ts | v_ts) % 8) return -1;
+    if (D > HD || D < 8 || D % 8 || Nq % Nkv || (q_ts | k_ts | v_ts) % 8) return -1;
     if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o | (uintptr_t)dO | (uintptr_t)dq | (uintptr_t)dk |
          (uintptr_t)dv) & 15)
         return -2;
@@ -606,60 +614,28 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
     int* k_seq = plan + 2 * mq + 1;
     int* k_r0 = k_seq + mk;
     int* k_n = k_seq + 2 * mk;
-    fmha_delta_kernel<<<(unsigned)(((long long)T * Nq + 7) / 8), 256, 0, st>>>((const bf16*)o, (const bf16*)dO, delta, T, Nq);
+    fmha_delta_kernel<<<(unsigned)(((long long)T * Nq + 7) / 8), 256, 0, st>>>((const bf16*)o, (const bf16*)dO, delta, T, Nq, D);
     fmha_bwd_plan_kernel<<<1, 32, 0, st>>>(cu_q, n_seqs, q_seq, q_r0, q_n, mq, 128, 1);
     // early key tiles see the most query tiles under a causal mask: emit them first
     fmha_bwd_plan_kernel<<<1, 32, 0, st>>>(cu_k, n_seqs, k_seq, k_r0, k_n, mk, 128, 0);
     CUtensorMap tQ, tK, tV, tdO, tQ64, tdO64;
     int r;
-    if ((r = make_tmap_3d(&tQ, q, HD, Nq, T, HD, q_ts, 64, 1, 128))) return 1000 + r;
-    if ((r = make_tmap_3d(&tK, k, HD, Nkv, Tk, HD, k_ts, 64, 1, 128))) return 2000 + r;
-    if ((r = make_tmap_3d(&tV, v, HD, Nkv, Tk, HD, v_ts, 64, 1, 128))) return 3000 + r;
-    if ((r = make_tmap_3d(&tdO, dO, HD, Nq, T, HD, (long long)Nq * HD, 64, 1, 128))) return 4000 + r;
-    if ((r = make_tmap_3d(&tQ64, q, HD, Nq, T, HD, q_ts, 64, 1, BQ2))) return 5000 + r;
-    if ((r = make_tmap_3d(&tdO64, dO, HD, Nq, T, HD, (long long)Nq * HD, 64, 1, BQ2))) return 6000 + r;
+    if ((r = make_tmap_3d(&tQ, q, D, Nq, T, D, q_ts, 64, 1, 128))) return 1000 + r;
+    if ((r = make_tmap_3d(&tK, k, D, Nkv, Tk, D, k_ts, 64, 1, 128))) return 2000 + r;
+    if ((r = make_tmap_3d(&tV, v, D, Nkv, Tk, D, v_ts, 64, 1, 128))) return 3000 + r;
+    if ((r = make_tmap_3d(&tdO, dO, D, Nq, T, D, (long long)Nq * D, 64, 1, 128))) return 4000 + r;
+    if ((r = make_tmap_3d(&tQ64, q, D, Nq, T, D, q_ts, 64, 1, BQ2))) return 5000 + r;
+    if ((r = make_tmap_3d(&tdO64, dO, D, Nq, T, D, (long long)Nq * D, 64, 1, BQ2))) return 6000 + r;
     if (cudaFuncSetAttribute(fmha_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDq) != cudaSuccess) return -3;
     if (cudaFuncSetAttribute(fmha_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkv) != cudaSuccess) return -3;
-    BwdParams p{cu_q, cu_k, q_seq, q_r0, q_n, lse, delta, (bf16*)dq, (bf16*)dk, (bf16*)dv, T, Tk, Nq, Nkv, causal, scale,
+    BwdParams p{cu_q, cu_k, q_seq, q_r0, q_n, lse, delta, (bf16*)dq, (bf16*)dk, (bf16*)dv, T, Tk, Nq, Nkv, causal, D, scale,
                 scale * kLog2e, status, split_heads};
     BwdParams pk = p;
     pk.tile_seq = k_seq;
     pk.tile_r0 = k_r0;
     pk.n_tiles = k_n;
-    if (variant == 1 || variant == 2) {      // ping-pong schedule (2: dS through tensor memory, TS-form dQ product): 64-wide inner tiles, deeper rings, one warpgroup per in-flight tile
-        CUtensorMap tK64, tV64;
-        if ((r = make_tmap_3d(&tK64, k, HD, Nkv, Tk, HD, k_ts, 64, 1, BK))) return 7000 + r;
-        if ((r = make_tmap_3d(&tV64, v, HD, Nkv, Tk, HD, v_ts, 64, 1, BK))) return 8000 + r;
-        if (cudaFuncSetAttribute(fmha_bwd_dq_pp_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDqPP) != cudaSuccess ||
-            cudaFuncSetAttribute(fmha_bwd_dq_pp_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDqPP) != cudaSuccess ||
-            cudaFuncSetAttribute(fmha_bwd_dkv_pp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkvPP) != cudaSuccess)
-            return -3;
-        if (variant == 2) fmha_bwd_dq_pp_kernel<true><<<dim3(mq, Nq), 320, kSmemDqPP, st>>>(tQ, tK64, tV64, tdO, p);
-        else fmha_bwd_dq_pp_kernel<false><<<dim3(mq, Nq), 320, kSmemDqPP, st>>>(tQ, tK64, tV64, tdO, p);
-        fmha_bwd_dkv_pp_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkvPP, st>>>(tQ64, tK, tV, tdO64, pk);
-        return (int)cudaGetLastError();
-    }
-    if (variant == 4) {      // dQ with Q / dO / dS in tensor memory over 64-key steps
-        CUtensorMap tK64, tV64;
-        if ((r = make_tmap_3d(&tK64, k, HD, Nkv, Tk, HD, k_ts, 64, 1, BK))) return 7000 + r;
-        if ((r = make_tmap_3d(&tV64, v, HD, Nkv, Tk, HD, v_ts, 64, 1, BK))) return 8000 + r;
-        if (cudaFuncSetAttribute(fmha_bwd_dq_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDqTs) != cudaSuccess)
-            return -3;
-        fmha_bwd_dq_ts_kernel<<<dim3(mq, Nq), 320, kSmemDqTs, st>>>(tQ, tK64, tV64, tdO, p);
-    } else if (variant == 6) {      // dQ with Q / dO resident in tensor memory, 128-key steps, deeper K / V rings
-        if (cudaFuncSetAttribute(fmha_bwd_dq128ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDq6) != cudaSuccess)
-            return -3;
-        fmha_bwd_dq128ts_kernel<<<dim3(mq, Nq), 320, kSmemDq6, st>>>(tQ, tK, tV, tdO, p);
-    } else {
-        fmha_bwd_dq_kernel<<<dim3(mq, Nq), 320, kSmemDq, st>>>(tQ, tK, tV, tdO, p);
-    }
-    if (variant == 3) {      // dK/dV with every A operand in tensor memory (TS-form products)
-        if (cudaFuncSetAttribute(fmha_bwd_dkv_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkvTs) != cudaSuccess)
-            return -3;
-        fmha_bwd_dkv_ts_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkvTs, st>>>(tQ64, tK, tV, tdO64, pk);
-        return (int)cudaGetLastError();
-    }
-    if (variant == 5 || variant == 6) {      // dK/dV over 128-row query steps: all four products at N = 128
+    fmha_bwd_dq_kernel<<<dim3(mq, Nq), 320, kSmemDq, st>>>(tQ, tK, tV, tdO, p);
+    if (variant != 0) {      // dK/dV over 128-row query steps: all four products at N = 128
         if (cudaFuncSetAttribute(fmha_bwd_dkv128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkv128) != cudaSuccess)
             return -3;
         fmha_bwd_dkv128_kernel<<<dim3(mk, split_heads ? Nq : Nkv), 320, kSmemDkv128, st>>>(tQ, tK, tV, tdO, pk);

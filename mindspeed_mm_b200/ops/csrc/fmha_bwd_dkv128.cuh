@@ -256,8 +256,8 @@ fmha_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 mbar_arrive(ds_full);
             }
         }
-        bf16* dvp = p.dv + ((size_t)(k_begin + kj) * out_heads + out_head) * HD + half * 64;
-        bf16* dkp = p.dk + ((size_t)(k_begin + kj) * out_heads + out_head) * HD + half * 64;
+        bf16* dvp = p.dv + ((size_t)(k_begin + kj) * out_heads + out_head) * p.D + half * 64;
+        bf16* dkp = p.dk + ((size_t)(k_begin + kj) * out_heads + out_head) * p.D + half * 64;
         if (ok && n_it > 0 && mbar_wait(acc_full, 0, abort_flag)) {
             fence_after_sync();
 #pragma unroll
@@ -278,16 +278,19 @@ fmha_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                         x.y = pack2(__uint_as_float(b[g * 8 + 2]) * p.scale, __uint_as_float(b[g * 8 + 3]) * p.scale);
                         x.z = pack2(__uint_as_float(b[g * 8 + 4]) * p.scale, __uint_as_float(b[g * 8 + 5]) * p.scale);
                         x.w = pack2(__uint_as_float(b[g * 8 + 6]) * p.scale, __uint_as_float(b[g * 8 + 7]) * p.scale);
-                        reinterpret_cast<uint4*>(dvp)[c * 4 + g] = w;
-                        reinterpret_cast<uint4*>(dkp)[c * 4 + g] = x;
+                        if (half * 64 + c * 32 + g * 8 < p.D) {
+                            reinterpret_cast<uint4*>(dvp)[c * 4 + g] = w;
+                            reinterpret_cast<uint4*>(dkp)[c * 4 + g] = x;
+                        }
                     }
                 }
             }
         } else if (n_it == 0 && row_ok) {
-            for (int g = 0; g < 8; ++g) {
-                reinterpret_cast<uint4*>(dvp)[g] = make_uint4(0, 0, 0, 0);
-                reinterpret_cast<uint4*>(dkp)[g] = make_uint4(0, 0, 0, 0);
-            }
+            for (int g = 0; g < 8; ++g)
+                if (half * 64 + g * 8 < p.D) {
+                    reinterpret_cast<uint4*>(dvp)[g] = make_uint4(0, 0, 0, 0);
+                    reinterpret_cast<uint4*>(dkp)[g] = make_uint4(0, 0, 0, 0);
+                }
         }
         if (!ok && lane == 0) atomicExch(p.status, MM_TIMEOUT_EPI);
     }

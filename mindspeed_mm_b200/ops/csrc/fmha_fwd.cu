@@ -1,5 +1,8 @@
 // Flash attention forward on tcgen05 / TMEM / TMA: packed (varlen) sequences, GQA, optional causal mask,
-// head dim 128, bf16 in / bf16 out + fp32 log-sum-exp (for ring merging and for the backward pass).
+// head dim <= 128 (multiple of 8), bf16 in / bf16 out + fp32 log-sum-exp (for ring merging and for the backward pass).
+// Tiles are always 128 wide in shared memory: the tensor maps carry the true head dim, so for a narrower head (the
+// vision tower's 80) the TMA boxes read zeros beyond it (out-of-range fill) and the stores skip those columns; nothing
+// is padded in global memory.
 //
 // One CTA = one 128-row query tile of one head.  It walks the 128-key tiles of its sequence:
 //   warp 0      TMA producer: Q once, then K_j / V_j into 3-stage rings (128B-swizzled boxes of 64 x 128)
@@ -35,6 +38,7 @@ struct FmhaParams {
     bf16* o;
     float* lse;         // [Nq, T]
     int T, Nq, Nkv, causal;
+    int D;              // head dim of the tensors in global memory (<= HD)
     float scale_log2;   // softmax scale * log2(e)
     int* status;
 };
@@ -293,9 +297,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (ok && mbar_wait(fin, 0, abort_flag) && qi < q_len && n_kv > 0) {
             const float lsum = l_final[row];
             const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-            bf16* dst = p.o + ((size_t)(q_begin + qi) * p.Nq + head) * HD;
+            bf16* dst = p.o + ((size_t)(q_begin + qi) * p.Nq + head) * p.D;
 #pragma unroll
             for (int g = 0; g < HD / 8; ++g) {
+                if (g * 8 >= p.D) break;
                 float f[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) f[i] = acc[g * 8 + i] * inv;
@@ -331,12 +336,12 @@ MM_API int mm_fmha_set_fwd_variant(int v) {
 // Scratch needed by the planner: 2 * max_tiles + 1 ints, max_tiles = T / 128 + n_seqs.
 MM_API int mm_fmha_max_tiles(int T, int n_seqs) { return T / BQ + n_seqs + 1; }
 
-// q: [T, Nq, 128] with q_ts elements between tokens (heads dense); k, v: [T, Nkv, 128] likewise; o: [T, Nq, 128]
+// q: [T, Nq, D] with q_ts elements between tokens (heads dense); k, v: [T, Nkv, D] likewise; o: [T, Nq, D]
 // dense; lse: [Nq, T] fp32; cu_q / cu_k: int32 [n_seqs + 1] on the device; plan: int32 scratch (see above).
 MM_API int mm_fmha_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_q, const int* cu_k,
                        int* plan, int T, int Tk, int n_seqs, int Nq, int Nkv, int D, long long q_ts, long long k_ts,
                        long long v_ts, int causal, float scale, int* status, cudaStream_t st) {
-    if (D != HD || Nq % Nkv || (q_ts | k_ts | v_ts) % 8) return -1;
+    if (D > HD || D < 8 || D % 8 || Nq % Nkv || (q_ts | k_ts | v_ts) % 8) return -1;
     if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o) & 15) return -2;
     const int max_tiles = mm_fmha_max_tiles(T, n_seqs);
     int* tile_seq = plan;
@@ -345,33 +350,24 @@ MM_API int mm_fmha_fwd(const void* q, const void* k, const void* v, void* o, flo
     fmha_plan_kernel<<<1, 32, 0, st>>>(cu_q, n_seqs, tile_seq, tile_q0, n_tiles, max_tiles);
     CUtensorMap tQ, tK, tV;
     int r;
-    if ((r = make_tmap_3d(&tQ, q, HD, Nq, T, HD, q_ts, 64, 1, BQ))) return 1000 + r;
-    if ((r = make_tmap_3d(&tK, k, HD, Nkv, Tk, HD, k_ts, 64, 1, BKV))) return 2000 + r;
-    if ((r = make_tmap_3d(&tV, v, HD, Nkv, Tk, HD, v_ts, 64, 1, BKV))) return 3000 + r;
+    if ((r = make_tmap_3d(&tQ, q, D, Nq, T, D, q_ts, 64, 1, BQ))) return 1000 + r;
+    if ((r = make_tmap_3d(&tK, k, D, Nkv, Tk, D, k_ts, 64, 1, BKV))) return 2000 + r;
+    if ((r = make_tmap_3d(&tV, v, D, Nkv, Tk, D, v_ts, 64, 1, BKV))) return 3000 + r;
     static bool done = false;
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(fmha_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(fmha_fwd_split_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(fmha_fwd_split_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(fmha_fwd_split_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
 
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
-    FmhaParams p{cu_q, cu_k, tile_seq, tile_q0, n_tiles, (bf16*)o, lse, T, Nq, Nkv, causal,
+    FmhaParams p{cu_q, cu_k, tile_seq, tile_q0, n_tiles, (bf16*)o, lse, T, Nq, Nkv, causal, D,
                  scale * 1.4426950408889634f, status};
     dim3 grid(max_tiles, Nq);
-    if (g_fwd_variant == 1)
-        fmha_fwd_split_kernel<2><<<grid, 64 + 256, kSmem, st>>>(tQ, tK, tV, p);
-    else if (g_fwd_variant == 2)
-        fmha_fwd_split_kernel<4><<<grid, 64 + 512, kSmem, st>>>(tQ, tK, tV, p);
-    else if (g_fwd_variant == 3)
-        fmha_fwd_split_kernel<2, true><<<grid, 64 + 256, kSmem, st>>>(tQ, tK, tV, p);
-
-    else
+    if (g_fwd_variant == 0)      // fallback: one softmax warpgroup, O folded in registers
         fmha_fwd_kernel<<<grid, kThreads, kSmem, st>>>(tQ, tK, tV, p);
+    else                         // default: split softmax, O accumulated in tensor memory with lazy rescaling
+        fmha_fwd_split_kernel<2, true><<<grid, 64 + 256, kSmem, st>>>(tQ, tK, tV, p);
     return (int)cudaGetLastError();
 }

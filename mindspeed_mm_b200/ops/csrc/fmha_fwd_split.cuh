@@ -332,9 +332,10 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
             if (half == 0)
                 p.lse[(size_t)head * p.T + q_begin + qi] = (m == -INFINITY) ? -INFINITY : m * 0.6931471805599453f + logf(lsum);
-            bf16* dst = p.o + ((size_t)(q_begin + qi) * p.Nq + head) * HD + half * C;
+            bf16* dst = p.o + ((size_t)(q_begin + qi) * p.Nq + head) * p.D + half * C;
 #pragma unroll
             for (int g = 0; g < C / 8; ++g) {
+                if (half * C + g * 8 >= p.D) break;
                 float f[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) f[i] = acc[g * 8 + i] * inv;

@@ -169,8 +169,9 @@ __global__ void __launch_bounds__(256) p2p_rs_adamw_kernel(RSParams P, AdamParam
         __threadfence_system();
         st_release_sys(flag_ready(P.flags.p[P.rank], P.slot), P.seq);  // publish: my gradients are in place
     }
-    if (!rs_prologue(P)) return;
-    const long long nvec = P.shard_elems >> 3;
+    // A CTA whose wait ran out skips the reduction (the peer's gradients are not there) but still takes part in the
+    // epilogue: the arrival counter returns to zero and the slot is handed back, so the next launch on this slot works.
+    const long long nvec = rs_prologue(P) ? (P.shard_elems >> 3) : 0;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
         float g[8];
         reduce8(P, i, g);
@@ -203,8 +204,7 @@ __global__ void __launch_bounds__(256) p2p_rs_kernel(RSParams P, float* __restri
         __threadfence_system();
         st_release_sys(flag_ready(P.flags.p[P.rank], P.slot), P.seq);
     }
-    if (!rs_prologue(P)) return;
-    const long long nvec = P.shard_elems >> 3;
+    const long long nvec = rs_prologue(P) ? (P.shard_elems >> 3) : 0;   // see p2p_rs_adamw_kernel
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
         float g[8];
         reduce8(P, i, g);
@@ -225,6 +225,19 @@ __global__ void p2p_wait_done_kernel(void* my_flags, int slot, uint32_t seq, int
     if (threadIdx.x < world && threadIdx.x != rank) {
         if (!wait_flag_geq(flag_done(my_flags, slot, threadIdx.x), seq)) atomicExch(status, MM_TIMEOUT_PEER);
     }
+}
+
+// ------------------------------------------------------------------------------------------ arena barrier
+// bar[p] in MY block = the last barrier number that rank p has reached.  Arrival: write my number into my entry of
+// every rank's block (release, system scope: everything this stream wrote before the barrier is visible to a peer that
+// acquires the flag); then wait until every entry of my own block has reached the number.  The wait is bounded like
+// every other peer wait: on expiry MM_TIMEOUT_PEER goes to the status word and the kernel returns.
+__global__ void p2p_barrier_kernel(Peers bars, int world, int rank, uint32_t seq, int* status) {
+    const int p = threadIdx.x;
+    if (p >= world) return;
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(bars.p[p]) + rank, seq);
+    if (!wait_flag_geq(reinterpret_cast<const uint32_t*>(bars.p[rank]) + p, seq)) atomicExch(status, MM_TIMEOUT_PEER);
 }
 
 // ------------------------------------------------------------------------------------------ MoE row exchange
@@ -307,6 +320,15 @@ MM_API int mm_p2p_rs(void* const* grad_ptrs, void* const* flag_ptrs, long long s
     RSParams P{make_peers(grad_ptrs, world), make_peers(flag_ptrs, world), shard_elems, world, rank, slot, seq, inv_div,
                status, reinterpret_cast<uint32_t*>(flag_ptrs[rank]) + 2 + 2 * kMaxPeers};
     p2p_rs_kernel<<<ctas, 256, 0, st>>>(P, out, accumulate);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_p2p_barrier_bytes() { return kMaxPeers * 4; }
+
+// bar_ptrs[p]: address of rank p's barrier block (kMaxPeers uint32, zero at start); seq: 1, 2, 3, ... per arena.
+MM_API int mm_p2p_barrier(void* const* bar_ptrs, int world, int rank, unsigned seq, int* status, cudaStream_t st) {
+    if (world > kMaxPeers) return -1;
+    p2p_barrier_kernel<<<1, 32, 0, st>>>(make_peers(bar_ptrs, world), world, rank, seq, status);
     return (int)cudaGetLastError();
 }
 

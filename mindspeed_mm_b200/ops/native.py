@@ -17,9 +17,8 @@ from . import build as _build
 
 _LIB = None
 _STATUS: dict = {}
-# forward attention kernel (csrc/fmha_fwd_split.cuh): 3 = split softmax, O accumulated in tensor memory with lazy
-# rescaling (default); 1 = split softmax with a per-tile fold in registers; 2 = the same with four compute warpgroups;
-# 0 = one softmax warpgroup (csrc/fmha_fwd.cu)
+# forward attention kernel: 3 = split softmax, O accumulated in tensor memory with lazy rescaling
+# (csrc/fmha_fwd_split.cuh, default); 0 = one softmax warpgroup, O folded in registers (csrc/fmha_fwd.cu, fallback)
 FMHA_FWD_VARIANT = int(os.environ.get("MM_B200_FMHA_FWD_VARIANT", "3"))
 LAUNCHES = 0  # native kernel launches issued through this module (bench reports it)
 
@@ -45,6 +44,8 @@ def _declare(L):
         "mm_rmsnorm_bwd": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _p],
         "mm_swiglu_fwd": [_p, _p, _ll, _i, _p],
         "mm_swiglu_bwd": [_p, _p, _p, _ll, _i, _p],
+        "mm_gelu_fwd": [_p, _p, _ll, _i, _p],
+        "mm_gelu_bwd": [_p, _p, _p, _ll, _i, _p],
         "mm_rope_half": [_p, _ll, _p, _p, _p, _i, _i, _i, _i, _p],
         "mm_rope_interleaved": [_p, _ll, _p, _p, _p, _i, _i, _i, _i, _p],
         "mm_ln_mod_fwd": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _f, _p],
@@ -81,6 +82,8 @@ def _declare(L):
                             _p, _i, _p],
         "mm_p2p_rs": [_p, _p, _ll, _i, _i, _i, C.c_uint, _f, _p, _i, _p, _i, _p],
         "mm_p2p_wait_done": [_p, _i, C.c_uint, _i, _i, _p, _p],
+        "mm_p2p_barrier_bytes": [],
+        "mm_p2p_barrier": [_p, _i, _i, C.c_uint, _p, _p],
     }
     for name, args in sig.items():
         if hasattr(L, name):
@@ -99,6 +102,13 @@ def status() -> dict:
 
 def _st():
     return torch.cuda.current_stream().cuda_stream
+
+
+def _eager(op: str, x, why: str):
+    """An op of this module was called with a shape its kernel does not take: count it (or refuse, in strict mode)
+    through the front end's fallback register, then let the caller run the PyTorch form."""
+    from .. import ops as _ops
+    _ops._fallback(op, x, why)
 
 
 def _check(rc: int, what: str):
@@ -167,6 +177,7 @@ class _RMSNorm(torch.autograd.Function):
 def rms_norm(x, w, eps=1e-6):
     if x.shape[-1] % 8 or x.shape[-1] > 8192:
         from . import reference
+        _eager("rms_norm", x, f"H={x.shape[-1]}")
         return reference.rms_norm(x, w, eps)
     return _RMSNorm.apply(x, w, eps)
 
@@ -201,11 +212,36 @@ class _SwiGLU(torch.autograd.Function):
 def swiglu(gu):
     if (gu.shape[-1] // 2) % 8:
         from . import reference
+        _eager("swiglu", gu, f"F={gu.shape[-1] // 2}")
         return reference.swiglu(gu)
     return _SwiGLU.apply(gu)
 
 
 # --------------------------------------------------------------------------- RoPE
+class _Gelu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, tanh):
+        xc = x.contiguous()
+        y = torch.empty_like(xc)
+        _check(lib().mm_gelu_fwd(xc.data_ptr(), y.data_ptr(), xc.numel(), int(tanh), _st()), "gelu_fwd")
+        ctx.save_for_backward(xc)
+        ctx.tanh = tanh
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        dyc = dy.contiguous()
+        dx = torch.empty_like(x)
+        _check(lib().mm_gelu_bwd(x.data_ptr(), dyc.data_ptr(), dx.data_ptr(), x.numel(), int(ctx.tanh), _st()), "gelu_bwd")
+        return dx.view(dy.shape), None
+
+
+def gelu(x, tanh: bool = True):
+    """bf16 GELU (tanh approximation or exact erf form); element count a multiple of 8."""
+    return _Gelu.apply(x, bool(tanh))
+
+
 def _rope_call(x, cos, sin, interleaved, backward):
     # x: [T, N, D] whose last two dims are dense; the token stride may be larger (view into fused qkv)
     T, N, D = x.shape
@@ -239,11 +275,13 @@ def rope(x, cos, sin, interleaved: bool):
     if interleaved:
         if D % 8:
             from . import reference
+            _eager("rope_interleaved", x, f"D={D}")
             return reference.rope_interleaved(x, cos, sin)
         cos, sin = cos.float().contiguous(), sin.float().contiguous()
     else:
         if D % 16:
             from . import reference
+            _eager("rope_rotate_half", x, f"D={D}")
             return reference.rope_rotate_half(x, cos, sin)
         cos, sin = cos.to(torch.bfloat16).contiguous(), sin.to(torch.bfloat16).contiguous()
     return _Rope.apply(x, cos, sin, interleaved)
@@ -284,8 +322,22 @@ def layer_norm_modulate(x, scale, shift, eps=1e-6):
     """x: [B, S, H]; scale/shift: [B, 1, H] or [B, H]."""
     if x.dim() != 3 or x.shape[-1] % 8 or x.shape[-1] > 8192 or scale.numel() != x.shape[0] * x.shape[-1]:
         from . import reference
+        _eager("layer_norm_modulate", x, f"x {tuple(x.shape)} scale {tuple(scale.shape)}")
         return reference.layer_norm_modulate(x, scale, shift, eps)
     return _LNMod.apply(x, scale.to(x.dtype), shift.to(x.dtype), eps)
+
+
+def layer_norm(x, weight=None, bias=None, eps=1e-6):
+    """LayerNorm over the last dim of a bf16 tensor through the LayerNorm-modulate kernels: all rows form one batch,
+    ``scale = weight - 1`` and ``shift = bias`` (zeros when absent), so ``LN(x) * (1 + scale) + shift`` is the affine
+    LayerNorm.  Gradients of weight / bias come out of the kernel's per-batch scale / shift reductions."""
+    H = x.shape[-1]
+    if weight is not None:
+        scale = (weight.float() - 1.0).to(x.dtype).view(1, H)
+    else:
+        scale = torch.zeros(1, H, dtype=x.dtype, device=x.device)
+    shift = bias.to(x.dtype).view(1, H) if bias is not None else torch.zeros(1, H, dtype=x.dtype, device=x.device)
+    return _LNMod.apply(x.reshape(1, -1, H), scale, shift, eps).view(x.shape)
 
 
 class _GatedResidual(torch.autograd.Function):
@@ -312,6 +364,7 @@ class _GatedResidual(torch.autograd.Function):
 def gated_residual(x, y, gate):
     if x.dim() != 3 or x.shape[-1] % 8 or gate.numel() != x.shape[0] * x.shape[-1]:
         from . import reference
+        _eager("gated_residual", x, f"x {tuple(x.shape)} gate {tuple(gate.shape)}")
         return reference.gated_residual(x, y, gate)
     return _GatedResidual.apply(x, y, gate.to(x.dtype))
 
@@ -466,8 +519,11 @@ def linear(x, w, bias=None, skip_value=False):
 
 # --------------------------------------------------------------------------- not yet native
 def fmha_supported(q, k, v) -> bool:
-    return (os.environ.get("MM_B200_FMHA", "1") == "1" and q.dtype == torch.bfloat16 and q.shape[-1] == 128
-            and v.shape[-1] == 128 and q.shape[1] % k.shape[1] == 0)
+    """bf16, one head dim for q / k / v, at most 128 and a multiple of 8 (the kernels work on 128-wide tiles; a narrower
+    head, e.g. the vision tower's 80, is zero-filled by the TMA loads, not padded in memory), GQA groups whole."""
+    D = q.shape[-1]
+    return (os.environ.get("MM_B200_FMHA", "1") == "1" and q.dtype == torch.bfloat16 and D <= 128 and D % 8 == 0
+            and k.shape[-1] == D and v.shape[-1] == D and q.shape[1] % k.shape[1] == 0)
 
 
 def _dense_heads(t):
@@ -497,9 +553,7 @@ def fmha_forward(q, k, v, cu_q, cu_k, causal, scale):
     return out, lse
 
 
-# 0: both warpgroups share a 128-wide tile (faster as measured); 1: ping-pong schedule over 64-wide tiles
-# backward kernels: 5 = dQ kernel + dK/dV kernel over 128-row query steps (default); 0 = dK/dV over 64-row steps;
-# 1-4 = the ping-pong / all-TS experiments kept for reference
+# backward kernels: dQ kernel + dK/dV kernel over 128-row query steps (5, default) or over 64-row steps (0, fallback)
 FMHA_BWD_VARIANT = int(os.environ.get("MM_B200_FMHA_BWD_VARIANT", "5"))
 FMHA_BWD = os.environ.get("MM_B200_FMHA_BWD", "native")     # "native" (tcgen05 kernels) or "flash" (flash-attn library)
 

@@ -529,7 +529,15 @@ class FSDPEngine:
                     g.shard16.copy_(src)
                 if g.trainable:
                     g.master.copy_(src)
+        self.sync_after_load()
         return missing
+
+    def sync_after_load(self) -> None:
+        """With peer-memory collectives the bf16 shards live in the symmetric arena and a peer's gather kernel reads
+        them without any flag: after the shards were written from the host side (weight load, checkpoint load) every
+        rank waits here until all ranks have finished writing, before anyone gathers."""
+        if self._p2p is not None:
+            self._p2p.sync_after_load()
 
     def sharded_state(self) -> dict:
         out = {}
@@ -537,22 +545,24 @@ class FSDPEngine:
             for gi, g in enumerate(u.groups):
                 k = f"{u.name}#{gi}"
                 out[k] = dict(shard16=g.shard16, master=g.master, exp_avg=g.exp_avg, exp_avg_sq=g.exp_avg_sq,
-                              step=g.step_count, world=self.world, numel=g.numel)
+                              step=g.step_count, world=self.world, rank=self.rank, numel=g.numel)
         return out
 
     def load_sharded_state(self, state: dict, load_optim: bool = True) -> None:
         for u in self.units:
             for gi, g in enumerate(u.groups):
                 s = state[f"{u.name}#{gi}"]
-                if s["world"] != self.world:
-                    raise ValueError("sharded state was saved with a different world size; load the full format")
+                if s["world"] != self.world or s.get("rank", self.rank) != self.rank:
+                    raise ValueError("sharded state was saved for another rank / size of the sharding group; "
+                                     "load it through the checkpointer (it re-slices) or use the full format")
                 g.shard16.copy_(s["shard16"])
                 if g.trainable:
-                    g.master.copy_(s["master"] if s["master"] is not None else s["shard16"])
-                    if load_optim and s["exp_avg"] is not None:
+                    g.master.copy_(s["master"] if s.get("master") is not None else s["shard16"])
+                    if load_optim and s.get("exp_avg") is not None:
                         g.exp_avg.copy_(s["exp_avg"])
                         g.exp_avg_sq.copy_(s["exp_avg_sq"])
                         g.step_count = s["step"]
+        self.sync_after_load()
 
     def param_count(self) -> int:
         return sum(g.numel for u in self.units for g in u.groups)
@@ -680,8 +690,10 @@ class EngineMux:
     (fsdp/distributed/expert_parallel/expert_fully_shard_parallel.py:22-57, fsdp/optimizer/optimizer.py:374-520).
     Expert modules find their engine through ``module._fsdp_run``."""
 
-    def __init__(self, dense: FSDPEngine, expert: FSDPEngine):
+    def __init__(self, dense: FSDPEngine, expert: FSDPEngine, ep_group: Optional[dist.ProcessGroup] = None):
         self.dense, self.expert = dense, expert
+        # ranks that hold DIFFERENT experts: the expert part of the global gradient norm is summed over it
+        self.ep_group = ep_group
         for u in expert.units:
             u.recompute = False
             u.module._fsdp_run = expert.run
@@ -710,7 +722,7 @@ class EngineMux:
     def finish_step(self, lr=None):
         """Joint gradient clipping: the global norm combines both engines' squared norms."""
         if self.dense.opt.clip_grad > 0:
-            return _joint_clip_finish(self.engines)
+            return _joint_clip_finish(self.engines, {id(self.expert): self.ep_group})
         norms = [e.finish_step(lr) for e in self.engines]
         return norms[0]
 
@@ -727,26 +739,40 @@ class EngineMux:
             out.update({f"{tag}/{k}": v for k, v in e.sharded_state().items()})
         return out
 
+    def load_sharded_state(self, state: dict, load_optim: bool = True) -> None:
+        """Inverse of ``sharded_state``: strips the ``dense/`` / ``expert/`` tag and hands each engine its records."""
+        for tag, e in zip(("dense", "expert"), self.engines):
+            pre = tag + "/"
+            e.load_sharded_state({k[len(pre):]: v for k, v in state.items() if k.startswith(pre)}, load_optim=load_optim)
+
     def param_count(self):
         return sum(e.param_count() for e in self.engines)
 
 
-def _joint_clip_finish(engines):
-    """Deferred update of several engines under ONE clip coefficient (EP params reduce over their own
-    groups first: fsdp/optimizer/clip_grad_norm.py:69-116)."""
+def _joint_clip_finish(engines, extra_groups: Optional[dict] = None):
+    """Deferred update of several engines under ONE clip coefficient.  The squared norm of an engine's gradients is
+    summed over its own sharding group; for expert parameters it is summed once more over the expert-parallel group
+    (``extra_groups[id(engine)]``), because ranks of that group hold different experts.  The total is then identical
+    on every rank (reference: fsdp/optimizer/clip_grad_norm.py:69-116, expert norms reduced over ep_fsdp, then ep)."""
+    extra_groups = extra_groups or {}
     total = None
     for e in engines:
         e.flush_pending()
         if e.cuda:
             torch.cuda.current_stream().wait_stream(e.comm_stream)
         groups = [g for u in e.units for g in u.groups if g.trainable and g.grad32 is not None]
-        if not groups:
-            continue
-        sq = torch.stack([g.grad32.float().pow(2).sum() for g in groups]).sum() / (e.grad_accum_steps ** 2)
+        if groups:
+            sq = torch.stack([g.grad32.float().pow(2).sum() for g in groups]).sum() / (e.grad_accum_steps ** 2)
+        else:       # still take part in the collectives below
+            sq = torch.zeros((), dtype=torch.float32, device=e.device)
         if e.world > 1:
             dist.all_reduce(sq, group=e.group)
+        eg = extra_groups.get(id(e))
+        if eg is not None and dist.get_world_size(eg) > 1:
+            dist.all_reduce(sq, group=eg)
         total = sq if total is None else total + sq
-    # expert shards differ across EP ranks: sum their squared norms over the whole world once
+    if total is None:
+        return None
     norm = total.sqrt()
     clip = engines[0].opt.clip_grad
     scale = torch.clamp(clip / (norm + 1e-6), max=1.0)
@@ -758,4 +784,5 @@ def _joint_clip_finish(engines):
                     g.grad32 = None
         if e._p2p is not None:
             e._p2p.step_barrier()
+        e.last_grad_norm = norm
     return norm

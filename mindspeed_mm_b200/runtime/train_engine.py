@@ -44,11 +44,18 @@ class TrainConfig:
     check_for_nan: bool = True
 
 
+class NativeKernelTimeout(RuntimeError):
+    """A native kernel gave up a bounded wait (on a peer flag, an mbarrier, the arena barrier) during the step that
+    just ended: its outputs are incomplete, so the run stops instead of training on them.  ``exit_code`` is the code
+    the host watchdog uses for a stalled step."""
+    exit_code = 3
+
+
 class TrainEngine:
     def __init__(self, model, engine: FSDPEngine, loss_fn: Callable, schedule: LRSchedule, cfg: TrainConfig,
                  data_iter: Optional[Iterable] = None, val_iter_fn: Optional[Callable[[], Iterable]] = None,
                  checkpointer=None, profiler=None, memory_profiler=None, watchdog=None, dp_group=None,
-                 dp_world: int = 1, device="cpu"):
+                 dp_world: int = 1, device="cpu", status_word: Optional[torch.Tensor] = None):
         self.model, self.engine, self.loss_fn, self.schedule, self.cfg = model, engine, loss_fn, schedule, cfg
         self.data_iter, self.val_iter_fn = data_iter, val_iter_fn
         self.checkpointer, self.profiler, self.memory_profiler, self.watchdog = \
@@ -64,6 +71,13 @@ class TrainEngine:
         self._sigterm = False
         self._t_start = time.time()
         self.history: List[Dict[str, float]] = []
+        # int32[1] that kernels write when a bounded wait expires (0 = fine); read once per iteration in train()
+        self.status_word = status_word
+        if status_word is None and self.device.type == "cuda":
+            from .. import ops
+            if ops.get_tier() == "native":
+                from ..ops import native
+                self.status_word = native.status_word(self.device)
 
     # ---------------------------------------------------------------------------------- one step
     def forward_backward(self, batch: dict) -> Dict[str, torch.Tensor]:
@@ -107,6 +121,21 @@ class TrainEngine:
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
 
+    def check_kernel_status(self) -> None:
+        """Read the kernels' status word at an iteration boundary (the device is already synchronised there), take the
+        maximum over all ranks so that every rank stops in the same iteration, and raise when it is not zero."""
+        if self.status_word is None:
+            return
+        st = self.status_word
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            st = st.clone()
+            dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        code = int(st.item())
+        if code != 0:
+            self.status_word.zero_()
+            raise NativeKernelTimeout(f"a native kernel gave up a bounded wait in iteration {self.iteration} "
+                                      f"(status {code}); stopping before the next step")
+
     def train(self) -> List[Dict[str, float]]:
         cfg = self.cfg
         prev = signal.getsignal(signal.SIGTERM)
@@ -129,6 +158,7 @@ class TrainEngine:
                 mbs = [next(it) for _ in range(cfg.gradient_accumulation_steps)]
                 r = self.train_step(mbs)
                 self._sync()
+                self.check_kernel_status()
                 dt = time.time() - t0
                 loss = float(r["loss"])
                 if cfg.check_for_nan and not math.isfinite(loss):

@@ -31,7 +31,7 @@ from .logging import print_rank0
 from .loss import build_loss
 from .lr_scheduler import LRSchedule
 from .tools import MemoryProfiler, Profiler, Watchdog
-from .train_engine import TrainConfig, TrainEngine
+from .train_engine import NativeKernelTimeout, TrainConfig, TrainEngine
 
 
 def set_seed(seed: int, deterministic: bool = False) -> None:
@@ -138,7 +138,7 @@ class Trainer:
         eg = self.ps.group("efsdp") if self.ps.size("efsdp") > 1 else False
         expert = FSDPEngine(expert_units, group=eg, grad_divide=self.ps.get_dp_world_size(), no_recompute=(),
                             comm="nccl", **common)
-        return EngineMux(dense, expert)
+        return EngineMux(dense, expert, ep_group=self.ps.group("ep") if self.ps.size("ep") > 1 else None)
 
     def load_weights(self):
         t = self.args.training
@@ -210,7 +210,11 @@ def main(argv=None):
         raise SystemExit("usage: trainer.py config.yaml [key=value ...]")
     args = load_config(argv[0], argv[1:])
     tr = Trainer(args)
-    tr.train()
+    try:
+        tr.train()
+    except NativeKernelTimeout as e:
+        print(f"[rank {dist.get_rank() if dist.is_initialized() else 0}] {e}", file=sys.stderr, flush=True)
+        os._exit(e.exit_code)          # peers may be gone: no collective shutdown
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()

@@ -11,11 +11,32 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def _close(a, b, rtol=2e-2, atol=2e-2):
+def _close(a, b, rtol=2e-2, atol=2e-2, rel_l2=1e-2, tile=128):
+    """Three checks against the fp32 reference ``b``:
+    * whole tensor: max |a - b| <= atol + rtol * max |b|
+    * relative L2 error <= ``rel_l2`` (bf16 outputs of fp32-accumulated kernels sit near 3e-3), which a dropped K slice
+      or a systematically wrong scale cannot meet
+    * every ``tile`` x ``tile`` block of the 2-D view on its own: max error of the block <= rtol * max |b| of that
+      block + 1e-3 * max |b| of the tensor, so a zeroed or stale tile of small values fails although it would hide
+      under the whole-tensor maximum."""
     a, b = a.float(), b.float()
     err = (a - b).abs().max().item()
     scale = b.abs().max().item() + 1e-6
     assert err <= atol + rtol * scale, f"max err {err} vs scale {scale}"
+    if rel_l2 is not None and b.numel() > 1:
+        l2 = ((a - b).norm() / (b.norm() + 1e-12)).item()
+        assert l2 <= rel_l2 or (a - b).abs().max().item() <= atol * 1e-2, f"relative L2 error {l2} > {rel_l2}"
+    if tile and a.dim() >= 2 and a.shape[-1] >= tile:
+        a2, b2 = a.reshape(-1, a.shape[-1]), b.reshape(-1, b.shape[-1])
+        R, Cc = a2.shape
+        pr, pc = (-R) % tile, (-Cc) % tile
+        e2 = torch.nn.functional.pad((a2 - b2).abs(), (0, pc, 0, pr))
+        s2 = torch.nn.functional.pad(b2.abs(), (0, pc, 0, pr))
+        e_t = e2.view((R + pr) // tile, tile, (Cc + pc) // tile, tile).amax(dim=(1, 3))
+        s_t = s2.view((R + pr) // tile, tile, (Cc + pc) // tile, tile).amax(dim=(1, 3))
+        bad = e_t > rtol * s_t + 1e-3 * scale + 1e-6
+        assert not bool(bad.any()), (f"{int(bad.sum())} of {bad.numel()} {tile}x{tile} tiles off; worst tile error "
+                                     f"{float(e_t[bad].max())} against tile scale {float(s_t[bad][e_t[bad].argmax()])}")
 
 
 @pytest.fixture(autouse=True)
@@ -143,7 +164,7 @@ def test_gemm_nt(M, N, K):
     bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
     c = native.gemm_nt(a, b, bias)
     r = a.float() @ b.float().t() + bias.float()
-    _close(c, r, rtol=1e-2, atol=1e-2 * math.sqrt(K))
+    _close(c, r, rtol=1e-2, atol=1e-2)
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
@@ -153,7 +174,7 @@ def test_gemm_nn(M, N, K):
     a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
     b = torch.randn(K, N, device=DEV, dtype=torch.bfloat16)
     c = native.gemm_nn(a, b)
-    _close(c, a.float() @ b.float(), rtol=1e-2, atol=1e-2 * math.sqrt(K))
+    _close(c, a.float() @ b.float(), rtol=1e-2, atol=1e-2)
 
 
 @pytest.mark.parametrize("M,N,K", [(m, n, k) for m, n, k in GEMM_SHAPES if m % 8 == 0])
@@ -163,7 +184,7 @@ def test_gemm_tn(M, N, K):
     a = torch.randn(K, M, device=DEV, dtype=torch.bfloat16)
     b = torch.randn(K, N, device=DEV, dtype=torch.bfloat16)
     c = native.gemm_tn(a, b)
-    _close(c, a.float().t() @ b.float(), rtol=1e-2, atol=1e-2 * math.sqrt(K))
+    _close(c, a.float().t() @ b.float(), rtol=1e-2, atol=1e-2)
 
 
 def test_linear_autograd():
@@ -179,8 +200,8 @@ def test_linear_autograd():
     yr.backward(dy.float())
     _close(y, yr)
     _close(x.grad, xr.grad)
-    _close(w.grad, wr.grad, atol=0.5)
-    _close(b.grad, br.grad, atol=0.5)
+    _close(w.grad, wr.grad)
+    _close(b.grad, br.grad)
 
 
 @pytest.mark.parametrize("T,H,V", [(300, 512, 32000), (1024, 1024, 152064)])
@@ -228,9 +249,9 @@ def test_fmha_forward_and_grad(lens, nq, nkv, causal):
     _close(vg.grad, vr.grad, rtol=3e-2, atol=3e-2)
 
 
-@pytest.mark.parametrize("fwd_variant,bwd_variant", [(0, 0), (1, 6), (2, 5), (3, 5)])
+@pytest.mark.parametrize("fwd_variant,bwd_variant", [(0, 0), (3, 5)])
 def test_fmha_kernel_variants_agree_with_reference(fwd_variant, bwd_variant):
-    """The non-default forward / backward kernels stay correct: GQA + causal, ragged packing."""
+    """The fallback forward / backward kernels stay correct beside the defaults: GQA + causal, ragged packing."""
     from mindspeed_mm_b200.ops import native
     torch.manual_seed(0)
     lens, nq, nkv, D = [300, 129, 700], 4, 2, 128
@@ -257,21 +278,34 @@ def test_fmha_kernel_variants_agree_with_reference(fwd_variant, bwd_variant):
     _close(vg.grad, vr.grad, rtol=3e-2, atol=3e-2)
 
 
-def test_attention_head_dim_80_padded_onto_native_kernels():
-    """ViT heads (D = 80) with window-sized segments: zero-padded to 128 and run by the tcgen05 forward / backward."""
+@pytest.mark.parametrize("D,lens,N,strided", [
+    (80, [64] * 20 + [37, 256], 16, False),      # vision tower: 64-token windows, a ragged one, a full-image segment
+    (80, [1024, 1024, 400], 16, True),           # vision tower full-attention layers, q/k/v views of a fused projection
+    (64, [300, 129, 700], 4, False),
+    (96, [130, 257], 2, False),
+])
+def test_attention_narrow_heads_run_the_tcgen05_kernels(D, lens, N, strided):
+    """Head dims below 128 (a multiple of 8) run the same 128-wide kernels: the tensor maps carry the true head dim,
+    TMA fills the missing columns with zeros and the stores skip them.  Nothing is padded in global memory and no
+    library kernel runs (strict mode)."""
     from mindspeed_mm_b200.ops import native
-    ops._PAD_SMALL_HEADS = True          # opt-in path (off by default for speed)
     torch.manual_seed(0)
-    lens = [64] * 20 + [37, 256]
-    T, N, D = sum(lens), 16, 80
+    T = sum(lens)
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
-    q, k, v = (torch.randn(T, N, D, device=DEV, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+    if strided:
+        qkv = torch.randn(T, 3, N, D, device=DEV, dtype=torch.bfloat16)
+        q, k, v = (t.detach().requires_grad_() for t in qkv.unbind(1))
+    else:
+        q, k, v = (torch.randn(T, N, D, device=DEV, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
     before = native.LAUNCHES
-    o = ops.attention_varlen(q, k, v, cu, cu, max(lens), max(lens), causal=False)
-    do = torch.randn_like(o)
-    o.backward(do)
-    ops._PAD_SMALL_HEADS = False
-    assert native.LAUNCHES > before
+    ops.set_strict(True)
+    try:
+        o = ops.attention_varlen(q, k, v, cu, cu, max(lens), max(lens), causal=False)
+        do = torch.randn_like(o)
+        o.backward(do)
+    finally:
+        ops.set_strict(False)
+    assert native.LAUNCHES > before and o.shape == (T, N, D)
     qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
     orf = ref.attention_varlen(qr, kr, vr, cu.cpu(), cu.cpu(), False)
     orf.backward(do.float())
@@ -279,6 +313,61 @@ def test_attention_head_dim_80_padded_onto_native_kernels():
     _close(q.grad, qr.grad, rtol=3e-2, atol=3e-2)
     _close(k.grad, kr.grad, rtol=3e-2, atol=3e-2)
     _close(v.grad, vr.grad, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("tanh", [True, False])
+def test_gelu_fwd_bwd(tanh):
+    torch.manual_seed(0)
+    x = (3 * torch.randn(333, 1280, device=DEV)).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(333, 1280, device=DEV, dtype=torch.bfloat16)
+    y = ops.gelu_tanh(x) if tanh else ops.gelu(x)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    yr = torch.nn.functional.gelu(xr, approximate="tanh" if tanh else "none")
+    yr.backward(dy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad)
+
+
+@pytest.mark.parametrize("shape,affine", [((2, 300, 1280), True), ((777, 5120), True), ((64, 1152), False)])
+def test_layer_norm_affine_fwd_bwd(shape, affine):
+    torch.manual_seed(0)
+    H = shape[-1]
+    x = torch.randn(*shape, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16).requires_grad_() if affine else None
+    b = (0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16).requires_grad_() if affine else None
+    dy = torch.randn(*shape, device=DEV, dtype=torch.bfloat16)
+    ops.set_strict(True)
+    try:
+        y = ops.layer_norm(x, w, b, 1e-6)
+        y.backward(dy)
+    finally:
+        ops.set_strict(False)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_() if affine else None
+    br = b.detach().float().requires_grad_() if affine else None
+    yr = torch.nn.functional.layer_norm(xr, (H,), wr, br, 1e-6)
+    yr.backward(dy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad, rtol=3e-2)
+    if affine:
+        _close(w.grad, wr.grad, rtol=3e-2, tile=0)
+        _close(b.grad, br.grad, rtol=3e-2, tile=0)
+
+
+def test_fallback_register_counts_and_strict_mode_refuses():
+    """A call the kernels do not take (fp32 activations here) is counted by op name; strict mode raises instead."""
+    x = torch.randn(8, 64, device=DEV)            # fp32: no kernel
+    w = torch.ones(64, device=DEV)
+    ops.library_fallbacks(reset=True)
+    ops.rms_norm(x, w)
+    assert ops.library_fallbacks(reset=True) == {"rms_norm": 1}
+    ops.set_strict(True)
+    try:
+        with pytest.raises(RuntimeError):
+            ops.rms_norm(x, w)
+    finally:
+        ops.set_strict(False)
 
 
 def test_fmha_backward_cross_attention_shapes():
@@ -473,3 +562,73 @@ def test_peer_flag_wait_runs_out_and_reports_status():
     w = torch.ones(512, device=dev, dtype=torch.bfloat16)
     _close(ops.rms_norm(x, w), ref.rms_norm(x.float(), w.float()))
     assert int(native.status_word(dev).item()) == 0
+
+
+def test_arena_barrier_wait_runs_out_then_passes():
+    """The arena barrier is a kernel with a bounded wait: with a "peer" that never arrives (its flag lives in local
+    memory and nothing writes it) the kernel gives up, reports MM_TIMEOUT_PEER and returns; once the flag is there the
+    next barrier passes."""
+    import ctypes as C
+    from mindspeed_mm_b200.ops import native
+    L = native.lib()
+    dev = torch.device(DEV)
+    n = L.mm_p2p_barrier_bytes() // 4
+    blocks = torch.zeros(2, n, dtype=torch.int32, device=dev)        # rank 0's block (mine) and rank 1's
+    ptrs = (C.c_void_p * 2)(blocks[0].data_ptr(), blocks[1].data_ptr())
+    st = native.status_word(dev)
+    assert L.mm_p2p_set_wait_limit(1 << 27) == 0
+    try:
+        st.zero_()
+        assert L.mm_p2p_barrier(ptrs, 2, 0, 1, st.data_ptr(), native._st()) == 0
+        torch.cuda.synchronize()
+        assert int(st.item()) == 4
+        assert blocks[0, 0].item() == 1 and blocks[1, 0].item() == 1     # my arrival was published to both blocks
+        st.zero_()
+        blocks[0, 1] = 2                                                  # the peer arrives at barrier 2
+        assert L.mm_p2p_barrier(ptrs, 2, 0, 2, st.data_ptr(), native._st()) == 0
+        torch.cuda.synchronize()
+        assert int(st.item()) == 0
+    finally:
+        assert L.mm_p2p_set_wait_limit(0) == 0
+        st.zero_()
+
+
+def test_reduce_scatter_time_out_leaves_the_slot_usable():
+    """A reduce-scatter launch whose peer never publishes its gradients skips the reduction, reports the time-out,
+    and still completes its counter / done-flag protocol: the next launch on the same slot, with the peer present,
+    reduces correctly."""
+    import ctypes as C
+    from mindspeed_mm_b200.ops import native
+    L = native.lib()
+    dev = torch.device(DEV)
+    nflag = L.mm_p2p_flag_bytes() // 4
+    flags = torch.zeros(2, nflag, dtype=torch.int32, device=dev)     # my flag block and the "peer's" (local memory)
+    S = 1 << 14
+    torch.manual_seed(0)
+    g0 = torch.randn(2 * S, device=dev, dtype=torch.bfloat16)
+    g1 = torch.randn(2 * S, device=dev, dtype=torch.bfloat16)
+    gp = (C.c_void_p * 2)(g0.data_ptr(), g1.data_ptr())
+    fp = (C.c_void_p * 2)(flags[0].data_ptr(), flags[1].data_ptr())
+    out = torch.zeros(S, dtype=torch.float32, device=dev)
+    st = native.status_word(dev)
+    counter_idx, done_idx = 2 + 2 * 16, 2                            # ready[2] | done[2][16] | counter
+    assert L.mm_p2p_set_wait_limit(1 << 27) == 0
+    try:
+        st.zero_()
+        assert L.mm_p2p_rs(gp, fp, S, 2, 0, 0, 1, 0.5, out.data_ptr(), 0, st.data_ptr(), 8, native._st()) == 0
+        torch.cuda.synchronize()
+        assert int(st.item()) == 4
+        assert float(out.abs().max()) == 0.0                           # the reduction was skipped
+        assert flags[0, counter_idx].item() == 0                      # arrival counter is back to zero
+        assert flags[1, done_idx + 0].item() == 1                     # slot handed back: done[slot 0][rank 0] = seq
+        st.zero_()
+        flags[1, 0] = 2                                               # the peer publishes ready[slot 0] = 2
+        assert L.mm_p2p_rs(gp, fp, S, 2, 0, 0, 2, 0.5, out.data_ptr(), 0, st.data_ptr(), 8, native._st()) == 0
+        torch.cuda.synchronize()
+        assert int(st.item()) == 0
+        want = (g0[:S].float() + g1[:S].float()) * 0.5
+        assert torch.allclose(out, want, rtol=1e-6, atol=1e-6)
+        assert flags[1, done_idx + 0].item() == 2
+    finally:
+        assert L.mm_p2p_set_wait_limit(0) == 0
+        st.zero_()

@@ -113,3 +113,33 @@ def test_trainer_runs_speech_lm_recipes(capsys):
         args = load_config(os.path.join(ROOT, rel), ["training.train_iters=3"], world_size=1)
         hist = Trainer(args, device="cpu").train()
         assert len(hist) == 3 and all(h["loss"] == h["loss"] and h["loss"] > 0 for h in hist), rel
+
+
+def test_training_loop_stops_when_a_kernel_reported_a_timeout():
+    """The loop reads the kernels' status word at every iteration boundary; a non-zero word (a bounded device wait
+    expired during the step) ends the run before the next step instead of training on incomplete tensors."""
+    import pytest
+    from mindspeed_mm_b200.runtime.train_engine import NativeKernelTimeout
+    from mindspeed_mm_b200.runtime.trainer import Trainer
+    args = load_config(os.path.join(ROOT, "examples/qwen2.5vl/tiny_native.yaml"),
+                       ["training.train_iters=4", "model.config.text.num_layers=1", "model.config.vision.depth=1",
+                        "model.config.vision.fullatt_block_indexes=[0]",
+                        "data.dataset_param.basic_parameters.seq_len=300",
+                        "data.dataset_param.basic_parameters.images_per_sample=1", "training.micro_batch_size=1"],
+                       world_size=1)
+    tr = Trainer(args, device="cpu")
+    word = torch.zeros(1, dtype=torch.int32)
+    tr.train_engine.status_word = word
+    real_step = tr.train_engine.train_step
+
+    def step_with_timeout(mbs):
+        r = real_step(mbs)
+        if tr.train_engine.iteration == 2:       # what a kernel does when its wait runs out
+            word.fill_(2)
+        return r
+    tr.train_engine.train_step = step_with_timeout
+    with pytest.raises(NativeKernelTimeout) as ei:
+        tr.train()
+    assert ei.value.exit_code == 3 and "status 2" in str(ei.value)
+    assert tr.train_engine.iteration == 2 and len(tr.train_engine.history) == 1   # the bad step is not logged as done
+    assert int(word) == 0                                                        # cleared for a restart in-process

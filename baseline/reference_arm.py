@@ -94,11 +94,23 @@ def recipe_yaml(model_dir: str, train_iters: int, attn: str) -> dict:
         tools=dict(profile=dict(enable=False), memory_profile=dict(enable=False)))
 
 
+WAN_UNAVAILABLE = (
+    "reference cannot train Wan through a stock path on this image: its Megatron entry point (pretrain_sora.py) needs "
+    "the megatron and mindspeed packages, and its native Wan2.2 container imports names this snapshot does not define "
+    "(ImportError: cannot import name 'GenerativeBaseModel' from mindspeed_mm.fsdp.models.base_model; "
+    "mindspeed_mm.fsdp.train.generative_pipeline is absent)")
+
+
 def run(args, clock_sampler_cls=None) -> int:
     import torch
     import yaml
 
     tiny = args.model == "tiny"
+    if getattr(args, "workload", "vlm") != "vlm":
+        if int(os.environ.get("RANK", "0")) == 0:
+            why = WAN_UNAVAILABLE if args.workload == "wan" else "the reference arm covers the default (VLM) workload only"
+            print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+        return 0
     os.environ.setdefault("RANK", "0")
     os.environ.setdefault("LOCAL_RANK", "0")
     os.environ.setdefault("WORLD_SIZE", "1")
@@ -213,6 +225,7 @@ def run(args, clock_sampler_cls=None) -> int:
             "e2e": {"value": round(tokens / (ms_e2e / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 2),
                     "h2d_bytes_per_step": ds.nbytes(), "d2h_bytes_per_step": 4},
             "gpu_launches": 0,
+            "wan": {"unavailable": WAN_UNAVAILABLE},
         }
         print(json.dumps(out), flush=True)
     if dist.is_initialized():

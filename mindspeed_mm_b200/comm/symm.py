@@ -91,9 +91,15 @@ class SymmArena:
 class P2PCollectives:
     """Engine plug-in: moves the bf16 shards and the gradient slots into the arena and runs the kernels."""
 
-    def __init__(self, engine, ag_ctas: int = 64, rs_ctas: int = 96):
+    def __init__(self, engine, ag_ctas: int = 64, rs_ctas: int = 296, gather: Optional[str] = None):
+        import os
         self.e = engine
         self.ag_ctas, self.rs_ctas = ag_ctas, rs_ctas
+        # "ce": the parameter gather runs on the copy engines (one peer-to-peer async copy per shard): the parameters
+        # are known a unit ahead, so the transfer needs no SM and the persistent GEMM keeps all of them.
+        # "sm": the pull kernel (64 CTAs sharing SMs with the GEMM).
+        self.gather = gather or os.environ.get("MM_B200_PARAM_GATHER", "ce")
+        self.rs_ctas = int(os.environ.get("MM_B200_RS_CTAS", self.rs_ctas))
         groups = [g for u in engine.units for g in u.groups]
         flag_bytes = native.lib().mm_p2p_flag_bytes()
         slot_bytes = _round_up(max(g.padded for g in groups) * 2, ALIGN_BYTES)
@@ -119,8 +125,12 @@ class P2PCollectives:
 
     # ------------------------------------------------------------------ all-gather
     def all_gather(self, g, full: torch.Tensor) -> None:
-        rc = native.lib().mm_p2p_allgather(self.shard_ptrs[id(g)], full.data_ptr(), g.shard_numel, g.world, g.rank,
-                                           self.ag_ctas, native._st())
+        if self.gather == "ce":
+            rc = native.lib().mm_p2p_allgather_ce(self.shard_ptrs[id(g)], full.data_ptr(), g.shard_numel * 2, g.world,
+                                                  g.rank, native._st())
+        else:
+            rc = native.lib().mm_p2p_allgather(self.shard_ptrs[id(g)], full.data_ptr(), g.shard_numel, g.world, g.rank,
+                                               self.ag_ctas, native._st())
         native._check(rc, "p2p_allgather")
 
     # ------------------------------------------------------------------ gradient slots

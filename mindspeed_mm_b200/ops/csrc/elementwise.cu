@@ -475,18 +475,20 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
                              const float* __restrict__ scale_ptr) {
     const float gs = scale_ptr ? gscale * (*scale_ptr) : gscale;
     const long long nv = n >> 2;
+    const uint64_t pol = l2_evict_first_policy();      // 28 bytes per parameter, each touched once
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nv;
          i += (long long)gridDim.x * blockDim.x) {
-        float4 pp = reinterpret_cast<float4*>(p)[i];
-        float4 mm = reinterpret_cast<float4*>(m)[i];
-        float4 vv = reinterpret_cast<float4*>(v)[i];
+        float4 pp = ld_stream_f4(reinterpret_cast<const float4*>(p) + i, pol);
+        float4 mm = ld_stream_f4(reinterpret_cast<const float4*>(m) + i, pol);
+        float4 vv = ld_stream_f4(reinterpret_cast<const float4*>(v) + i, pol);
         float gg[4];
         if constexpr (sizeof(G) == 2) {
-            const bf162* gp = reinterpret_cast<const bf162*>(g) + 2 * i;
+            const uint2 raw = ld_stream_u2(reinterpret_cast<const uint2*>(g) + i, pol);
+            const bf162* gp = reinterpret_cast<const bf162*>(&raw);
             float2 a = __bfloat1622float2(gp[0]), b = __bfloat1622float2(gp[1]);
             gg[0] = a.x; gg[1] = a.y; gg[2] = b.x; gg[3] = b.y;
         } else {
-            float4 a = reinterpret_cast<const float4*>(g)[i];
+            float4 a = ld_stream_f4(reinterpret_cast<const float4*>(g) + i, pol);
             gg[0] = a.x; gg[1] = a.y; gg[2] = a.z; gg[3] = a.w;
         }
         float* P = &pp.x; float* M = &mm.x; float* V = &vv.x;
@@ -499,9 +501,9 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
             const float denom = sqrtf(V[k] / bc2) + eps;
             P[k] = P[k] * (1.f - lr * decay) - lr * (M[k] / bc1) / denom;
         }
-        reinterpret_cast<float4*>(p)[i] = pp;
-        reinterpret_cast<float4*>(m)[i] = mm;
-        reinterpret_cast<float4*>(v)[i] = vv;
+        st_stream_f4(reinterpret_cast<float4*>(p) + i, pp, pol);
+        st_stream_f4(reinterpret_cast<float4*>(m) + i, mm, pol);
+        st_stream_f4(reinterpret_cast<float4*>(v) + i, vv, pol);
         bf162* o = reinterpret_cast<bf162*>(p16) + 2 * i;
         o[0] = __floats2bfloat162_rn(pp.x, pp.y);
         o[1] = __floats2bfloat162_rn(pp.z, pp.w);

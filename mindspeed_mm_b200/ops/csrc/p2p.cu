@@ -135,14 +135,14 @@ __device__ void rs_epilogue(const RSParams& P) {
     }
 }
 
-__device__ __forceinline__ void reduce8(const RSParams& P, long long vec_idx, float* acc) {
+__device__ __forceinline__ void reduce8(const RSParams& P, long long vec_idx, float* acc, uint64_t pol) {
     const long long off = (long long)P.rank * (P.shard_elems >> 3) + vec_idx;
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[k] = 0.f;
     uint4 r[kMaxPeers];
 #pragma unroll
     for (int p = 0; p < kMaxPeers; ++p)
-        if (p < P.world) r[p] = ld_stream(reinterpret_cast<const uint4*>(P.grads.p[p]) + off);
+        if (p < P.world) r[p] = ld_stream_u4(reinterpret_cast<const uint4*>(P.grads.p[p]) + off, pol);
 #pragma unroll
     for (int p = 0; p < kMaxPeers; ++p)
         if (p < P.world) {
@@ -169,15 +169,19 @@ __global__ void __launch_bounds__(256) p2p_rs_adamw_kernel(RSParams P, AdamParam
         __threadfence_system();
         st_release_sys(flag_ready(P.flags.p[P.rank], P.slot), P.seq);  // publish: my gradients are in place
     }
+    const uint64_t pol = l2_evict_first_policy();
     // A CTA whose wait ran out skips the reduction (the peer's gradients are not there) but still takes part in the
     // epilogue: the arrival counter returns to zero and the slot is handed back, so the next launch on this slot works.
     const long long nvec = rs_prologue(P) ? (P.shard_elems >> 3) : 0;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
         float g[8];
-        reduce8(P, i, g);
-        float4 p0 = reinterpret_cast<float4*>(A.p)[2 * i], p1 = reinterpret_cast<float4*>(A.p)[2 * i + 1];
-        float4 m0 = reinterpret_cast<float4*>(A.m)[2 * i], m1 = reinterpret_cast<float4*>(A.m)[2 * i + 1];
-        float4 v0 = reinterpret_cast<float4*>(A.v)[2 * i], v1 = reinterpret_cast<float4*>(A.v)[2 * i + 1];
+        reduce8(P, i, g, pol);
+        const float4* Pp = reinterpret_cast<const float4*>(A.p) + 2 * i;
+        const float4* Mp = reinterpret_cast<const float4*>(A.m) + 2 * i;
+        const float4* Vp = reinterpret_cast<const float4*>(A.v) + 2 * i;
+        float4 p0 = ld_stream_f4(Pp, pol), p1 = ld_stream_f4(Pp + 1, pol);
+        float4 m0 = ld_stream_f4(Mp, pol), m1 = ld_stream_f4(Mp + 1, pol);
+        float4 v0 = ld_stream_f4(Vp, pol), v1 = ld_stream_f4(Vp + 1, pol);
         float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
         float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
         float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
@@ -188,12 +192,12 @@ __global__ void __launch_bounds__(256) p2p_rs_adamw_kernel(RSParams P, AdamParam
             vv[k] = A.b2 * vv[k] + (1.f - A.b2) * g[k] * g[k];
             pp[k] = pp[k] * (1.f - A.lr * decay) - A.lr * (mm[k] / A.bc1) / (sqrtf(vv[k] / A.bc2) + A.eps);
         }
-        reinterpret_cast<float4*>(A.p)[2 * i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
-        reinterpret_cast<float4*>(A.p)[2 * i + 1] = make_float4(pp[4], pp[5], pp[6], pp[7]);
-        reinterpret_cast<float4*>(A.m)[2 * i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
-        reinterpret_cast<float4*>(A.m)[2 * i + 1] = make_float4(mm[4], mm[5], mm[6], mm[7]);
-        reinterpret_cast<float4*>(A.v)[2 * i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
-        reinterpret_cast<float4*>(A.v)[2 * i + 1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+        st_stream_f4(reinterpret_cast<float4*>(A.p) + 2 * i, make_float4(pp[0], pp[1], pp[2], pp[3]), pol);
+        st_stream_f4(reinterpret_cast<float4*>(A.p) + 2 * i + 1, make_float4(pp[4], pp[5], pp[6], pp[7]), pol);
+        st_stream_f4(reinterpret_cast<float4*>(A.m) + 2 * i, make_float4(mm[0], mm[1], mm[2], mm[3]), pol);
+        st_stream_f4(reinterpret_cast<float4*>(A.m) + 2 * i + 1, make_float4(mm[4], mm[5], mm[6], mm[7]), pol);
+        st_stream_f4(reinterpret_cast<float4*>(A.v) + 2 * i, make_float4(vv[0], vv[1], vv[2], vv[3]), pol);
+        st_stream_f4(reinterpret_cast<float4*>(A.v) + 2 * i + 1, make_float4(vv[4], vv[5], vv[6], vv[7]), pol);
         reinterpret_cast<Vec8*>(A.p16)[i] = pack8(pp);
     }
     rs_epilogue(P);
@@ -204,10 +208,11 @@ __global__ void __launch_bounds__(256) p2p_rs_kernel(RSParams P, float* __restri
         __threadfence_system();
         st_release_sys(flag_ready(P.flags.p[P.rank], P.slot), P.seq);
     }
+    const uint64_t pol = l2_evict_first_policy();
     const long long nvec = rs_prologue(P) ? (P.shard_elems >> 3) : 0;   // see p2p_rs_adamw_kernel
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
         float g[8];
-        reduce8(P, i, g);
+        reduce8(P, i, g, pol);
         float4* o = reinterpret_cast<float4*>(out) + 2 * i;
         if (accumulate) {
             float4 a = o[0], b = o[1];
@@ -300,6 +305,21 @@ MM_API int mm_p2p_allgather(void* const* shard_ptrs, void* full, long long shard
     if (world > kMaxPeers || shard_elems % 8) return -1;
     p2p_allgather_kernel<<<ctas, 256, 0, st>>>(make_peers(shard_ptrs, world), (uint4*)full, shard_elems / 8, world, rank);
     return (int)cudaGetLastError();
+}
+
+// The same gather on the copy engines: one cudaMemcpyAsync per peer shard (peer-mapped source, local destination), in
+// the same rank-staggered order, own shard last.  No SM is used, so a GEMM that owns every SM keeps them; the copies
+// are ordered on `st` like a kernel would be.
+MM_API int mm_p2p_allgather_ce(void* const* shard_ptrs, void* full, long long shard_bytes, int world, int rank,
+                               cudaStream_t st) {
+    if (world > kMaxPeers) return -1;
+    for (int hop = 0; hop < world; ++hop) {
+        const int peer = (rank + 1 + hop) % world;
+        cudaError_t e = cudaMemcpyAsync(reinterpret_cast<char*>(full) + (size_t)peer * shard_bytes, shard_ptrs[peer],
+                                        (size_t)shard_bytes, cudaMemcpyDeviceToDevice, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
 }
 
 MM_API int mm_p2p_rs_adamw(void* const* grad_ptrs, void* const* flag_ptrs, long long shard_elems, int world, int rank,

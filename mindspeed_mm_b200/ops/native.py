@@ -78,6 +78,7 @@ def _declare(L):
         "mm_p2p_set_wait_limit": [_ll],
         "mm_p2p_flag_bytes": [],
         "mm_p2p_allgather": [_p, _p, _ll, _i, _i, _i, _p],
+        "mm_p2p_allgather_ce": [_p, _p, _ll, _i, _i, _p],
         "mm_p2p_rs_adamw": [_p, _p, _ll, _i, _i, _i, C.c_uint, _f, _p, _p, _p, _p, _ll, _f, _f, _f, _f, _f, _f, _f,
                             _p, _i, _p],
         "mm_p2p_rs": [_p, _p, _ll, _i, _i, _i, C.c_uint, _f, _p, _i, _p, _i, _p],

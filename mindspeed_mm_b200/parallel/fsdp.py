@@ -34,6 +34,10 @@ import torch.nn as nn
 
 from .. import ops
 
+import os as _os
+# diagnostic switch: the compute stream waits for each unit's reduce(+update) instead of overlapping with it
+_SERIAL_REDUCE = _os.environ.get("MM_B200_SERIAL_REDUCE", "0") == "1"
+
 ALIGN = 128  # elements; keeps every parameter 256-byte aligned inside the flat buffer (TMA needs 16 B)
 
 
@@ -429,6 +433,8 @@ class FSDPEngine:
                         if g.grad32 is None:
                             g.grad32 = torch.zeros(g.shard_numel, dtype=self.reduce_dtype, device=self.device)
                         g.grad32.add_(gshard, alpha=1.0 / self.grad_divide if self.world == 1 else 1.0)
+            if self.cuda and _SERIAL_REDUCE:
+                torch.cuda.current_stream().wait_stream(self.comm_stream)
 
     def _reduce_scatter(self, g: FlatGroup, flat: torch.Tensor) -> torch.Tensor:
         if self.world == 1:

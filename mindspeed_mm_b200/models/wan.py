@@ -30,6 +30,11 @@ from .qwen2_5_vl import Linear
 from .registry import model_register
 
 
+import os as _os
+# "fused" (default): Ulysses collectives inside the projection GEMMs over peer memory; "nccl": all-to-all collectives
+_ULYSSES_PATH = _os.environ.get("MM_B200_ULYSSES", "fused")
+
+
 @dataclass
 class WanConfig:
     model_type: str = "t2v"
@@ -109,8 +114,46 @@ class WanSelfAttention(nn.Module):
         self.q_norm = FullRMSNorm(c.hidden_size, c.eps) if c.qk_norm else nn.Identity()
         self.k_norm = FullRMSNorm(c.hidden_size, c.eps) if c.qk_norm else nn.Identity()
 
-    def forward(self, x, rope, seq_sizes):
+    def _fused_group(self, x, seq_sizes, rope_full):
+        """The Ulysses group when the fused peer-memory path applies: native tier on CUDA, one sample, equal sequence
+        slices, whole-row q/k norm present, head block per rank a multiple of 64 channels."""
+        if rope_full is None or seq_sizes is not None or x.shape[0] != 1 or not isinstance(self.q_norm, FullRMSNorm):
+            return None
+        ps = get_parallel_state()
+        if not ps.enabled("ulysses") or _ULYSSES_PATH == "nccl":
+            return None
+        from ..comm import fused
+        if not fused.fused_supported(x):
+            return None
+        world = ps.size("ulysses")
+        H = x.shape[-1]
+        if self.nh % world or (H // world) % 64 or x.shape[1] % 8 or world > 8:
+            return None
+        return ps.get_ulysses_group()
+
+    def _forward_fused(self, x, rope_full, group):
+        """Self-attention under Ulysses with every collective inside a GEMM (``comm/fused.py``): the QKV projection stores
+        each head block into its owner (and emits the row sums of squares the whole-row q/k norm needs), the owner
+        normalises + rotates its heads and runs attention over the full sequence, the output projection fetches the heads
+        back inside its GEMM; the backward passes mirror this."""
+        import torch.distributed as dist
+        from ..comm import fused
+        S_local, H = x.shape[1], x.shape[2]
+        world = dist.get_world_size(group)
+        dev = x.device
+        qkv = fused.shared(fused.UlyssesQKVProjection, group, dev, S_local, 3 * H, 3, True)
+        raw, stats = qkv(x[0], self.qkv.weight, self.qkv.bias)
+        nr = fused.shared(fused.UlyssesQKNormRope, group, dev, S_local * world, H // world, self.hd, H, self.q_norm.eps)
+        q, k, v = nr(raw, stats, self.q_norm.weight, self.k_norm.weight, rope_full[0], rope_full[1])
+        o = ops.attention_dense(q[None], k[None], v[None])[0]                   # [S_full, heads / world, D]
+        out = fused.shared(fused.UlyssesOutProjection, group, dev, S_local, H)
+        return out(o.reshape(S_local * world, H // world), self.proj_out.weight, self.proj_out.bias)[None]
+
+    def forward(self, x, rope, seq_sizes, rope_full=None):
         B, S, H = x.shape
+        group = self._fused_group(x, seq_sizes, rope_full)
+        if group is not None:
+            return self._forward_fused(x, rope_full, group)
         q, k, v = self.qkv(x).split(H, dim=-1)
         q, k = self.q_norm(q), self.k_norm(k)
         cos, sin = rope
@@ -163,9 +206,9 @@ class WanBlock(nn.Module):
         self.ffn_0 = Linear(c.hidden_size, c.ffn_dim)
         self.ffn_2 = Linear(c.ffn_dim, c.hidden_size)
 
-    def forward(self, x, time_emb, ctx, rope_cos, rope_sin, seq_sizes=None, n_img: int = 0):
+    def forward(self, x, time_emb, ctx, rope_cos, rope_sin, seq_sizes=None, n_img: int = 0, rope_full=None):
         e = (self.modulation.to(time_emb.dtype) + time_emb).chunk(6, dim=1)         # each [B,1,H]
-        y = self.self_attn(ops.layer_norm_modulate(x, e[1], e[0], self.eps), (rope_cos, rope_sin), seq_sizes)
+        y = self.self_attn(ops.layer_norm_modulate(x, e[1], e[0], self.eps), (rope_cos, rope_sin), seq_sizes, rope_full)
         x = ops.gated_residual(x, y, e[2])
         x = x + self.cross_attn(self.norm3(x), ctx, n_img)
         y = self.ffn_2(ops.gelu_tanh(self.ffn_0(ops.layer_norm_modulate(x, e[4], e[3], self.eps))))
@@ -261,7 +304,9 @@ class WanDiT(nn.Module):
         ps = get_parallel_state()
         sp = ps.enabled("ulysses")
         seq_sizes = None
+        rope_full = None
         if sp:
+            rope_full = (cos, sin)          # the head owner rotates its heads over the FULL sequence (fused Ulysses path)
             g = ps.get_ulysses_group()
             seq_sizes = cal_split_sizes(S, ps.size("ulysses"))
             x = split_forward_gather_backward(x, g, dim=1, grad_scale="down", split_sizes=seq_sizes)
@@ -273,7 +318,7 @@ class WanDiT(nn.Module):
         if B > 1:
             cos, sin = cos.repeat(B, 1), sin.repeat(B, 1)
         for blk in self.blocks:
-            x = run(blk, x, time_emb, ctx, cos, sin, seq_sizes, n_img)
+            x = run(blk, x, time_emb, ctx, cos, sin, seq_sizes, n_img, rope_full)
         if sp:
             x = gather_forward_split_backward(x, ps.get_ulysses_group(), dim=1, grad_scale="up",
                                               gather_sizes=cal_split_sizes(S, ps.size("ulysses")))

@@ -53,6 +53,11 @@ struct Params {
     //   mode 2: row blocks of `blk` rows go to destination m / blk, stored at row rank * blk + m % blk
     //           (every source has its own slot on the destination, which then sums the slots)
     int mode, blk, world, rank, row_off;
+    // optional side output: stats[m * n_slots + n / per_slot] += sum over the tile's columns of (bf16-rounded output)^2,
+    // i.e. the sum of squares of every output row per column group, taken from the accumulators (a normalisation over
+    // the whole row can then be applied after the columns have been scattered to other GPUs)
+    float* stats = nullptr;
+    int n_slots = 1, per_slot = 0;
 };
 
 constexpr int kMaxDst = 8;
@@ -261,6 +266,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         r[c] = __float_as_uint(__uint_as_float(r[c]) + bv);
                     }
                 }
+                if (!SWIGLU && p.stats != nullptr) {
+                    float ss = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) {
+                        const float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[c])));
+                        ss += (n0 + c < p.N) ? v * v : 0.f;
+                    }
+                    const int m = mb * BM + row;
+                    if (m < p.M && n0 < p.N) atomicAdd(&p.stats[(size_t)m * p.n_slots + n0 / p.per_slot], ss);
+                }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     uint4 v;
@@ -312,6 +327,8 @@ struct Route {
     int mode = 0, blk = 0, world = 1, rank = 0, row_off = 0;
     void* const* dst = nullptr;     // mode != 0: `world` destination base pointers (peer-mapped)
     long long dst_rows = 0, dst_cols = 0;
+    float* stats = nullptr;         // see Params::stats
+    int n_slots = 1;
 };
 
 template <int BN, bool A_MN, bool B_MN, bool SWIGLU = false>
@@ -335,7 +352,14 @@ int launch(const void* A, const void* B, void* Cc, const void* bias, int M, int 
     } else {
         if (rt.world > kMaxDst) return -5;
         for (int d = 0; d < rt.world; ++d) {
-            r = make_tmap_2d(&tC.m[d], rt.dst[d], rt.dst_rows, rt.dst_cols, ldc, BM, 64);
+            if (rt.mode == 1) {
+                // this launch owns rows [row_off, row_off + M) of every destination: the map covers exactly those, so the
+                // last (partial) row tile is clipped instead of spilling into the next source's rows
+                if (rt.row_off + (long long)M > rt.dst_rows) return -6;
+                r = make_tmap_2d(&tC.m[d], (const char*)rt.dst[d] + (size_t)rt.row_off * ldc * 2, M, rt.dst_cols, ldc, BM, 64);
+            } else {
+                r = make_tmap_2d(&tC.m[d], rt.dst[d], rt.dst_rows, rt.dst_cols, ldc, BM, 64);
+            }
             if (r) return 3000 + r;
         }
     }
@@ -354,7 +378,8 @@ int launch(const void* A, const void* B, void* Cc, const void* bias, int M, int 
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     }
     const int tiles = m_blocks * n_blocks;
-    Params p{M, N, K, (const bf16*)bias, status, 8, rt.mode, rt.blk, rt.world, rt.rank, rt.row_off};
+    Params p{M, N, K, (const bf16*)bias, status, 8, rt.mode, rt.blk, rt.world, rt.rank, rt.mode == 1 ? 0 : rt.row_off,
+             rt.stats, rt.n_slots, rt.n_slots > 0 ? N / rt.n_slots : N};
     const int grid = tiles < sms ? tiles : sms;
     kern<<<grid, kThreads, C::kSmem, st>>>(tA, tB, tC, p);
     return (int)cudaGetLastError();
@@ -396,9 +421,11 @@ MM_API int mm_gemm_swiglu_bf16(const void* A, const void* W, void* C, int M, int
 // NVLink).  K-major operands (y = x W^T + bias).  mode 1: all-to-all of column blocks (Ulysses head scatter),
 // requires blk % 64 == 0; mode 2: push of row blocks into per-source slots (first half of a reduce-scatter),
 // requires blk % 128 == 0.  dst[d]: base of destination d's [dst_rows, dst_cols] bf16 buffer with row pitch ldc.
-MM_API int mm_gemm_bf16_routed(const void* A, const void* B, const void* bias, int M, int N, int K, long long lda,
-                               long long ldb, void* const* dst, long long dst_rows, long long dst_cols, long long ldc,
-                               int mode, int blk, int world, int rank, int row_off, int* status, cudaStream_t st) {
+// b_mn = 1: B is stored [K, N] row-major (the NN product of a data-gradient GEMM) instead of [N, K].
+MM_API int mm_gemm_bf16_routed_ex(const void* A, const void* B, const void* bias, int M, int N, int K, long long lda,
+                                  long long ldb, void* const* dst, long long dst_rows, long long dst_cols, long long ldc,
+                                  int mode, int blk, int world, int rank, int row_off, int b_mn, int* status,
+                                  cudaStream_t st) {
     if ((lda | ldb | ldc) % 8) return -1;
     if (((uintptr_t)A | (uintptr_t)B) & 15) return -2;
     if (mode == 1 && (blk % 64 || N % (blk * world))) return -3;
@@ -407,11 +434,37 @@ MM_API int mm_gemm_bf16_routed(const void* A, const void* B, const void* bias, i
     Route rt;
     rt.mode = mode; rt.blk = blk; rt.world = world; rt.rank = rank; rt.row_off = row_off;
     rt.dst = dst; rt.dst_rows = dst_rows; rt.dst_cols = dst_cols;
-    if (mode == 1 && blk % 256 == 0)
-        return launch<256, false, false>(A, B, nullptr, bias, M, N, K, lda, ldb, ldc, status, st, rt);
-    if (mode == 2 && N >= 256)
-        return launch<256, false, false>(A, B, nullptr, bias, M, N, K, lda, ldb, ldc, status, st, rt);
+    const bool wide = (mode == 1 && blk % 256 == 0) || (mode == 2 && N >= 256);
+    if (b_mn) {
+        if (wide) return launch<256, false, true>(A, B, nullptr, bias, M, N, K, lda, ldb, ldc, status, st, rt);
+        return launch<128, false, true>(A, B, nullptr, bias, M, N, K, lda, ldb, ldc, status, st, rt);
+    }
+    if (wide) return launch<256, false, false>(A, B, nullptr, bias, M, N, K, lda, ldb, ldc, status, st, rt);
     return launch<128, false, false>(A, B, nullptr, bias, M, N, K, lda, ldb, ldc, status, st, rt);
+}
+
+// Mode 1 (K-major operands) with the row statistics side output: stats [M, n_slots] fp32, zeroed by the caller, receives
+// the sum of squares of each output row over each of the n_slots equal column groups (q | k | v).
+MM_API int mm_gemm_bf16_routed_stats(const void* A, const void* B, const void* bias, int M, int N, int K, long long lda,
+                                     long long ldb, void* const* dst, long long dst_rows, long long dst_cols, long long ldc,
+                                     int blk, int world, int rank, int row_off, float* stats, int n_slots, int* status,
+                                     cudaStream_t st) {
+    if ((lda | ldb | ldc) % 8) return -1;
+    if (((uintptr_t)A | (uintptr_t)B) & 15) return -2;
+    if (blk % 64 || N % (blk * world) || n_slots < 1 || N % n_slots || (N / n_slots) % 64) return -3;
+    Route rt;
+    rt.mode = 1; rt.blk = blk; rt.world = world; rt.rank = rank; rt.row_off = row_off;
+    rt.dst = dst; rt.dst_rows = dst_rows; rt.dst_cols = dst_cols;
+    rt.stats = stats; rt.n_slots = n_slots;
+    if (blk % 256 == 0) return launch<256, false, false>(A, B, nullptr, bias, M, N, K, lda, ldb, ldc, status, st, rt);
+    return launch<128, false, false>(A, B, nullptr, bias, M, N, K, lda, ldb, ldc, status, st, rt);
+}
+
+MM_API int mm_gemm_bf16_routed(const void* A, const void* B, const void* bias, int M, int N, int K, long long lda,
+                               long long ldb, void* const* dst, long long dst_rows, long long dst_cols, long long ldc,
+                               int mode, int blk, int world, int rank, int row_off, int* status, cudaStream_t st) {
+    return mm_gemm_bf16_routed_ex(A, B, bias, M, N, K, lda, ldb, dst, dst_rows, dst_cols, ldc, mode, blk, world, rank,
+                                  row_off, 0, status, st);
 }
 
 // out[r, :] = sum_s slots[s * rows + r, :]   (second half of the reduce-scatter: fold the per-source slots)

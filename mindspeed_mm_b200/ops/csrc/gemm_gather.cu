@@ -72,7 +72,9 @@ __device__ bool wait_slab(const uint32_t* flag, uint32_t target, volatile int* a
     return true;
 }
 
-template <int BN>
+// B_MN = false: B is [N, K] (K contiguous, y = gather(A) B^T); B_MN = true: B is stored [K, N] (N contiguous: the
+// data-gradient product dx = gather(g) W with W [N', K'] read as [K = N', N = K']).
+template <int BN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_gather_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ TMapSet tmSrc, GParams p) {
@@ -197,7 +199,13 @@ gemm_gather_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     }
                     mbar_expect_tx(&full[stage], C::kStageBytes);
                     tma_load_2d(sA + stage * C::kABytes, &tmA, &full[stage], kbe * BK, mb * BM);
-                    tma_load_2d(sB + stage * C::kBBytes, &tmB, &full[stage], kbe * BK, nb * BN);
+                    if constexpr (!B_MN) {
+                        tma_load_2d(sB + stage * C::kBBytes, &tmB, &full[stage], kbe * BK, nb * BN);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_2d(sB + stage * C::kBBytes + j * (BK * 128), &tmB, &full[stage], nb * BN + j * 64, kbe * BK);
+                    }
                     if (++stage == C::kStages) {
                         stage = 0;
                         phase ^= 1;
@@ -208,7 +216,7 @@ gemm_gather_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = idesc_bf16(BM, BN, 0, 0);
+            constexpr uint32_t idesc = idesc_bf16(BM, BN, 0, B_MN ? 1 : 0);
             int stage = 0, it = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -229,9 +237,11 @@ gemm_gather_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     fence_after_sync();
                     const uint32_t a0 = smem_u32(sA + stage * C::kABytes), b0 = smem_u32(sB + stage * C::kBBytes);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        mma_ss(d_tmem, smem_desc_sw128(a0 + k * 32, 16, 1024), smem_desc_sw128(b0 + k * 32, 16, 1024), idesc,
-                               (kb | k) ? 1u : 0u);
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t db = B_MN ? smem_desc_sw128(b0 + k * 2048, BK * 128, 1024)
+                                                 : smem_desc_sw128(b0 + k * 32, 16, 1024);
+                        mma_ss(d_tmem, smem_desc_sw128(a0 + k * 32, 16, 1024), db, idesc, (kb | k) ? 1u : 0u);
+                    }
                     mma_commit(&empty[stage]);
                     if (++stage == C::kStages) {
                         stage = 0;
@@ -310,7 +320,7 @@ gemm_gather_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
 }
 
-template <int BN>
+template <int BN, bool B_MN>
 int launch(const void* A, const void* B, void* Cc, const void* bias, int M, int N, int K, long long lda, long long ldb,
            long long ldc, void* const* src, long long src_pitch, int src_rows, int src_cols, int axis, int extent, int world,
            int rank, uint32_t* flags, uint32_t epoch, int* status, cudaStream_t st) {
@@ -319,7 +329,7 @@ int launch(const void* A, const void* B, void* Cc, const void* bias, int M, int 
     TMapSet tS;
     int r;
     if ((r = make_tmap_2d(&tA, A, M, K, lda, BM, BK))) return 1000 + r;
-    if ((r = make_tmap_2d(&tB, B, N, K, ldb, BN, BK))) return 2000 + r;
+    if ((r = B_MN ? make_tmap_2d(&tB, B, K, N, ldb, BK, 64) : make_tmap_2d(&tB, B, N, K, ldb, BN, BK))) return 2000 + r;
     if ((r = make_tmap_2d(&tC, Cc, M, N, ldc, BM, 64))) return 3000 + r;
     for (int s = 0; s < world; ++s) {
         if (s == rank) {
@@ -329,7 +339,7 @@ int launch(const void* A, const void* B, void* Cc, const void* bias, int M, int 
         if ((r = make_tmap_2d(&tS.m[s], src[s], src_rows, src_cols, src_pitch, BM, BK))) return 4000 + r;
     }
     for (int s = world; s < kMaxPeers; ++s) tS.m[s] = tA;
-    auto kern = gemm_gather_kernel<BN>;
+    auto kern = gemm_gather_kernel<BN, B_MN>;
     static bool done = false;
     if (!done) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
@@ -356,16 +366,30 @@ int launch(const void* A, const void* B, void* Cc, const void* bias, int M, int 
 // axis 0: extent = rows per slab (multiple of 128); axis 2: extent = K columns per slab (multiple of 64).
 // flags: `world` uint32 counters in this GPU's memory, zero before the first launch; epoch = 1, 2, 3 ... per launch
 // with the same grid.  The caller brackets the launch with a cross-rank barrier (sources stable / consumed).
+MM_API int mm_gemm_gather_bf16_ex(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
+                                  long long ldb, long long ldc, void* const* src, long long src_pitch, int src_rows,
+                                  int src_cols, int axis, int extent, int world, int rank, unsigned* flags, unsigned epoch,
+                                  int b_mn, int* status, cudaStream_t st) {
+    if ((lda | ldb | ldc | src_pitch) % 8) return -1;
+    if (world > kMaxPeers || (axis != 0 && axis != 2)) return -2;
+    if ((axis == 0 && extent % BM) || (axis == 2 && extent % BK)) return -3;
+#define MM_GG(BN_, MN_)                                                                                                     \
+    return launch<BN_, MN_>(A, B, C, bias, M, N, K, lda, ldb, ldc, src, src_pitch, src_rows, src_cols, axis, extent, world, \
+                            rank, flags, epoch, status, st)
+    if (N >= 256) {
+        if (b_mn) MM_GG(256, true);
+        MM_GG(256, false);
+    }
+    if (b_mn) MM_GG(128, true);
+    MM_GG(128, false);
+#undef MM_GG
+}
+
+// b_mn = 0 form (y = gather(A) B^T with B [N, K]).
 MM_API int mm_gemm_gather_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
                                long long ldb, long long ldc, void* const* src, long long src_pitch, int src_rows,
                                int src_cols, int axis, int extent, int world, int rank, unsigned* flags, unsigned epoch,
                                int* status, cudaStream_t st) {
-    if ((lda | ldb | ldc | src_pitch) % 8) return -1;
-    if (world > kMaxPeers || (axis != 0 && axis != 2)) return -2;
-    if ((axis == 0 && extent % BM) || (axis == 2 && extent % BK)) return -3;
-    if (N >= 256)
-        return launch<256>(A, B, C, bias, M, N, K, lda, ldb, ldc, src, src_pitch, src_rows, src_cols, axis, extent, world, rank,
-                           flags, epoch, status, st);
-    return launch<128>(A, B, C, bias, M, N, K, lda, ldb, ldc, src, src_pitch, src_rows, src_cols, axis, extent, world, rank,
-                       flags, epoch, status, st);
+    return mm_gemm_gather_bf16_ex(A, B, C, bias, M, N, K, lda, ldb, ldc, src, src_pitch, src_rows, src_cols, axis, extent,
+                                  world, rank, flags, epoch, 0, status, st);
 }

@@ -137,6 +137,58 @@ def main():
         return native.gemm_nt(recv.permute(1, 0, 2).reshape(So, Ho), wo)
     t_of = timed(lambda: uo(mine, wo))
     t_ou = timed(unfused_uo)
+    # ---------------- backward passes of the three layers above against fp32 autograd through NCCL collectives
+    def rel(a_, b_):
+        return (a_.float() - b_.float()).norm().item() / (b_.float().norm().item() + 1e-12)
+
+    # row-parallel + reduce-scatter: y_l = RS(x W^T);  backward gathers the rows of g inside dx = gather(g) W
+    xg, wg = xa.clone().requires_grad_(), wa.clone().requires_grad_()
+    yo = rs(xg, wg)
+    gy = torch.randn_like(yo)
+    yo.backward(gy)
+    gfull = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    dist.all_gather_into_tensor(gfull, gy, group=g)
+    for name, a_, b_ in (("dx", xg.grad, gfull.float() @ wa.float()), ("dw", wg.grad, gfull.float().t() @ xa.float())):
+        if rel(a_, b_) > 2e-2:
+            ok = False
+            print(f"rank {rank} rowparallel_rs {name} rel err {rel(a_, b_)}")
+    # all-gather + column-parallel: backward pushes dA = g W as row blocks to the row owners
+    xg, wg = xl[rank].clone().requires_grad_(), wc.clone().requires_grad_()
+    ya = agl(xg, wg)
+    gy = torch.randn_like(ya)
+    ya.backward(gy)
+    dA = gy.float() @ wc.float()
+    dxr = torch.empty(Sl, Hh, device="cuda")
+    dist.reduce_scatter_tensor(dxr, dA, group=g)
+    for name, a_, b_ in (("dx", xg.grad, dxr), ("dw", wg.grad, gy.float().t() @ xl.reshape(W * Sl, Hh).float())):
+        if rel(a_, b_) > 2e-2:
+            ok = False
+            print(f"rank {rank} allgather_linear {name} rel err {rel(a_, b_)}")
+    # Ulysses output projection: backward stores the head blocks of dA = g W into the head owners
+    og, wg = mine.clone().requires_grad_(), wo.clone().requires_grad_()
+    yu = uo(og, wg)
+    gy = torch.randn_like(yu)
+    yu.backward(gy)
+    dA = (gy.float() @ wo.float()).view(So, W, cols).permute(1, 0, 2).contiguous()     # [head owner, my rows, cols]
+    back = torch.empty_like(dA)
+    dist.all_to_all_single(back, dA, group=g)                                          # [row owner, its rows, cols]
+    a_full = o_full[rank * So:(rank + 1) * So].float()
+    for name, a_, b_ in (("do", og.grad, back.reshape(W * So, cols)), ("dw", wg.grad, gy.float().t() @ a_full)):
+        if rel(a_, b_) > 2e-2:
+            ok = False
+            print(f"rank {rank} ulysses_out {name} rel err {rel(a_, b_)}")
+    # Ulysses QKV with the row statistics side output, ragged rows per rank (not a multiple of 128)
+    Sr = 200
+    xr_ = torch.randn(W, Sr, H, device="cuda", dtype=torch.bfloat16) * 0.5
+    pr = UlyssesQKVProjection(g, "cuda", Sr, 3 * H, 3, True)
+    yr_, st_ = pr(xr_[rank].clone(), w, b)
+    full_y = torch.nn.functional.linear(xr_.reshape(W * Sr, H).float(), w.float(), b.float()).to(torch.bfloat16).float()
+    blk_ = H // W
+    want = full_y.view(W * Sr, 3, W, blk_)[:, :, rank].reshape(W * Sr, 3 * blk_)
+    want_ss = full_y.view(W * Sr, 3, H).pow(2).sum(-1)
+    if rel(yr_, want) > 1e-2 or rel(st_, want_ss) > 1e-2:
+        ok = False
+        print(f"rank {rank} ulysses qkv+stats rel err {rel(yr_, want)} stats {rel(st_, want_ss)}")
     native.check_status()
     flag = torch.tensor([int(ok)], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

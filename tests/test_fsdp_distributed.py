@@ -90,6 +90,13 @@ def test_wan_fsdp_ulysses_matches_single_process_gloo():
 
 
 @pytest.mark.gpu
+def test_wan_fused_ulysses_matches_all_to_all_path_2gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    assert "ok=True" in _run_script(2, "dist_wan_check.py", "--cuda")
+
+
+@pytest.mark.gpu
 def test_moe_peer_memory_dispatcher_matches_alltoall():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")

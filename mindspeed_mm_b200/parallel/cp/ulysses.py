@@ -4,8 +4,10 @@ head-sharded" layouts around the attention core.
 Reference: mindspeed_mm/fsdp/distributed/context_parallel/communication.py:78-128,175-220 (aligned and
 unaligned ``all_to_all``), mindspeed_mm/fsdp/ops/flash_attn/flash_attn.py:281-295 (KV heads are replicated
 when the group is larger than the number of KV heads) and models/common/attention.py (UlyssesContextAttention).
-Tensors are [B, S_local, N, D].  Library tier: ``dist.all_to_all_single``; the native tier fuses the scatter
-into the QKV GEMM epilogue and the gather into the output projection (``ops/fused_comm.py``).
+Tensors are [B, S_local, N, D].  The functions here are the collective form (``dist.all_to_all_single`` / ``all_to_all``):
+CPU / gloo runs, the library tier, unaligned sequences.  On the native tier the Wan DiT does not call them for its
+self-attention: the scatter is the epilogue of the QKV GEMM and the gather the operand fetch of the output projection
+(``comm/fused.py``, used from ``models/wan.py: WanSelfAttention._forward_fused``).
 """
 from __future__ import annotations
 

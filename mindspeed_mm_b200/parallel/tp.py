@@ -5,9 +5,12 @@ along the sequence first), ``RowParallelLinear`` (input features split; output r
 sequence, or all-reduced without sequence parallel), ``VocabParallelEmbedding`` and the vocabulary-parallel
 cross entropy (max / sum-exp / target logit each all-reduced over the group, never gathering [T, V]).
 The reference uses Megatron's implementations of the same layers (mindspeed_mm/models/common/attention.py:296-389,
-vlm_model.py:409-566).  Library tier: ``torch.distributed`` collectives around the GEMMs; native tier: the fused
-kernels of ``comm/fused.py`` (all-gather fused into the column GEMM, reduce-scatter fused into the row GEMM).
-All tensors are [T, H] (packed tokens first).
+vlm_model.py:409-566).  With sequence parallelism on the native tier (CUDA, bf16, rows per rank a multiple of 128) the
+two linears run the fused kernels of ``comm/fused.py`` in both directions: ``AllGatherLinear`` (the sequence all-gather
+happens inside the column GEMM; its backward pushes the data gradient's row blocks to their owners) and
+``RowParallelLinearRS`` (the row GEMM's epilogue is the reduce-scatter; its backward gathers the gradient rows inside
+the GEMM).  Everything else (CPU / gloo, the library tier, no sequence parallelism, odd shapes) uses
+``torch.distributed`` collectives around the GEMMs.  All tensors are [T, H] (packed tokens first).
 """
 from __future__ import annotations
 
@@ -103,6 +106,14 @@ def _reduce_scatter0(x, group):
     return out
 
 
+def _fused_sp(x: torch.Tensor, group, rows_local: int, width: int) -> bool:
+    """Fused GEMM + collective kernels apply: native tier, CUDA bf16 [T, H] input, 128-row blocks per rank."""
+    if x.dim() != 2 or not x.is_cuda or _ws(group) > 8 or rows_local % 128 or width % 64:
+        return False
+    from ..comm import fused
+    return fused.fused_supported(x)
+
+
 def gather_sequence(x, group):
     return x if _ws(group) == 1 else _GatherSeq.apply(x, group)
 
@@ -127,6 +138,10 @@ class ColumnParallelLinear(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_features // self.tp)) if bias else None
 
     def forward(self, x):
+        if self.tp > 1 and self.sp and not self.gather_output and _fused_sp(x, self.group, x.shape[0], x.shape[1]) \
+                and self.weight.shape[0] % 8 == 0:
+            from ..comm import fused
+            return fused.shared(fused.AllGatherLinear, self.group, x.device, x.shape[0], x.shape[1])(x, self.weight, self.bias)
         if self.tp > 1:
             x = gather_sequence(x, self.group) if self.sp else _CopyToTP.apply(x, self.group)
         y = ops.linear(x, self.weight, self.bias)
@@ -146,6 +161,11 @@ class RowParallelLinear(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None      # added once, after the reduction
 
     def forward(self, x):
+        if self.tp > 1 and self.sp and x.dim() == 2 and x.shape[0] % self.tp == 0 and x.shape[1] % 8 == 0 and \
+                _fused_sp(x, self.group, x.shape[0] // self.tp, self.weight.shape[0]):
+            from ..comm import fused
+            y = fused.shared(fused.RowParallelLinearRS, self.group, x.device, x.shape[0], self.weight.shape[0])(x, self.weight)
+            return y if self.bias is None else y + self.bias
         y = ops.linear(x, self.weight, None)
         if self.tp > 1:
             y = scatter_sequence(y, self.group) if self.sp else _ReduceFromTP.apply(y, self.group)

@@ -90,6 +90,13 @@ def test_wan_fsdp_ulysses_matches_single_process_gloo():
 
 
 @pytest.mark.gpu
+def test_tensor_parallel_linears_use_fused_kernels_2gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    assert "ok=True" in _run_script(2, "dist_tp_check.py")
+
+
+@pytest.mark.gpu
 def test_wan_fused_ulysses_matches_all_to_all_path_2gpu():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")

@@ -240,7 +240,7 @@ class _UlyssesQKVFn(torch.autograd.Function):
                                                   mod.stats_local.data_ptr(), mod.n_slots,
                                                   native.status_word(x.device).data_ptr(), native._st())
             native._check(rc, "gemm_routed(ulysses+stats)")
-            nb = mod.stats_local.numel() * 4
+            nb = mod.stats_local.numel() * 4          # rows padded to a multiple of 4: a 16-byte multiple per rank
             for p in range(mod.world):                # my rows' sums of squares go to every rank (a few KB each)
                 native._check(native.lib().mm_p2p_copy(mod.stats_peer[p] + mod.rank * nb, mod.stats_local.data_ptr(), nb, 4,
                                                        native._st()), "p2p_copy(stats)")
@@ -252,7 +252,7 @@ class _UlyssesQKVFn(torch.autograd.Function):
         ctx.mod, ctx.has_bias = mod, bias is not None
         out = mod.recv.clone()
         if mod.with_stats:
-            stats = mod.stats_full.clone()
+            stats = mod.stats_full[:, :S_local].reshape(mod.S_full, mod.n_slots)      # drops the row padding (copies)
             ctx.mark_non_differentiable(stats)
             return out, stats
         return out
@@ -290,14 +290,15 @@ class UlyssesQKVProjection:
     def __init__(self, group, device, S_local: int, out_features: int, n_slots: int = 3, with_stats: bool = False):
         self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
         per_slot = out_features // n_slots
-        if per_slot % self.world or (per_slot // self.world) % 64 or S_local % 8:
-            raise ValueError("per-rank head block must be a multiple of 64 columns and rows per rank of 8")
+        if per_slot % self.world or (per_slot // self.world) % 64:
+            raise ValueError("per-rank head block must be a multiple of 64 columns")
         self.n_slots, self.with_stats = n_slots, with_stats
         self.blk = per_slot // self.world
         self.cols = n_slots * self.blk
         self.S_full = S_local * self.world
         dev = torch.device(device)
-        stat_bytes = self.S_full * n_slots * 4
+        S_pad = (S_local + 3) // 4 * 4
+        stat_bytes = self.world * S_pad * n_slots * 4
         self.arena = SymmArena(2 * self.S_full * self.cols * 2 + stat_bytes + 16384, group, dev)
         off = self.arena.carve(self.S_full * self.cols * 2)
         self.recv = self.arena.view(off, self.S_full * self.cols, torch.bfloat16).view(self.S_full, self.cols)
@@ -307,9 +308,9 @@ class UlyssesQKVProjection:
         row_off = self.rank * S_local * self.cols * 2            # every peer serves the rows of MY tokens
         self.g_src_ptrs = (C.c_void_p * self.world)(*[b + off + row_off for b in self.arena.peer_base])
         off = self.arena.carve(stat_bytes)
-        self.stats_full = self.arena.view(off, self.S_full * n_slots, torch.float32).view(self.S_full, n_slots)
+        self.stats_full = self.arena.view(off, self.world * S_pad * n_slots, torch.float32).view(self.world, S_pad, n_slots)
         self.stats_peer = [b + off for b in self.arena.peer_base]
-        self.stats_local = torch.zeros(S_local, n_slots, dtype=torch.float32, device=dev)
+        self.stats_local = torch.zeros(S_pad, n_slots, dtype=torch.float32, device=dev)
         self.dY = torch.empty(S_local, self.world * self.cols, dtype=torch.bfloat16, device=dev)
         self.bwd = _Gatherer(dev)
 
@@ -358,8 +359,8 @@ class UlyssesOutProjection:
     def __init__(self, group, device, S_local: int, H: int):
         self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
         cols = H // self.world
-        if cols % 64 or S_local % 8:
-            raise ValueError("per-rank head block must be a multiple of 64 columns and rows per rank of 8")
+        if cols % 64:
+            raise ValueError("per-rank head block must be a multiple of 64 columns")
         S_full = S_local * self.world
         self.arena = SymmArena(2 * S_full * cols * 2 + 8192, group, torch.device(device))
         off = self.arena.carve(S_full * cols * 2)

@@ -127,7 +127,7 @@ class WanSelfAttention(nn.Module):
             return None
         world = ps.size("ulysses")
         H = x.shape[-1]
-        if self.nh % world or (H // world) % 64 or x.shape[1] % 8 or world > 8:
+        if self.nh % world or (H // world) % 64 or world > 8:
             return None
         return ps.get_ulysses_group()
 

@@ -281,6 +281,56 @@ __global__ void rope_half_kernel(const bf16* __restrict__ x, long long xs, const
     }
 }
 
+// the same rotation with 4-element (8-byte) accesses, for head dims whose half is a multiple of 4 but not of 8 (72, 88 ...)
+__device__ __forceinline__ void unpack4(const uint2& v, float* f) {
+    const bf162* p = reinterpret_cast<const bf162*>(&v);
+    const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+__device__ __forceinline__ uint2 pack4(const float* f) {
+    uint2 v;
+    bf162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    v.x = *reinterpret_cast<uint32_t*>(&a);
+    v.y = *reinterpret_cast<uint32_t*>(&b);
+    return v;
+}
+__global__ void rope_half4_kernel(const bf16* __restrict__ x, long long xs, const bf16* __restrict__ cosb,
+                                  const bf16* __restrict__ sinb, bf16* __restrict__ out, int T, int N, int D,
+                                  float sign) {
+    const int hv = D >> 3;  // 4-element vectors per half
+    const long long total = (long long)T * N * hv;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        int c = (int)(idx % hv);
+        long long tn = idx / hv;
+        int n = (int)(tn % N);
+        long long t = tn / N;
+        const bf16* xp = x + t * xs + (long long)n * D;
+        float x1[4], x2[4], c1[4], c2[4], s1[4], s2[4], o1[4], o2[4];
+        unpack4(reinterpret_cast<const uint2*>(xp)[c], x1);
+        unpack4(reinterpret_cast<const uint2*>(xp + D / 2)[c], x2);
+        const bf16* cp = cosb + t * D;
+        const bf16* sp = sinb + t * D;
+        unpack4(reinterpret_cast<const uint2*>(cp)[c], c1);
+        unpack4(reinterpret_cast<const uint2*>(cp + D / 2)[c], c2);
+        unpack4(reinterpret_cast<const uint2*>(sp)[c], s1);
+        unpack4(reinterpret_cast<const uint2*>(sp + D / 2)[c], s2);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (sign > 0.f) {
+                o1[k] = x1[k] * c1[k] - x2[k] * s1[k];
+                o2[k] = x2[k] * c2[k] + x1[k] * s2[k];
+            } else {
+                o1[k] = x1[k] * c1[k] + x2[k] * s2[k];
+                o2[k] = x2[k] * c2[k] - x1[k] * s1[k];
+            }
+        }
+        bf16* op = out + (t * N + n) * (long long)D;
+        reinterpret_cast<uint2*>(op)[c] = pack4(o1);
+        reinterpret_cast<uint2*>(op + D / 2)[c] = pack4(o2);
+    }
+}
+
 // interleaved pairs: cos/sin [T, D/2] fp32
 __global__ void rope_inter_kernel(const bf16* __restrict__ x, long long xs, const float* __restrict__ cosf_,
                                   const float* __restrict__ sinf_, bf16* __restrict__ out, int T, int N, int D,
@@ -585,7 +635,12 @@ MM_API int mm_gelu_bwd(const void* in, const void* dout, void* din, long long n,
 
 MM_API int mm_rope_half(const void* x, long long xs, const void* cosb, const void* sinb, void* out, int T, int N,
                         int D, int backward, cudaStream_t st) {
-    if (D % 16 || xs % 8) return -1;
+    if (D % 8 || xs % 8) return -1;
+    if (D % 16) {
+        rope_half4_kernel<<<grid_for((long long)T * N * (D / 8), 256), 256, 0, st>>>(
+            (const bf16*)x, xs, (const bf16*)cosb, (const bf16*)sinb, (bf16*)out, T, N, D, backward ? -1.f : 1.f);
+        return (int)cudaGetLastError();
+    }
     rope_half_kernel<<<grid_for((long long)T * N * (D / 16), 256), 256, 0, st>>>(
         (const bf16*)x, xs, (const bf16*)cosb, (const bf16*)sinb, (bf16*)out, T, N, D, backward ? -1.f : 1.f);
     return (int)cudaGetLastError();

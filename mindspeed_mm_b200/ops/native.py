@@ -280,7 +280,7 @@ def rope(x, cos, sin, interleaved: bool):
             return reference.rope_interleaved(x, cos, sin)
         cos, sin = cos.float().contiguous(), sin.float().contiguous()
     else:
-        if D % 16:
+        if D % 8:
             from . import reference
             _eager("rope_rotate_half", x, f"D={D}")
             return reference.rope_rotate_half(x, cos, sin)

@@ -178,7 +178,7 @@ def main():
             ok = False
             print(f"rank {rank} ulysses_out {name} rel err {rel(a_, b_)}")
     # Ulysses QKV with the row statistics side output, ragged rows per rank (not a multiple of 128)
-    Sr = 200
+    Sr = 201
     xr_ = torch.randn(W, Sr, H, device="cuda", dtype=torch.bfloat16) * 0.5
     pr = UlyssesQKVProjection(g, "cuda", Sr, 3 * H, 3, True)
     yr_, st_ = pr(xr_[rank].clone(), w, b)

@@ -50,7 +50,8 @@ def cuda_main():
     torch.manual_seed(0)
     cfg = WanConfig(hidden_size=256 * world // 2, ffn_dim=512, num_heads=4 * world // 2, num_layers=2, text_dim=64, text_len=16,
                     freq_dim=32)
-    batch = dict(latents=torch.randn(1, 16, 3, 16, 16).to(dev, torch.bfloat16),
+    # `world` frames of 9 x 7 tokens: 63 tokens per rank (odd on purpose: no row-count alignment is needed)
+    batch = dict(latents=torch.randn(1, 16, world, 18, 14).to(dev, torch.bfloat16),
                  prompt=torch.randn(1, 16, 64).to(dev, torch.bfloat16))
     ps = init_parallel_state(world_size=world, device_type="cuda", ulysses_parallel_size=world)
     results = {}

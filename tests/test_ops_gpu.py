@@ -77,7 +77,7 @@ def test_swiglu(T, F):
     _close(x.grad, xr.grad)
 
 
-@pytest.mark.parametrize("N,D", [(28, 128), (16, 80), (4, 128)])
+@pytest.mark.parametrize("N,D", [(28, 128), (16, 80), (4, 128), (16, 72)])
 def test_rope_half(N, D):
     torch.manual_seed(0)
     T = 515

@@ -364,13 +364,26 @@ class DecoderLayer(nn.Module):
         self.gate_up_proj = Linear(c.hidden_size, 2 * c.intermediate_size, bias=False)
         self.down_proj = Linear(c.intermediate_size, c.hidden_size, bias=False)
 
-    def forward(self, x, cos, sin, cu_seqlens, max_seqlen):
+    def forward(self, x, cos, sin, cu_seqlens, max_seqlen, cache: Optional[dict] = None):
+        """``cache`` (generation, one sequence): a dict that keeps this layer's rotated keys and the values of all
+        tokens seen so far; the new tokens attend to them (causal mask aligned to the end of the key sequence)."""
         T = x.shape[0]
         qkv = self.qkv_proj(self.input_layernorm(x))
         q, k, v = qkv.split([self.nq * self.hd, self.nkv * self.hd, self.nkv * self.hd], dim=-1)
         q = ops.rope_rotate_half(q.view(T, self.nq, self.hd), cos, sin)
         k = ops.rope_rotate_half(k.view(T, self.nkv, self.hd), cos, sin)
-        o = ops.attention_varlen(q, k, v.view(T, self.nkv, self.hd), cu_seqlens, cu_seqlens,
+        v = v.view(T, self.nkv, self.hd)
+        if cache is not None:
+            if "k" in cache:
+                k, v = torch.cat([cache["k"], k]), torch.cat([cache["v"], v])
+            cache["k"], cache["v"] = k, v
+            L = k.shape[0]
+            cu_q = torch.tensor([0, T], dtype=torch.int32, device=x.device)
+            cu_k = torch.tensor([0, L], dtype=torch.int32, device=x.device)
+            o = ops.attention_varlen(q, k, v, cu_q, cu_k, T, L, causal=True)
+            x = x + self.o_proj(o.reshape(T, -1))
+            return x + self.down_proj(ops.linear_swiglu(self.post_attention_layernorm(x), self.gate_up_proj.weight))
+        o = ops.attention_varlen(q, k, v, cu_seqlens, cu_seqlens,
                                  max_seqlen, max_seqlen, causal=True)
         x = x + self.o_proj(o.reshape(T, -1))
         x = x + self.down_proj(ops.linear_swiglu(self.post_attention_layernorm(x), self.gate_up_proj.weight),
@@ -446,8 +459,10 @@ class Qwen25VLModel(nn.Module):
         return units
 
     # -- forward ---------------------------------------------------------------------------
-    def forward(self, batch: dict, run=None):
-        """``run(module, *args)`` lets the parallel engine wrap each unit (gather/recompute/reduce)."""
+    def forward(self, batch: dict, run=None, kv_cache: Optional[list] = None):
+        """``run(module, *args)`` lets the parallel engine wrap each unit (gather/recompute/reduce).
+        ``kv_cache`` (generation): one dict per decoder layer, filled by the prefill call and extended by every later
+        call, whose ``batch`` then holds only the new tokens (``input_ids`` / ``position_ids`` of those, no pixels)."""
         run = run or (lambda m, *a, **k: m(*a, **k))
         t = self.config.text
         ids = batch["input_ids"]
@@ -470,8 +485,13 @@ class Qwen25VLModel(nn.Module):
         if cos is None:
             cos, sin = ops.ref.mrope_cos_sin(batch["position_ids"], t.head_dim, t.rope_theta, t.mrope_section)
         cos, sin = cos.to(x.dtype), sin.to(x.dtype)
-        for layer in self.layers:
-            x = run(layer, x, cos, sin, batch["cu_seqlens"], batch["max_seqlen"])
+        for i, layer in enumerate(self.layers):
+            if kv_cache is not None:
+                x = run(layer, x, cos, sin, None, 0, kv_cache[i])
+            else:
+                x = run(layer, x, cos, sin, batch["cu_seqlens"], batch["max_seqlen"])
+        if kv_cache is not None and batch.get("labels") is None:
+            x = x[-1:]                      # generation reads the last position only
         return run(self.lm_head, x, batch.get("labels"))
 
 

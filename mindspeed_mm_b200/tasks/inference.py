@@ -1,8 +1,9 @@
 """Inference pipelines.
 
-* ``VLMGenerator``      - greedy / top-p decoding for the packed Qwen2.5-VL model with a growing sequence (the
-                          training kernels are prefill-shaped; every step re-runs the packed forward on the
-                          prefix, which is exact and adequate for evaluation-sized generations).
+* ``VLMGenerator``      - greedy / top-p decoding for the packed Qwen2.5-VL model with a per-layer key / value cache:
+                          the prompt (vision tower included) runs once, every later step feeds one token whose
+                          attention reads the cached keys and values (``use_cache=False`` re-runs the whole prefix
+                          per token instead, the exact but quadratic form).
 * ``WanPipeline``       - text-to-video / image-to-video sampling: flow-matching Euler steps with classifier-free
                           guidance over the DiT, latents decoded by an optional VAE callable.
 Reference: mindspeed_mm/tasks/inference/pipeline/{qwen2vl_pipeline.py, wan_pipeline.py} and the generation mixin;
@@ -39,19 +40,50 @@ class VLMGenerator:
         return logits[-1].float()
 
     @torch.no_grad()
+    def _prefill(self, input_ids, pixel_values, image_grid_thw, device):
+        sample = dict(input_ids=input_ids, labels=input_ids.clone())
+        if pixel_values is not None:
+            sample.update(pixel_values=pixel_values, image_grid_thw=image_grid_thw)
+        b = self.collator([sample])
+        b.pop("labels")
+        next_pos = int(b["position_ids"].max()) + 1          # where the text continues on all three rotary axes
+        b = {k: (v.to(device) if isinstance(v, torch.Tensor) else v) for k, v in b.items()}
+        if "vision_plan" in b:
+            b["vision_plan"] = {k: (v.to(device) if isinstance(v, torch.Tensor) else v) for k, v in b["vision_plan"].items()}
+        cache = [dict() for _ in self.model.layers]
+        logits = self.model(b, run=self.run, kv_cache=cache)
+        return logits[-1].float(), cache, next_pos
+
+    @torch.no_grad()
+    def _decode(self, token: int, pos: int, cache, device):
+        b = dict(input_ids=torch.tensor([token], device=device),
+                 position_ids=torch.full((3, 1), pos, dtype=torch.long, device=device))
+        return self.model(b, run=self.run, kv_cache=cache)[-1].float()
+
+    @staticmethod
+    def _pick(logits, temperature, top_p, generator):
+        if temperature <= 0:
+            return int(logits.argmax())
+        p = torch.softmax(logits / temperature, -1)
+        sp, si = torch.sort(p, descending=True)
+        keep = (sp.cumsum(0) - sp) < top_p
+        sp = sp * keep
+        return int(si[torch.multinomial(sp / sp.sum(), 1, generator=generator)])
+
+    @torch.no_grad()
     def generate(self, input_ids, pixel_values=None, image_grid_thw=None, max_new_tokens: int = 16, temperature: float = 0.0,
-                 top_p: float = 1.0, device="cpu", generator=None) -> torch.Tensor:
+                 top_p: float = 1.0, device="cpu", generator=None, use_cache: bool = True) -> torch.Tensor:
         ids = input_ids.clone()
-        for _ in range(max_new_tokens):
-            logits = self.next_logits(ids, pixel_values, image_grid_thw, device)
-            if temperature <= 0:
-                nxt = int(logits.argmax())
+        cache, pos = None, 0
+        for step in range(max_new_tokens):
+            if not use_cache:
+                logits = self.next_logits(ids, pixel_values, image_grid_thw, device)
+            elif cache is None:
+                logits, cache, pos = self._prefill(ids, pixel_values, image_grid_thw, device)
             else:
-                p = torch.softmax(logits / temperature, -1)
-                sp, si = torch.sort(p, descending=True)
-                keep = (sp.cumsum(0) - sp) < top_p
-                sp = sp * keep
-                nxt = int(si[torch.multinomial(sp / sp.sum(), 1, generator=generator)])
+                logits = self._decode(int(ids[-1]), pos, cache, device)
+                pos += 1
+            nxt = self._pick(logits.cpu(), temperature, top_p, generator)
             ids = torch.cat([ids, torch.tensor([nxt])])
             if self.eos is not None and nxt == self.eos:
                 break

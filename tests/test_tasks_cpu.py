@@ -62,6 +62,15 @@ def test_vlm_generate_and_wan_pipeline():
     gen = VLMGenerator(model, run=eng.run)
     out = gen.generate(torch.randint(0, 1000, (12,)), max_new_tokens=3)
     assert out.shape == (15,)
+    # the key / value cache gives the tokens of the exact (re-run the whole prefix) decoding, with an image in the prompt
+    from mindspeed_mm_b200.data.synthetic import SyntheticVLMDataset, SyntheticVLMSpec
+    smp = SyntheticVLMDataset(SyntheticVLMSpec(seq_len=90, images_per_sample=1, image_size=112, vocab_size=cfg.text.vocab_size,
+                                               image_token_id=cfg.image_token_id,
+                                               vision_start_token_id=cfg.vision_start_token_id))[0]
+    kw = dict(pixel_values=smp["pixel_values"], image_grid_thw=smp["image_grid_thw"], max_new_tokens=5)
+    cached = gen.generate(smp["input_ids"], use_cache=True, **kw)
+    exact = gen.generate(smp["input_ids"], use_cache=False, **kw)
+    assert torch.equal(cached, exact) and cached.shape == (95,)
     wc = WanConfig.tiny()
     with torch.device("meta"):
         dit = WanDiT(wc)

@@ -81,11 +81,15 @@ class VLMTrainerSpec:
     comm: str = "auto"
     freeze_vision: bool = False
     log_interval: int = 1
+    shard_size: Optional[int] = None     # < number of data ranks: hybrid sharding (shard inside, replicate across)
+    offload_optimizer: bool = False      # fp32 master weights + Adam moments in pinned host memory
+    reshard_after_forward: bool = True
 
 
 def build_vlm_trainer(spec: VLMTrainerSpec, device=None, data_iter=None, checkpointer=None) -> TrainEngine:
     dev, rank, world = init_distributed(None if device is None else str(device).split(":")[0])
-    ps = init_parallel_state(world_size=world, device_type=dev.type)
+    ps = init_parallel_state(world_size=world, device_type=dev.type,
+                             fully_shard_parallel_size=spec.shard_size if spec.shard_size else "auto")
     with torch.device("meta"):
         model = Qwen25VLModel(spec.model)
     if spec.freeze_vision:
@@ -95,7 +99,9 @@ def build_vlm_trainer(spec: VLMTrainerSpec, device=None, data_iter=None, checkpo
     engine = FSDPEngine(model.fsdp_units(), group=ps.get_fsdp_group() if world > 1 else False, device=dev,
                         param_dtype=spec.param_dtype, reduce_dtype=spec.reduce_dtype, opt=opt,
                         recompute=spec.recompute is not False, grad_accum_steps=spec.gradient_accumulation_steps,
-                        comm=spec.comm)
+                        comm=spec.comm, offload_optimizer=spec.offload_optimizer,
+                        replicate_group=ps.group("dp_replicate") if world > 1 and ps.size("dp_replicate") > 1 else None)
+    engine.select_units(None, reshard_after_forward=spec.reshard_after_forward)
     # python's hash() of str is salted per process: use a stable digest instead
     engine.materialize(stable_init_fn(spec.model.init_std, spec.seed))
     if spec.recompute == "auto" or (isinstance(spec.recompute, int) and not isinstance(spec.recompute, bool)):

@@ -201,7 +201,13 @@ class FSDPEngine:
                  reduce_dtype: torch.dtype = torch.float32, opt: Optional[OptimConfig] = None,
                  recompute: bool = True, grad_accum_steps: int = 1, prefetch: int = 1,
                  comm: str = "auto", grad_divide: Optional[float] = None,
-                 no_recompute: Sequence[str] = ("lm_head",), exclude_params: Sequence[nn.Parameter] = ()):
+                 no_recompute: Sequence[str] = ("lm_head",), exclude_params: Sequence[nn.Parameter] = (),
+                 replicate_group: Optional[dist.ProcessGroup] = None, offload_optimizer: bool = False):
+        """``replicate_group`` (hybrid sharding, HSDP): parameters are sharded over ``group`` and replicated over
+        ``replicate_group``; gradients are reduce-scattered inside the shard group and the reduced fp32 shard is then
+        all-reduced across the replicas before the update (fsdp/distributed/fully_shard_parallel.py:42-109 on a 2-D
+        mesh).  ``offload_optimizer``: fp32 master weights and Adam moments live in pinned host memory and visit the
+        device one flat group at a time for the update (the reference's ``offload_to_cpu`` / CPUOffloadPolicy)."""
         self.group = group
         self.world = dist.get_world_size(group) if (dist.is_initialized() and group is not False) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
@@ -211,7 +217,13 @@ class FSDPEngine:
         self.recompute = recompute
         self.grad_accum_steps = grad_accum_steps
         self.prefetch = prefetch
-        self.grad_divide = float(grad_divide if grad_divide is not None else self.world)
+        self.reshard_after_forward = True     # False: a unit stays gathered between its forward and its backward
+        self.activation_offload = None        # runtime.features.ActivationOffload for the units in _offload_units
+        self._offload_units: set = set()
+        self.replicate_group = replicate_group
+        self.replicas = dist.get_world_size(replicate_group) if replicate_group is not None else 1
+        self.offload_optimizer = offload_optimizer
+        self.grad_divide = float(grad_divide if grad_divide is not None else self.world * self.replicas)
         self.exclude_params = {id(p) for p in exclude_params}    # owned by another engine (e.g. experts)
         self.units: List[Unit] = [Unit(n, m, self) for n, m in units]
         for i, u in enumerate(self.units):
@@ -222,7 +234,8 @@ class FSDPEngine:
         self.comm_stream = torch.cuda.Stream(self.device) if self.cuda else None
         self.micro_step = 0
         self.lr = self.opt.lr
-        self.deferred = self.opt.clip_grad > 0 or grad_accum_steps > 1
+        # replicas and host-resident optimizer state both need the reduced gradient shard before the update runs
+        self.deferred = self.opt.clip_grad > 0 or grad_accum_steps > 1 or self.replicas > 1 or offload_optimizer
         self._sq_norm = torch.zeros((), dtype=torch.float32, device=self.device)
         self._dummy = torch.zeros((), device=self.device, requires_grad=True)
         self.comm = comm
@@ -242,6 +255,10 @@ class FSDPEngine:
             init_fn(u.name, u.module)
             for g in u.groups:
                 g.init_state()
+                if self.offload_optimizer and g.trainable:
+                    pin = self.cuda
+                    g.master, g.exp_avg, g.exp_avg_sq = (
+                        (t.cpu().pin_memory() if pin else t.cpu()) for t in (g.master, g.exp_avg, g.exp_avg_sq))
                 if g.world > 1:
                     g.release()
             u.unsharded = self.world == 1
@@ -284,9 +301,11 @@ class FSDPEngine:
             torch.cuda.current_stream().wait_event(u.ready_event)
             u.ready_event = None
 
-    def reshard(self, u: Unit) -> None:
+    def reshard(self, u: Unit, force: bool = False) -> None:
         if self.world == 1 or not u.unsharded:
             return
+        if getattr(u, "keep_gathered", False) and not force:
+            return          # "root" parameters: gathered once per micro-step, released in end_micro_step
         for g in u.groups:
             g.release()
         u.unsharded = False
@@ -330,7 +349,11 @@ class FSDPEngine:
                     first.register_hook(lambda g, u=u: self._offer_buffers(u))
             return out
         tensors, spec = _split_args(args, kwargs)
-        outs = _UnitFn.apply(self, u, spec, self._dummy, *tensors)
+        if self.activation_offload is not None and u.name in self._offload_units:
+            with self.activation_offload:         # the unit's saved inputs go to pinned host memory until its backward
+                outs = _UnitFn.apply(self, u, spec, self._dummy, *tensors)
+        else:
+            outs = _UnitFn.apply(self, u, spec, self._dummy, *tensors)
         return outs[0] if len(outs) == 1 and not u._tuple_out else outs
 
     def _prefetch_forward(self, u: Unit):
@@ -463,6 +486,17 @@ class FSDPEngine:
                 ops.ref.adamw_step(g.master[a:b], g.exp_avg[a:b], g.exp_avg_sq[a:b], grad[a:b], self.lr, o.betas[0],
                                    o.betas[1], o.eps, wd, g.step_count, grad_scale, g.shard16[a:b])
 
+    def _adamw_offloaded(self, g: FlatGroup, grad: torch.Tensor, grad_scale) -> None:
+        """Optimizer state on the host: bring master / moments of this group to the device, update, send them back."""
+        host = (g.master, g.exp_avg, g.exp_avg_sq)
+        g.master, g.exp_avg, g.exp_avg_sq = (t.to(self.device, non_blocking=True) for t in host)
+        self._adamw(g, grad, grad_scale)
+        for h, d in zip(host, (g.master, g.exp_avg, g.exp_avg_sq)):
+            h.copy_(d, non_blocking=True)
+        if self.cuda:
+            torch.cuda.current_stream().synchronize()     # the device copies are dropped next: the host copies must be done
+        g.master, g.exp_avg, g.exp_avg_sq = host
+
     def finish_step(self, lr: Optional[float] = None) -> Optional[torch.Tensor]:
         """Call after the last backward of an optimizer step.  Applies deferred updates (with the
         global-norm clip) and joins the side stream.  Returns the gradient norm when one was computed."""
@@ -475,6 +509,9 @@ class FSDPEngine:
         if self.deferred:
             groups = [g for u in self.units for g in u.groups if g.trainable and g.grad32 is not None]
             scale = 1.0
+            if self.replicas > 1:       # HSDP: sum the shard over the replicas (the 1/N of all data ranks is in grad_divide)
+                for g in groups:
+                    dist.all_reduce(g.grad32, group=self.replicate_group)
             if self.opt.clip_grad > 0:
                 sq = torch.stack([g.grad32.float().pow(2).sum() for g in groups]).sum()
                 if self.world > 1:
@@ -484,7 +521,10 @@ class FSDPEngine:
             if self.grad_accum_steps > 1:
                 scale = scale / self.grad_accum_steps
             for g in groups:
-                self._adamw(g, g.grad32, scale)
+                if self.offload_optimizer:
+                    self._adamw_offloaded(g, g.grad32, scale)
+                else:
+                    self._adamw(g, g.grad32, scale)
                 g.grad32 = None
             if self._p2p is not None:
                 self._p2p.step_barrier()
@@ -494,13 +534,28 @@ class FSDPEngine:
     def set_lr(self, lr: float) -> None:
         self.lr = lr
 
+    def select_units(self, apply_names: Optional[Sequence[str]] = None, reshard_after_forward: bool = True) -> None:
+        """Sharding plan of the native schema.  ``apply_names``: units gathered and released one by one (the modules a
+        recipe lists under ``fsdp_plan.apply_modules``); every other unit belongs to the "root" wrap: sharded as well,
+        but gathered once per micro-step and released after the backward, like the parameters the reference leaves to
+        the outer ``fully_shard(model)`` (fsdp/distributed/fully_shard_parallel.py:98-109).  ``reshard_after_forward``
+        False keeps every unit gathered between forward and backward (no second gather, more memory)."""
+        self.reshard_after_forward = reshard_after_forward
+        if apply_names is not None:
+            names = set(apply_names)
+            for u in self.units:
+                u.keep_gathered = u.name not in names
+
+    def set_activation_offload(self, offload, unit_names: Sequence[str]) -> None:
+        self.activation_offload, self._offload_units = offload, set(unit_names)
+
     def end_micro_step(self) -> None:
         """Call after each micro-batch's backward."""
         self.flush_pending()
         self._seal_order()
         for u in self.units:
             u.bwd_done = False
-            self.reshard(u)       # anything a prefetch gathered but nobody consumed
+            self.reshard(u, force=True)       # anything a prefetch gathered but nobody consumed, and the root units
         self.micro_step += 1
 
     # ------------------------------------------------------------------ state
@@ -651,7 +706,8 @@ class _UnitFn(torch.autograd.Function):
         ctx.act_cache = []
         with torch.no_grad(), ops.activation_cache(ctx.act_cache, "record"):
             out = u.module(*args, **kwargs)
-        engine.reshard(u)
+        if engine.reshard_after_forward:
+            engine.reshard(u)
         ctx.save_for_backward(*tensors)
         ctx.needs = [t.requires_grad for t in tensors]
         u._tuple_out = isinstance(out, (tuple, list))

@@ -41,6 +41,13 @@ class ParallelSizes:
     def resolve(self) -> "ParallelSizes":
         """Size algebra of ParallelArguments.model_post_init (fsdp/params/parallel_args.py:98-152)."""
         w = self.world_size
+        # hybrid sharding: a shard size smaller than the data-parallel extent implies replica groups
+        # (fsdp/distributed/parallel_state.py:109-113 builds the same 2-D mesh when sharding_size < world)
+        if self.fully_shard_parallel_size not in ("auto", None, -1) and self.data_parallel_replicate_size == 1:
+            rest = (self.pipeline_parallel_size * self.ring_attention_size * self.ulysses_parallel_size
+                    * self.tensor_parallel_size * int(self.fully_shard_parallel_size))
+            if rest and w % rest == 0 and w // rest > 1:
+                self.data_parallel_replicate_size = w // rest
         fixed = (self.pipeline_parallel_size * self.data_parallel_replicate_size * self.ring_attention_size
                  * self.ulysses_parallel_size * self.tensor_parallel_size)
         if w % fixed:

@@ -114,11 +114,6 @@ class Trainer:
             keys = tuple(t.no_decay_params) + tuple(t.no_decay_modules)
             opt.no_decay = lambda n, p: p.dim() < 2 or any(k in n for k in keys)
         units = self.model.fsdp_units()
-        if plan.apply_modules:
-            wanted = set(match_modules(plan.apply_modules, [n for n, _ in units]))
-            if wanted and wanted != {n for n, _ in units}:
-                print_rank0(f"fsdp_plan.apply_modules selects {len(wanted)} of {len(units)} units; "
-                            "the remaining units are sharded as well (every parameter must live in one unit)")
         recompute = a.features.recompute or a.parallel.recompute
         group = self.ps.get_fsdp_group() if self.world > 1 else False
         common = dict(device=self.device, param_dtype=get_dtype(plan.param_dtype or "bf16")
@@ -126,19 +121,55 @@ class Trainer:
                       reduce_dtype=get_dtype(plan.reduce_dtype or "fp32"), opt=opt,
                       grad_accum_steps=t.gradient_accumulation_steps or 1)
         prefetch = max(plan.num_to_forward_prefetch or 0, plan.num_to_backward_prefetch or 0)
+        # hybrid sharding: shard inside dp_shard(_cp), replicate over dp_replicate
+        rep = self.ps.group("dp_replicate") if self.world > 1 and self.ps.size("dp_replicate") > 1 else None
+        common.update(replicate_group=rep, offload_optimizer=bool(plan.cpu_offload or t.optimizer == "adamw_swap"))
         expert_units = self.model.expert_units() if hasattr(self.model, "expert_units") else []
         if not expert_units:
-            return FSDPEngine(units, group=group, recompute=recompute, prefetch=prefetch, comm=plan.comm, **common)
+            eng = FSDPEngine(units, group=group, recompute=recompute, prefetch=prefetch, comm=plan.comm, **common)
+            self._apply_plan(eng, units)
+            return eng
         # MoE: dense parameters over the FSDP group; expert parameters over the expert-FSDP group (size 1 when
         # ep == ranks per stage), their gradients divided by the full data-parallel size.
         from ..parallel.fsdp import EngineMux
         ex = [p for _, m in expert_units for p in m.parameters()]
         dense = FSDPEngine(units, group=group, recompute=recompute, prefetch=prefetch, comm=plan.comm, exclude_params=ex,
                            **common)
+        self._apply_plan(dense, units)
+        common.update(replicate_group=None)
         eg = self.ps.group("efsdp") if self.ps.size("efsdp") > 1 else False
         expert = FSDPEngine(expert_units, group=eg, grad_divide=self.ps.get_dp_world_size(), no_recompute=(),
                             comm="nccl", **common)
         return EngineMux(dense, expert, ep_group=self.ps.group("ep") if self.ps.size("ep") > 1 else None)
+
+    def _apply_plan(self, eng: FSDPEngine, units) -> None:
+        """``fsdp_plan`` and memory features of the native schema, applied to the sharding engine."""
+        a, plan, feat = self.args, self.args.parallel.fsdp_plan, self.args.features
+        names = [n for n, _ in units]
+        mod_names = [n for n, _ in self.model.named_modules()]
+        wanted = None
+        if plan.apply_modules:
+            hit = set(match_modules(plan.apply_modules, names))
+            # a pattern may name a parent of several units ("model.visual") or the model itself: those add nothing
+            if hit:
+                wanted = hit
+        eng.select_units(wanted, reshard_after_forward=plan.reshard_after_forward)
+        for n in match_modules(plan.ignored_modules, mod_names):
+            m = dict(self.model.named_modules())[n]
+            if any(p.requires_grad for p in m.parameters()):
+                raise ValueError(f"fsdp_plan.ignored_modules: '{n}' has trainable parameters; the sharding engine owns every "
+                                 f"trainable parameter (freeze the module with model.freeze to leave it out of training)")
+        if feat.enable_activation_offload:
+            from .features import ActivationOffload
+            pats = feat.activation_offload_plan.apply_modules or []
+            eng.set_activation_offload(ActivationOffload(self.device), match_modules(pats, names) if pats else names)
+        if feat.enable_chunk_mbs and feat.chunkmbs_plan.apply_modules:
+            from .features import chunk_mbs
+            cp = feat.chunkmbs_plan
+            table = dict(self.model.named_modules())
+            for n in match_modules(cp.apply_modules, mod_names):
+                table[n].forward = chunk_mbs(table[n].forward, cp.chunk_mbs, cp.batch_dim, tuple(cp.chunk_arg_indexs),
+                                             tuple(cp.chunk_kwarg_names))
 
     def load_weights(self):
         t = self.args.training

@@ -36,6 +36,9 @@ def main():
     ap.add_argument("--comm", default="auto")
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--clip", type=float, default=0.0)
+    ap.add_argument("--shard-size", type=int, default=0, help="hybrid sharding: ranks per shard group (replicas = world / it)")
+    ap.add_argument("--offload", action="store_true", help="optimizer state in host memory")
+    ap.add_argument("--keep-gathered", action="store_true", help="reshard_after_forward = False")
     ap.add_argument("--recompute-layers", type=int, default=-1,
                     help=">= 0: recompute only that many decoder layers, keep the graph of the rest")
     a = ap.parse_args()
@@ -44,7 +47,9 @@ def main():
     cfg = small_cfg()
     spec = VLMTrainerSpec(model=cfg, lr=1e-3, lr_warmup_ratio=0.0, lr_decay_style="constant", param_dtype=dtype,
                           clip_grad=a.clip, comm=a.comm, log_interval=0, weight_decay=0.01,
-                          recompute=True if a.recompute_layers < 0 else a.recompute_layers)
+                          recompute=True if a.recompute_layers < 0 else a.recompute_layers,
+                          shard_size=a.shard_size or None, offload_optimizer=a.offload,
+                          reshard_after_forward=not a.keep_gathered)
     tr = build_vlm_trainer(spec, device=a.device)
     rank, world = dist.get_rank(), dist.get_world_size()
     packs = [make_batches(cfg, a.steps, 512, 1, 1, 224, r, pin=False) for r in range(world)]
@@ -91,10 +96,13 @@ def main():
             # +-lr steps and bf16 storage has 2^-8 relative spacing, so compare the mean deviation instead.
             d = (full[n] - t).abs().max().item() if not cuda else (full[n] - t).abs().mean().item()
             worst = max(worst, d)
-            if d > (3e-4 if cuda else 2e-5):
+            # fp32: summation order differs with the number of ranks; Adam's normalised step turns that into ~1e-5 steps
+            if d > (3e-4 if cuda else (2e-5 if world <= 2 else 5e-5)):
                 ok = False
                 print(f"param mismatch {n}: {d}")
-        print(f"dist_fsdp_check world={world} device={a.device} comm={a.comm} "
+        if a.shard_size:
+            ok = ok and tr.engine.world == a.shard_size and tr.engine.replicas == world // a.shard_size
+        print(f"dist_fsdp_check world={world} shard={tr.engine.world} replicas={tr.engine.replicas} device={a.device} comm={a.comm} "
               f"p2p={getattr(tr.engine, '_p2p', None) is not None} losses={losses} ref={ref_losses} "
               f"max_param_diff={worst:.3e} ok={ok}", flush=True)
     flag = torch.tensor([int(ok)], device=tr.device)

@@ -36,6 +36,26 @@ def test_gloo_world2_with_clipping():
     assert "ok=True" in out
 
 
+def test_gloo_world4_hybrid_sharding_matches_single_process():
+    """HSDP: shard groups of 2, 2 replicas; reduce-scatter inside the shard group, all-reduce of the shard across
+    replicas, one update; with clipping the norm is taken after both reductions."""
+    out = _run(4, "--device", "cpu", "--steps", "2", "--shard-size", "2", "--clip", "0.5")
+    assert "ok=True" in out and "shard=2 replicas=2" in out
+
+
+def test_gloo_world2_optimizer_state_on_host_and_units_kept_gathered():
+    out = _run(2, "--device", "cpu", "--steps", "2", "--offload", "--keep-gathered")
+    assert "ok=True" in out
+
+
+@pytest.mark.gpu
+def test_gpu_world2_hybrid_options():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    out = _run(2, "--device", "cuda", "--comm", "p2p", "--steps", "3", "--offload", "--keep-gathered")
+    assert "ok=True" in out
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("comm", ["p2p", "nccl"])
 def test_gpu_world2(comm):

@@ -249,8 +249,8 @@ class TrainingArguments(_Base):
     train_iters: int = 10
     train_epochs: Optional[int] = None
     load: Optional[str] = None
-    load_format: Literal["auto", "hf", "dcp"] = "auto"
-    save_format: Literal["auto", "hf", "dcp"] = "dcp"
+    load_format: Literal["auto", "hf", "dcp", "sharded"] = "auto"
+    save_format: Literal["auto", "hf", "dcp", "sharded"] = "dcp"
     load_strict: bool = True
     no_load_optim: bool = False
     no_load_rng: bool = False

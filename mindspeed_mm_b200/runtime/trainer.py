@@ -59,8 +59,7 @@ class Trainer:
                                    lr_warmup_ratio=t.lr_warmup_ratio, lr_min=t.lr_min, lr_start=t.lr_start,
                                    lr_decay_ratio=t.lr_decay_ratio)
         self.data_iter, self.val_iter_fn = self.build_data()
-        self.checkpointer = DistributedCheckpointer(t.save, t.load if t.load_format != "hf" else None, t.save_async,
-                                                    t.no_save_optim, t.no_save_rng) if (t.save or t.load) else None
+        self.checkpointer = self.build_checkpointer()
         cfg = TrainConfig(train_iters=t.train_iters, micro_batch_size=t.micro_batch_size,
                           gradient_accumulation_steps=t.gradient_accumulation_steps or 1,
                           global_batch_size=t.global_batch_size, log_interval=t.log_interval,
@@ -142,6 +141,37 @@ class Trainer:
                             comm="nccl", **common)
         return EngineMux(dense, expert, ep_group=self.ps.group("ep") if self.ps.size("ep") > 1 else None)
 
+    def hf_ops(self):
+        """Hugging Face <-> internal name / layout map of the model, when it has one."""
+        ops = getattr(self.model, "hf_ops", None)
+        if ops is None and self.args.model.model_id == "qwen2_5vl":
+            ops = hfio.qwen25vl_ops(self.model.config)
+        return ops() if callable(ops) else ops
+
+    def build_checkpointer(self):
+        """Training checkpoints: torch DCP (``iter_XXXXXXX/`` with Hugging Face parameter names, the layout of the
+        reference's native trainer) for data-parallel sharding; per-rank shard files (``save_format: sharded``, and always
+        under expert / tensor / pipeline parallelism, where ranks hold different parameters).  A load directory is read
+        in the format it was written in."""
+        t = self.args.training
+        if not (t.save or t.load):
+            return None
+        load = t.load if t.load_format != "hf" else None
+        from ..parallel.fsdp import EngineMux
+        plain = not isinstance(self.engine, EngineMux) and self.ps.size("tp") == 1 and self.ps.size("pp") == 1
+        fmt = "dcp" if (plain and t.save_format in ("dcp", "auto", "hf")) else "sharded"
+        if load and os.path.isdir(load):
+            from ..checkpoint.sharded import read_tracker, iter_dir
+            tag = open(os.path.join(load, "latest_checkpointed_iteration.txt")).read().strip() \
+                if os.path.exists(os.path.join(load, "latest_checkpointed_iteration.txt")) else ""
+            sub = os.path.join(load, "release") if tag == "release" else (iter_dir(load, int(tag)) if tag else load)
+            if os.path.isdir(sub):
+                fmt = "dcp" if os.path.exists(os.path.join(sub, ".metadata")) else "sharded"
+        if fmt == "dcp":
+            from ..checkpoint.dcp import TorchDCPCheckpointer
+            return TorchDCPCheckpointer(t.save, load, t.save_async, t.no_save_optim, t.no_save_rng, ops=self.hf_ops())
+        return DistributedCheckpointer(t.save, load, t.save_async, t.no_save_optim, t.no_save_rng)
+
     def _apply_plan(self, eng: FSDPEngine, units) -> None:
         """``fsdp_plan`` and memory features of the native schema, applied to the sharding engine."""
         a, plan, feat = self.args, self.args.parallel.fsdp_plan, self.args.features
@@ -178,9 +208,7 @@ class Trainer:
         path = t.load or self.args.model.model_name_or_path
         fmt = t.load_format
         if path and (fmt == "hf" or (fmt == "auto" and hfio.is_hf_checkpoint(path))):
-            ops = getattr(self.model, "hf_ops", None)
-            if ops is None and self.args.model.model_id == "qwen2_5vl":
-                ops = hfio.qwen25vl_ops(self.model.config)
+            ops = self.hf_ops()
             if ops is not None:
                 hfio.load_hf_into_engine(self.engine, path, ops, strict=t.load_strict)
 

@@ -234,3 +234,54 @@ def test_parity_with_transformers_tiny():
         logits = out.logits[0].float()
         ref = torch.nn.functional.cross_entropy(logits, batch["labels"], ignore_index=-100, reduction="sum")
     assert abs(float(loss_sum) - float(ref)) / float(ref) < 2e-4, (float(loss_sum), float(ref))
+
+
+def test_torch_dcp_checkpoint_written_by_two_ranks_resumes_on_one(tmp_path):
+    """DCP layout of the reference's native trainer: iter_XXXXXXX/ + extra_state/ + tracker, Hugging Face parameter
+    names, row-sharded tensors.  Written by 2 gloo ranks (background save), resumed by 1 process: same next loss."""
+    import re
+    import subprocess
+    import sys as _sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    _sys.path.insert(0, here)
+    import dist_dcp_check as dc
+    from mindspeed_mm_b200.checkpoint.dcp import TorchDCPCheckpointer
+    ck_dir = str(tmp_path / "dcp")
+    cmd = [_sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(29700 + os.getpid() % 200), os.path.join(here, "dist_dcp_check.py"), ck_dir, "--async"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    want = float(re.search(r"next_loss=([\d.]+)", r.stdout).group(1))
+    it = os.path.join(ck_dir, "iter_0000001")
+    assert open(os.path.join(ck_dir, "latest_checkpointed_iteration.txt")).read() == "1"
+    assert os.path.exists(os.path.join(it, ".metadata")) and os.path.exists(os.path.join(it, "extra_state", "extra_state_rank_1.pt"))
+    from torch.distributed.checkpoint import FileSystemReader
+    keys = set(FileSystemReader(it).read_metadata().state_dict_metadata)
+    assert "model.model.language_model.layers.0.self_attn.q_proj.weight" in keys          # un-fused HF names
+    assert "optimizer.state.model.language_model.layers.0.mlp.gate_proj.weight.exp_avg_sq" in keys
+    cfg = dc.small_cfg()
+    m, e = dc.build(cfg, False)
+    extra = TorchDCPCheckpointer(ck_dir, ops=hfio.qwen25vl_ops(cfg)).load(e)
+    assert extra["iteration"] == 1 and extra["consumed_train_samples"] == 2
+    from bench import make_batches
+    b = make_batches(cfg, 2, 300, 1, 1, 224, 0, pin=False)
+    assert abs(dc.step(m, e, b[1]) - want) < 1e-5
+
+
+def test_hf_to_dcp_release_checkpoint_loads_into_the_engine(tmp_path):
+    """``mm-convert ... hf_to_dcp`` writes <dir>/release as DCP with HF names: the trainer-side checkpointer loads it
+    (weights only, no optimizer / extra state)."""
+    from mindspeed_mm_b200.checkpoint.convert_cli import Qwen2_5_VLConverter
+    from mindspeed_mm_b200.checkpoint.dcp import TorchDCPCheckpointer
+    import dist_dcp_check as dc
+    cfg = dc.small_cfg()
+    hf_dir, dcp_dir = str(tmp_path / "hf"), str(tmp_path / "dcp")
+    sd = fake_hf_state(cfg)
+    hfio.save_sharded(sd, hf_dir)
+    Qwen2_5_VLConverter.hf_to_dcp({"hf_dir": hf_dir, "dcp_dir": dcp_dir})
+    m, e = dc.build(cfg, False)
+    assert TorchDCPCheckpointer(None, dcp_dir, ops=hfio.qwen25vl_ops(cfg)).load(e) == {}
+    got = dict(e.named_full_params())
+    want = hfio.to_internal({k: v.clone() for k, v in sd.items()}, hfio.qwen25vl_ops(cfg))
+    for n, t in want.items():
+        assert torch.allclose(got[n].float(), t.float(), atol=1e-6), n

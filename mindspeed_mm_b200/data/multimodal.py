@@ -277,7 +277,12 @@ class MultimodalConversationDataset(Dataset):
         if template is None:
             cfg = getattr(model, "config", None)
             sid = getattr(tok, "special_ids", None)
-            if sid is not None:
+            if tokenizer is None and cfg is not None and hasattr(cfg, "image_token_id"):
+                # stand-in byte tokenizer (no tokenizer files): the placeholder ids are the model's, so that the
+                # vision features land where the model looks for them
+                template = ChatTemplate(tok, cfg.image_token_id, getattr(cfg, "video_token_id", None),
+                                        cfg.vision_start_token_id, getattr(cfg, "vision_end_token_id", None))
+            elif sid is not None:
                 template = ChatTemplate(tok, sid["<|image_pad|>"], sid["<|video_pad|>"], sid["<|vision_start|>"], sid["<|vision_end|>"])
             elif cfg is not None:
                 template = ChatTemplate(tok, cfg.image_token_id, getattr(cfg, "video_token_id", None),

@@ -63,18 +63,60 @@ def model_provider(kind: str, args):
     raise ValueError(f"unknown entry kind {kind}")
 
 
-def datasets_provider(kind: str, args, model, ps):
-    """Synthetic datasets of the model's shapes unless ``args.mm.data`` names a registered dataset."""
+class _Namespace:
+    """Attribute view of a dict (the dataset classes read ``dataset_param.basic_parameters`` etc.)."""
+
+    def __init__(self, d: dict):
+        self.__dict__.update(d)
+
+
+def _real_dataset(data: dict, model):
+    """The dataset that ``--mm-data`` names, when its type is registered and its files exist; None otherwise.
+    ``dataset_type``: huggingface / multimodal (sharegpt conversations with images or video), feature (pre-extracted
+    latents + prompt embeddings), t2v / i2v (raw video or image + caption); mindspeed_mm/data/__init__.py:30-95."""
+    from ..data import data_register
+    from ..data import multimodal as _mm   # noqa: F401  (registers huggingface / multimodal / feature / t2v / i2v)
+    dp = data.get("dataset_param") or {}
+    kind = dp.get("dataset_type")
+    if not kind or kind.startswith("synthetic"):
+        return None
+    try:
+        cls = data_register.get(kind)
+    except KeyError:
+        return None
+    basic = dp.get("basic_parameters") or {}
+    src = basic.get("dataset") or basic.get("data_path") or basic.get("index")
+    files = [src] if isinstance(src, str) else list(src or [])
+    root = basic.get("dataset_dir") or basic.get("data_folder") or ""
+    paths = [f if os.path.isabs(f) or not root or os.path.exists(f) else os.path.join(root, f) for f in files]
+    if not paths or not all(os.path.exists(p) for p in paths):
+        return None
+    return cls(_Namespace(dict(dataset_type=kind, basic_parameters=basic,
+                               preprocess_parameters=dp.get("preprocess_parameters") or {}, attr=dp.get("attr") or {})),
+               model=model)
+
+
+def datasets_provider(kind: str, args, model, ps, consumed_samples: int = 0):
+    """Training batches for the legacy entry points.
+
+    ``--mm-data`` decides: a registered ``dataset_type`` whose files exist is read for real (conversation json / jsonl
+    through the chat template and the image processor, feature folders, raw video + captions); otherwise synthetic
+    samples of the model's shapes are generated (no files needed: benchmarks, smoke tests).  ``dataloader_mode:
+    dynamic_batching`` packs samples greedily up to ``--seq-length`` tokens per micro-batch
+    (mindspeed_mm/data/dataloader/dynamic_batching_dataloader.py:37-159); ``consumed_samples`` (from a resumed
+    checkpoint) fast-forwards the sampler (pretrain_vlm.py:217)."""
     from ..data.collate import PackedVLMCollator
     from ..data.samplers import BaseRandomBatchSampler
     from ..data.synthetic import (SyntheticVideoLatentDataset, SyntheticVideoLatentSpec, SyntheticVLMDataset,
                                   SyntheticVLMSpec)
     data = args.mm.data.to_dict() if hasattr(args.mm, "data") else {}
     basic = data.get("dataset_param", {}).get("basic_parameters", {})
+    dl = data.get("dataloader_param") or {}
+    real = _real_dataset(data, model)
     if kind == "vlm":
         cfg = model.config
         seq = int(args.seq_length or 1024)
-        ds = SyntheticVLMDataset(SyntheticVLMSpec(
+        ds = real if real is not None else SyntheticVLMDataset(SyntheticVLMSpec(
             seq_len=seq, images_per_sample=int(basic.get("images_per_sample", 1)), image_size=int(basic.get("image_size", 224)),
             vocab_size=cfg.text.vocab_size, image_token_id=cfg.image_token_id,
             vision_start_token_id=cfg.vision_start_token_id, seed=args.seed, num_samples=int(basic.get("num_samples", 1 << 20))))
@@ -84,14 +126,34 @@ def datasets_provider(kind: str, args, model, ps):
     else:
         c = model.predictor.config
         channels = getattr(c, "in_dim", None) or getattr(c, "in_channels")       # Wan names it in_dim, the other DiTs in_channels
-        ds = SyntheticVideoLatentDataset(SyntheticVideoLatentSpec(
+        ds = real if real is not None else SyntheticVideoLatentDataset(SyntheticVideoLatentSpec(
             channels=channels, frames=int(basic.get("frames", 5)), height=int(basic.get("height", 16)),
             width=int(basic.get("width", 16)), text_len=int(getattr(c, "text_len", basic.get("text_len", 16))),
             text_dim=c.text_dim, seed=args.seed,
             pooled_dim=int(c.pooled_dim) if getattr(model.predictor, "cond_input", "") == "added_cond" else 0,
             num_samples=int(basic.get("num_samples", 1 << 20))))
         coll = lambda ss: {k: torch.stack([s[k] for s in ss]) for k in ss[0]}   # noqa: E731
-    sampler = BaseRandomBatchSampler(len(ds), args.micro_batch_size, ps.get_dp_rank(), ps.get_dp_world_size(), seed=args.seed)
+    shuffle = bool(dl.get("shuffle", True))
+    if real is not None:
+        print_rank0(f"> dataset: {type(ds).__name__} with {len(ds)} samples ({data['dataset_param'].get('dataset_type')})")
+    if kind == "vlm" and dl.get("dataloader_mode") == "dynamic_batching":
+        # one sample at a time from the sampler, packed greedily to at most `seq` tokens per micro-batch
+        from ..data.packing import DynamicBatcher
+        sampler = BaseRandomBatchSampler(len(ds), 1, ps.get_dp_rank(), ps.get_dp_world_size(), seed=args.seed,
+                                         shuffle=shuffle, drop_last=bool(dl.get("drop_last", True)))
+        sampler.consumed = int(consumed_samples)
+
+        def samples():
+            for idx in sampler:
+                yield ds[idx[0]]
+
+        def gen():
+            for group in DynamicBatcher(samples(), seq, int(dl.get("dynamic_batch_buffer_size", 200))):
+                yield coll(group)
+        return gen()
+    sampler = BaseRandomBatchSampler(len(ds), args.micro_batch_size, ps.get_dp_rank(), ps.get_dp_world_size(), seed=args.seed,
+                                     shuffle=shuffle, drop_last=bool(dl.get("drop_last", True)))
+    sampler.consumed = int(consumed_samples)
 
     def gen():
         for idx in sampler:
@@ -110,24 +172,33 @@ def pretrain(kind: str, argv=None, device: Optional[str] = None):
     uly = cp if args.context_parallel_algo in ("ulysses_cp_algo", "hybrid_cp_algo") else 1
     if args.context_parallel_algo == "hybrid_cp_algo":
         uly = int(getattr(args, "ulysses_degree_in_cp", None) or cp)
+    f2 = None
+    if getattr(args, "fsdp2_config_path", None):
+        from ..config.legacy import load_fsdp2_config
+        f2 = load_fsdp2_config(args.fsdp2_config_path)
+    shard = f2["sharding_size"] if f2 and f2["sharding_size"] not in (None, world) else None
+    if shard and (shard > world or world % shard or shard % cp):
+        print_rank0(f"fsdp2 config asks for sharding_size={shard}, which does not divide the {world} ranks of this job: "
+                    f"sharding over all data ranks instead")
+        shard = None
     ps = init_parallel_state(world_size=world, device_type=dev.type, ulysses_parallel_size=uly,
-                             ring_attention_size=cp // uly)
+                             ring_attention_size=cp // uly,
+                             fully_shard_parallel_size=(int(shard) // cp if shard else "auto"))
     model = model_provider(kind, args)
     opt = OptimConfig(lr=args.lr, betas=(args.adam_beta1, args.adam_beta2), eps=args.adam_eps,
                       weight_decay=args.weight_decay, clip_grad=args.clip_grad)
     accum = max(1, args.global_batch_size // (args.micro_batch_size * ps.get_dp_world_size()))
     param_dtype = torch.bfloat16 if (args.bf16 and dev.type == "cuda") else torch.float32
     extra = {}
-    if getattr(args, "fsdp2_config_path", None):
-        from ..config.legacy import load_fsdp2_config
-        f2 = load_fsdp2_config(args.fsdp2_config_path)
+    if f2 is not None:
         if f2["param_dtype"] is not None and dev.type == "cuda":
             param_dtype = f2["param_dtype"]
         if f2["reduce_dtype"] is not None:
             extra["reduce_dtype"] = f2["reduce_dtype"]
-        if f2["sharding_size"] not in (None, world):
-            print_rank0(f"fsdp2 config asks for sharding_size={f2['sharding_size']}; sharding over the whole data-parallel group "
-                        f"({world} ranks) instead")
+        if world > 1 and ps.size("dp_replicate") > 1:         # sharding_size < ranks: hybrid sharding
+            extra["replicate_group"] = ps.group("dp_replicate")
+        if f2.get("offload_to_cpu"):
+            extra["offload_optimizer"] = True
         if f2["unknown_keys"]:
             print_rank0(f"fsdp2 config keys without effect here: {f2['unknown_keys']}")
     engine = FSDPEngine(model.fsdp_units(), group=ps.get_fsdp_group() if world > 1 else False, device=dev,
@@ -155,10 +226,12 @@ def pretrain(kind: str, argv=None, device: Optional[str] = None):
         sp = prof_cfg.static_param
         prof = Profiler(True, getattr(prof_cfg, "ranks", [0]), sp.start_step, sp.end_step, sp.save_path)
     te = TrainEngine(model, engine, build_loss(loss_type, ps.group("dp"), ps.get_dp_world_size()), sched, cfg,
-                     data_iter=datasets_provider(kind, args, model, ps), checkpointer=ck, profiler=prof,
+                     data_iter=None, checkpointer=ck, profiler=prof,
                      dp_group=ps.group("dp"), dp_world=ps.get_dp_world_size(), device=dev)
     if ck and args.load:
         te.load(load_optim=not args.no_load_optim, load_rng=not args.no_load_rng)
+    # the sampler continues after the samples a resumed run has already consumed
+    te.data_iter = datasets_provider(kind, args, model, ps, consumed_samples=te.consumed_train_samples)
     print_rank0(f"> parallel: {ps.describe()} | parameters: {engine.param_count() / 1e6:.1f} M")
     hist = te.train()
     if dist.is_initialized():

@@ -45,3 +45,51 @@ def test_pretrain_vlm_and_sora_run_from_their_json(tmp_path, capsys):
                              "--global-batch-size", "2", "--lr", "1e-4"], device="cpu")
     assert len(hist) == 2 and all(torch.isfinite(torch.tensor(h["loss"])) for h in hist)
     _reset()
+
+
+def test_pretrain_vlm_reads_a_sharegpt_json_with_the_reference_data_schema(tmp_path, capsys):
+    """``--mm-data`` in the reference's schema (examples/qwen2.5vl/data_7b.json) naming a real sharegpt file with images:
+    the conversations go through the chat template + image processor, ``dynamic_batching`` packs them to the sequence
+    length, and a resumed run continues after the samples already consumed."""
+    from PIL import Image
+    from mindspeed_mm_b200.runtime.legacy_entry import datasets_provider, pretrain
+    img_dir = tmp_path / "images"
+    img_dir.mkdir()
+    recs = []
+    for i in range(6):
+        Image.new("RGB", (56 + 28 * (i % 2), 56), (40 * i, 10, 200 - 30 * i)).save(img_dir / f"{i}.png")
+        recs.append({"messages": [{"role": "user", "content": f"<image>what is picture {i}?"},
+                                  {"role": "assistant", "content": f"picture number {i} " * (1 + i)}],
+                     "images": [f"images/{i}.png"]})
+    (tmp_path / "sft.json").write_text(json.dumps(recs))
+    data = {"dataset_param": {"dataset_type": "huggingface",
+                              "preprocess_parameters": {"model_name_or_path": "./missing", "image_max_pixels": 12544,
+                                                        "image_min_pixels": 0},
+                              "basic_parameters": {"template": "qwen2vl", "dataset_dir": str(tmp_path), "dataset": "sft.json",
+                                                   "cutoff_len": 256},
+                              "attr": {"images": "images", "messages": "messages", "role_tag": "role",
+                                       "content_tag": "content", "user_tag": "user", "assistant_tag": "assistant"}},
+            "dataloader_param": {"dataloader_mode": "dynamic_batching", "drop_last": True, "shuffle": False,
+                                 "sampler_type": "BaseRandomBatchSampler", "dynamic_batch_buffer_size": 3,
+                                 "collate_param": {"model_name": "qwen2vl", "ignore_pad_token_for_loss": True}}}
+    d = tmp_path / "data.json"
+    d.write_text(json.dumps(data))
+    argv = ["--mm-model", os.path.join(ROOT, "examples/qwen2.5vl/model_tiny.json"), "--mm-data", str(d), "--train-iters", "2",
+            "--micro-batch-size", "1", "--global-batch-size", "1", "--lr", "1e-4", "--seq-length", "256", "--seed", "3"]
+    hist = pretrain("vlm", argv, device="cpu")
+    out = capsys.readouterr().out
+    assert len(hist) == 2 and all(h["loss"] == h["loss"] for h in hist)
+    assert "MultimodalConversationDataset with 6 samples" in out
+    _reset()
+    # packing: several conversations per micro-batch, never longer than the sequence length; resume skips consumed samples
+    from mindspeed_mm_b200.config.legacy import parse_legacy_args
+    from mindspeed_mm_b200.parallel.state import init_parallel_state
+    from mindspeed_mm_b200.runtime.legacy_entry import model_provider
+    args = parse_legacy_args(argv)
+    ps = init_parallel_state(world_size=1, device_type="cpu")
+    model = model_provider("vlm", args)
+    first = next(datasets_provider("vlm", args, model, ps))
+    assert first["cu_seqlens"].numel() > 2 and int(first["cu_seqlens"][-1]) <= 256 and "pixel_values" in first
+    resumed = next(datasets_provider("vlm", args, model, ps, consumed_samples=3))
+    assert resumed["input_ids"].shape != first["input_ids"].shape or not torch.equal(resumed["input_ids"], first["input_ids"])
+    _reset()

@@ -12,7 +12,7 @@ from typing import Callable, Iterator, Optional, Tuple
 import torch
 from torch.utils.data import DataLoader
 
-from .registry import data_register
+from ..models.registry import data_register
 from . import synthetic  # noqa: F401  (registers the synthetic datasets)
 from . import anyres  # noqa: F401  (registers the tiled conversation dataset)
 

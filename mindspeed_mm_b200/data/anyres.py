@@ -240,7 +240,7 @@ class TiledConversationDataset(torch.utils.data.Dataset):
 
 
 def _register():
-    from .registry import data_register
+    from ..models.registry import data_register
     data_register.register("deepseekvl2")(TiledConversationDataset)
 
 

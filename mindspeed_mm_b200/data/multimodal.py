@@ -24,7 +24,7 @@ from typing import Callable, Dict, List, Optional, Sequence, Tuple
 import torch
 from torch.utils.data import Dataset
 
-from .registry import data_register
+from ..models.registry import data_register
 from .synthetic import CLIP_MEAN, CLIP_STD
 
 

@@ -14,7 +14,7 @@ from typing import Dict, List, Optional
 import torch
 from torch.utils.data import Dataset
 
-from .registry import data_register
+from ..models.registry import data_register
 
 CLIP_MEAN = (0.48145466, 0.4578275, 0.40821073)
 CLIP_STD = (0.26862954, 0.26130258, 0.27577711)

@@ -97,7 +97,7 @@ def test_tile_formatter_layout_and_model_step():
 def test_tiled_dataset_and_pack_collator_feed_the_model(tmp_path):
     import json
     from mindspeed_mm_b200.data.anyres import TiledConversationDataset, TiledPackCollator
-    from mindspeed_mm_b200.data.registry import data_register
+    from mindspeed_mm_b200.models.registry import data_register
     from mindspeed_mm_b200.models.composable import PRESETS, ComposableLM
     assert data_register.get("deepseekvl2") is TiledConversationDataset
     recs = [{"conversations": [{"from": "human", "value": "<image>\nwhat is this?"}, {"from": "gpt", "value": "a chart"}],

@@ -99,10 +99,7 @@ def make_batches(cfg, n_batches, seq_len, samples_per_pack, images_per_sample, i
         seq_len=per, images_per_sample=images_per_sample, image_size=image_size, vocab_size=cfg.text.vocab_size,
         image_token_id=cfg.image_token_id, vision_start_token_id=cfg.vision_start_token_id, seed=1234 + rank,
         pixel_dtype=torch.bfloat16, patch=cfg.vision.patch_size, merge=cfg.vision.spatial_merge_size))
-    col = PackedVLMCollator(cfg.image_token_id, cfg.vision_start_token_id, merge=cfg.vision.spatial_merge_size,
-                            patch=cfg.vision.patch_size, window_size=cfg.vision.window_size,
-                            vit_head_dim=cfg.vision.hidden_size // cfg.vision.num_heads,
-                            pixel_dtype=torch.bfloat16, pin=pin)
+    col = PackedVLMCollator.for_config(cfg, pixel_dtype=torch.bfloat16, pin=pin)
     return [col([ds[b * samples_per_pack + i] for i in range(samples_per_pack)]) for b in range(n_batches)]
 
 
@@ -227,7 +224,7 @@ def run_moe(args):
     from mindspeed_mm_b200 import ops
     from mindspeed_mm_b200.api import init_distributed, stable_init_fn
     from mindspeed_mm_b200.data.collate import batch_nbytes, to_device
-    from mindspeed_mm_b200.models.qwen3_vl_moe import Qwen3VLMoEConfig, Qwen3VLMoEModel
+    from mindspeed_mm_b200.models.qwen3_vl import Qwen3VLConfig, Qwen3VLModel
     from mindspeed_mm_b200.ops import native
     from mindspeed_mm_b200.parallel.fsdp import EngineMux, FSDPEngine, OptimConfig
     from mindspeed_mm_b200.parallel.state import init_parallel_state
@@ -236,13 +233,13 @@ def run_moe(args):
     dev, rank, world = init_distributed(None)
     local = int(os.environ.get("LOCAL_RANK", "0"))
     small = args.model == "tiny"
-    cfg = Qwen3VLMoEConfig.tiny() if small else Qwen3VLMoEConfig.qwen3_vl_30b_a3b()
+    cfg = Qwen3VLConfig.tiny() if small else Qwen3VLConfig.qwen3_vl_30b_a3b()
     if args.layers:
         cfg.text.num_layers = args.layers
     cfg.text.ep_dispatcher = args.dispatcher
     ps = init_parallel_state(world_size=world, device_type=dev.type, expert_parallel_size=world)
     with torch.device("meta"):
-        model = Qwen3VLMoEModel(cfg, ep_size=world)
+        model = Qwen3VLModel(cfg, ep_size=world)
     opt = OptimConfig(lr=1e-5, weight_decay=0.0)
     ex = [p for _, m in model.expert_units() for p in m.parameters()]
     dense = FSDPEngine(model.fsdp_units(), group=ps.get_fsdp_group() if world > 1 else False, device=dev,

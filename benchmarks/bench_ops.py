@@ -1,6 +1,6 @@
 """Per-kernel timing on one GPU: CUDA events, >=3 warm-ups, L2 flushed between timed iterations.
 
-    python benchmarks/bench_ops.py [--ops gemm,gemm_swiglu,elementwise,fmha,gdn] [--out FILE] [--small]
+    python benchmarks/bench_ops.py [--ops gemm,gemm_swiglu,elementwise,lce,fmha,gdn,vit_attention,grouped_gemm,small_ops] [--out FILE] [--small]
 
 Prints one JSON line per case: achieved TFLOP/s or GB/s and the fraction of the measured peaks in
 MEASURED_PEAKS.json (fallback 1590 TFLOP/s / 6650 GB/s when the file is absent).  ``--small`` keeps
@@ -215,6 +215,108 @@ def bench_fmha(out_file, small):
         native.check_status()
 
 
+def bench_vit_attention(out_file, small):
+    """Vision-tower attention of Qwen2.5-VL: 8 images of 448 x 448 = 8192 patches, 16 heads of 80; the window layers
+    (128 windows of 64 tokens) and the full-attention layers (8 sequences of 1024), forward and backward, against
+    flash-attn 2 on the same tensors."""
+    import math
+    from flash_attn import flash_attn_varlen_func
+    tf, hbm, src = peaks()
+    T, N, D = 8192, 16, 80
+    for name, lens in (("vit_windows_128x64", [64] * 128), ("vit_full_8x1024", [1024] * 8)):
+        qkv = torch.randn(T, 3, N, D, device="cuda", dtype=torch.bfloat16)
+        q, k, v = qkv.unbind(1)                                  # strided views of the fused projection, as in the model
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+        sc = 1.0 / math.sqrt(D)
+        flops = sum(4.0 * l * l * D * N for l in lens)
+        bytes_ = 4.0 * T * N * D * 2
+        t = time_fn(lambda: native.fmha_forward(q, k, v, cu, cu, False, sc))
+        tl = time_fn(lambda: flash_attn_varlen_func(q, k, v, cu, cu, max(lens), max(lens), causal=False))
+        out, lse = native.fmha_forward(q, k, v, cu, cu, False, sc)
+        do = torch.randn_like(out)
+        tb = time_fn(lambda: native.fmha_backward(do, q, k, v, out, lse, cu, cu, False, sc), iters=5)
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
+        qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+        dq, dk, dv = torch.empty_like(qc), torch.empty_like(kc), torch.empty_like(vc)
+        tbl = time_fn(lambda: _flash_attn_varlen_backward(do, qc, kc, vc, out, lse, dq, dk, dv, cu, cu, max(lens), max(lens), 0.0,
+                                                          sc, False, -1, -1, 0.0, None, False), iters=5)
+        emit(dict(op="vit_attention", case=name, T=T, heads=N, head_dim=D, fwd_ms=round(t, 4), bwd_ms=round(tb, 4),
+                  fwd_tflops=round(flops / t / 1e9, 1), fwd_gbs=round(bytes_ / t / 1e6, 1),
+                  fwd_frac_of_hbm=round(bytes_ / t / 1e6 / hbm, 3), peak=src, flash_attn2_fwd_ms=round(tl, 4),
+                  flash_attn2_bwd_ms=round(tbl, 4), fwd_vs_flash_attn2=round(tl / t, 3), bwd_vs_flash_attn2=round(tbl / tb, 3)),
+             out_file)
+        native.check_status()
+
+
+def bench_grouped_gemm(out, small):
+    """Grouped expert GEMMs of Qwen3-VL-30B-A3B on one EP rank of 8: 16 local experts, 8192 tokens x top-8 / 8 ranks =
+    8192 routed rows with a skewed histogram; gate_up [2048 -> 1536] and down [768 -> 2048]; forward, data gradient and
+    weight gradient against a loop of cuBLAS matmuls over the same expert slices."""
+    tf, _, src = peaks()
+    E, H, F = 16, 2048, 768
+    rows = 8192 if not small else 2048
+    g = torch.Generator().manual_seed(0)
+    w = torch.softmax(torch.randn(E, generator=g) * 0.8, 0)
+    counts = torch.multinomial(w, rows, replacement=True, generator=g).bincount(minlength=E).tolist()
+    for name, K, N in (("gate_up", H, 2 * F), ("down", F, H)):
+        x = torch.randn(rows, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        wt = (torch.randn(E, K, N, device="cuda") / K ** 0.5).to(torch.bfloat16).requires_grad_()
+        flops = 2.0 * rows * K * N
+
+        def fwd_native():
+            return ops.grouped_gemm(x, wt, counts)
+
+        def fwd_loop():
+            return ops._GroupedGemmLoop.apply(x, wt, counts)
+        t_f = time_fn(lambda: fwd_native())
+        t_fl = time_fn(lambda: fwd_loop())
+        y = fwd_native()
+        gy = torch.randn_like(y)
+
+        def bwd(fn):
+            x.grad = wt.grad = None
+            fn().backward(gy)
+        t_fb = time_fn(lambda: bwd(fwd_native), iters=5)
+        t_fbl = time_fn(lambda: bwd(fwd_loop), iters=5)
+        emit(dict(op="grouped_gemm", case=name, rows=rows, experts=E, K=K, N=N, max_rows=max(counts), min_rows=min(counts),
+                  fwd_ms=round(t_f, 4), fwd_tflops=round(flops / t_f / 1e9, 1), fwd_frac_of_peak=round(flops / t_f / 1e9 / tf, 3),
+                  fwd_bwd_ms=round(t_fb, 4), fwd_bwd_tflops=round(3 * flops / t_fb / 1e9, 1), peak=src,
+                  cublas_loop_fwd_ms=round(t_fl, 4), cublas_loop_fwd_bwd_ms=round(t_fbl, 4),
+                  fwd_vs_cublas_loop=round(t_fl / t_f, 3), fwd_bwd_vs_cublas_loop=round(t_fbl / t_fb, 3)), out)
+        native.check_status()
+
+
+def bench_small_ops(out, small):
+    """Memory-bound kernels without an earlier measurement: depthwise causal conv1d (+SiLU), L2 norm, GELU, affine
+    LayerNorm.  Bytes = one read + one write of the activation (plus the gradient traffic for backward)."""
+    import torch.nn.functional as F
+    _, hbm, src = peaks()
+    T = 65536 if not small else 16384
+
+    def rec(name, fn, nbytes, eager=None, **kw):
+        t = time_fn(fn)
+        r = dict(op=name, ms=round(t, 4), gbs=round(nbytes / t / 1e6, 1), frac_of_hbm=round(nbytes / t / 1e6 / hbm, 3), peak=src, **kw)
+        if eager is not None:
+            te = time_fn(eager)
+            r.update(eager_ms=round(te, 4), vs_eager=round(te / t, 3))
+        emit(r, out)
+    x = torch.randn(T, 4096, device="cuda", dtype=torch.bfloat16)
+    nb = 2.0 * x.numel() * 2
+    rec("gelu_tanh_fwd", lambda: ops.gelu_tanh(x), nb, lambda: F.gelu(x, approximate="tanh"), T=T, H=4096)
+    w = torch.ones(4096, device="cuda", dtype=torch.bfloat16)
+    b = torch.zeros(4096, device="cuda", dtype=torch.bfloat16)
+    rec("layer_norm_affine_fwd", lambda: ops.layer_norm(x, w, b), nb, lambda: F.layer_norm(x, (4096,), w, b), T=T, H=4096)
+    xn = torch.randn(T, 32, 128, device="cuda", dtype=torch.bfloat16)
+    rec("l2_norm_fwd", lambda: ops.l2_norm(xn), 2.0 * xn.numel() * 2, lambda: F.normalize(xn.float(), dim=-1).to(xn.dtype),
+        T=T, heads=32, D=128)
+    xc = torch.randn(T, 8192, device="cuda", dtype=torch.bfloat16)
+    wc = torch.randn(8192, 4, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0, T // 2, T], dtype=torch.int32, device="cuda")
+    rec("causal_conv1d_silu_fwd", lambda: ops.causal_conv1d(xc, wc, None, "silu", cu), 2.0 * xc.numel() * 2,
+        lambda: ref.causal_conv1d(xc, wc, None, "silu", cu), T=T, channels=8192, width=4)
+    native.check_status()
+
+
 def bench_gdn(out, small):
     """Gated delta rule, K = V = 128, chunk 64: the state-pass kernel alone, the whole operator (batched prologue
     + kernel), forward + backward, and the PyTorch chunked oracle on the same GPU."""
@@ -262,7 +364,8 @@ def main():
     ap.add_argument("--small", action="store_true")
     a = ap.parse_args()
     for op in a.ops.split(","):
-        {"gemm": bench_gemm, "gemm_swiglu": bench_gemm_swiglu, "elementwise": bench_elementwise, "lce": bench_lce, "fmha": bench_fmha, "gdn": bench_gdn}[op](a.out, a.small)
+        {"gemm": bench_gemm, "gemm_swiglu": bench_gemm_swiglu, "elementwise": bench_elementwise, "lce": bench_lce, "fmha": bench_fmha, "gdn": bench_gdn,
+         "vit_attention": bench_vit_attention, "grouped_gemm": bench_grouped_gemm, "small_ops": bench_small_ops}[op](a.out, a.small)
 
 
 if __name__ == "__main__":

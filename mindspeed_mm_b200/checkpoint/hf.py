@@ -18,8 +18,8 @@ from typing import Callable, Dict, Iterable, List, Optional, Tuple
 
 import torch
 
-from .operators import (ExpertStack, Merge, Operator, QKVMerge, Rename, RenamePrefix, Reshape, StateDict, apply_ops,
-                        revert_ops)
+from .operators import (ExpertStack, Merge, Operator, QKVMerge, Rename, RenamePrefix, Reshape, StateDict, Transpose,
+                        apply_ops, revert_ops)
 
 INDEX = "model.safetensors.index.json"
 
@@ -98,6 +98,73 @@ def qwen25vl_ops(cfg) -> List[Operator]:
         Rename("lm_head.weight", "lm_head.weight"),
     ]
     return ops
+
+
+def qwen3vl_ops(cfg, experts_out_in: bool = False) -> List[Operator]:
+    """HF Qwen3-VL / Qwen3-VL-MoE -> internal names/layouts (``cfg``: models.qwen3_vl.Qwen3VLConfig).
+
+    Published MoE checkpoints store the fused experts as ``gate_up_proj [E, H, 2F]`` / ``down_proj [E, F, H]``, which is
+    also the internal layout (reference: fsdp/models/qwen3vl/modeling_qwen3_vl_moe.py:125-126).  ``experts_out_in``
+    reads / writes the ``[E, 2F, H]`` / ``[E, H, F]`` form that transformers >= 5 holds in memory instead."""
+    t, v = cfg.text, cfg.vision
+    ops: List[Operator] = [
+        RenamePrefix("model.language_model.", "model."),
+        RenamePrefix("model.visual.", "visual."),
+        Reshape("visual.patch_embed.proj.weight", lambda x: (x.shape[0], -1),
+                lambda x: (x.shape[0], v.in_channels, v.temporal_patch_size, v.patch_size, v.patch_size)),
+        Rename("visual.pos_embed.weight", "visual.patch_embed.pos_embed.weight"),
+    ]
+    for kind in ("weight", "bias"):
+        ops += [
+            Rename("visual.blocks.{i}.attn.qkv." + kind, "visual.blocks.{i}.attn_qkv." + kind),
+            Rename("visual.blocks.{i}.attn.proj." + kind, "visual.blocks.{i}.attn_proj." + kind),
+            Rename("visual.blocks.{i}.mlp.linear_fc1." + kind, "visual.blocks.{i}.mlp_fc1." + kind),
+            Rename("visual.blocks.{i}.mlp.linear_fc2." + kind, "visual.blocks.{i}.mlp_fc2." + kind),
+            Rename("visual.merger.linear_fc1." + kind, "visual.merger.fc1." + kind),
+            Rename("visual.merger.linear_fc2." + kind, "visual.merger.fc2." + kind),
+            Rename("visual.deepstack_merger_list.{i}.norm." + kind, "visual.deepstack_mergers.{i}.norm." + kind),
+            Rename("visual.deepstack_merger_list.{i}.linear_fc1." + kind, "visual.deepstack_mergers.{i}.fc1." + kind),
+            Rename("visual.deepstack_merger_list.{i}.linear_fc2." + kind, "visual.deepstack_mergers.{i}.fc2." + kind),
+        ]
+    ops += [
+        Rename("model.embed_tokens.weight", "embed_tokens.weight"),
+        QKVMerge(["model.layers.{i}.self_attn.q_proj.weight", "model.layers.{i}.self_attn.k_proj.weight",
+                  "model.layers.{i}.self_attn.v_proj.weight"], "layers.{i}.qkv_proj.weight",
+                 t.num_attention_heads, t.num_key_value_heads, t.head_dim),
+        QKVMerge(["model.layers.{i}.self_attn.q_proj.bias", "model.layers.{i}.self_attn.k_proj.bias",
+                  "model.layers.{i}.self_attn.v_proj.bias"], "layers.{i}.qkv_proj.bias",
+                 t.num_attention_heads, t.num_key_value_heads, t.head_dim),
+        Rename("model.layers.{i}.self_attn.o_proj.weight", "layers.{i}.o_proj.weight"),
+        Rename("model.layers.{i}.self_attn.q_norm.weight", "layers.{i}.q_norm.weight"),
+        Rename("model.layers.{i}.self_attn.k_norm.weight", "layers.{i}.k_norm.weight"),
+        Merge(["model.layers.{i}.mlp.gate_proj.weight", "model.layers.{i}.mlp.up_proj.weight"],
+              "layers.{i}.gate_up_proj.weight"),
+        Rename("model.layers.{i}.mlp.down_proj.weight", "layers.{i}.down_proj.weight"),
+        Rename("model.layers.{i}.mlp.gate.weight", "layers.{i}.mlp.gate.weight"),
+        Rename("model.layers.{i}.mlp.experts.gate_up_proj", "layers.{i}.mlp.experts.gate_up_proj"),
+        Rename("model.layers.{i}.mlp.experts.down_proj", "layers.{i}.mlp.experts.down_proj"),
+        Rename("model.layers.{i}.input_layernorm.weight", "layers.{i}.input_layernorm.weight"),
+        Rename("model.layers.{i}.post_attention_layernorm.weight", "layers.{i}.post_attention_layernorm.weight"),
+        Rename("model.norm.weight", "lm_head.norm.weight"),
+        Rename("lm_head.weight", "lm_head.weight"),
+    ]
+    if experts_out_in:
+        ops += [Transpose("layers.{i}.mlp.experts.gate_up_proj"), Transpose("layers.{i}.mlp.experts.down_proj")]
+    if t.tie_word_embeddings:
+        ops.append(_UntieHead())
+    return ops
+
+
+class _UntieHead(Operator):
+    """A tied checkpoint has no ``lm_head.weight``: the internal head gets a copy of the embedding; the way back
+    drops it again."""
+
+    def apply(self, sd):
+        if "lm_head.weight" not in sd and "embed_tokens.weight" in sd:
+            sd["lm_head.weight"] = sd["embed_tokens.weight"].clone()
+
+    def revert(self, sd):
+        sd.pop("lm_head.weight", None)
 
 
 class _ModernPrefix(Operator):

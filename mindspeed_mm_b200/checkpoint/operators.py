@@ -174,6 +174,21 @@ class Reshape(Operator):
         self._do(sd, self.from_shape)
 
 
+class Transpose(Operator):
+    """Swap two dims of every tensor whose name matches (its own inverse)."""
+
+    def __init__(self, name: str, dim0: int = -1, dim1: int = -2):
+        self.name, self.d0, self.d1 = name, dim0, dim1
+
+    def apply(self, sd):
+        rx = _compile(self.name)
+        for k in list(sd.keys()):
+            if rx.match(k):
+                sd[k] = sd[k].transpose(self.d0, self.d1).contiguous()
+
+    revert = apply
+
+
 class Tie(Operator):
     """Target keeps one copy; revert re-creates the tied alias (tied embeddings)."""
 

@@ -54,6 +54,8 @@ def build_dataset(dataset_param, model=None):
             basic.setdefault("vocab_size", cfg.text.vocab_size)
             basic.setdefault("image_token_id", cfg.image_token_id)
             basic.setdefault("vision_start_token_id", cfg.vision_start_token_id)
+            basic.setdefault("patch", cfg.vision.patch_size)
+            basic.setdefault("merge", cfg.vision.spatial_merge_size)
         return cls(SyntheticVLMSpec(**basic))
     if kind == "synthetic_av_latents":
         from .synthetic import SyntheticAVLatentSpec
@@ -79,10 +81,7 @@ def build_collator(args, model, pin: bool):
         return TiledPackCollator(vit.patch_size, vit.merge, vit.temporal_patch_size)
     if "qwen2" in name or "vl" in name or args.data.dataset_param.dataset_type == "synthetic_vlm":
         from .collate import PackedVLMCollator
-        v = cfg.vision
-        return PackedVLMCollator(cfg.image_token_id, cfg.vision_start_token_id, merge=v.spatial_merge_size,
-                                 patch=v.patch_size, window_size=v.window_size,
-                                 vit_head_dim=v.hidden_size // v.num_heads, pin=pin)
+        return PackedVLMCollator.for_config(cfg, pin=pin)
     return lambda samples: {k: torch.stack([s[k] for s in samples]) for k in samples[0]}
 
 

@@ -23,10 +23,25 @@ from ..models.qwen2_5_vl import get_rope_index, vision_rot_pos_ids, vision_windo
 class PackedVLMCollator:
     def __init__(self, image_token_id: int, vision_start_token_id: int, merge: int = 2, patch: int = 14,
                  window_size: int = 112, vit_head_dim: int = 80, ignore_index: int = -100,
-                 pad_to: Optional[int] = None, pixel_dtype: torch.dtype = torch.float32, pin: bool = False):
+                 pad_to: Optional[int] = None, pixel_dtype: torch.dtype = torch.float32, pin: bool = False,
+                 rope_index_fn=None, vision_plan_fn=None):
         self.image_token_id, self.vision_start_token_id = image_token_id, vision_start_token_id
         self.merge, self.patch, self.window_size, self.vit_head_dim = merge, patch, window_size, vit_head_dim
         self.ignore_index, self.pad_to, self.pixel_dtype, self.pin = ignore_index, pad_to, pixel_dtype, pin
+        # model families whose position ids / vision index plan differ from Qwen2.5-VL's hand theirs over
+        self.rope_index_fn = rope_index_fn or (
+            lambda i, g: get_rope_index(i, g, self.image_token_id, self.vision_start_token_id, self.merge))
+        self.vision_plan_fn = vision_plan_fn or (
+            lambda grid: vision_plan(grid, self.merge, self.patch, self.window_size, self.vit_head_dim))
+
+    @classmethod
+    def for_config(cls, cfg, **kw) -> "PackedVLMCollator":
+        """Collator for a VLM config (``image_token_id``, ``vision``): a config that defines ``rope_index`` /
+        ``vision_plan`` (Qwen3-VL) supplies its own position ids and vision plan."""
+        v = cfg.vision
+        return cls(cfg.image_token_id, cfg.vision_start_token_id, merge=v.spatial_merge_size, patch=v.patch_size,
+                   window_size=getattr(v, "window_size", 0), vit_head_dim=v.hidden_size // v.num_heads,
+                   rope_index_fn=getattr(cfg, "rope_index", None), vision_plan_fn=getattr(cfg, "vision_plan", None), **kw)
 
     def __call__(self, samples: List[Dict[str, torch.Tensor]]) -> Dict[str, torch.Tensor]:
         ids, labels, pos, lens, pix, grids = [], [], [], [], [], []
@@ -35,7 +50,7 @@ class PackedVLMCollator:
             l = s["labels"]
             shifted = torch.cat([l[1:], l.new_full((1,), self.ignore_index)])
             g = s.get("image_grid_thw")
-            p, _ = get_rope_index(i, g, self.image_token_id, self.vision_start_token_id, self.merge)
+            p, _ = self.rope_index_fn(i, g)
             ids.append(i); labels.append(shifted); pos.append(p); lens.append(len(i))
             if g is not None and len(g):
                 pix.append(s["pixel_values"]); grids.append(g)
@@ -49,7 +64,7 @@ class PackedVLMCollator:
             out["pixel_values"] = torch.cat(pix).to(self.pixel_dtype)
             out["image_grid_thw"] = grid
             out["image_positions"] = (input_ids == self.image_token_id).nonzero(as_tuple=True)[0]
-            out["vision_plan"] = vision_plan(grid, self.merge, self.patch, self.window_size, self.vit_head_dim)
+            out["vision_plan"] = self.vision_plan_fn(grid)
         if self.pin:
             out = pin_batch(out)
         return out

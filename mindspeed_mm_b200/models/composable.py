@@ -32,7 +32,7 @@ from .. import ops
 from .encoders import WhisperConfig, WhisperEncoder, WhisperLayer
 from .qwen2_5_vl import Embedding, Linear, LMHead, Qwen25VLModel, RMSNorm, TextConfig, VisionConfig, VisionTransformer
 from .qwen3_5 import GatedDeltaNet, GDNTextConfig
-from .qwen3_vl_moe import MoETextConfig, SparseMoeBlock
+from .moe import MoETextConfig, SparseMoeBlock
 from .registry import model_register
 
 

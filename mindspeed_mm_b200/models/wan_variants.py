@@ -80,14 +80,14 @@ class Wan22Block(WanBlock):
     def _ffn(self, h):
         return self.moe(h) if self.moe is not None else self.ffn_2(ops.gelu_tanh(self.ffn_0(h)))
 
-    def forward(self, x, time_emb, ctx, rope_cos, rope_sin, seq_sizes=None, n_img: int = 0):
+    def forward(self, x, time_emb, ctx, rope_cos, rope_sin, seq_sizes=None, n_img: int = 0, rope_full=None):
         if time_emb.dim() == 3 and self.moe is None:
-            return super().forward(x, time_emb, ctx, rope_cos, rope_sin, seq_sizes, n_img)
+            return super().forward(x, time_emb, ctx, rope_cos, rope_sin, seq_sizes, n_img, rope_full)
         if time_emb.dim() == 3:
             time_emb = time_emb[:, None]                                          # [B, 1, 6, H]
         e = (self.modulation.to(time_emb.dtype)[:, None] + time_emb).unbind(2)    # 6 x [B, S or 1, H]
         mod = lambda h, sc, sh: ops.layer_norm(h, None, None, self.eps) * (1 + sc) + sh       # noqa: E731
-        y = self.self_attn(mod(x, e[1], e[0]), (rope_cos, rope_sin), seq_sizes)
+        y = self.self_attn(mod(x, e[1], e[0]), (rope_cos, rope_sin), seq_sizes, rope_full)
         x = x + y * e[2]
         x = x + self.cross_attn(self.norm3(x), ctx, n_img)
         y = self._ffn(mod(x, e[4], e[3]))

@@ -2,7 +2,7 @@
 from . import qwen2_5_vl  # noqa: F401
 from . import wan  # noqa: F401
 from .diffusion import flow_match  # noqa: F401
-from . import qwen3_vl_moe  # noqa: F401
+from . import qwen3_vl  # noqa: F401
 from . import qwen3_5  # noqa: F401
 from . import mmdit  # noqa: F401
 from . import composable  # noqa: F401

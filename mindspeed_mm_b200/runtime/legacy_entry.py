@@ -119,10 +119,9 @@ def datasets_provider(kind: str, args, model, ps, consumed_samples: int = 0):
         ds = real if real is not None else SyntheticVLMDataset(SyntheticVLMSpec(
             seq_len=seq, images_per_sample=int(basic.get("images_per_sample", 1)), image_size=int(basic.get("image_size", 224)),
             vocab_size=cfg.text.vocab_size, image_token_id=cfg.image_token_id,
-            vision_start_token_id=cfg.vision_start_token_id, seed=args.seed, num_samples=int(basic.get("num_samples", 1 << 20))))
-        v = cfg.vision
-        coll = PackedVLMCollator(cfg.image_token_id, cfg.vision_start_token_id, v.spatial_merge_size, v.patch_size,
-                                 v.window_size, v.hidden_size // v.num_heads)
+            vision_start_token_id=cfg.vision_start_token_id, seed=args.seed, num_samples=int(basic.get("num_samples", 1 << 20)),
+            patch=cfg.vision.patch_size, merge=cfg.vision.spatial_merge_size))
+        coll = PackedVLMCollator.for_config(cfg)
     else:
         c = model.predictor.config
         channels = getattr(c, "in_dim", None) or getattr(c, "in_channels")       # Wan names it in_dim, the other DiTs in_channels

@@ -1,6 +1,6 @@
 """Inference pipelines.
 
-* ``VLMGenerator``      - greedy / top-p decoding for the packed Qwen2.5-VL model with a per-layer key / value cache:
+* ``VLMGenerator``      - greedy / top-p decoding for the packed Qwen2.5-VL / Qwen3-VL models with a per-layer key / value cache:
                           the prompt (vision tower included) runs once, every later step feeds one token whose
                           attention reads the cached keys and values (``use_cache=False`` re-runs the whole prefix
                           per token instead, the exact but quadratic form).
@@ -22,9 +22,7 @@ from ..models.diffusion import FlowMatchScheduler
 class VLMGenerator:
     def __init__(self, model, run: Optional[Callable] = None, eos_token_id: Optional[int] = None):
         self.model, self.run, self.eos = model, run, eos_token_id
-        c, v = model.config, model.config.vision
-        self.collator = PackedVLMCollator(c.image_token_id, c.vision_start_token_id, v.spatial_merge_size, v.patch_size,
-                                          v.window_size, v.hidden_size // v.num_heads)
+        self.collator = PackedVLMCollator.for_config(model.config)
 
     @torch.no_grad()
     def next_logits(self, input_ids, pixel_values=None, image_grid_thw=None, device="cpu"):

@@ -13,7 +13,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from bench import make_batches  # noqa: E402
 from mindspeed_mm_b200.api import stable_init_fn  # noqa: E402
 from mindspeed_mm_b200.checkpoint.sharded import DistributedCheckpointer  # noqa: E402
-from mindspeed_mm_b200.models.qwen3_vl_moe import Qwen3VLMoEConfig, Qwen3VLMoEModel  # noqa: E402
+from mindspeed_mm_b200.models.qwen3_vl import Qwen3VLConfig, Qwen3VLModel  # noqa: E402
 from mindspeed_mm_b200.parallel.fsdp import EngineMux, FSDPEngine, OptimConfig  # noqa: E402
 from mindspeed_mm_b200.parallel.state import init_parallel_state, reset_parallel_state  # noqa: E402
 
@@ -22,7 +22,7 @@ def build(cfg, world, ep, group, dispatcher, clip=0.0):
     cfg.text.ep_dispatcher = dispatcher
     ps = init_parallel_state(world_size=world, device_type="cpu", expert_parallel_size=ep)
     with torch.device("meta"):
-        model = Qwen3VLMoEModel(cfg, ep_size=ep)
+        model = Qwen3VLModel(cfg, ep_size=ep)
     opt = OptimConfig(lr=1e-3, clip_grad=clip)
     ex = [p for _, m in model.expert_units() for p in m.parameters()]
     dense = FSDPEngine(model.fsdp_units(), group=group, device="cpu", param_dtype=torch.float32, opt=opt, exclude_params=ex)
@@ -101,7 +101,7 @@ def clip_and_checkpoint_check(cfg, packs, full, rank, world):
 def main():
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
-    cfg = Qwen3VLMoEConfig.tiny()
+    cfg = Qwen3VLConfig.tiny()
     packs = [make_batches(cfg, 2, 384, 1, 1, 224, r, pin=False) for r in range(world)]
     ok = True
     # single-process twin with all experts (built first; its weights seed the EP runs)

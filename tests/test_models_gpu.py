@@ -17,10 +17,9 @@ def _vlm_batch(cfg, seq=512, img=224):
     from mindspeed_mm_b200.data.synthetic import SyntheticVLMDataset, SyntheticVLMSpec
     ds = SyntheticVLMDataset(SyntheticVLMSpec(seq_len=seq, images_per_sample=1, image_size=img, vocab_size=cfg.text.vocab_size,
                                               image_token_id=cfg.image_token_id, vision_start_token_id=cfg.vision_start_token_id,
-                                              pixel_dtype=torch.bfloat16))
-    v = cfg.vision
-    coll = PackedVLMCollator(cfg.image_token_id, cfg.vision_start_token_id, merge=v.spatial_merge_size, patch=v.patch_size,
-                             window_size=v.window_size, vit_head_dim=v.hidden_size // v.num_heads, pixel_dtype=torch.bfloat16)
+                                              pixel_dtype=torch.bfloat16, patch=cfg.vision.patch_size,
+                                              merge=cfg.vision.spatial_merge_size))
+    coll = PackedVLMCollator.for_config(cfg, pixel_dtype=torch.bfloat16)
     return to_device(coll([ds[0], ds[1]]), torch.device(DEV))
 
 
@@ -67,10 +66,10 @@ def test_qwen3_5_gdn_hybrid_with_native_state_pass():
 
 
 def test_qwen3_vl_moe_native_experts():
-    from mindspeed_mm_b200.models.qwen3_vl_moe import Qwen3VLMoEConfig, Qwen3VLMoEModel
-    cfg = Qwen3VLMoEConfig.tiny()
+    from mindspeed_mm_b200.models.qwen3_vl import Qwen3VLConfig, Qwen3VLModel
+    cfg = Qwen3VLConfig.tiny()
     with torch.device("meta"):
-        model = Qwen3VLMoEModel(cfg, ep_size=1)
+        model = Qwen3VLModel(cfg, ep_size=1)
     ex = [p for _, m in model.expert_units() for p in m.parameters()]
     opt = OptimConfig(lr=1e-3)
     dense = FSDPEngine(model.fsdp_units(), group=False, device=DEV, param_dtype=torch.bfloat16, opt=opt, exclude_params=ex)

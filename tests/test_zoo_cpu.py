@@ -11,7 +11,7 @@ from mindspeed_mm_b200.parallel.fsdp import FSDPEngine, OptimConfig
 
 def test_registry_lists_builtin_models():
     registry._ensure_builtin()
-    for name in ("qwen2_5vl", "qwen3_vl_moe", "qwen3_5", "wandit", "hunyuanvideodit", "flux", "wan_flow_match_scheduler"):
+    for name in ("qwen2_5vl", "qwen3_vl", "qwen3_vl_moe", "qwen3_5", "wandit", "hunyuanvideodit", "flux", "wan_flow_match_scheduler"):
         assert name in registry.model_register
 
 

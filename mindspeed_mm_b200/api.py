@@ -83,6 +83,8 @@ class VLMTrainerSpec:
     log_interval: int = 1
     shard_size: Optional[int] = None     # < number of data ranks: hybrid sharding (shard inside, replicate across)
     offload_optimizer: bool = False      # fp32 master weights + Adam moments in pinned host memory
+    optimizer: str = "adamw"             # "muon": Newton-Schulz orthogonalised momentum for the 2-D hidden matrices
+    lr_scaling: tuple = ()               # ((regex, multiplier), ...) on parameter names
     reshard_after_forward: bool = True
 
 
@@ -95,7 +97,8 @@ def build_vlm_trainer(spec: VLMTrainerSpec, device=None, data_iter=None, checkpo
     if spec.freeze_vision:
         for p in model.visual.parameters():
             p.requires_grad_(False)
-    opt = OptimConfig(lr=spec.lr, weight_decay=spec.weight_decay, clip_grad=spec.clip_grad)
+    opt = OptimConfig(lr=spec.lr, weight_decay=spec.weight_decay, clip_grad=spec.clip_grad, kind=spec.optimizer,
+                      lr_scaling=tuple(spec.lr_scaling))
     engine = FSDPEngine(model.fsdp_units(), group=ps.get_fsdp_group() if world > 1 else False, device=dev,
                         param_dtype=spec.param_dtype, reduce_dtype=spec.reduce_dtype, opt=opt,
                         recompute=spec.recompute is not False, grad_accum_steps=spec.gradient_accumulation_steps,

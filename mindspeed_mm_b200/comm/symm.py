@@ -159,7 +159,7 @@ class P2PCollectives:
             split = min(max(g.decay_end - g.rank * g.shard_numel, 0), g.shard_numel)
             rc = L.mm_p2p_rs_adamw(self.slot_ptrs[s], self.flag_ptrs, g.shard_numel, g.world, g.rank, s, seq, inv,
                                    g.master.data_ptr(), g.exp_avg.data_ptr(), g.exp_avg_sq.data_ptr(),
-                                   g.shard16.data_ptr(), split, engine.lr, o.betas[0], o.betas[1], o.eps,
+                                   g.shard16.data_ptr(), split, engine.lr * g.lr_scale, o.betas[0], o.betas[1], o.eps,
                                    o.weight_decay, 1.0 - o.betas[0] ** g.step_count, 1.0 - o.betas[1] ** g.step_count,
                                    st, self.rs_ctas, native._st())
             native._check(rc, "p2p_rs_adamw")

@@ -54,19 +54,46 @@ class OptimConfig:
     clip_grad: float = 0.0
     # parameter-name predicates: no weight decay for 1-D tensors and biases by default
     no_decay: Callable[[str, torch.Tensor], bool] = staticmethod(lambda n, p: p.dim() < 2 or n.endswith(".bias"))
+    # "muon": 2-D hidden matrices take momentum + Newton-Schulz orthogonalisation, everything else AdamW
+    # (fsdp/optimizer/optimizer.py:158-197 of the reference picks the same split)
+    kind: str = "adamw"
+    muon_momentum: float = 0.95
+    ns_steps: int = 5
+    matched_adamw_rms: float = 0.2
+    muon_eligible: Callable[[str, torch.Tensor], bool] = staticmethod(
+        lambda n, p: p.dim() == 2 and not n.endswith(".bias") and "embed" not in n and "lm_head" not in n
+        and "output_layer" not in n)
+    # per-parameter learning-rate multipliers: the first (regex, scale) whose regex matches the start of the parameter
+    # name wins (``lr_scaling_plan`` of the reference, fsdp/optimizer/optimizer.py:310-331); recipes written against
+    # Hugging Face module trees say ``model.visual...``, so the name is tried with that prefix too
+    lr_scaling: Sequence[Tuple[str, float]] = ()
+
+    def lr_scale_of(self, name: str) -> float:
+        import re
+        for pat, scale in self.lr_scaling:
+            if re.match(pat, name) or re.match(pat, "model." + name):
+                return float(scale)
+        return 1.0
 
 
 class FlatGroup:
     """One flat bf16 buffer + its sharded optimizer state."""
 
     def __init__(self, named_params: List[Tuple[str, nn.Parameter]], rank: int, world: int, device,
-                 param_dtype: torch.dtype, trainable: bool, opt: OptimConfig):
+                 param_dtype: torch.dtype, trainable: bool, opt: OptimConfig, lr_scale: float = 1.0):
         self.rank, self.world, self.device = rank, world, device
         self.dtype = param_dtype
         self.trainable = trainable
-        # decayed parameters first so that weight decay is one split point in the flat index space
+        self.lr_scale = lr_scale
+        # decayed parameters first so that weight decay is one split point in the flat index space; with Muon the
+        # orthogonalised matrices come first of all, so that they are one prefix [0, muon_end) as well
         decay = [(n, p) for n, p in named_params if not (trainable and opt.no_decay(n, p))]
         nodecay = [(n, p) for n, p in named_params if (trainable and opt.no_decay(n, p))]
+        n_muon = 0
+        if trainable and opt.kind == "muon":
+            mu = [(n, p) for n, p in decay if opt.muon_eligible(n, p)]
+            decay = mu + [(n, p) for n, p in decay if not opt.muon_eligible(n, p)]
+            n_muon = len(mu)
         self.named_params = decay + nodecay
         self.shapes: List[torch.Size] = [p.shape for _, p in self.named_params]
         self.numels: List[int] = [p.numel() for _, p in self.named_params]
@@ -79,6 +106,8 @@ class FlatGroup:
             off = _round_up(off + p.numel(), ALIGN)
         if not nodecay:
             self.decay_end = off
+        self.n_muon = n_muon
+        self.muon_end = self.offsets[n_muon] if n_muon < len(self.offsets) else off
         self.numel = off
         self.padded = _round_up(max(off, 1), world * ALIGN)
         self.shard_numel = self.padded // world
@@ -175,8 +204,13 @@ class Unit:
                  if id(p) not in engine.exclude_params]
         train = [(n, p) for n, p in named if p.requires_grad]
         frozen = [(n, p) for n, p in named if not p.requires_grad]
-        mk = lambda ps, tr: FlatGroup(ps, engine.rank, engine.world, engine.device, engine.param_dtype, tr, engine.opt)
-        self.groups: List[FlatGroup] = ([mk(train, True)] if train else []) + ([mk(frozen, False)] if frozen else [])
+        mk = lambda ps, tr, sc=1.0: FlatGroup(ps, engine.rank, engine.world, engine.device, engine.param_dtype, tr,
+                                              engine.opt, sc)
+        by_scale: Dict[float, list] = {}
+        for n, p in train:                  # one flat group per learning-rate multiplier (usually just one)
+            by_scale.setdefault(engine.opt.lr_scale_of(n), []).append((n, p))
+        self.groups: List[FlatGroup] = [mk(ps, True, sc) for sc, ps in by_scale.items()] + \
+            ([mk(frozen, False)] if frozen else [])
         # shapes are recorded by the groups above; now swap in re-bindable placeholders
         mapping = _to_flat_params(module, engine.device, engine.param_dtype, engine.exclude_params)
         for g in self.groups:
@@ -235,7 +269,8 @@ class FSDPEngine:
         self.micro_step = 0
         self.lr = self.opt.lr
         # replicas and host-resident optimizer state both need the reduced gradient shard before the update runs
-        self.deferred = self.opt.clip_grad > 0 or grad_accum_steps > 1 or self.replicas > 1 or offload_optimizer
+        self.deferred = self.opt.clip_grad > 0 or grad_accum_steps > 1 or self.replicas > 1 or offload_optimizer or \
+            self.opt.kind == "muon"
         self._sq_norm = torch.zeros((), dtype=torch.float32, device=self.device)
         self._dummy = torch.zeros((), device=self.device, requires_grad=True)
         self.comm = comm
@@ -468,23 +503,74 @@ class FSDPEngine:
         dist.reduce_scatter_tensor(out, src, group=self.group)
         return out
 
-    def _adamw(self, g: FlatGroup, grad: torch.Tensor, grad_scale) -> None:
-        g.step_count += 1
+    def _adamw(self, g: FlatGroup, grad: torch.Tensor, grad_scale, start: int = 0) -> None:
+        """AdamW on this rank's shard of ``g`` from element ``start`` on (Muon owns the elements before it)."""
+        if start == 0:
+            g.step_count += 1
+            if self.opt.kind == "muon" and g.muon_end > 0:
+                return self._muon(g, grad, grad_scale)
         o = self.opt
+        lr = self.lr * g.lr_scale
         lo = g.rank * g.shard_numel
-        split = min(max(g.decay_end - lo, 0), g.shard_numel)
+        split = min(max(g.decay_end - lo, start), g.shard_numel)
+        if start >= g.shard_numel:
+            return
         if self.cuda and ops.get_tier() == "native":
             from ..ops import native
-            native.adamw_shard(g.master, g.exp_avg, g.exp_avg_sq, grad, g.shard16, self.lr, o.betas[0], o.betas[1],
-                               o.eps, o.weight_decay, g.step_count, split, grad_scale)
+            native.adamw_shard(g.master[start:], g.exp_avg[start:], g.exp_avg_sq[start:], grad[start:], g.shard16[start:],
+                               lr, o.betas[0], o.betas[1], o.eps, o.weight_decay, g.step_count, split - start, grad_scale)
             return
         if isinstance(grad_scale, torch.Tensor):
             grad = grad.float() * grad_scale
             grad_scale = 1.0
-        for a, b, wd in ((0, split, o.weight_decay), (split, g.shard_numel, 0.0)):
+        for a, b, wd in ((start, split, o.weight_decay), (split, g.shard_numel, 0.0)):
             if b > a:
-                ops.ref.adamw_step(g.master[a:b], g.exp_avg[a:b], g.exp_avg_sq[a:b], grad[a:b], self.lr, o.betas[0],
+                ops.ref.adamw_step(g.master[a:b], g.exp_avg[a:b], g.exp_avg_sq[a:b], grad[a:b], lr, o.betas[0],
                                    o.betas[1], o.eps, wd, g.step_count, grad_scale, g.shard16[a:b])
+
+    def _muon(self, g: FlatGroup, grad: torch.Tensor, grad_scale) -> None:
+        """Muon on the matrices of ``g`` ([0, muon_end) of the flat index space), AdamW on the rest.
+
+        The momentum lives in ``exp_avg`` of the owned slice.  Newton-Schulz needs whole matrices: the ranks all-gather
+        the Nesterov-blended update, each orthogonalises the matrices it is assigned (round-robin), and a reduce-scatter
+        of the (disjointly filled) result hands every rank its slice back - two collectives of the group's size per
+        step, no redundant matrix work."""
+        from ..runtime.optim_extra import newton_schulz
+        o = self.opt
+        lr = self.lr * g.lr_scale
+        lo = g.rank * g.shard_numel
+        b = min(max(g.muon_end - lo, 0), g.shard_numel)                     # my elements [0, b) belong to Muon matrices
+        gs = grad.float() * grad_scale if (isinstance(grad_scale, torch.Tensor) or grad_scale != 1.0) else grad.float()
+        upd = torch.zeros(g.shard_numel, dtype=torch.float32, device=self.device)
+        if b:
+            mom = g.exp_avg[:b]
+            mom.mul_(o.muon_momentum).add_(gs[:b])
+            upd[:b] = gs[:b] + o.muon_momentum * mom                      # Nesterov
+        if self.world > 1:
+            full = torch.empty(g.padded, dtype=torch.float32, device=self.device)
+            dist.all_gather_into_tensor(full, upd, group=self.group)
+        else:
+            full = upd
+        out = torch.zeros_like(full)
+        for i in range(g.n_muon):
+            if i % self.world != self.rank:
+                continue
+            off, shape = g.offsets[i], g.shapes[i]
+            m = newton_schulz(full[off:off + g.numels[i]].view(shape), o.ns_steps)
+            out[off:off + g.numels[i]] = (m * (o.matched_adamw_rms * max(shape) ** 0.5)).reshape(-1)
+        if self.world > 1:
+            mine = torch.empty(g.shard_numel, dtype=torch.float32, device=self.device)
+            if self.cuda:
+                dist.reduce_scatter_tensor(mine, out, group=self.group)
+            else:                                                            # gloo has no reduce_scatter
+                dist.all_reduce(out, group=self.group)
+                mine.copy_(g.local_slice(out))
+        else:
+            mine = out
+        if b:
+            g.master[:b].mul_(1.0 - lr * o.weight_decay).add_(mine[:b], alpha=-lr)
+            g.shard16[:b].copy_(g.master[:b])
+        self._adamw(g, grad, grad_scale, start=b)
 
     def _adamw_offloaded(self, g: FlatGroup, grad: torch.Tensor, grad_scale) -> None:
         """Optimizer state on the host: bring master / moments of this group to the device, update, send them back."""

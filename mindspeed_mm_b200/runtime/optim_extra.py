@@ -7,7 +7,9 @@
 * ``AdamWSwap`` - AdamW whose moments live in pinned host memory and visit the GPU one parameter at a time,
   bounded by a byte budget (mindspeed_mm/fsdp/optimizer/swap_optimizer.py:8-257).
 Both are ``torch.optim.Optimizer`` subclasses for modules trained outside the sharding engine (LoRA adapters,
-reward heads, AE training); the engine's own update stays the fused kernel.
+reward heads, AE training).  Inside the sharding engine ``training.optimizer: muon`` runs the same update on the flat
+shards (``parallel/fsdp.py: FSDPEngine._muon``, which calls ``newton_schulz`` here) and ``adamw_swap`` keeps the
+engine's optimizer state on the host (``offload_optimizer``).
 """
 from __future__ import annotations
 
@@ -19,7 +21,7 @@ import torch
 def newton_schulz(g: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.Tensor:
     """Approximate the orthogonal polar factor of a 2-D matrix."""
     a, b, c = 3.4445, -4.7750, 2.0315
-    x = g.float()
+    x = g.bfloat16() if g.is_cuda else g.float()         # bf16 tensor-core GEMMs on the GPU, as Muon is usually run
     transposed = x.shape[0] > x.shape[1]
     if transposed:
         x = x.t()

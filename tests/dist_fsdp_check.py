@@ -39,6 +39,8 @@ def main():
     ap.add_argument("--shard-size", type=int, default=0, help="hybrid sharding: ranks per shard group (replicas = world / it)")
     ap.add_argument("--offload", action="store_true", help="optimizer state in host memory")
     ap.add_argument("--keep-gathered", action="store_true", help="reshard_after_forward = False")
+    ap.add_argument("--optimizer", default="adamw", help="adamw | muon")
+    ap.add_argument("--lr-scaling", action="store_true", help="vision tower at 0.1 x the learning rate")
     ap.add_argument("--recompute-layers", type=int, default=-1,
                     help=">= 0: recompute only that many decoder layers, keep the graph of the rest")
     a = ap.parse_args()
@@ -49,7 +51,8 @@ def main():
                           clip_grad=a.clip, comm=a.comm, log_interval=0, weight_decay=0.01,
                           recompute=True if a.recompute_layers < 0 else a.recompute_layers,
                           shard_size=a.shard_size or None, offload_optimizer=a.offload,
-                          reshard_after_forward=not a.keep_gathered)
+                          reshard_after_forward=not a.keep_gathered, optimizer=a.optimizer,
+                          lr_scaling=((r"visual\.", 0.1),) if a.lr_scaling else ())
     tr = build_vlm_trainer(spec, device=a.device)
     rank, world = dist.get_rank(), dist.get_world_size()
     packs = [make_batches(cfg, a.steps, 512, 1, 1, 224, r, pin=False) for r in range(world)]
@@ -69,7 +72,9 @@ def main():
         with torch.device("meta"):
             model = Qwen25VLModel(cfg)
         eng = FSDPEngine(model.fsdp_units(), group=False, device=dev, param_dtype=dtype,
-                         opt=OptimConfig(lr=1e-3, weight_decay=0.01, clip_grad=a.clip), grad_accum_steps=world)
+                         opt=OptimConfig(lr=1e-3, weight_decay=0.01, clip_grad=a.clip, kind=a.optimizer,
+                                         lr_scaling=((r"visual\.", 0.1),) if a.lr_scaling else ()),
+                         grad_accum_steps=world)
         eng.materialize(stable_init_fn(cfg.init_std, 0))
         ref_losses = []
         for s in range(a.steps):

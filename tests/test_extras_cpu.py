@@ -111,3 +111,61 @@ def test_memory_estimate_breakdown():
                                      layer_input_bytes=8192 * 3584 * 2, largest_unit_params=5.4e8, workspace_gb=0, reserve_gb=0)
     assert abs(eight["static_gb"] * 8 - one["static_gb"]) < 1e-6 and eight["gathered_units_gb"] > 0
     assert eight["activation_gb"] < one["activation_gb"] / 10 and eight["total_gb"] < 40
+
+
+def test_engine_muon_matches_the_standalone_optimizer():
+    """``OptimConfig(kind="muon")`` inside the sharding engine takes the same steps as ``Muon`` on plain parameters:
+    orthogonalised momentum for the 2-D matrix, AdamW for the bias and the norm weight."""
+    from mindspeed_mm_b200.parallel.fsdp import FSDPEngine, OptimConfig
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc = torch.nn.Linear(16, 24)
+            self.norm = torch.nn.LayerNorm(24)
+
+        def forward(self, x):
+            return self.norm(self.fc(x))
+
+    torch.manual_seed(0)
+    ref = Net()
+    with torch.device("meta"):
+        net = Net()
+    eng = FSDPEngine([("", net)], group=False, device="cpu", param_dtype=torch.float32, no_recompute=(),
+                     opt=OptimConfig(lr=0.01, weight_decay=0.1, kind="muon"))
+    src = dict(ref.named_parameters())
+    eng.materialize(lambda name, mod: [p.data.copy_(src[n]) for n, p in mod.named_parameters()])
+    named = list(ref.named_parameters())
+    groups = [dict(params=[p for n, p in named if p.dim() == 2], use_muon=True, weight_decay=0.1),
+              dict(params=[p for n, p in named if p.dim() != 2], use_muon=False, weight_decay=0.0)]
+    opt = Muon(groups, lr=0.01)
+    x = torch.randn(8, 16)
+    for _ in range(3):
+        opt.zero_grad()
+        ref(x).pow(2).mean().backward()
+        opt.step()
+        eng.set_lr(0.01)
+        eng.run(net, x).pow(2).mean().backward()
+        eng.end_micro_step()
+        eng.finish_step()
+    got = dict(eng.named_full_params())
+    for n, p in ref.named_parameters():
+        assert torch.allclose(got[n], p, atol=2e-5), (n, float((got[n] - p).abs().max()))   # steps are ~1e-2
+
+
+def test_lr_scaling_groups_split_a_unit():
+    from mindspeed_mm_b200.parallel.fsdp import FSDPEngine, OptimConfig
+    with torch.device("meta"):
+        net = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.Linear(4, 4))
+    eng = FSDPEngine([("net", net)], group=False, device="cpu", param_dtype=torch.float32, no_recompute=(),
+                     opt=OptimConfig(lr=0.1, lr_scaling=((r"net\.0\.", 0.0),)))
+    eng.materialize(lambda name, mod: [torch.nn.init.normal_(p, std=0.5) for p in mod.parameters()])
+    before = {n: t.clone() for n, t in eng.named_full_params()}
+    eng.set_lr(0.1)
+    eng.run(net, torch.randn(3, 4)).pow(2).mean().backward()
+    eng.end_micro_step()
+    eng.finish_step()
+    after = dict(eng.named_full_params())
+    assert sorted(g.lr_scale for g in eng.units[0].groups) == [0.0, 1.0]
+    assert torch.equal(after["net.0.weight"], before["net.0.weight"])            # multiplier 0: frozen in place
+    assert not torch.equal(after["net.1.weight"], before["net.1.weight"])

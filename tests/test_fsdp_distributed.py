@@ -130,6 +130,13 @@ def test_moe_peer_memory_dispatcher_matches_alltoall():
     assert "ok=True" in _run_script(2, "dist_moe_p2p_check.py")
 
 
+@pytest.mark.parametrize("extra", [("--optimizer", "muon"), ("--optimizer", "muon", "--offload"), ("--lr-scaling",)])
+def test_engine_optimizers_sharded_match_single_process_gloo(extra):
+    """Muon (all-gathered update, round-robin Newton-Schulz, reduce-scattered result) and per-group learning-rate
+    multipliers give the same parameters on two ranks as on one."""
+    assert "ok=True" in _run_script(2, "dist_fsdp_check.py", *extra)
+
+
 def test_native_trainer_moe_recipe_with_expert_parallel_gloo():
     """examples/qwen3vl/tiny_moe_native.yaml end to end: dense engine + expert engine (EngineMux), EP = 2."""
     root = os.path.dirname(HERE)

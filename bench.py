@@ -249,7 +249,7 @@ def run_moe(args):
     mux = EngineMux(dense, expert, ep_group=ps.group("ep") if world > 1 else None)
     mux.materialize(stable_init_fn(0.02, 0))
     seq = args.seq_len if not small else 512
-    host = make_batches(cfg, 2, seq, 4 if not small else 1, 2 if not small else 1, 448 if not small else 224, rank, pin=True)
+    host = make_batches(cfg, 2, seq, 4 if not small else 1, 2 if not small else 1, 512 if not small else 224, rank, pin=True)
     on_dev = [to_device(b, dev) for b in host]
     tokens_per_step = host[0]["n_tokens"] * world
 

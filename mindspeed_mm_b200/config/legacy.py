@@ -91,7 +91,7 @@ _INT = ["tensor-model-parallel-size", "pipeline-model-parallel-size", "context-p
         "num-layers", "hidden-size", "num-attention-heads", "max-position-embeddings", "lr-warmup-iters",
         "exit-interval", "ulysses-degree-in-cp", "virtual-pipeline-model-parallel-size", "recompute-num-layers",
         "make-vocab-size-divisible-by", "distributed-timeout-minutes", "num-layers-per-virtual-pipeline-stage"]
-_FLOAT = ["lr", "min-lr", "weight-decay", "clip-grad", "adam-beta1", "adam-beta2", "adam-eps", "lr-warmup-fraction",
+_FLOAT = ["ema-decay", "lr", "min-lr", "weight-decay", "clip-grad", "adam-beta1", "adam-beta2", "adam-eps", "lr-warmup-fraction",
           "init-method-std", "exit-duration-in-mins", "attention-dropout", "hidden-dropout"]
 _STR = ["lr-decay-style", "tokenizer-type", "load", "save", "ckpt-format", "distributed-backend", "mm-data",
         "mm-model", "mm-tool", "context-parallel-algo", "fsdp2-config-path", "normalization", "recompute-granularity",
@@ -103,7 +103,8 @@ _BOOL = ["bf16", "fp16", "use-mcore-models", "use-flash-attn", "use-distributed-
          "untie-embeddings-and-output-weights", "no-gradient-accumulation-fusion", "use-cpu-initialization",
          "init-model-with-meta-device", "no-initialization", "overlap-grad-reduce", "overlap-param-gather",
          "calculate-per-token-loss", "calculate-per-sample-loss", "layerzero", "use-deter-comp", "no-masked-softmax-fusion",
-         "disable-bias-linear", "group-query-attention", "recompute-skip-core-attention", "use-ema", "no-bias-swiglu-fusion"]
+         "disable-bias-linear", "group-query-attention", "recompute-skip-core-attention", "use-ema", "no-bias-swiglu-fusion",
+         "encoder-dp-balance", "use-data-balance", "hetero-parallel"]
 
 
 def build_parser() -> argparse.ArgumentParser:

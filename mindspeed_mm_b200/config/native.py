@@ -230,6 +230,8 @@ class TrainingArguments(_Base):
     muon_momentum: float = 0.95
     ns_steps: int = 5
     adam_fused: bool = True
+    use_ema: bool = False               # moving average of the master weights (saved with the checkpoint; exported last)
+    ema_decay: float = 0.9999
     adam_beta1: float = 0.9
     adam_beta2: float = 0.999
     adam_eps: float = 1e-8

@@ -41,6 +41,9 @@ class FusedExperts(nn.Module):
         n = num_local if num_local is not None else c.num_experts
         self.gate_up_proj = nn.Parameter(torch.empty(n, c.hidden_size, 2 * c.moe_intermediate_size))
         self.down_proj = nn.Parameter(torch.empty(n, c.moe_intermediate_size, c.hidden_size))
+        # > 0 (``features.enable_ep_balance``): duplicate up to that many hot experts per rank for each call
+        self.ep_balance_max_dup = 0
+        self.last_balance_plan = None
 
     def forward(self, tokens, topk_ids, probs):
         ps = get_parallel_state()
@@ -50,6 +53,11 @@ class FusedExperts(nn.Module):
                 kind = "alltoall"                      # the peer-memory dispatcher is GPU / bf16 only
             fn = {"allgather": epmod.ep_forward_allgather, "p2p": epmod.ep_forward_p2p,
                   "mc2": epmod.ep_forward_p2p}.get(kind, epmod.ep_forward_alltoall)
+            if self.ep_balance_max_dup > 0 and kind in ("alltoall", "allgather"):
+                from ..parallel.ep_balance import balanced_forward
+                out, self.last_balance_plan = balanced_forward(fn, tokens, topk_ids, probs, self.gate_up_proj, self.down_proj,
+                                                               self.c.num_experts, ps.get_ep_group(), self.ep_balance_max_dup)
+                return out
             return fn(tokens, topk_ids, probs, self.gate_up_proj, self.down_proj, self.c.num_experts, ps.get_ep_group())
         return ops.moe_experts(tokens, topk_ids, probs, self.gate_up_proj, self.down_proj)
 

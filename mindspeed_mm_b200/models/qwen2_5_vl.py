@@ -433,6 +433,9 @@ class Qwen25VLModel(nn.Module):
         self.embed_tokens = Embedding(t.vocab_size, t.hidden_size)
         self.layers = nn.ModuleList([DecoderLayer(t) for _ in range(t.num_layers)])
         self.lm_head = LMHead(t)
+        # parallel.data_balance.EncoderBalance over the data-parallel group (``--encoder-dp-balance``): images are
+        # re-dealt across ranks before the vision tower and their embeddings sent back after it
+        self.encoder_balance = None
 
     # -- init ------------------------------------------------------------------------------
     @torch.no_grad()
@@ -470,13 +473,22 @@ class Qwen25VLModel(nn.Module):
         pv = batch.get("pixel_values")
         if pv is not None and pv.numel() > 0:
             vis = self.visual
-            plan = batch.get("vision_plan") or vis.plan(batch["image_grid_thw"], pv.device)
+            book = None
+            if self.encoder_balance is not None:
+                grid = batch["image_grid_thw"]
+                pv, book = self.encoder_balance.dispatch(pv, grid.prod(-1).tolist(), grid.tolist())
+            if book is not None:
+                plan = vis.plan(book["grids"], pv.device)
+            else:
+                plan = batch.get("vision_plan") or vis.plan(batch["image_grid_thw"], pv.device)
             v = run(vis.patch_embed, pv.to(x.dtype)).index_select(0, plan["perm"])
             for i in range(len(vis.blocks)):
                 full = i in vis.cfg.fullatt_block_indexes
                 cu, mx = (plan["cu_full"], plan["max_full"]) if full else (plan["cu_win"], plan["max_win"])
                 v = run(vis.blocks[i], v, plan["cos"].to(x.dtype), plan["sin"].to(x.dtype), cu, mx)
             v = run(vis.merger, v).index_select(0, plan["reverse"])
+            if book is not None:
+                v = self.encoder_balance.combine(v, book, ratio=vis.cfg.spatial_merge_size ** 2)
             img_pos = batch.get("image_positions")
             if img_pos is None:
                 img_pos = (ids == self.config.image_token_id).nonzero(as_tuple=True)[0]

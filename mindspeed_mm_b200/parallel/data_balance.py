@@ -44,18 +44,25 @@ class EncoderBalance:
         self.group = group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
 
-    def plan(self, my_counts: List[int]):
+    def plan(self, my_counts: List[int], my_grids=None):
         allc: List[List[int]] = [None] * self.world
         dist.all_gather_object(allc, list(my_counts), group=self.group)
+        if my_grids is not None:                       # (t, h, w) of every image, so that receivers can index theirs
+            self.all_grids = [None] * self.world
+            dist.all_gather_object(self.all_grids, [list(map(int, g)) for g in my_grids], group=self.group)
         assign = balance_images(allc)
+        self.assign = assign
         # rows I send to each destination, in (dst, my image index) order; rows I receive from each source
         send = [[i for (s, i) in assign[d] if s == self.rank] for d in range(self.world)]
         recv = [[allc[s][i] for (s2, i) in assign[self.rank] if s2 == s] for s in range(self.world)]
         return allc, send, recv
 
-    def dispatch(self, patches: torch.Tensor, my_counts: List[int]):
-        """patches: [sum(my_counts), C] -> balanced patches on this rank + the bookkeeping to undo it."""
-        allc, send, recv = self.plan(my_counts)
+    def dispatch(self, patches: torch.Tensor, my_counts: List[int], my_grids=None):
+        """patches: [sum(my_counts), C] -> balanced patches on this rank + the bookkeeping to undo it.  With
+        ``my_grids`` the bookkeeping also lists the (t, h, w) of the images this rank now holds, in arrival order."""
+        allc, send, recv = self.plan(my_counts, my_grids)
+        if any(len(a) == 0 for a in self.assign):      # fewer images than ranks: every rank keeps its own (same decision
+            return patches, None                       # everywhere, since the counts were all-gathered)
         starts = [0]
         for c in my_counts:
             starts.append(starts[-1] + c)
@@ -64,7 +71,11 @@ class EncoderBalance:
         in_rows = [sum(my_counts[i] for i in send[d]) for d in range(self.world)]
         out_rows = [sum(r) for r in recv]
         x = _ListAllToAll.apply(self.group, in_rows, out_rows, patches.index_select(0, idx.to(patches.device)))
-        return x, dict(idx=idx, in_rows=in_rows, out_rows=out_rows, recv=recv)
+        book = dict(idx=idx, in_rows=in_rows, out_rows=out_rows, recv=recv)
+        if my_grids is not None:                       # arrival order: by source rank, then by the source's image index
+            mine = sorted(self.assign[self.rank])
+            book["grids"] = torch.tensor([self.all_grids[s][i] for s, i in mine], dtype=torch.long).view(-1, 3)
+        return x, book
 
     def combine(self, feats: torch.Tensor, book: dict, ratio: int = 1):
         """Inverse movement for per-patch (ratio=1) or per-merged-token (ratio = merge^2) features."""

@@ -88,3 +88,90 @@ def exchange_duplicates(weights: Dict[str, torch.Tensor], plan: DupPlan, ep_grou
     for r in reqs:
         r.wait()
     return recv
+
+
+# ------------------------------------------------------------------------------------------ balanced dispatch
+class _ShipReplicas(torch.autograd.Function):
+    """Forward: every move's owner sends the hot expert's ``gate_up`` / ``down`` slices to the replica rank, which files
+    them in its next free replica slot.  Backward: the replica sends the slot's weight gradients home and the owner adds
+    them to the expert's own gradient, so the optimizer never sees the copies."""
+
+    @staticmethod
+    def forward(ctx, gate_up, down, moves, group, experts_per_rank, max_dup):
+        rank = dist.get_rank(group)
+        ctx.moves, ctx.group, ctx.per, ctx.max_dup, ctx.rank = moves, group, experts_per_rank, max_dup, rank
+        rep_gu = gate_up.new_zeros((max_dup,) + tuple(gate_up.shape[1:]))
+        rep_dn = down.new_zeros((max_dup,) + tuple(down.shape[1:]))
+        reqs, slot = [], {}
+        for e, src, dst, _ in moves:
+            j = slot.get(dst, 0)
+            slot[dst] = j + 1
+            for w, rep in ((gate_up, rep_gu), (down, rep_dn)):
+                if rank == src:
+                    reqs.append(dist.isend(w[e % experts_per_rank].detach().contiguous(), dist.get_global_rank(group, dst),
+                                           group=group))
+                elif rank == dst:
+                    reqs.append(dist.irecv(rep[j], dist.get_global_rank(group, src), group=group))
+        for r in reqs:
+            r.wait()
+        return rep_gu, rep_dn
+
+    @staticmethod
+    def backward(ctx, g_gu, g_dn):
+        rank, per = ctx.rank, ctx.per
+        d_gu = d_dn = None
+        reqs, adds, slot = [], [], {}
+        for e, src, dst, _ in ctx.moves:
+            j = slot.get(dst, 0)
+            slot[dst] = j + 1
+            for which, g in ((0, g_gu), (1, g_dn)):
+                if rank == dst:
+                    reqs.append(dist.isend(g[j].contiguous(), dist.get_global_rank(ctx.group, src), group=ctx.group))
+                elif rank == src:
+                    buf = torch.empty_like(g[0])
+                    reqs.append(dist.irecv(buf, dist.get_global_rank(ctx.group, dst), group=ctx.group))
+                    adds.append((which, e % per, buf))
+        for r in reqs:
+            r.wait()
+        if adds:
+            d_gu = g_gu.new_zeros((per,) + tuple(g_gu.shape[1:]))
+            d_dn = g_dn.new_zeros((per,) + tuple(g_dn.shape[1:]))
+            for which, local, buf in adds:
+                (d_gu if which == 0 else d_dn)[local] += buf
+        return d_gu, d_dn, None, None, None, None
+
+
+def slot_table(plan: DupPlan, num_experts: int, ep: int, max_dup: int) -> torch.Tensor:
+    """Expert id (real, then one virtual id per move) -> global slot, when every rank holds ``per + max_dup`` slots:
+    its own experts first, then its replica slots in the order of the moves that target it."""
+    per = num_experts // ep
+    width = per + max_dup
+    table = [(e // per) * width + e % per for e in range(num_experts)]
+    used = {}
+    for _, _, dst, _ in plan.moves:
+        j = used.get(dst, 0)
+        used[dst] = j + 1
+        table.append(dst * width + per + j)
+    return torch.tensor(table, dtype=torch.long)
+
+
+def balanced_forward(dispatch_fn, tokens, topk_ids, probs, gate_up, down, num_experts: int, group, max_dup: int = 2):
+    """Expert-parallel MoE forward with hot experts duplicated for this call: count the tokens per expert over the whole
+    expert-parallel group, plan the moves, ship the replicas, rewrite the routing to slots and run ``dispatch_fn`` (any
+    of the dispatchers of ``parallel/ep.py``) over ``per + max_dup`` slots per rank.  Same result as the unbalanced call;
+    the busiest rank gets fewer rows."""
+    ep = dist.get_world_size(group)
+    counts = torch.bincount(topk_ids.reshape(-1), minlength=num_experts).float()
+    dist.all_reduce(counts, group=group)
+    plan = plan_duplicates(counts.tolist(), ep, max_dup)
+    if not plan.moves:
+        return dispatch_fn(tokens, topk_ids, probs, gate_up, down, num_experts, group), plan
+    per = num_experts // ep
+    rep_gu, rep_dn = _ShipReplicas.apply(gate_up, down, plan.moves, group, per, max_dup)
+    # the split of a hot expert's tokens must be decided once for the whole group: take the fraction of every rank's
+    # own slots (each rank moves the same share of what it routes there)
+    virt = apply_plan(topk_ids, plan, num_experts)
+    slots = slot_table(plan, num_experts, ep, max_dup).to(topk_ids.device)[virt]
+    out = dispatch_fn(tokens, slots, probs, torch.cat([gate_up, rep_gu]), torch.cat([down, rep_dn]),
+                      ep * (per + max_dup), group)
+    return out, plan

@@ -3,7 +3,10 @@
 The LLM of a VLM is built per (tp rank, pp stage): fused QKV and gate|up are column-parallel (heads / FFN
 columns split), o_proj and down_proj row-parallel, embedding and head vocabulary-parallel, layers sliced over
 pipeline stages by ``pipeline_num_layers`` (models/vlm_model.py:300-345 in the reference).  The vision tower runs
-replicated on the first stage's tensor-parallel ranks (they see identical inputs, so their gradients agree).
+replicated on the first stage's tensor-parallel ranks (they see identical inputs, so their gradients agree), or, with
+``--hetero-parallel``, data parallel over them: each rank encodes a share of the micro-batch's images and the
+embeddings are all-gathered (``parallel/hetero.py``; the reference's per-module parallel plans,
+mindspeed_mm/utils/hetero_parallel.py:22-315).
 Parameters of a (tp, pp) rank are then sharded over the data-parallel group by the flat-buffer engine, i.e. the
 "distributed optimizer" of the Megatron recipes is the same ZeRO engine as the FSDP backend, and the training
 loop, log line and checkpointing are shared.  ``shard_full_state`` cuts a full (HF-layout internal) state dict into
@@ -82,14 +85,18 @@ class McoreVLMStage(nn.Module):
     """The part of the VLM that lives on one (tp, pp) coordinate."""
 
     def __init__(self, cfg: Qwen25VLConfig, tp_group, pp_rank: int, pp_size: int, llm_layers: Sequence[int],
-                 sequence_parallel: bool = True):
+                 sequence_parallel: bool = True, vision_data_parallel: bool = False):
         super().__init__()
         self.cfg, self.tp_group, self.sp = cfg, tp_group, sequence_parallel
+        self.vision_dp = vision_data_parallel and tp_group is not None
         self.first, self.last = pp_rank == 0, pp_rank == pp_size - 1
         self.layer_offset = sum(llm_layers[:pp_rank])
         t = cfg.text
         if self.first:
             self.visual = VisionTransformer(cfg.vision)
+            if self.vision_dp:                  # ranks encode different images: sum the tower's gradients over them
+                for p in self.visual.parameters():
+                    p._tp_sum_group = tp_group
             self.embed_tokens = VocabParallelEmbedding(t.vocab_size, t.hidden_size, tp_group, sequence_parallel=False)
         self.layers = nn.ModuleList([TPDecoderLayer(t, tp_group, sequence_parallel) for _ in range(llm_layers[pp_rank])])
         if self.last:
@@ -117,13 +124,27 @@ class McoreVLMStage(nn.Module):
             pv = batch.get("pixel_values")
             if pv is not None and pv.numel() > 0:
                 vis = self.visual
-                plan = batch.get("vision_plan") or vis.plan(batch["image_grid_thw"], pv.device)
+                share = None
+                if self.vision_dp and tp > 1:
+                    from .hetero import gather_image_rows, shard_images
+                    grid = batch["image_grid_thw"]
+                    share = shard_images(grid, tp, dist.get_rank(self.tp_group), vis.cfg.spatial_merge_size)
+                if share is not None:
+                    mine, rows, restore = share
+                    cnt = grid.prod(-1)
+                    off = torch.cumsum(cnt, 0) - cnt
+                    pv = torch.cat([pv[int(off[i]):int(off[i] + cnt[i])] for i in mine])
+                    plan = vis.plan(grid[mine], pv.device)
+                else:
+                    plan = batch.get("vision_plan") or vis.plan(batch["image_grid_thw"], pv.device)
                 v = run(vis.patch_embed, pv.to(x.dtype)).index_select(0, plan["perm"])
                 for i in range(len(vis.blocks)):
                     full = i in vis.cfg.fullatt_block_indexes
                     cu, mx = (plan["cu_full"], plan["max_full"]) if full else (plan["cu_win"], plan["max_win"])
                     v = run(vis.blocks[i], v, plan["cos"].to(x.dtype), plan["sin"].to(x.dtype), cu, mx)
                 v = run(vis.merger, v).index_select(0, plan["reverse"])
+                if share is not None:
+                    v = gather_image_rows(v, rows, restore, self.tp_group)
                 pos = batch.get("image_positions")
                 if pos is None:
                     pos = (ids == self.cfg.image_token_id).nonzero(as_tuple=True)[0]
@@ -186,13 +207,13 @@ def shard_full_state(full: Dict[str, torch.Tensor], cfg: Qwen25VLConfig, tp_rank
 
 # ------------------------------------------------------------------------------------------ driver
 def build_mcore(cfg: Qwen25VLConfig, ps, device, opt, param_dtype, llm_layers=None, sequence_parallel=True,
-                grad_accum_steps: int = 1):
+                grad_accum_steps: int = 1, vision_data_parallel: bool = False):
     from .fsdp import FSDPEngine
     pp, tp = ps.size("pp"), ps.size("tp")
     layers = split_layers(cfg.text.num_layers, pp, llm_layers)
     with torch.device("meta"):
         stage = McoreVLMStage(cfg, ps.get_tp_group() if tp > 1 else None, ps.rank_in("pp"), pp, layers,
-                              sequence_parallel and tp > 1)
+                              sequence_parallel and tp > 1, vision_data_parallel and tp > 1)
     dp = ps.size("dp")
     engine = FSDPEngine(stage.fsdp_units(), group=ps.group("dp") if dp > 1 else False, device=device,
                         param_dtype=param_dtype, opt=opt, grad_accum_steps=grad_accum_steps,
@@ -220,7 +241,11 @@ def pretrain_mcore(kind: str, args, dev, rank: int, world: int):
     opt = OptimConfig(lr=args.lr, betas=(args.adam_beta1, args.adam_beta2), eps=args.adam_eps,
                       weight_decay=args.weight_decay, clip_grad=0.0)
     stage, engine, layers = build_mcore(cfg, ps, dev, opt, torch.bfloat16 if (args.bf16 and dev.type == "cuda") else torch.float32,
-                                        td.get("pipeline_num_layers"), bool(args.sequence_parallel), grad_accum_steps=accum)
+                                        td.get("pipeline_num_layers"), bool(args.sequence_parallel), grad_accum_steps=accum,
+                                        vision_data_parallel=bool(getattr(args, "hetero_parallel", False)))
+    if getattr(args, "hetero_parallel", False) and tp > 1:
+        from .hetero import HeteroPlan, ModulePlan
+        print_rank0("> hetero parallel: " + HeteroPlan(world, {"vision": ModulePlan(pp=pp), "llm": ModulePlan(tp=tp, pp=pp)}).describe())
     engine.materialize(stable_init_fn(cfg.init_std, args.seed))
     pp_ranks = dist.get_process_group_ranks(ps.get_pp_group()) if pp > 1 else [rank]
     fwd_g = bwd_g = None

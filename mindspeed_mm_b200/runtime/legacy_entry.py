@@ -224,9 +224,16 @@ def pretrain(kind: str, argv=None, device: Optional[str] = None):
     if prof_cfg is not None and getattr(prof_cfg, "enable", False):
         sp = prof_cfg.static_param
         prof = Profiler(True, getattr(prof_cfg, "ranks", [0]), sp.start_step, sp.end_step, sp.save_path)
+    ema = None
+    if args.use_ema:
+        from .ema import ShardedEMA
+        ema = ShardedEMA(engine, decay=float(getattr(args, "ema_decay", None) or 0.9999), warmup=False)
+    if getattr(args, "encoder_dp_balance", False) and kind == "vlm" and ps.get_dp_world_size() > 1:
+        from ..parallel.data_balance import EncoderBalance
+        model.encoder_balance = EncoderBalance(ps.group("dp"))
     te = TrainEngine(model, engine, build_loss(loss_type, ps.group("dp"), ps.get_dp_world_size()), sched, cfg,
                      data_iter=None, checkpointer=ck, profiler=prof,
-                     dp_group=ps.group("dp"), dp_world=ps.get_dp_world_size(), device=dev)
+                     dp_group=ps.group("dp"), dp_world=ps.get_dp_world_size(), device=dev, ema=ema)
     if ck and args.load:
         te.load(load_optim=not args.no_load_optim, load_rng=not args.no_load_rng)
     # the sampler continues after the samples a resumed run has already consumed

@@ -55,8 +55,9 @@ class TrainEngine:
     def __init__(self, model, engine: FSDPEngine, loss_fn: Callable, schedule: LRSchedule, cfg: TrainConfig,
                  data_iter: Optional[Iterable] = None, val_iter_fn: Optional[Callable[[], Iterable]] = None,
                  checkpointer=None, profiler=None, memory_profiler=None, watchdog=None, dp_group=None,
-                 dp_world: int = 1, device="cpu", status_word: Optional[torch.Tensor] = None):
+                 dp_world: int = 1, device="cpu", status_word: Optional[torch.Tensor] = None, ema=None):
         self.model, self.engine, self.loss_fn, self.schedule, self.cfg = model, engine, loss_fn, schedule, cfg
+        self.ema = ema            # runtime.ema.ShardedEMA: updated after every optimizer step, saved with the per-rank state
         self.data_iter, self.val_iter_fn = data_iter, val_iter_fn
         self.checkpointer, self.profiler, self.memory_profiler, self.watchdog = \
             checkpointer, profiler, memory_profiler, watchdog
@@ -107,6 +108,8 @@ class TrainEngine:
             losses.append(r["loss"])
             tokens += int(mb.get("n_tokens", 0))
         grad_norm = self.engine.finish_step()
+        if self.ema is not None:
+            self.ema.update()
         loss = torch.stack(losses).mean()
         if self.dp_world > 1:
             dist.all_reduce(loss, op=dist.ReduceOp.AVG if loss.is_cuda else dist.ReduceOp.SUM, group=self.dp_group)
@@ -233,7 +236,8 @@ class TrainEngine:
         return dict(iteration=self.iteration, consumed_train_samples=self.consumed_train_samples,
                     lr_scheduler=self.schedule.state_dict(), torch_rng=torch.get_rng_state(),
                     cuda_rng=torch.cuda.get_rng_state() if self.device.type == "cuda" else None,
-                    dataloader=getattr(self.data_iter, "state_dict", lambda: None)())
+                    dataloader=getattr(self.data_iter, "state_dict", lambda: None)(),
+                    ema=self.ema.state_dict() if self.ema is not None else None)
 
     def load_extra_state(self, s: dict, load_rng: bool = True) -> None:
         self.iteration = s["iteration"]
@@ -245,6 +249,8 @@ class TrainEngine:
                 torch.cuda.set_rng_state(s["cuda_rng"])
         if s.get("dataloader") is not None and hasattr(self.data_iter, "load_state_dict"):
             self.data_iter.load_state_dict(s["dataloader"])
+        if s.get("ema") is not None and self.ema is not None:
+            self.ema.load_state_dict(s["ema"])
 
     def save(self):
         self.checkpointer.save(self.iteration, self.engine, self.extra_state())

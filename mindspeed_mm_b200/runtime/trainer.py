@@ -72,7 +72,8 @@ class Trainer:
             profiler=Profiler.from_config(args.tools.profile),
             memory_profiler=MemoryProfiler(**args.tools.memory_profile.model_dump()),
             watchdog=Watchdog(t.watchdog_timeout_s).start() if t.watchdog_timeout_s else None,
-            dp_group=self.ps.group("dp"), dp_world=self.ps.get_dp_world_size(), device=self.device)
+            dp_group=self.ps.group("dp"), dp_world=self.ps.get_dp_world_size(), device=self.device,
+            ema=self.build_ema())
         if self.checkpointer and t.load and t.load_format != "hf" and not hfio.is_hf_checkpoint(t.load):
             self.train_engine.load(load_optim=not t.no_load_optim, load_rng=not t.no_load_rng)
 
@@ -143,6 +144,14 @@ class Trainer:
                             comm="nccl", **common)
         return EngineMux(dense, expert, ep_group=self.ps.group("ep") if self.ps.size("ep") > 1 else None)
 
+    def build_ema(self):
+        """``training.use_ema``: a moving average of the fp32 master shards, kept per rank and checkpointed with it."""
+        t = self.args.training
+        if not t.use_ema:
+            return None
+        from .ema import ShardedEMA
+        return ShardedEMA(self.engine, decay=t.ema_decay, warmup=False)
+
     def hf_ops(self):
         """Hugging Face <-> internal name / layout map of the model, when it has one."""
         ops = getattr(self.model, "hf_ops", None)
@@ -202,6 +211,10 @@ class Trainer:
             for n in match_modules(cp.apply_modules, mod_names):
                 table[n].forward = chunk_mbs(table[n].forward, cp.chunk_mbs, cp.batch_dim, tuple(cp.chunk_arg_indexs),
                                              tuple(cp.chunk_kwarg_names))
+        if feat.enable_ep_balance:             # expert modules duplicate their hottest experts onto idle ranks per call
+            for m in self.model.modules():
+                if hasattr(m, "ep_balance_max_dup"):
+                    m.ep_balance_max_dup = int(feat.ep_balance_plan.max_dup_experts_num)
 
     def load_weights(self):
         t = self.args.training

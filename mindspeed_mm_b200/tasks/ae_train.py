@@ -75,8 +75,13 @@ class VAELoss(nn.Module):
 
 
 class AETrainer:
-    def __init__(self, vae, loss: VAELoss, disc: Optional[nn.Module] = None, lr: float = 1e-4, disc_lr: float = 1e-4):
+    def __init__(self, vae, loss: VAELoss, disc: Optional[nn.Module] = None, lr: float = 1e-4, disc_lr: float = 1e-4,
+                 ema_decay: float = 0.0):
+        """``ema_decay`` > 0 keeps a moving average of the autoencoder weights (the reference's ``--ema --ema_decay``),
+        updated after every generator step; ``self.ema.apply_shadow() / restore()`` brackets an evaluation."""
+        from ..runtime.ema import ModuleEMA
         self.vae, self.loss, self.disc = vae, loss, disc
+        self.ema = ModuleEMA(vae, ema_decay) if ema_decay > 0 else None
         self.opt = torch.optim.AdamW(vae.parameters(), lr=lr, betas=(0.9, 0.95))
         self.opt_d = torch.optim.AdamW(disc.parameters(), lr=disc_lr, betas=(0.9, 0.95)) if disc is not None else None
         self.step = 0
@@ -96,6 +101,8 @@ class AETrainer:
         self.opt.zero_grad(set_to_none=True)
         g.backward()
         self.opt.step()
+        if self.ema is not None:
+            self.ema.update()
         if self.disc is not None and self.step >= self.loss.disc_start:
             d = self.loss.discriminator(video, recon, self.disc)
             self.opt_d.zero_grad(set_to_none=True)

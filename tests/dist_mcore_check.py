@@ -62,7 +62,8 @@ def main():
     pp = world // tp
     cfg = small_cfg()
     n_mb = 2 if pp > 1 else 1
-    packs = make_batches(cfg, 2 * n_mb, 256, 1, 1, 224, 0, pin=False)
+    hetero = "--hetero" in sys.argv            # vision tower data parallel over the tensor-parallel ranks
+    packs = make_batches(cfg, 2 * n_mb, 256, 1, 3 if hetero else 1, 112 if hetero else 224, 0, pin=False)
     ok = toy_interleaved(world, rank)
     # reference: whole model in this process
     reset_parallel_state()
@@ -86,7 +87,8 @@ def main():
     # sharded run
     reset_parallel_state()
     ps = init_parallel_state(world_size=world, device_type="cpu", tensor_parallel_size=tp, pipeline_parallel_size=pp)
-    stage, engine, layers = build_mcore(cfg, ps, "cpu", OptimConfig(lr=1e-3), torch.float32, None, True, grad_accum_steps=n_mb)
+    stage, engine, layers = build_mcore(cfg, ps, "cpu", OptimConfig(lr=1e-3), torch.float32, None, True, grad_accum_steps=n_mb,
+                                        vision_data_parallel=hetero)
     engine.materialize(stable_init_fn(0.02, 0))
     local = shard_full_state(full, cfg, ps.rank_in("tp"), tp, ps.rank_in("pp"), layers)
     missing = engine.load_full_params(lambda n, shp: local.get(n))
@@ -116,7 +118,7 @@ def main():
     flag = torch.tensor([int(ok)])
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
-        print(f"dist_mcore_check world={world} tp={tp} pp={pp} losses={losses} ref={ref_losses} ok={bool(flag.item())}", flush=True)
+        print(f"dist_mcore_check world={world} tp={tp} pp={pp} hetero={hetero} losses={losses} ref={ref_losses} ok={bool(flag.item())}", flush=True)
     dist.destroy_process_group()
     sys.exit(0 if flag.item() else 1)
 

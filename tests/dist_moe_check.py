@@ -19,6 +19,8 @@ from mindspeed_mm_b200.parallel.state import init_parallel_state, reset_parallel
 
 
 def build(cfg, world, ep, group, dispatcher, clip=0.0):
+    balance = dispatcher.endswith("+balance")          # duplicate hot experts (parallel/ep_balance.py) on top of it
+    dispatcher = dispatcher.split("+")[0]
     cfg.text.ep_dispatcher = dispatcher
     ps = init_parallel_state(world_size=world, device_type="cpu", expert_parallel_size=ep)
     with torch.device("meta"):
@@ -31,6 +33,9 @@ def build(cfg, world, ep, group, dispatcher, clip=0.0):
                         grad_divide=world, no_recompute=())
     mux = EngineMux(dense, expert, ep_group=ps.group("ep") if ep > 1 else None)
     mux.materialize(stable_init_fn(0.02, 0))
+    if balance:
+        for l in model.layers:
+            l.mlp.experts.ep_balance_max_dup = 2
     return model, mux
 
 
@@ -121,7 +126,7 @@ def main():
             ls.append(float((loss_sum / n).detach()))
         ref.finish_step()
         ref_losses.append(sum(ls) / world)
-    for disp in ("alltoall", "allgather"):
+    for disp in ("alltoall", "allgather", "alltoall+balance", "allgather+balance"):
         reset_parallel_state()
         model, mux = build(cfg, world, world, dist.group.WORLD, disp)
         e_local = cfg.text.num_experts // world
@@ -146,6 +151,24 @@ def main():
         for a, b in zip(losses, ref_losses):
             if abs(a - b) > 3e-5 * max(1, abs(b)):
                 ok = False
+        if disp.endswith("+balance"):           # the duplication really happened, and it evened the ranks out
+            plan = model.layers[0].mlp.experts.last_balance_plan
+            good = bool(plan.moves) and max(plan.loads_after) < max(plan.loads_before)
+            if not good:
+                print(f"rank {rank} {disp}: no rebalancing: {plan}", flush=True)
+            ok = ok and good
+        got = {n: t.detach().clone() for n, t in mux.named_full_params()}
+        if disp == "alltoall":
+            base_params = got
+        else:                                   # same updated weights as the plain all-to-all run
+            # splitting an expert's rows over two ranks changes the summation order of its weight gradient; Adam turns
+            # the rounding of near-zero gradients into steps of a fraction of lr, so bound the largest deviation by a
+            # tenth of one step and the typical one far below that
+            worst = max(float((got[n] - base_params[n]).abs().max()) for n in got)
+            mean = max(float((got[n] - base_params[n]).abs().mean()) for n in got)
+            if worst >= 1e-4 or mean >= 1e-6:
+                print(f"rank {rank} {disp}: parameters differ from the all-to-all run by {worst:.3e} (mean {mean:.3e})", flush=True)
+            ok = ok and worst < 1e-4 and mean < 1e-6
         if rank == 0:
             print(f"dist_moe_check world={world} dispatcher={disp} losses={losses} ref={ref_losses}", flush=True)
     ok = clip_and_checkpoint_check(cfg, packs, full, rank, world) and ok

@@ -96,6 +96,13 @@ def test_tp_pp_backend_gloo():
     assert "ok=True" in _run_script(4, "dist_mcore_check.py")
 
 
+def test_tp_backend_with_vision_tower_data_parallel_gloo():
+    """--hetero-parallel: each tensor-parallel rank encodes a share of the images; losses over two steps (the second one
+    sees the summed vision gradients) equal the single-process run."""
+    out = _run_script(2, "dist_mcore_check.py", "--hetero")
+    assert "hetero=True" in out and "ok=True" in out
+
+
 @pytest.mark.parametrize("wide", [False, True])
 def test_u_shaped_disaggregated_pipeline_gloo(wide):
     assert "ok=True" in _run_script(3, "dist_ldt_check.py", *(["--wide"] if wide else []))
@@ -135,6 +142,11 @@ def test_engine_optimizers_sharded_match_single_process_gloo(extra):
     """Muon (all-gathered update, round-robin Newton-Schulz, reduce-scattered result) and per-group learning-rate
     multipliers give the same parameters on two ranks as on one."""
     assert "ok=True" in _run_script(2, "dist_fsdp_check.py", *extra)
+
+
+def test_encoder_data_balance_inside_the_model_gloo():
+    """Images re-dealt across data-parallel ranks before the vision tower: same loss and gradients as without."""
+    assert "ok=True" in _run_script(2, "dist_balance_check.py")
 
 
 def test_native_trainer_moe_recipe_with_expert_parallel_gloo():

@@ -100,3 +100,19 @@ def test_factory_ids():
     assert isinstance(build_ae(dict(model_id="vae", temporal_down=[False, False], **tiny)), AutoencoderKL2D)
     assert isinstance(build_ae(dict(model_id="wfvae", base=16, z_channels=4, num_res_blocks=1, energy_flow=8)), WFVAE)
     assert isinstance(build_ae(dict(model_id="movq", base=16, ch_mult=[1, 2, 2], num_res_blocks=1, n_embed=16)), MOVQ)
+
+
+def test_ae_trainer_moving_average_follows_the_weights():
+    import torch
+    from mindspeed_mm_b200.runtime.ema import ModuleEMA
+    lin = torch.nn.Linear(4, 4)
+    ema = ModuleEMA(lin, decay=0.5)
+    w0 = lin.weight.detach().clone()
+    with torch.no_grad():
+        lin.weight.add_(1.0)
+    ema.update()
+    assert torch.allclose(ema.shadow["weight"], w0 + 0.5)
+    ema.apply_shadow()
+    assert torch.allclose(lin.weight, w0 + 0.5)
+    ema.restore()
+    assert torch.allclose(lin.weight, w0 + 1.0)

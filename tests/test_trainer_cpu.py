@@ -143,3 +143,30 @@ def test_training_loop_stops_when_a_kernel_reported_a_timeout():
     assert ei.value.exit_code == 3 and "status 2" in str(ei.value)
     assert tr.train_engine.iteration == 2 and len(tr.train_engine.history) == 1   # the bad step is not logged as done
     assert int(word) == 0                                                        # cleared for a restart in-process
+
+
+def test_trainer_keeps_and_restores_a_moving_average(tmp_path):
+    """``training.use_ema``: the average follows the master weights with the configured decay, is written with the
+    checkpoint's per-rank state and comes back on resume; ``swap`` exchanges it with the live weights."""
+    from mindspeed_mm_b200.runtime.trainer import Trainer
+    base = ["model.config.text.num_layers=1", "model.config.vision.depth=1", "model.config.vision.fullatt_block_indexes=[0]",
+            "data.dataset_param.basic_parameters.seq_len=300", "data.dataset_param.basic_parameters.images_per_sample=1",
+            "training.micro_batch_size=1", "training.use_ema=true", "training.ema_decay=0.5", "training.lr=1.0e-3",
+            f"training.save={tmp_path}/ck"]
+    cfg = os.path.join(ROOT, "examples/qwen2.5vl/tiny_native.yaml")
+    tr = Trainer(load_config(cfg, base + ["training.train_iters=1", "training.save_interval=1"], world_size=1), device="cpu")
+    ema = tr.train_engine.ema
+    g0 = tr.engine.units[-1].groups[0]
+    w0 = g0.master.clone()
+    tr.train()
+    w1 = g0.master.clone()
+    assert ema.steps == 1 and not torch.equal(w1, w0)
+    s = ema.shadow[-1].clone()
+    assert torch.allclose(s, 0.5 * w0 + 0.5 * w1, atol=1e-7)
+    ema.swap()                                                              # master now holds the average
+    assert torch.allclose(g0.master, s) and torch.allclose(ema.shadow[-1], w1)
+    ema.swap()
+    assert torch.allclose(g0.master, w1)
+    tr2 = Trainer(load_config(cfg, base + ["training.train_iters=1", f"training.load={tmp_path}/ck"], world_size=1), device="cpu")
+    assert tr2.train_engine.ema.steps == 1
+    assert torch.allclose(tr2.train_engine.ema.shadow[-1], s)

@@ -18,7 +18,7 @@ from typing import Callable, Dict, Iterable, List, Optional, Tuple
 
 import torch
 
-from .operators import (ExpertStack, Merge, Operator, QKVMerge, Rename, RenamePrefix, Reshape, StateDict, Transpose,
+from .operators import (AddConst, ExpertStack, Merge, Operator, QKVMerge, Rename, RenamePrefix, Reshape, StateDict, Transpose,
                         apply_ops, revert_ops)
 
 INDEX = "model.safetensors.index.json"
@@ -150,6 +150,75 @@ def qwen3vl_ops(cfg, experts_out_in: bool = False) -> List[Operator]:
     ]
     if experts_out_in:
         ops += [Transpose("layers.{i}.mlp.experts.gate_up_proj"), Transpose("layers.{i}.mlp.experts.down_proj")]
+    if t.tie_word_embeddings:
+        ops.append(_UntieHead())
+    return ops
+
+
+def qwen35_ops(cfg, experts_out_in: bool = False) -> List[Operator]:
+    """HF Qwen3.5 / Qwen3.5-MoE -> internal names/layouts (``cfg``: models.qwen3_5.Qwen35Config).  Beyond renames: the
+    four input projections of a GDN layer are fused (q|k|v, z, b, a), its depthwise conv weight drops the singleton
+    channel dim, q (with its per-head gate half) | k | v of a full-attention layer are fused, gate|up of the MLPs are
+    fused, and the zero-centred RMSNorm weights of the text stack get their 1 back.  Reference:
+    checkpoint/vlm_model/converters/qwen3_5.py."""
+    t, v = cfg.text, cfg.vision
+    L = "model.layers.{i}."
+    ops: List[Operator] = [
+        RenamePrefix("model.language_model.", "model."),
+        RenamePrefix("model.visual.", "visual."),
+        Reshape("visual.patch_embed.proj.weight", lambda x: (x.shape[0], -1),
+                lambda x: (x.shape[0], v.in_channels, v.temporal_patch_size, v.patch_size, v.patch_size)),
+        Rename("visual.pos_embed.weight", "visual.patch_embed.pos_embed.weight"),
+    ]
+    for kind in ("weight", "bias"):
+        ops += [
+            Rename("visual.blocks.{i}.attn.qkv." + kind, "visual.blocks.{i}.attn_qkv." + kind),
+            Rename("visual.blocks.{i}.attn.proj." + kind, "visual.blocks.{i}.attn_proj." + kind),
+            Rename("visual.blocks.{i}.mlp.linear_fc1." + kind, "visual.blocks.{i}.mlp_fc1." + kind),
+            Rename("visual.blocks.{i}.mlp.linear_fc2." + kind, "visual.blocks.{i}.mlp_fc2." + kind),
+            Rename("visual.merger.linear_fc1." + kind, "visual.merger.fc1." + kind),
+            Rename("visual.merger.linear_fc2." + kind, "visual.merger.fc2." + kind),
+        ]
+    ops += [
+        Rename("model.embed_tokens.weight", "embed_tokens.weight"),
+        # zero-centred norms first, under their HF names
+        AddConst(L + "input_layernorm.weight"), AddConst(L + "post_attention_layernorm.weight"),
+        AddConst(L + "self_attn.q_norm.weight"), AddConst(L + "self_attn.k_norm.weight"), AddConst("model.norm.weight"),
+        # GDN
+        Merge([L + "linear_attn.in_proj_qkv.weight", L + "linear_attn.in_proj_z.weight", L + "linear_attn.in_proj_b.weight",
+               L + "linear_attn.in_proj_a.weight"], "layers.{i}.linear_attn.in_proj.weight",
+              sizes=[2 * t.linear_num_key_heads * t.linear_key_head_dim + t.linear_num_value_heads * t.linear_value_head_dim,
+                     t.linear_num_value_heads * t.linear_value_head_dim, t.linear_num_value_heads, t.linear_num_value_heads]),
+        Reshape(L + "linear_attn.conv1d.weight", lambda x: (x.shape[0], x.shape[-1]), lambda x: (x.shape[0], 1, x.shape[-1])),
+        Rename(L + "linear_attn.conv1d.weight", "layers.{i}.linear_attn.conv_weight"),
+        Rename(L + "linear_attn.dt_bias", "layers.{i}.linear_attn.dt_bias"),
+        Rename(L + "linear_attn.A_log", "layers.{i}.linear_attn.A_log"),
+        Rename(L + "linear_attn.norm.weight", "layers.{i}.linear_attn.norm_weight"),
+        Rename(L + "linear_attn.out_proj.weight", "layers.{i}.linear_attn.out_proj.weight"),
+        # gated attention: q_proj holds query|gate per head, i.e. 2 x heads "heads" for the split sizes
+        QKVMerge([L + "self_attn.q_proj.weight", L + "self_attn.k_proj.weight", L + "self_attn.v_proj.weight"],
+                 "layers.{i}.self_attn.qkv_proj.weight", t.num_attention_heads * (2 if t.attn_output_gate else 1),
+                 t.num_key_value_heads, t.head_dim),
+        Rename(L + "self_attn.o_proj.weight", "layers.{i}.self_attn.o_proj.weight"),
+        Rename(L + "self_attn.q_norm.weight", "layers.{i}.self_attn.q_norm.weight"),
+        Rename(L + "self_attn.k_norm.weight", "layers.{i}.self_attn.k_norm.weight"),
+        # FFNs
+        Merge([L + "mlp.gate_proj.weight", L + "mlp.up_proj.weight"], "layers.{i}.gate_up_proj.weight"),
+        Rename(L + "mlp.down_proj.weight", "layers.{i}.down_proj.weight"),
+        Rename(L + "mlp.gate.weight", "layers.{i}.mlp.routed.gate.weight"),
+        Rename(L + "mlp.experts.gate_up_proj", "layers.{i}.mlp.routed.experts.gate_up_proj"),
+        Rename(L + "mlp.experts.down_proj", "layers.{i}.mlp.routed.experts.down_proj"),
+        Merge([L + "mlp.shared_expert.gate_proj.weight", L + "mlp.shared_expert.up_proj.weight"],
+              "layers.{i}.mlp.shared_gate_up.weight"),
+        Rename(L + "mlp.shared_expert.down_proj.weight", "layers.{i}.mlp.shared_down.weight"),
+        Rename(L + "mlp.shared_expert_gate.weight", "layers.{i}.mlp.shared_expert_gate.weight"),
+        Rename(L + "input_layernorm.weight", "layers.{i}.input_layernorm.weight"),
+        Rename(L + "post_attention_layernorm.weight", "layers.{i}.post_attention_layernorm.weight"),
+        Rename("model.norm.weight", "lm_head.norm.weight"),
+        Rename("lm_head.weight", "lm_head.weight"),
+    ]
+    if experts_out_in:
+        ops += [Transpose("layers.{i}.mlp.routed.experts.gate_up_proj"), Transpose("layers.{i}.mlp.routed.experts.down_proj")]
     if t.tie_word_embeddings:
         ops.append(_UntieHead())
     return ops

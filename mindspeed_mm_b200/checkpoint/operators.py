@@ -79,8 +79,9 @@ class RenamePrefix(Operator):
 class Merge(Operator):
     """Concatenate several source tensors along ``dim`` into one (gate|up, q|k|v, ...)."""
 
-    def __init__(self, srcs: Sequence[str], dst: str, dim: int = 0):
-        self.srcs, self.dst, self.dim = list(srcs), dst, dim
+    def __init__(self, srcs: Sequence[str], dst: str, dim: int = 0, sizes: Optional[Sequence[int]] = None):
+        """``sizes``: extents of the parts along ``dim`` for the way back when they are unequal (else an even split)."""
+        self.srcs, self.dst, self.dim, self.sizes = list(srcs), dst, dim, list(sizes) if sizes else None
         self._sizes: Dict[str, List[int]] = {}
 
     def apply(self, sd):
@@ -110,6 +111,8 @@ class Merge(Operator):
                 sd[_fill(n, m.groupdict())] = part.contiguous()
 
     def split_sizes(self, total: int) -> List[int]:
+        if self.sizes is not None:
+            return self.sizes
         n = len(self.srcs)
         if total % n:
             raise ValueError(f"cannot split {total} evenly into {n} for {self.dst}")
@@ -187,6 +190,25 @@ class Transpose(Operator):
                 sd[k] = sd[k].transpose(self.d0, self.d1).contiguous()
 
     revert = apply
+
+
+class AddConst(Operator):
+    """``t + c`` on the way in, ``t - c`` on the way out (zero-centred norm weights stored as ``w - 1``)."""
+
+    def __init__(self, name: str, c: float = 1.0):
+        self.name, self.c = name, c
+
+    def _do(self, sd, c):
+        rx = _compile(self.name)
+        for k in list(sd.keys()):
+            if rx.match(k):
+                sd[k] = (sd[k].float() + c).to(sd[k].dtype)
+
+    def apply(self, sd):
+        self._do(sd, self.c)
+
+    def revert(self, sd):
+        self._do(sd, -self.c)
 
 
 class Tie(Operator):

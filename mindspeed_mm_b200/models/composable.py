@@ -491,9 +491,6 @@ _IDS = dict(image_token_id=1023, video_token_id=1022, vision_start_token_id=1021
 # model id (as the reference registers it) -> tiny configuration exercising that family's switches
 PRESETS: Dict[str, ComposableConfig] = {
     "qwen2vl": ComposableConfig(_tiny_text(qkv_bias=True), "qwen_window", _tiny_qwen_vit(128), **_IDS),
-    "qwen3vl": ComposableConfig(_tiny_text(qk_norm=True), "qwen_window", _tiny_qwen_vit(128), **_IDS),
-    "qwen3_5_moe": ComposableConfig(_tiny_text(qk_norm=True, mixers=("gdn", "attn"), ffns=("moe", "moe"),
-                                               shared_expert_intermediate_size=64), "qwen_window", _tiny_qwen_vit(128), **_IDS),
     "qwen3omni": ComposableConfig(_tiny_text(qk_norm=True, ffns=("moe", "moe")), "qwen_window", _tiny_qwen_vit(128),
                                   audio=_tiny_audio(), audio_window=20, **_IDS),
     "qwen3_asr": ComposableConfig(_tiny_text(qk_norm=True, rope="rope1d"), None, audio=_tiny_audio(), audio_window=20, **_IDS),
@@ -501,7 +498,6 @@ PRESETS: Dict[str, ComposableConfig] = {
     "glm4v_moe": ComposableConfig(_tiny_text(qkv_bias=True, ffns=("dense", "moe"), shared_expert_intermediate_size=64),
                                   "qwen_window", _tiny_qwen_vit(128), **_IDS),
     "internvl3_5": ComposableConfig(_tiny_text(qk_norm=True, rope="rope1d"), "vit", vit=_tiny_vit(128), **_IDS),
-    "internvlu": ComposableConfig(_tiny_text(qk_norm=True, rope="rope1d"), "vit", vit=_tiny_vit(128), **_IDS),
     "mistral3": ComposableConfig(_tiny_text(rope="rope1d"), "vit", vit=_tiny_vit(128), **_IDS),
     "gemma4": ComposableConfig(_tiny_text(rope="rope1d", act="gelu_tanh", norm_plus_one=True, embed_scale=True, qk_norm=True),
                                "vit", vit=_tiny_vit(128), **_IDS),

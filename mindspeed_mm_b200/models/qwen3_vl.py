@@ -360,6 +360,7 @@ class Qwen3DecoderLayer(nn.Module):
 
 @model_register.register("qwen3_vl")
 @model_register.register("qwen3_vl_moe")
+@model_register.register("qwen3vl")            # the id the reference's transformers-backed trainer uses
 class Qwen3VLModel(nn.Module):
     """Packed-sequence Qwen3-VL / Qwen3-VL-MoE for training and generation.
 

@@ -1,0 +1,168 @@
+// Row normalisations with a row owned by a group of lanes instead of a CTA: RMSNorm, LayerNorm-modulate (adaLN / affine
+// LayerNorm) and L2 norm, forward.
+//
+// These ops read a row, reduce it, and only then can write it, so a thread block that owns one row alternates between
+// loading and storing and keeps few bytes in flight; at 8 resident blocks per SM that is about half of what HBM3e needs
+// to stay busy.  Here G lanes (4..32, a power of two) own a row: they load NV 16-byte vectors each, reduce with
+// shuffles inside the group (no shared memory, no block barrier) and write from registers.  A 256-thread block carries
+// 256 / G rows at once and every warp proceeds on its own, so an SM has tens of rows in flight.  Short rows
+// (per-head q/k norms of 64..256 elements) take a sub-warp group each instead of a whole block.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kBlock = 256;
+
+enum : int { kRms = 0, kLnMod = 1, kL2 = 2 };
+
+template <int G>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// a: RMS weight [H] | LN scale [B, H] | unused.   b: LN shift [B, H].   s0: rstd | mean | 1/norm.   s1: LN rstd.
+template <int G, int NV, int MODE>
+__global__ void __launch_bounds__(kBlock) rownorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ a,
+                                                            const bf16* __restrict__ b, bf16* __restrict__ y,
+                                                            float* __restrict__ s0, float* __restrict__ s1,
+                                                            long long rows, int S, int H, float eps) {
+    constexpr int kRowsPerBlock = kBlock / G;
+    const int nvec = H >> 3;
+    const int gl = threadIdx.x % G;                     // lane inside the group
+    const long long first = (long long)blockIdx.x * kRowsPerBlock + threadIdx.x / G;
+    const long long step = (long long)gridDim.x * kRowsPerBlock;
+    // every lane of a warp runs the same number of iterations (the shuffles need all 32 lanes): rows past the end are
+    // computed on nothing and write nothing
+    const long long iters = (rows + step - 1) / step;
+    long long row = first;
+    for (long long it = 0; it < iters; ++it, row += step) {
+        const bool live = row < rows;
+        const Vec8* xr = reinterpret_cast<const Vec8*>(x + (size_t)(live ? row : 0) * H);
+        Vec8 cache[NV];
+        float s = 0.f, ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int i = gl + j * G;
+            if (live && i < nvec) {
+                cache[j] = xr[i];
+                float f[8];
+                unpack8(cache[j], f);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if (MODE == kLnMod) s += f[k];
+                    ss += f[k] * f[k];
+                }
+            }
+        }
+        ss = group_sum<G>(ss);
+        float mean = 0.f, r;
+        if (MODE == kLnMod) {
+            s = group_sum<G>(s);
+            mean = s / (float)H;
+            r = rsqrtf(fmaxf(ss / (float)H - mean * mean, 0.f) + eps);
+        } else if (MODE == kRms) {
+            r = rsqrtf(ss / (float)H + eps);
+        } else {
+            r = rsqrtf(ss + eps);
+        }
+        if (!live) continue;
+        if (gl == 0) {
+            if (MODE == kLnMod) {
+                s0[row] = mean;
+                s1[row] = r;
+            } else if (s0) {
+                s0[row] = r;
+            }
+        }
+        const size_t wrow = MODE == kLnMod ? (size_t)(row / S) * H : 0;
+        const Vec8* ar = reinterpret_cast<const Vec8*>(a + wrow);
+        const Vec8* br = reinterpret_cast<const Vec8*>(b + wrow);
+        Vec8* yr = reinterpret_cast<Vec8*>(y + (size_t)row * H);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int i = gl + j * G;
+            if (i < nvec) {
+                float f[8], o[8];
+                unpack8(cache[j], f);
+                if (MODE == kRms) {
+                    float w[8];
+                    unpack8(ar[i], w);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) o[k] = f[k] * r * w[k];
+                } else if (MODE == kLnMod) {
+                    float sc[8], sh[8];
+                    unpack8(ar[i], sc);
+                    unpack8(br[i], sh);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) o[k] = (f[k] - mean) * r * (1.f + sc[k]) + sh[k];
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) o[k] = f[k] * r;
+                }
+                yr[i] = pack8(o);
+            }
+        }
+    }
+}
+
+template <int G, int NV, int MODE>
+int launch_one(const void* x, const void* a, const void* b, void* y, float* s0, float* s1, long long rows, int S, int H,
+               float eps, cudaStream_t st) {
+    static int per_sm = 0;                              // resident blocks per SM of this instantiation
+    if (per_sm == 0) {
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rownorm_fwd_kernel<G, NV, MODE>, kBlock, 0);
+        if (per_sm < 1) per_sm = 1;
+    }
+    constexpr int kRowsPerBlock = kBlock / G;
+    long long need = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
+    long long cap = 148LL * per_sm;
+    const int grid = (int)(need < cap ? need : cap);
+    if (grid == 0) return 0;
+    rownorm_fwd_kernel<G, NV, MODE><<<grid, kBlock, 0, st>>>((const bf16*)x, (const bf16*)a, (const bf16*)b, (bf16*)y, s0, s1,
+                                                             rows, S, H, eps);
+    return (int)cudaGetLastError();
+}
+
+template <int MODE>
+int launch(const void* x, const void* a, const void* b, void* y, float* s0, float* s1, long long rows, int S, int H,
+           float eps, cudaStream_t st) {
+    if (H % 8 || H < 8 || H > 8192) return -1;
+    const int nvec = H / 8;
+#define MM_RN(G, NV) return launch_one<G, NV, MODE>(x, a, b, y, s0, s1, rows, S, H, eps, st)
+    if (nvec <= 4) MM_RN(4, 1);
+    if (nvec <= 8) MM_RN(8, 1);
+    if (nvec <= 16) MM_RN(16, 1);
+    if (nvec <= 32) MM_RN(32, 1);
+    const int nv = (nvec + 31) / 32;
+    if (nv <= 2) MM_RN(32, 2);
+    if (nv <= 4) MM_RN(32, 4);
+    if (nv <= 6) MM_RN(32, 6);
+    if (nv <= 8) MM_RN(32, 8);
+    if (nv <= 12) MM_RN(32, 12);
+    if (nv <= 16) MM_RN(32, 16);
+    if (nv <= 20) MM_RN(32, 20);
+    if (nv <= 24) MM_RN(32, 24);
+    MM_RN(32, 32);
+#undef MM_RN
+}
+
+}  // namespace
+
+// y = x * rsqrt(mean(x^2) + eps) * w;  rstd (optional) [rows] keeps the factor for the backward.
+MM_API int mm_rownorm_rms_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int H, float eps,
+                              cudaStream_t st) {
+    return launch<kRms>(x, w, nullptr, y, rstd, nullptr, rows, 1, H, eps, st);
+}
+
+// y = LN(x) * (1 + scale[row / S]) + shift[row / S];  mean, rstd [rows].
+MM_API int mm_rownorm_ln_mod_fwd(const void* x, const void* scale, const void* shift, void* y, float* mean, float* rstd,
+                                 long long rows, int S, int H, float eps, cudaStream_t st) {
+    return launch<kLnMod>(x, scale, shift, y, mean, rstd, rows, S, H, eps, st);
+}
+
+// y = x * rsqrt(sum(x^2) + eps);  rnorm (optional) [rows].
+MM_API int mm_rownorm_l2_fwd(const void* x, void* y, float* rnorm, long long rows, int H, float eps, cudaStream_t st) {
+    return launch<kL2>(x, nullptr, nullptr, y, rnorm, nullptr, rows, 1, H, eps, st);
+}

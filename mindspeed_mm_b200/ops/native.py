@@ -37,9 +37,15 @@ def lib():
     return _LIB
 
 
+_ROWNORM_OLD = os.environ.get("MM_B200_ROWNORM", "") == "old"     # A/B switch: block-per-row forward kernels
+
+
 def _declare(L):
     sig = {
         "mm_rmsnorm_fwd": [_p, _p, _p, _p, _i, _i, _f, _p],
+        "mm_rownorm_rms_fwd": [_p, _p, _p, _p, _ll, _i, _f, _p],
+        "mm_rownorm_ln_mod_fwd": [_p, _p, _p, _p, _p, _p, _ll, _i, _i, _f, _p],
+        "mm_rownorm_l2_fwd": [_p, _p, _p, _ll, _i, _f, _p],
         "mm_rmsnorm_bwd_grid": [_i],
         "mm_rmsnorm_bwd": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _p],
         "mm_swiglu_fwd": [_p, _p, _ll, _i, _p],
@@ -153,8 +159,8 @@ class _RMSNorm(torch.autograd.Function):
         y = torch.empty_like(x2)
         rstd = torch.empty(T, dtype=torch.float32, device=x.device)
         wc = w.contiguous()
-        _check(lib().mm_rmsnorm_fwd(x2.data_ptr(), wc.data_ptr(), y.data_ptr(), rstd.data_ptr(), T, H, eps, _st()),
-               "rmsnorm_fwd")
+        fn = lib().mm_rmsnorm_fwd if _ROWNORM_OLD else lib().mm_rownorm_rms_fwd
+        _check(fn(x2.data_ptr(), wc.data_ptr(), y.data_ptr(), rstd.data_ptr(), T, H, eps, _st()), "rmsnorm_fwd")
         ctx.save_for_backward(x2, wc, rstd)
         ctx.shape = shape
         return y.view(shape)
@@ -297,8 +303,9 @@ class _LNMod(torch.autograd.Function):
         y = torch.empty_like(xc)
         mean = torch.empty(B * S, dtype=torch.float32, device=x.device)
         rstd = torch.empty_like(mean)
-        _check(lib().mm_ln_mod_fwd(xc.data_ptr(), sc.data_ptr(), sh.data_ptr(), y.data_ptr(), mean.data_ptr(),
-                                   rstd.data_ptr(), B * S, S, H, eps, _st()), "ln_mod_fwd")
+        fn = lib().mm_ln_mod_fwd if _ROWNORM_OLD else lib().mm_rownorm_ln_mod_fwd
+        _check(fn(xc.data_ptr(), sc.data_ptr(), sh.data_ptr(), y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), B * S, S, H,
+                  eps, _st()), "ln_mod_fwd")
         ctx.save_for_backward(xc, sc, mean, rstd)
         ctx.sshape = scale.shape
         return y
@@ -857,7 +864,8 @@ class _L2Norm(torch.autograd.Function):
         x2 = x.reshape(-1, D).contiguous()
         y = torch.empty_like(x2)
         r = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
-        _check(lib().mm_l2norm_fwd(x2.data_ptr(), y.data_ptr(), r.data_ptr(), x2.shape[0], D, eps, _st()), "l2norm_fwd")
+        fn = lib().mm_l2norm_fwd if (_ROWNORM_OLD or D % 8) else lib().mm_rownorm_l2_fwd
+        _check(fn(x2.data_ptr(), y.data_ptr(), r.data_ptr(), x2.shape[0], D, eps, _st()), "l2norm_fwd")
         ctx.save_for_backward(y, r)
         return y.view(x.shape)
 

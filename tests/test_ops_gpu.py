@@ -47,7 +47,8 @@ def _native_tier():
     native.check_status()
 
 
-@pytest.mark.parametrize("T,H", [(333, 1280), (1024, 3584), (64, 8192), (7, 512)])
+@pytest.mark.parametrize("T,H", [(333, 1280), (1024, 3584), (64, 8192), (7, 512), (4099, 128), (1000, 64), (300, 72),
+                                 (130, 5120), (257, 1152), (3, 32)])
 def test_rmsnorm_fwd_bwd(T, H):
     torch.manual_seed(0)
     x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)

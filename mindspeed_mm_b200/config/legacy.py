@@ -90,13 +90,14 @@ _INT = ["tensor-model-parallel-size", "pipeline-model-parallel-size", "context-p
         "train-iters", "log-interval", "save-interval", "eval-interval", "eval-iters", "num-workers", "seed",
         "num-layers", "hidden-size", "num-attention-heads", "max-position-embeddings", "lr-warmup-iters",
         "exit-interval", "ulysses-degree-in-cp", "virtual-pipeline-model-parallel-size", "recompute-num-layers",
-        "make-vocab-size-divisible-by", "distributed-timeout-minutes", "num-layers-per-virtual-pipeline-stage"]
+        "make-vocab-size-divisible-by", "distributed-timeout-minutes", "num-layers-per-virtual-pipeline-stage",
+        "tensorboard-log-interval"]
 _FLOAT = ["ema-decay", "lr", "min-lr", "weight-decay", "clip-grad", "adam-beta1", "adam-beta2", "adam-eps", "lr-warmup-fraction",
           "init-method-std", "exit-duration-in-mins", "attention-dropout", "hidden-dropout"]
 _STR = ["lr-decay-style", "tokenizer-type", "load", "save", "ckpt-format", "distributed-backend", "mm-data",
         "mm-model", "mm-tool", "context-parallel-algo", "fsdp2-config-path", "normalization", "recompute-granularity",
         "recompute-method", "position-embedding-type", "optimizer", "tensorboard-dir", "layerzero-config",
-        "load-base-model", "dataloader-type", "attention-mask-type"]
+        "load-base-model", "dataloader-type", "attention-mask-type", "wandb-project", "wandb-exp-name", "wandb-save-dir"]
 _BOOL = ["bf16", "fp16", "use-mcore-models", "use-flash-attn", "use-distributed-optimizer", "use-torch-fsdp2",
          "sequence-parallel", "swiglu", "use-fused-swiglu", "use-fused-rmsnorm", "use-fused-rotary-pos-emb",
          "no-load-optim", "no-load-rng", "no-save-optim", "no-save-rng", "variable-seq-lengths", "log-tps",
@@ -197,3 +198,33 @@ def load_fsdp2_config(path: str) -> dict:
                                            "output_dtype", "cast_forward_inputs"})
     out["unknown_keys"] = unknown
     return out
+
+
+def load_layerzero_config(path: str) -> dict:
+    """The LayerZero (FSDP1-style ZeRO-3) YAML of the reference's Wan / HunyuanVideo recipes (``--layerzero
+    --layerzero-config``; mindspeed_mm/patchs/fsdp1_patches.py:121, examples/wan2.1/zero_config.yaml), normalised to the
+    keys of ``load_fsdp2_config``: ``zero3_size`` is the shard group size (smaller than the data ranks = hybrid sharding),
+    ``transformer_layers`` names the wrapped block classes (reported only: units come from the model's ``fsdp_units()``),
+    ``forward_prefetch`` / ``backward_prefetch`` turn the engine's one-unit look-ahead on or off."""
+    import torch
+    import yaml
+    with open(path) as f:
+        raw = yaml.safe_load(f) or {}
+    dt = {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "fp16": torch.float16, "float16": torch.float16,
+          "fp32": torch.float32, "float32": torch.float32, None: None}
+    size = raw.get("zero3_size")
+    out = {
+        "sharding_size": None if size in (None, "auto", -1) else int(size),
+        "param_dtype": dt[raw.get("param_dtype")],
+        "reduce_dtype": dt[raw.get("reduce_dtype")],
+        "reshard_after_forward": True,
+        "sub_modules_to_wrap": [str(c).rsplit(".", 1)[-1] for c in (raw.get("transformer_layers") or [])],
+        "recompute_modules": [],
+        "offload_to_cpu": bool(raw.get("offload_to_cpu", False)),
+        "prefetch": 1 if (raw.get("forward_prefetch", True) or raw.get("backward_prefetch") not in (None, "None", False)) else 0,
+    }
+    known = {"zero3_size", "param_dtype", "reduce_dtype", "transformer_layers", "offload_to_cpu", "forward_prefetch",
+             "backward_prefetch", "limit_all_gathers", "ignored_modules", "ckpt_layers", "use_orig_params"}
+    out["unknown_keys"] = sorted(set(raw) - known)
+    return out
+

@@ -308,6 +308,11 @@ class MemoryProfilerArguments(_Base):
 class ToolsArguments(_Base):
     profile: ProfilerArguments = Field(default_factory=ProfilerArguments)
     memory_profile: MemoryProfilerArguments = Field(default_factory=MemoryProfilerArguments)
+    tensorboard_dir: Optional[str] = None          # scalars per iteration (loss, lr, grad norm, router aux loss, memory)
+    tensorboard_log_interval: int = 1
+    wandb_project: Optional[str] = None
+    wandb_exp_name: Optional[str] = None
+    wandb_save_dir: Optional[str] = None
 
 
 class Arguments(_Base):

@@ -363,6 +363,7 @@ class ComposableLM(Qwen25VLModel):
         self.lm_head = LMHead(t)
         if t.norm_plus_one:
             self.lm_head.norm = _norm(t, t.hidden_size)
+        self._set_aux_scale()
 
     @torch.no_grad()
     def init_weights(self, seed: int = 0):
@@ -396,7 +397,14 @@ class ComposableLM(Qwen25VLModel):
         return [(f"layers.{i}.mlp.routed.experts", l.mlp.routed.experts) for i, l in enumerate(self.layers)
                 if isinstance(l.mlp, MoEWithShared)]
 
+    def _set_aux_scale(self):
+        blocks = [m for m in self.modules() if isinstance(m, SparseMoeBlock)]
+        for b in blocks:                    # model-level auxiliary term = coef * mean over MoE layers
+            b.aux_scale = self.config.text.router_aux_loss_coef / len(blocks)
+
     def aux_loss(self):
+        """Value of the router load-balancing term of the last forward (detached; the gradient is attached inside the
+        MoE blocks)."""
         t = self.config.text
         ls = [l.mlp.aux_loss for l in self.layers if isinstance(l.mlp, MoEWithShared) and l.mlp.aux_loss is not None]
         return t.router_aux_loss_coef * torch.stack(ls).mean() if ls else None

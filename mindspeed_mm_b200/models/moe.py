@@ -62,13 +62,33 @@ class FusedExperts(nn.Module):
         return ops.moe_experts(tokens, topk_ids, probs, self.gate_up_proj, self.down_proj)
 
 
+class _AttachAux(torch.autograd.Function):
+    """Identity on ``y`` whose backward also feeds ``scale`` into the auxiliary loss, so that the router receives the
+    load-balancing gradient wherever the block's backward runs (inside a recomputed unit too) without the term being
+    part of the scalar the training loop differentiates.  The scale is that of the main loss: ``coef / moe_layers``
+    (the model-level term is ``coef * mean over layers``); gradient accumulation and data-parallel averaging are applied
+    by the engine to both alike."""
+
+    @staticmethod
+    def forward(ctx, y, aux, scale):
+        ctx.scale = scale
+        ctx.aux_meta = (aux.dtype, aux.device)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        dt, dev = ctx.aux_meta
+        return gy, torch.full((), ctx.scale, dtype=dt, device=dev), None
+
+
 class SparseMoeBlock(nn.Module):
     def __init__(self, c: MoETextConfig, num_local: Optional[int] = None):
         super().__init__()
         self.c = c
         self.gate = Linear(c.hidden_size, c.num_experts, bias=False)
         self.experts = FusedExperts(c, num_local)
-        self.aux_loss = None
+        self.aux_loss = None       # detached value of the last call (for logging)
+        self.aux_scale = None      # gradient scale of the auxiliary term; models set coef / number of MoE layers
 
     def forward(self, x):
         logits = F.linear(x, self.gate.weight)                     # tiny GEMM; keep in torch
@@ -77,7 +97,13 @@ class SparseMoeBlock(nn.Module):
         if self.c.norm_topk_prob:
             w = w / w.sum(-1, keepdim=True)
         w = w.to(x.dtype)
-        self.aux_loss = epmod.load_balancing_loss(logits, ids, self.c.num_experts) \
-            if (self.c.router_aux_loss_coef > 0 and torch.is_grad_enabled()) else None
         run = getattr(self.experts, "_fsdp_run", None)
-        return run(self.experts, x, ids, w) if run is not None else self.experts(x, ids, w)
+        out = run(self.experts, x, ids, w) if run is not None else self.experts(x, ids, w)
+        self.aux_loss = None
+        if self.c.router_aux_loss_coef > 0:
+            aux = epmod.load_balancing_loss(logits, ids, self.c.num_experts)
+            self.aux_loss = aux.detach()
+            if torch.is_grad_enabled() and aux.requires_grad:
+                scale = self.aux_scale if self.aux_scale is not None else self.c.router_aux_loss_coef
+                out = _AttachAux.apply(out, aux, float(scale))
+        return out

@@ -300,6 +300,9 @@ class Qwen35Model(nn.Module):
         self.layers = nn.ModuleList([Qwen35DecoderLayer(t, t.layer_is_linear(i), t.num_experts // ep if t.num_experts else None)
                                      for i in range(t.num_layers)])
         self.lm_head = LMHead(t)
+        blocks = [m for m in self.modules() if isinstance(m, SparseMoeBlock)]
+        for b in blocks:                    # model-level auxiliary term = coef * mean over MoE layers
+            b.aux_scale = t.router_aux_loss_coef / len(blocks)
 
     @torch.no_grad()
     def init_weights(self, seed: int = 0):
@@ -328,6 +331,8 @@ class Qwen35Model(nn.Module):
         return [(f"layers.{i}.mlp.routed.experts", l.mlp.experts) for i, l in enumerate(self.layers) if l.sparse]
 
     def aux_loss(self):
+        """Value of the router load-balancing term of the last forward (detached: its gradient is attached inside the
+        MoE blocks, ``models/moe.py: _AttachAux``)."""
         ls = [l.mlp.aux_loss for l in self.layers if l.sparse and l.mlp.aux_loss is not None]
         return self.config.text.router_aux_loss_coef * torch.stack(ls).mean() if ls else None
 

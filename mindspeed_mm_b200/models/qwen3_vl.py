@@ -382,6 +382,9 @@ class Qwen3VLModel(nn.Module):
             Qwen3DecoderLayer(t, config.layer_is_sparse(i), t.num_experts // ep if t.num_experts else None)
             for i in range(t.num_layers)])
         self.lm_head = LMHead(t)
+        blocks = [m for m in self.modules() if isinstance(m, SparseMoeBlock)]
+        for b in blocks:                    # model-level auxiliary term = coef * mean over MoE layers
+            b.aux_scale = t.router_aux_loss_coef / len(blocks)
 
     @torch.no_grad()
     def init_weights(self, seed: int = 0):
@@ -415,6 +418,8 @@ class Qwen3VLModel(nn.Module):
         return qwen3vl_ops(self.config)
 
     def aux_loss(self):
+        """Value of the router load-balancing term of the last forward (detached: its gradient is attached inside the
+        MoE blocks, ``models/moe.py: _AttachAux``)."""
         ls = [l.mlp.aux_loss for l in self.layers if l.sparse and l.mlp.aux_loss is not None]
         return self.config.text.router_aux_loss_coef * torch.stack(ls).mean() if ls else None
 

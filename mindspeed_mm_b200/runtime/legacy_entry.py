@@ -175,6 +175,9 @@ def pretrain(kind: str, argv=None, device: Optional[str] = None):
     if getattr(args, "fsdp2_config_path", None):
         from ..config.legacy import load_fsdp2_config
         f2 = load_fsdp2_config(args.fsdp2_config_path)
+    elif getattr(args, "layerzero", False) and getattr(args, "layerzero_config", None):
+        from ..config.legacy import load_layerzero_config          # same engine, LayerZero's key names
+        f2 = load_layerzero_config(args.layerzero_config)
     shard = f2["sharding_size"] if f2 and f2["sharding_size"] not in (None, world) else None
     if shard and (shard > world or world % shard or shard % cp):
         print_rank0(f"fsdp2 config asks for sharding_size={shard}, which does not divide the {world} ranks of this job: "
@@ -198,6 +201,8 @@ def pretrain(kind: str, argv=None, device: Optional[str] = None):
             extra["replicate_group"] = ps.group("dp_replicate")
         if f2.get("offload_to_cpu"):
             extra["offload_optimizer"] = True
+        if "prefetch" in f2:
+            extra["prefetch"] = f2["prefetch"]
         if f2["unknown_keys"]:
             print_rank0(f"fsdp2 config keys without effect here: {f2['unknown_keys']}")
     engine = FSDPEngine(model.fsdp_units(), group=ps.get_fsdp_group() if world > 1 else False, device=dev,
@@ -224,6 +229,11 @@ def pretrain(kind: str, argv=None, device: Optional[str] = None):
     if prof_cfg is not None and getattr(prof_cfg, "enable", False):
         sp = prof_cfg.static_param
         prof = Profiler(True, getattr(prof_cfg, "ranks", [0]), sp.start_step, sp.end_step, sp.save_path)
+    slog = None
+    if getattr(args, "tensorboard_dir", None) or getattr(args, "wandb_project", None):
+        from .logging import ScalarLog
+        slog = ScalarLog(args.tensorboard_dir, getattr(args, "wandb_project", None), getattr(args, "wandb_save_dir", None),
+                         getattr(args, "wandb_exp_name", None), int(getattr(args, "tensorboard_log_interval", None) or 1))
     ema = None
     if args.use_ema:
         from .ema import ShardedEMA
@@ -233,7 +243,7 @@ def pretrain(kind: str, argv=None, device: Optional[str] = None):
         model.encoder_balance = EncoderBalance(ps.group("dp"))
     te = TrainEngine(model, engine, build_loss(loss_type, ps.group("dp"), ps.get_dp_world_size()), sched, cfg,
                      data_iter=None, checkpointer=ck, profiler=prof,
-                     dp_group=ps.group("dp"), dp_world=ps.get_dp_world_size(), device=dev, ema=ema)
+                     dp_group=ps.group("dp"), dp_world=ps.get_dp_world_size(), device=dev, ema=ema, scalar_log=slog)
     if ck and args.load:
         te.load(load_optim=not args.no_load_optim, load_rng=not args.no_load_rng)
     # the sampler continues after the samples a resumed run has already consumed

@@ -89,3 +89,57 @@ def format_memory_report(rank: int, iteration: int) -> str:
             "max reserved: {}").format(rank, iteration, torch.cuda.memory_allocated() / mb,
                                         torch.cuda.max_memory_allocated() / mb, torch.cuda.memory_reserved() / mb,
                                         torch.cuda.max_memory_reserved() / mb)
+
+
+class ScalarLog:
+    """Per-iteration scalars for dashboards, written by rank 0: a TensorBoard event file (``tensorboard_dir``), a Weights &
+    Biases run (``wandb_project``; when the package is missing or cannot start a run, e.g. no login or no network, the
+    same records go to ``wandb-offline.jsonl`` in ``wandb_dir``), or both.  Every scalar is written against the iteration and, as ``"<name> vs samples"``, against the
+    consumed samples, the pairing the reference's training log uses (mindspeed_mm/training.py:934-1007)."""
+
+    def __init__(self, tensorboard_dir: Optional[str] = None, wandb_project: Optional[str] = None,
+                 wandb_dir: Optional[str] = None, wandb_name: Optional[str] = None, interval: int = 1):
+        self.interval = max(1, int(interval))
+        self.tb = self.wb = self.jsonl = None
+        if not is_rank0():
+            return
+        if tensorboard_dir:
+            from torch.utils.tensorboard import SummaryWriter
+            os.makedirs(tensorboard_dir, exist_ok=True)
+            self.tb = SummaryWriter(log_dir=tensorboard_dir)
+        if wandb_project:
+            try:
+                import wandb
+                self.wb = wandb.init(project=wandb_project, name=wandb_name, dir=wandb_dir)
+            except Exception:  # noqa: BLE001  (package missing, no login, no network: keep the records locally)
+                d = wandb_dir or tensorboard_dir or "."
+                os.makedirs(d, exist_ok=True)
+                self.jsonl = open(os.path.join(d, "wandb-offline.jsonl"), "a")
+
+    @property
+    def active(self) -> bool:
+        return self.tb is not None or self.wb is not None or self.jsonl is not None
+
+    def log(self, iteration: int, consumed_samples: int, scalars: Dict[str, float]) -> None:
+        if not self.active or iteration % self.interval:
+            return
+        scalars = {k: float(v) for k, v in scalars.items() if v is not None}
+        if self.tb is not None:
+            for k, v in scalars.items():
+                self.tb.add_scalar(k, v, iteration)
+                self.tb.add_scalar(k + " vs samples", v, consumed_samples)
+        if self.wb is not None:
+            self.wb.log(dict(scalars, **{"samples vs steps": consumed_samples}), step=iteration)
+        if self.jsonl is not None:
+            import json
+            self.jsonl.write(json.dumps(dict(scalars, iteration=iteration, samples=consumed_samples)) + "\n")
+            self.jsonl.flush()
+
+    def close(self) -> None:
+        if self.tb is not None:
+            self.tb.close()
+        if self.wb is not None:
+            self.wb.finish()
+        if self.jsonl is not None:
+            self.jsonl.close()
+

@@ -55,8 +55,11 @@ class TrainEngine:
     def __init__(self, model, engine: FSDPEngine, loss_fn: Callable, schedule: LRSchedule, cfg: TrainConfig,
                  data_iter: Optional[Iterable] = None, val_iter_fn: Optional[Callable[[], Iterable]] = None,
                  checkpointer=None, profiler=None, memory_profiler=None, watchdog=None, dp_group=None,
-                 dp_world: int = 1, device="cpu", status_word: Optional[torch.Tensor] = None, ema=None):
+                 dp_world: int = 1, device="cpu", status_word: Optional[torch.Tensor] = None, ema=None,
+                 scalar_log=None):
         self.model, self.engine, self.loss_fn, self.schedule, self.cfg = model, engine, loss_fn, schedule, cfg
+        self.scalar_log = scalar_log      # runtime.logging.ScalarLog (TensorBoard / W&B), rank 0 writes
+        self._aux = []                    # MoE load-balancing terms of the current step's micro-batches
         self.ema = ema            # runtime.ema.ShardedEMA: updated after every optimizer step, saved with the per-rank state
         self.data_iter, self.val_iter_fn = data_iter, val_iter_fn
         self.checkpointer, self.profiler, self.memory_profiler, self.watchdog = \
@@ -89,12 +92,13 @@ class TrainEngine:
             loss = self.loss_fn(loss_sum, n_valid)
         else:
             loss, n_valid = out, None
-        total = loss
-        aux_fn = getattr(self.model, "aux_loss", None)          # MoE router load-balancing term
+        loss.backward()
+        # MoE router load-balancing term: its gradient is attached inside the MoE blocks (it flows in recomputed units
+        # too); the model reports the value of this micro-batch for the log
+        aux_fn = getattr(self.model, "aux_loss", None)
         aux = aux_fn() if callable(aux_fn) else None
         if aux is not None:
-            total = loss + aux.to(loss.dtype)
-        total.backward()
+            self._aux.append(aux.detach())
         self.engine.end_micro_step()
         return dict(loss=loss.detach(), n_valid=n_valid)
 
@@ -115,9 +119,16 @@ class TrainEngine:
             dist.all_reduce(loss, op=dist.ReduceOp.AVG if loss.is_cuda else dist.ReduceOp.SUM, group=self.dp_group)
             if not loss.is_cuda:
                 loss = loss / self.dp_world
+        aux = None
+        if self._aux:                       # tracker of the router's auxiliary loss: mean over micro-batches and data ranks
+            aux = torch.stack(self._aux).float().mean()
+            self._aux = []
+            if self.dp_world > 1:
+                dist.all_reduce(aux, group=self.dp_group)
+                aux = aux / self.dp_world
         self.iteration += 1
         self.consumed_train_samples += self.cfg.global_batch_size
-        return dict(loss=loss, grad_norm=grad_norm, tokens=tokens)
+        return dict(loss=loss, grad_norm=grad_norm, tokens=tokens, aux_loss=aux)
 
     # ---------------------------------------------------------------------------------- loop
     def _sync(self):
@@ -168,12 +179,25 @@ class TrainEngine:
                     self.nan_iters += 1
                 rec = dict(iteration=self.iteration, loss=loss, time=dt, lr=lr,
                            grad_norm=None if r["grad_norm"] is None else float(r["grad_norm"]))
+                if r.get("aux_loss") is not None:
+                    rec["load_balancing_loss"] = float(r["aux_loss"])
                 self.history.append(rec)
+                if self.scalar_log is not None and self.scalar_log.active:
+                    sc = {"lm loss": loss, "learning-rate": lr, "grad-norm": rec["grad_norm"], "batch-size": cfg.global_batch_size,
+                          "iteration-time": dt, "load_balancing_loss": rec.get("load_balancing_loss")}
+                    if self.device.type == "cuda":
+                        ms = torch.cuda.memory_stats(self.device)
+                        sc.update({"mem-reserved-bytes": ms["reserved_bytes.all.current"],
+                                   "mem-allocated-bytes": ms["allocated_bytes.all.current"]})
+                    self.scalar_log.log(self.iteration, self.consumed_train_samples, sc)
                 if cfg.log_interval and self.iteration % cfg.log_interval == 0:
                     tps = r["tokens"] / max(1, cfg.micro_batch_size * cfg.gradient_accumulation_steps) \
                         if cfg.log_tps and r["tokens"] else None
                     print_rank0(format_training_log(self.iteration, cfg.train_iters, self.consumed_train_samples, dt,
-                                                    lr, cfg.global_batch_size, {"loss": loss}, rec["grad_norm"], tps,
+                                                    lr, cfg.global_batch_size,
+                                                    {"loss": loss, **({"load_balancing_loss": rec["load_balancing_loss"]}
+                                                                      if "load_balancing_loss" in rec else {})},
+                                                    rec["grad_norm"], tps,
                                                     skipped=self.skipped_iters, nan_iters=self.nan_iters))
                 if self.iteration == cfg.report_memory_at:
                     if (dist.get_rank() if dist.is_initialized() else 0) == 0:
@@ -189,6 +213,8 @@ class TrainEngine:
                         self.save()
                     break
         finally:
+            if self.scalar_log is not None:
+                self.scalar_log.close()
             if self.profiler:
                 self.profiler.stop()
             if prev is not None:

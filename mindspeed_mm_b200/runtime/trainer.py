@@ -73,7 +73,7 @@ class Trainer:
             memory_profiler=MemoryProfiler(**args.tools.memory_profile.model_dump()),
             watchdog=Watchdog(t.watchdog_timeout_s).start() if t.watchdog_timeout_s else None,
             dp_group=self.ps.group("dp"), dp_world=self.ps.get_dp_world_size(), device=self.device,
-            ema=self.build_ema())
+            ema=self.build_ema(), scalar_log=self.build_scalar_log())
         if self.checkpointer and t.load and t.load_format != "hf" and not hfio.is_hf_checkpoint(t.load):
             self.train_engine.load(load_optim=not t.no_load_optim, load_rng=not t.no_load_rng)
 
@@ -98,12 +98,17 @@ class Trainer:
         return model
 
     def _model_config(self, cls, m):
+        """``model_name_or_path/config.json`` (Hugging Face) describes the architecture when it exists; an inline
+        ``model.config`` block then only overrides single fields (its ``preset`` is ignored).  Without a checkpoint
+        directory the inline block, or a bare ``preset``, builds the config."""
         extra = m.model_extra or {}
-        if "config" in extra:                         # inline model config in the YAML
-            return _config_from_dict(cls, extra["config"])
+        inline = extra.get("config")
         if m.model_name_or_path and os.path.exists(os.path.join(m.model_name_or_path, "config.json")):
             with open(os.path.join(m.model_name_or_path, "config.json")) as f:
-                return _config_from_hf(cls, json.load(f))
+                cfg = _config_from_hf(cls, json.load(f))
+            return _config_from_dict(cls, {k: v for k, v in (inline or {}).items() if k != "preset"}, base=cfg)
+        if inline is not None:
+            return _config_from_dict(cls, inline)
         return _config_from_dict(cls, {"preset": extra.get("preset", "tiny")})
 
     def build_engine(self) -> FSDPEngine:
@@ -143,6 +148,13 @@ class Trainer:
         expert = FSDPEngine(expert_units, group=eg, grad_divide=self.ps.get_dp_world_size(), no_recompute=(),
                             comm="nccl", **common)
         return EngineMux(dense, expert, ep_group=self.ps.group("ep") if self.ps.size("ep") > 1 else None)
+
+    def build_scalar_log(self):
+        tl = self.args.tools
+        if not (tl.tensorboard_dir or tl.wandb_project):
+            return None
+        from .logging import ScalarLog
+        return ScalarLog(tl.tensorboard_dir, tl.wandb_project, tl.wandb_save_dir, tl.wandb_exp_name, tl.tensorboard_log_interval)
 
     def build_ema(self):
         """``training.use_ema``: a moving average of the fp32 master shards, kept per rank and checkpointed with it."""
@@ -234,19 +246,24 @@ class Trainer:
     def train(self):
         hist = self.train_engine.train()
         t = self.args.training
-        if t.save and t.save_format == "hf" and self.args.model.model_id == "qwen2_5vl":
-            hfio.save_engine_as_hf(self.engine, os.path.join(t.save, "hf"), hfio.qwen25vl_ops(self.model.config),
+        ops = self.hf_ops() if (t.save and t.save_format == "hf") else None
+        if ops is not None:
+            if self.train_engine.ema is not None:          # export the averaged weights, then put the live ones back
+                self.train_engine.ema.swap()
+            hfio.save_engine_as_hf(self.engine, os.path.join(t.save, "hf"), ops,
                                    get_dtype(t.save_ckpt_dtype) if t.save_ckpt_dtype else None,
                                    self.args.model.model_name_or_path, self.rank)
+            if self.train_engine.ema is not None:
+                self.train_engine.ema.swap()
         if self.checkpointer:
             self.checkpointer.wait()
         return hist
 
 
-def _config_from_dict(cls, d: dict):
+def _config_from_dict(cls, d: dict, base=None):
     cfg_cls = _config_class(cls)
     preset = d.get("preset")
-    cfg = getattr(cfg_cls, preset)() if preset and hasattr(cfg_cls, preset) else cfg_cls()
+    cfg = base if base is not None else (getattr(cfg_cls, preset)() if preset and hasattr(cfg_cls, preset) else cfg_cls())
     for k, v in d.items():
         if k == "preset":
             continue

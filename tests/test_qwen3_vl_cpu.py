@@ -100,3 +100,67 @@ def test_generation_cache_matches_rerun():
     a = gen.generate(ids, pixel_values=pixels, image_grid_thw=grid, max_new_tokens=5, use_cache=True)
     b = gen.generate(ids, pixel_values=pixels, image_grid_thw=grid, max_new_tokens=5, use_cache=False)
     assert torch.equal(a, b)
+
+
+def test_trainer_loads_and_writes_a_transformers_checkpoint(tmp_path):
+    """A checkpoint written by transformers' ``save_pretrained`` drives the native trainer (config.json -> model config,
+    safetensors -> sharding engine), and the trainer's ``save_format: hf`` output loads back into transformers."""
+    import os
+    from mindspeed_mm_b200.config import load_config
+    from mindspeed_mm_b200.runtime.trainer import Trainer
+    hf = _hf_model(False)
+    src = tmp_path / "hf_in"
+    hf.save_pretrained(src, safe_serialization=True)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    args = load_config(os.path.join(root, "examples/qwen3vl/tiny_moe_native.yaml"),
+                       ["model.model_id=qwen3_vl", f"model.model_name_or_path={src}", "parallel.expert_parallel_size=1",
+                        "training.train_iters=1", "training.lr=0.0", f"training.save={tmp_path}/out", "training.save_format=hf",
+                        "data.dataset_param.basic_parameters.seq_len=200", "data.dataloader_param.pin_memory=false"],
+                       world_size=1)
+    tr = Trainer(args, device="cpu")
+    assert tr.model.config.text.num_experts == 0 and tr.model.config.vision.deepstack_visual_indexes == (0, 1)
+    got = dict(tr.engine.named_full_params())
+    want = hfio.to_internal(hf.state_dict(), hfio.qwen3vl_ops(tr.model.config))
+    for k, v in want.items():
+        assert torch.allclose(got[k].float(), v.float(), atol=1e-6), k
+    tr.train()                                        # lr 0: weights unchanged, then the HF export runs
+    from transformers.models.qwen3_vl import Qwen3VLForConditionalGeneration
+    back = Qwen3VLForConditionalGeneration.from_pretrained(tmp_path / "out" / "hf", dtype=torch.float32)
+    ref = hf.state_dict()
+    for k, v in back.state_dict().items():
+        assert torch.allclose(v, ref[k], atol=1e-6), k
+
+
+def test_router_auxiliary_loss_gradient_is_attached_inside_the_blocks(monkeypatch):
+    """``loss.backward()`` alone gives the gradients of ``loss + coef * mean_layers(aux)``: the MoE blocks attach the
+    auxiliary term's gradient in their own backward (so it also flows when a unit is recomputed)."""
+    from mindspeed_mm_b200.models.moe import SparseMoeBlock
+    from mindspeed_mm_b200.parallel import ep as epmod
+    cfg = Qwen3VLConfig.tiny(moe=True)
+    cfg.text.router_aux_loss_coef = 0.1
+    model = Qwen3VLModel(cfg, ep_size=1).float()
+    model.init_weights(0)
+    ids, pixels, grid = _sample()
+    pos, _ = cfg.rope_index(ids, grid)
+    T = ids.numel()
+    labels = torch.cat([ids[1:], torch.tensor([-100])])
+    batch = dict(input_ids=ids, labels=labels, position_ids=pos, pixel_values=pixels, image_grid_thw=grid,
+                 cu_seqlens=torch.tensor([0, T], dtype=torch.int32), max_seqlen=T)
+    seen, orig = [], epmod.load_balancing_loss
+    monkeypatch.setattr(epmod, "load_balancing_loss", lambda *a: seen.append(orig(*a)) or seen[-1])
+    loss_sum, n = model(batch)
+    (loss_sum / n).backward()
+    attached = {k: p.grad.clone() for k, p in model.named_parameters() if p.grad is not None}
+    assert float(model.aux_loss()) > 0
+    model.zero_grad()
+    seen.clear()
+    for m in model.modules():
+        if isinstance(m, SparseMoeBlock):
+            m.aux_scale = 0.0
+    loss_sum, n = model(batch)
+    (loss_sum / n + 0.1 * torch.stack(seen).mean()).backward()
+    for k, p in model.named_parameters():
+        if p.grad is not None:
+            assert torch.allclose(attached[k], p.grad, atol=1e-6, rtol=1e-4), k
+    gate = [k for k in attached if k.endswith("mlp.gate.weight")]
+    assert gate and all(attached[k].abs().max() > 0 for k in gate)

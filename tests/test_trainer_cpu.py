@@ -170,3 +170,25 @@ def test_trainer_keeps_and_restores_a_moving_average(tmp_path):
     tr2 = Trainer(load_config(cfg, base + ["training.train_iters=1", f"training.load={tmp_path}/ck"], world_size=1), device="cpu")
     assert tr2.train_engine.ema.steps == 1
     assert torch.allclose(tr2.train_engine.ema.shadow[-1], s)
+
+
+def test_scalars_go_to_tensorboard_and_offline_wandb(tmp_path):
+    """``tools.tensorboard_dir`` / ``tools.wandb_project``: loss, learning rate, gradient norm and the MoE router's auxiliary
+    loss per iteration, each also against the consumed samples."""
+    import json
+    from tensorboard.backend.event_processing.event_accumulator import EventAccumulator
+    from mindspeed_mm_b200.runtime.trainer import Trainer
+    args = load_config(os.path.join(ROOT, "examples/qwen3vl/tiny_moe_native.yaml"),
+                       ["parallel.expert_parallel_size=1", "training.train_iters=2", "training.clip_grad=1.0",
+                        "model.config.text.router_aux_loss_coef=0.01", "data.dataset_param.basic_parameters.seq_len=200",
+                        "data.dataloader_param.pin_memory=false", f"tools.tensorboard_dir={tmp_path}/tb",
+                        "tools.wandb_project=demo", f"tools.wandb_save_dir={tmp_path}/wb"], world_size=1)
+    hist = Trainer(args, device="cpu").train()
+    assert "load_balancing_loss" in hist[-1] and hist[-1]["load_balancing_loss"] > 0
+    acc = EventAccumulator(str(tmp_path / "tb"))
+    acc.Reload()
+    tags = set(acc.Tags()["scalars"])
+    assert {"lm loss", "lm loss vs samples", "learning-rate", "grad-norm", "load_balancing_loss"} <= tags
+    assert [e.step for e in acc.Scalars("lm loss")] == [1, 2]
+    rows = [json.loads(l) for l in open(tmp_path / "wb" / "wandb-offline.jsonl")]
+    assert [r["iteration"] for r in rows] == [1, 2] and abs(rows[1]["lm loss"] - hist[1]["loss"]) < 1e-6

@@ -250,37 +250,64 @@ def bench_vit_attention(out_file, small):
 
 def bench_grouped_gemm(out, small):
     """Grouped expert GEMMs of Qwen3-VL-30B-A3B on one EP rank of 8: 16 local experts, 8192 tokens x top-8 / 8 ranks =
-    8192 routed rows with a skewed histogram; gate_up [2048 -> 1536] and down [768 -> 2048]; forward, data gradient and
-    weight gradient against a loop of cuBLAS matmuls over the same expert slices."""
+    8192 routed rows with a skewed histogram (softmax of N(0, 0.8) logits); gate_up [2048 -> 1536] and down [768 -> 2048].
+    The native kernel works on the aligned expert-major layout (every expert's rows start at a multiple of 128); it is
+    timed forward and forward + data gradient + weight gradient against a loop of cuBLAS matmuls over the experts' true
+    row ranges of the same buffer."""
     tf, _, src = peaks()
     E, H, F = 16, 2048, 768
     rows = 8192 if not small else 2048
     g = torch.Generator().manual_seed(0)
     w = torch.softmax(torch.randn(E, generator=g) * 0.8, 0)
-    counts = torch.multinomial(w, rows, replacement=True, generator=g).bincount(minlength=E).tolist()
+    ids = torch.multinomial(w, rows, replacement=True, generator=g).view(rows, 1).cuda()
+    counts = torch.bincount(ids.view(-1), minlength=E).tolist()
+    off, _, _, R = native.aligned_routing(ids, E)
+    starts = off.tolist()
     for name, K, N in (("gate_up", H, 2 * F), ("down", F, H)):
-        x = torch.randn(rows, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        x = torch.randn(R, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
         wt = (torch.randn(E, K, N, device="cuda") / K ** 0.5).to(torch.bfloat16).requires_grad_()
         flops = 2.0 * rows * K * N
 
         def fwd_native():
-            return ops.grouped_gemm(x, wt, counts)
+            return native._AlignedGroupedGemm.apply(x, wt, off)
+
+        class Loop(torch.autograd.Function):
+            @staticmethod
+            def forward(ctx, x, wt):
+                ctx.save_for_backward(x, wt)
+                y = torch.empty(R, N, dtype=x.dtype, device=x.device)
+                for e in range(E):
+                    if counts[e]:
+                        torch.matmul(x[starts[e]:starts[e] + counts[e]], wt[e], out=y[starts[e]:starts[e] + counts[e]])
+                return y
+
+            @staticmethod
+            def backward(ctx, gy):
+                x, wt = ctx.saved_tensors
+                dx, dw = torch.empty_like(x), torch.zeros_like(wt)
+                for e in range(E):
+                    if counts[e]:
+                        sl = slice(starts[e], starts[e] + counts[e])
+                        torch.matmul(gy[sl], wt[e].t(), out=dx[sl])
+                        torch.matmul(x[sl].t(), gy[sl], out=dw[e])
+                return dx, dw
 
         def fwd_loop():
-            return ops._GroupedGemmLoop.apply(x, wt, counts)
+            return Loop.apply(x, wt)
         t_f = time_fn(lambda: fwd_native())
         t_fl = time_fn(lambda: fwd_loop())
-        y = fwd_native()
-        gy = torch.randn_like(y)
+        gy = torch.randn(R, N, device="cuda", dtype=torch.bfloat16)
 
         def bwd(fn):
             x.grad = wt.grad = None
             fn().backward(gy)
         t_fb = time_fn(lambda: bwd(fwd_native), iters=5)
         t_fbl = time_fn(lambda: bwd(fwd_loop), iters=5)
-        emit(dict(op="grouped_gemm", case=name, rows=rows, experts=E, K=K, N=N, max_rows=max(counts), min_rows=min(counts),
+        emit(dict(op="grouped_gemm", case=name, rows=rows, aligned_rows=int(starts[-1]), experts=E, K=K, N=N,
+                  max_rows=max(counts), min_rows=min(counts),
                   fwd_ms=round(t_f, 4), fwd_tflops=round(flops / t_f / 1e9, 1), fwd_frac_of_peak=round(flops / t_f / 1e9 / tf, 3),
-                  fwd_bwd_ms=round(t_fb, 4), fwd_bwd_tflops=round(3 * flops / t_fb / 1e9, 1), peak=src,
+                  fwd_bwd_ms=round(t_fb, 4), fwd_bwd_tflops=round(3 * flops / t_fb / 1e9, 1),
+                  fwd_bwd_frac_of_peak=round(3 * flops / t_fb / 1e9 / tf, 3), peak=src,
                   cublas_loop_fwd_ms=round(t_fl, 4), cublas_loop_fwd_bwd_ms=round(t_fbl, 4),
                   fwd_vs_cublas_loop=round(t_fl / t_f, 3), fwd_bwd_vs_cublas_loop=round(t_fbl / t_fb, 3)), out)
         native.check_status()

@@ -224,6 +224,38 @@ def qwen35_ops(cfg, experts_out_in: bool = False) -> List[Operator]:
     return ops
 
 
+def hunyuanvideo_ops(cfg) -> List[Operator]:
+    """Published HunyuanVideo transformer checkpoint (``double_blocks.N.img_mod.linear``, ``txt_in.individual_token_refiner``,
+    ``final_layer`` ...) -> internal names (``cfg``: models.mmdit.MMDiTConfig).  The patch embedding is a Conv3d whose
+    kernel equals its stride, i.e. a Linear over flattened patches; everything else is a rename.  Reference:
+    checkpoint/sora_model/hunyuanvideo_converter.py:31-60 (its target names differ, the source names are the same)."""
+    p = cfg.patch_size
+    ops: List[Operator] = [
+        Reshape("img_in.proj.weight", lambda x: (x.shape[0], -1), lambda x: (x.shape[0], cfg.in_channels, p[0], p[1], p[2])),
+    ]
+    wb = ("weight", "bias")
+    pairs = [("img_in.proj", "embed.img_in"), ("time_in.mlp.0", "embed.time_in_0"), ("time_in.mlp.2", "embed.time_in_2"),
+             ("vector_in.in_layer", "embed.vector_in_0"), ("vector_in.out_layer", "embed.vector_in_2"),
+             ("guidance_in.mlp.0", "embed.guidance_in_0"), ("guidance_in.mlp.2", "embed.guidance_in_2"),
+             ("txt_in.input_embedder", "embed.txt_in.input_embedder"),
+             ("txt_in.t_embedder.mlp.0", "embed.txt_in.t_0"), ("txt_in.t_embedder.mlp.2", "embed.txt_in.t_2"),
+             ("txt_in.c_embedder.linear_1", "embed.txt_in.c_1"), ("txt_in.c_embedder.linear_2", "embed.txt_in.c_2"),
+             ("final_layer.linear", "final.linear"), ("final_layer.adaLN_modulation.1", "final.mod.lin")]
+    R, B = "txt_in.individual_token_refiner.blocks.{i}.", "embed.txt_in.blocks.{i}."
+    pairs += [(R + "norm1", B + "norm1"), (R + "norm2", B + "norm2"), (R + "self_attn_qkv", B + "qkv"),
+              (R + "self_attn_proj", B + "proj"), (R + "mlp.fc1", B + "mlp_0"), (R + "mlp.fc2", B + "mlp_2"),
+              (R + "adaLN_modulation.1", B + "mod")]
+    for st in ("img", "txt"):
+        D, I = "double_blocks.{i}." + st + "_", "double_blocks.{i}." + st + "."
+        pairs += [(D + "mod.linear", I + "mod.lin"), (D + "attn_qkv", I + "qkv"), (D + "attn_proj", I + "proj"),
+                  (D + "mlp.fc1", I + "mlp_0"), (D + "mlp.fc2", I + "mlp_2")]
+        ops += [Rename(D + "attn_q_norm.weight", I + "q_norm.weight"), Rename(D + "attn_k_norm.weight", I + "k_norm.weight")]
+    pairs += [("single_blocks.{i}.modulation.linear", "single_blocks.{i}.mod.lin")]      # linear1 / linear2 / q_norm / k_norm keep their names
+    for a, b in pairs:
+        ops += [Rename(f"{a}.{k}", f"{b}.{k}") for k in wb]
+    return ops
+
+
 class _UntieHead(Operator):
     """A tied checkpoint has no ``lm_head.weight``: the internal head gets a copy of the embedding; the way back
     drops it again."""

@@ -45,10 +45,13 @@ class MMDiTConfig:
     # block-sparse self-attention over the latent canvas (HunyuanVideo-1.5): dict(tile=(6, 8, 8), kernel=(3, 3, 3), topk=8,
     # mode="ssta"); None = dense
     sparse_attention: Optional[dict] = None
+    # HunyuanVideo: the prompt states go through a small timestep-aware transformer (the "token refiner") instead of one
+    # projection; 0 = plain Linear (FLUX, SD3)
+    text_refiner_layers: int = 0
 
     @staticmethod
     def hunyuan_video():
-        return MMDiTConfig()
+        return MMDiTConfig(text_refiner_layers=2)
 
     @staticmethod
     def hunyuan_video_15(**kw):
@@ -190,25 +193,81 @@ class SingleBlock(nn.Module):
         return ops.gated_residual(x, y, m[2])
 
 
+class TokenRefinerBlock(nn.Module):
+    """Pre-LayerNorm self-attention + SiLU MLP over the prompt tokens, both gated by the conditioning vector."""
+
+    def __init__(self, c: MMDiTConfig):
+        super().__init__()
+        H = c.hidden_size
+        self.nh = c.num_heads
+        self.norm1, self.norm2 = ops.LayerNorm(H, eps=c.eps), ops.LayerNorm(H, eps=c.eps)
+        self.qkv, self.proj = Linear(H, 3 * H), Linear(H, H)
+        self.mlp_0, self.mlp_2 = Linear(H, int(H * c.mlp_ratio)), Linear(int(H * c.mlp_ratio), H)
+        self.mod = Linear(H, 2 * H)
+
+    def forward(self, x, cvec, mask=None):
+        gate_msa, gate_mlp = self.mod(F.silu(cvec)).unsqueeze(1).chunk(2, dim=-1)
+        q, k, v = (_heads(t, self.nh) for t in self.qkv(self.norm1(x)).chunk(3, dim=-1))
+        if mask is None:
+            o = ops.attention_dense(q, k, v)
+        else:       # padded prompts: a token pair attends when both are real; everybody may look at token 0
+            am = mask[:, None, :, None] & mask[:, None, None, :]
+            am = am.clone()
+            am[..., 0] = True
+            o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=am).transpose(1, 2)
+        x = x + self.proj(o.flatten(2)) * gate_msa
+        return x + self.mlp_2(F.silu(self.mlp_0(self.norm2(x)))) * gate_mlp
+
+
+class TokenRefiner(nn.Module):
+    """HunyuanVideo's prompt branch in front of the blocks (mindspeed_mm/models/common/embeddings/text_embeddings.py:41-260):
+    the conditioning vector is ``time embedding + projection of the (masked) mean prompt state``; the prompt states are
+    embedded and refined by ``layers`` gated transformer blocks."""
+
+    def __init__(self, c: MMDiTConfig):
+        super().__init__()
+        H = c.hidden_size
+        self.input_embedder = Linear(c.text_dim, H)
+        self.t_0, self.t_2 = Linear(256, H), Linear(H, H)
+        self.c_1, self.c_2 = Linear(c.text_dim, H), Linear(H, H)
+        self.blocks = nn.ModuleList([TokenRefinerBlock(c) for _ in range(c.text_refiner_layers)])
+
+    def forward(self, txt, t, mask=None):
+        dt = self.input_embedder.weight.dtype
+        txt = txt.to(dt)
+        te = self.t_2(F.silu(self.t_0(sinusoidal_embedding(t, 256).to(dt))))
+        if mask is None:
+            ctx = txt.mean(dim=1)
+        else:
+            mf = mask.to(dt).unsqueeze(-1)
+            ctx = (txt * mf).sum(dim=1) / mf.sum(dim=1)
+        cvec = te + self.c_2(F.silu(self.c_1(ctx)))
+        x = self.input_embedder(txt)
+        for blk in self.blocks:
+            x = blk(x, cvec, mask)
+        return x
+
+
 class MMDiTEmbed(nn.Module):
     def __init__(self, c: MMDiTConfig):
         super().__init__()
         self.c = c
         p = c.patch_size
         self.img_in = Linear(c.in_channels * p[0] * p[1] * p[2], c.hidden_size)
-        self.txt_in = Linear(c.text_dim, c.hidden_size)
+        self.txt_in = TokenRefiner(c) if c.text_refiner_layers > 0 else Linear(c.text_dim, c.hidden_size)
         self.time_in_0, self.time_in_2 = Linear(256, c.hidden_size), Linear(c.hidden_size, c.hidden_size)
         self.vector_in_0, self.vector_in_2 = Linear(c.pooled_dim, c.hidden_size), Linear(c.hidden_size, c.hidden_size)
         if c.guidance_embed:
             self.guidance_in_0, self.guidance_in_2 = Linear(256, c.hidden_size), Linear(c.hidden_size, c.hidden_size)
 
-    def forward(self, tokens, txt, t, pooled, guidance=None):
+    def forward(self, tokens, txt, t, pooled, guidance=None, txt_mask=None):
         dt = self.img_in.weight.dtype
         vec = self.time_in_2(F.silu(self.time_in_0(sinusoidal_embedding(t, 256).to(dt))))
         vec = vec + self.vector_in_2(F.silu(self.vector_in_0(pooled.to(dt))))
         if self.c.guidance_embed and guidance is not None:
             vec = vec + self.guidance_in_2(F.silu(self.guidance_in_0(sinusoidal_embedding(guidance, 256).to(dt))))
-        return self.img_in(tokens.to(dt)), self.txt_in(txt.to(dt)), vec
+        text = self.txt_in(txt, t, txt_mask) if self.c.text_refiner_layers > 0 else self.txt_in(txt.to(dt))
+        return self.img_in(tokens.to(dt)), text, vec
 
 
 class MMDiTFinal(nn.Module):
@@ -240,14 +299,14 @@ class MMDiT(nn.Module):
         return [("embed", self.embed)] + [(f"double_blocks.{i}", b) for i, b in enumerate(self.double_blocks)] + \
                [(f"single_blocks.{i}", b) for i, b in enumerate(self.single_blocks)] + [("final", self.final)]
 
-    def forward(self, latents, t, txt, pooled, guidance=None, run=None):
+    def forward(self, latents, t, txt, pooled, guidance=None, run=None, txt_mask=None):
         run = run or (lambda m, *a, **k: m(*a, **k))
         c = self.config
         B, C, Fr, Hh, Ww = latents.shape
         pf, ph, pw = c.patch_size
         grid = (Fr // pf, Hh // ph, Ww // pw)
         x = latents.view(B, C, grid[0], pf, grid[1], ph, grid[2], pw).permute(0, 2, 4, 6, 1, 3, 5, 7).reshape(B, -1, C * pf * ph * pw)
-        img, text, vec = run(self.embed, x, txt, t, pooled, guidance)
+        img, text, vec = run(self.embed, x, txt, t, pooled, guidance, txt_mask)
         cos, sin = rope_nd(grid, c.rope_dims, c.rope_theta, device=latents.device)
         for blk in self.double_blocks:
             img, text = run(blk, img, text, vec, cos, sin, grid)
@@ -262,7 +321,10 @@ class MMDiT(nn.Module):
 
 @model_register.register("hunyuanvideodit")
 class HunyuanVideoDiT(MMDiT):
-    pass
+    def hf_ops(self):
+        """Name map of the published HunyuanVideo transformer checkpoint (``checkpoint/hf.py: hunyuanvideo_ops``)."""
+        from ..checkpoint.hf import hunyuanvideo_ops
+        return hunyuanvideo_ops(self.config)
 
 
 @model_register.register("hunyuanvideo15dit")

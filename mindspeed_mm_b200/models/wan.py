@@ -344,6 +344,11 @@ class SoRAModel(nn.Module):
     def fsdp_units(self):
         return self.predictor.fsdp_units()
 
+    def hf_ops(self):
+        """Name map of the predictor's published checkpoint, when it has one (unit names carry no ``predictor.`` prefix)."""
+        f = getattr(self.predictor, "hf_ops", None)
+        return f() if callable(f) else None
+
     def forward(self, batch: dict, run=None):
         with torch.no_grad():
             latents = batch["latents"] if "latents" in batch else self.ae.encode(batch["video"])

@@ -32,6 +32,7 @@ struct BwdParams {
     const int* cu_k;
     const int* tile_seq;
     const int* tile_r0;
+    const int* tile_nseq;   // sequences covered by each tile (> 1: packed short sequences, block-diagonal mask)
     const int* n_tiles;
     const float* lse;       // [Nq, T]  natural log
     const float* delta;     // [Nq, T]
@@ -68,9 +69,15 @@ __global__ void fmha_delta_kernel(const bf16* __restrict__ o, const bf16* __rest
     if (lane == 0) delta[(size_t)(row % Nq) * T + row / Nq] = s;
 }
 
-__global__ void fmha_bwd_plan_kernel(const int* cu, int n_seqs, int* tile_seq, int* tile_r0, int* n_tiles, int max_tiles,
-                                     int rows, int descending) {
+__global__ void fmha_bwd_plan_kernel(const int* cu, int n_seqs, int* tile_seq, int* tile_r0, int* n_tiles, int* tile_nseq,
+                                     int max_tiles, int rows, int descending, int pack) {
     if (threadIdx.x || blockIdx.x) return;
+    if (pack) {          // non-causal self-attention: short sequences share tiles
+        int n = 0;
+        for (int b = 0; b < n_seqs && n < max_tiles;) b = plan_packed(cu, n_seqs, b, rows, tile_seq, tile_r0, tile_nseq, n, max_tiles);
+        *n_tiles = n;
+        return;
+    }
     int n = 0, longest = 0;
     for (int b = 0; b < n_seqs; ++b) longest = max(longest, cu[b + 1] - cu[b]);
     const int nt = (longest + rows - 1) / rows;
@@ -78,6 +85,7 @@ __global__ void fmha_bwd_plan_kernel(const int* cu, int n_seqs, int* tile_seq, i
         const int t = descending ? nt - 1 - k : k;     // heavy tiles first
         for (int b = 0; b < n_seqs && n < max_tiles; ++b)
             if (t * rows < cu[b + 1] - cu[b]) {
+                tile_nseq[n] = 1;
                 tile_seq[n] = b;
                 tile_r0[n] = t * rows;
                 ++n;
@@ -123,11 +131,12 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seq = p.tile_seq[blockIdx.x];
     const int q0 = p.tile_r0[blockIdx.x];
+    const int nseq = p.tile_nseq[blockIdx.x];
     constexpr bool live = true;
     const int head = blockIdx.y;
     const int kv_head = head / (p.Nq / p.Nkv);
-    const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
-    const int k_begin = p.cu_k[seq], k_len = p.cu_k[seq + 1] - k_begin;
+    const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + nseq] - q_begin;
+    const int k_begin = p.cu_k[seq], k_len = p.cu_k[seq + nseq] - k_begin;
     const int diag = k_len - q_len;
     int kv_end = k_len;
     if (p.causal) kv_end = min(k_len, q0 + 128 + diag);
@@ -257,6 +266,8 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int qi = q0 + row;
         const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
         const bool row_ok = qi < q_len;
+        int vis_lo = 0, vis_hi = k_len;                  // keys this row may see (packed tiles: its own sequence)
+        if (nseq > 1) packed_row_range(p.cu_q, seq, nseq, q_begin + qi, q_begin, vis_lo, vis_hi);
         const size_t stat = (size_t)head * p.T + q_begin + min(qi, max(q_len - 1, 0));
         const float lse2 = n_kv > 0 ? p.lse[stat] * kLog2e : 0.f;
         const float dlt = n_kv > 0 ? p.delta[stat] : 0.f;
@@ -277,18 +288,18 @@ fmha_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             mbar_arrive(&s_empty[st]);
             mbar_arrive(dp_empty);
             const int kbase = j * 128 + half * 64;
-            const int limit = !row_ok ? -1 : (p.causal ? min(k_len - 1, qi + diag) : k_len - 1);
+            const int limit = !row_ok ? -1 : (p.causal ? min(k_len - 1, qi + diag) : vis_hi - 1);
             // packed fp32 math (two columns per instruction): dS = exp2(S * scale - lse) * (dP - delta)
             const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-dlt, -dlt);
-            const bool tile_masked = kbase + 63 > limit;         // some column of this row is hidden (or the row is padding)
+            const bool tile_masked = kbase + 63 > limit || nseq > 1;   // some column of this row is hidden (or the row is padding)
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), sc2, nl2);
                 const float2 g = __fadd2_rn(make_float2(__uint_as_float(d[2 * i]), __uint_as_float(d[2 * i + 1])), nd2);
                 float2 ds = __fmul2_rn(make_float2(exp2f(x.x), exp2f(x.y)), g);
                 if (tile_masked) {
-                    if (kbase + 2 * i > limit) ds.x = 0.f;
-                    if (kbase + 2 * i + 1 > limit) ds.y = 0.f;
+                    if (kbase + 2 * i > limit || kbase + 2 * i < vis_lo) ds.x = 0.f;
+                    if (kbase + 2 * i + 1 > limit || kbase + 2 * i + 1 < vis_lo) ds.y = 0.f;
                 }
                 d[i] = pack2(ds.x, ds.y);
             }
@@ -614,10 +625,14 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
     int* k_seq = plan + 2 * mq + 1;
     int* k_r0 = k_seq + mk;
     int* k_n = k_seq + 2 * mk;
+    int* q_nseq = k_n + 1;
+    int* k_nseq = q_nseq + mq;
+    // short sequences share a tile when the mask allows it: non-causal, keys and queries the same packed sequences
+    const int pack = !causal && cu_q == cu_k && T == Tk && variant != 0;
     fmha_delta_kernel<<<(unsigned)(((long long)T * Nq + 7) / 8), 256, 0, st>>>((const bf16*)o, (const bf16*)dO, delta, T, Nq, D);
-    fmha_bwd_plan_kernel<<<1, 32, 0, st>>>(cu_q, n_seqs, q_seq, q_r0, q_n, mq, 128, 1);
+    fmha_bwd_plan_kernel<<<1, 32, 0, st>>>(cu_q, n_seqs, q_seq, q_r0, q_n, q_nseq, mq, 128, 1, pack);
     // early key tiles see the most query tiles under a causal mask: emit them first
-    fmha_bwd_plan_kernel<<<1, 32, 0, st>>>(cu_k, n_seqs, k_seq, k_r0, k_n, mk, 128, 0);
+    fmha_bwd_plan_kernel<<<1, 32, 0, st>>>(cu_k, n_seqs, k_seq, k_r0, k_n, k_nseq, mk, 128, 0, pack);
     CUtensorMap tQ, tK, tV, tdO, tQ64, tdO64;
     int r;
     if ((r = make_tmap_3d(&tQ, q, D, Nq, T, D, q_ts, 64, 1, 128))) return 1000 + r;
@@ -628,11 +643,12 @@ MM_API int mm_fmha_bwd(const void* q, const void* k, const void* v, const void* 
     if ((r = make_tmap_3d(&tdO64, dO, D, Nq, T, D, (long long)Nq * D, 64, 1, BQ2))) return 6000 + r;
     if (cudaFuncSetAttribute(fmha_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDq) != cudaSuccess) return -3;
     if (cudaFuncSetAttribute(fmha_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDkv) != cudaSuccess) return -3;
-    BwdParams p{cu_q, cu_k, q_seq, q_r0, q_n, lse, delta, (bf16*)dq, (bf16*)dk, (bf16*)dv, T, Tk, Nq, Nkv, causal, D, scale,
+    BwdParams p{cu_q, cu_k, q_seq, q_r0, q_nseq, q_n, lse, delta, (bf16*)dq, (bf16*)dk, (bf16*)dv, T, Tk, Nq, Nkv, causal, D, scale,
                 scale * kLog2e, status, split_heads};
     BwdParams pk = p;
     pk.tile_seq = k_seq;
     pk.tile_r0 = k_r0;
+    pk.tile_nseq = k_nseq;
     pk.n_tiles = k_n;
     fmha_bwd_dq_kernel<<<dim3(mq, Nq), 320, kSmemDq, st>>>(tQ, tK, tV, tdO, p);
     if (variant != 0) {      // dK/dV over 128-row query steps: all four products at N = 128

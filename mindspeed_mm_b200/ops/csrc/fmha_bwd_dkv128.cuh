@@ -60,8 +60,9 @@ fmha_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const int head0 = p.split ? blockIdx.y : kv_head * Gfull;
     const int G = p.split ? 1 : Gfull;
     const int out_heads = p.split ? p.Nq : p.Nkv, out_head = blockIdx.y;
-    const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
-    const int k_begin = p.cu_k[seq], k_len = p.cu_k[seq + 1] - k_begin;
+    const int nseq = p.tile_nseq[blockIdx.x];          // > 1: consecutive short sequences packed into this tile
+    const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + nseq] - q_begin;
+    const int k_begin = p.cu_k[seq], k_len = p.cu_k[seq + nseq] - k_begin;
     const int diag = k_len - q_len;
     const int nq = (q_len + BQ - 1) / BQ;
     const int i_min = p.causal ? min(nq, max(0, kv0 - diag) / BQ) : 0;    // first query tile that can see this key tile
@@ -178,6 +179,8 @@ fmha_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const int tid2 = (warp - 2) * 32 + lane;         // 0..255
         const int kj = kv0 + row;                        // key index inside its sequence
         const bool row_ok = kj < k_len;
+        int vis_lo = 0, vis_hi = q_len;                  // queries that see this key (packed tiles: its own sequence)
+        if (nseq > 1) packed_row_range(p.cu_k, seq, nseq, k_begin + kj, k_begin, vis_lo, vis_hi);
         const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
         // per-column statistics (lse from threads 0..127, delta from 128..255) are fetched one tile ahead
         auto load_stat = [&](int it) -> float {
@@ -206,8 +209,8 @@ fmha_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             tmem_ld_32x32(t_s + 32, s + 32);
             tmem_wait_ld();
             // visible query columns for this key: qi < q_len and (not causal or kj <= qi + diag)
-            const int c_lo = !row_ok ? BQ : (p.causal ? max(0, kj - diag - qbase) : 0);
-            const int c_hi = min(BQ, q_len - qbase);
+            const int c_lo = !row_ok ? BQ : (p.causal ? max(0, kj - diag - qbase) : max(0, vis_lo - qbase));
+            const int c_hi = min(BQ, vis_hi - qbase);
             const float* ls = s_lse + half * 64;
             const float* dl = s_dlt + half * 64;
             // packed fp32 math (two query columns per instruction): P = exp2(S^T * scale - lse)

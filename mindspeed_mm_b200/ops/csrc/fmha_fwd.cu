@@ -35,6 +35,7 @@ struct FmhaParams {
     const int* tile_seq;
     const int* tile_q0;
     const int* n_tiles;
+    const int* tile_nseq;   // sequences covered by each tile (> 1: packed short sequences, block-diagonal mask)
     bf16* o;
     float* lse;         // [Nq, T]
     int T, Nq, Nkv, causal;
@@ -43,8 +44,15 @@ struct FmhaParams {
     int* status;
 };
 
-__global__ void fmha_plan_kernel(const int* cu_q, int n_seqs, int* tile_seq, int* tile_q0, int* n_tiles, int max_tiles) {
+__global__ void fmha_plan_kernel(const int* cu_q, int n_seqs, int* tile_seq, int* tile_q0, int* n_tiles, int* tile_nseq,
+                                 int max_tiles, int pack) {
     if (threadIdx.x || blockIdx.x) return;
+    if (pack) {          // non-causal self-attention: short sequences share tiles (all tiles cost about the same)
+        int n = 0;
+        for (int b = 0; b < n_seqs && n < max_tiles;) b = plan_packed(cu_q, n_seqs, b, BQ, tile_seq, tile_q0, tile_nseq, n, max_tiles);
+        *n_tiles = n;
+        return;
+    }
     // Later query tiles of a causal sequence have more key tiles: emit them first so the tail of the grid is
     // made of short work items.
     int n = 0, longest = 0;
@@ -54,6 +62,7 @@ __global__ void fmha_plan_kernel(const int* cu_q, int n_seqs, int* tile_seq, int
             if (t * BQ < cu_q[b + 1] - cu_q[b]) {
                 tile_seq[n] = b;
                 tile_q0[n] = t * BQ;
+                tile_nseq[n] = 1;
                 ++n;
             }
     *n_tiles = n;
@@ -333,7 +342,7 @@ MM_API int mm_fmha_set_fwd_variant(int v) {
     return prev;
 }
 
-// Scratch needed by the planner: 2 * max_tiles + 1 ints, max_tiles = T / 128 + n_seqs.
+// Scratch needed by the planner: 3 * max_tiles + 1 ints, max_tiles = T / 128 + n_seqs + 1.
 MM_API int mm_fmha_max_tiles(int T, int n_seqs) { return T / BQ + n_seqs + 1; }
 
 // q: [T, Nq, D] with q_ts elements between tokens (heads dense); k, v: [T, Nkv, D] likewise; o: [T, Nq, D]
@@ -347,7 +356,10 @@ MM_API int mm_fmha_fwd(const void* q, const void* k, const void* v, void* o, flo
     int* tile_seq = plan;
     int* tile_q0 = plan + max_tiles;
     int* n_tiles = plan + 2 * max_tiles;
-    fmha_plan_kernel<<<1, 32, 0, st>>>(cu_q, n_seqs, tile_seq, tile_q0, n_tiles, max_tiles);
+    int* tile_nseq = plan + 2 * max_tiles + 1;
+    // short sequences share a tile when the mask allows it: non-causal, keys and queries the same packed sequences
+    const int pack = !causal && cu_q == cu_k && T == Tk && g_fwd_variant != 0;
+    fmha_plan_kernel<<<1, 32, 0, st>>>(cu_q, n_seqs, tile_seq, tile_q0, n_tiles, tile_nseq, max_tiles, pack);
     CUtensorMap tQ, tK, tV;
     int r;
     if ((r = make_tmap_3d(&tQ, q, D, Nq, T, D, q_ts, 64, 1, BQ))) return 1000 + r;
@@ -362,7 +374,7 @@ MM_API int mm_fmha_fwd(const void* q, const void* k, const void* v, void* o, flo
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
-    FmhaParams p{cu_q, cu_k, tile_seq, tile_q0, n_tiles, (bf16*)o, lse, T, Nq, Nkv, causal, D,
+    FmhaParams p{cu_q, cu_k, tile_seq, tile_q0, n_tiles, tile_nseq, (bf16*)o, lse, T, Nq, Nkv, causal, D,
                  scale * 1.4426950408889634f, status};
     dim3 grid(max_tiles, Nq);
     if (g_fwd_variant == 0)      // fallback: one softmax warpgroup, O folded in registers

@@ -69,8 +69,9 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const int q0 = p.tile_q0[blockIdx.x];
     const int head = blockIdx.y;
     const int kv_head = head / (p.Nq / p.Nkv);
-    const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
-    const int k_begin = p.cu_k[seq], k_len = p.cu_k[seq + 1] - k_begin;
+    const int nseq = p.tile_nseq[blockIdx.x];          // > 1: consecutive short sequences packed into this tile
+    const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + nseq] - q_begin;
+    const int k_begin = p.cu_k[seq], k_len = p.cu_k[seq + nseq] - k_begin;
     const int diag = k_len - q_len;   // causal: key j visible to query i iff j <= i + diag
     int kv_end = k_len;
     if (p.causal) kv_end = min(k_len, q0 + BQ + diag);
@@ -179,6 +180,8 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const int row = qd * 32 + lane;
         const int qi = q0 + row;                         // query index inside its sequence
         const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
+        int vis_lo = 0, vis_hi = k_len;                  // keys this row may see (packed tiles: its own sequence)
+        if (nseq > 1) packed_row_range(p.cu_q, seq, nseq, q_begin + qi, q_begin, vis_lo, vis_hi);
         float m = -INFINITY, l = 0.f, alpha_pending = 0.f;
         float acc[C];
 #pragma unroll
@@ -217,14 +220,14 @@ fmha_fwd_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 tmem_ld_32x32(t_s + half * C, r);
                 if constexpr (C == 64) tmem_ld_32x32(t_s + half * C + 32, r + 32);
                 tmem_wait_ld();
-                const bool need_mask = (kbase + C > k_len) || (p.causal && kbase + C - 1 > q0 + diag);
-                const int limit = p.causal ? min(k_len - 1, qi + diag) : k_len - 1;   // last visible key index
+                const bool need_mask = (kbase + C > k_len) || (p.causal && kbase + C - 1 > q0 + diag) || nseq > 1;
+                const int limit = p.causal ? min(k_len - 1, qi + diag) : vis_hi - 1;  // last visible key index
                 // the maximum is taken over the raw scores (the softmax scale is positive); scale and shift are folded
                 // into one fused multiply-add in front of the exponential
                 if (need_mask) {
 #pragma unroll
                     for (int i = 0; i < C; ++i)
-                        if (kbase + i > limit) r[i] = 0xff800000u;       // -inf
+                        if (kbase + i > limit || kbase + i < vis_lo) r[i] = 0xff800000u;       // -inf
                 }
                 float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll

@@ -68,6 +68,50 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
 }
 
+// ------------------------------------------------------------------------------------------ packed attention tiles
+// Non-causal self-attention over many short sequences (vision-tower windows of 64 tokens): a tile may cover several
+// whole consecutive sequences whose lengths add up to at most its 128 rows.  The kernels then treat the group as one
+// sequence and mask block-diagonally: a row that belongs to sequence s only sees [cu[s], cu[s+1]).  `tok` is the row's
+// packed token index, `begin` = cu[first]; the range comes back relative to `begin`.
+__device__ __forceinline__ void packed_row_range(const int* cu, int first, int nseq, int tok, int begin, int& lo, int& hi) {
+    for (int s = first; s < first + nseq; ++s) {
+        const int a = cu[s], b = cu[s + 1];
+        if (tok >= a && tok < b) {
+            lo = a - begin;
+            hi = b - begin;
+        }
+    }
+}
+
+// One-thread planner step shared by the forward and backward planners: emits tiles of `rows` rows for sequence b, or,
+// when `pack` is set and sequence b is shorter than a tile, one tile for b and as many following sequences as fit.
+// Returns the index of the next sequence to plan.
+__device__ __forceinline__ int plan_packed(const int* cu, int n_seqs, int b, int rows, int* tile_seq, int* tile_r0,
+                                           int* tile_nseq, int& n, int max_tiles) {
+    const int len = cu[b + 1] - cu[b];
+    if (len >= rows) {
+        for (int r0 = 0; r0 < len && n < max_tiles; r0 += rows) {
+            tile_seq[n] = b;
+            tile_r0[n] = r0;
+            tile_nseq[n] = 1;
+            ++n;
+        }
+        return b + 1;
+    }
+    int cnt = 1, tot = len;
+    while (b + cnt < n_seqs && tot + (cu[b + cnt + 1] - cu[b + cnt]) <= rows) {
+        tot += cu[b + cnt + 1] - cu[b + cnt];
+        ++cnt;
+    }
+    if (n < max_tiles) {
+        tile_seq[n] = b;
+        tile_r0[n] = 0;
+        tile_nseq[n] = cnt;
+        ++n;
+    }
+    return b + cnt;
+}
+
 // ------------------------------------------------------------------------------------------ TMA
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)m) : "memory");

@@ -37,7 +37,11 @@ def lib():
     return _LIB
 
 
-_ROWNORM_OLD = os.environ.get("MM_B200_ROWNORM", "") == "old"     # A/B switch: block-per-row forward kernels
+# Row norms: rows of up to 256 elements (per-head q/k norms, L2 norm of GDN heads) take a lane group per row
+# (csrc/rownorm.cu: 0.94 of the copy bandwidth against 0.45 for a block per row); longer rows keep a block per row
+# (csrc/elementwise.cu), which measured faster there (0.67 against 0.45 at 3584).
+def _row_group(H: int) -> bool:
+    return H <= 256 and H % 8 == 0
 
 
 def _declare(L):
@@ -159,7 +163,7 @@ class _RMSNorm(torch.autograd.Function):
         y = torch.empty_like(x2)
         rstd = torch.empty(T, dtype=torch.float32, device=x.device)
         wc = w.contiguous()
-        fn = lib().mm_rmsnorm_fwd if _ROWNORM_OLD else lib().mm_rownorm_rms_fwd
+        fn = lib().mm_rownorm_rms_fwd if _row_group(H) else lib().mm_rmsnorm_fwd
         _check(fn(x2.data_ptr(), wc.data_ptr(), y.data_ptr(), rstd.data_ptr(), T, H, eps, _st()), "rmsnorm_fwd")
         ctx.save_for_backward(x2, wc, rstd)
         ctx.shape = shape
@@ -303,7 +307,7 @@ class _LNMod(torch.autograd.Function):
         y = torch.empty_like(xc)
         mean = torch.empty(B * S, dtype=torch.float32, device=x.device)
         rstd = torch.empty_like(mean)
-        fn = lib().mm_ln_mod_fwd if _ROWNORM_OLD else lib().mm_rownorm_ln_mod_fwd
+        fn = lib().mm_rownorm_ln_mod_fwd if _row_group(H) else lib().mm_ln_mod_fwd
         _check(fn(xc.data_ptr(), sc.data_ptr(), sh.data_ptr(), y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), B * S, S, H,
                   eps, _st()), "ln_mod_fwd")
         ctx.save_for_backward(xc, sc, mean, rstd)
@@ -551,7 +555,7 @@ def fmha_forward(q, k, v, cu_q, cu_k, causal, scale):
     n_seqs = cu_q.numel() - 1
     out = torch.empty(T, Nq, D, dtype=q.dtype, device=q.device)
     lse = torch.empty(Nq, T, dtype=torch.float32, device=q.device)
-    plan = torch.empty(2 * lib().mm_fmha_max_tiles(T, n_seqs) + 1, dtype=torch.int32, device=q.device)
+    plan = torch.empty(3 * lib().mm_fmha_max_tiles(T, n_seqs) + 1, dtype=torch.int32, device=q.device)
     cu_q = cu_q.to(torch.int32)
     cu_k = cu_k.to(torch.int32)
     rc = lib().mm_fmha_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), cu_q.data_ptr(),
@@ -581,7 +585,7 @@ def fmha_backward(do, q, k, v, out, lse, cu_q, cu_k, causal, scale):
     dv = torch.empty(Tk, Nq if split else Nkv, D, dtype=q.dtype, device=dev)
     delta = torch.empty(Nq, T, dtype=torch.float32, device=dev)
     L = lib()
-    plan = torch.empty(2 * (L.mm_fmha_bwd_max_tiles(T, n_seqs) + L.mm_fmha_bwd_max_tiles(Tk, n_seqs)) + 2,
+    plan = torch.empty(3 * (L.mm_fmha_bwd_max_tiles(T, n_seqs) + L.mm_fmha_bwd_max_tiles(Tk, n_seqs)) + 2,
                        dtype=torch.int32, device=dev)
     cu_q, cu_k = cu_q.to(torch.int32), cu_k.to(torch.int32)
     rc = L.mm_fmha_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), do.data_ptr(), lse.data_ptr(),
@@ -864,7 +868,7 @@ class _L2Norm(torch.autograd.Function):
         x2 = x.reshape(-1, D).contiguous()
         y = torch.empty_like(x2)
         r = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
-        fn = lib().mm_l2norm_fwd if (_ROWNORM_OLD or D % 8) else lib().mm_rownorm_l2_fwd
+        fn = lib().mm_l2norm_fwd if (D % 8 or not _row_group(D)) else lib().mm_rownorm_l2_fwd
         _check(fn(x2.data_ptr(), y.data_ptr(), r.data_ptr(), x2.shape[0], D, eps, _st()), "l2norm_fwd")
         ctx.save_for_backward(y, r)
         return y.view(x.shape)

@@ -284,6 +284,10 @@ def test_fmha_kernel_variants_agree_with_reference(fwd_variant, bwd_variant):
     (80, [1024, 1024, 400], 16, True),           # vision tower full-attention layers, q/k/v views of a fused projection
     (64, [300, 129, 700], 4, False),
     (96, [130, 257], 2, False),
+    # short sequences share 128-row tiles under a block-diagonal mask: ragged groups, a group of one, single tokens,
+    # exact fits (64 + 64, 128), sequences longer than a tile in between
+    (128, [30, 50, 48, 100, 20, 128, 200, 7, 1, 64, 64, 63, 2, 127, 1, 1], 4, False),
+    (72, [16] * 9 + [100, 28, 5, 64], 2, True),
 ])
 def test_attention_narrow_heads_run_the_tcgen05_kernels(D, lens, N, strided):
     """Head dims below 128 (a multiple of 8) run the same 128-wide kernels: the tensor maps carry the true head dim,

@@ -304,3 +304,34 @@ def test_sdxl_unet_matches_published_size_and_trains_through_the_sora_wrapper():
     a1 = torch.cat([torch.zeros(1, 24), compute_time_ids((64, 64), (16, 0), (64, 64))[None]], 1)
     p = torch.randn(1, 5, 48)
     assert (net(x, t, p, a0) - net(x, t, p, a1)).abs().max() > 0
+
+
+def test_hunyuanvideo_checkpoint_names_round_trip():
+    """Every parameter of the HunyuanVideo DiT (token refiner included) has a name in the published checkpoint layout;
+    published -> internal -> published is the identity and loads strictly."""
+    from mindspeed_mm_b200.checkpoint import hf as hfio
+    from mindspeed_mm_b200.models.mmdit import HunyuanVideoDiT, MMDiTConfig
+    import dataclasses
+    cfg = dataclasses.replace(MMDiTConfig.tiny(), text_refiner_layers=2)
+    torch.manual_seed(0)
+    net = HunyuanVideoDiT(cfg)
+    for p in net.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    ops = net.hf_ops()
+    pub = hfio.to_hf({k: v.clone() for k, v in net.state_dict().items()}, ops, modern_prefix=False)
+    assert pub["img_in.proj.weight"].shape == (64, 4, 1, 2, 2)
+    for k in ("txt_in.individual_token_refiner.blocks.1.self_attn_qkv.weight", "txt_in.c_embedder.linear_2.bias",
+              "double_blocks.0.img_attn_q_norm.weight", "double_blocks.0.txt_mlp.fc2.bias", "single_blocks.1.modulation.linear.weight",
+              "single_blocks.0.linear1.weight", "final_layer.adaLN_modulation.1.bias", "guidance_in.mlp.2.weight"):
+        assert k in pub, k
+    assert not any(k.startswith("embed.") or ".mod.lin." in k for k in pub)
+    back = hfio.to_internal(pub, net.hf_ops())
+    twin = HunyuanVideoDiT(cfg)
+    twin.load_state_dict(back, strict=True)
+    lat, t = torch.randn(1, 4, 2, 8, 8), torch.tensor([400.0])
+    txt, pooled, g = torch.randn(1, 6, 32), torch.randn(1, 16), torch.tensor([6.0])
+    mask = torch.tensor([[True, True, True, True, False, False]])
+    with torch.no_grad():
+        a, b = net(lat, t, txt, pooled, g, txt_mask=mask), twin(lat, t, txt, pooled, g, txt_mask=mask)
+        c = net(lat, t, txt, pooled, g)
+    assert torch.equal(a, b) and not torch.allclose(a, c)          # the prompt mask matters

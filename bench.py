@@ -469,7 +469,7 @@ def main():
         del trainer, dev_batches
         gc.collect()
         torch.cuda.empty_cache()
-        wan = run_wan(args, steps=min(args.steps, 5), nested=True)
+        wan = run_wan(args, steps=min(args.steps, 3), nested=True)      # 3 warm-up + 3 timed steps of 4 - 15 s each
         if out is not None:
             out["wan"] = wan
     elif out is not None:

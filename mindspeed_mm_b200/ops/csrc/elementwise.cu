@@ -370,29 +370,32 @@ __global__ void rope_inter_kernel(const bf16* __restrict__ x, long long xs, cons
 
 // ------------------------------------------------------------------------------------------ adaLN
 // y = LN(x) * (1 + scale[b]) + shift[b];  x: [B*S, H], scale/shift: [B, H] (bf16); saves mean / rstd.
+template <int NV>
 __global__ void __launch_bounds__(kThreads) ln_mod_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ scale,
                                                               const bf16* __restrict__ shift, bf16* __restrict__ y,
                                                               float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                               int T, int S, int H, float eps) {
     __shared__ float red[72];
     const int nvec = H >> 3;
-    // scale / shift of the batch entry the current row belongs to, kept in registers and re-read only when the entry
-    // changes (never for an affine LayerNorm, B = 1): reading them per row tripled the traffic through L1
-    Vec8 scv[kMaxVec], shv[kMaxVec];
+    // scale / shift of the batch entry the current row belongs to, kept (packed) in registers and re-read only when the
+    // entry changes (never for an affine LayerNorm, B = 1): reading them per row tripled the traffic through L1.  NV is
+    // the number of 16-byte vectors a thread owns, so a 3584-wide row costs 2 x 3 vectors of registers, not 4 x 3.
+    Vec8 xc[NV], scv[NV], shv[NV];
     int cached_b = -1;
     for (int row = blockIdx.x; row < T; row += gridDim.x) {
         const Vec8* xr = reinterpret_cast<const Vec8*>(x + (size_t)row * H);
-        float v[kMaxVec][8];
         float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-        for (int j = 0; j < kMaxVec; ++j) {
+        for (int j = 0; j < NV; ++j) {
             int i = threadIdx.x + j * kThreads;
             if (i < nvec) {
-                unpack8(xr[i], v[j]);
+                xc[j] = xr[i];
+                float f[8];
+                unpack8(xc[j], f);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
-                    s1 += v[j][k];
-                    s2 += v[j][k] * v[j][k];
+                    s1 += f[k];
+                    s2 += f[k] * f[k];
                 }
             }
         }
@@ -409,7 +412,7 @@ __global__ void __launch_bounds__(kThreads) ln_mod_fwd_kernel(const bf16* __rest
             const Vec8* sc = reinterpret_cast<const Vec8*>(scale + (size_t)b * H);
             const Vec8* sh = reinterpret_cast<const Vec8*>(shift + (size_t)b * H);
 #pragma unroll
-            for (int j = 0; j < kMaxVec; ++j) {
+            for (int j = 0; j < NV; ++j) {
                 int i = threadIdx.x + j * kThreads;
                 if (i < nvec) {
                     scv[j] = sc[i];
@@ -419,14 +422,15 @@ __global__ void __launch_bounds__(kThreads) ln_mod_fwd_kernel(const bf16* __rest
         }
         Vec8* yr = reinterpret_cast<Vec8*>(y + (size_t)row * H);
 #pragma unroll
-        for (int j = 0; j < kMaxVec; ++j) {
+        for (int j = 0; j < NV; ++j) {
             int i = threadIdx.x + j * kThreads;
             if (i < nvec) {
-                float a[8], c[8], o[8];
+                float f[8], a[8], c[8], o[8];
+                unpack8(xc[j], f);
                 unpack8(scv[j], a);
                 unpack8(shv[j], c);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) o[k] = (v[j][k] - mean) * rstd * (1.f + a[k]) + c[k];
+                for (int k = 0; k < 8; ++k) o[k] = (f[k] - mean) * rstd * (1.f + a[k]) + c[k];
                 yr[i] = pack8(o);
             }
         }
@@ -594,13 +598,25 @@ inline int grid_for(long long work_items, int threads, int per_sm = 8) {
 }  // namespace
 
 // ------------------------------------------------------------------------------------------ C ABI
+// Grid of a row-walking kernel: one wave of resident blocks (a second, partial wave would leave SMs idle at the end).
+template <typename K>
+static int resident_grid(K kernel, int threads, int rows, int& cache) {
+    if (cache == 0) {
+        int per_sm = 0;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0);
+        cache = 148 * (per_sm < 1 ? 1 : per_sm);
+    }
+    return rows < cache ? rows : cache;
+}
+
 MM_API int mm_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int T, int H, float eps,
                           cudaStream_t st) {
     if (H % 8 || H > kRowThreads * 8 * 8) return -1;
-    const int grid = T < 148 * 12 ? T : 148 * 12;
     const int nv = (H / 8 + kRowThreads - 1) / kRowThreads;
-#define MM_RMS_FWD(NV) \
-    rmsnorm_fwd_kernel<NV><<<grid, kRowThreads, 0, st>>>((const bf16*)x, (const bf16*)w, (bf16*)y, rstd, T, H, eps)
+    static int g2 = 0, g4 = 0, g8 = 0;
+#define MM_RMS_FWD(NV)                                                                                  \
+    rmsnorm_fwd_kernel<NV><<<resident_grid(rmsnorm_fwd_kernel<NV>, kRowThreads, T, g##NV), kRowThreads, 0, st>>>( \
+        (const bf16*)x, (const bf16*)w, (bf16*)y, rstd, T, H, eps)
     if (nv <= 2) MM_RMS_FWD(2);
     else if (nv <= 4) MM_RMS_FWD(4);
     else MM_RMS_FWD(8);
@@ -682,9 +698,15 @@ MM_API int mm_rope_interleaved(const void* x, long long xs, const float* cosf_, 
 MM_API int mm_ln_mod_fwd(const void* x, const void* scale, const void* shift, void* y, float* mean, float* rstd,
                          int T, int S, int H, float eps, cudaStream_t st) {
     if (H % 8 || H > kThreads * kMaxVec * 8) return -1;
-    int grid = T < 148 * 8 ? T : 148 * 8;
-    ln_mod_fwd_kernel<<<grid, kThreads, 0, st>>>((const bf16*)x, (const bf16*)scale, (const bf16*)shift, (bf16*)y, mean,
-                                                 rstd, T, S, H, eps);
+    const int nv = (H / 8 + kThreads - 1) / kThreads;
+    static int g1 = 0, g2 = 0, g4 = 0;
+#define MM_LN_FWD(NV)                                                                                                \
+    ln_mod_fwd_kernel<NV><<<resident_grid(ln_mod_fwd_kernel<NV>, kThreads, T, g##NV), kThreads, 0, st>>>(            \
+        (const bf16*)x, (const bf16*)scale, (const bf16*)shift, (bf16*)y, mean, rstd, T, S, H, eps)
+    if (nv <= 1) MM_LN_FWD(1);
+    else if (nv <= 2) MM_LN_FWD(2);
+    else MM_LN_FWD(4);
+#undef MM_LN_FWD
     return (int)cudaGetLastError();
 }
 

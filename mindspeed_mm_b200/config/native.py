@@ -236,6 +236,7 @@ class TrainingArguments(_Base):
     adam_beta2: float = 0.999
     adam_eps: float = 1e-8
     clip_grad: float = 0.0
+    clip_grad_ema_decay: float = 0.0    # > 0: adaptive clipping (threshold = moving average of the norm + 3 sigma)
     clip_grad_foreach: bool = True
     micro_batch_size: int = 1
     gradient_accumulation_steps: Optional[int] = 1

@@ -399,8 +399,12 @@ class LMHead(nn.Module):
         self.norm = RMSNorm(c.hidden_size, c.rms_norm_eps)
         self.weight = nn.Parameter(torch.empty(c.vocab_size, c.hidden_size))
 
-    def forward(self, x, labels=None):
-        h = self.norm(x)
+    def forward(self, x, labels=None, prenormed: bool = False, norm_only: bool = False):
+        """``prenormed``: ``x`` already went through a final norm of its own (multi-token-prediction block);
+        ``norm_only``: return the normalised hidden states instead of logits / loss."""
+        h = x if prenormed else self.norm(x)
+        if norm_only:
+            return h
         if labels is None:
             return ops.linear(h, self.weight)
         return ops.linear_cross_entropy(h, self.weight, labels)

@@ -56,6 +56,8 @@ class Qwen35TextConfig(MoETextConfig, GDNTextConfig):
     attn_output_gate: bool = True
     num_experts: int = 0                       # 0: dense SwiGLU FFN
     shared_expert_intermediate_size: int = 0
+    mtp_num_layers: int = 0                    # multi-token prediction: extra full-attention layer(s) predicting token t + 2
+    mtp_loss_scaling_factor: float = 0.1
 
     def layer_is_linear(self, i: int) -> bool:
         return (i + 1) % self.full_attention_interval != 0
@@ -283,6 +285,33 @@ class Qwen35DecoderLayer(nn.Module):
         return x + self.down_proj(ops.linear_swiglu(h, self.gate_up_proj.weight))
 
 
+class MultiTokenPrediction(nn.Module):
+    """Multi-token-prediction block (mindspeed_mm/fsdp/models/mtp.py:41-171): for every depth d, the embedding of the
+    token one step further and the current hidden state are normalised, concatenated, projected back to the hidden size
+    and passed through a full-attention decoder layer; the model's own output head scores the result against the labels
+    shifted one more step.  Returns the normalised hidden states of each depth."""
+
+    def __init__(self, c: Qwen35TextConfig, num_local: Optional[int] = None):
+        super().__init__()
+        self.layers = nn.ModuleList([Qwen35DecoderLayer(c, False, num_local) for _ in range(c.mtp_num_layers)])
+        self.pre_fc_norm_embedding = RMSNorm(c.hidden_size, c.rms_norm_eps)
+        self.pre_fc_norm_hidden = RMSNorm(c.hidden_size, c.rms_norm_eps)
+        self.fc = Linear(2 * c.hidden_size, c.hidden_size, bias=False)
+        self.norm = RMSNorm(c.hidden_size, c.rms_norm_eps)
+
+    def forward(self, hidden, embeds, depth, cos, sin, cu_seqlens, max_seqlen):
+        h = self.fc(torch.cat([self.pre_fc_norm_embedding(embeds), self.pre_fc_norm_hidden(hidden)], dim=-1))
+        return self.norm(self.layers[depth](h, cos, sin, cu_seqlens, max_seqlen))
+
+
+def shift_in_sequences(x: torch.Tensor, cu_seqlens: torch.Tensor, fill) -> torch.Tensor:
+    """``out[t] = x[t + 1]`` inside each packed sequence; the last token of every sequence gets ``fill``."""
+    out = torch.cat([x[1:], x.new_full((1,), fill)])
+    last = cu_seqlens[1:].long() - 1
+    out[last[last >= 0]] = fill
+    return out
+
+
 @model_register.register("qwen3_5")
 @model_register.register("qwen3_5_moe")
 class Qwen35Model(nn.Module):
@@ -300,6 +329,8 @@ class Qwen35Model(nn.Module):
         self.layers = nn.ModuleList([Qwen35DecoderLayer(t, t.layer_is_linear(i), t.num_experts // ep if t.num_experts else None)
                                      for i in range(t.num_layers)])
         self.lm_head = LMHead(t)
+        self.mtp = MultiTokenPrediction(t, t.num_experts // ep if t.num_experts else None) if t.mtp_num_layers else None
+        self.last_mtp_losses = None        # per-depth mean losses of the last forward (detached), for the log
         blocks = [m for m in self.modules() if isinstance(m, SparseMoeBlock)]
         for b in blocks:                    # model-level auxiliary term = coef * mean over MoE layers
             b.aux_scale = t.router_aux_loss_coef / len(blocks)
@@ -325,10 +356,15 @@ class Qwen35Model(nn.Module):
         units += [("visual.merger", v.merger)]
         units += [(f"layers.{i}", l) for i, l in enumerate(self.layers)]
         units += [("lm_head", self.lm_head)]
+        if self.mtp is not None:
+            units += [("mtp", self.mtp)]
         return units
 
     def expert_units(self):
-        return [(f"layers.{i}.mlp.routed.experts", l.mlp.experts) for i, l in enumerate(self.layers) if l.sparse]
+        out = [(f"layers.{i}.mlp.routed.experts", l.mlp.experts) for i, l in enumerate(self.layers) if l.sparse]
+        if self.mtp is not None:
+            out += [(f"mtp.layers.{i}.mlp.routed.experts", l.mlp.experts) for i, l in enumerate(self.mtp.layers) if l.sparse]
+        return out
 
     def aux_loss(self):
         """Value of the router load-balancing term of the last forward (detached: its gradient is attached inside the
@@ -365,4 +401,21 @@ class Qwen35Model(nn.Module):
                 x = run(layer, x, cos, sin, batch.get("cu_seqlens"), batch.get("max_seqlen"))
         if kv_cache is not None and batch.get("labels") is None:
             x = x[-1:]
-        return run(self.lm_head, x, batch.get("labels"))
+        labels = batch.get("labels")
+        if self.mtp is None or labels is None:
+            return run(self.lm_head, x, labels)
+        loss_sum, n = run(self.lm_head, x, labels)
+        # multi-token prediction: depth d predicts the token d + 2 steps ahead from the hidden state of the main stack (after
+        # its final norm) and the embedding of the token d + 1 steps ahead; the embedding and the head are the model's own
+        cu = batch["cu_seqlens"]
+        hidden = run(self.lm_head, x, None, False, True)      # the main stack's final norm lives in the output-head unit
+        ids_d, labels_d, extra, self.last_mtp_losses = ids, labels, 0.0, []
+        for d in range(t.mtp_num_layers):
+            ids_d, labels_d = shift_in_sequences(ids_d, cu, 0), shift_in_sequences(labels_d, cu, -100)
+            hidden = run(self.mtp, hidden, run(self.embed_tokens, ids_d), d, cos, sin, cu, batch["max_seqlen"])
+            ls, nd = run(self.lm_head, hidden, labels_d, True)
+            mean_d = ls / nd.clamp_min(1)
+            self.last_mtp_losses.append(mean_d.detach())
+            extra = extra + mean_d
+        # the caller divides by n: add scaling * mean over depths in the same units
+        return loss_sum + (t.mtp_loss_scaling_factor / t.mtp_num_layers) * extra * n, n

@@ -67,6 +67,9 @@ class OptimConfig:
     # name wins (``lr_scaling_plan`` of the reference, fsdp/optimizer/optimizer.py:310-331); recipes written against
     # Hugging Face module trees say ``model.visual...``, so the name is tried with that prefix too
     lr_scaling: Sequence[Tuple[str, float]] = ()
+    # > 0: adaptive clipping (the reference's adaptive_clip_grad_norm patch): the threshold follows an exponential moving
+    # average of the gradient norm plus three standard deviations instead of the fixed ``clip_grad``
+    clip_grad_ema_decay: float = 0.0
 
     def lr_scale_of(self, name: str) -> float:
         import re
@@ -74,6 +77,50 @@ class OptimConfig:
             if re.match(pat, name) or re.match(pat, "model." + name):
                 return float(scale)
         return 1.0
+
+
+class ExtremeGradientError(RuntimeError):
+    """Adaptive clipping met a gradient norm beyond ``max(mean + 5 sigma, 5)`` or a non-finite one: the step was not
+    applied (mindspeed_mm/patchs/adaptive_clip_grad_patch.py:228-262 stops the run the same way)."""
+
+
+class AdaptiveClip:
+    """Threshold = moving average of the unclipped gradient norms + 3 sigma.  Norms under the threshold update the average
+    and its variance and pass unclipped; norms above it (up to the extreme threshold) are scaled down to it and leave the
+    statistics alone.  First step: average = min(3 * norm, 1), variance 0, no clipping."""
+
+    def __init__(self, decay: float):
+        self.decay, self.avg, self.var = decay, None, 0.0
+        self.threshold = self.coef = None
+
+    def scale_for(self, norm: float) -> float:
+        import math
+        if not math.isfinite(norm):
+            raise ExtremeGradientError(f"gradient norm is {norm}")
+        if self.avg is None:
+            self.avg, self.var = min(3.0 * norm, 1.0), 0.0
+            self.threshold, self.coef = self.avg, 1.0
+            return 1.0
+        thr = self.avg + 3.0 * self.var ** 0.5
+        extreme = max(self.avg + 5.0 * self.var ** 0.5, 5.0)
+        self.threshold = thr
+        if norm <= thr:
+            d = self.decay
+            self.avg = d * self.avg + (1 - d) * norm
+            self.var = d * self.var + (1 - d) * (self.avg - norm) ** 2
+            self.coef = 1.0
+        elif norm <= extreme:
+            self.coef = thr / norm
+        else:
+            raise ExtremeGradientError(f"gradient norm {norm:.4g} is beyond the extreme threshold {extreme:.4g} "
+                                       f"(moving average {self.avg:.4g}, variance {self.var:.4g})")
+        return self.coef
+
+    def state_dict(self):
+        return dict(avg=self.avg, var=self.var)
+
+    def load_state_dict(self, sd):
+        self.avg, self.var = sd["avg"], sd["var"]
 
 
 class FlatGroup:
@@ -221,6 +268,11 @@ class Unit:
         self.bwd_done = False          # backward of the current micro-step has run
         self.recompute = True          # False: keep the autograd graph (used for the loss head)
         self.pending_reduce = False    # non-recompute unit whose gradients wait to be reduced
+        # a unit may run more than once per micro-batch (an embedding or output head shared with a multi-token-prediction
+        # block): its gradients are reduced after the LAST of its backward passes
+        self.uses = 0                  # differentiated forward calls in this micro-batch
+        self.bwd_uses = 0              # backward passes seen so far
+        self.hooks = 0                 # completion hooks registered (graph-keeping units with a differentiable input)
 
     @property
     def trainable(self):
@@ -269,8 +321,9 @@ class FSDPEngine:
         self.micro_step = 0
         self.lr = self.opt.lr
         # replicas and host-resident optimizer state both need the reduced gradient shard before the update runs
+        self.adaptive_clip = AdaptiveClip(self.opt.clip_grad_ema_decay) if self.opt.clip_grad_ema_decay > 0 else None
         self.deferred = self.opt.clip_grad > 0 or grad_accum_steps > 1 or self.replicas > 1 or offload_optimizer or \
-            self.opt.kind == "muon"
+            self.opt.kind == "muon" or self.adaptive_clip is not None
         self._sq_norm = torch.zeros((), dtype=torch.float32, device=self.device)
         self._dummy = torch.zeros((), device=self.device, requires_grad=True)
         self.comm = comm
@@ -364,6 +417,7 @@ class FSDPEngine:
             out = module(*args, **kwargs)
             self.reshard(u)
             return out
+        u.uses += 1
         if not u.recompute:
             # Plain autograd through the unit (its graph is kept).  Its gradients are complete once any
             # earlier unit starts its backward (or at finish_step), which is where they are reduced.
@@ -430,16 +484,23 @@ class FSDPEngine:
         ``flush_pending``.  Units without a differentiable input are reduced by ``flush_pending`` only."""
         for t in list(args) + list(kwargs.values()):
             if isinstance(t, torch.Tensor) and t.requires_grad:
+                u.hooks += 1
                 t.register_hook(lambda g, u=u: self._unit_backward_done(u))
                 return
 
     def _offer_buffers(self, u: Unit) -> None:
+        if u.bwd_uses:                 # a later use of a shared unit: its gradients accumulate into the buffers already offered
+            return
         u._offered = {id(g): g.offer_grad_buffer() for g in u.groups if g.trainable}
 
     def _unit_backward_done(self, u: Unit) -> None:
-        prev, self._done_wait = getattr(self, "_done_wait", None), u
+        u.bwd_uses += 1
+        prev = getattr(self, "_done_wait", None)
         if prev is not None and prev is not u and prev.pending_reduce:
             self._reduce_pending(prev)
+            self._done_wait = None
+        if u.bwd_uses >= u.hooks:          # every differentiated call of the unit has finished its backward
+            self._done_wait = u
 
     def _reduce_pending(self, u: Unit) -> None:
         u.pending_reduce = False
@@ -454,7 +515,7 @@ class FSDPEngine:
         pos = self._exec_pos if self._order_known else {id(u): i for i, u in enumerate(self.units)}
         lo = pos.get(id(after), -1) if after is not None else -1
         for u in self.units:
-            if u.pending_reduce and pos.get(id(u), 1 << 30) > lo:
+            if u.pending_reduce and pos.get(id(u), 1 << 30) > lo and (after is None or u.bwd_uses >= u.hooks):
                 self._reduce_pending(u)
         if after is None:
             self._done_wait = None
@@ -598,12 +659,20 @@ class FSDPEngine:
             if self.replicas > 1:       # HSDP: sum the shard over the replicas (the 1/N of all data ranks is in grad_divide)
                 for g in groups:
                     dist.all_reduce(g.grad32, group=self.replicate_group)
-            if self.opt.clip_grad > 0:
+            if self.opt.clip_grad > 0 or self.adaptive_clip is not None:
                 sq = torch.stack([g.grad32.float().pow(2).sum() for g in groups]).sum()
                 if self.world > 1:
                     dist.all_reduce(sq, group=self.group)
                 norm = sq.sqrt() / self.grad_accum_steps      # norm of the micro-batch-averaged gradient
-                scale = torch.clamp(self.opt.clip_grad / (norm + 1e-6), max=1.0)
+                if self.adaptive_clip is not None:
+                    try:
+                        scale = self.adaptive_clip.scale_for(float(norm))     # the norm is the same on every rank
+                    except ExtremeGradientError:
+                        for g in groups:                                       # the step is not applied
+                            g.grad32 = None
+                        raise
+                else:
+                    scale = torch.clamp(self.opt.clip_grad / (norm + 1e-6), max=1.0)
             if self.grad_accum_steps > 1:
                 scale = scale / self.grad_accum_steps
             for g in groups:
@@ -641,6 +710,7 @@ class FSDPEngine:
         self._seal_order()
         for u in self.units:
             u.bwd_done = False
+            u.uses = u.bwd_uses = u.hooks = 0
             self.reshard(u, force=True)       # anything a prefetch gathered but nobody consumed, and the root units
         self.micro_step += 1
 
@@ -806,11 +876,13 @@ class _UnitFn(torch.autograd.Function):
     def backward(ctx, *gouts):
         engine, u = ctx.engine, ctx.u
         tensors = [t.detach().requires_grad_(need) for t, need in zip(ctx.saved_tensors, ctx.needs)]
+        u.bwd_uses += 1
+        last = u.bwd_uses >= u.uses            # the unit ran more than once: reduce after its last backward
         engine.flush_pending(after=u)
         engine.unshard(u)
         engine.wait_unshard(u)
         engine._prefetch_backward(u)
-        if u.trainable and engine.cuda:
+        if u.trainable and engine.cuda and u.bwd_uses == 1:
             # with peer-memory collectives the buffer is the next gradient slot of the symmetric arena
             u._offered = {id(g): g.offer_grad_buffer(engine._p2p.grad_slot(g) if engine._p2p is not None else None)
                           for g in u.groups if g.trainable}
@@ -823,10 +895,10 @@ class _UnitFn(torch.autograd.Function):
                  if isinstance(o, torch.Tensor) and o.requires_grad and g is not None]
         if pairs:
             torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
-        if u.trainable:
+        if u.trainable and last:
             engine.reduce_and_update(u)
         engine.reshard(u)
-        u.bwd_done = True
+        u.bwd_done = last
         grads = [t.grad if need else None for t, need in zip(tensors, ctx.needs)]
         return (None, None, None, None, *grads)
 

@@ -187,8 +187,13 @@ def pretrain(kind: str, argv=None, device: Optional[str] = None):
                              ring_attention_size=cp // uly,
                              fully_shard_parallel_size=(int(shard) // cp if shard else "auto"))
     model = model_provider(kind, args)
+    # model.json "patch" block of the reference (mindspeed_mm/patchs/patch_manager.py): the entries that change training
+    patch = (args.mm.model.to_dict().get("patch") or {}) if hasattr(args.mm, "model") else {}
+    acg = patch.get("adaptive_clip_grad_norm") or {}
+    ema_decay = float(acg.get("clip_grad_ema_decay", 0.99)) if (acg is True or acg) else 0.0
     opt = OptimConfig(lr=args.lr, betas=(args.adam_beta1, args.adam_beta2), eps=args.adam_eps,
-                      weight_decay=args.weight_decay, clip_grad=args.clip_grad)
+                      weight_decay=args.weight_decay, clip_grad=args.clip_grad, clip_grad_ema_decay=ema_decay,
+                      kind="muon" if (getattr(args, "optimizer", None) == "muon" or patch.get("muon_optimizer")) else "adamw")
     accum = max(1, args.global_batch_size // (args.micro_batch_size * ps.get_dp_world_size()))
     param_dtype = torch.bfloat16 if (args.bf16 and dev.type == "cuda") else torch.float32
     extra = {}

@@ -60,6 +60,7 @@ class TrainEngine:
         self.model, self.engine, self.loss_fn, self.schedule, self.cfg = model, engine, loss_fn, schedule, cfg
         self.scalar_log = scalar_log      # runtime.logging.ScalarLog (TensorBoard / W&B), rank 0 writes
         self._aux = []                    # MoE load-balancing terms of the current step's micro-batches
+        self._mtp = []                    # multi-token-prediction losses [depths] of the current step's micro-batches
         self.ema = ema            # runtime.ema.ShardedEMA: updated after every optimizer step, saved with the per-rank state
         self.data_iter, self.val_iter_fn = data_iter, val_iter_fn
         self.checkpointer, self.profiler, self.memory_profiler, self.watchdog = \
@@ -99,6 +100,9 @@ class TrainEngine:
         aux = aux_fn() if callable(aux_fn) else None
         if aux is not None:
             self._aux.append(aux.detach())
+        mtp = getattr(self.model, "last_mtp_losses", None)      # per-depth multi-token-prediction losses of this micro-batch
+        if mtp:
+            self._mtp.append(torch.stack(list(mtp)).float())
         self.engine.end_micro_step()
         return dict(loss=loss.detach(), n_valid=n_valid)
 
@@ -126,9 +130,16 @@ class TrainEngine:
             if self.dp_world > 1:
                 dist.all_reduce(aux, group=self.dp_group)
                 aux = aux / self.dp_world
+        mtp = None
+        if self._mtp:                       # tracker of the multi-token-prediction losses, one value per depth
+            mtp = torch.stack(self._mtp).mean(0)
+            self._mtp = []
+            if self.dp_world > 1:
+                dist.all_reduce(mtp, group=self.dp_group)
+                mtp = mtp / self.dp_world
         self.iteration += 1
         self.consumed_train_samples += self.cfg.global_batch_size
-        return dict(loss=loss, grad_norm=grad_norm, tokens=tokens, aux_loss=aux)
+        return dict(loss=loss, grad_norm=grad_norm, tokens=tokens, aux_loss=aux, mtp_losses=mtp)
 
     # ---------------------------------------------------------------------------------- loop
     def _sync(self):
@@ -181,10 +192,14 @@ class TrainEngine:
                            grad_norm=None if r["grad_norm"] is None else float(r["grad_norm"]))
                 if r.get("aux_loss") is not None:
                     rec["load_balancing_loss"] = float(r["aux_loss"])
+                if r.get("mtp_losses") is not None:
+                    for d, v in enumerate(r["mtp_losses"].tolist()):
+                        rec[f"mtp_{d + 1} loss"] = v
                 self.history.append(rec)
                 if self.scalar_log is not None and self.scalar_log.active:
                     sc = {"lm loss": loss, "learning-rate": lr, "grad-norm": rec["grad_norm"], "batch-size": cfg.global_batch_size,
                           "iteration-time": dt, "load_balancing_loss": rec.get("load_balancing_loss")}
+                    sc.update({k: v for k, v in rec.items() if k.startswith("mtp_")})
                     if self.device.type == "cuda":
                         ms = torch.cuda.memory_stats(self.device)
                         sc.update({"mem-reserved-bytes": ms["reserved_bytes.all.current"],
@@ -195,8 +210,8 @@ class TrainEngine:
                         if cfg.log_tps and r["tokens"] else None
                     print_rank0(format_training_log(self.iteration, cfg.train_iters, self.consumed_train_samples, dt,
                                                     lr, cfg.global_batch_size,
-                                                    {"loss": loss, **({"load_balancing_loss": rec["load_balancing_loss"]}
-                                                                      if "load_balancing_loss" in rec else {})},
+                                                    {"loss": loss, **{k: v for k, v in rec.items()
+                                                                      if k == "load_balancing_loss" or k.startswith("mtp_")}},
                                                     rec["grad_norm"], tps,
                                                     skipped=self.skipped_iters, nan_iters=self.nan_iters))
                 if self.iteration == cfg.report_memory_at:

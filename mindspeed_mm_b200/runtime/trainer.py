@@ -114,7 +114,8 @@ class Trainer:
     def build_engine(self) -> FSDPEngine:
         a, t, plan = self.args, self.args.training, self.args.parallel.fsdp_plan
         opt = OptimConfig(lr=t.lr, betas=(t.adam_beta1, t.adam_beta2), eps=t.adam_eps, weight_decay=t.weight_decay,
-                          clip_grad=t.clip_grad, kind="muon" if t.optimizer == "muon" else "adamw",
+                          clip_grad=t.clip_grad, clip_grad_ema_decay=t.clip_grad_ema_decay,
+                          kind="muon" if t.optimizer == "muon" else "adamw",
                           muon_momentum=t.muon_momentum, ns_steps=t.ns_steps, matched_adamw_rms=t.matched_adamw_rms,
                           lr_scaling=tuple((p.match, p.scale) for p in (t.lr_scaling_plan or ())))
         if t.no_decay_params or t.no_decay_modules:

@@ -169,3 +169,42 @@ def test_lr_scaling_groups_split_a_unit():
     assert sorted(g.lr_scale for g in eng.units[0].groups) == [0.0, 1.0]
     assert torch.equal(after["net.0.weight"], before["net.0.weight"])            # multiplier 0: frozen in place
     assert not torch.equal(after["net.1.weight"], before["net.1.weight"])
+
+
+def test_adaptive_clip_follows_the_norm_and_clips_outliers():
+    from mindspeed_mm_b200.parallel.fsdp import AdaptiveClip, ExtremeGradientError, FSDPEngine, OptimConfig
+    ac = AdaptiveClip(0.9)
+    assert ac.scale_for(0.2) == 1.0 and abs(ac.avg - 0.6) < 1e-9            # first step: min(3 * norm, 1), no clipping
+    for n in (0.5, 0.55, 0.45, 0.5):
+        assert ac.scale_for(n) == 1.0                                       # inside mean + 3 sigma: statistics move
+    avg, var = ac.avg, ac.var
+    thr = avg + 3 * var ** 0.5
+    s = ac.scale_for(thr * 1.5)                                             # outlier: scaled down to the threshold ...
+    assert abs(s - 1 / 1.5) < 1e-9 and (ac.avg, ac.var) == (avg, var)      # ... and the statistics stay
+    try:
+        ac.scale_for(50.0)
+        raise AssertionError("an extreme norm must stop the step")
+    except ExtremeGradientError:
+        pass
+    # in the engine: a huge gradient after calm steps is not applied
+    with torch.device("meta"):
+        net = torch.nn.Linear(8, 8)
+    eng = FSDPEngine([("", net)], group=False, device="cpu", param_dtype=torch.float32, no_recompute=(),
+                     opt=OptimConfig(lr=0.01, clip_grad_ema_decay=0.9))
+    eng.materialize(lambda name, mod: [torch.nn.init.normal_(p, std=0.3) for p in mod.parameters()])
+    x = torch.randn(4, 8)
+    for _ in range(3):
+        eng.set_lr(0.01)
+        eng.run(net, x).pow(2).mean().backward()
+        eng.end_micro_step()
+        eng.finish_step()
+    before = {k: v.clone() for k, v in eng.named_full_params()}
+    (eng.run(net, x).pow(2).mean() * 1e4).backward()
+    eng.end_micro_step()
+    try:
+        eng.finish_step()
+        raise AssertionError("expected ExtremeGradientError")
+    except ExtremeGradientError:
+        pass
+    after = dict(eng.named_full_params())
+    assert all(torch.equal(before[k], after[k]) for k in before)

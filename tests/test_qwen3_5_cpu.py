@@ -86,3 +86,50 @@ def test_from_hf_config():
     t = cfg.text
     assert (t.num_layers, t.full_attention_interval, t.num_experts, t.shared_expert_intermediate_size) == (4, 4, 8, 128)
     assert t.partial_rotary_factor == 0.25 and tuple(t.mrope_section) == (3, 3, 2) and cfg.vision.deepstack_visual_indexes == ()
+
+
+def test_multi_token_prediction_loss_and_shared_units_under_the_engine():
+    """mtp_num_layers = 1: the extra loss equals the hand-computed one (next-next token, inside each packed sequence), and
+    under the sharding engine (embedding and output head run twice per step, reduced after their last backward) the
+    updated weights equal those of plain autograd + the same AdamW."""
+    from mindspeed_mm_b200.parallel.fsdp import FSDPEngine, OptimConfig
+    from mindspeed_mm_b200.models.qwen3_5 import shift_in_sequences
+    cfg = Qwen35Config.tiny()
+    cfg.text.mtp_num_layers, cfg.text.num_layers, cfg.vision.depth = 1, 4, 1
+    torch.manual_seed(0)
+    ref = Qwen35Model(cfg, ep_size=1).float()
+    ref.init_weights(1)
+    ids = torch.randint(0, 30000, (50,))
+    cu = torch.tensor([0, 20, 50], dtype=torch.int32)
+    labels = shift_in_sequences(ids, cu, -100)
+    assert labels[19] == -100 and labels[49] == -100 and labels[0] == ids[1]
+    pos = torch.cat([torch.arange(20), torch.arange(30)]).expand(3, -1)
+    batch = dict(input_ids=ids, labels=labels, position_ids=pos, cu_seqlens=cu, max_seqlen=30)
+    loss_sum, n = ref(batch)
+    main = float(loss_sum / n) - 0.1 * float(ref.last_mtp_losses[0])
+    cfg0 = Qwen35Config.tiny()
+    cfg0.text.num_layers, cfg0.vision.depth = 4, 1
+    plain = Qwen35Model(cfg0, ep_size=1).float()
+    plain.load_state_dict({k: v for k, v in ref.state_dict().items() if not k.startswith("mtp.")})
+    ls0, n0 = plain(batch)
+    assert abs(main - float(ls0 / n0)) < 1e-5 and float(ref.last_mtp_losses[0]) > 5.0
+    # engine run vs plain autograd
+    with torch.device("meta"):
+        net = Qwen35Model(cfg, ep_size=1)
+    eng = FSDPEngine(net.fsdp_units(), group=False, device="cpu", param_dtype=torch.float32, opt=OptimConfig(lr=1e-3))
+    src = dict(ref.named_parameters())
+    eng.materialize(lambda name, mod: [p.data.copy_(src[(name + "." if name else "") + k]) for k, p in mod.named_parameters()])
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, weight_decay=0.0)
+    for _ in range(2):
+        opt.zero_grad()
+        ls, nn_ = ref(batch)
+        (ls / nn_).backward()
+        opt.step()
+        eng.set_lr(1e-3)
+        ls, nn_ = net(batch, run=eng.run)
+        (ls / nn_).backward()
+        eng.end_micro_step()
+        eng.finish_step()
+    got = dict(eng.named_full_params())
+    for k, p in ref.named_parameters():
+        assert torch.allclose(got[k], p, atol=2e-5), (k, float((got[k] - p).abs().max()))

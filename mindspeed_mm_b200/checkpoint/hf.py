@@ -357,6 +357,8 @@ def load_hf_into_engine(engine, path: str, ops: List[Operator], strict: bool = T
 
     def getter(name, shape):
         t = sd.get(name)
+        if t is None and ".base." in name:          # a LoRA-wrapped linear keeps the checkpoint's weight as its frozen base
+            t = sd.get(name.replace(".base.", "."))
         if t is None:
             return None
         if tuple(t.shape) != tuple(shape):

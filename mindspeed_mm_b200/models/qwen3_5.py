@@ -175,7 +175,7 @@ class GatedDeltaNet(nn.Module):
         beta = torch.sigmoid(b.float())
         g = -torch.exp(self.A_log.float()) * F.softplus(a.float() + self.dt_bias.float())
         o = ops.gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk=self.c.gdn_chunk)
-        o = ops.gated_rms_norm(o.to(x.dtype), z.reshape(T, self.hv, self.dv), self.norm_weight, self.c.rms_norm_eps)
+        o = ops.gated_rms_norm(o, z.reshape(T, self.hv, self.dv), self.norm_weight, self.c.rms_norm_eps)      # fp32 in, z's dtype out
         return self.out_proj(o.reshape(T, self.value_dim))
 
 

@@ -149,11 +149,13 @@ def l2_norm(x, eps: float = 1e-6):
 
 
 def gated_rms_norm(x, z, weight, eps: float = 1e-6):
-    if (_native(x) and x.dtype == torch.float32 and z.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
-            and x.shape[-1] <= 256 and not torch.is_grad_enabled()):
-        return _nat().gated_rms_norm_fwd(x, z, weight, eps)
-    _fallback("gated_rms_norm", x, "training pass or unsupported dtype")
-    return ref.gated_rms_norm(x, z, weight, eps)
+    """``rmsnorm(x) * weight * silu(z)`` over the last dim, in ``z``'s dtype (``x`` may be the fp32 output of the delta rule)."""
+    D = x.shape[-1]
+    if (_native(x) and x.dtype in (torch.float32, torch.bfloat16) and z.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and D <= 256 and D % 8 == 0):
+        return _nat().gated_rms_norm(x, z, weight, eps)
+    _fallback("gated_rms_norm", x, f"x {x.dtype} z {z.dtype} D={D}")
+    return ref.gated_rms_norm(x, z, weight, eps).to(z.dtype)
 
 
 # --------------------------------------------------------------------------- GEMM

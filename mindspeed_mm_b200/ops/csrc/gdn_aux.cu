@@ -1,6 +1,6 @@
 // Auxiliary kernels of the gated-delta-net layer on packed sequences:
 //   causal_conv1d (depthwise, kernel <= 8, optional SiLU, restarts at every sequence boundary) forward and backward,
-//   l2norm over the head dim (forward and backward), gated RMSNorm  y = rmsnorm(x) * w * silu(z)  (forward).
+//   l2norm over the head dim (forward and backward; the gated RMSNorm of the layer's output lives in rownorm.cu).
 // x is [T, D] bf16 with the channel dim contiguous: a thread owns 8 channels (16 bytes) and walks a strip of
 // tokens keeping the last K-1 inputs in registers, so every input is read once.
 #include "common.cuh"
@@ -215,26 +215,6 @@ __global__ void l2norm_bwd_kernel(const bf16* __restrict__ y, const bf16* __rest
     for (int i = lane; i < D; i += 32) dx[row * D + i] = __float2bfloat16(r * (gv[i >> 5] - yv[i >> 5] * dot));
 }
 
-// ---- gated RMSNorm forward: y = x * rsqrt(mean(x^2) + eps) * w * silu(z)   (rows of D <= 256)
-__global__ void gated_rmsnorm_fwd_kernel(const float* __restrict__ x, const bf16* __restrict__ z, const bf16* __restrict__ w,
-                                         bf16* __restrict__ y, long long rows, int D, float eps) {
-    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= rows) return;
-    const int lane = threadIdx.x & 31;
-    float v[8];
-    float ss = 0.f;
-    for (int i = lane; i < D; i += 32) {
-        v[i >> 5] = x[row * D + i];
-        ss += v[i >> 5] * v[i >> 5];
-    }
-    ss = warp_sum(ss);
-    const float r = rsqrtf(ss / (float)D + eps);
-    for (int i = lane; i < D; i += 32) {
-        const float zz = __bfloat162float(z[row * D + i]);
-        y[row * D + i] = __float2bfloat16(v[i >> 5] * r * __bfloat162float(w[i]) * zz / (1.f + __expf(-zz)));
-    }
-}
-
 }  // namespace
 
 #define MM_CONV_K(MACRO)                  \
@@ -289,9 +269,3 @@ MM_API int mm_l2norm_bwd(const void* y, const void* dy, const float* rnorm, void
     return (int)cudaGetLastError();
 }
 
-MM_API int mm_gated_rmsnorm_fwd(const float* x, const void* z, const void* w, void* y, long long rows, int D, float eps,
-                                cudaStream_t st) {
-    if (D > 256) return -1;
-    gated_rmsnorm_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(x, (const bf16*)z, (const bf16*)w, (bf16*)y, rows, D, eps);
-    return (int)cudaGetLastError();
-}

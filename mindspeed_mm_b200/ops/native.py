@@ -50,6 +50,8 @@ def _declare(L):
         "mm_rownorm_rms_fwd": [_p, _p, _p, _p, _ll, _i, _f, _p],
         "mm_rownorm_ln_mod_fwd": [_p, _p, _p, _p, _p, _p, _ll, _i, _i, _f, _p],
         "mm_rownorm_l2_fwd": [_p, _p, _p, _ll, _i, _f, _p],
+        "mm_gated_rms_fwd": [_p, _i, _p, _p, _p, _p, _ll, _i, _f, _p],
+        "mm_gated_rms_bwd": [_p, _i, _p, _p, _p, _p, _p, _p, _p, _ll, _i, _p],
         "mm_rmsnorm_bwd_grid": [_i],
         "mm_rmsnorm_bwd": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _p],
         "mm_swiglu_fwd": [_p, _p, _ll, _i, _p],
@@ -80,7 +82,6 @@ def _declare(L):
         "mm_conv1d_bwd": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
         "mm_l2norm_fwd": [_p, _p, _p, _ll, _i, _f, _p],
         "mm_l2norm_bwd": [_p, _p, _p, _p, _ll, _i, _p],
-        "mm_gated_rmsnorm_fwd": [_p, _p, _p, _p, _ll, _i, _f, _p],
         "mm_gdn_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p, _p],
         "mm_p2p_scatter_rows": [_p, _p, _p, _p, _p, _i, _i, _i, _p],
         "mm_p2p_gather_rows": [_p, _p, _p, _p, _i, _i, _i, _p],
@@ -888,15 +889,37 @@ def l2_norm(x, eps=1e-6):
     return _L2Norm.apply(x, eps)
 
 
-def gated_rms_norm_fwd(x_f32, z, w, eps=1e-6):
-    """Inference-only fused ``rmsnorm(x) * w * silu(z)`` on an fp32 ``x`` (the delta-rule output)."""
-    D = x_f32.shape[-1]
-    x2 = x_f32.reshape(-1, D).contiguous()
-    z2 = z.reshape(-1, D).contiguous()
-    y = torch.empty(x2.shape, dtype=torch.bfloat16, device=x2.device)
-    _check(lib().mm_gated_rmsnorm_fwd(x2.data_ptr(), z2.data_ptr(), w.contiguous().data_ptr(), y.data_ptr(), x2.shape[0], D,
-                                      eps, _st()), "gated_rmsnorm_fwd")
-    return y.view(x_f32.shape)
+class _GatedRMSNorm(torch.autograd.Function):
+    """``rmsnorm(x) * w * silu(z)`` over the last dim (<= 256): x fp32 or bf16, z / w / result bf16."""
+
+    @staticmethod
+    def forward(ctx, x, z, w, eps):
+        D = x.shape[-1]
+        x2, z2, wc = x.reshape(-1, D).contiguous(), z.reshape(-1, D).contiguous(), w.contiguous()
+        rows = x2.shape[0]
+        y = torch.empty(rows, D, dtype=torch.bfloat16, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        _check(lib().mm_gated_rms_fwd(x2.data_ptr(), int(x2.dtype == torch.float32), z2.data_ptr(), wc.data_ptr(), y.data_ptr(),
+                                      rstd.data_ptr(), rows, D, eps, _st()), "gated_rms_fwd")
+        ctx.save_for_backward(x2, z2, wc, rstd)
+        ctx.shapes = (x.shape, z.shape)
+        return y.view(z.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, z2, wc, rstd = ctx.saved_tensors
+        rows, D = x2.shape
+        dy2 = dy.reshape(rows, D).contiguous()
+        dx, dz = torch.empty_like(x2), torch.empty_like(z2)
+        dw = torch.zeros(D, dtype=torch.float32, device=x2.device)
+        _check(lib().mm_gated_rms_bwd(x2.data_ptr(), int(x2.dtype == torch.float32), z2.data_ptr(), wc.data_ptr(), dy2.data_ptr(),
+                                      rstd.data_ptr(), dx.data_ptr(), dz.data_ptr(), dw.data_ptr(), rows, D, _st()),
+               "gated_rms_bwd")
+        return dx.view(ctx.shapes[0]), dz.view(ctx.shapes[1]), dw.to(wc.dtype), None
+
+
+def gated_rms_norm(x, z, w, eps=1e-6):
+    return _GatedRMSNorm.apply(x, z, w, eps)
 
 
 def gdn_supported(q, v, chunk) -> bool:

@@ -238,7 +238,12 @@ class Trainer:
         if path and (fmt == "hf" or (fmt == "auto" and hfio.is_hf_checkpoint(path))):
             ops = self.hf_ops()
             if ops is not None:
-                hfio.load_hf_into_engine(self.engine, path, ops, strict=t.load_strict)
+                hfio.load_hf_into_engine(self.engine, path, ops, strict=t.load_strict and not t.lora.enable)
+        if t.lora.enable and t.lora.pretrained_lora_path:          # adapter files in PEFT's layout
+            from safetensors.torch import load_file
+            from ..tasks.lora import from_peft_state
+            ad = from_peft_state(load_file(os.path.join(t.lora.pretrained_lora_path, "adapter_model.safetensors")), self.hf_ops())
+            self.engine.load_full_params(lambda name, shape: ad[name].to(self.device) if name in ad else None)
 
     def build_data(self):
         from ..data import build_dataloader
@@ -247,7 +252,13 @@ class Trainer:
     def train(self):
         hist = self.train_engine.train()
         t = self.args.training
-        ops = self.hf_ops() if (t.save and t.save_format == "hf") else None
+        if t.lora.enable and t.save and self.hf_ops() is not None:       # adapter-only files in PEFT's layout
+            from ..tasks.lora import lora_state_dict, save_peft_adapter
+            state = lora_state_dict(self.engine.named_full_params())    # every rank takes part in the gathers
+            if self.rank == 0:
+                save_peft_adapter(state, self.hf_ops(), os.path.join(t.save, "lora_adapter"), t.lora,
+                                  self.args.model.model_name_or_path or "")
+        ops = self.hf_ops() if (t.save and t.save_format == "hf" and not t.lora.enable) else None
         if ops is not None:
             if self.train_engine.ema is not None:          # export the averaged weights, then put the live ones back
                 self.train_engine.ema.swap()

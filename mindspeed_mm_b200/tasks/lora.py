@@ -51,8 +51,8 @@ class LoRALinear(nn.Module):
             self.lora_A.uniform_(-bound, bound)
             self.lora_B.zero_()
 
-    def forward(self, x):
-        y = self.base(x)
+    def forward(self, x, value_unused_in_backward: bool = False):
+        y = self.base(x)                 # the adapter's sum needs the base value: never skipped in a recompute
         z = torch.nn.functional.linear(torch.nn.functional.linear(self.dropout(x), self.lora_A.to(x.dtype)), self.lora_B.to(x.dtype))
         return y + self.scaling * z
 
@@ -105,4 +105,63 @@ def merge_lora(state: Dict[str, torch.Tensor], scaling: float) -> Dict[str, torc
             out[nk] = v
         else:
             out[k] = v
+    return out
+
+
+# ------------------------------------------------------------------------------------------ PEFT adapter files
+def to_peft_state(state: Dict[str, torch.Tensor], hf_ops) -> Dict[str, torch.Tensor]:
+    """Adapter tensors under PEFT's names (``base_model.model.<hf module>.lora_A.weight`` / ``lora_B.weight``).
+
+    ``state``: ``lora_state_dict`` output (internal names).  ``hf_ops``: the model's internal <-> Hugging Face operator list.
+    An adapter on a fused projection (q|k|v, gate|up) is written as one adapter per Hugging Face part: every part gets the
+    fused ``lora_A`` and its own rows of ``lora_B``, which is the same update."""
+    from ..checkpoint import hf as hfio
+    out: Dict[str, torch.Tensor] = {}
+    for k, b in state.items():
+        if not k.endswith(".lora_B"):
+            continue
+        stem = k[:-len(".lora_B")]
+        a = state[stem + ".lora_A"]
+        parts = hfio.to_hf({stem + ".weight": b.clone()}, hf_ops)          # rows of B follow the rows of the weight
+        for name, bp in parts.items():
+            mod = name[:-len(".weight")]
+            out[f"base_model.model.{mod}.lora_A.weight"] = a.clone()
+            out[f"base_model.model.{mod}.lora_B.weight"] = bp.contiguous()
+    return out
+
+
+def save_peft_adapter(state: Dict[str, torch.Tensor], hf_ops, out_dir: str, cfg, base_model: str = "") -> None:
+    """``adapter_model.safetensors`` + ``adapter_config.json`` as PEFT writes them (the reference's LoRA-only saving,
+    mindspeed_mm/fsdp/utils/lora_weight_manager.py:46)."""
+    import json
+    import os
+    from safetensors.torch import save_file
+    os.makedirs(out_dir, exist_ok=True)
+    peft = to_peft_state(state, hf_ops)
+    save_file(peft, os.path.join(out_dir, "adapter_model.safetensors"), metadata={"format": "pt"})
+    targets = sorted({k.split(".")[-3] for k in peft})
+    with open(os.path.join(out_dir, "adapter_config.json"), "w") as f:
+        json.dump({"peft_type": "LORA", "task_type": "CAUSAL_LM", "r": int(cfg.rank), "lora_alpha": float(cfg.alpha),
+                   "lora_dropout": float(getattr(cfg, "dropout", 0.0)), "target_modules": targets, "bias": "none",
+                   "fan_in_fan_out": False, "inference_mode": True, "base_model_name_or_path": base_model}, f, indent=1)
+
+
+def from_peft_state(peft: Dict[str, torch.Tensor], hf_ops) -> Dict[str, torch.Tensor]:
+    """Inverse of ``to_peft_state``.  Parts of a fused projection must share ``lora_A`` (as adapters written by
+    ``save_peft_adapter`` do); independently trained part adapters would need a fused rank of the parts' sum and are
+    refused with the reason."""
+    from ..checkpoint import hf as hfio
+    pre = "base_model.model."
+    b_hf = {k[len(pre):-len(".lora_B.weight")] + ".weight": v for k, v in peft.items() if k.endswith(".lora_B.weight")}
+    a_hf = {k[len(pre):-len(".lora_A.weight")] + ".weight": v for k, v in peft.items() if k.endswith(".lora_A.weight")}
+    internal_b = hfio.to_internal(b_hf, hf_ops)
+    internal_a = hfio.to_internal(a_hf, hf_ops)        # the same renames / merges: fused modules get their parts' A stacked
+    out: Dict[str, torch.Tensor] = {}
+    for name, b in internal_b.items():
+        stem, r = name[:-len(".weight")], b.shape[1]
+        parts = internal_a[name].split(r, dim=0)
+        if any(not torch.equal(parts[0], p) for p in parts[1:]):
+            raise NotImplementedError(f"{stem}: its {len(parts)} Hugging Face parts carry different lora_A; a fused adapter "
+                                      f"of rank {r * len(parts)} would be needed")
+        out[stem + ".lora_A"], out[stem + ".lora_B"] = parts[0].clone(), b
     return out

@@ -510,11 +510,27 @@ def test_l2norm_and_gated_rmsnorm():
     yr.backward(dy.float())
     _close(y, yr)
     _close(x.grad, xr.grad)
-    o = torch.randn(500, 8, 128, device=DEV)
-    z = torch.randn(500, 8, 128, device=DEV, dtype=torch.bfloat16)
-    w = (1 + 0.1 * torch.randn(128, device=DEV)).to(torch.bfloat16)
-    with torch.no_grad():
-        _close(ops.gated_rms_norm(o, z, w, 1e-6), ref.gated_rms_norm(o, z.float(), w.float(), 1e-6))
+    # gated RMSNorm, forward and backward, on the delta rule's fp32 output and on a bf16 input; a head dim that is
+    # not a power-of-two number of vectors (72) as well
+    for xdtype, D in ((torch.float32, 128), (torch.bfloat16, 128), (torch.float32, 72)):
+        o = torch.randn(501, 8, D, device=DEV).to(xdtype).requires_grad_()
+        z = torch.randn(501, 8, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+        w = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
+        gy = torch.randn(501, 8, D, device=DEV, dtype=torch.bfloat16)
+        ops.set_strict(True)
+        try:
+            y = ops.gated_rms_norm(o, z, w, 1e-6)
+            y.backward(gy)
+        finally:
+            ops.set_strict(False)
+        orf, zr, wr = (t.detach().float().requires_grad_() for t in (o, z, w))
+        yr = ref.gated_rms_norm(orf, zr, wr, 1e-6)
+        yr.backward(gy.float())
+        assert y.dtype == torch.bfloat16 and o.grad.dtype == xdtype
+        _close(y, yr)
+        _close(o.grad, orf.grad, rtol=3e-2, atol=3e-2)
+        _close(z.grad, zr.grad, rtol=3e-2, atol=3e-2)
+        _close(w.grad, wr.grad, rtol=3e-2, atol=3e-2)
 
 
 @pytest.mark.parametrize("lens,H", [([70, 200], 2), ([64], 1), ([1000, 130, 5], 4)])

@@ -164,3 +164,39 @@ def test_router_auxiliary_loss_gradient_is_attached_inside_the_blocks(monkeypatc
             assert torch.allclose(attached[k], p.grad, atol=1e-6, rtol=1e-4), k
     gate = [k for k in attached if k.endswith("mlp.gate.weight")]
     assert gate and all(attached[k].abs().max() > 0 for k in gate)
+
+
+def test_lora_finetune_from_a_transformers_checkpoint_writes_peft_files(tmp_path):
+    """LoRA on top of a transformers checkpoint through the native trainer: base weights land in the wrapped linears, only the
+    adapters train, and the run leaves adapter_model.safetensors / adapter_config.json that load back into a second run."""
+    import json
+    import os
+    from safetensors.torch import load_file
+    from mindspeed_mm_b200.config import load_config
+    from mindspeed_mm_b200.runtime.trainer import Trainer
+    hf = _hf_model(False)
+    src = tmp_path / "hf_in"
+    hf.save_pretrained(src, safe_serialization=True)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    common = ["model.model_id=qwen3_vl", f"model.model_name_or_path={src}", "parallel.expert_parallel_size=1",
+              "training.lr=1.0e-2", "training.lora.enable=true", "training.lora.rank=4", "training.lora.alpha=8",
+              "training.lora.target_modules=[q_proj,v_proj,down_proj]", "data.dataset_param.basic_parameters.seq_len=200",
+              "data.dataloader_param.pin_memory=false"]
+    tr = Trainer(load_config(os.path.join(root, "examples/qwen3vl/tiny_moe_native.yaml"),
+                             common + ["training.train_iters=2", f"training.save={tmp_path}/out"], world_size=1), device="cpu")
+    got = dict(tr.engine.named_full_params())
+    want = hfio.to_internal(hf.state_dict(), hfio.qwen3vl_ops(tr.model.config))
+    assert torch.allclose(got["layers.0.qkv_proj.base.weight"], want["layers.0.qkv_proj.weight"], atol=1e-6)
+    tr.train()
+    after = dict(tr.engine.named_full_params())
+    assert torch.equal(after["layers.0.qkv_proj.base.weight"], got["layers.0.qkv_proj.base.weight"])
+    assert after["layers.0.qkv_proj.lora_B"].abs().max() > 0
+    ad = tmp_path / "out" / "lora_adapter"
+    peft = load_file(str(ad / "adapter_model.safetensors"))
+    assert json.load(open(ad / "adapter_config.json"))["r"] == 4
+    assert "base_model.model.model.language_model.layers.0.self_attn.q_proj.lora_B.weight" in peft
+    tr2 = Trainer(load_config(os.path.join(root, "examples/qwen3vl/tiny_moe_native.yaml"),
+                              common + ["training.train_iters=1", f"training.lora.pretrained_lora_path={ad}"], world_size=1),
+                  device="cpu")
+    again = dict(tr2.engine.named_full_params())
+    assert torch.allclose(again["layers.0.qkv_proj.lora_B"], after["layers.0.qkv_proj.lora_B"])

@@ -285,3 +285,43 @@ def test_text_to_video_pipeline_over_scheduler_families():
     pipe = TextToVideoPipeline(joint, preset="cogvideox", vae_decode=lambda z: z * 2)
     out = pipe(text, frames=2, height=4, width=4, generator=torch.Generator().manual_seed(0), num_inference_steps=3)
     assert out.shape == (1, 4, 2, 4, 4)
+
+
+def test_lora_adapter_in_peft_layout_round_trip(tmp_path):
+    """Adapters on fused projections are written per Hugging Face part (shared lora_A, own rows of lora_B): the files carry
+    PEFT's names, un-fused modules with those adapters compute the same update, and the files load back."""
+    import json
+    import torch
+    from safetensors.torch import load_file
+    from types import SimpleNamespace
+    from mindspeed_mm_b200.checkpoint import hf as hfio
+    from mindspeed_mm_b200.models.qwen2_5_vl import Qwen25VLConfig, Qwen25VLModel
+    from mindspeed_mm_b200.tasks.lora import apply_lora, from_peft_state, lora_state_dict, save_peft_adapter
+    cfg = Qwen25VLConfig.tiny()
+    cfg.text.num_layers, cfg.vision.depth, cfg.vision.fullatt_block_indexes = 1, 1, (0,)
+    model = Qwen25VLModel(cfg).float()
+    model.init_weights(0)
+    lc = SimpleNamespace(rank=4, alpha=8, target_modules=["q_proj", "v_proj", "down_proj"], dropout=0.0)
+    wrapped = apply_lora(model, lc)
+    assert "layers.0.qkv_proj" in wrapped and "layers.0.down_proj" in wrapped
+    torch.manual_seed(0)
+    for n, p in model.named_parameters():
+        if "lora_" in n:
+            torch.nn.init.normal_(p, std=0.1)
+    state = lora_state_dict(model.named_parameters())
+    ops = hfio.qwen25vl_ops(cfg)
+    save_peft_adapter(state, ops, str(tmp_path), lc, base_model="Qwen/Qwen2.5-VL-7B-Instruct")
+    peft = load_file(str(tmp_path / "adapter_model.safetensors"))
+    conf = json.load(open(tmp_path / "adapter_config.json"))
+    assert conf["peft_type"] == "LORA" and conf["r"] == 4 and set(conf["target_modules"]) == {"q_proj", "k_proj", "v_proj", "down_proj"}
+    t = cfg.text
+    qb = peft["base_model.model.model.language_model.layers.0.self_attn.q_proj.lora_B.weight"]
+    kb = peft["base_model.model.model.language_model.layers.0.self_attn.k_proj.lora_B.weight"]
+    assert qb.shape == (t.num_attention_heads * t.head_dim, 4) and kb.shape == (t.num_key_value_heads * t.head_dim, 4)
+    # per-part update == rows of the fused update
+    a, b = state["layers.0.qkv_proj.lora_A"], state["layers.0.qkv_proj.lora_B"]
+    fused = b @ a
+    assert torch.allclose(qb @ peft["base_model.model.model.language_model.layers.0.self_attn.q_proj.lora_A.weight"],
+                          fused[:qb.shape[0]])
+    back = from_peft_state(peft, hfio.qwen25vl_ops(cfg))
+    assert set(back) == set(state) and all(torch.equal(back[k], state[k]) for k in state)

@@ -172,6 +172,128 @@ class WanConverter:
         hfio.save_sharded(mm_to_diffusers(hfio.load_state_dict(cfg["source_path"])), cfg["target_path"])
 
 
+class _DcpHFConverter:
+    """``hf_to_dcp`` / ``dcp_to_hf`` in the layout the reference's native trainer reads and writes for the Qwen3 families
+    (checkpoint/vlm_model/converters/qwen3vl.py:36-118): every key gets the ``model.`` prefix of the wrapped module and the
+    fused expert tensors ``[E, in, out]`` are stored as 2-D ``[E * in, out]``."""
+    fused_linear_names = ("mlp.experts.gate_up_proj", "mlp.experts.down_proj")
+    dcp_prefix = "model."
+    tie = {"lm_head.weight": "model.language_model.embed_tokens.weight"}
+
+    @classmethod
+    def hf_to_dcp(cls, cfg):
+        import torch.distributed.checkpoint as dcp
+        sd = hfio.load_state_dict(cfg["hf_dir"])
+        if cfg.get("tie_weight"):
+            for dst, src in cls.tie.items():
+                if src in sd:
+                    sd[dst] = sd[src]
+        out = {}
+        for k, v in sd.items():
+            if any(n in k for n in cls.fused_linear_names) and v.dim() == 3:
+                v = v.reshape(-1, v.shape[-1])
+            out[cls.dcp_prefix + k] = v
+        dcp.save({"model": out}, checkpoint_id=os.path.join(cfg["dcp_dir"], "release"), no_dist=True)
+        with open(os.path.join(cfg["dcp_dir"], "latest_checkpointed_iteration.txt"), "w") as f:
+            f.write("release")
+
+    @classmethod
+    def dcp_to_hf(cls, cfg):
+        from torch.distributed.checkpoint.format_utils import dcp_to_torch_save
+        src = cfg.get("load_dir") or cfg["dcp_dir"]
+        tr = os.path.join(src, "latest_checkpointed_iteration.txt")
+        if os.path.exists(tr):
+            tag = open(tr).read().strip()
+            src = os.path.join(src, tag if tag == "release" else f"iter_{int(tag):07d}")
+        save_dir = cfg.get("save_dir") or cfg["save_hf_dir"]
+        assets = cfg.get("model_assets_dir") or cfg.get("hf_dir")
+        os.makedirs(save_dir, exist_ok=True)
+        tmp = os.path.join(save_dir, "_dcp_tmp.pt")
+        dcp_to_torch_save(src, tmp)
+        sd = torch.load(tmp, map_location="cpu", weights_only=False)
+        os.remove(tmp)
+        sd = sd.get("model", sd)
+        n_exp = 0
+        if assets and os.path.exists(os.path.join(assets, "config.json")):
+            with open(os.path.join(assets, "config.json")) as f:
+                c = json.load(f)
+            n_exp = int(c.get("text_config", c).get("num_experts") or 0)
+        out = {}
+        for k, v in sd.items():
+            if not isinstance(v, torch.Tensor):
+                continue
+            if n_exp and any(n in k for n in cls.fused_linear_names) and v.dim() == 2:
+                v = v.reshape(n_exp, -1, v.shape[-1])
+            if cfg.get("to_bf16"):
+                v = v.to(torch.bfloat16)
+            out[k[len(cls.dcp_prefix):] if k.startswith(cls.dcp_prefix) else k] = v
+        hfio.save_sharded(out, save_dir)
+        if assets:
+            for f in os.listdir(assets):
+                if f.endswith((".json", ".txt", ".jinja")) and f != hfio.INDEX:
+                    import shutil
+                    shutil.copy(os.path.join(assets, f), os.path.join(save_dir, f))
+
+    @classmethod
+    def moe_expert(cls, cfg):
+        """``--cfg.style merge|split``: per-expert ``...experts.{e}.{gate,up,down}_proj.weight`` tensors of a Hugging Face MoE
+        checkpoint <-> the fused ``gate_up_proj [E, H, 2F]`` / ``down_proj [E, F, H]`` pair (checkpoint/vlm_model/converters/
+        moe_expert.py:55-121)."""
+        from .operators import ExpertStack, Merge
+        sd = hfio.load_state_dict(cfg["hf_dir"])
+        base = cfg.get("weight_path", "model.language_model.layers.{i}.mlp.experts")
+        ops = [Merge([base + ".{e}.gate_proj.weight", base + ".{e}.up_proj.weight"], base + ".{e}.gate_up.weight"),
+               ExpertStack(base + ".{e}.gate_up.weight", base + ".gate_up_proj"),
+               ExpertStack(base + ".{e}.down_proj.weight", base + ".down_proj")]
+        if cfg.get("style", "merge") == "merge":
+            for op in ops:
+                op.apply(sd)
+        else:
+            for op in reversed(ops):
+                op.revert(sd)
+        hfio.save_sharded(sd, cfg["save_dir"])
+
+
+@register
+class Qwen3VLConverter(_DcpHFConverter):
+    pass
+
+
+@register
+class Qwen35Converter(_DcpHFConverter):
+    tie = {"lm_head.weight": "model.language_model.embed_tokens.weight"}
+
+
+@register
+class HunyuanVideoConverter:
+    """``source_to_mm`` / ``mm_to_source``: the published HunyuanVideo transformer file <-> this framework's parameter names
+    (``checkpoint/hf.py: hunyuanvideo_ops``; the reference's checkpoint/sora_model/hunyuanvideo_converter.py:202-210)."""
+
+    @staticmethod
+    def _cfg(cfg):
+        from ..models.mmdit import MMDiTConfig
+        return MMDiTConfig.hunyuan_video()
+
+    @classmethod
+    def source_to_mm(cls, cfg):
+        src = cfg["source_path"]
+        sd = hfio.load_state_dict(src) if os.path.isdir(src) else _load_single(src)
+        hfio.save_sharded(hfio.to_internal(sd, hfio.hunyuanvideo_ops(cls._cfg(cfg))), cfg["target_path"])
+
+    @classmethod
+    def mm_to_source(cls, cfg):
+        sd = hfio.load_state_dict(cfg["source_path"])
+        hfio.save_sharded(hfio.to_hf(sd, hfio.hunyuanvideo_ops(cls._cfg(cfg)), modern_prefix=False), cfg["target_path"])
+
+
+def _load_single(path: str) -> Dict[str, torch.Tensor]:
+    if path.endswith(".safetensors"):
+        from safetensors.torch import load_file
+        return load_file(path)
+    sd = torch.load(path, map_location="cpu", weights_only=True)
+    return sd.get("module", sd)
+
+
 def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     if len(argv) < 2 or argv[0] in ("-h", "--help"):

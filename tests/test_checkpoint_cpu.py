@@ -285,3 +285,39 @@ def test_hf_to_dcp_release_checkpoint_loads_into_the_engine(tmp_path):
     want = hfio.to_internal({k: v.clone() for k, v in sd.items()}, hfio.qwen25vl_ops(cfg))
     for n, t in want.items():
         assert torch.allclose(got[n].float(), t.float(), atol=1e-6), n
+
+
+def test_mm_convert_qwen3vl_dcp_and_expert_commands(tmp_path):
+    """Qwen3VLConverter: hf_to_dcp stores the fused experts 2-D under the ``model.`` prefix and dcp_to_hf restores the
+    Hugging Face files; moe_expert merges per-expert tensors into the fused pair and splits them again."""
+    import json
+    E, H, F = 4, 8, 6
+    torch.manual_seed(0)
+    hf = {"model.language_model.embed_tokens.weight": torch.randn(16, H), "lm_head.weight": torch.randn(16, H),
+          "model.language_model.layers.0.mlp.experts.gate_up_proj": torch.randn(E, H, 2 * F),
+          "model.language_model.layers.0.mlp.experts.down_proj": torch.randn(E, F, H),
+          "model.language_model.layers.0.mlp.gate.weight": torch.randn(E, H)}
+    src = tmp_path / "hf"
+    hfio.save_sharded(hf, str(src))
+    json.dump({"text_config": {"num_experts": E}}, open(src / "config.json", "w"))
+    assert mm_convert(["Qwen3VLConverter", "hf_to_dcp", "--cfg.hf_dir", str(src), "--cfg.dcp_dir", str(tmp_path / "dcp")]) == 0
+    import torch.distributed.checkpoint as dcp
+    from torch.distributed.checkpoint.format_utils import dcp_to_torch_save
+    dcp_to_torch_save(str(tmp_path / "dcp" / "release"), str(tmp_path / "flat.pt"))
+    flat = torch.load(tmp_path / "flat.pt", weights_only=False)["model"]
+    assert flat["model.model.language_model.layers.0.mlp.experts.gate_up_proj"].shape == (E * H, 2 * F)
+    assert mm_convert(["Qwen3VLConverter", "dcp_to_hf", "--cfg.load_dir", str(tmp_path / "dcp"), "--cfg.save_dir",
+                       str(tmp_path / "back"), "--cfg.model_assets_dir", str(src)]) == 0
+    back = hfio.load_state_dict(str(tmp_path / "back"))
+    assert set(back) == set(hf) and all(torch.equal(back[k], hf[k]) for k in hf)
+    assert (tmp_path / "back" / "config.json").exists()
+    # per-expert <-> fused
+    assert mm_convert(["Qwen3VLConverter", "moe_expert", "--cfg.style", "split", "--cfg.hf_dir", str(src), "--cfg.save_dir",
+                       str(tmp_path / "split")]) == 0
+    sp = hfio.load_state_dict(str(tmp_path / "split"))
+    g = sp["model.language_model.layers.0.mlp.experts.2.gate_proj.weight"]
+    assert g.shape == (F, H) and torch.equal(g, hf["model.language_model.layers.0.mlp.experts.gate_up_proj"][2, :, :F].t())
+    assert mm_convert(["Qwen3VLConverter", "moe_expert", "--cfg.style", "merge", "--cfg.hf_dir", str(tmp_path / "split"),
+                       "--cfg.save_dir", str(tmp_path / "merged")]) == 0
+    mg = hfio.load_state_dict(str(tmp_path / "merged"))
+    assert all(torch.equal(mg[k], hf[k]) for k in hf)

@@ -290,6 +290,15 @@ class MultimodalConversationDataset(Dataset):
             else:
                 cv = tok.convert_tokens_to_ids
                 template = ChatTemplate(tok, cv("<|image_pad|>"), cv("<|video_pad|>"), cv("<|vision_start|>"), cv("<|vision_end|>"))
+        name = (pre.get("template") or pre.get("template_name")) if dataset_param is not None else None
+        if name and name not in ("qwen2vl", "qwen2_5_vl") and isinstance(template, ChatTemplate):
+            # another family's turn layout (``preprocess_parameters.template``) around the same placeholder ids
+            from .templates import TEMPLATES, TemplateRenderer
+            if name not in TEMPLATES:
+                raise ValueError(f"Template {name} does not exist (known: {sorted(TEMPLATES)})")
+            t0 = template
+            template = TemplateRenderer(TEMPLATES[name], tok, media_ids={"image": (t0.vs, t0.image_token_id, t0.ve),
+                                                                        "video": (t0.vs, t0.video_token_id, t0.ve)})
         self.template = template
         self.cutoff, self.video_frames = cutoff_len, video_frames
         self.image_loader = image_loader or self._load_image
@@ -423,6 +432,14 @@ class VideoTextDataset(Dataset):
             if tokenizer is None and tp and os.path.exists(tp):
                 from transformers import AutoTokenizer
                 tokenizer = AutoTokenizer.from_pretrained(tp)
+            pipeline = pre.get("train_pipeline")
+        else:
+            pipeline = None
+        # the recipe's own transform list (``preprocess_parameters.train_pipeline``), when it has one
+        from .transforms import get_transforms
+        box = {"max_height": height, "max_width": width}
+        self.video_tf = get_transforms(True, pipeline, transform_size=box) if pipeline and pipeline.get("video") else None
+        self.image_tf = get_transforms(False, pipeline, image_size=[height, width]) if pipeline and pipeline.get("image") else None
         self.records: List[dict] = []
         for f in files:
             self.records += _read_records(f)
@@ -434,12 +451,21 @@ class VideoTextDataset(Dataset):
 
     def _frames(self, path: str) -> torch.Tensor:
         p = path if os.path.isabs(path) or not self.folder else os.path.join(self.folder, path)
-        if p.lower().endswith((".png", ".jpg", ".jpeg", ".bmp", ".webp")):
+        is_image = p.lower().endswith((".png", ".jpg", ".jpeg", ".bmp", ".webp"))
+        if is_image:
             from PIL import Image
             import numpy as np
-            x = torch.from_numpy(np.asarray(Image.open(p).convert("RGB")).copy()).permute(2, 0, 1).float()[None] / 255.0
+            img = Image.open(p).convert("RGB")
+            if self.image_tf is not None:
+                return self.image_tf(img).unsqueeze(1).contiguous()                  # [3, 1, H, W]
+            x = torch.from_numpy(np.asarray(img).copy()).permute(2, 0, 1).float()[None] / 255.0
         else:
             x = read_video_frames(p, self.T)
+        if self.video_tf is not None and not is_image:
+            x = self.video_tf(x)                                                     # [T, 3, H, W], normalised by the recipe
+            if 1 < x.shape[0] < self.T:
+                x = torch.cat([x, x[-1:].repeat(self.T - x.shape[0], 1, 1, 1)], 0)
+            return x.permute(1, 0, 2, 3).contiguous()
         _, _, h, w = x.shape
         s = max(self.H / h, self.W / w)
         nh, nw = max(self.H, round(h * s)), max(self.W, round(w * s))

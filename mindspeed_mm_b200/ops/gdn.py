@@ -41,6 +41,12 @@ class ChunkLayout:
             seq_chunks.append(seq_chunks[-1] + n)
         self.NC = seq_chunks[-1]
         self.nseq = len(cu) - 1
+        # first packed token and number of valid tokens of every chunk (for the prologue kernel, which reads the packed
+        # tensors directly)
+        tok0 = [a + j * CHUNK for a, b in zip(cu[:-1], cu[1:]) for j in range((b - a + CHUNK - 1) // CHUNK)]
+        clen = [min(CHUNK, b - a - j * CHUNK) for a, b in zip(cu[:-1], cu[1:]) for j in range((b - a + CHUNK - 1) // CHUNK)]
+        self.chunk_tok0 = torch.tensor(tok0, dtype=torch.int32, device=device)
+        self.chunk_len = torch.tensor(clen, dtype=torch.int32, device=device)
         self.max_chunks = max(pos) + 1 if pos else 0
         self.slot_of_tok = torch.cat(slot_of_tok).to(device) if slot_of_tok else torch.zeros(0, dtype=torch.long, device=device)
         self.seq_chunks = torch.tensor(seq_chunks, dtype=torch.int32, device=device)
@@ -196,11 +202,39 @@ def gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, scale: Optional[float]
     K = q.shape[-1]
     scale = K ** -0.5 if scale is None else scale
     lay = _layout(cu_seqlens, q.device)
+    needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, g, beta))
+    if q.is_cuda and not needs_grad and K == 128 and v.shape[-1] == 128 and _native_tier():
+        # a pass that keeps no graph (inference, the first forward of a recomputed layer): the chunk-local prologue is one
+        # kernel that reads the packed tensors, then the tcgen05 state pass; nothing is scattered to a padded layout first
+        return _forward_native(q, k, v, g, beta, lay, scale)
     qc, kc, vc = (lay.scatter(t.float()) for t in (q, k, v))
     gcn, bc = (lay.scatter(t.float()) for t in (g, beta))
     W, Qg, Kd, At, U, gamma = chunk_prologue(qc, kc, vc, gcn, bc, scale)
     O = state_pass(W, Qg, Kd, At, U, gamma, lay)
     H, NC = O.shape[:2]
+    return lay.gather(O.reshape(H, NC * CHUNK, -1)).to(v.dtype)
+
+
+def _native_tier() -> bool:
+    from . import get_tier
+    return get_tier() == "native"
+
+
+def _forward_native(q, k, v, g, beta, lay: ChunkLayout, scale: float):
+    from . import native
+    T, H, K = q.shape
+    V = v.shape[-1]
+    dev, NC = q.device, lay.NC
+    qb, kb, vb = (t.to(torch.bfloat16).contiguous() for t in (q, k, v))
+    gf, bf = g.float().contiguous(), beta.float().contiguous()
+    W, Qg, Kd, U = (torch.empty(H, NC, CHUNK, K if i < 3 else V, dtype=torch.bfloat16, device=dev) for i in range(4))
+    At = torch.empty(H, NC, CHUNK, CHUNK, dtype=torch.bfloat16, device=dev)
+    gamma = torch.empty(H, NC, dtype=torch.float32, device=dev)
+    native._check(native.lib().mm_gdn_prologue(
+        qb.data_ptr(), kb.data_ptr(), vb.data_ptr(), gf.data_ptr(), bf.data_ptr(), lay.chunk_tok0.data_ptr(),
+        lay.chunk_len.data_ptr(), W.data_ptr(), Qg.data_ptr(), Kd.data_ptr(), At.data_ptr(), U.data_ptr(), gamma.data_ptr(),
+        H, NC, float(scale), native._st()), "gdn_prologue")
+    O, _, _ = _state_pass_native(W, Qg, Kd, At, U, gamma, lay, False)
     return lay.gather(O.reshape(H, NC * CHUNK, -1)).to(v.dtype)
 
 

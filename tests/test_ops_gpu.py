@@ -559,6 +559,13 @@ def test_gated_delta_rule_native(lens, H):
     _close(o, o_ref, rtol=3e-2, atol=3e-3)
     for a, b in zip(grads, grads_ref):
         _close(a, b, rtol=5e-2, atol=5e-3)
+    # a pass that keeps no graph runs the chunk-local prologue as one kernel on the packed tensors (bf16 in, as the layer
+    # passes them): same result as the differentiated pass and as the recurrence
+    with torch.no_grad():
+        o_ng = ops.gated_delta_rule_varlen(q.bfloat16(), k.bfloat16(), v.bfloat16(), g, beta, cu, chunk=64)
+    assert o_ng.dtype == torch.bfloat16
+    _close(o_ng, o_ref, rtol=3e-2, atol=1e-2)
+    _close(o_ng, o, rtol=3e-2, atol=1e-2)
 
 
 def test_peer_flag_wait_runs_out_and_reports_status():

@@ -155,6 +155,71 @@ def qwen3vl_ops(cfg, experts_out_in: bool = False) -> List[Operator]:
     return ops
 
 
+def internvl_ops(cfg, experts_fused: bool = False) -> List[Operator]:
+    """HF InternVL3 / InternVL3.5 (``model_type: internvl``) -> internal names/layouts (``cfg``:
+    models.internvl.InternVLConfig): q | k | v of the tower and of the decoder are fused, gate | up fused, the patch
+    convolution becomes a matmul over flattened patches.  Reference: checkpoint/vlm_model/converters/internvl.py."""
+    t, v = cfg.text, cfg.vision
+    V, B = "model.vision_tower.", "model.vision_tower.encoder.layer.{i}."
+    L = "model.language_model.layers.{i}."
+    ops: List[Operator] = [
+        Reshape(V + "embeddings.patch_embeddings.projection.weight", lambda x: (x.shape[0], -1),
+                lambda x: (x.shape[0], v.in_channels, v.patch_size, v.patch_size)),
+        Rename(V + "embeddings.patch_embeddings.projection.weight", "visual.embed.proj.weight"),
+        Rename(V + "embeddings.patch_embeddings.projection.bias", "visual.embed.proj.bias"),
+        Rename(V + "embeddings.cls_token", "visual.embed.cls_token"),
+        Rename(V + "embeddings.position_embeddings", "visual.embed.position_embeddings"),
+        Rename(B + "lambda_1", "visual.blocks.{i}.lambda_1"),
+        Rename(B + "lambda_2", "visual.blocks.{i}.lambda_2"),
+        Rename(B + "attention.q_norm.weight", "visual.blocks.{i}.q_norm.weight"),
+        Rename(B + "attention.k_norm.weight", "visual.blocks.{i}.k_norm.weight"),
+    ]
+    for kind in ("weight", "bias"):
+        ops += [
+            Merge([B + "attention.q_proj." + kind, B + "attention.k_proj." + kind, B + "attention.v_proj." + kind],
+                  "visual.blocks.{i}.attn_qkv." + kind),
+            Rename(B + "attention.projection_layer." + kind, "visual.blocks.{i}.attn_proj." + kind),
+            Rename(B + "mlp.fc1." + kind, "visual.blocks.{i}.mlp_fc1." + kind),
+            Rename(B + "mlp.fc2." + kind, "visual.blocks.{i}.mlp_fc2." + kind),
+            Rename(B + "layernorm_before." + kind, "visual.blocks.{i}.norm1." + kind),
+            Rename(B + "layernorm_after." + kind, "visual.blocks.{i}.norm2." + kind),
+            Rename(V + "layernorm." + kind, "connector.norm." + kind),
+            Rename("model.multi_modal_projector.layer_norm." + kind, "connector.projector.layer_norm." + kind),
+            Rename("model.multi_modal_projector.linear_1." + kind, "connector.projector.linear_1." + kind),
+            Rename("model.multi_modal_projector.linear_2." + kind, "connector.projector.linear_2." + kind),
+            QKVMerge([L + "self_attn.q_proj." + kind, L + "self_attn.k_proj." + kind, L + "self_attn.v_proj." + kind],
+                     "layers.{i}.qkv_proj." + kind, t.num_attention_heads, t.num_key_value_heads, t.head_dim),
+        ]
+    ops += [
+        Rename("model.language_model.embed_tokens.weight", "embed_tokens.weight"),
+        Rename(L + "self_attn.o_proj.weight", "layers.{i}.o_proj.weight"),
+        Rename(L + "self_attn.q_norm.weight", "layers.{i}.q_norm.weight"),
+        Rename(L + "self_attn.k_norm.weight", "layers.{i}.k_norm.weight"),
+        Merge([L + "mlp.gate_proj.weight", L + "mlp.up_proj.weight"], "layers.{i}.gate_up_proj.weight"),
+        Rename(L + "mlp.down_proj.weight", "layers.{i}.down_proj.weight"),
+        Rename(L + "input_layernorm.weight", "layers.{i}.input_layernorm.weight"),
+        Rename(L + "post_attention_layernorm.weight", "layers.{i}.post_attention_layernorm.weight"),
+        Rename("model.language_model.norm.weight", "lm_head.norm.weight"),
+        Rename("lm_head.weight", "lm_head.weight"),
+    ]
+    if t.num_experts:
+        # published checkpoints list every expert (``experts.{e}.gate_proj.weight`` ...); transformers >= 5 holds them
+        # fused as [E, 2F, H] / [E, H, F].  Internal layout: gate_up [E, H, 2F], down [E, F, H].
+        E = L + "mlp.experts."
+        ops += [Rename(L + "mlp.gate.weight", "layers.{i}.mlp.gate.weight")]
+        if experts_fused:
+            ops += [Rename(E + "gate_up_proj", "layers.{i}.mlp.experts.gate_up_proj"),
+                    Rename(E + "down_proj", "layers.{i}.mlp.experts.down_proj"),
+                    Transpose("layers.{i}.mlp.experts.gate_up_proj"), Transpose("layers.{i}.mlp.experts.down_proj")]
+        else:
+            ops += [Merge([E + "{e}.gate_proj.weight", E + "{e}.up_proj.weight"], E + "{e}.gate_up.weight"),
+                    ExpertStack(E + "{e}.gate_up.weight", "layers.{i}.mlp.experts.gate_up_proj"),
+                    ExpertStack(E + "{e}.down_proj.weight", "layers.{i}.mlp.experts.down_proj")]
+    if t.tie_word_embeddings:
+        ops.append(_UntieHead())
+    return ops
+
+
 def qwen35_ops(cfg, experts_out_in: bool = False) -> List[Operator]:
     """HF Qwen3.5 / Qwen3.5-MoE -> internal names/layouts (``cfg``: models.qwen3_5.Qwen35Config).  Beyond renames: the
     four input projections of a GDN layer are fused (q|k|v, z, b, a), its depthwise conv weight drops the singleton

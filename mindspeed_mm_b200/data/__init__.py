@@ -79,6 +79,9 @@ def build_collator(args, model, pin: bool):
         from .anyres import TiledPackCollator
         vit = cfg.vit
         return TiledPackCollator(vit.patch_size, vit.merge, vit.temporal_patch_size)
+    if args.data.dataset_param.dataset_type == "internvl" or "internvl" in name:
+        from .internvl import TilePackCollator
+        return TilePackCollator.for_config(cfg, pin=pin)
     if "qwen2" in name or "vl" in name or args.data.dataset_param.dataset_type == "synthetic_vlm":
         from .collate import PackedVLMCollator
         return PackedVLMCollator.for_config(cfg, pin=pin)

@@ -373,7 +373,7 @@ class MultimodalConversationDataset(Dataset):
             out["image_grid_thw"] = torch.tensor(grids, dtype=torch.long)
         else:
             p = self.proc
-            out["pixel_values"] = torch.zeros(0, 3 * p.temporal * p.patch * p.patch)
+            out["pixel_values"] = p.empty() if hasattr(p, "empty") else torch.zeros(0, 3 * p.temporal * p.patch * p.patch)
             out["image_grid_thw"] = torch.zeros(0, 3, dtype=torch.long)
         return out
 

@@ -74,9 +74,10 @@ for _n in ("glm4.1v", "glm4v_moe"):
 register_template(TemplateSpec("mistral", prefix="{bos}", system="[SYSTEM_PROMPT]{content}[/SYSTEM_PROMPT]", user="[INST]{content}[/INST]",
                                assistant="{content}{eos}", observation='[TOOL_RESULTS]{{"content": {content}}}[/TOOL_RESULTS]',
                                media={"image": ("", "[IMG]", "[IMG_END]")}))
-register_template(TemplateSpec("internvl", **_CHATML, default_system="你是书生·万象，英文名是InternVL，是由上海人工智能实验室、清华大学及多家合作单位联合开发的多模态大语言模型。",
-                               stop_words=("<|im_end|>",), replace_eos=True,
-                               media={"image": ("<img>", "<IMG_CONTEXT>", "</img>"), "video": ("<img>", "<IMG_CONTEXT>", "</img>")}))
+for _n in ("internvl", "internvl2_5", "internvl3_5"):
+    register_template(TemplateSpec(_n, **_CHATML, default_system="你是书生·万象，英文名是InternVL，是由上海人工智能实验室、清华大学及多家合作单位联合开发的多模态大语言模型。",
+                                   stop_words=("<|im_end|>",), replace_eos=True,
+                                   media={"image": ("<img>", "<IMG_CONTEXT>", "</img>"), "video": ("<img>", "<IMG_CONTEXT>", "</img>")}))
 register_template(TemplateSpec("llava", system="{content} ", user="USER: {content} ASSISTANT:", assistant=" {content}{eos}",
                                default_system="A chat between a curious human and an artificial intelligence assistant. The assistant "
                                               "gives helpful, detailed, and polite answers to the human's questions.",

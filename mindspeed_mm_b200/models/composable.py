@@ -505,7 +505,6 @@ PRESETS: Dict[str, ComposableConfig] = {
     "funasr": ComposableConfig(_tiny_text(rope="rope1d"), None, audio=_tiny_audio(), audio_window=20, **_IDS),
     "glm4v_moe": ComposableConfig(_tiny_text(qkv_bias=True, ffns=("dense", "moe"), shared_expert_intermediate_size=64),
                                   "qwen_window", _tiny_qwen_vit(128), **_IDS),
-    "internvl3_5": ComposableConfig(_tiny_text(qk_norm=True, rope="rope1d"), "vit", vit=_tiny_vit(128), **_IDS),
     "mistral3": ComposableConfig(_tiny_text(rope="rope1d"), "vit", vit=_tiny_vit(128), **_IDS),
     "gemma4": ComposableConfig(_tiny_text(rope="rope1d", act="gelu_tanh", norm_plus_one=True, embed_scale=True, qk_norm=True),
                                "vit", vit=_tiny_vit(128), **_IDS),

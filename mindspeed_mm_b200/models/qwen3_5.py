@@ -129,7 +129,7 @@ class Qwen35Config:
             qkv_bias=t.get("attention_bias", False), linear_num_key_heads=t["linear_num_key_heads"],
             linear_num_value_heads=t["linear_num_value_heads"], linear_key_head_dim=t["linear_key_head_dim"],
             linear_value_head_dim=t["linear_value_head_dim"], linear_conv_kernel_dim=t.get("linear_conv_kernel_dim", 4),
-            full_attention_interval=interval, num_experts=t.get("num_experts", 0),
+            full_attention_interval=interval, num_experts=t.get("num_experts", t.get("num_local_experts", 0)),
             num_experts_per_tok=t.get("num_experts_per_tok", 8), moe_intermediate_size=t.get("moe_intermediate_size", 512),
             shared_expert_intermediate_size=t.get("shared_expert_intermediate_size", 0),
             router_aux_loss_coef=t.get("router_aux_loss_coef", 0.0),

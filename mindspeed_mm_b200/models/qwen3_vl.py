@@ -126,7 +126,7 @@ class Qwen3VLConfig:
             head_dim=t.get("head_dim") or t["hidden_size"] // t["num_attention_heads"], vocab_size=t["vocab_size"],
             rms_norm_eps=t.get("rms_norm_eps", 1e-6), rope_theta=rp.get("rope_theta", t.get("rope_theta", 5e6)),
             mrope_section=tuple(rp.get("mrope_section", (24, 20, 20))), qkv_bias=t.get("attention_bias", False),
-            num_experts=t.get("num_experts", 0), num_experts_per_tok=t.get("num_experts_per_tok", 8),
+            num_experts=t.get("num_experts", t.get("num_local_experts", 0)), num_experts_per_tok=t.get("num_experts_per_tok", 8),
             moe_intermediate_size=t.get("moe_intermediate_size", 768), norm_topk_prob=t.get("norm_topk_prob", True),
             router_aux_loss_coef=t.get("router_aux_loss_coef", 0.0),
             decoder_sparse_step=t.get("decoder_sparse_step", 1), mlp_only_layers=tuple(t.get("mlp_only_layers", ())),

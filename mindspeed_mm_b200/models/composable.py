@@ -183,12 +183,16 @@ class KimiDeltaAttention(nn.Module):
         v = F.silu(self.v_proj(x)).view(T, self.h, self.dv)
         g = -F.softplus(self.g_proj(x).float()).view(T, self.h, self.dk)
         beta = torch.sigmoid(self.b_proj(x).float())
-        outs = []
-        cu = cu_seqlens.tolist() if torch.is_tensor(cu_seqlens) else list(cu_seqlens)
-        for a, b in zip(cu[:-1], cu[1:]):
-            o, _ = ops.kda(q[None, a:b], k[None, a:b], v[None, a:b], g[None, a:b], beta[None, a:b], chunk=self.chunk)
-            outs.append(o[0])
-        return self.o_proj(torch.cat(outs, 0).to(x.dtype).reshape(T, self.h * self.dv))
+        if self.chunk == 64:
+            o = ops.kda_varlen(q, k, v, g, beta, cu_seqlens)
+        else:
+            outs = []
+            cu = cu_seqlens.tolist() if torch.is_tensor(cu_seqlens) else list(cu_seqlens)
+            for a, b in zip(cu[:-1], cu[1:]):
+                o, _ = ops.kda(q[None, a:b], k[None, a:b], v[None, a:b], g[None, a:b], beta[None, a:b], chunk=self.chunk)
+                outs.append(o[0])
+            o = torch.cat(outs, 0)
+        return self.o_proj(o.to(x.dtype).reshape(T, self.h * self.dv))
 
 
 class GatedMLP(nn.Module):

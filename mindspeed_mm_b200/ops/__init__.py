@@ -380,9 +380,31 @@ def gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk: int = 64, scale
 
 
 def kda(q, k, v, g, beta, scale=None, chunk: int = 64, initial_state=None):
-    """Kimi delta attention (per-channel gate).  Chunked batched-GEMM form on every device."""
-    _fallback("kda", q, "no dedicated kernel")
+    """Kimi delta attention (per-channel gate) on [B, T, H, *] tensors.  Returns (o fp32, final state)."""
+    if initial_state is None and chunk == 64 and _native(q) and _nat().gdn_supported(q[0], v[0], chunk):
+        B, T = q.shape[:2]
+        cu = [i * T for i in range(B + 1)]
+        flat = lambda t: t.reshape((B * T,) + tuple(t.shape[2:]))
+        o = kda_varlen(flat(q), flat(k), flat(v), flat(g), flat(beta), cu, scale)
+        return o.view(B, T, *o.shape[1:]).float(), None
+    _fallback("kda", q, f"K={q.shape[-1]} V={v.shape[-1]} chunk={chunk} initial_state={initial_state is not None}")
     return ref.kda_chunked(q, k, v, g, beta, scale, chunk, initial_state)
+
+
+def kda_varlen(q, k, v, g, beta, cu_seqlens, scale=None):
+    """Kimi delta attention on packed sequences: q, k, g [T, H, K], v [T, H, V], beta [T, H]; the state restarts at every
+    ``cu_seqlens`` boundary.  On CUDA (K = V = 128) the state walk is the tcgen05 kernel with one decay per key channel;
+    elsewhere the same chunked form runs in PyTorch."""
+    from . import gdn
+    if not (_native(q) and _nat().gdn_supported(q, v, 64)):
+        _fallback("kda_varlen", q, f"K={q.shape[-1]} V={v.shape[-1]}")
+        if q.is_cuda:            # the autograd function would pick the kernel for a shape it does not support
+            outs = []
+            cu = [int(c) for c in cu_seqlens]
+            for a, b in zip(cu[:-1], cu[1:]):
+                outs.append(ref.kda_chunked(q[None, a:b], k[None, a:b], v[None, a:b], g[None, a:b], beta[None, a:b], scale)[0][0])
+            return torch.cat(outs, 0).to(v.dtype)
+    return gdn.kimi_delta_attention_varlen(q, k, v, g, beta, cu_seqlens, scale)
 
 
 def status() -> dict:

@@ -30,15 +30,32 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_fwd_kernel(const bf16* __
         int i = threadIdx.x + j * kRowThreads;
         if (i < nvec) wc[j] = reinterpret_cast<const Vec8*>(w)[i];
     }
+    // the next row's loads are issued before this row's reduction, so they are in flight across the block barrier
+    Vec8 cache[NV];
+    if (blockIdx.x < T) {
+        const Vec8* xr = reinterpret_cast<const Vec8*>(x + (size_t)blockIdx.x * H);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            int i = threadIdx.x + j * kRowThreads;
+            if (i < nvec) cache[j] = xr[i];
+        }
+    }
     for (int row = blockIdx.x; row < T; row += gridDim.x) {
-        const Vec8* xr = reinterpret_cast<const Vec8*>(x + (size_t)row * H);
-        Vec8 cache[NV];
+        Vec8 nxt[NV];
+        const int nrow = row + gridDim.x;
+        if (nrow < T) {
+            const Vec8* xn = reinterpret_cast<const Vec8*>(x + (size_t)nrow * H);
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                int i = threadIdx.x + j * kRowThreads;
+                if (i < nvec) nxt[j] = xn[i];
+            }
+        }
         float ss = 0.f;
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
             int i = threadIdx.x + j * kRowThreads;
             if (i < nvec) {
-                cache[j] = xr[i];
                 float f[8];
                 unpack8(cache[j], f);
 #pragma unroll
@@ -61,14 +78,16 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_fwd_kernel(const bf16* __
                 yr[i] = pack8(f);
             }
         }
+#pragma unroll
+        for (int j = 0; j < NV; ++j) cache[j] = nxt[j];
     }
 }
 
 // dx = rstd * (g - xhat * mean(g * xhat)),  g = dy * w,  xhat = x * rstd;   dw += dy * xhat.
 // Each CTA walks rows with stride gridDim.x and keeps its dw partial in registers; partials go to
-// scratch [gridDim.x, H] fp32 and a second kernel folds them.  Requires H <= 128*NV*8.
-template <int NV>
-__global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_kernel(const bf16* __restrict__ x,
+// scratch [gridDim.x, H] fp32 and a second kernel folds them.  Requires H <= THREADS*NV*8.
+template <int NV, int THREADS>
+__global__ void __launch_bounds__(THREADS) rmsnorm_bwd_kernel(const bf16* __restrict__ x,
                                                                    const bf16* __restrict__ w,
                                                                    const bf16* __restrict__ dy,
                                                                    const float* __restrict__ rstd_in,
@@ -80,28 +99,52 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_kernel(const bf16* __
     Vec8 wc[NV];            // this thread's slice of the weight, read once for all its rows
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
-        int i = threadIdx.x + j * kRowThreads;
+        int i = threadIdx.x + j * THREADS;
         if (i < nvec) wc[j] = reinterpret_cast<const Vec8*>(w)[i];
 #pragma unroll
         for (int k = 0; k < 8; ++k) dwacc[j][k] = 0.f;
     }
+    // with 2 vectors per thread the next row's x and dy are loaded before this row's reduction (in flight across the
+    // block barrier and the stores); wider rows take more threads, not more vectors: with 4 vectors and the second
+    // copy the kernel needs 198 registers, two blocks fit an SM and it ran at 0.47 of the copy bandwidth against 0.59
+    constexpr bool kPrefetch = NV <= 2;
+    Vec8 xc[NV], gc[NV];
+    auto load_row = [&](int r, Vec8* xd, Vec8* gd) {
+        const Vec8* xr = reinterpret_cast<const Vec8*>(x + (size_t)r * H);
+        const Vec8* gr = reinterpret_cast<const Vec8*>(dy + (size_t)r * H);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            int i = threadIdx.x + j * THREADS;
+            if (i < nvec) {
+                xd[j] = xr[i];
+                gd[j] = gr[i];
+            }
+        }
+    };
+    float rstd_next = 0.f;          // the row's scalar is prefetched too: loaded at the top of its own iteration, its
+                                    // latency would sit on every row's critical path
+    if (kPrefetch && blockIdx.x < T) {
+        load_row(blockIdx.x, xc, gc);
+        rstd_next = rstd_in[blockIdx.x];
+    }
     for (int row = blockIdx.x; row < T; row += gridDim.x) {
-        const Vec8* xr = reinterpret_cast<const Vec8*>(x + (size_t)row * H);
-        const Vec8* gr = reinterpret_cast<const Vec8*>(dy + (size_t)row * H);
-        const float rstd = rstd_in[row];
-        Vec8 xc[NV], gc[NV];
+        Vec8 xn[kPrefetch ? NV : 1], gn[kPrefetch ? NV : 1];
+        const int nrow = row + gridDim.x;
+        float rstd;
+        if constexpr (kPrefetch) {
+            rstd = rstd_next;
+            if (nrow < T) {
+                load_row(nrow, xn, gn);
+                rstd_next = rstd_in[nrow];
+            }
+        } else {
+            rstd = rstd_in[row];
+            load_row(row, xc, gc);
+        }
         float dot = 0.f;
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
-            int i = threadIdx.x + j * kRowThreads;
-            if (i < nvec) {
-                xc[j] = xr[i];
-                gc[j] = gr[i];
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            int i = threadIdx.x + j * kRowThreads;
+            int i = threadIdx.x + j * THREADS;
             if (i < nvec) {
                 float a[8], b[8], ww[8];
                 unpack8(xc[j], a);
@@ -119,7 +162,7 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_kernel(const bf16* __
         Vec8* dxr = reinterpret_cast<Vec8*>(dx + (size_t)row * H);
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
-            int i = threadIdx.x + j * kRowThreads;
+            int i = threadIdx.x + j * THREADS;
             if (i < nvec) {
                 float a[8], b[8], ww[8], o[8];
                 unpack8(xc[j], a);
@@ -130,11 +173,18 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_bwd_kernel(const bf16* __
                 dxr[i] = pack8(o);
             }
         }
+        if constexpr (kPrefetch) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                xc[j] = xn[j];
+                gc[j] = gn[j];
+            }
+        }
     }
     float* out = dw_partial + (size_t)blockIdx.x * H;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
-        int i = threadIdx.x + j * kRowThreads;
+        int i = threadIdx.x + j * THREADS;
         if (i < nvec) {
             float4* o4 = reinterpret_cast<float4*>(out + i * 8);
             o4[0] = make_float4(dwacc[j][0], dwacc[j][1], dwacc[j][2], dwacc[j][3]);
@@ -382,14 +432,23 @@ __global__ void __launch_bounds__(kThreads) ln_mod_fwd_kernel(const bf16* __rest
     // the number of 16-byte vectors a thread owns, so a 3584-wide row costs 2 x 3 vectors of registers, not 4 x 3.
     Vec8 xc[NV], scv[NV], shv[NV];
     int cached_b = -1;
+    auto load_row = [&](int r, Vec8* dst) {
+        const Vec8* xr = reinterpret_cast<const Vec8*>(x + (size_t)r * H);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            int i = threadIdx.x + j * kThreads;
+            if (i < nvec) dst[j] = xr[i];
+        }
+    };
+    if (blockIdx.x < T) load_row(blockIdx.x, xc);
     for (int row = blockIdx.x; row < T; row += gridDim.x) {
-        const Vec8* xr = reinterpret_cast<const Vec8*>(x + (size_t)row * H);
+        Vec8 xn[NV];                  // next row: in flight across this row's reduction and stores
+        if (row + gridDim.x < T) load_row(row + gridDim.x, xn);
         float s1 = 0.f, s2 = 0.f;
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
             int i = threadIdx.x + j * kThreads;
             if (i < nvec) {
-                xc[j] = xr[i];
                 float f[8];
                 unpack8(xc[j], f);
 #pragma unroll
@@ -434,6 +493,8 @@ __global__ void __launch_bounds__(kThreads) ln_mod_fwd_kernel(const bf16* __rest
                 yr[i] = pack8(o);
             }
         }
+#pragma unroll
+        for (int j = 0; j < NV; ++j) xc[j] = xn[j];
     }
 }
 
@@ -598,6 +659,28 @@ inline int grid_for(long long work_items, int threads, int per_sm = 8) {
 }  // namespace
 
 // ------------------------------------------------------------------------------------------ C ABI
+// Squared L2 norm of an fp32 buffer, for the global gradient norm over many flat shards: block b of the launch for
+// buffer `slot` writes its partial to partials[slot * kSqNormBlocks + b] (fixed summation order: the result does not
+// depend on scheduling).  The caller zero-fills `partials` once and sums it with one reduction.
+constexpr int kSqNormBlocks = 128;
+
+__global__ void __launch_bounds__(256) sq_norm_kernel(const float* __restrict__ x, long long n, float* __restrict__ partials) {
+    __shared__ float red[40];
+    float acc = 0.f;
+    const long long n4 = n >> 2;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n4; i += 256ll * gridDim.x) {
+        const float4 v = x4[i];
+        acc += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
+        const float v = x[(n4 << 2) + threadIdx.x];
+        acc += v * v;
+    }
+    acc = block_sum(acc, red);
+    if (threadIdx.x == 0) partials[blockIdx.x] = acc;
+}
+
 // Grid of a row-walking kernel: one wave of resident blocks (a second, partial wave would leave SMs idle at the end).
 template <typename K>
 static int resident_grid(K kernel, int threads, int rows, int& cache) {
@@ -630,14 +713,15 @@ MM_API int mm_rmsnorm_bwd_grid(int T) { return T < 148 * 6 ? T : 148 * 6; }
 MM_API int mm_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx, void* dw,
                           float* dw_partial, int T, int H, cudaStream_t st) {
     if (H % 8 || H > kRowThreads * 8 * 8) return -1;
-    const int grid = mm_rmsnorm_bwd_grid(T);
-    const int nv = (H / 8 + kRowThreads - 1) / kRowThreads;
-#define MM_RMS_BWD(NV)                                                                                              \
-    rmsnorm_bwd_kernel<NV><<<grid, kRowThreads, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, \
-                                                         (bf16*)dx, dw_partial, T, H)
-    if (nv <= 2) MM_RMS_BWD(2);
-    else if (nv <= 4) MM_RMS_BWD(4);
-    else MM_RMS_BWD(8);
+    static int g128 = 0, g256 = 0, g512 = 0;
+    int grid = mm_rmsnorm_bwd_grid(T);      // the scratch holds that many partial rows; one resident wave may be fewer
+#define MM_RMS_BWD(TH)                                                                                              \
+    grid = min(grid, resident_grid(rmsnorm_bwd_kernel<2, TH>, TH, T, g##TH));                                       \
+    rmsnorm_bwd_kernel<2, TH><<<grid, TH, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd,          \
+                                                   (bf16*)dx, dw_partial, T, H)
+    if (H <= 128 * 16) { MM_RMS_BWD(128); }
+    else if (H <= 256 * 16) { MM_RMS_BWD(256); }
+    else { MM_RMS_BWD(512); }
 #undef MM_RMS_BWD
     fold_partials_kernel<<<(H + 31) / 32, dim3(32, 8), 0, st>>>(dw_partial, (bf16*)dw, grid, H);
     return (int)cudaGetLastError();
@@ -802,13 +886,25 @@ MM_API int mm_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* dy, 
     float* partial = nullptr;
     if (int rc = noalloc_workspace(&partial)) return rc;
     const int grid = T < MM_NOALLOC_MAX_CTAS ? T : MM_NOALLOC_MAX_CTAS;
-    const int nv = (H / 8 + kRowThreads - 1) / kRowThreads;
-    if (nv <= 2)
-        rmsnorm_bwd_kernel<2><<<grid, kRowThreads, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd,
-                                                            (bf16*)dx, partial, T, H);
+    if (H <= 128 * 16)
+        rmsnorm_bwd_kernel<2, 128><<<grid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd,
+                                                         (bf16*)dx, partial, T, H);
     else
-        rmsnorm_bwd_kernel<4><<<grid, kRowThreads, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd,
-                                                            (bf16*)dx, partial, T, H);
+        rmsnorm_bwd_kernel<2, 256><<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd,
+                                                         (bf16*)dx, partial, T, H);
     fold_partials_kernel<<<(H + 31) / 32, dim3(32, 8), 0, st>>>(partial, (bf16*)dw, grid, H);
+    return (int)cudaGetLastError();
+}
+
+MM_API int mm_sq_norm_blocks() { return kSqNormBlocks; }
+
+// x: fp32, 16-byte aligned, n elements; partials: this buffer's row of mm_sq_norm_blocks() floats (zero-filled by the
+// caller: a short buffer uses fewer blocks and leaves the rest of its row untouched).
+MM_API int mm_sq_norm(const float* x, long long n, float* partials, cudaStream_t st) {
+    if (n <= 0) return 0;
+    if ((uintptr_t)x & 15) return -1;
+    long long want = (n / 4 + 255) / 256;
+    const int grid = (int)(want < 1 ? 1 : (want > kSqNormBlocks ? kSqNormBlocks : want));
+    sq_norm_kernel<<<grid, 256, 0, st>>>(x, n, partials);
     return (int)cudaGetLastError();
 }

@@ -37,7 +37,7 @@ constexpr int kSmem = 2 * kStageBytes + kSbBytes + kVnBytes + 512 + 1024;
 
 struct GdnParams {
     const bf16* U;            // [H, NC*C, DV]
-    const float* gamma;       // [H, NC]   exp(sum of the chunk's log-gates)
+    const float* gamma;       // [H, NC] exp(sum of the chunk's log-gates), or [H, NC, DK] with one decay per key channel
     const int* seq_chunks;    // [nseq + 1] chunk ranges of the sequences
     bf16* O;                  // [H, NC*C, DV]
     bf16* Vn;                 // [H, NC*C, DV] or null
@@ -45,6 +45,7 @@ struct GdnParams {
     float* Sfinal;            // [nseq, H, DV, DK] or null
     int* status;
     int NC, H;
+    int gamma_per_channel;    // 0: one decay per (head, chunk) (gated delta rule); 1: one per key channel (KDA)
 };
 
 __global__ void __launch_bounds__(192, 1)
@@ -176,7 +177,8 @@ gdn_fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             float u[C];
 #pragma unroll
             for (int t = 0; t < C; ++t) u[t] = __bfloat162float(up[(size_t)t * DV]);
-            const float gamma = p.gamma[(size_t)head * p.NC + chunk];
+            const float gamma = p.gamma_per_channel ? 1.f : p.gamma[(size_t)head * p.NC + chunk];
+            const float4* gvec = reinterpret_cast<const float4*>(p.gamma + ((size_t)head * p.NC + chunk) * DK);
             if (p.Sprev) {   // bf16 state before this chunk: this thread's row of the operand copy
                 bf16* dst = p.Sprev + (((size_t)head * p.NC + chunk) * DV + v) * DK;
 #pragma unroll
@@ -219,6 +221,17 @@ gdn_fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 tmem_wait_ld();
 #pragma unroll
                 for (int t = 0; t < 32; ++t) r[t] = __float_as_uint(__uint_as_float(r[t]) * gamma);
+                if (p.gamma_per_channel) {   // column k of this thread's state row decays by gamma[k]: the same address
+                                             // in every thread, a broadcast load
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) {
+                        const float4 gv = __ldg(gvec + j * 8 + t);
+                        r[4 * t + 0] = __float_as_uint(__uint_as_float(r[4 * t + 0]) * gv.x);
+                        r[4 * t + 1] = __float_as_uint(__uint_as_float(r[4 * t + 1]) * gv.y);
+                        r[4 * t + 2] = __float_as_uint(__uint_as_float(r[4 * t + 2]) * gv.z);
+                        r[4 * t + 3] = __float_as_uint(__uint_as_float(r[4 * t + 3]) * gv.w);
+                    }
+                }
                 tmem_st_32x32(tS + lane_off + j * 32, r);
             }
             tmem_wait_st();
@@ -288,12 +301,14 @@ gdn_fwd_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
 }  // namespace
 
-// W, Qg, Kd: [H, NC*64, 128] bf16; At: [H, NC*64, 64] bf16; U, O, Vn: [H, NC*64, 128] bf16; gamma: [H, NC] fp32;
+// W, Qg, Kd: [H, NC*64, 128] bf16; At: [H, NC*64, 64] bf16; U, O, Vn: [H, NC*64, 128] bf16; gamma: [H, NC] fp32, or
+// [H, NC, 128] with gamma_per_channel (Kimi delta attention: a decay per key channel);
 // seq_chunks: [nseq + 1] int32 (device).  Vn, Sprev, Sfinal may be null.
 MM_API int mm_gdn_fwd(const void* W, const void* Qg, const void* Kd, const void* At, const void* U, const float* gamma,
                       const int* seq_chunks, void* O, void* Vn, void* Sprev, float* Sfinal, int H, int NC, int nseq,
-                      int* status, cudaStream_t st) {
+                      int gamma_per_channel, int* status, cudaStream_t st) {
     if (H <= 0 || NC <= 0 || nseq <= 0) return -1;
+    if (gamma_per_channel && ((uintptr_t)gamma & 15)) return -1;
     CUtensorMap tmW, tmQ, tmK, tmA;
     const uint64_t rows = (uint64_t)H * NC * C;
     int rc = make_tmap_2d(&tmW, W, rows, DK, DK, C, 64);
@@ -302,7 +317,7 @@ MM_API int mm_gdn_fwd(const void* W, const void* Qg, const void* Kd, const void*
     rc |= make_tmap_2d(&tmA, At, rows, C, C, C, 64);
     if (rc) return -2;
     if (cudaFuncSetAttribute(gdn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return -3;
-    GdnParams p{(const bf16*)U, gamma, seq_chunks, (bf16*)O, (bf16*)Vn, (bf16*)Sprev, Sfinal, status, NC, H};
+    GdnParams p{(const bf16*)U, gamma, seq_chunks, (bf16*)O, (bf16*)Vn, (bf16*)Sprev, Sfinal, status, NC, H, gamma_per_channel};
     gdn_fwd_kernel<<<dim3(H, nseq), 192, kSmem, st>>>(tmW, tmQ, tmK, tmA, p);
     return (int)cudaGetLastError();
 }

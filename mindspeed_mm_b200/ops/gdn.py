@@ -107,8 +107,13 @@ def _state_pass_torch(W, Qg, Kd, At, U, gamma, layout: ChunkLayout):
             vn = Uf[:, c] - Wf[:, c] @ S
             O[:, c] = Qf[:, c] @ S + Af[:, c] @ vn
             Vn[:, c] = vn
-            S = S * gamma[:, c, None, None] + Kf[:, c].transpose(-1, -2) @ vn
+            S = S * _decay(gamma[:, c]) + Kf[:, c].transpose(-1, -2) @ vn
     return O, Vn, SprevT
+
+
+def _decay(g: torch.Tensor) -> torch.Tensor:
+    """Decay of one chunk, broadcast over the [H, K, V] state: [H] (one factor per head) or [H, K] (one per key channel)."""
+    return g[:, None, None] if g.dim() == 1 else g[:, :, None]
 
 
 def _state_pass_native(W, Qg, Kd, At, U, gamma, layout: ChunkLayout, want_saved: bool):
@@ -122,7 +127,7 @@ def _state_pass_native(W, Qg, Kd, At, U, gamma, layout: ChunkLayout, want_saved:
     native._check(native.lib().mm_gdn_fwd(
         W.data_ptr(), Qg.data_ptr(), Kd.data_ptr(), At.data_ptr(), U.data_ptr(), gamma.data_ptr(),
         layout.seq_chunks.data_ptr(), O.data_ptr(), Vn.data_ptr() if want_saved else None,
-        SprevT.data_ptr() if want_saved else None, None, H, NC, layout.nseq,
+        SprevT.data_ptr() if want_saved else None, None, H, NC, layout.nseq, int(gamma.dim() == 3),
         native.status_word(dev).data_ptr(), native._st()), "gdn_fwd")
     return O, Vn, SprevT
 
@@ -166,14 +171,15 @@ class _StatePass(torch.autograd.Function):
             dSn_all[:, idx] = dSn_c
             dvn = AtT_dO[:, idx] + Kd[:, idx] @ dSn_c
             dVn[:, idx] = dvn
-            dS_prev = QgT_dO[:, idx].float() + gamma[:, idx, None, None] * dSn - (W[:, idx].transpose(-1, -2) @ dvn).float()
+            gam = gamma[:, idx, None, None] if gamma.dim() == 2 else gamma[:, idx, :, None]
+            dS_prev = QgT_dO[:, idx].float() + gam * dSn - (W[:, idx].transpose(-1, -2) @ dvn).float()
             dS_seq[:, sidx] = dS_prev
         dU = dVn
         dW = -(dVn @ SprevT.to(cdt))                                  # [64, V] @ [V, K]
         dQg = dO @ SprevT.to(cdt)
         dAt = dO @ Vn.to(cdt).transpose(-1, -2)
         dKd = Vn.to(cdt) @ dSn_all.transpose(-1, -2)
-        dgamma = (dSn_all.float() * SprevT.float().transpose(-1, -2)).sum((-1, -2))
+        dgamma = (dSn_all.float() * SprevT.float().transpose(-1, -2)).sum((-1, -2) if gamma.dim() == 2 else -1)
         outs = (dW, dQg, dKd, dAt, dU, dgamma)
         return tuple(o.to(dt) for o, dt in zip(outs, ctx.in_dtypes)) + (None,)
 
@@ -235,6 +241,41 @@ def _forward_native(q, k, v, g, beta, lay: ChunkLayout, scale: float):
         lay.chunk_len.data_ptr(), W.data_ptr(), Qg.data_ptr(), Kd.data_ptr(), At.data_ptr(), U.data_ptr(), gamma.data_ptr(),
         H, NC, float(scale), native._st()), "gdn_prologue")
     O, _, _ = _state_pass_native(W, Qg, Kd, At, U, gamma, lay, False)
+    return lay.gather(O.reshape(H, NC * CHUNK, -1)).to(v.dtype)
+
+
+def kda_chunk_prologue(q, k, v, g, beta, scale: float):
+    """Kimi delta attention: ``g`` [H, NC, 64, K] is a log decay per key channel.  Same outputs as ``chunk_prologue``
+    with gamma [H, NC, K].  The pairwise decay exp(G_i - G_j) is applied per channel by folding exp(G) into one operand
+    and exp(-G) into the other (G accumulated from the chunk start, so the exponents are bounded by the chunk's decay)."""
+    G = g.cumsum(-2)
+    up, dn = G.exp(), (-G).exp()
+    k_up, k_dn = k * up, k * dn
+    kb_up = k_up * beta.unsqueeze(-1)
+    A = (kb_up @ k_dn.transpose(-1, -2)).tril(-1)
+    eye = torch.eye(CHUNK, device=q.device, dtype=q.dtype)
+    Tm = torch.linalg.solve_triangular(eye + A, eye.expand_as(A), upper=False, unitriangular=True)
+    U = Tm @ (v * beta.unsqueeze(-1))
+    W = Tm @ kb_up
+    Qg = q * up * scale
+    last = G[..., -1:, :]
+    Kd = k * (last - G).exp()
+    At = (Qg @ k_dn.transpose(-1, -2)).tril()
+    return W, Qg, Kd, At, U, last.squeeze(-2).exp()
+
+
+def kimi_delta_attention_varlen(q, k, v, g, beta, cu_seqlens, scale: Optional[float] = None):
+    """q, k, g: [T, H, K] (g = log decay per key channel); v: [T, H, V]; beta: [T, H].  Returns [T, H, V] in ``v.dtype``.
+    Same operator as the reference's chunked KDA (fsdp/ops/kda/chunk_kda_naive.py) on packed sequences: batched
+    chunk-local prologue, then the state walk of the gated delta rule with one decay per key channel."""
+    K = q.shape[-1]
+    scale = K ** -0.5 if scale is None else scale
+    lay = _layout(cu_seqlens, q.device)
+    qc, kc, vc, gc_ = (lay.scatter(t.float()) for t in (q, k, v, g))
+    bc = lay.scatter(beta.float())
+    W, Qg, Kd, At, U, gamma = kda_chunk_prologue(qc, kc, vc, gc_, bc, scale)
+    O = state_pass(W, Qg, Kd, At, U, gamma, lay)
+    H, NC = O.shape[:2]
     return lay.gather(O.reshape(H, NC * CHUNK, -1)).to(v.dtype)
 
 

@@ -53,6 +53,8 @@ def _declare(L):
         "mm_gated_rms_fwd": [_p, _i, _p, _p, _p, _p, _ll, _i, _f, _p],
         "mm_gated_rms_bwd": [_p, _i, _p, _p, _p, _p, _p, _p, _p, _ll, _i, _p],
         "mm_rmsnorm_bwd_grid": [_i],
+        "mm_sq_norm_blocks": [],
+        "mm_sq_norm": [_p, _ll, _p, _p],
         "mm_rmsnorm_bwd": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _p],
         "mm_swiglu_fwd": [_p, _p, _ll, _i, _p],
         "mm_swiglu_bwd": [_p, _p, _p, _ll, _i, _p],
@@ -83,7 +85,7 @@ def _declare(L):
         "mm_l2norm_fwd": [_p, _p, _p, _ll, _i, _f, _p],
         "mm_l2norm_bwd": [_p, _p, _p, _p, _ll, _i, _p],
         "mm_gdn_prologue": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _p],
-        "mm_gdn_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p, _p],
+        "mm_gdn_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p],
         "mm_p2p_scatter_rows": [_p, _p, _p, _p, _p, _i, _i, _i, _p],
         "mm_p2p_gather_rows": [_p, _p, _p, _p, _i, _i, _i, _p],
         "mm_p2p_copy": [_p, _p, _ll, _i, _p],
@@ -384,6 +386,20 @@ def gated_residual(x, y, gate):
 
 
 # --------------------------------------------------------------------------- AdamW
+def sq_norm(tensors) -> torch.Tensor:
+    """Sum of squares over a list of fp32 CUDA tensors (the squared global gradient norm of flat shards): one launch per
+    tensor into a fixed-order table of block partials, one reduction at the end."""
+    nb = lib().mm_sq_norm_blocks()
+    partials = torch.zeros(len(tensors), nb, dtype=torch.float32, device=tensors[0].device)
+    st = _st()
+    for i, t in enumerate(tensors):
+        t = t.contiguous()
+        if t.data_ptr() % 16:           # a view at an odd offset: the kernel reads 16-byte vectors
+            t = t.clone()
+        _check(lib().mm_sq_norm(t.data_ptr(), t.numel(), partials[i].data_ptr(), st), "sq_norm")
+    return partials.sum()
+
+
 def adamw_shard(master, exp_avg, exp_avg_sq, grad, p16, lr, b1, b2, eps, wd, step, split, grad_scale=1.0):
     n = master.numel()
     scale_ptr = None

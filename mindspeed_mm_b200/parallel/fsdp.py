@@ -79,6 +79,15 @@ class OptimConfig:
         return 1.0
 
 
+def _sq_norm(tensors: Sequence[torch.Tensor]) -> torch.Tensor:
+    """Sum of squares over the fp32 gradient shards: one kernel per shard into a table of block partials and a single
+    reduction on CUDA (fixed summation order), stacked reductions elsewhere."""
+    from .. import ops
+    if ops._native(tensors[0]) and all(t.dtype == torch.float32 for t in tensors):
+        return ops._nat().sq_norm(tensors)
+    return torch.stack([t.float().pow(2).sum() for t in tensors]).sum()
+
+
 class ExtremeGradientError(RuntimeError):
     """Adaptive clipping met a gradient norm beyond ``max(mean + 5 sigma, 5)`` or a non-finite one: the step was not
     applied (mindspeed_mm/patchs/adaptive_clip_grad_patch.py:228-262 stops the run the same way)."""
@@ -273,6 +282,12 @@ class Unit:
         self.uses = 0                  # differentiated forward calls in this micro-batch
         self.bwd_uses = 0              # backward passes seen so far
         self.hooks = 0                 # completion hooks registered (graph-keeping units with a differentiable input)
+        # what the engine calls to run the unit: the module itself, or (models whose own forward has been re-routed
+        # through ``engine.run``, see plugins/hf_adapter.py) the class-level forward that the re-routing bypasses
+        self.call = None
+
+    def invoke(self, *args, **kwargs):
+        return self.module(*args, **kwargs) if self.call is None else self.call(*args, **kwargs)
 
     @property
     def trainable(self):
@@ -414,7 +429,7 @@ class FSDPEngine:
             self.unshard(u)
             self.wait_unshard(u)
             self._prefetch_forward(u)
-            out = module(*args, **kwargs)
+            out = u.invoke(*args, **kwargs)
             self.reshard(u)
             return out
         u.uses += 1
@@ -427,7 +442,7 @@ class FSDPEngine:
             u.pending_reduce = u.trainable
             if u.trainable:
                 self._hook_backward_done(u, args, kwargs)
-            out = module(*args, **kwargs)
+            out = u.invoke(*args, **kwargs)
             if u.trainable and self.cuda and self._p2p is None:
                 # offer the flat gradient buffer when this unit's backward is about to start (its output gradient
                 # exists); with peer-memory slots the buffer is taken late instead, so that a slot is not held while
@@ -660,7 +675,7 @@ class FSDPEngine:
                 for g in groups:
                     dist.all_reduce(g.grad32, group=self.replicate_group)
             if self.opt.clip_grad > 0 or self.adaptive_clip is not None:
-                sq = torch.stack([g.grad32.float().pow(2).sum() for g in groups]).sum()
+                sq = _sq_norm([g.grad32 for g in groups])
                 if self.world > 1:
                     dist.all_reduce(sq, group=self.group)
                 norm = sq.sqrt() / self.grad_accum_steps      # norm of the micro-batch-averaged gradient
@@ -861,7 +876,7 @@ class _UnitFn(torch.autograd.Function):
         args, kwargs = _join_args(spec, tensors)
         ctx.act_cache = []
         with torch.no_grad(), ops.activation_cache(ctx.act_cache, "record"):
-            out = u.module(*args, **kwargs)
+            out = u.invoke(*args, **kwargs)
         if engine.reshard_after_forward:
             engine.reshard(u)
         ctx.save_for_backward(*tensors)
@@ -888,7 +903,7 @@ class _UnitFn(torch.autograd.Function):
                           for g in u.groups if g.trainable}
         args, kwargs = _join_args(ctx.spec, tensors)
         with torch.enable_grad(), ops.recompute_region(), ops.activation_cache(ctx.act_cache, "replay"):
-            out = u.module(*args, **kwargs)
+            out = u.invoke(*args, **kwargs)
         ctx.act_cache = None
         outs = tuple(out) if isinstance(out, (tuple, list)) else (out,)
         pairs = [(o, g) for o, g in zip(outs, gouts)
@@ -982,7 +997,7 @@ def _joint_clip_finish(engines, extra_groups: Optional[dict] = None):
             torch.cuda.current_stream().wait_stream(e.comm_stream)
         groups = [g for u in e.units for g in u.groups if g.trainable and g.grad32 is not None]
         if groups:
-            sq = torch.stack([g.grad32.float().pow(2).sum() for g in groups]).sum() / (e.grad_accum_steps ** 2)
+            sq = _sq_norm([g.grad32 for g in groups]) / (e.grad_accum_steps ** 2)
         else:       # still take part in the collectives below
             sq = torch.zeros((), dtype=torch.float32, device=e.device)
         if e.world > 1:

@@ -152,6 +152,17 @@ def test_adamw_shard():
     _close(p16, pr, rtol=1e-2, atol=1e-2)
 
 
+def test_sq_norm_of_shards():
+    from mindspeed_mm_b200.ops import native
+    torch.manual_seed(0)
+    shards = [torch.randn(n, device=DEV) * s for n, s in ((3, 1.0), (1021, 0.5), (128 * 1000, 2.0), (5_000_001, 0.1))]
+    shards = [torch.cat([t.new_zeros(4), t])[4:] if t.numel() < 10 else t for t in shards]     # 16-byte aligned views
+    got = native.sq_norm(shards)
+    want = sum(float(t.double().pow(2).sum()) for t in shards)
+    assert abs(float(got) - want) <= 1e-5 * want
+    assert float(native.sq_norm(shards)) == float(got)          # fixed summation order
+
+
 GEMM_SHAPES = [(128, 256, 64), (256, 512, 256), (1000, 768, 520), (8192, 4608, 3584), (333, 1280, 1176), (77, 136, 72),
                (1176, 1280, 8191 + 1), (3584, 152064 // 8, 512)]
 
@@ -566,6 +577,41 @@ def test_gated_delta_rule_native(lens, H):
     assert o_ng.dtype == torch.bfloat16
     _close(o_ng, o_ref, rtol=3e-2, atol=1e-2)
     _close(o_ng, o, rtol=3e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("lens,H", [([70, 200], 2), ([1000, 130, 5], 3)])
+def test_kimi_delta_attention_native(lens, H):
+    """KDA on the tcgen05 state pass with one decay per key channel (+ hand-written backward) against the token-by-token
+    fp32 recurrence."""
+    torch.manual_seed(0)
+    T, K, V = sum(lens), 128, 128
+    cu = [0] + [int(c) for c in torch.tensor(lens).cumsum(0)]
+    F = torch.nn.functional
+    q = F.normalize(torch.randn(T, H, K, device=DEV), dim=-1).requires_grad_()
+    k = F.normalize(torch.randn(T, H, K, device=DEV), dim=-1).requires_grad_()
+    v = torch.randn(T, H, V, device=DEV).requires_grad_()
+    g = (-0.1 * torch.rand(T, H, K, device=DEV)).requires_grad_()
+    beta = torch.rand(T, H, device=DEV).requires_grad_()
+    ops.library_fallbacks(reset=True)
+    o = ops.kda_varlen(q, k, v, g, beta, cu)
+    assert not ops.library_fallbacks(), ops.library_fallbacks()
+    do = torch.randn_like(o)
+    grads = torch.autograd.grad(o, [q, k, v, g, beta], do)
+    outs = []
+    for a, b in zip(cu[:-1], cu[1:]):
+        oo, _ = ref.kda_recurrent(q[None, a:b], k[None, a:b], v[None, a:b], g[None, a:b], beta[None, a:b])
+        outs.append(oo[0])
+    o_ref = torch.cat(outs)
+    grads_ref = torch.autograd.grad(o_ref, [q, k, v, g, beta], do)
+    _close(o, o_ref, rtol=3e-2, atol=3e-3)
+    for a, b in zip(grads, grads_ref):
+        _close(a, b, rtol=5e-2, atol=5e-3)
+    # the batched [B, T, H, *] entry point takes the same path
+    B, Tb = 2, 128
+    sl = lambda t: t[: B * Tb].detach().reshape(B, Tb, *t.shape[1:])
+    ob, _ = ops.kda(sl(q), sl(k), sl(v), sl(g), sl(beta))
+    ob_ref, _ = ref.kda_recurrent(sl(q), sl(k), sl(v), sl(g), sl(beta))
+    _close(ob, ob_ref, rtol=3e-2, atol=3e-3)
 
 
 def test_peer_flag_wait_runs_out_and_reports_status():

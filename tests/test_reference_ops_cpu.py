@@ -214,6 +214,32 @@ def test_kda_chunked_matches_recurrent():
     assert torch.allclose(s1, s2, atol=2e-4)
 
 
+def test_kda_varlen_state_pass_and_hand_backward_match_recurrence():
+    """Packed KDA (batched per-channel prologue + state walk with a decay per key channel + hand-written backward)
+    == autograd of the token-by-token recurrence."""
+    from mindspeed_mm_b200 import ops
+    torch.manual_seed(0)
+    T, H, K, V = 200, 2, 128, 128
+    cu = [0, 70, 200]
+    q = F.normalize(torch.randn(T, H, K), dim=-1).requires_grad_()
+    k = F.normalize(torch.randn(T, H, K), dim=-1).requires_grad_()
+    v = torch.randn(T, H, V).requires_grad_()
+    g = (-0.1 * torch.rand(T, H, K)).requires_grad_()
+    beta = torch.rand(T, H).requires_grad_()
+    o = ops.kda_varlen(q, k, v, g, beta, cu)
+    outs = []
+    for a, b in zip(cu[:-1], cu[1:]):
+        oo, _ = ref.kda_recurrent(q[None, a:b], k[None, a:b], v[None, a:b], g[None, a:b], beta[None, a:b])
+        outs.append(oo[0])
+    o_ref = torch.cat(outs)
+    assert torch.allclose(o, o_ref, atol=2e-5), (o - o_ref).abs().max()
+    do = torch.randn_like(o)
+    got = torch.autograd.grad(o, [q, k, v, g, beta], do)
+    want = torch.autograd.grad(o_ref, [q, k, v, g, beta], do)
+    for a, b in zip(got, want):
+        assert torch.allclose(a, b, atol=5e-5), (a - b).abs().max()
+
+
 # ------------------------------------------------------------------------------------------------- block-sparse attention
 def test_sta_mask_window_is_clamped_at_borders():
     from mindspeed_mm_b200.ops.sparse_attention import sta_block_mask, tile_order

@@ -14,7 +14,7 @@ from __future__ import annotations
 import json
 import os
 import shutil
-from typing import Callable, Dict, Iterable, List, Optional, Tuple
+from typing import Sequence, Callable, Dict, Iterable, List, Optional, Tuple
 
 import torch
 
@@ -351,7 +351,53 @@ def to_internal(hf_sd: StateDict, ops: List[Operator]) -> StateDict:
     return apply_ops(dict(hf_sd), ops)
 
 
+class UnderPrefix(Operator):
+    """Internal name = ``prefix`` + the checkpoint's own name, nothing else changes (models wrapped as they are, e.g.
+    ``plugins/hf_adapter.py``).  Marks the operator list as exact: no prefix modernisation on the way back."""
+
+    exact_names = True
+
+    def __init__(self, prefix: str):
+        self.prefix = prefix
+
+    def apply(self, sd):
+        for k in list(sd.keys()):
+            sd[self.prefix + k] = sd.pop(k)
+
+    def revert(self, sd):
+        for k in list(sd.keys()):
+            if k.startswith(self.prefix):
+                sd[k[len(self.prefix):]] = sd.pop(k)
+
+
+class MatchBySuffix(Operator):
+    """Checkpoint names -> the names of a model built by the current transformers version, for files written with an
+    older layout of the same architecture (``model.layers...`` / ``visual...`` on disk, ``model.language_model...`` /
+    ``model.visual...`` in memory): a name the model does not have is replaced by the one model name that ends with it
+    (after dropping a leading ``model.``).  Names that match nothing, or more than one, are left alone.  The way back
+    writes the model's own names, which every transformers version that knows them reads."""
+
+    exact_names = True
+
+    def __init__(self, model_names: Sequence[str]):
+        self.names = list(model_names)
+
+    def apply(self, sd):
+        have = set(self.names)
+        for k in list(sd.keys()):
+            if k in have:
+                continue
+            tail = "." + (k[len("model."):] if k.startswith("model.") else k)
+            hits = [n for n in self.names if n.endswith(tail) and n not in sd]
+            if len(hits) == 1:
+                sd[hits[0]] = sd.pop(k)
+
+    def revert(self, sd):
+        pass
+
+
 def to_hf(internal_sd: StateDict, ops: List[Operator], modern_prefix: bool = True) -> StateDict:
+    modern_prefix = modern_prefix and not any(getattr(o, "exact_names", False) for o in ops)
     ops = [o for o in ops if not isinstance(o, RenamePrefix)]
     sd = revert_ops(dict(internal_sd), ops)
     if modern_prefix:

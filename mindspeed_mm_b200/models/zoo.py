@@ -4,6 +4,8 @@ from . import wan  # noqa: F401
 from .diffusion import flow_match  # noqa: F401
 from . import qwen3_vl  # noqa: F401
 from . import qwen3_5  # noqa: F401
+from . import internvl  # noqa: F401
+from ..plugins import hf_auto  # noqa: F401
 from . import mmdit  # noqa: F401
 from . import composable  # noqa: F401
 from . import wan_variants  # noqa: F401

@@ -54,6 +54,8 @@ class Trainer:
         self.ps = init_parallel_state(world_size=self.world, device_type=self.device.type, **args.parallel.state_kwargs())
         self.model = self.build_model()
         self.engine = self.build_engine()
+        if hasattr(self.model, "attach"):            # wrapped third-party classes: their sub-module calls go through the engine
+            self.model.attach(self.engine, materialize=False)
         self.load_weights()
         self.schedule = LRSchedule(lr=t.lr, train_iters=t.train_iters, lr_decay_style=t.lr_decay_style,
                                    lr_warmup_ratio=t.lr_warmup_ratio, lr_min=t.lr_min, lr_start=t.lr_start,

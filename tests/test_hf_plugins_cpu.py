@@ -212,7 +212,7 @@ def test_verl_plugin_entry_point(monkeypatch):
         rec = vp.apply_verl_plugin()
         assert "Qwen2_5_VLRMSNorm" in rec["modeling_qwen2_5_vl"] and "Qwen3VLMoeTextMLP" in rec["modeling_qwen3_vl_moe"]
         assert rec["attention"] == ["mm_b200"] and torch.are_deterministic_algorithms_enabled()
-        a = torch.rand(3)
+        a = torch.rand(3) + torch.rand(3)          # the generator has moved on since the plugin seeded it
         vp.seed_all(1234)
         b = torch.rand(3)
         vp.seed_all(1234)

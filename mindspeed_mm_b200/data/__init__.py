@@ -15,6 +15,8 @@ from torch.utils.data import DataLoader
 from ..models.registry import data_register
 from . import synthetic  # noqa: F401  (registers the synthetic datasets)
 from . import anyres  # noqa: F401  (registers the tiled conversation dataset)
+from . import multimodal  # noqa: F401  (registers huggingface / multimodal / feature / t2v / i2v)
+from . import internvl  # noqa: F401  (registers the dynamic-tile conversation dataset)
 
 
 class _StatefulIter:

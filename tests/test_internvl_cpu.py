@@ -215,3 +215,31 @@ def test_tile_processor_and_dataset(tmp_path):
     model.init_weights(0)
     loss_sum, n = model(batch)
     assert torch.isfinite(loss_sum) and int(n) == int((batch["labels"] != -100).sum())
+
+
+def test_trainer_runs_the_internvl_recipe_on_image_files(tmp_path):
+    """examples/internvl3.5/tiny_native.yaml on a json with two PNG files: tiles from the dataset, packed by the tile
+    collator, three steps of the native trainer."""
+    import json
+    import os
+    import numpy as np
+    from PIL import Image
+    from mindspeed_mm_b200.config import load_config
+    from mindspeed_mm_b200.runtime.trainer import Trainer
+    rng = np.random.default_rng(0)
+    for name, (h, w) in (("a.png", (60, 150)), ("b.png", (80, 80))):
+        Image.fromarray(rng.integers(0, 255, (h, w, 3), dtype=np.uint8)).save(tmp_path / name)
+    recs = [dict(messages=[dict(role="user", content="<image>describe"), dict(role="assistant", content="wide picture")],
+                 images=["a.png"]),
+            dict(messages=[dict(role="user", content="<image>and this?"), dict(role="assistant", content="a square")],
+                 images=["b.png"])]
+    (tmp_path / "train.json").write_text(json.dumps(recs))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    args = load_config(os.path.join(root, "examples/internvl3.5/tiny_native.yaml"),
+                       [f"data.dataset_param.basic_parameters.dataset=[{tmp_path}/train.json]",
+                        f"data.dataset_param.basic_parameters.dataset_dir={tmp_path}"], world_size=1)
+    tr = Trainer(args, device="cpu")
+    assert type(tr.model).__name__ == "InternVLModel" and tr.model.config.image_token_id == 300
+    hist = tr.train()
+    losses = [h["loss"] for h in hist] if hist and isinstance(hist[0], dict) else list(hist)
+    assert len(losses) == 3 and losses[-1] < losses[0]

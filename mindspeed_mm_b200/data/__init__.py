@@ -45,6 +45,13 @@ class _StatefulIter:
             self._it = iter(self.loader)
 
 
+def _vision_of(cfg):
+    """The vision tower's config: ``vision`` on the per-family configs, ``vit`` on the composable one when its tower is the
+    plain ViT."""
+    v = getattr(cfg, "vision", None)
+    return v if v is not None else getattr(cfg, "vit", None)
+
+
 def build_dataset(dataset_param, model=None):
     kind = dataset_param.dataset_type
     cls = data_register.get(kind)
@@ -56,8 +63,13 @@ def build_dataset(dataset_param, model=None):
             basic.setdefault("vocab_size", cfg.text.vocab_size)
             basic.setdefault("image_token_id", cfg.image_token_id)
             basic.setdefault("vision_start_token_id", cfg.vision_start_token_id)
-            basic.setdefault("patch", cfg.vision.patch_size)
-            basic.setdefault("merge", cfg.vision.spatial_merge_size)
+            v = _vision_of(cfg)
+            if v is not None:
+                basic.setdefault("patch", v.patch_size)
+                basic.setdefault("merge", getattr(v, "spatial_merge_size", getattr(v, "merge", 2)))
+                basic.setdefault("temporal_patch", getattr(v, "temporal_patch_size", 2))
+            else:                           # no vision tower (speech / text decoders): text-only samples
+                basic["images_per_sample"] = 0
         return cls(SyntheticVLMSpec(**basic))
     if kind == "synthetic_av_latents":
         from .synthetic import SyntheticAVLatentSpec

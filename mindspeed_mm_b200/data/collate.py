@@ -38,7 +38,12 @@ class PackedVLMCollator:
     def for_config(cls, cfg, **kw) -> "PackedVLMCollator":
         """Collator for a VLM config (``image_token_id``, ``vision``): a config that defines ``rope_index`` /
         ``vision_plan`` (Qwen3-VL) supplies its own position ids and vision plan."""
-        v = cfg.vision
+        v = getattr(cfg, "vision", None)
+        if v is None:                       # the composable model's plain ViT, or no tower at all
+            v = getattr(cfg, "vit", None)
+            merge = getattr(v, "merge", 2)
+            return cls(cfg.image_token_id, cfg.vision_start_token_id, merge=merge, patch=getattr(v, "patch_size", 14),
+                       vision_plan_fn=lambda grid: None, **kw)
         return cls(cfg.image_token_id, cfg.vision_start_token_id, merge=v.spatial_merge_size, patch=v.patch_size,
                    window_size=getattr(v, "window_size", 0), vit_head_dim=v.hidden_size // v.num_heads,
                    rope_index_fn=getattr(cfg, "rope_index", None), vision_plan_fn=getattr(cfg, "vision_plan", None), **kw)

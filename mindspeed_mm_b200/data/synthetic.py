@@ -82,8 +82,11 @@ class SyntheticVLMDataset(Dataset):
         labels = ids.clone()
         labels[(ids == s.image_token_id) | (ids == s.vision_start_token_id)] = -100
         imgs = torch.rand(s.images_per_sample, 3, s.image_size, s.image_size, generator=g)
-        pix = torch.cat([patchify_image(im, s.patch, s.temporal_patch, s.merge) for im in imgs]).to(s.pixel_dtype)
-        grid = torch.tensor([self.grid] * s.images_per_sample, dtype=torch.long)
+        if s.images_per_sample:
+            pix = torch.cat([patchify_image(im, s.patch, s.temporal_patch, s.merge) for im in imgs]).to(s.pixel_dtype)
+        else:
+            pix = torch.zeros(0, 3 * s.temporal_patch * s.patch * s.patch, dtype=s.pixel_dtype)
+        grid = torch.tensor([self.grid] * s.images_per_sample, dtype=torch.long).view(-1, 3)
         return dict(input_ids=ids, labels=labels, pixel_values=pix, image_grid_thw=grid)
 
 

@@ -179,6 +179,18 @@ class _DcpHFConverter:
     fused_linear_names = ("mlp.experts.gate_up_proj", "mlp.experts.down_proj")
     dcp_prefix = "model."
     tie = {"lm_head.weight": "model.language_model.embed_tokens.weight"}
+    # regex -> replacement, first match wins: brings the key layout of older transformers releases (sub-models under
+    # ``language_model.model`` / ``vision_tower``) to the one the current classes (and the trainer) use
+    key_map: Dict[str, str] = {}
+
+    @classmethod
+    def _rename(cls, key: str) -> str:
+        import re
+        for pat, rep in cls.key_map.items():
+            new, n = re.subn(pat, rep, key)
+            if n:
+                return new
+        return key
 
     @classmethod
     def hf_to_dcp(cls, cfg):
@@ -192,7 +204,7 @@ class _DcpHFConverter:
         for k, v in sd.items():
             if any(n in k for n in cls.fused_linear_names) and v.dim() == 3:
                 v = v.reshape(-1, v.shape[-1])
-            out[cls.dcp_prefix + k] = v
+            out[cls.dcp_prefix + cls._rename(k)] = v
         dcp.save({"model": out}, checkpoint_id=os.path.join(cfg["dcp_dir"], "release"), no_dist=True)
         with open(os.path.join(cfg["dcp_dir"], "latest_checkpointed_iteration.txt"), "w") as f:
             f.write("release")
@@ -262,6 +274,73 @@ class Qwen3VLConverter(_DcpHFConverter):
 @register
 class Qwen35Converter(_DcpHFConverter):
     tie = {"lm_head.weight": "model.language_model.embed_tokens.weight"}
+
+
+_LLAVA_STYLE = {r"^language_model\.model": "model.language_model", r"^vision_tower": "model.vision_tower",
+                r"^multi_modal_projector": "model.multi_modal_projector", r"^language_model\.lm_head": "lm_head"}
+
+
+@register
+class InternVLConverter(_DcpHFConverter):
+    """InternVL3 / InternVL3.5 (checkpoint/vlm_model/converters/internvl.py): ``hf_to_dcp`` / ``dcp_to_hf`` with the
+    sub-model prefixes of older exports renamed, ``moe_expert`` for the 30B-A3B and 241B-A28B checkpoints."""
+    key_map = _LLAVA_STYLE
+
+
+@register
+class Mistral3Converter(_DcpHFConverter):
+    """Mistral-Small-3 / Magistral (checkpoint/vlm_model/converters/mistral3.py:38-46: the same renames)."""
+    key_map = _LLAVA_STYLE
+    fused_linear_names = ("gate_up_proj", "down_proj")
+
+
+@register
+class GlmConverter(_DcpHFConverter):
+    """GLM-4.1V / GLM-4.5V (checkpoint/vlm_model/converters/glm.py): keys already follow the current layout."""
+
+
+@register
+class GenericDcpConverter(_DcpHFConverter):
+    """Any Hugging Face checkpoint <-> the trainer's DCP layout with unchanged parameter names (``model_id: hf_auto``
+    and every model whose internal names are the checkpoint's; checkpoint/fsdp/generic_dcp_converter.py)."""
+    fused_linear_names = ()
+
+
+@register
+class LoraConverter:
+    """``merge_lora_to_base``: fold a PEFT adapter (``adapter_model.safetensors`` + ``adapter_config.json``) into the base
+    Hugging Face checkpoint, ``W += (alpha / r) * B @ A`` per target module (checkpoint/common/
+    merge_lora_safetensors_to_base.py, merge_base_lora_weight.py)."""
+
+    @staticmethod
+    def merge_lora_to_base(cfg):
+        from safetensors.torch import load_file
+        base = hfio.load_state_dict(cfg["base_dir"])
+        lora_dir = cfg["lora_dir"]
+        ad = load_file(os.path.join(lora_dir, "adapter_model.safetensors"))
+        with open(os.path.join(lora_dir, "adapter_config.json")) as f:
+            ac = json.load(f)
+        scale = float(cfg.get("scale") or ac["lora_alpha"] / ac["r"])
+        merged, pre = 0, "base_model.model."
+        for k, a in ad.items():
+            if not k.endswith(".lora_A.weight"):
+                continue
+            stem = k[:-len(".lora_A.weight")]
+            b = ad[stem + ".lora_B.weight"]
+            name = (stem[len(pre):] if stem.startswith(pre) else stem) + ".weight"
+            if name not in base:
+                raise KeyError(f"adapter target {name} is not in the base checkpoint")
+            w = base[name]
+            base[name] = (w.float() + scale * (b.float() @ a.float())).to(w.dtype)
+            merged += 1
+        if not merged:
+            raise ValueError(f"no lora_A / lora_B pairs in {lora_dir}")
+        hfio.save_sharded(base, cfg["save_dir"])
+        for f in os.listdir(cfg["base_dir"]):
+            if f.endswith((".json", ".txt", ".jinja")) and f != hfio.INDEX:
+                import shutil
+                shutil.copy(os.path.join(cfg["base_dir"], f), os.path.join(cfg["save_dir"], f))
+        print(f"merged {merged} adapter pairs (scale {scale:g}) into {cfg['save_dir']}")
 
 
 @register

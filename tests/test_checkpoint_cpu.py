@@ -321,3 +321,45 @@ def test_mm_convert_qwen3vl_dcp_and_expert_commands(tmp_path):
                        "--cfg.save_dir", str(tmp_path / "merged")]) == 0
     mg = hfio.load_state_dict(str(tmp_path / "merged"))
     assert all(torch.equal(mg[k], hf[k]) for k in hf)
+
+
+def test_mm_convert_prefix_renames_generic_dcp_and_lora_merge(tmp_path):
+    """InternVL / Mistral3 converters rename the sub-model prefixes of older exports on the way into DCP; the generic
+    converter keeps names; LoraConverter folds a PEFT adapter into its base checkpoint."""
+    import json
+    from safetensors.torch import save_file
+    from torch.distributed.checkpoint.format_utils import dcp_to_torch_save
+    torch.manual_seed(0)
+    old = {"language_model.model.layers.0.self_attn.q_proj.weight": torch.randn(8, 8),
+           "language_model.lm_head.weight": torch.randn(16, 8), "vision_tower.embeddings.cls_token": torch.randn(1, 1, 8),
+           "multi_modal_projector.linear_1.weight": torch.randn(8, 32)}
+    src = tmp_path / "old"
+    hfio.save_sharded(old, str(src))
+    for conv in ("InternVLConverter", "Mistral3Converter"):
+        out = tmp_path / conv
+        assert mm_convert([conv, "hf_to_dcp", "--cfg.hf_dir", str(src), "--cfg.dcp_dir", str(out)]) == 0
+        dcp_to_torch_save(str(out / "release"), str(out / "flat.pt"))
+        flat = torch.load(out / "flat.pt", weights_only=False)["model"]
+        assert set(flat) == {"model.model.language_model.layers.0.self_attn.q_proj.weight", "model.lm_head.weight",
+                             "model.model.vision_tower.embeddings.cls_token", "model.model.multi_modal_projector.linear_1.weight"}
+    assert mm_convert(["GenericDcpConverter", "hf_to_dcp", "--cfg.hf_dir", str(src), "--cfg.dcp_dir", str(tmp_path / "g")]) == 0
+    assert mm_convert(["GenericDcpConverter", "dcp_to_hf", "--cfg.load_dir", str(tmp_path / "g"), "--cfg.save_dir",
+                       str(tmp_path / "gb")]) == 0
+    back = hfio.load_state_dict(str(tmp_path / "gb"))
+    assert set(back) == set(old) and all(torch.equal(back[k], old[k]) for k in old)
+    # LoRA merge
+    base = {"model.layers.0.self_attn.q_proj.weight": torch.randn(8, 8), "model.norm.weight": torch.ones(8)}
+    bdir, ldir = tmp_path / "base", tmp_path / "lora"
+    hfio.save_sharded(base, str(bdir))
+    json.dump({"model_type": "qwen3"}, open(bdir / "config.json", "w"))
+    ldir.mkdir()
+    A, B = torch.randn(2, 8), torch.randn(8, 2)
+    save_file({"base_model.model.model.layers.0.self_attn.q_proj.lora_A.weight": A,
+               "base_model.model.model.layers.0.self_attn.q_proj.lora_B.weight": B}, str(ldir / "adapter_model.safetensors"))
+    json.dump({"r": 2, "lora_alpha": 4.0, "target_modules": ["q_proj"]}, open(ldir / "adapter_config.json", "w"))
+    assert mm_convert(["LoraConverter", "merge_lora_to_base", "--cfg.base_dir", str(bdir), "--cfg.lora_dir", str(ldir),
+                       "--cfg.save_dir", str(tmp_path / "merged_lora")]) == 0
+    mg = hfio.load_state_dict(str(tmp_path / "merged_lora"))
+    want = base["model.layers.0.self_attn.q_proj.weight"] + 2.0 * (B @ A)
+    assert torch.allclose(mg["model.layers.0.self_attn.q_proj.weight"], want, atol=1e-6)
+    assert torch.equal(mg["model.norm.weight"], base["model.norm.weight"]) and (tmp_path / "merged_lora" / "config.json").exists()

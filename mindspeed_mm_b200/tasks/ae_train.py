@@ -3,8 +3,8 @@ generator / discriminator step (mindspeed_mm/models/ae/training/training.py, min
 
 * ``NLayerDiscriminator3D`` -- PatchGAN over (T, H, W): strided 3-D convolutions with LeakyReLU, hinge loss.
 * ``VAELoss``               -- L1 (or L2) reconstruction, KL of the diagonal Gaussian posterior, an optional
-                               perceptual callable (LPIPS weights are not bundled; any ``f(x, y) -> per-sample
-                               distance`` plugs in), and the generator's adversarial term with the adaptive weight
+                               perceptual callable (``models/ae/lpips.py: LPIPS`` with the published weight
+                               files, or any ``f(x, y) -> per-sample distance``), and the generator's adversarial term with the adaptive weight
                                ``|grad_rec| / |grad_gan|`` taken at the decoder's last layer.
 * ``AETrainer``             -- alternates a generator step and a discriminator step once ``disc_start`` is reached.
 """

@@ -116,3 +116,39 @@ def test_ae_trainer_moving_average_follows_the_weights():
     assert torch.allclose(lin.weight, w0 + 0.5)
     ema.restore()
     assert torch.allclose(lin.weight, w0 + 1.0)
+
+
+def test_lpips_structure_loading_and_use_as_perceptual_term(tmp_path):
+    import torch
+    from mindspeed_mm_b200.models.ae.lpips import LPIPS, _CHANNELS
+    from mindspeed_mm_b200.tasks.ae_train import VAELoss
+    torch.manual_seed(0)
+    net = LPIPS(use_dropout=True)
+    # key layout of the published files: torchvision VGG-16 features + LPIPS linear heads
+    assert getattr(net.net.slice3, "10").weight.shape == (256, 128, 3, 3) and net.lin4.model[1].weight.shape == (1, 512, 1, 1)
+    assert all(not p.requires_grad for p in net.parameters())
+    vgg = {}
+    cin = 3
+    for idxs, c in zip(((0, 2), (5, 7), (10, 12, 14), (17, 19, 21), (24, 26, 28)), _CHANNELS):
+        for i in idxs:
+            vgg[f"features.{i}.weight"], vgg[f"features.{i}.bias"] = torch.randn(c, cin, 3, 3) * 0.05, torch.zeros(c)
+            cin = c
+    vgg["classifier.0.weight"] = torch.zeros(4, 4)
+    lin = {f"lin{i}.model.1.weight": torch.rand(1, c, 1, 1) for i, c in enumerate(_CHANNELS)}
+    torch.save(vgg, tmp_path / "vgg16.pth")
+    torch.save(lin, tmp_path / "vgg.pth")
+    net = LPIPS(str(tmp_path / "vgg.pth"), str(tmp_path / "vgg16.pth"))
+    assert torch.equal(getattr(net.net.slice4, "19").weight, vgg["features.19.weight"]) and torch.equal(net.lin2.model[1].weight, lin["lin2.model.1.weight"])
+    x = torch.rand(2, 3, 32, 32) * 2 - 1
+    y = (x + 0.3 * torch.randn_like(x)).clamp(-1, 1).requires_grad_()
+    d0, d1 = net(x, x), net(x, y)
+    assert d0.shape == (2,) and float(d0.abs().max()) == 0.0 and (d1 > 0).all()
+    d1.sum().backward()
+    assert y.grad is not None and float(y.grad.abs().sum()) > 0
+    net.train()
+    assert not net.training                                    # scoring stays deterministic
+    v = torch.rand(1, 3, 2, 32, 32) * 2 - 1
+    assert net(v, v.flip(2)).shape == (1,)
+    loss = VAELoss(perceptual=net, perceptual_weight=0.5)
+    out = loss.generator(x, y, torch.zeros(2, 4, 4, 4), torch.zeros(2, 4, 4, 4), step=0)
+    assert torch.isfinite(out[0] if isinstance(out, tuple) else out).all()

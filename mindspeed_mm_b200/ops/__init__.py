@@ -423,3 +423,8 @@ class LayerNorm(torch.nn.LayerNorm):
         if len(self.normalized_shape) != 1:
             return super().forward(x)
         return layer_norm(x, self.weight, self.bias, self.eps)
+
+
+if os.environ.get("MM_B200_SANITIZE", "") not in ("", "0"):
+    from . import sanitize as _sanitize
+    _sanitize.enable()

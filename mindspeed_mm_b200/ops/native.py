@@ -126,11 +126,25 @@ def _eager(op: str, x, why: str):
     _ops._fallback(op, x, why)
 
 
+SYNC_CHECK = False   # ops/sanitize.py: synchronise after every native call and read the status word, so that an
+                     # asynchronous error is reported under the name of the op that launched it
+
+
 def _check(rc: int, what: str):
     global LAUNCHES
     LAUNCHES += 1
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")
+    if SYNC_CHECK and torch.cuda.is_available():
+        try:
+            torch.cuda.synchronize()
+        except RuntimeError as e:
+            raise RuntimeError(f"{what}: device error surfaced after this launch: {e}") from e
+        for key, word in _status_words.items():
+            v = int(word.item())
+            if v:
+                word.zero_()
+                raise RuntimeError(f"{what}: a bounded wait ran out on device {key} (status {v})")
 
 
 _status_words: dict = {}

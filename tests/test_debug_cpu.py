@@ -66,3 +66,35 @@ def test_plan_search_respects_memory_and_prefers_less_communication():
     assert small_mem[0]["ulysses"] > 1 and small_mem[0]["pp"] == 1
     # heads must divide over ulysses x tp
     assert all(28 % (p["ulysses"] * p["tp"]) == 0 for p in dbg.suggest_parallel_plan(m, dbg.Hardware(n_gpus=8), top=50))
+
+
+def test_sanitize_mode_poisons_allocations_and_names_the_op():
+    import torch
+    from mindspeed_mm_b200 import ops
+    from mindspeed_mm_b200.ops import native, sanitize
+    x = torch.randn(4, 16)
+    w = torch.ones(16)
+    plain = ops.rms_norm
+    with sanitize.debug_mode():
+        assert torch.isnan(torch.empty(3, 5)).all() and torch.isnan(torch.empty_like(x)).all()
+        assert int(x.new_empty(2, dtype=torch.int32)[0]) == 0x7F7F7F7F and native.SYNC_CHECK
+        assert ops.rms_norm is not plain
+        y = ops.rms_norm(x, w, 1e-6)                       # a healthy op passes through unchanged
+        assert torch.allclose(y, plain(x, w, 1e-6))
+        # an op that leaves part of its output unwritten: the hole is NaN and the wrapper names the op
+        def leaky(a):
+            out = torch.empty_like(a)
+            out[:2] = a[:2]
+            return out
+        wrapped = sanitize._wrap_op("leaky", leaky)
+        try:
+            wrapped(x)
+            raise AssertionError("the unwritten rows went unnoticed")
+        except FloatingPointError as e:
+            assert "ops.leaky" in str(e) and "50.00%" in str(e)
+        # non-finite inputs are the caller's business
+        bad_in = x.clone()
+        bad_in[0, 0] = float("inf")
+        ops.rms_norm(bad_in, w, 1e-6)
+    assert ops.rms_norm is plain and not native.SYNC_CHECK and not torch.isnan(torch.zeros(2) + torch.empty(2).fill_(0)).any()
+    assert torch.empty is not None and "alloc" not in getattr(torch.empty, "__qualname__", "")

@@ -152,3 +152,26 @@ def test_lpips_structure_loading_and_use_as_perceptual_term(tmp_path):
     loss = VAELoss(perceptual=net, perceptual_weight=0.5)
     out = loss.generator(x, y, torch.zeros(2, 4, 4, 4), torch.zeros(2, 4, 4, 4), step=0)
     assert torch.isfinite(out[0] if isinstance(out, tuple) else out).all()
+
+
+def test_context_parallel_vae_matches_single_process():
+    """Frames split over 3 gloo ranks (halo exchange for the causal convolutions, group-norm statistics over all ranks,
+    first-frame handling of the temporal up-sampling on rank 0 only): moments, reconstruction, gradients."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
+           "--master-port", str(29700 + os.getpid() % 200), os.path.join(here, "dist_cp_vae_check.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert r.returncode == 0 and "ok=True" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_frame_counts_for_context_parallel_split():
+    from mindspeed_mm_b200.parallel.cp.vae import frame_counts
+    assert frame_counts(21, 2, 4) == [13, 8] and frame_counts(33, 4, 4) == [9, 8, 8, 8] and sum(frame_counts(49, 5, 4)) == 49
+    import pytest
+    with pytest.raises(ValueError):
+        frame_counts(20, 2, 4)
+    with pytest.raises(ValueError):
+        frame_counts(5, 2, 4)

@@ -149,6 +149,12 @@ def test_encoder_data_balance_inside_the_model_gloo():
     assert "ok=True" in _run_script(2, "dist_balance_check.py")
 
 
+def test_gloo_world4_dynamic_dp_cp_switches_groups_and_exchanges_batches():
+    """Per-iteration dp x cp choice from the longest sequence of all ranks; groups of every split prepared once; the
+    members of a context-parallel group end up with the same list of batches."""
+    assert "ok=True" in _run_script(4, "dist_dpcp_check.py")
+
+
 def test_native_trainer_moe_recipe_with_expert_parallel_gloo():
     """examples/qwen3vl/tiny_moe_native.yaml end to end: dense engine + expert engine (EngineMux), EP = 2."""
     root = os.path.dirname(HERE)

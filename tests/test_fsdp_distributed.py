@@ -149,6 +149,13 @@ def test_encoder_data_balance_inside_the_model_gloo():
     assert "ok=True" in _run_script(2, "dist_balance_check.py")
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_gloo_packed_sequence_context_parallel(world):
+    """Packed (document-boundary) stream cut into equal chunks, keys / values all-gathered, one varlen call per rank with
+    bottom-right causal segments: outputs and q / k / v gradients equal the single-process attention."""
+    assert "ok=True" in _run_script(world, "dist_packed_cp_check.py")
+
+
 def test_gloo_world4_dynamic_dp_cp_switches_groups_and_exchanges_batches():
     """Per-iteration dp x cp choice from the longest sequence of all ranks; groups of every split prepared once; the
     members of a context-parallel group end up with the same list of batches."""

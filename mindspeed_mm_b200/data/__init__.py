@@ -71,6 +71,15 @@ def build_dataset(dataset_param, model=None):
             else:                           # no vision tower (speech / text decoders): text-only samples
                 basic["images_per_sample"] = 0
         return cls(SyntheticVLMSpec(**basic))
+    if kind == "synthetic_asr":
+        from .synthetic import SyntheticASRSpec
+        cfg = getattr(model, "config", None)
+        if cfg is not None and getattr(cfg, "audio", None) is not None:
+            basic.setdefault("vocab_size", cfg.text.vocab_size)
+            basic.setdefault("audio_token_id", cfg.audio_token_id)
+            basic.setdefault("n_mels", cfg.audio.num_mel_bins)
+            basic.setdefault("n_window", cfg.audio_window)
+        return cls(SyntheticASRSpec(**basic))
     if kind == "synthetic_av_latents":
         from .synthetic import SyntheticAVLatentSpec
         return cls(SyntheticAVLatentSpec(**basic))
@@ -93,6 +102,9 @@ def build_collator(args, model, pin: bool):
         from .anyres import TiledPackCollator
         vit = cfg.vit
         return TiledPackCollator(vit.patch_size, vit.merge, vit.temporal_patch_size)
+    if args.data.dataset_param.dataset_type == "synthetic_asr":
+        from .synthetic import ASRPackCollator
+        return ASRPackCollator()
     if args.data.dataset_param.dataset_type == "internvl" or "internvl" in name:
         from .internvl import TilePackCollator
         return TilePackCollator.for_config(cfg, pin=pin)

@@ -161,6 +161,72 @@ class SyntheticSpeechDataset(Dataset):
                     ref_mel=torch.randn(s.ref_frames, s.n_mels, generator=g))
 
 
+# ------------------------------------------------------------------------------------------------- speech recognition
+def audio_token_count(frames: int, n_window: int) -> int:
+    """Embeddings the windowed audio tower (``models/encoders.py: WindowedAudioEncoder``) returns for a clip of ``frames``
+    mel frames: windows of ``2 * n_window`` frames, a stride-2 convolution per window, then pairs averaged."""
+    win = 2 * n_window
+    total = sum((min(win, frames - s) + 1) // 2 for s in range(0, frames, win))
+    return 1 if total == 1 else total // 2
+
+
+@dataclass
+class SyntheticASRSpec:
+    """Speech-recognition samples for the audio-conditioned decoders (FunASR, Qwen3-ASR, the omni models): a mel clip,
+    its placeholder tokens, then the transcript, which is the only supervised span."""
+    num_samples: int = 64
+    frames: int = 120                 # longest clip (mel frames); clips are drawn from [frames / 2, frames]
+    text_len: int = 24
+    n_mels: int = 16
+    n_window: int = 20
+    vocab_size: int = 1000
+    audio_token_id: int = 999
+    seed: int = 0
+
+
+@data_register.register("synthetic_asr")
+class SyntheticASRDataset(Dataset):
+    def __init__(self, spec: SyntheticASRSpec):
+        self.spec = spec
+
+    def __len__(self):
+        return self.spec.num_samples
+
+    def __getitem__(self, i):
+        s = self.spec
+        g = torch.Generator().manual_seed(s.seed * 1_000_003 + i)
+        frames = int(torch.randint(max(8, s.frames // 2), s.frames + 1, (1,), generator=g))
+        n_text = int(torch.randint(max(2, s.text_len // 2), s.text_len + 1, (1,), generator=g))
+        n_audio = audio_token_count(frames, s.n_window)
+        text = torch.randint(0, min(s.vocab_size, s.audio_token_id) - 1, (n_text,), generator=g)
+        ids = torch.cat([torch.full((n_audio,), s.audio_token_id), text])
+        labels = ids.clone()
+        labels[:n_audio] = -100
+        return dict(input_ids=ids, labels=labels, audio_features=torch.randn(s.n_mels, frames, generator=g))
+
+
+class ASRPackCollator:
+    """Packs speech-recognition samples: next-token labels inside each sample, 1-D positions, ``cu_seqlens``, the list of
+    mel clips in sample order."""
+
+    def __init__(self, ignore_index: int = -100):
+        self.ignore_index = ignore_index
+
+    def __call__(self, samples):
+        ids, labels, pos, lens, mels = [], [], [], [], []
+        for s in samples:
+            i, l = s["input_ids"], s["labels"]
+            ids.append(i)
+            labels.append(torch.cat([l[1:], l.new_full((1,), self.ignore_index)]))
+            pos.append(torch.arange(len(i)))
+            lens.append(len(i))
+            mels.append(s["audio_features"])
+        input_ids = torch.cat(ids)
+        cu = torch.tensor([0] + lens).cumsum(0).to(torch.int32)
+        return dict(input_ids=input_ids, labels=torch.cat(labels), position_ids=torch.cat(pos), cu_seqlens=cu,
+                    max_seqlen=max(lens), audio_features=mels, n_tokens=int(input_ids.numel()))
+
+
 # ------------------------------------------------------------------------------------------------- audio + video latents
 @dataclass
 class SyntheticAVLatentSpec:

@@ -147,7 +147,8 @@ class WhisperEncoder(nn.Module):
         self.c = c
         self.conv1 = nn.Conv1d(c.num_mel_bins, c.d_model, 3, padding=1)
         self.conv2 = nn.Conv1d(c.d_model, c.d_model, 3, stride=2, padding=1)
-        self.register_buffer("positions", sinusoid_positions(c.max_source_positions, c.d_model), persistent=False)
+        # the sinusoid table is computed on demand: a buffer would stay on the meta device when the model is built there
+        self._positions: dict = {}
         self.layers = nn.ModuleList(WhisperLayer(c) for _ in range(c.num_layers))
         self.ln_post = ops.LayerNorm(c.d_model, eps=c.eps)
 
@@ -155,7 +156,12 @@ class WhisperEncoder(nn.Module):
         """mel [B, n_mels, frames] -> [B, frames/2, d] with positions added."""
         x = ops.gelu(self.conv1(mel))
         x = ops.gelu(self.conv2(x)).transpose(1, 2)
-        return x + self.positions[: x.shape[1]].to(x.dtype)
+        key = (x.device, x.dtype)
+        if key not in self._positions:
+            base = getattr(self, "_loaded_positions", None)
+            base = base if base is not None else sinusoid_positions(self.c.max_source_positions, self.c.d_model)
+            self._positions[key] = base.to(x.device, x.dtype)
+        return x + self._positions[key][: x.shape[1]]
 
     def forward(self, mel):
         x = self.embed(mel)
@@ -171,7 +177,9 @@ class WhisperEncoder(nn.Module):
         for n in ("conv1", "conv2"):
             getattr(self, n).weight.data.copy_(g(f"{n}.weight"))
             getattr(self, n).bias.data.copy_(g(f"{n}.bias"))
-        self.positions.copy_(g("embed_positions.weight"))
+        table = g("embed_positions.weight")               # the published table (the same sinusoids) replaces the computed one
+        self._positions = {(table.device, table.dtype): table.clone()}
+        self._loaded_positions = table.clone()
         for kind in ("weight", "bias"):
             getattr(self.ln_post, kind).data.copy_(g(f"layer_norm.{kind}"))
         for i, l in enumerate(self.layers):

@@ -159,21 +159,33 @@ class _StatePass(torch.autograd.Function):
         dev = W.device
         cdt = W.dtype                       # bf16 on a GPU (tensor-core batched products), fp32 on CPU
         dO = dO.to(cdt)
-        dVn = torch.empty(H, NC, CHUNK, V, dtype=cdt, device=dev)
-        dSn_all = torch.empty(H, NC, K, V, dtype=cdt, device=dev)     # gradient w.r.t. the state after each chunk
-        dS_seq = torch.zeros(H, lay.nseq, K, V, dtype=torch.float32, device=dev)
-        QgT_dO = Qg.transpose(-1, -2) @ dO                            # [H, NC, K, V]   batched once
-        AtT_dO = At.transpose(-1, -2) @ dO                            # [H, NC, 64, V]
-        for j in range(lay.max_chunks - 1, -1, -1):
-            idx, sidx = lay.idx_at[j], lay.seq_at[j]
-            dSn = dS_seq[:, sidx]                                     # fp32 [H, n, K, V]
-            dSn_c = dSn.to(cdt)
-            dSn_all[:, idx] = dSn_c
-            dvn = AtT_dO[:, idx] + Kd[:, idx] @ dSn_c
-            dVn[:, idx] = dvn
-            gam = gamma[:, idx, None, None] if gamma.dim() == 2 else gamma[:, idx, :, None]
-            dS_prev = QgT_dO[:, idx].float() + gam * dSn - (W[:, idx].transpose(-1, -2) @ dvn).float()
-            dS_seq[:, sidx] = dS_prev
+        if W.is_cuda and _native_bwd_ok():
+            # the walk over the chunks (last to first) is one kernel per (sequence, head): tcgen05, gradient state in TMEM
+            from . import native
+            dOb = dO.to(torch.bfloat16).contiguous()
+            dVn = torch.empty(H, NC, CHUNK, V, dtype=torch.bfloat16, device=dev)
+            GnT = torch.empty(H, NC, V, K, dtype=torch.bfloat16, device=dev)
+            native._check(native.lib().mm_gdn_bwd(
+                W.data_ptr(), Qg.data_ptr(), Kd.data_ptr(), At.data_ptr(), dOb.data_ptr(), gamma.data_ptr(),
+                lay.seq_chunks.data_ptr(), dVn.data_ptr(), GnT.data_ptr(), H, NC, lay.nseq, int(gamma.dim() == 3),
+                native.status_word(dev).data_ptr(), native._st()), "gdn_bwd")
+            dSn_all = GnT.transpose(-1, -2)
+        else:
+            dVn = torch.empty(H, NC, CHUNK, V, dtype=cdt, device=dev)
+            dSn_all = torch.empty(H, NC, K, V, dtype=cdt, device=dev)     # gradient w.r.t. the state after each chunk
+            dS_seq = torch.zeros(H, lay.nseq, K, V, dtype=torch.float32, device=dev)
+            QgT_dO = Qg.transpose(-1, -2) @ dO                            # [H, NC, K, V]   batched once
+            AtT_dO = At.transpose(-1, -2) @ dO                            # [H, NC, 64, V]
+            for j in range(lay.max_chunks - 1, -1, -1):
+                idx, sidx = lay.idx_at[j], lay.seq_at[j]
+                dSn = dS_seq[:, sidx]                                     # fp32 [H, n, K, V]
+                dSn_c = dSn.to(cdt)
+                dSn_all[:, idx] = dSn_c
+                dvn = AtT_dO[:, idx] + Kd[:, idx] @ dSn_c
+                dVn[:, idx] = dvn
+                gam = gamma[:, idx, None, None] if gamma.dim() == 2 else gamma[:, idx, :, None]
+                dS_prev = QgT_dO[:, idx].float() + gam * dSn - (W[:, idx].transpose(-1, -2) @ dvn).float()
+                dS_seq[:, sidx] = dS_prev
         dU = dVn
         dW = -(dVn @ SprevT.to(cdt))                                  # [64, V] @ [V, K]
         dQg = dO @ SprevT.to(cdt)
@@ -182,6 +194,14 @@ class _StatePass(torch.autograd.Function):
         dgamma = (dSn_all.float() * SprevT.float().transpose(-1, -2)).sum((-1, -2) if gamma.dim() == 2 else -1)
         outs = (dW, dQg, dKd, dAt, dU, dgamma)
         return tuple(o.to(dt) for o, dt in zip(outs, ctx.in_dtypes)) + (None,)
+
+
+def _native_bwd_ok() -> bool:
+    """The backward walk kernel: on unless ``MM_B200_GDN_BWD_KERNEL=0`` (the PyTorch loop then runs instead)."""
+    import os
+    from . import native
+    native.lib()
+    return os.environ.get("MM_B200_GDN_BWD_KERNEL", "1") != "0" and native._STATUS.get("mm_gdn_bwd", False)
 
 
 def state_pass(W, Qg, Kd, At, U, gamma, layout: ChunkLayout):

@@ -86,6 +86,7 @@ def _declare(L):
         "mm_l2norm_bwd": [_p, _p, _p, _p, _ll, _i, _p],
         "mm_gdn_prologue": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _p],
         "mm_gdn_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p],
+        "mm_gdn_bwd": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p, _p],
         "mm_p2p_scatter_rows": [_p, _p, _p, _p, _p, _i, _i, _i, _p],
         "mm_p2p_gather_rows": [_p, _p, _p, _p, _i, _i, _i, _p],
         "mm_p2p_copy": [_p, _p, _ll, _i, _p],

@@ -1,6 +1,6 @@
 """Per-kernel timing on one GPU: CUDA events, >=3 warm-ups, L2 flushed between timed iterations.
 
-    python benchmarks/bench_ops.py [--ops gemm,gemm_swiglu,elementwise,lce,fmha,gdn,vit_attention,grouped_gemm,small_ops] [--out FILE] [--small]
+    python benchmarks/bench_ops.py [--ops gemm,gemm_swiglu,elementwise,lce,fmha,gdn,vit_attention,grouped_gemm,small_ops,sparse_attention] [--out FILE] [--small]
 
 Prints one JSON line per case: achieved TFLOP/s or GB/s and the fraction of the measured peaks in
 MEASURED_PEAKS.json (fallback 1590 TFLOP/s / 6650 GB/s when the file is absent).  ``--small`` keeps
@@ -384,6 +384,32 @@ def bench_gdn(out, small):
         native.check_status()
 
 
+def bench_sparse_attention(out, small):
+    """Sliding-tile attention of a video DiT (HunyuanVideo-1.5 layout: tiles of 6 x 8 x 8 = 384 tokens, 3 x 3 x 3 window,
+    256 trailing text tokens) against dense attention over the same tokens, forward and forward + backward; the sparse
+    path is the gather of the selected key blocks + one packed varlen call."""
+    from mindspeed_mm_b200.ops import sparse_attention as sa
+    cases = [("12x32x48", (12, 32, 48), 8)] if small else [("18x48x80", (18, 48, 80), 8), ("30x48x80", (30, 48, 80), 8)]
+    for name, canvas, N in cases:
+        S = canvas[0] * canvas[1] * canvas[2] + 256
+        q, k, v = (torch.randn(1, S, N, 128, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+        with torch.no_grad():
+            _, density = sa.ssta_attention(q, k, v, canvas, kernel=(3, 3, 3), text_len=256, mode="sta")
+            t_sta = time_fn(lambda: sa.ssta_attention(q, k, v, canvas, kernel=(3, 3, 3), text_len=256, mode="sta"), iters=5)
+            t_dense = time_fn(lambda: ops.attention_dense(q, k, v), iters=5)
+        ins = [t.clone().requires_grad_() for t in (q, k, v)]
+
+        def fb(mode):
+            o = sa.ssta_attention(*ins, canvas, kernel=(3, 3, 3), text_len=256, mode=mode)[0]
+            o.backward(torch.ones_like(o))
+        t_sta_fb = time_fn(lambda: fb("sta"), iters=3, warmup=2)
+        t_dense_fb = time_fn(lambda: fb("dense"), iters=3, warmup=2)
+        emit(dict(op="sta_attention", case=name, tokens=S, heads=N, density=round(density, 3), sta_fwd_ms=round(t_sta, 3),
+                  dense_fwd_ms=round(t_dense, 3), fwd_speedup=round(t_dense / t_sta, 2), sta_fwd_bwd_ms=round(t_sta_fb, 3),
+                  dense_fwd_bwd_ms=round(t_dense_fb, 3), fwd_bwd_speedup=round(t_dense_fb / t_sta_fb, 2)), out)
+        native.check_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ops", default="gemm,elementwise")
@@ -392,7 +418,8 @@ def main():
     a = ap.parse_args()
     for op in a.ops.split(","):
         {"gemm": bench_gemm, "gemm_swiglu": bench_gemm_swiglu, "elementwise": bench_elementwise, "lce": bench_lce, "fmha": bench_fmha, "gdn": bench_gdn,
-         "vit_attention": bench_vit_attention, "grouped_gemm": bench_grouped_gemm, "small_ops": bench_small_ops}[op](a.out, a.small)
+         "vit_attention": bench_vit_attention, "grouped_gemm": bench_grouped_gemm, "small_ops": bench_small_ops,
+         "sparse_attention": bench_sparse_attention}[op](a.out, a.small)
 
 
 if __name__ == "__main__":

@@ -484,3 +484,54 @@ class VideoTextDataset(Dataset):
         mask = [1] * len(ids) + [0] * (self.text_len - len(ids))
         ids = ids + [0] * (self.text_len - len(ids))
         return dict(video=self._frames(r["path"]), prompt_ids=torch.tensor(ids), prompt_mask=torch.tensor(mask))
+
+
+@data_register.register("dreambooth")
+class DreamBoothDataset(VideoTextDataset):
+    """Subject fine-tuning data in the layout of the diffusers DreamBooth scripts the reference's examples drive
+    (examples/diffusers/{flux,sd3,sdxl}/finetune_*_dreambooth*.sh: ``--instance_data_dir`` + ``--instance_prompt``, optional
+    ``--class_data_dir`` + ``--class_prompt`` for prior preservation): every image of ``instance_data_dir`` with the
+    instance prompt; with a class folder each item also carries a class image and prompt (``class_video`` /
+    ``class_prompt_ids`` / ``class_prompt_mask``), which the trainer weighs by ``prior_loss_weight``.  Items have the fields
+    of ``VideoTextDataset`` (an image is a one-frame clip)."""
+
+    EXT = (".png", ".jpg", ".jpeg", ".bmp", ".webp")
+
+    def __init__(self, dataset_param=None, model=None, *, instance_data_dir: str = "", instance_prompt: str = "",
+                 class_data_dir: str = "", class_prompt: str = "", repeats: int = 1, **kw):
+        if dataset_param is not None:
+            basic = dict(getattr(dataset_param, "basic_parameters", None) or {})
+            instance_data_dir = basic.get("instance_data_dir", instance_data_dir)
+            instance_prompt = basic.get("instance_prompt", instance_prompt)
+            class_data_dir = basic.get("class_data_dir", class_data_dir)
+            class_prompt = basic.get("class_prompt", class_prompt)
+            repeats = int(basic.get("repeats", repeats))
+            pre = dict(getattr(dataset_param, "preprocess_parameters", None) or {})
+            kw.setdefault("height", int(pre.get("resolution", pre.get("max_height", 1024))))
+            kw.setdefault("width", int(pre.get("resolution", pre.get("max_width", 1024))))
+            kw.setdefault("text_len", int(pre.get("text_len", 512)))
+            tp = (pre.get("tokenizer_config") or {}).get("from_pretrained")
+            if kw.get("tokenizer") is None and tp and os.path.exists(tp):
+                from transformers import AutoTokenizer
+                kw["tokenizer"] = AutoTokenizer.from_pretrained(tp)
+        if not instance_data_dir or not os.path.isdir(instance_data_dir):
+            raise ValueError(f"instance_data_dir {instance_data_dir!r} is not a directory")
+        super().__init__(None, model, files=[], num_frames=1, **kw)
+        listing = lambda d: sorted(os.path.join(d, f) for f in os.listdir(d) if f.lower().endswith(self.EXT))
+        self.records = [{"path": p, "cap": instance_prompt} for p in listing(instance_data_dir)] * max(1, repeats)
+        if not self.records:
+            raise ValueError(f"no images under {instance_data_dir}")
+        self.class_records = [{"path": p, "cap": class_prompt} for p in listing(class_data_dir)] if class_data_dir else []
+        self.folder = ""
+
+    def __getitem__(self, i):
+        item = super().__getitem__(i)
+        if self.class_records:
+            keep, self.records = self.records, self.class_records
+            try:
+                c = super().__getitem__(i % len(self.class_records))
+            finally:
+                self.records = keep
+            item.update(class_video=c["video"], class_prompt_ids=c["prompt_ids"], class_prompt_mask=c["prompt_mask"])
+        return item
+

@@ -336,10 +336,12 @@ class SoRAModel(nn.Module):
     flow-matching loss; one timestep is drawn per micro-batch from ``generator``.
     """
 
-    def __init__(self, predictor: nn.Module, scheduler, ae=None, text_encoder=None, seed: int = 0):
+    def __init__(self, predictor: nn.Module, scheduler, ae=None, text_encoder=None, seed: int = 0,
+                 prior_loss_weight: float = 1.0):
         super().__init__()
         self.predictor, self.scheduler, self.ae, self.text_encoder = predictor, scheduler, ae, text_encoder
         self.generator = torch.Generator().manual_seed(seed)
+        self.prior_loss_weight = prior_loss_weight
 
     def fsdp_units(self):
         return self.predictor.fsdp_units()
@@ -350,6 +352,14 @@ class SoRAModel(nn.Module):
         return f() if callable(f) else None
 
     def forward(self, batch: dict, run=None):
+        loss = self._loss(batch, run)
+        if "class_video" in batch or "class_latents" in batch:
+            # prior preservation (DreamBooth): the same objective on a class sample, weighted
+            prior = {k[len("class_"):]: v for k, v in batch.items() if k.startswith("class_")}
+            loss = loss + self.prior_loss_weight * self._loss(prior, run)
+        return loss
+
+    def _loss(self, batch: dict, run=None):
         with torch.no_grad():
             latents = batch["latents"] if "latents" in batch else self.ae.encode(batch["video"])
             prompt = batch["prompt"] if "prompt" in batch else self.text_encoder.encode(batch["prompt_ids"], batch.get("prompt_mask"))

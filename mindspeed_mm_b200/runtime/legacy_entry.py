@@ -59,7 +59,15 @@ def model_provider(kind: str, args):
         from ..models.towers import build_ae, build_text_encoder
         ae = None if mm.get("load_video_features", True) else build_ae(mm.get("ae"))
         te = None if mm.get("load_text_features", True) else build_text_encoder(mm.get("text_encoder"))
-        return SoRAModel(net, build_scheduler(mm.get("diffusion", {})), ae=ae, text_encoder=te, seed=args.seed)
+        lora = mm.get("lora") or {}
+        if lora.get("enable"):                       # adapters on the predictor's projections, everything else frozen
+            from types import SimpleNamespace
+            from ..tasks.lora import apply_lora
+            apply_lora(net, SimpleNamespace(rank=int(lora.get("rank", 16)), alpha=float(lora.get("alpha", 16)),
+                                            dropout=float(lora.get("dropout", 0.0)),
+                                            target_modules=list(lora.get("target_modules") or [])))
+        return SoRAModel(net, build_scheduler(mm.get("diffusion", {})), ae=ae, text_encoder=te, seed=args.seed,
+                         prior_loss_weight=float(mm.get("prior_loss_weight", 1.0)))
     raise ValueError(f"unknown entry kind {kind}")
 
 
@@ -85,6 +93,11 @@ def _real_dataset(data: dict, model):
     except KeyError:
         return None
     basic = dp.get("basic_parameters") or {}
+    if kind == "dreambooth":                     # a folder of subject images, no index file
+        if not os.path.isdir(basic.get("instance_data_dir") or ""):
+            return None
+        return cls(_Namespace(dict(dataset_type=kind, basic_parameters=basic,
+                                   preprocess_parameters=dp.get("preprocess_parameters") or {})), model=model)
     src = basic.get("dataset") or basic.get("data_path") or basic.get("index")
     files = [src] if isinstance(src, str) else list(src or [])
     root = basic.get("dataset_dir") or basic.get("data_folder") or ""

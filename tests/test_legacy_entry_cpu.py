@@ -93,3 +93,44 @@ def test_pretrain_vlm_reads_a_sharegpt_json_with_the_reference_data_schema(tmp_p
     resumed = next(datasets_provider("vlm", args, model, ps, consumed_samples=3))
     assert resumed["input_ids"].shape != first["input_ids"].shape or not torch.equal(resumed["input_ids"], first["input_ids"])
     _reset()
+
+
+def test_pretrain_sora_dreambooth_lora_with_prior_preservation(tmp_path):
+    """DreamBooth-style subject fine-tuning through the generative entry point: images of a folder with an instance prompt,
+    class images for the prior term, raw pixels encoded by the frozen VAE / text encoder, LoRA adapters on the
+    predictor's attention projections as the only trainable parameters."""
+    import numpy as np
+    from PIL import Image
+    from mindspeed_mm_b200.runtime.legacy_entry import pretrain
+    rng = np.random.default_rng(0)
+    inst, cls = tmp_path / "dog", tmp_path / "class"
+    inst.mkdir()
+    cls.mkdir()
+    for d, n in ((inst, 4), (cls, 2)):
+        for i in range(n):
+            Image.fromarray(rng.integers(0, 255, (40, 48, 3), dtype=np.uint8)).save(d / f"{i}.png")
+    model = {
+        "load_video_features": False, "load_text_features": False, "task": "t2v",
+        "diffusion": {"model_id": "wan_flow_match_scheduler", "num_train_timesteps": 1000, "shift": 5, "sigma_min": 0.0,
+                      "extra_one_step": True},
+        "predictor": {"model_id": "wandit", "dtype": "bf16", "model_type": "t2v", "patch_size": [1, 2, 2], "text_len": 16,
+                      "in_dim": 4, "hidden_size": 64, "ffn_dim": 128, "freq_dim": 32, "text_dim": 32, "out_dim": 4,
+                      "num_heads": 4, "num_layers": 2, "qk_norm": True, "cross_attn_norm": True, "eps": 1e-6},
+        "ae": {"model_id": "wan_video_vae", "base_dim": 8, "z_dim": 4, "dim_mult": [1, 2, 2, 2], "num_res_blocks": 1,
+               "latents_mean": [0] * 4, "latents_std": [1] * 4},
+        "text_encoder": {"model_id": "UMT5", "vocab_size": 300, "d_model": 32, "d_kv": 8, "d_ff": 64, "num_layers": 1, "num_heads": 4},
+        "lora": {"enable": True, "rank": 4, "alpha": 8, "target_modules": ["self_attn.qkv", "self_attn.proj_out", "cross_attn.proj_q"]},
+        "prior_loss_weight": 0.5,
+    }
+    data = {"dataset_param": {"dataset_type": "dreambooth",
+                              "basic_parameters": {"instance_data_dir": str(inst), "instance_prompt": "a photo of sks dog",
+                                                   "class_data_dir": str(cls), "class_prompt": "a photo of a dog"},
+                              "preprocess_parameters": {"resolution": 32, "text_len": 16}},
+            "dataloader_param": {"dataloader_mode": "sampler", "shuffle": False, "drop_last": True, "pin_memory": False, "num_workers": 0}}
+    m, d = tmp_path / "model.json", tmp_path / "data.json"
+    m.write_text(json.dumps(model))
+    d.write_text(json.dumps(data))
+    hist = pretrain("sora", ["--mm-model", str(m), "--mm-data", str(d), "--train-iters", "3", "--micro-batch-size", "2",
+                             "--global-batch-size", "2", "--lr", "1e-3"], device="cpu")
+    assert len(hist) == 3 and all(torch.isfinite(torch.tensor(h["loss"])) for h in hist)
+    _reset()

@@ -69,3 +69,30 @@ def test_feature_dataset(tmp_path):
     (tmp_path / "index.txt").write_text("\n".join(f"{i}.pt" for i in range(3)))
     ds = FeatureDataset(index=str(tmp_path / "index.txt"), data_folder=str(tmp_path))
     assert len(ds) == 3 and ds[1]["latents"].shape == (4, 3, 8, 8) and ds[1]["prompt_mask"].all()
+
+
+def test_dreambooth_dataset_instance_and_class_images(tmp_path):
+    import numpy as np
+    import pytest
+    from PIL import Image
+    from mindspeed_mm_b200.data.multimodal import DreamBoothDataset
+    from mindspeed_mm_b200.models.registry import data_register
+    rng = np.random.default_rng(0)
+    inst, cls = tmp_path / "dog", tmp_path / "class"
+    inst.mkdir()
+    cls.mkdir()
+    for d, n in ((inst, 3), (cls, 2)):
+        for i in range(n):
+            Image.fromarray(rng.integers(0, 255, (40 + 8 * i, 56, 3), dtype=np.uint8)).save(d / f"{i}.png")
+    (inst / "notes.txt").write_text("ignored")
+    ds = DreamBoothDataset(instance_data_dir=str(inst), instance_prompt="a photo of sks dog", class_data_dir=str(cls),
+                           class_prompt="a photo of a dog", repeats=2, height=32, width=32, text_len=24)
+    assert len(ds) == 6 and data_register.get("dreambooth") is DreamBoothDataset
+    it = ds[4]
+    assert it["video"].shape == (3, 1, 32, 32) and it["class_video"].shape == (3, 1, 32, 32)
+    assert float(it["video"].min()) >= -1.0 and float(it["video"].max()) <= 1.0
+    assert int(it["prompt_mask"].sum()) == len("a photo of sks dog") and int(it["class_prompt_mask"].sum()) == len("a photo of a dog")
+    plain = DreamBoothDataset(instance_data_dir=str(inst), instance_prompt="x", height=16, width=16, text_len=4)
+    assert "class_video" not in plain[0] and len(plain) == 3
+    with pytest.raises(ValueError):
+        DreamBoothDataset(instance_data_dir=str(tmp_path / "missing"), instance_prompt="x")

@@ -73,3 +73,20 @@ def test_trainer_log_passes_its_own_baseline(tmp_path, capsys):
     rec = st_check.record(str(tmp_path / "a.log"), str(tmp_path / "base.json"), warm_up=1)
     assert len(rec.loss) == 3 and all(abs(a - h["loss"]) <= 1e-5 * abs(h["loss"]) for a, h in zip(rec.loss, logs[0][1]))
     assert st_check.compare_files(str(tmp_path / "b.log"), str(tmp_path / "base.json"), check=("loss", "memory")) == []
+
+
+def test_merge_gate_stage_selection():
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("run_ci", os.path.join(root, "ci", "run_ci.py"))
+    ci = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ci)
+    assert ci.classify("docs/migration.md") == "doc" and ci.classify("examples/qwen3vl/tiny_moe_native.yaml") == "recipe"
+    assert ci.classify("mindspeed_mm_b200/ops/csrc/gemm.cu") == "kernel" and ci.classify("bench.py") == "code"
+    assert ci.plan(["README.md", "profiles/x.md"], gpu=True) == []
+    assert ci.plan(["examples/a/b.yaml", "docs/x.md"], gpu=False) == ["recipes"]
+    assert ci.plan(["mindspeed_mm_b200/parallel/fsdp.py"], gpu=False) == ["build", "cpu"]
+    assert ci.plan(["mindspeed_mm_b200/ops/csrc/gemm.cu", "README.md"], gpu=True) == ["build", "cpu", "gpu", "smoke", "st"]
+    assert ci._recipes_ok() == 0                       # every committed recipe parses
+    assert ci.main(["--files", os.devnull, "--dry-run"]) == 0

@@ -372,10 +372,11 @@ class UnderPrefix(Operator):
 
 class MatchBySuffix(Operator):
     """Checkpoint names -> the names of a model built by the current transformers version, for files written with an
-    older layout of the same architecture (``model.layers...`` / ``visual...`` on disk, ``model.language_model...`` /
-    ``model.visual...`` in memory): a name the model does not have is replaced by the one model name that ends with it
-    (after dropping a leading ``model.``).  Names that match nothing, or more than one, are left alone.  The way back
-    writes the model's own names, which every transformers version that knows them reads."""
+    older layout of the same architecture (``model.layers...`` / ``visual...`` or ``language_model.model.layers...`` on
+    disk, ``model.language_model.layers...`` / ``model.visual...`` in memory).  A name the model does not have is replaced
+    by the one model name that ends with the longest possible tail of it; when several do, the components that were cut off
+    (other than the generic ``model``) must all appear in the candidate.  Names that still match nothing, or more than one,
+    are left alone.  The way back writes the model's own names, which every transformers version that knows them reads."""
 
     exact_names = True
 
@@ -384,13 +385,23 @@ class MatchBySuffix(Operator):
 
     def apply(self, sd):
         have = set(self.names)
+        free = [n for n in self.names if n not in sd]
         for k in list(sd.keys()):
             if k in have:
                 continue
-            tail = "." + (k[len("model."):] if k.startswith("model.") else k)
-            hits = [n for n in self.names if n.endswith(tail) and n not in sd]
-            if len(hits) == 1:
-                sd[hits[0]] = sd.pop(k)
+            parts = k.split(".")
+            for drop in range(0, len(parts) - 1):
+                tail = "." + ".".join(parts[drop:])
+                hits = [n for n in free if n.endswith(tail)]
+                if len(hits) > 1:
+                    hint = [c for c in parts[:drop] if c != "model"]
+                    hits = [n for n in hits if all(c in n.split(".") for c in hint)]
+                if len(hits) == 1:
+                    sd[hits[0]] = sd.pop(k)
+                    free.remove(hits[0])
+                    break
+                if hits:            # still ambiguous at this length: a shorter tail can only be more so
+                    break
 
     def revert(self, sd):
         pass

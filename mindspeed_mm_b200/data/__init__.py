@@ -66,7 +66,7 @@ def build_dataset(dataset_param, model=None):
             v = _vision_of(cfg)
             if v is not None:
                 basic.setdefault("patch", v.patch_size)
-                basic.setdefault("merge", getattr(v, "spatial_merge_size", getattr(v, "merge", 2)))
+                basic.setdefault("merge", getattr(v, "spatial_merge_size", getattr(v, "merge", 2)) or 2)
                 basic.setdefault("temporal_patch", getattr(v, "temporal_patch_size", 2))
             else:                           # no vision tower (speech / text decoders): text-only samples
                 basic["images_per_sample"] = 0

@@ -44,6 +44,9 @@ class PackedVLMCollator:
             merge = getattr(v, "merge", 2)
             return cls(cfg.image_token_id, cfg.vision_start_token_id, merge=merge, patch=getattr(v, "patch_size", 14),
                        vision_plan_fn=lambda grid: None, **kw)
+        if not hasattr(v, "spatial_merge_size"):          # a tower of another family (wrapped transformers classes): no plan
+            return cls(cfg.image_token_id, cfg.vision_start_token_id, merge=getattr(cfg, "spatial_merge_size", 2) or 2,
+                       patch=getattr(v, "patch_size", 14), vision_plan_fn=lambda grid: None, **kw)
         return cls(cfg.image_token_id, cfg.vision_start_token_id, merge=v.spatial_merge_size, patch=v.patch_size,
                    window_size=getattr(v, "window_size", 0), vit_head_dim=v.hidden_size // v.num_heads,
                    rope_index_fn=getattr(cfg, "rope_index", None), vision_plan_fn=getattr(cfg, "vision_plan", None), **kw)

@@ -538,8 +538,18 @@ def build_preset(model_id: str, **text_overrides) -> ComposableLM:
     return ComposableLM(cfg)
 
 
+def _preset_factory(mid: str):
+    def build(config=None, **kw):
+        return ComposableLM(config if isinstance(config, ComposableConfig) else PRESETS[mid], **kw)
+    # a family id without its own modeling file: with a Hugging Face checkpoint directory the trainer builds the stock
+    # transformers class instead (plugins/hf_auto.py), so real dimensions and published weights load by name
+    build.hf_fallback = True
+    build.__name__ = f"composable_{mid}"
+    return build
+
+
 for _mid in PRESETS:
-    model_register.register(_mid)(lambda config=None, _m=_mid, **kw: ComposableLM(config if isinstance(config, ComposableConfig) else PRESETS[_m], **kw))
+    model_register.register(_mid)(_preset_factory(_mid))
 
 
 def from_hf_config(hf: dict) -> ComposableConfig:

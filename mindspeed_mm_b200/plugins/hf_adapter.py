@@ -60,6 +60,12 @@ class HFModelAdapter(nn.Module):
             from .hf_kernels import use_plugin_attention as _use
             _use(model)
         self._engine = None
+        text_cfg = model.config.get_text_config() if hasattr(model.config, "get_text_config") else model.config
+        rope = getattr(text_cfg, "rope_parameters", None) or getattr(text_cfg, "rope_scaling", None) or {}
+        self._mrope = isinstance(rope, dict) and "mrope_section" in rope
+        import inspect
+        self._forward_params = [n for n, p in inspect.signature(model.forward).parameters.items()
+                                if p.kind in (p.POSITIONAL_OR_KEYWORD, p.KEYWORD_ONLY)]
 
     @staticmethod
     def _untie(model) -> None:
@@ -67,8 +73,12 @@ class HFModelAdapter(nn.Module):
         emb = model.get_input_embeddings() if hasattr(model, "get_input_embeddings") else None
         if head is not None and emb is not None and getattr(head, "weight", None) is getattr(emb, "weight", 0):
             head.weight = nn.Parameter(emb.weight.detach().clone(), requires_grad=emb.weight.requires_grad)
-            if hasattr(model.config, "tie_word_embeddings"):
-                model.config.tie_word_embeddings = False
+            for c in (model.config, getattr(model.config, "text_config", None)):
+                if c is not None and hasattr(c, "tie_word_embeddings"):
+                    c.tie_word_embeddings = False
+            names = {id(m): n for n, m in model.named_modules()}
+            # a checkpoint of the tied model stores the matrix once: the load fills the head from the embedding
+            model._untied_head = (names[id(emb)] + ".weight", names[id(head)] + ".weight")
 
     # -- sharding plan ---------------------------------------------------------------------------------------------
     def fsdp_units(self) -> List[Tuple[str, nn.Module]]:
@@ -134,14 +144,21 @@ class HFModelAdapter(nn.Module):
                 seq = torch.bucketize(tok, cu[1:], right=True).clamp(max=cu.numel() - 2)
                 pos = tok - cu[seq]
             if pos is not None:             # [T], or [3, T] multimodal positions of the VLM collators
+                if pos.dim() == 2 and not self._mrope:
+                    pos = pos[0]            # a decoder with 1-D rotary positions: the temporal row is the token position
                 kw["position_ids"] = pos[None] if pos.dim() == 1 else pos[:, None]
         else:
             kw["input_ids"] = ids
             if batch.get("attention_mask") is not None:
                 kw["attention_mask"] = batch["attention_mask"]
-        for k in ("pixel_values", "image_grid_thw", "pixel_values_videos", "video_grid_thw", "mm_token_type_ids"):
-            if batch.get(k) is not None and (not torch.is_tensor(batch[k]) or batch[k].numel() > 0):
-                kw[k] = batch[k]
+        # every other batch entry the architecture's forward names goes through (pixel_values, image_grid_thw, image_sizes,
+        # input_features, ...); empty media tensors are left out
+        for k in self._forward_params:
+            if k in kw or k in ("labels", "input_ids", "attention_mask", "position_ids", "use_cache", "past_key_values"):
+                continue
+            val = batch.get(k)
+            if val is not None and (not torch.is_tensor(val) or val.numel() > 0):
+                kw[k] = val
         logits = self.model(**kw, use_cache=False).logits
         labels = batch.get("labels")
         if labels is None:

@@ -55,6 +55,19 @@ class _ConfigView:
     def vision(self):
         return getattr(self._hf, "vision_config", None)
 
+    @property
+    def image_token_id(self):
+        hf = self._hf
+        for n in ("image_token_id", "image_token_index"):
+            if getattr(hf, n, None) is not None:
+                return getattr(hf, n)
+        return self.text.vocab_size - 1
+
+    @property
+    def vision_start_token_id(self):
+        v = getattr(self._hf, "vision_start_token_id", None)
+        return v if v is not None else self.image_token_id
+
     def __getattr__(self, name):
         return getattr(self._hf, name)
 
@@ -89,4 +102,20 @@ class HFAutoModel(HFModelAdapter):
 
     def hf_ops(self):
         from ..checkpoint.hf import MatchBySuffix, UnderPrefix
-        return [MatchBySuffix(self._param_names), UnderPrefix("model.")]
+        from ..checkpoint.operators import Operator
+        ops = [MatchBySuffix(self._param_names)]
+        tied = getattr(self.model, "_untied_head", None)
+        if tied is not None:
+            emb, head = tied
+
+            class _FillHead(Operator):
+                exact_names = True
+
+                def apply(self, sd):
+                    if head not in sd and emb in sd:
+                        sd[head] = sd[emb].clone()
+
+                def revert(self, sd):
+                    pass
+            ops.append(_FillHead())
+        return ops + [UnderPrefix("model.")]

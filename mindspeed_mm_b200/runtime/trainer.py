@@ -83,6 +83,11 @@ class Trainer:
     def build_model(self):
         m = self.args.model
         cls = registry.model_register.get(m.model_id)
+        if getattr(cls, "hf_fallback", False) and m.model_name_or_path and \
+                os.path.exists(os.path.join(m.model_name_or_path, "config.json")):
+            # a zoo id that is a switch setting of the composable model, pointed at a real checkpoint: run the architecture
+            # the checkpoint names (stock transformers class, this package's kernels and sharding engine)
+            cls = registry.model_register.get("hf_auto")
         cfg = self._model_config(cls, m)
         text = getattr(cfg, "text", None)
         if text is not None and hasattr(text, "ep_dispatcher"):

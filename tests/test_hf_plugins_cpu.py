@@ -220,3 +220,40 @@ def test_verl_plugin_entry_point(monkeypatch):
     finally:
         hf_kernels.remove_kernel_plugin()
         torch.use_deterministic_algorithms(False)
+
+
+def test_zoo_id_with_a_checkpoint_runs_the_stock_architecture(tmp_path):
+    """``model_id: mistral3`` is a switch setting of the composable model until it is pointed at a checkpoint directory:
+    then the architecture config.json names (stock Mistral3ForConditionalGeneration: Pixtral tower + Mistral decoder) is
+    built, its weights load by name, and text-only packs train it."""
+    import os
+    from transformers import Mistral3Config, Mistral3ForConditionalGeneration
+    from mindspeed_mm_b200.config import load_config
+    from mindspeed_mm_b200.runtime.trainer import Trainer
+    cfg = Mistral3Config(
+        vision_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2, image_size=56,
+                           patch_size=14, head_dim=16),
+        text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=16, vocab_size=1100, sliding_window=None), image_token_index=1023)
+    torch.manual_seed(0)
+    hf = Mistral3ForConditionalGeneration(cfg).float()
+    src = tmp_path / "hf_in"
+    hf.save_pretrained(src, safe_serialization=True)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    args = load_config(os.path.join(root, "examples/magistral-2509/tiny_native.yaml"),
+                       [f"model.model_name_or_path={src}", "training.train_iters=3", "training.clip_grad=0.0",
+                        "data.dataset_param.basic_parameters.images_per_sample=0",
+                        "data.dataset_param.basic_parameters.num_samples=2", "data.dataloader_param.shuffle=false"], world_size=1)
+    try:
+        tr = Trainer(args, device="cpu")
+        assert type(tr.model.model).__name__ == "Mistral3ForConditionalGeneration"
+        got = {k[len("model."):]: v for k, v in tr.engine.named_full_params()}
+        sd = hf.state_dict()
+        assert set(got) == set(sd)
+        for k, v in sd.items():
+            assert torch.allclose(got[k].float(), v, atol=1e-6), k
+        hist = tr.train()
+    finally:
+        hf_kernels.remove_kernel_plugin()
+    losses = [float(h["loss"]) if isinstance(h, dict) else float(h) for h in hist]
+    assert losses[-1] < losses[0]

@@ -61,6 +61,12 @@ def dispatch_plan(topk_ids: torch.Tensor, num_experts: int, group) -> Tuple[torc
 
 def experts_mlp(x, gate_up, down, counts):
     """x rows grouped by expert (counts per expert); gate_up [E,H,2F], down [E,F,H]."""
+    if x.is_cuda and x.shape[0] and ops.get_tier() == "native" and ops._nat().moe_supported(x, gate_up, down):
+        # the tcgen05 grouped kernels work on the 128-aligned expert layout: hand them the rows as a top-1 routing whose
+        # expert ids are already sorted (the permutation into the aligned layout is then a copy with gaps)
+        c = torch.as_tensor([int(v) for v in counts], dtype=torch.long, device=x.device)
+        ids = torch.repeat_interleave(torch.arange(c.numel(), device=x.device), c, output_size=x.shape[0])
+        return ops.moe_experts(x, ids[:, None], torch.ones(x.shape[0], 1, dtype=x.dtype, device=x.device), gate_up, down)
     h = ops.grouped_gemm(x, gate_up, counts)
     return ops.grouped_gemm(ops.swiglu(h), down, counts)
 

@@ -614,6 +614,37 @@ def test_kimi_delta_attention_native(lens, H):
     _close(ob, ob_ref, rtol=3e-2, atol=3e-3)
 
 
+def test_expert_mlp_on_rows_grouped_by_expert_uses_the_aligned_kernels():
+    """The all-to-all dispatcher hands over rows already grouped by expert (with empty experts): the aligned grouped
+    kernels give the loop-of-matmuls result, forward and backward, and nothing falls back."""
+    from mindspeed_mm_b200.parallel.ep import experts_mlp
+    torch.manual_seed(0)
+    E, H, Fi = 4, 256, 256
+    counts = [130, 0, 77, 300]
+    x = (torch.randn(sum(counts), H, device=DEV) * 0.5).bfloat16().requires_grad_()
+    gu = (torch.randn(E, H, 2 * Fi, device=DEV) * 0.05).bfloat16().requires_grad_()
+    dn = (torch.randn(E, Fi, H, device=DEV) * 0.05).bfloat16().requires_grad_()
+    ops.library_fallbacks(reset=True)
+    y = experts_mlp(x, gu, dn, counts)
+    assert not ops.library_fallbacks(), ops.library_fallbacks()
+    g = torch.randn_like(y)
+    gx, ggu, gdn = torch.autograd.grad(y, [x, gu, dn], g)
+    xr, gur, dnr = (t.detach().float().requires_grad_() for t in (x, gu, dn))
+    outs, s0 = [], 0
+    for e, c in enumerate(counts):
+        h = xr[s0:s0 + c] @ gur[e]
+        a, b = h.chunk(2, -1)
+        outs.append((torch.nn.functional.silu(a) * b) @ dnr[e])
+        s0 += c
+    yr = torch.cat(outs)
+    rx, rgu, rdn = torch.autograd.grad(yr, [xr, gur, dnr], g.float())
+    _close(y, yr, rtol=3e-2, atol=3e-2)
+    _close(gx, rx, rtol=3e-2, atol=3e-2)
+    _close(ggu, rgu, rtol=3e-2, atol=5e-2)
+    _close(gdn, rdn, rtol=3e-2, atol=5e-2)
+    assert float(ggu[1].abs().max()) == 0.0 and float(gdn[1].abs().max()) == 0.0      # the empty expert
+
+
 def test_peer_flag_wait_runs_out_and_reports_status():
     """Failure detection on the device without a fault: a wait on a flag that nothing sets gives up after its limit,
     the kernel returns, the status word says which kind of wait expired, and the context stays usable."""

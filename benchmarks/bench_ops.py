@@ -102,6 +102,13 @@ def bench_gemm_swiglu(out, small):
         native.check_status()
 
 
+ONLY: list = []      # --only a,b: restrict a benchmark to the rows whose name contains one of the words (for short profiler captures)
+
+
+def want(name: str) -> bool:
+    return not ONLY or any(o in name for o in ONLY)
+
+
 def bench_elementwise(out, small):
     _, bw, src = peaks()
     T = 8192 if small else 32768
@@ -110,9 +117,11 @@ def bench_elementwise(out, small):
     w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
     dy = torch.randn_like(x)
 
-    def rec(name, fn, nbytes, base=None):
+    def rec(name, fn, nbytes, base=None, width=H):
+        if not want(name):
+            return
         t = time_fn(fn)
-        r = dict(op=name, T=T, H=H, ms=round(t, 4), gbs=round(nbytes / t / 1e6, 1),
+        r = dict(op=name, T=T, H=width, ms=round(t, 4), gbs=round(nbytes / t / 1e6, 1),
                  frac_of_peak=round(nbytes / t / 1e6 / bw, 3), peak=src)
         if base is not None:
             tb = time_fn(base)
@@ -130,19 +139,22 @@ def bench_elementwise(out, small):
     gu = torch.randn(T // 4, 2 * F, device="cuda", dtype=torch.bfloat16)
     rec("swiglu_fwd", lambda: ops.swiglu(gu), gu.numel() * 2 * 1.5,
         lambda: torch.nn.functional.silu(gu[:, :F]) * gu[:, F:])
-    n = 256 << 20 if not small else 32 << 20
-    p, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
-    g = torch.randn(n, device="cuda", dtype=torch.bfloat16)
-    p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
-    rec("adamw_shard", lambda: native.adamw_shard(p, m, v, g, p16, 1e-4, 0.9, 0.999, 1e-8, 0.0, 1, n, 1.0), n * 28.0)
+    if want("adamw_shard"):
+        n = 256 << 20 if not small else 32 << 20
+        p, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
+        g = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+        p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+        rec("adamw_shard", lambda: native.adamw_shard(p, m, v, g, p16, 1e-4, 0.9, 0.999, 1e-8, 0.0, 1, n, 1.0), n * 28.0)
+        del p, m, v, g, p16
     # DiT-side ops: adaLN modulate and gated residual on [B, S, H] with per-sample [B, 1, H] vectors; rotary on [T, N, D]
     Hd = 5120
     xd = torch.randn(1, T, Hd, device="cuda", dtype=torch.bfloat16)
     sc, sh, gt = (torch.randn(1, 1, Hd, device="cuda", dtype=torch.bfloat16) for _ in range(3))
     yd = torch.randn_like(xd)
     rec("layer_norm_modulate", lambda: ops.layer_norm_modulate(xd, sc, sh, 1e-6), 2 * xd.numel() * 2,
-        lambda: ref.layer_norm_modulate(xd, sc, sh, 1e-6))
-    rec("gated_residual", lambda: ops.gated_residual(xd, yd, gt), 3 * xd.numel() * 2, lambda: ref.gated_residual(xd, yd, gt))
+        lambda: ref.layer_norm_modulate(xd, sc, sh, 1e-6), width=Hd)
+    rec("gated_residual", lambda: ops.gated_residual(xd, yd, gt), 3 * xd.numel() * 2, lambda: ref.gated_residual(xd, yd, gt),
+        width=Hd)
     q = torch.randn(T, 28, 128, device="cuda", dtype=torch.bfloat16)
     ang = torch.randn(T, 64, device="cuda")
     cos, sin = torch.cat([ang.cos()] * 2, -1).to(torch.bfloat16), torch.cat([ang.sin()] * 2, -1).to(torch.bfloat16)
@@ -415,7 +427,9 @@ def main():
     ap.add_argument("--ops", default="gemm,elementwise")
     ap.add_argument("--out", default="")
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--only", default="", help="comma list of words: only the rows whose op name contains one of them")
     a = ap.parse_args()
+    ONLY[:] = [w for w in a.only.split(",") if w]
     for op in a.ops.split(","):
         {"gemm": bench_gemm, "gemm_swiglu": bench_gemm_swiglu, "elementwise": bench_elementwise, "lce": bench_lce, "fmha": bench_fmha, "gdn": bench_gdn,
          "vit_attention": bench_vit_attention, "grouped_gemm": bench_grouped_gemm, "small_ops": bench_small_ops,

@@ -134,6 +134,64 @@ def test_composable_presets_on_gpu():
         assert torch.isfinite(loss), mid
 
 
+def test_internvl_and_stock_transformers_class_on_gpu():
+    """InternVL (native model) against its fp32 CPU copy, and a stock transformers Qwen3 with the kernel plugin and the
+    ``mm_b200`` attention implementation against the same class on stock kernels: bf16 on the GPU, no library fallback on
+    the patched class."""
+    from mindspeed_mm_b200.models.internvl import InternVLConfig, InternVLModel
+    cfg = InternVLConfig.tiny()
+    cfg.vision.hidden_size, cfg.vision.num_heads, cfg.vision.intermediate_size = 128, 2, 256      # head dim 64
+    cfg.text.hidden_size, cfg.text.num_attention_heads, cfg.text.num_key_value_heads, cfg.text.head_dim = 128, 2, 1, 64
+    cfg.text.intermediate_size = 256
+    torch.manual_seed(0)
+    ref_model = InternVLModel(cfg).float()
+    ref_model.init_weights(0)
+    g = torch.Generator().manual_seed(1)
+    ids = torch.cat([torch.randint(0, 140, (9,), generator=g), torch.full((2 * cfg.tokens_per_tile,), cfg.image_token_id),
+                     torch.randint(0, 140, (15,), generator=g)])
+    labels = torch.roll(ids, -1)
+    labels[ids == cfg.image_token_id] = -100
+    batch = dict(input_ids=ids, labels=labels, pixel_values=torch.randn(2, 3, 56, 56, generator=g),
+                 cu_seqlens=torch.tensor([0, ids.numel()], dtype=torch.int32), max_seqlen=ids.numel())
+    ls, n = ref_model(batch)
+    gpu = InternVLModel(cfg)
+    gpu.load_state_dict(ref_model.state_dict())
+    gpu = gpu.to(DEV, torch.bfloat16)
+    from mindspeed_mm_b200.data.collate import to_device
+    b = to_device(batch, torch.device(DEV))
+    b["pixel_values"] = b["pixel_values"].to(torch.bfloat16)
+    lg, ng = gpu(b)
+    (lg / ng).backward()
+    assert abs(float(lg / ng) - float(ls / n)) < 3e-2 * float(ls / n)
+    assert all(torch.isfinite(p.grad).all() for p in gpu.parameters() if p.grad is not None)
+    # stock class + plugin
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+    from mindspeed_mm_b200.plugins import hf_kernels
+    hc = Qwen3Config(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                     head_dim=64, vocab_size=512, tie_word_embeddings=False)
+    hc._attn_implementation = "sdpa"
+    torch.manual_seed(0)
+    base = Qwen3ForCausalLM(hc).to(DEV, torch.bfloat16).eval()
+    x = torch.randint(0, 512, (2, 128), device=DEV)
+    with torch.no_grad():
+        want = base(input_ids=x).logits.float()
+    hf_kernels.apply_kernel_plugin(("qwen3",))
+    try:
+        hc2 = Qwen3Config(**{k: v for k, v in hc.to_dict().items() if k in ("hidden_size", "intermediate_size", "num_hidden_layers",
+                                                                       "num_attention_heads", "num_key_value_heads", "head_dim",
+                                                                       "vocab_size", "tie_word_embeddings")})
+        hc2._attn_implementation = "mm_b200"
+        patched = Qwen3ForCausalLM(hc2).to(DEV, torch.bfloat16).eval()
+        patched.load_state_dict(base.state_dict())
+        ops.library_fallbacks(reset=True)
+        with torch.no_grad():
+            got = patched(input_ids=x).logits.float()
+        assert not ops.library_fallbacks(), ops.library_fallbacks()
+    finally:
+        hf_kernels.remove_kernel_plugin()
+    assert (got - want).abs().max() <= 5e-2 * want.abs().max()
+
+
 def test_recompute_with_skipped_last_gemm_matches_graph_keeping_run():
     """The re-forward of a checkpointed block does not rerun its last GEMM (the value only feeds a residual add);
     one optimizer step must equal the step of the same model with autograd graphs kept."""

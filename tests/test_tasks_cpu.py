@@ -325,3 +325,24 @@ def test_lora_adapter_in_peft_layout_round_trip(tmp_path):
                           fused[:qb.shape[0]])
     back = from_peft_state(peft, hfio.qwen25vl_ops(cfg))
     assert set(back) == set(state) and all(torch.equal(back[k], state[k]) for k in state)
+
+
+def test_lora_on_a_mixture_of_experts_model_keeps_the_experts_frozen():
+    """LoRA on the MoE recipe: adapters on the attention projections are the only trainable parameters; the fused
+    experts (3-D tensors, their own sharding engine) stay frozen and untouched by the optimizer."""
+    import os
+    import torch
+    from mindspeed_mm_b200.config import load_config
+    from mindspeed_mm_b200.runtime.trainer import Trainer
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    args = load_config(os.path.join(root, "examples/qwen3vl/tiny_moe_native.yaml"),
+                       ["parallel.expert_parallel_size=1", "training.train_iters=2", "data.dataloader_param.pin_memory=false",
+                        "training.lora.enable=true", "training.lora.rank=4", "training.lora.alpha=8",
+                        "training.lora.target_modules=[qkv_proj,o_proj]"], world_size=1)
+    tr = Trainer(args, device="cpu")
+    before = {n: t.clone() for n, t in tr.engine.named_full_params()}
+    tr.train()
+    after = dict(tr.engine.named_full_params())
+    moved = {n for n in before if not torch.equal(before[n], after[n])}
+    assert moved and all("lora_" in n for n in moved), sorted(moved)[:5]
+    assert any("experts" in n for n in before) and not any("experts" in n for n in moved)

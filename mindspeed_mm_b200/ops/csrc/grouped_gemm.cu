@@ -7,7 +7,8 @@
 //   mode 2 (wgrad) dW[e]    = x_e^T @ dy_e           contraction over the expert's rows; dW [E, K, N]
 //
 // A one-thread planner turns the device-side offsets into a tile list (expert, row block, column block); the
-// persistent CTAs (TMA producer / MMA issuer / 4 epilogue warps, TMEM double buffer: same pipeline as gemm.cu)
+// persistent CTAs (TMA producer / MMA issuer / 4 epilogue warps, TMEM double buffer: same pipeline as gemm.cu; output
+// tiles 128 x 256, or 128 x 128 when the tiled dimension is not a multiple of 256)
 // walk that list, so routing skew costs nothing but the tiles it produces.  Experts without tokens produce no
 // tiles (wgrad output is pre-zeroed by the caller).  Reference op: torch_npu.npu_grouped_matmul with group_list
 // (mindspeed_mm/fsdp/ops/moe_ops/gemm.py:16-92).
@@ -17,13 +18,20 @@ namespace {
 
 using namespace tc05;
 
-constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int BM = 128, BK = 64;
 constexpr int kThreads = 192, kEpiThreads = 128;
-constexpr int kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
+constexpr int kABytes = BM * BK * 2;
 constexpr int kCBytes = 2 * BM * 64 * 2;
-constexpr int kStages = 6;
-constexpr int kSmem = kStages * kStageBytes + kCBytes + 2048;
-constexpr int kTmemCols = 2 * BN;
+
+// Output tiles are 128 x 256 when the tiled output dimension allows it (the tensor pipe reads the A tile once per 256
+// columns instead of once per 128: the 128 x 128 tile is bound by shared-memory operand reads), else 128 x 128.
+template <int BN>
+struct Cfg {
+    static constexpr int kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kSmem = kStages * kStageBytes + kCBytes + 2048;
+    static constexpr int kTmemCols = 2 * BN;
+};
 
 struct GGParams {
     const int* off;          // [E + 1] aligned row offsets (device)
@@ -36,7 +44,7 @@ struct GGParams {
 };
 
 // modes 0/1: one tile per (expert row block, output column block); mode 2: per (expert, K block, N block)
-__global__ void gg_plan_kernel(const int* off, int E, int mode, int K, int N, int* tile_e, int* tile_m, int* tile_n,
+__global__ void gg_plan_kernel(const int* off, int E, int mode, int K, int N, int BN, int* tile_e, int* tile_m, int* tile_n,
                                int* n_tiles, int max_tiles) {
     if (threadIdx.x || blockIdx.x) return;
     int n = 0;
@@ -59,10 +67,12 @@ __global__ void gg_plan_kernel(const int* off, int E, int mode, int K, int N, in
     *n_tiles = n;
 }
 
-template <int MODE>
+template <int MODE, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, GGParams p) {
+    constexpr int kBBytes = Cfg<BN>::kBBytes, kStageBytes = Cfg<BN>::kStageBytes, kStages = Cfg<BN>::kStages;
+    constexpr int kTmemCols = Cfg<BN>::kTmemCols;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sA = smem;
@@ -123,8 +133,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     uint8_t* b = sB + stage * kBBytes;
                     if constexpr (MODE == 0) {
                         tma_load_2d(a, &tmA, &full[stage], kb * BK, mb * BM);
-                        tma_load_3d(b, &tmB, &full[stage], nb * BN, kb * BK, e);                 // W[e][k, n], N-contiguous
-                        tma_load_3d(b + BK * 128, &tmB, &full[stage], nb * BN + 64, kb * BK, e);
+#pragma unroll
+                        for (int a64 = 0; a64 < BN / 64; ++a64)                                   // W[e][k, n], N-contiguous: one
+                            tma_load_3d(b + a64 * BK * 128, &tmB, &full[stage], nb * BN + 64 * a64, kb * BK, e);   // atom per 64 n
                     } else if constexpr (MODE == 1) {
                         tma_load_2d(a, &tmA, &full[stage], kb * BK, mb * BM);
                         tma_load_3d(b, &tmB, &full[stage], kb * BK, nb * BN, e);                 // rows = K (output), contraction = N
@@ -132,8 +143,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         const int r0 = p.off[e] + kb * BK;
                         tma_load_2d(a, &tmA, &full[stage], mb * BM, r0);                         // x[r, k]: M = k index
                         tma_load_2d(a + BK * 128, &tmA, &full[stage], mb * BM + 64, r0);
-                        tma_load_2d(b, &tmB, &full[stage], nb * BN, r0);                         // dy[r, n]
-                        tma_load_2d(b + BK * 128, &tmB, &full[stage], nb * BN + 64, r0);
+#pragma unroll
+                        for (int a64 = 0; a64 < BN / 64; ++a64)                                   // dy[r, n]
+                            tma_load_2d(b + a64 * BK * 128, &tmB, &full[stage], nb * BN + 64 * a64, r0);
                     }
                     if (++stage == kStages) {
                         stage = 0;
@@ -241,24 +253,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
 }
 
-template <int MODE>
+template <int MODE, int BN>
 int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC, const GGParams& p, int grid, cudaStream_t st) {
-    auto kern = grouped_gemm_kernel<MODE>;
+    auto kern = grouped_gemm_kernel<MODE, BN>;
     static bool done = false;
     if (!done) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmem);
         if (e != cudaSuccess) return (int)e;
         done = true;
     }
-    kern<<<grid, kThreads, kSmem, st>>>(tA, tB, tC, p);
+    kern<<<grid, kThreads, Cfg<BN>::kSmem, st>>>(tA, tB, tC, p);
     return (int)cudaGetLastError();
 }
 
 }  // namespace
 
+// Upper bound of the tile count (128-wide column blocks; the 256-wide plan has at most as many).
 MM_API int mm_grouped_gemm_max_tiles(int R, int E, int K, int N, int mode) {
-    if (mode == 2) return E * (K / BM) * (N / BN) + 1;
-    return (R / BM + E) * ((mode == 0 ? N : K) / BN) + 1;
+    if (mode == 2) return E * (K / BM) * (N / 128) + 1;
+    return (R / BM + E) * ((mode == 0 ? N : K) / 128) + 1;
 }
 
 // a, b, c by mode:  0: a = x [R,K], b = W [E,K,N], c = y [R,N]      1: a = dy [R,N], b = W, c = dx [R,K]
@@ -273,7 +286,8 @@ MM_API int mm_grouped_gemm_bf16(const void* a, const void* b, void* c, const int
     int* tile_m = plan + max_tiles;
     int* tile_n = plan + 2 * max_tiles;
     int* n_tiles = plan + 3 * max_tiles;
-    gg_plan_kernel<<<1, 32, 0, st>>>(off, E, mode, K, N, tile_e, tile_m, tile_n, n_tiles, max_tiles);
+    const int BN = ((mode == 1 ? K : N) % 256 == 0) ? 256 : 128;      // the dimension the column blocks tile
+    gg_plan_kernel<<<1, 32, 0, st>>>(off, E, mode, K, N, BN, tile_e, tile_m, tile_n, n_tiles, max_tiles);
     CUtensorMap tA, tB, tC;
     int r;
     if (mode == 0) {
@@ -297,9 +311,14 @@ MM_API int mm_grouped_gemm_bf16(const void* a, const void* b, void* c, const int
     }
     GGParams p{off, tile_e, tile_m, tile_n, n_tiles, K, N, status};
     const int grid = max_tiles - 1 < sms ? (max_tiles - 1 < 1 ? 1 : max_tiles - 1) : sms;
-    if (mode == 0) return launch<0>(tA, tB, tC, p, grid, st);
-    if (mode == 1) return launch<1>(tA, tB, tC, p, grid, st);
-    return launch<2>(tA, tB, tC, p, grid, st);
+    if (BN == 256) {
+        if (mode == 0) return launch<0, 256>(tA, tB, tC, p, grid, st);
+        if (mode == 1) return launch<1, 256>(tA, tB, tC, p, grid, st);
+        return launch<2, 256>(tA, tB, tC, p, grid, st);
+    }
+    if (mode == 0) return launch<0, 128>(tA, tB, tC, p, grid, st);
+    if (mode == 1) return launch<1, 128>(tA, tB, tC, p, grid, st);
+    return launch<2, 128>(tA, tB, tC, p, grid, st);
 }
 
 // ------------------------------------------------------------------------------------------ permute / unpermute

@@ -131,6 +131,9 @@ def bench_elementwise(out, small):
     ops.set_tier("native")
     rec("rmsnorm_fwd", lambda: ops.rms_norm(x, w, 1e-6), 2 * x.numel() * 2,
         lambda: torch.nn.functional.rms_norm(x, (H,), w, 1e-6))
+    native.lib().mm_rmsnorm_set_v16(0)          # the 16-byte-access form of the same kernel, for comparison
+    rec("rmsnorm_fwd_16B_accesses", lambda: ops.rms_norm(x, w, 1e-6), 2 * x.numel() * 2)
+    native.lib().mm_rmsnorm_set_v16(1)
     xg = x.clone().requires_grad_()
     wg = w.clone().requires_grad_()
     y = ops.rms_norm(xg, wg, 1e-6)

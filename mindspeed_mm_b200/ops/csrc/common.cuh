@@ -64,6 +64,41 @@ __device__ __forceinline__ uint2 ld_stream_u2(const uint2* p, uint64_t pol) {
     return v;
 }
 
+// 32-byte global accesses (sm_100: ld / st .v8.b32): 16 bf16 per instruction, half the load-store instructions of the
+// 16-byte form for the same bytes.  Addresses must be 32-byte aligned.
+struct Vec16 {
+    uint32_t r[8];
+};
+__device__ __forceinline__ Vec16 ld_v16(const void* p) {
+    Vec16 v;
+    asm volatile("ld.global.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v.r[0]), "=r"(v.r[1]), "=r"(v.r[2]), "=r"(v.r[3]), "=r"(v.r[4]), "=r"(v.r[5]), "=r"(v.r[6]), "=r"(v.r[7])
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st_v16(void* p, const Vec16& v) {
+    asm volatile("st.global.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v.r[0]), "r"(v.r[1]), "r"(v.r[2]), "r"(v.r[3]),
+                 "r"(v.r[4]), "r"(v.r[5]), "r"(v.r[6]), "r"(v.r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void unpack16(const Vec16& v, float* f) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.r[i]));
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+__device__ __forceinline__ Vec16 pack16(const float* f) {
+    Vec16 v;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+        v.r[i] = *reinterpret_cast<uint32_t*>(&t);
+    }
+    return v;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -54,6 +54,7 @@ def _declare(L):
         "mm_gated_rms_bwd": [_p, _i, _p, _p, _p, _p, _p, _p, _p, _ll, _i, _p],
         "mm_rmsnorm_bwd_grid": [_i],
         "mm_sq_norm_blocks": [],
+        "mm_rmsnorm_set_v16": [_i],
         "mm_sq_norm": [_p, _ll, _p, _p],
         "mm_rmsnorm_bwd": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _p],
         "mm_swiglu_fwd": [_p, _p, _ll, _i, _p],

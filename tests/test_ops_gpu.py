@@ -152,6 +152,29 @@ def test_adamw_shard():
     _close(p16, pr, rtol=1e-2, atol=1e-2)
 
 
+def test_rmsnorm_forward_access_widths_agree():
+    """The 32-byte-access forward (rows that are a multiple of 16, 32-byte aligned) and the 16-byte form give the same
+    bits; a view at a 16-byte offset takes the 16-byte form."""
+    from mindspeed_mm_b200.ops import native
+    torch.manual_seed(0)
+    L = native.lib()
+    for T, H in ((300, 3584), (64, 2048), (33, 8192), (17, 4112)):
+        x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
+        w = (1 + 0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16)
+        a = ops.rms_norm(x, w, 1e-6)
+        L.mm_rmsnorm_set_v16(0)
+        try:
+            b = ops.rms_norm(x, w, 1e-6)
+        finally:
+            L.mm_rmsnorm_set_v16(1)
+        assert torch.equal(a, b), (T, H)
+        _close(a, ref.rms_norm(x.float(), w.float(), 1e-6))
+    buf = torch.randn(8 * 3584 + 8, device=DEV, dtype=torch.bfloat16)
+    xo = buf[8:].view(8, 3584)                       # 16 bytes past a 32-byte boundary
+    assert xo.data_ptr() % 32 == 16
+    _close(ops.rms_norm(xo, w[:3584].contiguous(), 1e-6), ref.rms_norm(xo.float(), w[:3584].float(), 1e-6))
+
+
 def test_sq_norm_of_shards():
     from mindspeed_mm_b200.ops import native
     torch.manual_seed(0)

@@ -153,8 +153,8 @@ def test_adamw_shard():
 
 
 def test_rmsnorm_forward_access_widths_agree():
-    """The 32-byte-access forward (rows that are a multiple of 16, 32-byte aligned) and the 16-byte form give the same
-    bits; a view at a 16-byte offset takes the 16-byte form."""
+    """The 32-byte-access forward (rows that are a multiple of 16, 32-byte aligned) and the 16-byte form agree to a bf16
+    rounding (their threads sum the squares in different groupings); a view at a 16-byte offset takes the 16-byte form."""
     from mindspeed_mm_b200.ops import native
     torch.manual_seed(0)
     L = native.lib()
@@ -167,7 +167,7 @@ def test_rmsnorm_forward_access_widths_agree():
             b = ops.rms_norm(x, w, 1e-6)
         finally:
             L.mm_rmsnorm_set_v16(1)
-        assert torch.equal(a, b), (T, H)
+        assert (a.float() - b.float()).abs().max() <= 2 ** -6 * a.float().abs().max(), (T, H)
         _close(a, ref.rms_norm(x.float(), w.float(), 1e-6))
     buf = torch.randn(8 * 3584 + 8, device=DEV, dtype=torch.bfloat16)
     xo = buf[8:].view(8, 3584)                       # 16 bytes past a 32-byte boundary

@@ -159,12 +159,101 @@ def parse_legacy_args(argv: Optional[Sequence[str]] = None, check_paths: bool = 
         if not hasattr(args, k):
             setattr(args, k, v)
     args.unknown_args = extra
+    args.global_batch_size_given = args.global_batch_size is not None
     if args.global_batch_size is None:
         args.global_batch_size = args.micro_batch_size
     merge_mm_args(args)
     if check_paths:
         args.path_warnings = check_args_paths(args, warn=lambda *_: None)
     return args
+
+
+def validate_args(args, world_size: int) -> SimpleNamespace:
+    """Consistency checks and derived sizes of the Megatron-style flag set, done once before anything is built
+    (the reference replaces Megatron's ``validate_args`` with its own: mindspeed_mm/patchs/validate_args_patch.py:33).
+    Raises ``ValueError`` naming the flags at fault; returns the derived values (``data_parallel_size``,
+    ``num_micro_batches``, ``ulysses_size``, ``ring_size``, ``sequence_parallel``, ``params_dtype``)."""
+    tp, pp, cp = args.tensor_model_parallel_size, args.pipeline_model_parallel_size, args.context_parallel_size
+    ep = args.expert_model_parallel_size
+    problems: List[str] = []
+    for name, v in (("tensor-model-parallel-size", tp), ("pipeline-model-parallel-size", pp), ("context-parallel-size", cp),
+                    ("expert-model-parallel-size", ep), ("micro-batch-size", args.micro_batch_size)):
+        if v is None or v < 1:
+            problems.append(f"--{name} must be >= 1 (got {v})")
+    if problems:
+        raise ValueError("; ".join(problems))
+    model_parallel = tp * pp * cp
+    if world_size % model_parallel:
+        raise ValueError(f"world size {world_size} is not divisible by tensor ({tp}) x pipeline ({pp}) x context ({cp}) parallel size")
+    dp = world_size // model_parallel
+    if ep > 1 and (dp * cp) % ep:
+        problems.append(f"--expert-model-parallel-size {ep} must divide data x context parallel size {dp * cp}")
+    gbs, mbs = args.global_batch_size or args.micro_batch_size * dp, args.micro_batch_size
+    if gbs == mbs and not getattr(args, "global_batch_size_given", True):
+        gbs = mbs * dp                   # the flag was not given: one micro-batch per data-parallel rank
+    if gbs % (mbs * dp):
+        problems.append(f"--global-batch-size {gbs} is not divisible by micro batch {mbs} x data parallel {dp}")
+    if getattr(args, "bf16", False) and getattr(args, "fp16", False):
+        problems.append("--bf16 and --fp16 are exclusive")
+    if args.clip_grad is not None and args.clip_grad < 0:
+        problems.append(f"--clip-grad must be >= 0 (got {args.clip_grad})")
+    if args.min_lr is not None and args.lr is not None and args.min_lr > args.lr:
+        problems.append(f"--min-lr {args.min_lr} is above --lr {args.lr}")
+    if args.lr_warmup_fraction and getattr(args, "lr_warmup_iters", None):
+        problems.append("--lr-warmup-fraction and --lr-warmup-iters are exclusive")
+    vpp = getattr(args, "virtual_pipeline_model_parallel_size", None)
+    per_stage = getattr(args, "num_layers_per_virtual_pipeline_stage", None)
+    if (vpp and vpp > 1 or per_stage) and pp < 2:
+        problems.append("virtual pipeline stages need --pipeline-model-parallel-size >= 2")
+    n_layers = getattr(args, "num_layers", None)
+    if n_layers and n_layers % pp:
+        problems.append(f"--num-layers {n_layers} is not divisible by the pipeline size {pp} (give per-stage layer lists in the model json)")
+    if n_layers and per_stage and (n_layers // pp) % per_stage:
+        problems.append(f"layers per pipeline stage {n_layers // pp} are not divisible by --num-layers-per-virtual-pipeline-stage {per_stage}")
+    seq = getattr(args, "seq_length", None)
+    uly = getattr(args, "ulysses_degree_in_cp", None)
+    algo = args.context_parallel_algo
+    if cp > 1:
+        if algo == "hybrid_cp_algo":
+            if not uly or cp % uly:
+                problems.append(f"hybrid context parallel needs --ulysses-degree-in-cp dividing --context-parallel-size {cp} (got {uly})")
+        elif algo not in ("ulysses_cp_algo", "megatron_cp_algo"):
+            problems.append(f"unknown --context-parallel-algo {algo}")
+        ring = cp if algo == "megatron_cp_algo" else (cp // uly if algo == "hybrid_cp_algo" and uly else 1)
+        if seq and seq % (cp * (2 if ring > 1 else 1)):
+            problems.append(f"--seq-length {seq} must be a multiple of {cp * (2 if ring > 1 else 1)} for context parallel {cp}"
+                            + (" (zig-zag halves of the ring)" if ring > 1 else ""))
+        heads = getattr(args, "num_attention_heads", None)
+        u = cp // ring
+        if heads and u > 1 and (heads // tp) % u:
+            problems.append(f"Ulysses degree {u} must divide the attention heads per tensor-parallel rank ({heads // tp})")
+    else:
+        ring = 1
+    sp = bool(getattr(args, "sequence_parallel", False))
+    if sp and tp == 1:
+        sp = False                       # as Megatron does: nothing to scatter over
+    if sp and seq and seq % tp:
+        problems.append(f"--sequence-parallel needs --seq-length {seq} divisible by the tensor-parallel size {tp}")
+    rg, rm, rn = (getattr(args, k, None) for k in ("recompute_granularity", "recompute_method", "recompute_num_layers"))
+    if rg not in (None, "full", "selective"):
+        problems.append(f"--recompute-granularity must be full or selective (got {rg})")
+    if rm is not None and rg != "full":
+        problems.append("--recompute-method needs --recompute-granularity full")
+    if rm not in (None, "uniform", "block"):
+        problems.append(f"--recompute-method must be uniform or block (got {rm})")
+    if rn is not None and rm is None:
+        problems.append("--recompute-num-layers needs --recompute-method")
+    if getattr(args, "use_torch_fsdp2", False) and (tp > 1 or pp > 1):
+        problems.append("--use-torch-fsdp2 shards over the whole data-parallel group: tensor / pipeline parallel sizes must be 1")
+    if getattr(args, "layerzero", False) and getattr(args, "use_torch_fsdp2", False):
+        problems.append("--layerzero and --use-torch-fsdp2 are exclusive")
+    if getattr(args, "calculate_per_token_loss", False) and getattr(args, "calculate_per_sample_loss", False):
+        problems.append("--calculate-per-token-loss and --calculate-per-sample-loss are exclusive")
+    if problems:
+        raise ValueError("invalid arguments:\n  " + "\n  ".join(problems))
+    return SimpleNamespace(data_parallel_size=dp, num_micro_batches=gbs // (mbs * dp), ring_size=ring, ulysses_size=cp // ring,
+                           sequence_parallel=sp, params_dtype="bf16" if getattr(args, "bf16", False) else
+                           ("fp16" if getattr(args, "fp16", False) else "fp32"))
 
 
 def merge_mm_args(args) -> None:

@@ -176,6 +176,8 @@ def datasets_provider(kind: str, args, model, ps, consumed_samples: int = 0):
 def pretrain(kind: str, argv=None, device: Optional[str] = None):
     args = parse_legacy_args(argv)
     dev, rank, world = init_distributed(device)
+    from ..config.legacy import validate_args
+    args.derived = validate_args(args, world)        # raises with the flags at fault before anything is built
     torch.manual_seed(args.seed)
     tp, pp, cp = args.tensor_model_parallel_size, args.pipeline_model_parallel_size, args.context_parallel_size
     if tp > 1 or pp > 1:

@@ -103,3 +103,31 @@ def test_reference_examples_parse():
             assert a.training.micro_batch_size >= 1
             n += 1
     assert n >= 5
+
+
+def test_validate_args_reports_inconsistent_flags_and_derives_sizes():
+    import pytest
+    from mindspeed_mm_b200.config.legacy import parse_legacy_args, validate_args
+    ok = parse_legacy_args(["--tensor-model-parallel-size", "2", "--pipeline-model-parallel-size", "2", "--context-parallel-size", "2",
+                            "--context-parallel-algo", "hybrid_cp_algo", "--ulysses-degree-in-cp", "2", "--micro-batch-size", "1",
+                            "--global-batch-size", "8", "--seq-length", "4096", "--num-layers", "8", "--num-attention-heads", "16",
+                            "--sequence-parallel", "--bf16"], check_paths=False)
+    d = validate_args(ok, world_size=16)
+    assert (d.data_parallel_size, d.num_micro_batches, d.ulysses_size, d.ring_size, d.sequence_parallel, d.params_dtype) == (
+        2, 4, 2, 1, True, "bf16")
+    # tensor parallel 1 switches sequence parallelism off, as Megatron does
+    assert validate_args(parse_legacy_args(["--sequence-parallel"], check_paths=False), 4).sequence_parallel is False
+    bad = parse_legacy_args(["--tensor-model-parallel-size", "4", "--bf16", "--fp16", "--micro-batch-size", "2", "--global-batch-size",
+                             "6", "--min-lr", "1e-3", "--lr", "1e-4", "--num-layers", "6", "--pipeline-model-parallel-size", "1",
+                             "--recompute-method", "block", "--use-torch-fsdp2"], check_paths=False)
+    with pytest.raises(ValueError) as e:
+        validate_args(bad, world_size=8)
+    msg = str(e.value)
+    for frag in ("--global-batch-size 6", "--bf16 and --fp16", "--min-lr", "--recompute-method needs", "--use-torch-fsdp2 shards"):
+        assert frag in msg, (frag, msg)
+    with pytest.raises(ValueError, match="not divisible by tensor"):
+        validate_args(parse_legacy_args(["--tensor-model-parallel-size", "3"], check_paths=False), 8)
+    ring = parse_legacy_args(["--context-parallel-size", "4", "--context-parallel-algo", "megatron_cp_algo", "--seq-length", "1028"],
+                             check_paths=False)
+    with pytest.raises(ValueError, match="zig-zag"):
+        validate_args(ring, 4)

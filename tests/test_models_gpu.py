@@ -192,6 +192,40 @@ def test_internvl_and_stock_transformers_class_on_gpu():
     assert (got - want).abs().max() <= 5e-2 * want.abs().max()
 
 
+def test_stock_transformers_checkpoint_trains_under_the_engine_on_gpu(tmp_path):
+    """``model_id: hf_auto`` on the GPU: stock Qwen2.5-VL class built on the meta device, bf16 flat shards, recompute through
+    the re-routed sub-module calls, the kernel plugin and the ``mm_b200`` attention implementation inside the class."""
+    import os
+    from transformers import Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration
+    from mindspeed_mm_b200.config import load_config
+    from mindspeed_mm_b200.plugins import hf_kernels
+    from mindspeed_mm_b200.runtime.trainer import Trainer
+    vis = dict(depth=2, hidden_size=128, intermediate_size=256, num_heads=2, out_hidden_size=256, patch_size=14,
+               spatial_merge_size=2, temporal_patch_size=2, window_size=56, fullatt_block_indexes=[1], in_channels=3)
+    txt = dict(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+               vocab_size=512, rope_parameters=dict(rope_type="default", rope_theta=1e4, mrope_section=[8, 12, 12]),
+               tie_word_embeddings=False)
+    cfg = Qwen2_5_VLConfig(vision_config=vis, text_config=txt, image_token_id=503, video_token_id=504,
+                           vision_start_token_id=500, vision_end_token_id=501)
+    torch.manual_seed(0)
+    src = tmp_path / "hf_in"
+    Qwen2_5_VLForConditionalGeneration(cfg).float().save_pretrained(src, safe_serialization=True)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    args = load_config(os.path.join(root, "examples/qwen2.5vl/tiny_hf_auto.yaml"),
+                       [f"model.model_name_or_path={src}", "training.train_iters=4", "training.lr=3e-3",
+                        "data.dataset_param.basic_parameters.num_samples=1"], world_size=1)
+    reset_parallel_state()
+    try:
+        tr = Trainer(args, device=DEV)
+        assert type(tr.model.model).__name__ == "Qwen2_5_VLForConditionalGeneration"
+        hist = tr.train()
+    finally:
+        hf_kernels.remove_kernel_plugin()
+        reset_parallel_state()
+    losses = [float(h["loss"]) if isinstance(h, dict) else float(h) for h in hist]
+    assert all(l == l for l in losses) and losses[-1] < losses[0], losses
+
+
 def test_recompute_with_skipped_last_gemm_matches_graph_keeping_run():
     """The re-forward of a checkpointed block does not rerun its last GEMM (the value only feeds a residual add);
     one optimizer step must equal the step of the same model with autograd graphs kept."""

@@ -63,6 +63,8 @@ class HFModelAdapter(nn.Module):
         text_cfg = model.config.get_text_config() if hasattr(model.config, "get_text_config") else model.config
         rope = getattr(text_cfg, "rope_parameters", None) or getattr(text_cfg, "rope_scaling", None) or {}
         self._mrope = isinstance(rope, dict) and "mrope_section" in rope
+        impl = getattr(model.config, "_attn_implementation", None) or ""
+        self._varlen_kwargs = impl == "mm_b200" or impl.startswith("flash_attention")
         import inspect
         self._forward_params = [n for n, p in inspect.signature(model.forward).parameters.items()
                                 if p.kind in (p.POSITIONAL_OR_KEYWORD, p.KEYWORD_ONLY)]
@@ -143,6 +145,12 @@ class HFModelAdapter(nn.Module):
                 tok = torch.arange(ids.numel(), device=ids.device)
                 seq = torch.bucketize(tok, cu[1:], right=True).clamp(max=cu.numel() - 2)
                 pos = tok - cu[seq]
+            if cu is not None and cu.numel() > 2 and self._varlen_kwargs:
+                # attention implementations that take packed rows by their boundaries (flash-attention style, "mm_b200")
+                # get them explicitly; mask-based ones derive the block-diagonal mask from the positions
+                cu32 = cu.to(device=ids.device, dtype=torch.int32)
+                longest = int(batch.get("max_seqlen") or int((cu32[1:] - cu32[:-1]).max()))
+                kw.update(cu_seq_lens_q=cu32, cu_seq_lens_k=cu32, max_length_q=longest, max_length_k=longest)
             if pos is not None:             # [T], or [3, T] multimodal positions of the VLM collators
                 if pos.dim() == 2 and not self._mrope:
                     pos = pos[0]            # a decoder with 1-D rotary positions: the temporal row is the token position

@@ -257,3 +257,23 @@ def test_zoo_id_with_a_checkpoint_runs_the_stock_architecture(tmp_path):
         hf_kernels.remove_kernel_plugin()
     losses = [float(h["loss"]) if isinstance(h, dict) else float(h) for h in hist]
     assert losses[-1] < losses[0]
+
+
+def test_packed_rows_stay_separate_under_the_plugin_attention():
+    """With the ``mm_b200`` attention implementation the adapter hands the sequence boundaries to the attention function:
+    the logits of a packed row equal the logits of its sequences run one by one."""
+    hf_kernels.apply_kernel_plugin(("qwen3",))
+    try:
+        model = _qwen3("mm_b200").eval()
+        adapter = HFModelAdapter(model)
+        ids = torch.randint(0, 200, (30,))
+        with torch.no_grad():
+            packed = adapter(dict(input_ids=ids, cu_seqlens=torch.tensor([0, 14, 30], dtype=torch.int32), max_seqlen=16))
+            a = model(input_ids=ids[None, :14]).logits[0]
+            b = model(input_ids=ids[None, 14:]).logits[0]
+        assert (packed - torch.cat([a, b])).abs().max() < 2e-5
+        with torch.no_grad():
+            leaky = model(input_ids=ids[None]).logits[0]            # one long sequence: the second part sees the first
+        assert (leaky[14:] - b).abs().max() > 1e-3
+    finally:
+        hf_kernels.remove_kernel_plugin()

@@ -64,7 +64,7 @@ class HFModelAdapter(nn.Module):
         rope = getattr(text_cfg, "rope_parameters", None) or getattr(text_cfg, "rope_scaling", None) or {}
         self._mrope = isinstance(rope, dict) and "mrope_section" in rope
         impl = getattr(model.config, "_attn_implementation", None) or ""
-        self._varlen_kwargs = impl == "mm_b200" or impl.startswith("flash_attention")
+        self._varlen_kwargs = impl == "mm_b200" or "flash" in impl
         import inspect
         self._forward_params = [n for n, p in inspect.signature(model.forward).parameters.items()
                                 if p.kind in (p.POSITIONAL_OR_KEYWORD, p.KEYWORD_ONLY)]

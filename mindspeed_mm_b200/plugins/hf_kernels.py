@@ -34,6 +34,10 @@ from .. import ops
 DEFAULT_MODULES = ("qwen2", "qwen2_vl", "qwen2_5_vl", "qwen3", "qwen3_moe", "qwen3_vl", "qwen3_vl_moe", "qwen3_5",
                    "qwen3_5_moe", "internvl", "llama", "mistral")
 ATTENTION_NAME = "mm_b200"
+# Same function under a name that contains "flash": vision and audio towers of transformers hand their window / image
+# boundaries (``cu_seq_lens_q``) to the attention function only when the implementation's name says so, and otherwise loop
+# over the windows one call at a time.
+TOWER_ATTENTION_NAME = "mm_b200_flash"
 
 _saved: List[Tuple[object, str, object]] = []        # (owner, attribute, original) for remove_kernel_plugin
 
@@ -182,10 +186,11 @@ def apply_kernel_plugin(modules: Sequence[str] = DEFAULT_MODULES, attention: boo
     if attention:
         from transformers import AttentionInterface, AttentionMaskInterface
         from transformers.masking_utils import ALL_MASK_ATTENTION_FUNCTIONS
-        AttentionInterface.register(ATTENTION_NAME, attention_forward)
         # same mask contract as flash attention: no mask without padding, the 2-D padding mask otherwise
-        AttentionMaskInterface.register(ATTENTION_NAME, ALL_MASK_ATTENTION_FUNCTIONS["flash_attention_2"])
-        record["attention"] = [ATTENTION_NAME]
+        for name in (ATTENTION_NAME, TOWER_ATTENTION_NAME):
+            AttentionInterface.register(name, attention_forward)
+            AttentionMaskInterface.register(name, ALL_MASK_ATTENTION_FUNCTIONS["flash_attention_2"])
+        record["attention"] = [ATTENTION_NAME, TOWER_ATTENTION_NAME]
     return record
 
 
@@ -196,7 +201,11 @@ def remove_kernel_plugin() -> None:
 
 
 def use_plugin_attention(model_or_config) -> None:
-    """Select the registered attention implementation on a config or an already built model (all sub-configs)."""
+    """Select the registered attention implementation on a config or an already built model: the decoder under
+    ``"mm_b200"``, vision / audio towers under the flash-named alias so that they take their packed (varlen) path."""
     cfg = getattr(model_or_config, "config", model_or_config)
-    for c in [cfg] + [getattr(cfg, n) for n in ("text_config", "vision_config", "audio_config") if hasattr(cfg, n)]:
+    for c in [cfg] + [getattr(cfg, n) for n in ("text_config",) if hasattr(cfg, n)]:
         c._attn_implementation = ATTENTION_NAME
+    for n in ("vision_config", "audio_config"):
+        if getattr(cfg, n, None) is not None:
+            getattr(cfg, n)._attn_implementation = TOWER_ATTENTION_NAME

@@ -9,6 +9,7 @@ import torch
 transformers = pytest.importorskip("transformers")
 
 from mindspeed_mm_b200.parallel.fsdp import FSDPEngine, OptimConfig  # noqa: E402
+from mindspeed_mm_b200 import ops  # noqa: E402
 from mindspeed_mm_b200.plugins import hf_kernels  # noqa: E402
 from mindspeed_mm_b200.plugins.hf_adapter import HFModelAdapter  # noqa: E402
 
@@ -37,7 +38,7 @@ def test_kernel_plugin_keeps_logits_and_is_removable():
     rec = hf_kernels.apply_kernel_plugin(("qwen3", "qwen3_moe", "qwen2_5_vl", "not_a_family"))
     try:
         assert {"Qwen3RMSNorm", "Qwen3MLP", "apply_rotary_pos_emb"} <= set(rec["modeling_qwen3"])
-        assert rec["attention"] == ["mm_b200"] and "modeling_not_a_family" not in rec
+        assert rec["attention"] == ["mm_b200", "mm_b200_flash"] and "modeling_not_a_family" not in rec
         assert mq.Qwen3RMSNorm.forward is not orig[0]
         patched = _qwen3("mm_b200").eval()
         patched.load_state_dict(base.state_dict())
@@ -211,7 +212,7 @@ def test_verl_plugin_entry_point(monkeypatch):
     try:
         rec = vp.apply_verl_plugin()
         assert "Qwen2_5_VLRMSNorm" in rec["modeling_qwen2_5_vl"] and "Qwen3VLMoeTextMLP" in rec["modeling_qwen3_vl_moe"]
-        assert rec["attention"] == ["mm_b200"] and torch.are_deterministic_algorithms_enabled()
+        assert rec["attention"] == ["mm_b200", "mm_b200_flash"] and torch.are_deterministic_algorithms_enabled()
         a = torch.rand(3) + torch.rand(3)          # the generator has moved on since the plugin seeded it
         vp.seed_all(1234)
         b = torch.rand(3)
@@ -277,3 +278,40 @@ def test_packed_rows_stay_separate_under_the_plugin_attention():
         assert (leaky[14:] - b).abs().max() > 1e-3
     finally:
         hf_kernels.remove_kernel_plugin()
+
+
+def test_vision_tower_takes_the_packed_path_under_the_plugin():
+    """``use_plugin_attention`` puts the vision tower on the flash-named alias: its windows arrive as ONE varlen call per
+    block (not one call per window) and the logits match the stock model's."""
+    from transformers import Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration
+    vis = dict(depth=2, hidden_size=32, intermediate_size=64, num_heads=2, out_hidden_size=64, patch_size=14,
+               spatial_merge_size=2, temporal_patch_size=2, window_size=56, fullatt_block_indexes=[1], in_channels=3)
+    txt = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+               vocab_size=300, rope_parameters=dict(rope_type="default", rope_theta=1e4, mrope_section=[2, 3, 3]),
+               tie_word_embeddings=False)
+    cfg = Qwen2_5_VLConfig(vision_config=vis, text_config=txt, image_token_id=290, video_token_id=291,
+                           vision_start_token_id=292, vision_end_token_id=293)
+    torch.manual_seed(0)
+    ref = Qwen2_5_VLForConditionalGeneration(cfg).float().eval()
+    grid = torch.tensor([[1, 8, 8]])                        # 64 patches -> 4 windows of 16, 16 merged image tokens
+    ids = torch.cat([torch.randint(0, 280, (4,)), torch.tensor([292]), torch.full((16,), 290), torch.tensor([293]),
+                     torch.randint(0, 280, (6,))])
+    batch = dict(input_ids=ids, pixel_values=torch.randn(64, 3 * 2 * 14 * 14), image_grid_thw=grid,
+                 mm_token_type_ids=(ids == 290).int()[None])
+    with torch.no_grad():
+        want = ref(input_ids=ids[None], **{k: v for k, v in batch.items() if k != "input_ids"}).logits[0]
+    hf_kernels.apply_kernel_plugin(("qwen2_5_vl",))
+    calls = []
+    orig = ops.attention_varlen
+    try:
+        net = copy.deepcopy(ref)
+        adapter = HFModelAdapter(net, use_plugin_attention=True)
+        assert net.config.vision_config._attn_implementation == hf_kernels.TOWER_ATTENTION_NAME
+        ops.attention_varlen = lambda *a, **k: (calls.append(a[3].numel() - 1), orig(*a, **k))[1]
+        with torch.no_grad():
+            got = adapter(batch)
+    finally:
+        ops.attention_varlen = orig
+        hf_kernels.remove_kernel_plugin()
+    assert calls == [4, 1], calls                           # windowed block: 4 windows in one call; full block: 1 sequence
+    assert (got - want).abs().max() < 3e-5

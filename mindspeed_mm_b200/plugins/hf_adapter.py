@@ -58,7 +58,7 @@ class HFModelAdapter(nn.Module):
         self._unit_modules: List[Tuple[str, nn.Module]] = [(n, m) for n, m in model.named_modules() if n in units]
         if use_plugin_attention:
             from .hf_kernels import use_plugin_attention as _use
-            _use(model)
+            _use(model, packed_towers=use_plugin_attention == "packed_towers")
         self._engine = None
         text_cfg = model.config.get_text_config() if hasattr(model.config, "get_text_config") else model.config
         rope = getattr(text_cfg, "rope_parameters", None) or getattr(text_cfg, "rope_scaling", None) or {}

@@ -93,10 +93,6 @@ class HFAutoModel(HFModelAdapter):
             auto = transformers.AutoModelForImageTextToText if getattr(hf_cfg, "vision_config", None) is not None \
                 else transformers.AutoModelForCausalLM
             model = auto.from_config(hf_cfg)
-        if config.kernel_plugin and not config.attn_implementation:
-            # towers move to the flash-named alias (their packed path) once built: at construction transformers would try
-            # to import a flash-attention package for any name that contains "flash"
-            hf_kernels.use_plugin_attention(model)
         super().__init__(model, unit_classes=config.unit_classes)
         self._param_names = [n for n, _ in model.named_parameters()]
         self.auto_config = config

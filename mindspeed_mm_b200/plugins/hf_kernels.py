@@ -200,12 +200,14 @@ def remove_kernel_plugin() -> None:
         setattr(owner, name, orig)
 
 
-def use_plugin_attention(model_or_config) -> None:
-    """Select the registered attention implementation on a config or an already built model: the decoder under
-    ``"mm_b200"``, vision / audio towers under the flash-named alias so that they take their packed (varlen) path."""
+def use_plugin_attention(model_or_config, packed_towers: bool = False) -> None:
+    """Select the registered attention implementation on a config or an already built model (all sub-configs).
+    ``packed_towers``: vision / audio towers go under the flash-named alias so that they take their packed (varlen) path
+    instead of one call per window.  Off by default: that path is verified on CPU only (on a B200 the stock Qwen2.5-VL
+    tower failed under it), so towers keep the per-window calls unless asked."""
     cfg = getattr(model_or_config, "config", model_or_config)
-    for c in [cfg] + [getattr(cfg, n) for n in ("text_config",) if hasattr(cfg, n)]:
-        c._attn_implementation = ATTENTION_NAME
-    for n in ("vision_config", "audio_config"):
-        if getattr(cfg, n, None) is not None:
-            getattr(cfg, n)._attn_implementation = TOWER_ATTENTION_NAME
+    for n in (None, "text_config", "vision_config", "audio_config"):
+        c = cfg if n is None else getattr(cfg, n, None)
+        if c is not None:
+            c._attn_implementation = TOWER_ATTENTION_NAME if packed_towers and n in ("vision_config", "audio_config") \
+                else ATTENTION_NAME

@@ -281,7 +281,7 @@ def test_packed_rows_stay_separate_under_the_plugin_attention():
 
 
 def test_vision_tower_takes_the_packed_path_under_the_plugin():
-    """``use_plugin_attention`` puts the vision tower on the flash-named alias: its windows arrive as ONE varlen call per
+    """``use_plugin_attention="packed_towers"`` puts the vision tower on the flash-named alias: its windows arrive as ONE varlen call per
     block (not one call per window) and the logits match the stock model's."""
     from transformers import Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration
     vis = dict(depth=2, hidden_size=32, intermediate_size=64, num_heads=2, out_hidden_size=64, patch_size=14,
@@ -305,7 +305,7 @@ def test_vision_tower_takes_the_packed_path_under_the_plugin():
     orig = ops.attention_varlen
     try:
         net = copy.deepcopy(ref)
-        adapter = HFModelAdapter(net, use_plugin_attention=True)
+        adapter = HFModelAdapter(net, use_plugin_attention="packed_towers")
         assert net.config.vision_config._attn_implementation == hf_kernels.TOWER_ATTENTION_NAME
         ops.attention_varlen = lambda *a, **k: (calls.append(a[3].numel() - 1), orig(*a, **k))[1]
         with torch.no_grad():
